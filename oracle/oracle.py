@@ -1,0 +1,332 @@
+"""Python driver of the CPU oracle -- TEST INFRASTRUCTURE ONLY.
+
+Walks a `thnets_b200.fixtures.Graph` and evaluates it with the C restatement in
+`liboracle.so` (oracle_fp32.c / oracle_lowp.c), the way the reference's executor
+would: THProcessFloat normalisation (thapi.c:396-403), then one operator per
+node.  `run_lowp` follows the reference's int8 route: THMakeSpatial
+(thapi.c:642-690) then THLowp_ToLowp (lowp/lowp_basic.c:133-212), applied per image.
+
+Only tests/, the smoke check and the benchmark's CPU-baseline leg import this.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB = os.path.join(_HERE, "liboracle.so")
+REF_DIR = os.path.join(_HERE, "_ref")
+
+_f = C.POINTER(C.c_float)
+_u8 = C.POINTER(C.c_ubyte)
+
+
+def build(ref_root="/root/reference"):
+    """Compile the C restatement and, when the reference tree is present, the reference itself."""
+    subprocess.check_call(["make", "-s", "-C", _HERE, "port"])
+    if os.path.isdir(ref_root):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "reflowp", f"REF={ref_root}"])
+
+
+def ref_lib(kind="auto"):
+    """Path of a compiled reference library, or None when it was never built."""
+    if kind == "auto":
+        try:
+            flags = open("/proc/cpuinfo").read()
+        except OSError:
+            flags = ""
+        kind = "haswell" if (" avx2" in flags and " fma" in flags) else "penryn"
+    p = os.path.join(REF_DIR, f"libthnets_ref_{kind}.so")
+    return p if os.path.exists(p) else None
+
+
+def _fp(a):
+    return a.ctypes.data_as(_f)
+
+
+def _up(a):
+    return a.ctypes.data_as(_u8)
+
+
+class Oracle:
+    def __init__(self):
+        if not os.path.exists(LIB):
+            build()
+        self.lib = lib = C.CDLL(LIB)
+        lib.orc_conv_out.restype = C.c_int
+        lib.orc_pool_out.restype = C.c_int
+        lib.orc_exp_minus_approx.restype = C.c_double
+        lib.orc_exp_minus_approx.argtypes = [C.c_double]
+        lib.orc_lowp_scale_float.restype = C.c_ubyte
+        lib.orc_lowp_scale_float.argtypes = [C.c_float, C.c_float, C.c_float]
+        lib.orc_lowp_requant.restype = C.c_ubyte
+        lib.orc_batchnorm.argtypes = [_f, C.c_int, C.c_int, C.c_int, _f, _f, _f, _f, C.c_double, _f]
+        lib.orc_threshold.argtypes = [_f, C.c_long, C.c_float, C.c_float, C.c_float, _f]
+        lib.orc_lowp_gemm_params.argtypes = [C.c_float] * 6 + [C.POINTER(C.c_int)] * 5
+        lib.orc_lowp_conv.argtypes = [_u8, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float,
+                                      _u8, C.c_float, C.c_float, _u8, C.c_float, C.c_float] + \
+                                     [C.c_int] * 7 + [C.c_float, C.c_float, _u8]
+        lib.orc_lowp_dequantize.argtypes = [_u8, C.c_long, C.c_float, C.c_float, _f]
+        lib.orc_lowp_quantize.argtypes = [_f, C.c_long, _u8, _f, _f]
+        lib.orc_lowp_threshold.argtypes = [_u8, C.c_long, C.c_ubyte, C.c_ubyte, _u8]
+
+    # ---- fp32 operators on NCHW arrays ---------------------------------------
+    def conv2d(self, x, w, b, stride, pad):
+        n, c, h, ww = x.shape
+        co, _, kh, kw = w.shape
+        oh = self.lib.orc_conv_out(h, kh, stride[0], pad[0])
+        ow = self.lib.orc_conv_out(ww, kw, stride[1], pad[1])
+        y = np.empty((n, co, oh, ow), np.float32)
+        x = np.ascontiguousarray(x, np.float32)
+        w = np.ascontiguousarray(w, np.float32)
+        self.lib.orc_conv2d(_fp(x), n, c, h, ww, _fp(w), _fp(b) if b is not None else None, co, kh, kw,
+                            stride[0], stride[1], pad[0], pad[1], _fp(y))
+        return y
+
+    def fullconv2d(self, x, w, b, stride, pad, adj, strict_bias=0):
+        n, c, h, ww = x.shape
+        _, co, kh, kw = w.shape
+        oh = (h - 1) * stride[0] - 2 * pad[0] + kh + adj[0]
+        ow = (ww - 1) * stride[1] - 2 * pad[1] + kw + adj[1]
+        y = np.empty((n, co, oh, ow), np.float32)
+        x = np.ascontiguousarray(x, np.float32)
+        w = np.ascontiguousarray(w, np.float32)
+        self.lib.orc_fullconv2d(_fp(x), n, c, h, ww, _fp(w), _fp(b) if b is not None else None, co, kh, kw,
+                                stride[0], stride[1], pad[0], pad[1], adj[0], adj[1], strict_bias, _fp(y))
+        return y
+
+    def linear(self, x, w, b):
+        n, k = x.shape
+        m = w.shape[0]
+        y = np.empty((n, m), np.float32)
+        x = np.ascontiguousarray(x, np.float32)
+        w = np.ascontiguousarray(w, np.float32)
+        self.lib.orc_linear(_fp(x), n, k, _fp(w), _fp(b) if b is not None else None, m, _fp(y))
+        return y
+
+    def batchnorm(self, x, gamma, beta, mean, var, eps):
+        n, c = x.shape[:2]
+        hw = int(np.prod(x.shape[2:]))
+        y = np.empty_like(x)
+        x = np.ascontiguousarray(x, np.float32)
+        self.lib.orc_batchnorm(_fp(x), n, c, hw, _fp(mean), _fp(var), _fp(gamma) if gamma is not None else None,
+                               _fp(beta) if beta is not None else None, eps, _fp(y))
+        return y
+
+    def threshold(self, x, th=0.0, val=0.0, alpha=0.0):
+        x = np.ascontiguousarray(x, np.float32)
+        y = np.empty_like(x)
+        self.lib.orc_threshold(_fp(x), x.size, th, val, alpha, _fp(y))
+        return y
+
+    def prelu(self, x, w, nplanes):
+        x = np.ascontiguousarray(x, np.float32)
+        y = np.empty_like(x)
+        n, c = x.shape[:2]
+        self.lib.orc_prelu(_fp(x), n, c, int(np.prod(x.shape[2:])), _fp(w), nplanes, _fp(y))
+        return y
+
+    def maxpool(self, x, k, stride, pad, ceil_mode=0):
+        n, c, h, w = x.shape
+        oh = self.lib.orc_pool_out(h, k[0], stride[0], pad[0], ceil_mode)
+        ow = self.lib.orc_pool_out(w, k[1], stride[1], pad[1], ceil_mode)
+        x = np.ascontiguousarray(x, np.float32)
+        y = np.empty((n, c, oh, ow), np.float32)
+        self.lib.orc_maxpool(_fp(x), n, c, h, w, k[0], k[1], stride[0], stride[1], pad[0], pad[1], ceil_mode, _fp(y))
+        return y
+
+    def avgpool(self, x, k, stride, pad, ceil_mode=0, count_include_pad=0):
+        n, c, h, w = x.shape
+        kh, kw = (k[0] or h), (k[1] or w)
+        oh = self.lib.orc_pool_out(h, kh, stride[0], pad[0], ceil_mode)
+        ow = self.lib.orc_pool_out(w, kw, stride[1], pad[1], ceil_mode)
+        x = np.ascontiguousarray(x, np.float32)
+        y = np.empty((n, c, oh, ow), np.float32)
+        self.lib.orc_avgpool(_fp(x), n, c, h, w, k[0], k[1], stride[0], stride[1], pad[0], pad[1], ceil_mode,
+                             count_include_pad, _fp(y))
+        return y
+
+    def softmax(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        y = np.empty_like(x)
+        if x.ndim == 2:
+            self.lib.orc_softmax(_fp(x), x.shape[0], x.shape[1], 1, _fp(y))
+        else:
+            self.lib.orc_softmax(_fp(x), x.shape[0], x.shape[1], int(np.prod(x.shape[2:])), _fp(y))
+        return y
+
+    def caddtable(self, ins, is_csub=0):
+        ins = [np.ascontiguousarray(i, np.float32) for i in ins]
+        y = np.empty_like(ins[0])
+        ptrs = (_f * len(ins))(*[_fp(i) for i in ins])
+        ns = (C.c_long * len(ins))(*[i.size for i in ins])
+        self.lib.orc_caddtable(ptrs, ns, len(ins), is_csub, _fp(y))
+        return y
+
+    def join(self, ins):
+        ins = [np.ascontiguousarray(i, np.float32) for i in ins]
+        n = ins[0].shape[0]
+        hw = int(np.prod(ins[0].shape[2:]))
+        cs = (C.c_int * len(ins))(*[i.shape[1] for i in ins])
+        y = np.empty((n, sum(i.shape[1] for i in ins)) + ins[0].shape[2:], np.float32)
+        ptrs = (_f * len(ins))(*[_fp(i) for i in ins])
+        self.lib.orc_join_channels(ptrs, cs, len(ins), n, hw, _fp(y))
+        return y
+
+    def normalize(self, x, mean, std):
+        x = np.array(x, np.float32, order="C", copy=True)
+        n, c, h, w = x.shape
+        mean = np.asarray(mean, np.float32)
+        std = np.asarray(std, np.float32)
+        self.lib.orc_normalize(_fp(x), n, c, h, w, _fp(mean), _fp(std))
+        return x
+
+    # ---- graph execution -------------------------------------------------------
+    def run(self, graph, batch, keep=False, strict_bias=0):
+        """fp32 forward of `graph` on a raw [N,C,H,W] batch (normalised here first)."""
+        vals = {0: self.normalize(batch, graph.mean, graph.std)}
+        for i, node in enumerate(graph.nodes):
+            if i == 0:
+                continue
+            a = node.attrs
+            ts = [t for _, t in node.tensors]
+            xin = [vals[j] for j in node.inputs]
+            x = xin[0]
+            if node.op == "conv":
+                y = self.conv2d(x, ts[0], ts[1] if len(ts) > 1 else None, a["stride"], a["padding"])
+            elif node.op == "deconv":
+                y = self.fullconv2d(x, ts[0], ts[1] if len(ts) > 1 else None, a["stride"], a["padding"],
+                                    a["output_padding"], strict_bias)
+            elif node.op == "linear":
+                y = self.linear(x.reshape(x.shape[0], -1), ts[0], ts[1])
+            elif node.op == "bn":
+                y = self.batchnorm(x, ts[0], ts[1], ts[2], ts[3], a["eps"])
+            elif node.op == "threshold":
+                y = self.threshold(x, a["threshold"], a["value"])
+            elif node.op == "maxpool":
+                y = self.maxpool(x, a["kernel_size"], a["stride"], a["padding"], a["ceil_mode"])
+            elif node.op == "avgpool":
+                y = self.avgpool(x, a["kernel_size"], a["stride"], a["padding"], a["ceil_mode"])
+            elif node.op == "view":
+                y = x.reshape(-1, a["sizes"][1])
+            elif node.op == "dropout":
+                y = x
+            elif node.op == "softmax":
+                y = self.softmax(x)
+            elif node.op == "add":
+                y = self.caddtable(xin)
+            elif node.op == "concat":
+                y = self.join(xin)
+            else:
+                raise ValueError(node.op)
+            vals[i] = y
+        return vals if keep else vals[graph.output]
+
+    # ---- lowp ----------------------------------------------------------------
+    def lowp_quantize(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        q = np.empty(x.shape, np.uint8)
+        sub, mult = C.c_float(), C.c_float()
+        self.lib.orc_lowp_quantize(_fp(x), x.size, _up(q), C.byref(sub), C.byref(mult))
+        return q, sub.value, mult.value
+
+    def lowp_dequantize(self, q, sub, mult):
+        q = np.ascontiguousarray(q, np.uint8)
+        x = np.empty(q.shape, np.float32)
+        self.lib.orc_lowp_dequantize(_up(q), q.size, sub, mult, _fp(x))
+        return x
+
+    def lowp_gemm_params(self, w_sub, w_mult, in_sub, in_mult, out_sub, out_mult):
+        v = [C.c_int() for _ in range(5)]
+        self.lib.orc_lowp_gemm_params(w_sub, w_mult, in_sub, in_mult, out_sub, out_mult, *[C.byref(i) for i in v])
+        return tuple(i.value for i in v)  # a_offset, b_offset, c_offset, c_mult, c_shift
+
+    def lowp_conv(self, xq, in_sub, in_mult, wq, w_sub, w_mult, bq, b_sub, b_mult, stride, pad, out_sub, out_mult):
+        n, c, h, w = xq.shape
+        co, _, kh, kw = wq.shape
+        oh = self.lib.orc_conv_out(h, kh, stride[0], pad[0])
+        ow = self.lib.orc_conv_out(w, kw, stride[1], pad[1])
+        y = np.empty((n, co, oh, ow), np.uint8)
+        xq, wq, bq = (np.ascontiguousarray(t, np.uint8) for t in (xq, wq, bq))
+        self.lib.orc_lowp_conv(_up(xq), n, c, h, w, in_sub, in_mult, _up(wq), w_sub, w_mult, _up(bq), b_sub, b_mult,
+                               co, kh, kw, stride[0], stride[1], pad[0], pad[1], out_sub, out_mult, _up(y))
+        return y
+
+    def lowp_conv_acc(self, xq, wq, stride, pad, zero, a_off, b_off):
+        """int32 accumulators of ONE image [C,H,W] -> [Cout, oH, oW]."""
+        c, h, w = xq.shape
+        co, _, kh, kw = wq.shape
+        oh = self.lib.orc_conv_out(h, kh, stride[0], pad[0])
+        ow = self.lib.orc_conv_out(w, kw, stride[1], pad[1])
+        acc = np.empty((co, oh, ow), np.int32)
+        xq, wq = np.ascontiguousarray(xq, np.uint8), np.ascontiguousarray(wq, np.uint8)
+        self.lib.orc_lowp_conv_acc(_up(xq), c, h, w, _up(wq), co, kh, kw, stride[0], stride[1], pad[0], pad[1],
+                                   int(zero), int(a_off), int(b_off), acc.ctypes.data_as(C.POINTER(C.c_int)))
+        return acc
+
+    def lowp_maxpool(self, xq, k, stride, pad, ceil_mode=0):
+        n, c, h, w = xq.shape
+        oh = self.lib.orc_pool_out(h, k[0], stride[0], pad[0], ceil_mode)
+        ow = self.lib.orc_pool_out(w, k[1], stride[1], pad[1], ceil_mode)
+        xq = np.ascontiguousarray(xq, np.uint8)
+        y = np.empty((n, c, oh, ow), np.uint8)
+        self.lib.orc_lowp_maxpool(_up(xq), n, c, h, w, k[0], k[1], stride[0], stride[1], pad[0], pad[1], ceil_mode,
+                                  _up(y))
+        return y
+
+    def lowp_threshold(self, xq, sub, mult, th, val):
+        t = self.lib.orc_lowp_scale_float(sub, mult, th)
+        v = self.lib.orc_lowp_scale_float(sub, mult, val)
+        xq = np.ascontiguousarray(xq, np.uint8)
+        y = np.empty_like(xq)
+        self.lib.orc_lowp_threshold(_up(xq), xq.size, t, v, _up(y))
+        return y
+
+    def run_lowp(self, graph, batch, rng, spatial_size, keep=False):
+        """uint8 forward of a sequential conv/linear/relu/maxpool graph.
+
+        The input is quantised over the WHOLE batch tensor (lowp_basic.c:15-35); every
+        module output uses sub = -range/2, mult = 255/range (lowp_basic.c:137-148); the
+        convolution runs per image.  View nodes vanish and Linear nodes become k x k
+        convolutions exactly as THMakeSpatial does.
+        """
+        x = self.normalize(batch, graph.mean, graph.std)
+        q, sub, mult = self.lowp_quantize(x)
+        osub, omult = np.float32(-rng / 2), np.float32(np.float32(255) / np.float32(rng))
+        size = spatial_size
+        vals = {0: (q, sub, mult)}
+        cur = (q, sub, mult)
+        for i, node in enumerate(graph.nodes):
+            if i == 0:
+                continue
+            a = node.attrs
+            ts = [t for _, t in node.tensors]
+            q, sub, mult = cur
+            if node.op in ("conv", "linear"):
+                w, b = ts[0], ts[1]
+                if node.op == "linear":
+                    cin = q.shape[1]
+                    k = int(round((w.shape[1] / cin) ** 0.5))
+                    w = w.reshape(w.shape[0], cin, k, k)
+                    stride, pad = (1, 1), (0, 0)
+                else:
+                    stride, pad = a["stride"], a["padding"]
+                wq, wsub, wmult = self.lowp_quantize(w)
+                bq, bsub, bmult = self.lowp_quantize(b)
+                y = self.lowp_conv(q, sub, mult, wq, wsub, wmult, bq, bsub, bmult, stride, pad, float(osub), float(omult))
+                cur = (y, float(osub), float(omult))
+            elif node.op == "threshold":
+                cur = (self.lowp_threshold(q, sub, mult, a["threshold"], a["value"]), sub, mult)
+            elif node.op == "maxpool":
+                cur = (self.lowp_maxpool(q, a["kernel_size"], a["stride"], a["padding"], a["ceil_mode"]), sub, mult)
+            elif node.op in ("view", "dropout"):
+                pass
+            else:
+                raise ValueError("lowp engine has no " + node.op)
+            vals[i] = cur
+        _ = size
+        out = self.lowp_dequantize(*cur)
+        return (out, vals) if keep else out

@@ -1,0 +1,511 @@
+"""Seeded synthetic networks and the two on-disk formats thnets loads them from.
+
+A `Graph` is a small DAG description (conv, deconv, linear, bn, pools, threshold,
+view, add, concat, softmax ...) with NumPy weights.  It can be written as
+
+* a "PyTorch Graph Dump 1.00" file (`write_pymodel`), the format parsed by the
+  reference's pytorch.c:151-299: the root element is the network OUTPUT, inputs are
+  nested depth-first, a tensor with a second consumer is written as a type-7 id
+  reference (thexport.py:130-137);
+* a Torch7 directory `model.net` + `stat.t7` (`write_torch7`), the binary
+  serialisation parsed by thload.c:119-406 (only purely sequential graphs).
+
+The builders at the bottom reproduce the five benchmark architectures with
+He-normal weights drawn in layer order (weight, then bias) from
+`numpy.random.default_rng(seed)`; `width`/`size` arguments shrink them for tests.
+No dataset and no trained weights are involved anywhere.
+"""
+from __future__ import annotations
+
+import os
+import struct
+from dataclasses import dataclass, field
+
+import numpy as np
+
+
+@dataclass
+class Node:
+    op: str
+    inputs: list
+    attrs: dict = field(default_factory=dict)
+    tensors: list = field(default_factory=list)  # [(name, ndarray)], '' = positional
+
+
+class Graph:
+    """DAG under construction; node 0 is always the network input."""
+
+    def __init__(self, seed=0, mean=(0.0, 0.0, 0.0), std=(1.0, 1.0, 1.0)):
+        self.rng = np.random.default_rng(seed)
+        self.nodes = [Node("input", [])]
+        self.output = 0
+        self.mean = np.asarray(mean, np.float32)
+        self.std = np.asarray(std, np.float32)
+        self.input_shape = None  # (C, H, W)
+        self.input_dist = "normal"
+
+    # ---- helpers -------------------------------------------------------------
+    def _add(self, op, inputs, attrs=None, tensors=None):
+        self.nodes.append(Node(op, list(inputs), attrs or {}, tensors or []))
+        self.output = len(self.nodes) - 1
+        return self.output
+
+    def he(self, shape, fan_in):
+        return (self.rng.standard_normal(shape) * np.sqrt(2.0 / fan_in)).astype(np.float32)
+
+    # ---- layers --------------------------------------------------------------
+    def conv(self, x, cin, cout, k, stride=1, pad=0, bias="zero"):
+        kh, kw = (k, k) if isinstance(k, int) else k
+        w = self.he((cout, cin, kh, kw), cin * kh * kw)
+        t = [("", w)]
+        b = self._bias(bias, cout)
+        if b is not None:
+            t.append(("", b))
+        return self._add("conv", [x], dict(stride=(stride, stride), padding=(pad, pad)), t)
+
+    def deconv(self, x, cin, cout, k, stride=1, pad=0, adj=0, bias=None):
+        w = self.he((cin, cout, k, k), cin * k * k)
+        t = [("", w)]
+        b = self._bias(bias, cout)
+        if b is not None:
+            t.append(("", b))
+        return self._add("deconv", [x], dict(stride=(stride, stride), padding=(pad, pad),
+                                            output_padding=(adj, adj)), t)
+
+    def _bias(self, bias, n):
+        if bias is None:
+            return None
+        if isinstance(bias, str) and bias == "zero":
+            return np.zeros(n, np.float32)
+        if isinstance(bias, (int, float)):
+            return (self.rng.standard_normal(n) * bias).astype(np.float32)
+        return np.asarray(bias, np.float32)
+
+    def linear(self, x, cin, cout, bias="zero"):
+        w = self.he((cout, cin), cin)
+        return self._add("linear", [x], {}, [("", w), ("", self._bias(bias, cout))])
+
+    def bn(self, x, c, eps=1e-5):
+        rng = self.rng
+        mean = (rng.standard_normal(c) * 0.1).astype(np.float32)
+        var = rng.uniform(0.5, 1.5, c).astype(np.float32)
+        gamma = rng.uniform(0.8, 1.2, c).astype(np.float32)
+        beta = (rng.standard_normal(c) * 0.1).astype(np.float32)
+        return self._add("bn", [x], dict(eps=float(eps)),
+                         [("", gamma), ("", beta), ("running_mean", mean), ("running_var", var)])
+
+    def relu(self, x, threshold=0.0, value=0.0):
+        return self._add("threshold", [x], dict(threshold=float(threshold), value=float(value), inplace=0))
+
+    def maxpool(self, x, k, stride, pad=0, ceil_mode=0):
+        return self._add("maxpool", [x], dict(kernel_size=(k, k), stride=(stride, stride),
+                                             padding=(pad, pad), ceil_mode=int(ceil_mode)))
+
+    def avgpool(self, x, k, stride=None, pad=0, ceil_mode=0):
+        stride = stride or k
+        return self._add("avgpool", [x], dict(kernel_size=(k, k), stride=(stride, stride),
+                                             padding=(pad, pad), ceil_mode=int(ceil_mode)))
+
+    def view(self, x, n):
+        return self._add("view", [x], dict(sizes=(-1, int(n))))
+
+    def dropout(self, x):
+        return self._add("dropout", [x])
+
+    def softmax(self, x):
+        return self._add("softmax", [x])
+
+    def add(self, a, b):
+        """Reference semantics for two inputs: a - b (CAddTable.c:59-69)."""
+        return self._add("add", [a, b])
+
+    def concat(self, xs, dim=1):
+        return self._add("concat", list(xs), dict(dim=int(dim)))
+
+    # ---- misc ----------------------------------------------------------------
+    def make_input(self, batch, seed=1234):
+        rng = np.random.default_rng(seed)
+        c, h, w = self.input_shape
+        if self.input_dist == "uniform":
+            return rng.random((batch, c, h, w), dtype=np.float32)
+        return rng.standard_normal((batch, c, h, w)).astype(np.float32)
+
+    def is_sequential(self):
+        return all(n.inputs == [i - 1] for i, n in enumerate(self.nodes) if i > 0) and \
+            self.output == len(self.nodes) - 1
+
+
+# ============================================================================
+# "PyTorch Graph Dump 1.00" writer
+# ============================================================================
+_PYNAME = {
+    "conv": "ConvNd", "deconv": "ConvTransposedNd", "linear": "Linear", "bn": "BatchNorm",
+    "maxpool": "MaxPool2d", "avgpool": "AvgPool2d", "threshold": "Threshold", "dropout": "Dropout",
+    "softmax": "Softmax", "view": "View", "add": "Add", "concat": "Concat",
+}
+
+
+def _w_str(f, s):
+    f.write(s.encode("ascii") + b"\0")
+
+
+def _w_tensor(f, name, arr):
+    arr = np.ascontiguousarray(arr, np.float32)
+    f.write(b"\x03")
+    _w_str(f, name)
+    f.write(struct.pack("<i", arr.ndim))
+    f.write(struct.pack("<%di" % arr.ndim, *arr.shape))
+    f.write(struct.pack("<q", arr.size))
+    f.write(arr.tobytes())
+
+
+def write_pymodel(graph: Graph, path: str):
+    """Serialise `graph` depth-first from its output node."""
+    emitted = set()
+    with open(path, "wb") as f:
+        f.write(b"PyTorch Graph Dump 1.00\0")
+
+        def emit(i):
+            node = graph.nodes[i]
+            if node.op == "input":
+                f.write(b"\x01")
+                return
+            if i in emitted:
+                f.write(b"\x07" + struct.pack("<i", i))
+                return
+            emitted.add(i)
+            f.write(b"\x02" + struct.pack("<i", i))
+            _w_str(f, "torch.nn.fn." + _PYNAME[node.op])
+            for k, v in node.attrs.items():
+                if isinstance(v, tuple):
+                    f.write(b"\x06")
+                    _w_str(f, k)
+                    f.write(struct.pack("<i", len(v)) + struct.pack("<%di" % len(v), *v))
+                elif isinstance(v, float):
+                    f.write(b"\x05")
+                    _w_str(f, k)
+                    f.write(struct.pack("<f", v))
+                else:
+                    f.write(b"\x04")
+                    _w_str(f, k)
+                    f.write(struct.pack("<i", int(v)))
+            for j in node.inputs:
+                emit(j)
+            for name, arr in node.tensors:
+                _w_tensor(f, name, arr)
+            f.write(b"\x00")
+
+        emit(graph.output)
+
+
+# ============================================================================
+# Torch7 writer (sequential graphs; containers for the branchy test nets)
+# ============================================================================
+class _T7:
+    def __init__(self, f):
+        self.f = f
+        self.idx = 1
+
+    def i32(self, v):
+        self.f.write(struct.pack("<i", v))
+
+    def i64(self, v):
+        self.f.write(struct.pack("<q", v))
+
+    def string_raw(self, s):
+        b = s.encode("ascii")
+        self.i32(len(b))
+        self.f.write(b)
+
+    def number(self, v):
+        self.i32(1)
+        self.f.write(struct.pack("<d", float(v)))
+
+    def string(self, s):
+        self.i32(2)
+        self.string_raw(s)
+
+    def boolean(self, v):
+        self.i32(5)
+        self.i32(1 if v else 0)
+
+    def nil(self):
+        self.i32(0)
+
+    def tensor(self, arr):
+        if arr is None:
+            # a tensor object without storage (what Torch writes for an absent bias)
+            self.i32(4)
+            self.i32(self.idx)
+            self.idx += 1
+            self.string_raw("V 1")
+            self.string_raw("torch.FloatTensor")
+            self.i32(0)
+            self.i64(1)
+            self.nil()
+            return
+        arr = np.ascontiguousarray(arr, np.float32)
+        self.i32(4)
+        self.i32(self.idx)
+        self.idx += 1
+        self.string_raw("V 1")
+        self.string_raw("torch.FloatTensor")
+        self.i32(arr.ndim)
+        for s in arr.shape:
+            self.i64(s)
+        stride = 1
+        strides = []
+        for s in reversed(arr.shape):
+            strides.append(stride)
+            stride *= s
+        for s in reversed(strides):
+            self.i64(s)
+        self.i64(1)  # storageOffset, 1-based
+        self.i32(4)
+        self.i32(self.idx)
+        self.idx += 1
+        self.string_raw("V 1")
+        self.string_raw("torch.FloatStorage")
+        self.i64(arr.size)
+        self.f.write(arr.tobytes())
+
+    def table(self, items):
+        """items: list of (key, writer-callable); string or number keys."""
+        self.i32(3)
+        self.i32(self.idx)
+        self.idx += 1
+        self.i32(len(items))
+        for k, w in items:
+            if isinstance(k, str):
+                self.string(k)
+            else:
+                self.number(k)
+            w()
+
+    def module(self, name, items):
+        self.i32(4)
+        self.i32(self.idx)
+        self.idx += 1
+        self.string_raw("V 1")
+        self.string_raw(name)
+        self.table(items)
+
+
+def _t7_module(t: _T7, spec):
+    """spec = (torch class name, {field: value}) or (container name, [children], {fields})."""
+    name = spec[0]
+    if name in ("nn.Sequential", "nn.Concat", "nn.ConcatTable"):
+        children = spec[1]
+        extra = spec[2] if len(spec) > 2 else {}
+        items = [("modules", lambda: t.table([(i + 1, (lambda c=c: _t7_module(t, c)))
+                                              for i, c in enumerate(children)]))]
+        for k, v in extra.items():
+            items.append((k, (lambda v=v: t.number(v))))
+        t.module(name, items)
+        return
+    items = []
+    for k, v in spec[1].items():
+        if isinstance(v, np.ndarray) or v is None:
+            items.append((k, (lambda v=v: t.tensor(v))))
+        elif isinstance(v, bool):
+            items.append((k, (lambda v=v: t.boolean(v))))
+        else:
+            items.append((k, (lambda v=v: t.number(v))))
+    t.module(name, items)
+
+
+def graph_to_t7_spec(graph: Graph):
+    """Nested Torch7 module spec of a purely sequential graph."""
+    if not graph.is_sequential():
+        raise ValueError("only sequential graphs map onto a flat nn.Sequential")
+    mods = []
+    for node in graph.nodes[1:]:
+        a = node.attrs
+        ts = [arr for _, arr in node.tensors]
+        if node.op == "conv":
+            w = ts[0]
+            mods.append(("nn.SpatialConvolutionMM", dict(
+                padW=a["padding"][1], padH=a["padding"][0], dW=a["stride"][1], dH=a["stride"][0],
+                kW=w.shape[3], kH=w.shape[2], nInputPlane=w.shape[1], nOutputPlane=w.shape[0],
+                weight=w.reshape(w.shape[0], -1), bias=ts[1] if len(ts) > 1 else None)))
+        elif node.op == "linear":
+            mods.append(("nn.Linear", dict(weight=ts[0], bias=ts[1])))
+        elif node.op == "threshold":
+            mods.append(("nn.Threshold", dict(threshold=a["threshold"], val=a["value"], inplace=False)))
+        elif node.op == "maxpool":
+            mods.append(("nn.SpatialMaxPooling", dict(
+                padW=a["padding"][1], padH=a["padding"][0], dW=a["stride"][1], dH=a["stride"][0],
+                kW=a["kernel_size"][1], kH=a["kernel_size"][0], ceil_mode=a["ceil_mode"])))
+        elif node.op == "avgpool":
+            mods.append(("nn.SpatialAveragePooling", dict(
+                padW=a["padding"][1], padH=a["padding"][0], dW=a["stride"][1], dH=a["stride"][0],
+                kW=a["kernel_size"][1], kH=a["kernel_size"][0], ceil_mode=a["ceil_mode"],
+                count_include_pad=0)))
+        elif node.op == "view":
+            mods.append(("nn.View", dict(numElements=a["sizes"][1])))
+        elif node.op == "dropout":
+            mods.append(("nn.Dropout", dict(p=0.5, v2=True, inplace=False)))
+        elif node.op == "softmax":
+            mods.append(("nn.SoftMax", {}))
+        elif node.op == "bn":
+            mods.append(("nn.SpatialBatchNormalization", dict(
+                running_mean=ts[2], running_var=ts[3], weight=ts[0], bias=ts[1], eps=a["eps"])))
+        elif node.op == "deconv":
+            w = ts[0]
+            mods.append(("nn.SpatialFullConvolution", dict(
+                padW=a["padding"][1], padH=a["padding"][0], dW=a["stride"][1], dH=a["stride"][0],
+                adjW=a["output_padding"][1], adjH=a["output_padding"][0], kW=w.shape[3], kH=w.shape[2],
+                nInputPlane=w.shape[0], nOutputPlane=w.shape[1], weight=w,
+                bias=ts[1] if len(ts) > 1 else None)))
+        else:
+            raise ValueError("no Torch7 mapping for " + node.op)
+    return ("nn.Sequential", mods)
+
+
+def write_torch7(spec_or_graph, dirpath: str, mean=None, std=None):
+    """Write `dirpath/model.net` (+ `stat.t7` when mean/std are given)."""
+    os.makedirs(dirpath, exist_ok=True)
+    if isinstance(spec_or_graph, Graph):
+        g = spec_or_graph
+        spec = graph_to_t7_spec(g)
+        if mean is None and (np.any(g.mean != 0) or np.any(g.std != 1)):
+            mean, std = g.mean, g.std
+    else:
+        spec = spec_or_graph
+    with open(os.path.join(dirpath, "model.net"), "wb") as f:
+        _t7_module(_T7(f), spec)
+    if mean is not None:
+        with open(os.path.join(dirpath, "stat.t7"), "wb") as f:
+            t = _T7(f)
+            t.table([("mean", lambda: t.tensor(np.asarray(mean, np.float32))),
+                     ("std", lambda: t.tensor(np.asarray(std, np.float32)))])
+
+
+# ============================================================================
+# The benchmark architectures (seeded, synthetic)
+# ============================================================================
+def alexnet_owt(seed=0, width=1.0, size=224, classes=1000, fc=4096):
+    """AlexNet "one weird trick": profilealexnetowt.lua:8-31 minus Dropout, plus SoftMax."""
+    g = Graph(seed, mean=(0.45,) * 3, std=(0.225,) * 3)
+    g.input_shape, g.input_dist = (3, size, size), "uniform"
+    c = [max(8, int(round(v * width))) for v in (64, 192, 384, 256, 256)]
+    s = size
+    x = g.relu(g.conv(0, 3, c[0], 11, 4, 2)); s = (s + 4 - 11) // 4 + 1
+    x = g.maxpool(x, 3, 2); s = (s - 3) // 2 + 1
+    x = g.relu(g.conv(x, c[0], c[1], 5, 1, 2))
+    x = g.maxpool(x, 3, 2); s = (s - 3) // 2 + 1
+    x = g.relu(g.conv(x, c[1], c[2], 3, 1, 1))
+    x = g.relu(g.conv(x, c[2], c[3], 3, 1, 1))
+    x = g.relu(g.conv(x, c[3], c[4], 3, 1, 1))
+    x = g.maxpool(x, 3, 2); s = (s - 3) // 2 + 1
+    n = c[4] * s * s
+    x = g.view(x, n)
+    x = g.relu(g.linear(x, n, fc))
+    x = g.relu(g.linear(x, fc, fc))
+    x = g.linear(x, fc, classes)
+    g.softmax(x)
+    return g
+
+
+def vgg16(seed=2, width=1.0, size=224, classes=1000, fc=4096, bias_std=0.01):
+    """VGG-16; biases are non-zero because an all-zero bias is undefined in the lowp scheme."""
+    g = Graph(seed)
+    g.input_shape, g.input_dist = (3, size, size), "uniform"
+    cfg = [(64, 2), (128, 2), (256, 3), (512, 3), (512, 3)]
+    x, cin, s = 0, 3, size
+    for ch, reps in cfg:
+        ch = max(8, int(round(ch * width)))
+        for _ in range(reps):
+            x = g.relu(g.conv(x, cin, ch, 3, 1, 1, bias=bias_std))
+            cin = ch
+        x = g.maxpool(x, 2, 2); s //= 2
+    n = cin * s * s
+    x = g.view(x, n)
+    x = g.relu(g.linear(x, n, fc, bias=bias_std))
+    x = g.relu(g.linear(x, fc, fc, bias=bias_std))
+    g.linear(x, fc, classes, bias=bias_std)
+    g.fc_spatial = s  # size to pass to THMakeSpatial's first Linear
+    return g
+
+
+def _basic_block(g, x, cin, cout, stride):
+    y = g.relu(g.bn(g.conv(x, cin, cout, 3, stride, 1, bias=None), cout))
+    y = g.bn(g.conv(y, cout, cout, 3, 1, 1, bias=None), cout)
+    sc = x
+    if stride != 1 or cin != cout:
+        sc = g.bn(g.conv(x, cin, cout, 1, stride, 0, bias=None), cout)
+    return g.relu(g.add(y, sc))
+
+
+def _bottleneck(g, x, cin, mid, stride):
+    cout = mid * 4
+    y = g.relu(g.bn(g.conv(x, cin, mid, 1, 1, 0, bias=None), mid))
+    y = g.relu(g.bn(g.conv(y, mid, mid, 3, stride, 1, bias=None), mid))
+    y = g.bn(g.conv(y, mid, cout, 1, 1, 0, bias=None), cout)
+    sc = x
+    if stride != 1 or cin != cout:
+        sc = g.bn(g.conv(x, cin, cout, 1, stride, 0, bias=None), cout)
+    return g.relu(g.add(y, sc))
+
+
+def _resnet(seed, blocks, bottleneck, width, size, classes):
+    g = Graph(seed)
+    g.input_shape, g.input_dist = (3, size, size), "normal"
+    base = max(8, int(round(64 * width)))
+    x = g.relu(g.bn(g.conv(0, 3, base, 7, 2, 3, bias=None), base))
+    x = g.maxpool(x, 3, 2, 1)
+    s = ((size + 6 - 7) // 2 + 1 + 2 - 3) // 2 + 1
+    cin = base
+    for stage, reps in enumerate(blocks):
+        mid = base * (2 ** stage)
+        for r in range(reps):
+            stride = 2 if (r == 0 and stage > 0) else 1
+            if bottleneck:
+                x = _bottleneck(g, x, cin, mid, stride)
+                cin = mid * 4
+            else:
+                x = _basic_block(g, x, cin, mid, stride)
+                cin = mid
+            if stride == 2:
+                s = (s + 2 - 3) // 2 + 1
+    x = g.avgpool(x, s, s)
+    x = g.view(x, cin)
+    g.linear(x, cin, classes)
+    return g
+
+
+def resnet18(seed=1, width=1.0, size=224, classes=1000):
+    return _resnet(seed, [2, 2, 2, 2], False, width, size, classes)
+
+
+def resnet50(seed=4, width=1.0, size=224, classes=1000):
+    return _resnet(seed, [3, 4, 6, 3], True, width, size, classes)
+
+
+def segnet(seed=3, width=1.0, size=512, classes=21, deconv_bias=None):
+    """Encoder-decoder with transposed convolutions and channel-concat skips."""
+    g = Graph(seed)
+    g.input_shape, g.input_dist = (3, size, size), "normal"
+    ch = [max(4, int(round(v * width))) for v in (32, 64, 128, 256)]
+    x, cin, skips = 0, 3, []
+    for c in ch:
+        x = g.relu(g.bn(g.conv(x, cin, c, 3, 1, 1, bias=None), c))
+        skips.append((x, c))
+        x = g.maxpool(x, 2, 2)
+        cin = c
+    dec = [ch[3] // 2, ch[2] // 2, ch[1] // 2, ch[0] // 2]
+    for i, dc in enumerate(dec):
+        x = g.deconv(x, cin, dc, 4, 2, 1, 0, bias=deconv_bias)
+        sx, sc = skips[3 - i]
+        x = g.concat([x, sx], 1)
+        cin = dc + sc
+    g.conv(x, cin, classes, 1, 1, 0)
+    return g
+
+
+BUILDERS = {"alexnet_owt": alexnet_owt, "resnet18": resnet18, "vgg16": vgg16, "segnet": segnet,
+            "resnet50": resnet50}
+
+# algorithmic GFLOP per image at full size (2 * MACs of conv / deconv / linear layers)
+GFLOP_PER_IMAGE = {"alexnet_owt": 1.428, "resnet18": 3.628, "vgg16": 30.94, "segnet": 18.97,
+                   "resnet50": 8.178}
