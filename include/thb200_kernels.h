@@ -1,0 +1,152 @@
+/*
+ * thb200_kernels.h -- thin C ABI of the sm_100a kernels behind the thnets forward pass.
+ *
+ * Plain pointers, sizes and POD descriptors only; no C++ or framework types cross
+ * this boundary.  Every pointer is a DEVICE pointer unless its name ends in _host.
+ * Every function returns 0 on success, a negative thb_status otherwise, and never
+ * falls back to the CPU: an unsupported case is an error.
+ *
+ * Activation tensors are channels-innermost: element (n, h, w, c) of a tensor with
+ * pixel stride `ld` lives at ((n*H + h)*W + w)*ld + c.  `ld` may exceed C (padding,
+ * or a channel slice of a wider concatenation buffer).  ld and every channel offset
+ * are multiples of thb_channel_align(dtype) so that 16-byte accesses stay aligned.
+ *
+ * Each entry point names the reference operator it replaces (file:line within the
+ * reference project).
+ */
+#ifndef THB200_KERNELS_H
+#define THB200_KERNELS_H
+#include <stddef.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum { THB_F32 = 0, THB_F16 = 1, THB_BF16 = 2, THB_U8 = 3 } thb_dtype;
+
+typedef enum {
+    THB_OK = 0,
+    THB_ERR_UNSUPPORTED = -1, /* shape / dtype combination has no kernel */
+    THB_ERR_CUDA = -2,        /* a CUDA runtime call failed; see thb_last_cuda_error() */
+    THB_ERR_TIMEOUT = -3,     /* a bounded device-side wait ran out (kernel status word) */
+    THB_ERR_ARG = -4
+} thb_status;
+
+typedef void *thb_stream; /* cudaStream_t */
+
+/* fused activation, applied last.  Threshold.c:38-63, PReLU.c:32-92 */
+typedef enum { THB_ACT_NONE = 0, THB_ACT_THRESHOLD = 1, THB_ACT_LEAKY = 2, THB_ACT_PRELU = 3 } thb_act_kind;
+typedef struct thb_act {
+    int kind;
+    float threshold, value, alpha; /* x > threshold ? x : value   |   x >= 0 ? x : alpha*x */
+    const float *slope;            /* THB_ACT_PRELU: one slope per output channel: x > 0 ? x : slope[c]*x */
+} thb_act;
+
+/* 128-byte opaque TMA descriptor (CUtensorMap) of a packed weight matrix */
+typedef struct __attribute__((aligned(64))) thb_tmap { unsigned long long opaque[16]; } thb_tmap;
+
+/* ------------------------------------------------------------------------------------------
+ * Convolution: replaces nn_SpatialConvolutionMM_updateOutput (modules/SpatialConvolutionMM.c:126-225),
+ * THFloatTensor_convmm / sgemmargs (thbasic.c:1073-1103, OpenBLAS-stripped/sgemm.c:953-1036) and, in
+ * THB_U8, Lowp_SpatialConvolution_updateOutput + THLowpTensor_mm (lowp/lowp_SpatialConvolution.c:90-187,
+ * lowp/lowp_basic.c:299-321).  Implicit GEMM, no im2col buffer.  A Linear layer is the H=W=kH=kW=1 case.
+ *
+ * Floating-point epilogue (F32/F16/BF16), per output channel c:
+ *     y = act( self_coef * (acc*scale[c] + shift[c]) + res_coef * res )
+ * which covers bias, folded SpatialBatchNormalization and a fused two-input CAddTable/CSubTable.
+ *
+ * uint8 epilogue: exact int32 accumulator of sum (W+a_offset)*(X+b_offset) over the in-image taps,
+ * gemmlowp-style requantisation ((acc+c_offset)*c_mult + round) >> c_shift saturated to u8, the
+ * reference's per-plane saturating bias add (tail positions >= tail_start wrap below zero instead of
+ * clamping, lowp_SpatialConvolution.c:71-88), then the u8 threshold q > relu_thr ? q : relu_val.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct thb_conv_desc {
+    int dtype;
+    int N, H, W, Cin, in_ld;
+    int Cout, kH, kW, dH, dW, padH, padW, oH, oW, out_ld;
+    /* fp epilogue */
+    const float *scale, *shift; /* NULL: 1 / 0 */
+    const void *res;            /* NULL: none; same dtype and spatial shape as the output */
+    int res_ld;
+    float self_coef, res_coef;
+    thb_act act;
+    /* u8 epilogue */
+    int a_offset, b_offset, c_offset, c_mult, c_shift;
+    const int *wsat;     /* [Cout][(kH+1)*(kW+1)] summed-area table over taps of per-tap weight channel sums */
+    const int *bias_add; /* [Cout] addend of the saturating bias add */
+    const int *csum;     /* [N*H*W] per input pixel: sum of its Cin bytes (thb_u8_channel_sum) */
+    int tail_start;      /* oH*oW - (oH*oW % 8) */
+    int relu_thr, relu_val; /* relu_thr < 0: no threshold */
+    int *acc_out;        /* optional: raw corrected int32 accumulators [N*oH*oW][Cout] (tests) */
+    /* packed weights */
+    const void *w;        /* F32: [Ktot][Cout4] ; tensor-core dtypes: [Cout_pad][Ktot_pad], K = tap*Cin_pad + c */
+    const int *kinfo;     /* tensor-core dtypes: one word per 16-byte K chunk (thb_conv_pack_*) */
+    const thb_tmap *tmap; /* tensor-core dtypes: TMA descriptor of w (host pointer) */
+    int Cin_pad, Ktot_pad, Cout_pad, BN;
+    int *status;          /* device word: set non-zero when a bounded wait gave up */
+} thb_conv_desc;
+
+int thb_channel_align(int dtype);               /* 4 (F32), 8 (F16/BF16), 16 (U8) */
+int thb_conv_geometry(thb_conv_desc *d);        /* fills Cin_pad, Ktot_pad, Cout_pad, BN from the shape */
+size_t thb_conv_weight_bytes(const thb_conv_desc *d);
+size_t thb_conv_kinfo_words(const thb_conv_desc *d);
+/* host-side packing of OIHW fp32 weights (or pre-quantised u8 weights) into the kernel layout;
+ * chan_perm_hw > 0 reorders Cin from an NCHW flatten of [Cin/hw, hw] to channels-innermost (View -> Linear) */
+int thb_conv_pack_weights_host(const thb_conv_desc *d, const float *w_oihw, const unsigned char *wq_oihw,
+                               void *packed_host, int *kinfo_host, int *wsat_host);
+int thb_conv_make_tmap(const thb_conv_desc *d, thb_tmap *out);
+int thb_conv_fwd(const thb_conv_desc *d, const void *x, void *y, thb_stream s);
+
+/* Batch-small Linear: y[n][m] = sum_k W[m][k]*x[n][k] (+ epilogue as above), N <= 8, weights read once.
+ * Replaces nn_Linear_updateOutput's addmv path (modules/Linear.c:86-90, OpenBLAS-stripped/sgemv.c:48-105). */
+int thb_gemv_fwd(int dtype, const void *x, int N, int K, int x_ld, const void *w /*[M][K]*/, int M,
+                 const float *scale, const float *shift, const thb_act *act, void *y, int y_ld, thb_stream s);
+
+/* ---- layout / precision boundary (thapi.c:363-450, :452-573; lowp/lowp_basic.c:5-58) ---- */
+/* NCHW fp32 -> normalised NHWC dtype; also writes the normalised fp32 values back over `x` when inplace != 0 */
+int thb_preprocess(const float *x_nchw, float *x_inplace, int N, int C, int H, int W, const float *mean3,
+                   const float *std3, int dtype, void *y, int y_ld, float q_sub, float q_mult, thb_stream s);
+/* u8 HWC images (already on the device, row stride `stride`) -> normalised NHWC dtype (thapi.c:20-46) */
+int thb_preprocess_images(const unsigned char *img, int N, int H, int W, int stride, int cp, int bgr,
+                          const float *mean3, const float *std3, int dtype, void *y, int y_ld, thb_stream s);
+/* min and max (both seeded with 0) of the normalised input, for the dynamic input quantisation */
+int thb_minmax_normalized(const float *x_nchw, int N, int C, int H, int W, const float *mean3,
+                          const float *std3, float *minmax2, thb_stream s);
+/* NHWC dtype -> NCHW fp32 (dequantising u8 with q*inv_mult + sub) */
+int thb_postprocess(const void *x, int dtype, int N, int H, int W, int C, int x_ld, float q_sub, float q_invmult,
+                    float *y_nchw, thb_stream s);
+
+/* ---- pooling: SpatialMaxPooling.c:74-247, SpatialAveragePooling.c:71-207, lowp_SpatialMaxPooling.c ---- */
+int thb_maxpool(int dtype, const void *x, int N, int H, int W, int C, int x_ld, int kH, int kW, int dH, int dW,
+                int padH, int padW, int oH, int oW, void *y, int y_ld, thb_stream s);
+int thb_avgpool(int dtype, const void *x, int N, int H, int W, int C, int x_ld, int kH, int kW, int dH, int dW,
+                int padH, int padW, int oH, int oW, int count_include_pad, void *y, int y_ld, thb_stream s);
+
+/* ---- elementwise: SpatialBatchNormalization.c:57-116 / Threshold.c / PReLU.c / Dropout.c as y = act(x*scale[c]+shift[c]) ---- */
+int thb_affine_act(int dtype, const void *x, long pixels, int C, int x_ld, const float *scale, const float *shift,
+                   const thb_act *act, void *y, int y_ld, thb_stream s);
+/* u8 threshold: q > thr ? q : val (lowp/lowp_Threshold.c:3-28) */
+int thb_u8_threshold(const void *x, long pixels, int C, int x_ld, int thr, int val, void *y, int y_ld, thb_stream s);
+/* y = sum_i coef[i]*x[i], evaluated left to right (CAddTable.c:32-86) */
+int thb_combine(int dtype, int nin, const void *const *x_host, const int *ld_host, const float *coef_host,
+                long pixels, int C, void *y, int y_ld, thb_stream s);
+/* copy a C-channel tensor into a channel slice of a wider buffer (JoinTable.c:34-86, Concat.c:21-76) */
+int thb_copy_channels(int dtype, const void *x, long pixels, int C, int x_ld, void *y, int y_ld, thb_stream s);
+/* softmax over channels per pixel with the reference's polynomial exp (SoftMax.c:24-90, thbasic.c:462-491) */
+int thb_softmax(int dtype, const void *x, long pixels, int C, int x_ld, void *y, int y_ld, thb_stream s);
+/* col2im gather of a transposed convolution's column matrix [N*H*W][Cout*kH*kW] (SpatialFullConvolution.c:99-127),
+ * then y = act(beta*y + bias[c]) (:229-238: beta is 11 in the reference whenever a bias exists) */
+int thb_col2im(int dtype, const void *cols, int N, int H, int W, int Cout, int kH, int kW, int dH, int dW, int padH,
+               int padW, int oH, int oW, int cols_ld, float beta, const float *bias, const thb_act *act, void *y,
+               int y_ld, thb_stream s);
+/* per-pixel sum of the first C bytes (zero-point correction term of the u8 convolution) */
+int thb_u8_channel_sum(const void *x, long pixels, int C, int x_ld, int *csum, thb_stream s);
+/* channels-innermost -> plain NCHW flatten order of the same dtype (View feeding anything but a Linear) */
+int thb_to_nchw(int dtype, const void *x, int N, int H, int W, int C, int x_ld, void *y, thb_stream s);
+
+const char *thb_last_cuda_error(void);
+int thb_kernel_launch_count(void); /* launches issued through this ABI since load (bench bookkeeping) */
+
+#ifdef __cplusplus
+}
+#endif
+#endif

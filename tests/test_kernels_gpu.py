@@ -1,0 +1,400 @@
+"""Operator-level parity: every kernel, called through the C ABI of libthnets.so on raw device
+pointers, against the CPU oracle on the same seeded inputs.
+
+Tolerances: fp32 1e-4, fp16 1e-2 (max-abs error over max-abs reference, the metric used for whole
+networks); uint8 bit-exact, including the int32 accumulators.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+from thnets_b200 import kernels_abi as K  # noqa: E402
+
+
+@pytest.fixture(scope="module")
+def lib():
+    return K.load()
+
+
+@pytest.fixture(scope="module")
+def G():
+    import gpu_util
+    return gpu_util
+
+
+TOL = {K.THB_F32: 1e-4, K.THB_F16: 1e-2}
+
+CONV_CASES = [
+    # n, cin, h, w, cout, k, stride, pad
+    (2, 16, 12, 12, 32, 3, 1, 1),
+    (1, 3, 35, 35, 24, 7, 2, 3),
+    (3, 64, 9, 9, 64, 1, 1, 0),
+    (2, 24, 17, 13, 40, 3, 2, 1),
+    (1, 3, 67, 67, 16, 11, 4, 2),
+    (2, 40, 7, 7, 136, 5, 1, 2),
+    (5, 128, 7, 7, 72, 3, 1, 1),
+    (1, 8, 30, 30, 300, 1, 2, 0),
+]
+
+
+def _conv_inputs(case, seed, half):
+    n, cin, h, w, cout, k, s, p = case
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((n, cin, h, w)).astype(np.float32)
+    wt = (rng.standard_normal((cout, cin, k, k)) * np.sqrt(2.0 / (cin * k * k))).astype(np.float32)
+    if half:
+        x = x.astype(np.float16).astype(np.float32)
+        wt = wt.astype(np.float16).astype(np.float32)
+    return x, wt
+
+
+@pytest.mark.parametrize("dtype", [K.THB_F32, K.THB_F16])
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_conv_plain(lib, G, oracle, dtype, case):
+    n, cin, h, w, cout, k, s, p = case
+    x, wt = _conv_inputs(case, 1, dtype == K.THB_F16)
+    bias = np.random.default_rng(2).standard_normal(cout).astype(np.float32)
+    ref = oracle.conv2d(x, wt, bias, (s, s), (p, p))
+    conv = G.Conv(lib, dtype, x.shape, wt, (s, s), (p, p))
+    conv.set_affine(None, bias)
+    xt, _ = G.to_nhwc(x, dtype)
+    y = conv.run(xt, fill=7.0)
+    got = G.from_nhwc(y, cout)
+    assert G.rel_err(got, ref) < TOL[dtype], (case, G.rel_err(got, ref))
+    # padded output channels are written as exact zeros
+    pad = y[..., cout:G.ru(cout, K.ALIGN[dtype])]
+    assert pad.numel() == 0 or float(pad.float().abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("bn_tile", [32, 64, 128, 256])
+def test_conv_f16_all_tile_widths(lib, G, oracle, bn_tile):
+    case = (2, 72, 14, 14, 264, 3, 1, 1)
+    n, cin, h, w, cout, k, s, p = case
+    x, wt = _conv_inputs(case, 3, True)
+    ref = oracle.conv2d(x, wt, None, (s, s), (p, p))
+    conv = G.Conv(lib, K.THB_F16, x.shape, wt, (s, s), (p, p), bn_tile=bn_tile)
+    xt, _ = G.to_nhwc(x, K.THB_F16)
+    got = G.from_nhwc(conv.run(xt), cout)
+    assert G.rel_err(got, ref) < 1e-2, (bn_tile, G.rel_err(got, ref))
+
+
+def test_conv_f16_long_k(lib, G, oracle):
+    """K = 7*7*512 = 25088 (the VGG FC6-as-convolution shape): 392 pipeline stages."""
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((4, 512, 7, 7)).astype(np.float16).astype(np.float32)
+    wt = (rng.standard_normal((96, 512, 7, 7)) * 0.01).astype(np.float16).astype(np.float32)
+    ref = oracle.conv2d(x, wt, None, (1, 1), (0, 0))
+    conv = G.Conv(lib, K.THB_F16, x.shape, wt)
+    xt, _ = G.to_nhwc(x, K.THB_F16)
+    got = G.from_nhwc(conv.run(xt), 96)
+    assert G.rel_err(got, ref) < 1e-2
+
+
+@pytest.mark.parametrize("dtype", [K.THB_F32, K.THB_F16])
+def test_conv_fused_epilogue(lib, G, oracle, dtype):
+    """BN scale/shift, residual with the reference's a - b sign, then ReLU; then PReLU and leaky."""
+    case = (2, 32, 10, 10, 48, 3, 1, 1)
+    n, cin, h, w, cout, k, s, p = case
+    half = dtype == K.THB_F16
+    x, wt = _conv_inputs(case, 5, half)
+    rng = np.random.default_rng(6)
+    scale = rng.uniform(0.5, 1.5, cout).astype(np.float32)
+    shift = rng.standard_normal(cout).astype(np.float32)
+    res = rng.standard_normal((n, cout, h, w)).astype(np.float32)
+    if half:
+        res = res.astype(np.float16).astype(np.float32)
+    base = oracle.conv2d(x, wt, None, (s, s), (p, p)) * scale[None, :, None, None] + shift[None, :, None, None]
+    xt, _ = G.to_nhwc(x, dtype)
+    rt, rld = G.to_nhwc(res, dtype)
+    for self_c, res_c in ((1.0, -1.0), (-1.0, 1.0), (1.0, 1.0)):
+        conv = G.Conv(lib, dtype, x.shape, wt, (s, s), (p, p))
+        conv.set_affine(scale, shift)
+        conv.set_residual(rt, rld, self_c, res_c)
+        conv.set_act(K.ACT_THRESHOLD, 0.0, 0.0)
+        ref = oracle.threshold(self_c * base + res_c * res, 0.0, 0.0)
+        got = G.from_nhwc(conv.run(xt), cout)
+        assert G.rel_err(got, ref) < TOL[dtype]
+    slope = rng.uniform(0.1, 0.3, cout).astype(np.float32)
+    conv = G.Conv(lib, dtype, x.shape, wt, (s, s), (p, p))
+    conv.set_affine(scale, shift)
+    conv.set_act(K.ACT_PRELU, slope=slope)
+    assert G.rel_err(G.from_nhwc(conv.run(xt), cout), oracle.prelu(base, slope, cout)) < TOL[dtype]
+    conv = G.Conv(lib, dtype, x.shape, wt, (s, s), (p, p))
+    conv.set_affine(scale, shift)
+    conv.set_act(K.ACT_LEAKY, alpha=0.1)
+    assert G.rel_err(G.from_nhwc(conv.run(xt), cout), oracle.threshold(base, 0, 0, 0.1)) < TOL[dtype]
+    conv = G.Conv(lib, dtype, x.shape, wt, (s, s), (p, p))
+    conv.set_affine(scale, shift)
+    conv.set_act(K.ACT_THRESHOLD, 0.5, -1.0)
+    assert G.rel_err(G.from_nhwc(conv.run(xt), cout), oracle.threshold(base, 0.5, -1.0)) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [K.THB_F32, K.THB_F16])
+def test_conv_strided_views(lib, G, oracle, dtype):
+    """Input read from, and output written into, channel slices of wider buffers."""
+    case = (2, 16, 8, 8, 32, 3, 1, 1)
+    n, cin, h, w, cout, k, s, p = case
+    x, wt = _conv_inputs(case, 7, dtype == K.THB_F16)
+    ref = oracle.conv2d(x, wt, None, (s, s), (p, p))
+    xt, ld = G.to_nhwc(x, dtype, ld=48, fill=3.0)
+    conv = G.Conv(lib, dtype, x.shape, wt, (s, s), (p, p))
+    conv.d.in_ld = ld
+    y = conv.run(xt, out_ld=64, fill=9.0)
+    assert G.rel_err(G.from_nhwc(y, cout), ref) < TOL[dtype]
+    assert float((y[..., cout:].float() - 9.0).abs().max()) == 0.0
+
+
+# ---------------------------------------------------------------------------------------------- uint8
+def _lowp_case(oracle, G, case, seed, rng_range=8.0):
+    n, cin, h, w, cout, k, s, p = case
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((n, cin, h, w)).astype(np.float32)
+    wt = (rng.standard_normal((cout, cin, k, k)) * np.sqrt(2.0 / (cin * k * k))).astype(np.float32)
+    b = (rng.standard_normal(cout) * 0.1).astype(np.float32)
+    xq, xs, xm = oracle.lowp_quantize(x)
+    wq, ws, wm = oracle.lowp_quantize(wt)
+    bq, bs, bm = oracle.lowp_quantize(b)
+    osub, omult = float(np.float32(-rng_range / 2)), float(np.float32(255) / np.float32(rng_range))
+    return (xq, xs, xm), (wq, ws, wm), (bq, bs, bm), (osub, omult)
+
+
+@pytest.mark.parametrize("case", CONV_CASES + [(2, 72, 14, 14, 264, 3, 1, 1)])
+@pytest.mark.parametrize("relu", [False, True])
+def test_conv_u8_bit_exact(lib, G, oracle, case, relu):
+    n, cin, h, w, cout, k, s, p = case
+    (xq, xs, xm), (wq, ws, wm), (bq, bs, bm), (osub, omult) = _lowp_case(oracle, G, case, 11)
+    ref = oracle.lowp_conv(xq, xs, xm, wq, ws, wm, bq, bs, bm, (s, s), (p, p), osub, omult)
+    a_off, b_off, c_off, c_mult, c_shift = oracle.lowp_gemm_params(ws, wm, xs, xm, osub, omult)
+    zero = int(np.round(np.float32(-xs) * np.float32(xm)))
+    thr = oracle.lib.orc_lowp_scale_float(osub, omult, 0.0)
+    if relu:
+        ref = oracle.lowp_threshold(ref, osub, omult, 0.0, 0.0)
+    conv = G.Conv(lib, K.THB_U8, xq.shape, None, (s, s), (p, p), wq=wq)
+    d = conv.d
+    d.a_offset, d.b_offset, d.c_offset, d.c_mult, d.c_shift = a_off, b_off, c_off, c_mult, c_shift
+    # bias addend exactly as lowp_SpatialConvolution.c:112-119 computes it (float math on the host)
+    add = int(np.round(np.float32(bs) * np.float32(omult)))
+    mul = np.float32(omult) / np.float32(bm)
+    badd = np.array([int(np.round(np.float32(q) * mul)) + add for q in bq], np.int32)
+    ohw = d.oH * d.oW
+    d.tail_start = ohw - ohw % 8
+    d.relu_thr, d.relu_val = (thr, thr) if relu else (-1, 0)
+    xt, _ = G.to_nhwc(xq, K.THB_U8)
+    csum = G.dzeros(n * h * w, torch.int32)
+    acc = G.dzeros(n * ohw * cout, torch.int32)
+    tb = G.dev(badd)
+    d.bias_add, d.csum, d.acc_out = tb.data_ptr(), csum.data_ptr(), acc.data_ptr()
+    assert lib.thb_u8_channel_sum(G.ptr(xt), n * h * w, cin, d.in_ld, G.ptr(csum), None) == 0
+    y = conv.run(xt)
+    got = G.from_nhwc(y, cout)
+    acc_ref = np.stack([oracle.lowp_conv_acc(xq[i], wq, (s, s), (p, p), zero, a_off, b_off) for i in range(n)])
+    acc_got = acc.cpu().numpy().reshape(n, d.oH, d.oW, cout).transpose(0, 3, 1, 2)
+    assert np.array_equal(acc_got, acc_ref), ("int32 accumulators differ", int(np.abs(acc_got - acc_ref).max()))
+    assert np.array_equal(got, ref), ("requantised outputs differ", int(np.abs(got.astype(int) - ref.astype(int)).max()))
+
+
+# ---------------------------------------------------------------------------------------- other kernels
+@pytest.mark.parametrize("dtype", [K.THB_F32, K.THB_F16])
+@pytest.mark.parametrize("n", [1, 3, 8])
+def test_gemv(lib, G, oracle, dtype, n):
+    rng = np.random.default_rng(20)
+    kdim, m = 1064, 203
+    x = rng.standard_normal((n, kdim)).astype(np.float32)
+    w = (rng.standard_normal((m, kdim)) * 0.05).astype(np.float32)
+    b = rng.standard_normal(m).astype(np.float32)
+    if dtype == K.THB_F16:
+        x, w = x.astype(np.float16).astype(np.float32), w.astype(np.float16).astype(np.float32)
+    ref = oracle.threshold(oracle.linear(x, w, b), 0, 0)
+    td = torch.float32 if dtype == K.THB_F32 else torch.float16
+    xt, wt_, bt = G.dev(x).to(td), G.dev(w).to(td), G.dev(b)
+    yld = G.ru(m, K.ALIGN[dtype])
+    y = torch.full((n, yld), 5.0, dtype=td, device="cuda")
+    act = K.Act(K.ACT_THRESHOLD, 0.0, 0.0, 0.0, None)
+    rc = lib.thb_gemv_fwd(dtype, G.ptr(xt), n, kdim, kdim, G.ptr(wt_), m, None, G.ptr(bt), C.byref(act), G.ptr(y), yld, None)
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert G.rel_err(y[:, :m].float().cpu().numpy(), ref) < TOL[dtype]
+    assert float(y[:, m:].float().abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", [K.THB_F32, K.THB_F16, K.THB_U8])
+@pytest.mark.parametrize("geom", [(3, 2, 0, 0), (3, 2, 1, 0), (2, 2, 0, 0), (3, 2, 0, 1)])
+def test_maxpool(lib, G, oracle, dtype, geom):
+    k, s, p, ceil_mode = geom
+    rng = np.random.default_rng(30)
+    n, c, h, w = 2, 20, 13, 11
+    if dtype == K.THB_U8:
+        x = rng.integers(0, 256, (n, c, h, w)).astype(np.uint8)
+        ref = oracle.lowp_maxpool(x, (k, k), (s, s), (p, p), ceil_mode)
+    else:
+        x = rng.standard_normal((n, c, h, w)).astype(np.float32)
+        if dtype == K.THB_F16:
+            x = x.astype(np.float16).astype(np.float32)
+        ref = oracle.maxpool(x, (k, k), (s, s), (p, p), ceil_mode)
+    oh, ow = ref.shape[2:]
+    xt, ld = G.to_nhwc(x, dtype)
+    y = torch.zeros((n, oh, ow, ld), dtype=xt.dtype, device="cuda")
+    rc = lib.thb_maxpool(dtype, G.ptr(xt), n, h, w, c, ld, k, k, s, s, p, p, oh, ow, G.ptr(y), ld, None)
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert np.array_equal(G.from_nhwc(y, c), ref)
+
+
+@pytest.mark.parametrize("dtype", [K.THB_F32, K.THB_F16])
+@pytest.mark.parametrize("geom", [(7, 7, 0), (3, 2, 1), (2, 2, 0)])
+def test_avgpool(lib, G, oracle, dtype, geom):
+    k, s, p = geom
+    rng = np.random.default_rng(31)
+    n, c, h, w = 3, 24, 7, 7
+    x = rng.standard_normal((n, c, h, w)).astype(np.float32)
+    if dtype == K.THB_F16:
+        x = x.astype(np.float16).astype(np.float32)
+    ref = oracle.avgpool(x, (k, k), (s, s), (p, p))
+    oh, ow = ref.shape[2:]
+    xt, ld = G.to_nhwc(x, dtype)
+    y = torch.zeros((n, oh, ow, ld), dtype=xt.dtype, device="cuda")
+    rc = lib.thb_avgpool(dtype, G.ptr(xt), n, h, w, c, ld, k, k, s, s, p, p, oh, ow, 0, G.ptr(y), ld, None)
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert G.rel_err(G.from_nhwc(y, c), ref) < (1e-6 if dtype == K.THB_F32 else 2e-3)
+
+
+@pytest.mark.parametrize("dtype", [K.THB_F32, K.THB_F16])
+def test_affine_act_combine_copy(lib, G, oracle, dtype):
+    rng = np.random.default_rng(32)
+    n, c, h, w = 2, 20, 5, 6
+    half = dtype == K.THB_F16
+    rnd = (lambda a: a.astype(np.float16).astype(np.float32)) if half else (lambda a: a)
+    x = rnd(rng.standard_normal((n, c, h, w)).astype(np.float32))
+    x2 = rnd(rng.standard_normal((n, c, h, w)).astype(np.float32))
+    gamma, beta = rng.uniform(0.8, 1.2, c).astype(np.float32), rng.standard_normal(c).astype(np.float32)
+    mean, var = rng.standard_normal(c).astype(np.float32), rng.uniform(0.5, 1.5, c).astype(np.float32)
+    ref = oracle.threshold(oracle.batchnorm(x, gamma, beta, mean, var, 1e-5), 0, 0)
+    invstd = (1.0 / np.sqrt(var.astype(np.float64) + 1e-5)).astype(np.float32)
+    scale = invstd * gamma
+    shift = beta - mean * scale
+    xt, ld = G.to_nhwc(x, dtype)
+    x2t, _ = G.to_nhwc(x2, dtype)
+    y = torch.zeros_like(xt)
+    st, sh = G.dev(scale), G.dev(shift)
+    act = K.Act(K.ACT_THRESHOLD, 0.0, 0.0, 0.0, None)
+    assert lib.thb_affine_act(dtype, G.ptr(xt), n * h * w, c, ld, G.ptr(st), G.ptr(sh), C.byref(act), G.ptr(y), ld, None) == 0
+    torch.cuda.synchronize()
+    assert G.rel_err(G.from_nhwc(y, c), ref) < (2e-6 if not half else 2e-3)
+    # two-input CAddTable = a - b, three-input = 2a + b + c
+    for ins, coefs, refv in (((xt, x2t), (1.0, -1.0), oracle.caddtable([x, x2])),
+                             ((xt, xt, x2t, xt), (1.0, 1.0, 1.0, 1.0), oracle.caddtable([x, x2, x]))):
+        ptrs = (C.c_void_p * len(ins))(*[t.data_ptr() for t in ins])
+        lds = (C.c_int * len(ins))(*[ld] * len(ins))
+        cf = (C.c_float * len(ins))(*coefs)
+        assert lib.thb_combine(dtype, len(ins), ptrs, lds, cf, n * h * w, c, G.ptr(y), ld, None) == 0
+        torch.cuda.synchronize()
+        assert G.rel_err(G.from_nhwc(y, c), refv) < (1e-6 if not half else 2e-3)
+    # channel-slice copy = JoinTable along channels
+    al = K.ALIGN[dtype]
+    c1 = 2 * al
+    a = rnd(rng.standard_normal((n, c1, h, w)).astype(np.float32))
+    at, ald = G.to_nhwc(a, dtype)
+    wide = torch.zeros((n, h, w, c1 + ld), dtype=xt.dtype, device="cuda")
+    assert lib.thb_copy_channels(dtype, G.ptr(at), n * h * w, c1, ald, G.ptr(wide), c1 + ld, None) == 0
+    off = C.c_void_p(wide.data_ptr() + c1 * K.ESIZE[dtype])
+    assert lib.thb_copy_channels(dtype, G.ptr(xt), n * h * w, c, ld, off, c1 + ld, None) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(G.from_nhwc(wide, c1 + c), oracle.join([a, x]))
+
+
+@pytest.mark.parametrize("dtype", [K.THB_F32, K.THB_F16])
+def test_softmax(lib, G, oracle, dtype):
+    rng = np.random.default_rng(33)
+    x = (rng.standard_normal((5, 1000)) * 4).astype(np.float32)
+    if dtype == K.THB_F16:
+        x = x.astype(np.float16).astype(np.float32)
+    ref = oracle.softmax(x)
+    td = torch.float32 if dtype == K.THB_F32 else torch.float16
+    xt = G.dev(x).to(td)
+    y = torch.zeros_like(xt)
+    assert lib.thb_softmax(dtype, G.ptr(xt), 5, 1000, 1000, G.ptr(y), 1000, None) == 0
+    torch.cuda.synchronize()
+    assert G.rel_err(y.float().cpu().numpy(), ref) < (1e-5 if dtype == K.THB_F32 else 2e-3)
+
+
+@pytest.mark.parametrize("dtype", [K.THB_F32, K.THB_F16])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_fullconv_gemm_col2im(lib, G, oracle, dtype, with_bias):
+    """SpatialFullConvolution = 1x1 convolution to the column matrix, then the col2im gather;
+    with a bias the reference result is 11*deconv + bias."""
+    rng = np.random.default_rng(34)
+    n, cin, h, w, cout, k, s, p = 2, 24, 6, 5, 12, 4, 2, 1
+    half = dtype == K.THB_F16
+    rnd = (lambda a: a.astype(np.float16).astype(np.float32)) if half else (lambda a: a)
+    x = rnd(rng.standard_normal((n, cin, h, w)).astype(np.float32))
+    wt = rnd((rng.standard_normal((cin, cout, k, k)) * 0.1).astype(np.float32))
+    bias = rng.standard_normal(cout).astype(np.float32) if with_bias else None
+    ref = oracle.fullconv2d(x, wt, bias, (s, s), (p, p), (0, 0))
+    al = K.ALIGN[dtype]
+    cp = G.ru(cout, al)
+    # column index (kh*kW + kw)*cp + co  <-  W[ci][co][kh][kw]
+    w1 = np.zeros((k * k * cp, cin, 1, 1), np.float32)
+    for kh in range(k):
+        for kw in range(k):
+            w1[(kh * k + kw) * cp:(kh * k + kw) * cp + cout, :, 0, 0] = wt[:, :, kh, kw].T
+    conv = G.Conv(lib, dtype, x.shape, w1)
+    xt, _ = G.to_nhwc(x, dtype)
+    cols = conv.run(xt)
+    oh, ow = ref.shape[2:]
+    y = torch.zeros((n, oh, ow, cp), dtype=xt.dtype, device="cuda")
+    bt = G.dev(bias) if with_bias else None
+    rc = lib.thb_col2im(dtype, G.ptr(cols), n, h, w, cout, k, k, s, s, p, p, oh, ow, conv.d.out_ld, 11.0, G.ptr(bt), None,
+                        G.ptr(y), cp, None)
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert G.rel_err(G.from_nhwc(y, cout), ref) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [K.THB_F32, K.THB_F16, K.THB_U8])
+def test_pre_and_postprocess(lib, G, oracle, dtype):
+    rng = np.random.default_rng(35)
+    n, c, h, w = 3, 3, 9, 10
+    x = rng.random((n, c, h, w), dtype=np.float32)
+    mean, std = np.array([0.45, 0.4, 0.5], np.float32), np.array([0.225, 0.25, 0.2], np.float32)
+    norm = oracle.normalize(x, mean, std)
+    xd = G.dev(x)
+    mt, st = mean, std
+    ld = K.ALIGN[dtype]
+    tdt = {K.THB_F32: torch.float32, K.THB_F16: torch.float16, K.THB_U8: torch.uint8}[dtype]
+    y = torch.zeros((n, h, w, ld), dtype=tdt, device="cuda")
+    qsub = qmult = 0.0
+    if dtype == K.THB_U8:
+        mm = G.dzeros(2, torch.float32)
+        assert lib.thb_minmax_normalized(G.ptr(xd), n, c, h, w, mt.ctypes.data, st.ctypes.data, G.ptr(mm), None) == 0
+        torch.cuda.synchronize()
+        mn, mx = (float(v) for v in mm.cpu())
+        refq, rsub, rmult = oracle.lowp_quantize(norm)
+        assert mn == rsub
+        qsub, qmult = mn, float(np.float32(255.0 / (np.float64(np.float32(mx) - np.float32(mn)))))
+        assert qmult == rmult
+    rc = lib.thb_preprocess(G.ptr(xd), G.ptr(xd), n, c, h, w, mt.ctypes.data, st.ctypes.data, dtype, G.ptr(y), ld,
+                            qsub, qmult, None)
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert np.array_equal(xd.cpu().numpy(), norm)          # in-place normalisation of the fp32 input
+    got = G.from_nhwc(y, c)
+    if dtype == K.THB_U8:
+        assert np.array_equal(got, refq)
+    elif dtype == K.THB_F32:
+        assert np.array_equal(got, norm)
+    else:
+        assert np.array_equal(got, norm.astype(np.float16).astype(np.float32))
+    # back to NCHW fp32
+    out = G.dzeros((n, c, h, w), torch.float32)
+    inv = float(np.float32(1.0 / np.float64(np.float32(qmult)))) if dtype == K.THB_U8 else 1.0
+    assert lib.thb_postprocess(G.ptr(y), dtype, n, h, w, c, ld, qsub, inv, G.ptr(out), None) == 0
+    torch.cuda.synchronize()
+    if dtype == K.THB_U8:
+        assert np.array_equal(out.cpu().numpy(), oracle.lowp_dequantize(refq, rsub, rmult))
+    else:
+        assert np.array_equal(out.cpu().numpy(), got)

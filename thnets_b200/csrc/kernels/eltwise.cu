@@ -1,0 +1,597 @@
+// HBM-bound kernels of the forward pass: layout/precision boundary, pooling, per-channel affine +
+// activation, tensor combination, channel-slice copies, softmax, col2im gather, u8 helpers.
+// All of them walk channels-innermost tensors in 16-byte channel vectors so that every global access
+// of a warp is a run of full sectors.
+#include "common.cuh"
+#include <float.h>
+#include <math.h>
+
+namespace {
+
+// ---- 16-byte channel vectors --------------------------------------------------------------------
+template <typename T> struct Vec;
+template <> struct Vec<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float *p, float (&v)[4])
+    {
+        float4 t = *reinterpret_cast<const float4 *>(p);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    }
+    static __device__ __forceinline__ void store(float *p, const float (&v)[4])
+    {
+        *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Vec<__half> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __half *p, float (&v)[8])
+    {
+        uint4 t = *reinterpret_cast<const uint4 *>(p);
+        const __half2 *h = reinterpret_cast<const __half2 *>(&t);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float2 f = __half22float2(h[i]);
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store(__half *p, const float (&v)[8])
+    {
+        uint4 t;
+        __half2 *h = reinterpret_cast<__half2 *>(&t);
+#pragma unroll
+        for (int i = 0; i < 4; i++) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4 *>(p) = t;
+    }
+};
+template <> struct Vec<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16 *p, float (&v)[8])
+    {
+        uint4 t = *reinterpret_cast<const uint4 *>(p);
+        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&t);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float2 f = __bfloat1622float2(h[i]);
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16 *p, const float (&v)[8])
+    {
+        uint4 t;
+        __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&t);
+#pragma unroll
+        for (int i = 0; i < 4; i++) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4 *>(p) = t;
+    }
+};
+template <> struct Vec<uint8_t> {
+    static constexpr int N = 16;
+    static __device__ __forceinline__ void load(const uint8_t *p, float (&v)[16])
+    {
+        uint4 t = *reinterpret_cast<const uint4 *>(p);
+        const uint8_t *b = reinterpret_cast<const uint8_t *>(&t);
+#pragma unroll
+        for (int i = 0; i < 16; i++) v[i] = (float)b[i];
+    }
+    static __device__ __forceinline__ void store(uint8_t *p, const float (&v)[16])
+    {
+        uint4 t;
+        uint8_t *b = reinterpret_cast<uint8_t *>(&t);
+#pragma unroll
+        for (int i = 0; i < 16; i++) b[i] = (uint8_t)(int)v[i];
+        *reinterpret_cast<uint4 *>(p) = t;
+    }
+};
+
+inline int nblocks(long n, int bs = 256) { return (int)((n + bs - 1) / bs); }
+
+#define DISPATCH_FLOAT_DTYPE(dtype, CALL)                         \
+    switch (dtype) {                                               \
+    case THB_F32: { using T = float; CALL; break; }                \
+    case THB_F16: { using T = __half; CALL; break; }               \
+    case THB_BF16: { using T = __nv_bfloat16; CALL; break; }       \
+    default: return THB_ERR_UNSUPPORTED;                           \
+    }
+#define DISPATCH_ANY_DTYPE(dtype, CALL)                            \
+    switch (dtype) {                                               \
+    case THB_F32: { using T = float; CALL; break; }                \
+    case THB_F16: { using T = __half; CALL; break; }               \
+    case THB_BF16: { using T = __nv_bfloat16; CALL; break; }       \
+    case THB_U8: { using T = uint8_t; CALL; break; }               \
+    default: return THB_ERR_UNSUPPORTED;                           \
+    }
+
+// ---- preprocess: NCHW fp32 -> normalised NHWC T ---------------------------------------------------
+template <typename T>
+__global__ void preprocess_kernel(const float *x, float *x_inplace, int N, int C, long HW, float3 mean, float3 std_,
+                                  T *y, int y_ld, float q_min, float q_mult)
+{
+    constexpr int VN = Vec<T>::N;
+    const long pix = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (pix >= (long)N * HW) return;
+    const long n = pix / HW, hw = pix - n * HW;
+    const float m[3] = {mean.x, mean.y, mean.z}, sd[3] = {std_.x, std_.y, std_.z};
+    const float zr = roundf(q_min * q_mult);
+    const int Cpad = (C + VN - 1) / VN * VN;
+    for (int c0 = 0; c0 < Cpad; c0 += VN) {
+        float v[VN];
+#pragma unroll
+        for (int i = 0; i < VN; i++) {
+            const int c = c0 + i;
+            float val = 0.f;
+            if (c < C) {
+                const long idx = (n * C + c) * HW + hw;
+                val = x[idx];
+                if (c < 3) val = __fdiv_rn(__fsub_rn(val, m[c]), sd[c]);
+                if (x_inplace) x_inplace[idx] = val;
+                if (sizeof(T) == 1) val = (float)(((int)(roundf(val * q_mult) - zr)) & 255);
+            }
+            v[i] = val;
+        }
+        Vec<T>::store(y + pix * y_ld + c0, v);
+    }
+}
+
+// u8 HWC images -> normalised NHWC T (thapi.c:20-46: multiply by 0.003921568f and by 1/std)
+template <typename T>
+__global__ void preprocess_images_kernel(const uint8_t *img, int N, int H, int W, int stride, int cp, int bgr, float3 mean,
+                                         float3 istd, T *y, int y_ld)
+{
+    constexpr int VN = Vec<T>::N;
+    const long pix = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (pix >= (long)N * H * W) return;
+    const long n = pix / ((long)H * W);
+    const int hw = (int)(pix - n * (long)H * W), h = hw / W, w = hw - h * W;
+    const uint8_t *src = img + ((size_t)n * H + h) * stride + (size_t)w * cp;
+    const float m[3] = {mean.x, mean.y, mean.z}, is[3] = {istd.x, istd.y, istd.z};
+    float v[VN];
+#pragma unroll
+    for (int i = 0; i < VN; i++) {
+        float val = 0.f;
+        if (i < cp) {
+            const int sc = bgr ? cp - 1 - i : i;
+            val = __fmul_rn(__fsub_rn(__fmul_rn((float)src[sc], 0.003921568f), m[i]), is[i]);
+        }
+        v[i] = val;
+    }
+    Vec<T>::store(y + pix * y_ld, v);
+}
+
+__global__ void minmax_kernel(const float *x, int C, long HW, long total, float3 mean, float3 std_, float *minmax)
+{
+    const float m[3] = {mean.x, mean.y, mean.z}, sd[3] = {std_.x, std_.y, std_.z};
+    float mn = 0.f, mx = 0.f;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const int c = (int)((i / HW) % C);
+        float v = x[i];
+        if (c < 3) v = __fdiv_rn(__fsub_rn(v, m[c]), sd[c]);
+        mn = fminf(mn, v);
+        mx = fmaxf(mx, v);
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    if ((threadIdx.x & 31) == 0) {
+        // mn <= 0 <= mx: negative floats order like their unsigned bit patterns, non-negative like signed ints
+        if (mn < 0.f) atomicMax(reinterpret_cast<unsigned int *>(minmax), __float_as_uint(mn));
+        if (mx > 0.f) atomicMax(reinterpret_cast<int *>(minmax + 1), __float_as_int(mx));
+    }
+}
+
+// ---- NHWC Tin -> NCHW Tout through a 32x32 shared-memory transpose ---------------------------------
+template <typename Tin, typename Tout>
+__global__ void nhwc_to_nchw_kernel(const Tin *x, int HW, int C, int x_ld, float q_sub, float q_invmult, Tout *y)
+{
+    __shared__ float tile[32][33];
+    const int n = blockIdx.z, hw0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int hw = hw0 + r, c = c0 + threadIdx.x;
+        float v = 0.f;
+        if (hw < HW && c < C) {
+            v = dt<Tin>::ld(x + ((size_t)n * HW + hw) * x_ld + c);
+            if (sizeof(Tin) == 1) v = __fadd_rn(__fmul_rn(v, q_invmult), q_sub);
+        }
+        tile[r][threadIdx.x] = v;
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int c = c0 + r, hw = hw0 + threadIdx.x;
+        if (hw < HW && c < C) {
+            dt<Tout>::st(y + ((size_t)n * C + c) * HW + hw, tile[threadIdx.x][r]);
+        }
+    }
+}
+
+// ---- pooling ------------------------------------------------------------------------------------------
+template <typename T, bool IS_MAX>
+__global__ void pool_kernel(const T *x, int N, int H, int W, int C, int x_ld, int kH, int kW, int dH, int dW, int padH,
+                            int padW, int oH, int oW, int count_include_pad, T *y, int y_ld)
+{
+    constexpr int VN = Vec<T>::N;
+    const int cvecs = (C + VN - 1) / VN;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)N * oH * oW * cvecs) return;
+    const int cv = (int)(idx % cvecs);
+    const long opix = idx / cvecs;
+    const int ow = (int)(opix % oW), oh = (int)((opix / oW) % oH);
+    const long n = opix / ((long)oW * oH);
+    int hs = oh * dH - padH, ws = ow * dW - padW;
+    float acc[VN];
+    int he, we, div = 1;
+    if (IS_MAX) {
+        he = min(hs + kH, H); we = min(ws + kW, W);
+        hs = max(hs, 0); ws = max(ws, 0);
+#pragma unroll
+        for (int i = 0; i < VN; i++) acc[i] = sizeof(T) == 1 ? 0.f : -FLT_MAX;
+    } else {
+        he = min(hs + kH, H + padH); we = min(ws + kW, W + padW);
+        const int pool = (he - hs) * (we - ws);
+        hs = max(hs, 0); ws = max(ws, 0);
+        he = min(he, H); we = min(we, W);
+        div = count_include_pad ? pool : (he - hs) * (we - ws);
+#pragma unroll
+        for (int i = 0; i < VN; i++) acc[i] = 0.f;
+    }
+    for (int h = hs; h < he; h++)
+        for (int w = ws; w < we; w++) {
+            float v[VN];
+            Vec<T>::load(x + ((size_t)(n * H + h) * W + w) * x_ld + cv * VN, v);
+#pragma unroll
+            for (int i = 0; i < VN; i++) {
+                if (IS_MAX) acc[i] = v[i] > acc[i] ? v[i] : acc[i];
+                else acc[i] += v[i];
+            }
+        }
+    if (!IS_MAX) {
+#pragma unroll
+        for (int i = 0; i < VN; i++) acc[i] = acc[i] / (float)div;
+    }
+    Vec<T>::store(y + (size_t)opix * y_ld + cv * VN, acc);
+}
+
+// ---- y = act(x*scale[c] + shift[c]) ----------------------------------------------------------------------
+template <typename T>
+__global__ void affine_act_kernel(const T *x, long pixels, int C, int x_ld, const float *scale, const float *shift,
+                                  thb_act act, T *y, int y_ld)
+{
+    constexpr int VN = Vec<T>::N;
+    const int cvecs = (C + VN - 1) / VN;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= pixels * cvecs) return;
+    const int cv = (int)(idx % cvecs);
+    const long pix = idx / cvecs;
+    float v[VN];
+    Vec<T>::load(x + pix * x_ld + cv * VN, v);
+#pragma unroll
+    for (int i = 0; i < VN; i++) {
+        const int c = cv * VN + i;
+        if (c < C) {
+            float t = v[i];
+            if (scale) t = t * scale[c] + (shift ? shift[c] : 0.f);
+            else if (shift) t = t + shift[c];
+            v[i] = thb_apply_act(t, act.kind, act.threshold, act.value, act.alpha,
+                                 act.kind == THB_ACT_PRELU ? act.slope[c] : 0.f);
+        } else v[i] = 0.f;
+    }
+    Vec<T>::store(y + pix * y_ld + cv * VN, v);
+}
+
+__global__ void u8_threshold_kernel(const uint8_t *x, long pixels, int C, int x_ld, int thr, int val, uint8_t *y, int y_ld)
+{
+    const int cvecs = (C + 15) / 16;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= pixels * cvecs) return;
+    const int cv = (int)(idx % cvecs);
+    const long pix = idx / cvecs;
+    uint4 t = *reinterpret_cast<const uint4 *>(x + pix * x_ld + cv * 16);
+    uint8_t *b = reinterpret_cast<uint8_t *>(&t);
+#pragma unroll
+    for (int i = 0; i < 16; i++) b[i] = (cv * 16 + i < C) ? (b[i] > thr ? b[i] : (uint8_t)val) : 0;
+    *reinterpret_cast<uint4 *>(y + pix * y_ld + cv * 16) = t;
+}
+
+struct CombineArgs {
+    const void *x[8];
+    int ld[8];
+    float coef[8];
+    int nin;
+};
+template <typename T>
+__global__ void combine_kernel(CombineArgs a, long pixels, int C, T *y, int y_ld)
+{
+    constexpr int VN = Vec<T>::N;
+    const int cvecs = (C + VN - 1) / VN;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= pixels * cvecs) return;
+    const int cv = (int)(idx % cvecs);
+    const long pix = idx / cvecs;
+    float acc[VN], v[VN];
+    Vec<T>::load(reinterpret_cast<const T *>(a.x[0]) + pix * a.ld[0] + cv * VN, v);
+#pragma unroll
+    for (int i = 0; i < VN; i++) acc[i] = a.coef[0] * v[i];
+    for (int k = 1; k < a.nin; k++) {
+        Vec<T>::load(reinterpret_cast<const T *>(a.x[k]) + pix * a.ld[k] + cv * VN, v);
+#pragma unroll
+        for (int i = 0; i < VN; i++) acc[i] = fmaf(a.coef[k], v[i], acc[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < VN; i++)
+        if (cv * VN + i >= C) acc[i] = 0.f;
+    Vec<T>::store(y + pix * y_ld + cv * VN, acc);
+}
+
+template <typename T>
+__global__ void copy_channels_kernel(const T *x, long pixels, int cvecs, int x_ld, T *y, int y_ld)
+{
+    constexpr int VN = Vec<T>::N;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= pixels * cvecs) return;
+    const int cv = (int)(idx % cvecs);
+    const long pix = idx / cvecs;
+    *reinterpret_cast<uint4 *>(y + pix * y_ld + cv * VN) = *reinterpret_cast<const uint4 *>(x + pix * x_ld + cv * VN);
+}
+
+// ---- softmax over channels, one warp per pixel; exp(-d) = 1/(poly(d))^8 in double, 0 from 13 up ------------
+__device__ __forceinline__ float exp_minus_approx(float d)
+{
+    const double x = (double)d;
+    if (x < 13.0) {
+        double y = 1.0 + x * (0.125 + x * (0.0078125 + x * (0.00032552083 + x * 1.0172526e-5)));
+        y *= y; y *= y; y *= y;
+        return (float)(1 / y);
+    }
+    return 0.f;
+}
+template <typename T>
+__global__ void softmax_kernel(const T *x, long pixels, int C, int x_ld, T *y, int y_ld)
+{
+    const long pix = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (pix >= pixels) return;
+    const T *xp = x + pix * x_ld;
+    T *yp = y + pix * y_ld;
+    float mx = -FLT_MAX;
+    for (int c = lane; c < C; c += 32) mx = fmaxf(mx, dt<T>::ld(xp + c));
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+    for (int c = lane; c < C; c += 32) sum += exp_minus_approx(mx - dt<T>::ld(xp + c));
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1 / sum;
+    for (int c = lane; c < C; c += 32) dt<T>::st(yp + c, exp_minus_approx(mx - dt<T>::ld(xp + c)) * inv);
+}
+
+// ---- col2im gather for the transposed convolution ---------------------------------------------------------
+template <typename T>
+__global__ void col2im_kernel(const T *cols, int N, int H, int W, int Cout, int kH, int kW, int dH, int dW, int padH,
+                              int padW, int oH, int oW, int cols_ld, int Cp, float beta, const float *bias, thb_act act,
+                              T *y, int y_ld)
+{
+    constexpr int VN = Vec<T>::N;
+    const int cvecs = Cp / VN;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)N * oH * oW * cvecs) return;
+    const int cv = (int)(idx % cvecs);
+    const long opix = idx / cvecs;
+    const int ow = (int)(opix % oW), oh = (int)((opix / oW) % oH);
+    const long n = opix / ((long)oW * oH);
+    float acc[VN];
+#pragma unroll
+    for (int i = 0; i < VN; i++) acc[i] = 0.f;
+    for (int kh = 0; kh < kH; kh++) {
+        const int hn = oh + padH - kh;
+        if (hn < 0 || hn % dH) continue;
+        const int h = hn / dH;
+        if (h >= H) continue;
+        for (int kw = 0; kw < kW; kw++) {
+            const int wn = ow + padW - kw;
+            if (wn < 0 || wn % dW) continue;
+            const int w = wn / dW;
+            if (w >= W) continue;
+            float v[VN];
+            Vec<T>::load(cols + ((size_t)(n * H + h) * W + w) * cols_ld + (size_t)(kh * kW + kw) * Cp + cv * VN, v);
+#pragma unroll
+            for (int i = 0; i < VN; i++) acc[i] += v[i];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < VN; i++) {
+        const int c = cv * VN + i;
+        if (c < Cout) {
+            float t = acc[i];
+            if (bias) t = beta * t + bias[c];
+            acc[i] = thb_apply_act(t, act.kind, act.threshold, act.value, act.alpha,
+                                   act.kind == THB_ACT_PRELU ? act.slope[c] : 0.f);
+        } else acc[i] = 0.f;
+    }
+    Vec<T>::store(y + (size_t)opix * y_ld + cv * VN, acc);
+}
+
+__global__ void u8_channel_sum_kernel(const uint8_t *x, long pixels, int C, int x_ld, int *csum)
+{
+    const long pix = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (pix >= pixels) return;
+    const uint8_t *p = x + pix * x_ld;
+    int s = 0;
+    for (int c0 = 0; c0 < C; c0 += 16) {
+        uint4 t = *reinterpret_cast<const uint4 *>(p + c0);
+        const uint8_t *b = reinterpret_cast<const uint8_t *>(&t);
+#pragma unroll
+        for (int i = 0; i < 16; i++)
+            if (c0 + i < C) s += b[i];
+    }
+    csum[pix] = s;
+}
+
+}  // namespace
+
+// =================================================================================================
+extern "C" {
+
+int thb_channel_align(int dtype) { return dtype == THB_F32 ? 4 : dtype == THB_U8 ? 16 : 8; }
+
+int thb_preprocess(const float *x, float *x_inplace, int N, int C, int H, int W, const float *mean3, const float *std3,
+                   int dtype, void *y, int y_ld, float q_sub, float q_mult, thb_stream s)
+{
+    const long HW = (long)H * W, pix = (long)N * HW;
+    if (pix == 0) return THB_OK;
+    float3 m = make_float3(mean3[0], mean3[1], mean3[2]), sd = make_float3(std3[0], std3[1], std3[2]);
+    DISPATCH_ANY_DTYPE(dtype, (preprocess_kernel<T><<<nblocks(pix), 256, 0, (cudaStream_t)s>>>(
+                                  x, x_inplace, N, C, HW, m, sd, (T *)y, y_ld, q_sub, q_mult)));
+    return THB_LAUNCH_CHECK("preprocess_kernel");
+}
+
+int thb_preprocess_images(const unsigned char *img, int N, int H, int W, int stride, int cp, int bgr, const float *mean3,
+                          const float *std3, int dtype, void *y, int y_ld, thb_stream s)
+{
+    const long pix = (long)N * H * W;
+    if (pix == 0) return THB_OK;
+    if (cp != 1 && cp != 3) return THB_ERR_ARG;
+    float3 m = make_float3(mean3[0], mean3[1], mean3[2]);
+    float3 is = make_float3(1 / std3[0], 1 / std3[1], 1 / std3[2]);
+    DISPATCH_FLOAT_DTYPE(dtype, (preprocess_images_kernel<T><<<nblocks(pix), 256, 0, (cudaStream_t)s>>>(
+                                    img, N, H, W, stride, cp, bgr, m, is, (T *)y, y_ld)));
+    return THB_LAUNCH_CHECK("preprocess_images_kernel");
+}
+
+int thb_minmax_normalized(const float *x, int N, int C, int H, int W, const float *mean3, const float *std3,
+                          float *minmax2, thb_stream s)
+{
+    const long HW = (long)H * W, total = (long)N * C * HW;
+    cudaError_t e = cudaMemsetAsync(minmax2, 0, 2 * sizeof(float), (cudaStream_t)s);
+    if (e != cudaSuccess) return thb_note_launch(e, "minmax memset");
+    if (total == 0) return THB_OK;
+    float3 m = make_float3(mean3[0], mean3[1], mean3[2]), sd = make_float3(std3[0], std3[1], std3[2]);
+    int blocks = nblocks(total);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    minmax_kernel<<<blocks, 256, 0, (cudaStream_t)s>>>(x, C, HW, total, m, sd, minmax2);
+    return THB_LAUNCH_CHECK("minmax_kernel");
+}
+
+int thb_postprocess(const void *x, int dtype, int N, int H, int W, int C, int x_ld, float q_sub, float q_invmult,
+                    float *y, thb_stream s)
+{
+    const int HW = H * W;
+    if ((long)N * HW * C == 0) return THB_OK;
+    dim3 grid((HW + 31) / 32, (C + 31) / 32, N), block(32, 8);
+    DISPATCH_ANY_DTYPE(dtype, (nhwc_to_nchw_kernel<T, float><<<grid, block, 0, (cudaStream_t)s>>>(
+                                  (const T *)x, HW, C, x_ld, q_sub, q_invmult, y)));
+    return THB_LAUNCH_CHECK("nhwc_to_nchw_kernel");
+}
+
+int thb_to_nchw(int dtype, const void *x, int N, int H, int W, int C, int x_ld, void *y, thb_stream s)
+{
+    const int HW = H * W;
+    if ((long)N * HW * C == 0) return THB_OK;
+    dim3 grid((HW + 31) / 32, (C + 31) / 32, N), block(32, 8);
+    DISPATCH_ANY_DTYPE(dtype, (nhwc_to_nchw_kernel<T, T><<<grid, block, 0, (cudaStream_t)s>>>(
+                                  (const T *)x, HW, C, x_ld, 0.f, 1.f, (T *)y)));
+    return THB_LAUNCH_CHECK("nhwc_to_nchw_kernel");
+}
+
+int thb_maxpool(int dtype, const void *x, int N, int H, int W, int C, int x_ld, int kH, int kW, int dH, int dW, int padH,
+                int padW, int oH, int oW, void *y, int y_ld, thb_stream s)
+{
+    const int al = thb_channel_align(dtype);
+    const long total = (long)N * oH * oW * ((C + al - 1) / al);
+    if (total == 0) return THB_OK;
+    DISPATCH_ANY_DTYPE(dtype, (pool_kernel<T, true><<<nblocks(total), 256, 0, (cudaStream_t)s>>>(
+                                  (const T *)x, N, H, W, C, x_ld, kH, kW, dH, dW, padH, padW, oH, oW, 0, (T *)y, y_ld)));
+    return THB_LAUNCH_CHECK("pool_kernel<max>");
+}
+
+int thb_avgpool(int dtype, const void *x, int N, int H, int W, int C, int x_ld, int kH, int kW, int dH, int dW, int padH,
+                int padW, int oH, int oW, int count_include_pad, void *y, int y_ld, thb_stream s)
+{
+    const int al = thb_channel_align(dtype);
+    const long total = (long)N * oH * oW * ((C + al - 1) / al);
+    if (total == 0) return THB_OK;
+    DISPATCH_FLOAT_DTYPE(dtype, (pool_kernel<T, false><<<nblocks(total), 256, 0, (cudaStream_t)s>>>(
+                                    (const T *)x, N, H, W, C, x_ld, kH, kW, dH, dW, padH, padW, oH, oW,
+                                    count_include_pad, (T *)y, y_ld)));
+    return THB_LAUNCH_CHECK("pool_kernel<avg>");
+}
+
+int thb_affine_act(int dtype, const void *x, long pixels, int C, int x_ld, const float *scale, const float *shift,
+                   const thb_act *act, void *y, int y_ld, thb_stream s)
+{
+    const int al = thb_channel_align(dtype);
+    const long total = pixels * ((C + al - 1) / al);
+    if (total == 0) return THB_OK;
+    thb_act a = {THB_ACT_NONE, 0, 0, 0, nullptr};
+    if (act) a = *act;
+    DISPATCH_FLOAT_DTYPE(dtype, (affine_act_kernel<T><<<nblocks(total), 256, 0, (cudaStream_t)s>>>(
+                                    (const T *)x, pixels, C, x_ld, scale, shift, a, (T *)y, y_ld)));
+    return THB_LAUNCH_CHECK("affine_act_kernel");
+}
+
+int thb_u8_threshold(const void *x, long pixels, int C, int x_ld, int thr, int val, void *y, int y_ld, thb_stream s)
+{
+    const long total = pixels * ((C + 15) / 16);
+    if (total == 0) return THB_OK;
+    u8_threshold_kernel<<<nblocks(total), 256, 0, (cudaStream_t)s>>>((const uint8_t *)x, pixels, C, x_ld, thr, val,
+                                                                     (uint8_t *)y, y_ld);
+    return THB_LAUNCH_CHECK("u8_threshold_kernel");
+}
+
+int thb_combine(int dtype, int nin, const void *const *x_host, const int *ld_host, const float *coef_host, long pixels,
+                int C, void *y, int y_ld, thb_stream s)
+{
+    if (nin < 1 || nin > 8) return THB_ERR_UNSUPPORTED;
+    CombineArgs a;
+    a.nin = nin;
+    for (int i = 0; i < nin; i++) {
+        a.x[i] = x_host[i];
+        a.ld[i] = ld_host[i];
+        a.coef[i] = coef_host[i];
+    }
+    const int al = thb_channel_align(dtype);
+    const long total = pixels * ((C + al - 1) / al);
+    if (total == 0) return THB_OK;
+    DISPATCH_FLOAT_DTYPE(dtype, (combine_kernel<T><<<nblocks(total), 256, 0, (cudaStream_t)s>>>(a, pixels, C, (T *)y, y_ld)));
+    return THB_LAUNCH_CHECK("combine_kernel");
+}
+
+int thb_copy_channels(int dtype, const void *x, long pixels, int C, int x_ld, void *y, int y_ld, thb_stream s)
+{
+    const int al = thb_channel_align(dtype);
+    const int cvecs = (C + al - 1) / al;
+    const long total = pixels * cvecs;
+    if (total == 0) return THB_OK;
+    DISPATCH_ANY_DTYPE(dtype, (copy_channels_kernel<T><<<nblocks(total), 256, 0, (cudaStream_t)s>>>(
+                                  (const T *)x, pixels, cvecs, x_ld, (T *)y, y_ld)));
+    return THB_LAUNCH_CHECK("copy_channels_kernel");
+}
+
+int thb_softmax(int dtype, const void *x, long pixels, int C, int x_ld, void *y, int y_ld, thb_stream s)
+{
+    if (pixels == 0) return THB_OK;
+    DISPATCH_FLOAT_DTYPE(dtype, (softmax_kernel<T><<<nblocks(pixels * 32), 256, 0, (cudaStream_t)s>>>(
+                                    (const T *)x, pixels, C, x_ld, (T *)y, y_ld)));
+    return THB_LAUNCH_CHECK("softmax_kernel");
+}
+
+int thb_col2im(int dtype, const void *cols, int N, int H, int W, int Cout, int kH, int kW, int dH, int dW, int padH,
+               int padW, int oH, int oW, int cols_ld, float beta, const float *bias, const thb_act *act, void *y,
+               int y_ld, thb_stream s)
+{
+    const int al = thb_channel_align(dtype);
+    const int Cp = (Cout + al - 1) / al * al;
+    const long total = (long)N * oH * oW * (Cp / al);
+    if (total == 0) return THB_OK;
+    thb_act a = {THB_ACT_NONE, 0, 0, 0, nullptr};
+    if (act) a = *act;
+    DISPATCH_FLOAT_DTYPE(dtype, (col2im_kernel<T><<<nblocks(total), 256, 0, (cudaStream_t)s>>>(
+                                    (const T *)cols, N, H, W, Cout, kH, kW, dH, dW, padH, padW, oH, oW, cols_ld, Cp, beta,
+                                    bias, a, (T *)y, y_ld)));
+    return THB_LAUNCH_CHECK("col2im_kernel");
+}
+
+int thb_u8_channel_sum(const void *x, long pixels, int C, int x_ld, int *csum, thb_stream s)
+{
+    if (pixels == 0) return THB_OK;
+    u8_channel_sum_kernel<<<nblocks(pixels), 256, 0, (cudaStream_t)s>>>((const uint8_t *)x, pixels, C, x_ld, csum);
+    return THB_LAUNCH_CHECK("u8_channel_sum_kernel");
+}
+
+}  // extern "C"
