@@ -260,6 +260,8 @@ float THB200_LastDeviceMs(THNETWORK *network);
  * THProcessFloat call and returns the mean device time per forward in milliseconds (< 0 on error). */
 float THB200_TimeForward(THNETWORK *network, int iters);
 int THB200_KernelLaunches(void);
+/* one text line per operator of the lowered network; returns the length written, < 0 on error */
+int THB200_DescribeNetwork(THNETWORK *network, char *buf, int len);
 const char *THB200_LastErrorString(void);
 
 #ifdef __cplusplus

@@ -1,0 +1,144 @@
+"""Whole-network parity through the public C API (THLoadNetwork / THCreate*Network / THProcessFloat)
+on the GPU, against the CPU oracle on the same seeded fixture files and inputs.
+
+The five benchmark architectures run at reduced width / size so that the CPU side finishes in seconds.
+Metric: max|y - ref| / max|ref| per output tensor; fp32 <= 1e-4, fp16/bf16 <= 1e-2; uint8 bit-exact.
+"""
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+os.environ.setdefault("THB200_NO_EXIT", "1")
+
+from thnets_b200 import fixtures as fx  # noqa: E402
+from thnets_b200.capi import THNets  # noqa: E402
+
+# bf16 keeps 8 mantissa bits (unit round-off 3.9e-3, fp16: 4.9e-4): a ten-layer network lands at a few 1e-2
+TOL = {0: 1e-4, 1: 1e-2, 2: 6e-2}
+
+NETS = {
+    "alexnet_owt": (lambda: fx.alexnet_owt(width=0.25, size=224, classes=50, fc=128), 1, "t7"),
+    "alexnet_owt_b5": (lambda: fx.alexnet_owt(width=0.25, size=224, classes=50, fc=128), 5, "t7"),
+    "resnet18": (lambda: fx.resnet18(width=0.25, size=64, classes=10), 4, "py"),
+    "resnet50": (lambda: fx.resnet50(width=0.125, size=64, classes=10), 3, "py"),
+    "segnet": (lambda: fx.segnet(width=0.5, size=32, classes=21), 2, "py"),
+    "segnet_bias": (lambda: fx.segnet(width=0.5, size=32, classes=5, deconv_bias=0.1), 2, "py"),
+    "vgg16": (lambda: fx.vgg16(width=0.125, size=32, classes=10, fc=64), 2, "t7"),
+    "resnet18_b9": (lambda: fx.resnet18(width=0.25, size=64, classes=10), 9, "py"),
+}
+
+
+@pytest.fixture(scope="module")
+def th():
+    return THNets()
+
+
+def rel_err(a, ref):
+    return float(np.abs(np.asarray(a, np.float64) - np.asarray(ref, np.float64)).max() / max(np.abs(ref).max(), 1e-30))
+
+
+def _load(th, g, kind, tmp_path, name):
+    if kind == "t7":
+        d = str(tmp_path / name)
+        fx.write_torch7(g, d)
+        return th.load_network(d)
+    p = str(tmp_path / (name + ".net"))
+    fx.write_pymodel(g, p)
+    h = th.load_network(p)
+    th.set_stats(h, g.mean, g.std)
+    return h
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2], ids=["fp32", "fp16", "bf16"])
+@pytest.mark.parametrize("name", list(NETS))
+def test_network_parity(th, oracle, tmp_path, name, mode):
+    build, batch, kind = NETS[name]
+    g = build()
+    x = g.make_input(batch)
+    ref = oracle.run(g, x)
+    h = _load(th, g, kind, tmp_path, name)
+    th.lib.THB200_SetPrecision(mode)
+    hc = th.lib.THCreateCudaNetwork(h)
+    th.lib.THB200_SetPrecision(0)
+    assert hc, th.lib.THB200_LastErrorString()
+    th.free_network(h)  # the converted network must own everything it needs
+    out, ow, oh = th.process_float(hc, x)
+    assert out.size == ref.size, (out.size, ref.shape)
+    if ref.ndim == 4:
+        assert (ow, oh) == (ref.shape[3], ref.shape[2])
+    else:
+        assert (ow, oh) == (1, 1)
+    err = rel_err(out, ref.ravel())
+    assert err < TOL[mode], (name, mode, err)
+    # a second forward on the same handle gives the same answer (nothing is consumed by a forward)
+    out2, _, _ = th.process_float(hc, x)
+    assert np.array_equal(out, out2)
+    th.free_network(hc)
+
+
+def test_unconverted_network_runs_on_gpu_fp32(th, oracle, tmp_path):
+    g = fx.alexnet_owt(width=0.25, size=224, classes=50, fc=128)
+    x = g.make_input(1)
+    h = _load(th, g, "t7", tmp_path, "alex")
+    buf = np.array(x, copy=True)
+    out, _, _ = th.process_float(h, buf, copy_input=False)
+    assert rel_err(out, oracle.run(g, x).ravel()) < 1e-4
+    # the caller's buffer now holds the normalised input, as with the reference (thapi.c:396-403)
+    assert np.array_equal(buf, oracle.normalize(x, g.mean, g.std))
+    th.free_network(h)
+
+
+@pytest.mark.parametrize("batch", [1, 2, 5])
+def test_lowp_vgg_bit_exact(th, oracle, tmp_path, batch):
+    """THMakeSpatial + THCreateLowpNetwork: every output byte equals the oracle's (dequantised floats equal)."""
+    size, rng = 32, 8.0
+    g = fx.vgg16(width=0.125, size=size, classes=10, fc=64)
+    x = g.make_input(batch)
+    ref = oracle.run_lowp(g, x, rng, size)
+    h = _load(th, g, "t7", tmp_path, "vgg")
+    th.make_spatial(h, size)
+    hl = th.create_lowp_network(h, rng)
+    th.free_network(h)
+    out, ow, oh = th.process_float(hl, x)
+    assert (ow, oh) == (1, 1)
+    assert np.array_equal(out, ref.ravel()), np.abs(out - ref.ravel()).max()
+    out2, _, _ = th.process_float(hl, x)      # the reference loses its scales after one forward; this does not
+    assert np.array_equal(out2, out)
+    th.free_network(hl)
+
+
+def test_lowp_rejects_what_the_reference_rejects(th, tmp_path):
+    g = fx.resnet18(width=0.25, size=64, classes=10)
+    h = _load(th, g, "py", tmp_path, "r18")
+    hl = th.lib.THCreateLowpNetwork(h, 8.0)
+    if hl:
+        x = g.make_input(1)
+        n = th.lib.THProcessFloat  # forward must fail: BatchNorm has no lowp implementation
+        import ctypes as C
+        res = C.POINTER(C.c_float)()
+        ow, oh = C.c_int(), C.c_int()
+        assert n(hl, x.ctypes.data_as(C.c_void_p), 1, 64, 64, 3, C.byref(res), C.byref(ow), C.byref(oh)) == 0
+        assert b"Lowp" in th.lib.THB200_LastErrorString()
+        th.free_network(hl)
+    th.free_network(h)
+
+
+def test_process_images_matches_float_path(th, oracle, tmp_path):
+    g = fx.alexnet_owt(width=0.25, size=224, classes=50, fc=128)
+    h = _load(th, g, "t7", tmp_path, "alex")
+    rng = np.random.default_rng(3)
+    for batch in (1, 3):
+        imgs = [rng.integers(0, 256, (224, 224, 3)).astype(np.uint8) for _ in range(batch)]
+        out, _, _ = th.process_images(h, imgs, bgr=0)
+        import ctypes as C
+        dst = np.empty((batch, 3, 224, 224), np.float32)
+        ptrs = (C.POINTER(C.c_ubyte) * batch)(*[i.ctypes.data_as(C.POINTER(C.c_ubyte)) for i in imgs])
+        oracle.lib.orc_images_to_float(ptrs, batch, 224, 224, 224 * 3, 3, g.mean.ctypes.data_as(C.POINTER(C.c_float)),
+                                       g.std.ctypes.data_as(C.POINTER(C.c_float)), 0, dst.ctypes.data_as(C.POINTER(C.c_float)))
+        plain = fx.Graph()
+        plain.nodes, plain.output = g.nodes, g.output   # same weights, identity statistics
+        ref = oracle.run(plain, dst)
+        assert rel_err(out, ref.ravel()) < 1e-4
+    th.free_network(h)

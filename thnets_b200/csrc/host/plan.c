@@ -1,0 +1,1134 @@
+/*
+ * Execution planner and runtime of a converted network.
+ *
+ * The reference's engines swap one function pointer per module and allocate every activation on
+ * every forward (cudnn/cudnn_basic.c:189-303, thapi.c:203-210, :405-416).  Here a network becomes,
+ * once per input shape and per GPU, a list of kernel launches over two resident arenas:
+ *   1. shape inference over the flat model (ranks and sizes as the reference's operators produce them);
+ *   2. fusion: convolution/Linear + BatchNorm + two-input CAddTable + Threshold/PReLU collapse into one
+ *      launch when each intermediate has a single consumer; BatchNorm + activation otherwise;
+ *   3. liveness-based packing of all activations into one arena; weights packed and uploaded once;
+ *   4. a batch is cut into contiguous slices, one per GPU; every GPU runs the whole list on its slice
+ *      and the slices of the result are gathered by peer copies into GPU 0 (nothing is reduced).
+ * Activations are channels-innermost ([N][H][W][ld]); the API's NCHW fp32 tensors are converted at the
+ * two ends by the pre/postprocess kernels.
+ */
+#include <cuda_runtime_api.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+#include "thb_internal.h"
+
+static char g_error[512];
+const char *thb_engine_error(void) { return g_error; }
+void thb_set_error(const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    if (th_debug) fprintf(stderr, "thb200: %s\n", g_error);
+}
+#define CU(call)                                                                                   \
+    do {                                                                                           \
+        cudaError_t e_ = (call);                                                                   \
+        if (e_ != cudaSuccess) {                                                                   \
+            thb_set_error("%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
+            return -1;                                                                             \
+        }                                                                                          \
+    } while (0)
+
+void *thb_host_alloc_pinned(size_t bytes)
+{
+    void *p = 0;
+    if (cudaHostAlloc(&p, bytes ? bytes : 1, cudaHostAllocPortable) != cudaSuccess) return 0;
+    return p;
+}
+void thb_host_free_pinned(void *p)
+{
+    if (p) cudaFreeHost(p);
+}
+
+/* ------------------------------------------------------------------------------------------------ */
+typedef struct {
+    int N, C, H, W, rank;
+    int flat, fC, fH, fW; /* flat: logical [N, C] view of a channels-innermost [N, fH, fW, fC] tensor */
+} shape;
+
+typedef struct {
+    int buf;   /* activation buffer id, -1: not materialised */
+    int ld;    /* pixel stride in elements */
+    int coff;  /* channel offset inside the buffer */
+    shape s;
+    float q_sub, q_mult; /* u8 mode */
+    int q_dyn;           /* u8 mode: the scale is measured per forward (network input) */
+} value;
+
+typedef struct {
+    size_t bytes, offset;
+    int first, last;
+} abuf;
+
+enum step_kind {
+    ST_CONV, ST_GEMV, ST_MAXPOOL, ST_AVGPOOL, ST_AFFINE, ST_U8THR, ST_COMBINE, ST_COPY, ST_SOFTMAX, ST_COL2IM,
+    ST_CSUM, ST_TO_NCHW
+};
+
+typedef struct {
+    int kind, dtype;
+    int nin, in_buf[8], in_ld[8], in_coff[8];
+    int out_buf, out_ld, out_coff;
+    int aux_buf; /* csum scratch (conv u8) */
+    float coef[8];
+    int N, H, W, C, oH, oW, kH, kW, dH, dW, padH, padW, flag;
+    long pixels;
+    const float *scale, *shift, *bias;
+    thb_act act;
+    float beta;
+    int thr, val;
+    thb_conv_desc conv;
+    thb_tmap *tmap;
+    const void *w; /* gemv weights */
+    int K, M;
+    int dyn_quant; /* conv u8 whose input scale is only known per forward (first layer) */
+    /* u8 conv constants needed to derive the per-forward parameters */
+    float w_sub, w_mult, out_sub, out_mult;
+    int flops_node; /* model node index of the conv (profiling) */
+} step;
+
+typedef struct instance {
+    int device, slice_n, slice_off;
+    cudaStream_t stream;
+    cudaEvent_t ev0, ev1;
+    void **allocs;
+    int nallocs, capallocs;
+    unsigned char *arena;
+    size_t arena_bytes;
+    float *d_in;          /* staged NCHW fp32 input */
+    unsigned char *d_img; /* staged u8 HWC images */
+    float *d_out;         /* NCHW fp32 result */
+    float *d_minmax;
+    int *d_status;
+    abuf *bufs;
+    int nbufs;
+    step *steps;
+    int nsteps;
+    value in_val, out_val;
+    shape out_shape;
+    long out_count;
+    float last_ms;
+} instance;
+
+struct thb_engine {
+    thb_model *model;
+    int mode, dtype, ngpus;
+    float range;
+    int strict_math;
+    /* shape the instances were planned for */
+    int N, C, H, W, rank, cp;
+    int built;
+    instance inst[8];
+    float *h_out;
+    size_t h_out_bytes;
+    float last_ms;
+    int peer_gather;
+};
+
+static int align_of(int dtype) { return thb_channel_align(dtype); }
+static int esize_of(int dtype) { return dtype == THB_F32 ? 4 : dtype == THB_U8 ? 1 : 2; }
+static int ru(int v, int m) { return (v + m - 1) / m * m; }
+
+/* ---- device allocations owned by an instance ---- */
+static void *dalloc(instance *I, size_t bytes)
+{
+    void *p = 0;
+    if (cudaMalloc(&p, bytes ? bytes : 16) != cudaSuccess) {
+        thb_set_error("cudaMalloc of %zu bytes failed on device %d", bytes, I->device);
+        return 0;
+    }
+    if (I->nallocs == I->capallocs) {
+        I->capallocs = I->capallocs ? I->capallocs * 2 : 64;
+        I->allocs = realloc(I->allocs, I->capallocs * sizeof(void *));
+    }
+    I->allocs[I->nallocs++] = p;
+    return p;
+}
+static void *dupload(instance *I, const void *host, size_t bytes)
+{
+    void *p = dalloc(I, bytes);
+    if (p && cudaMemcpy(p, host, bytes, cudaMemcpyHostToDevice) != cudaSuccess) {
+        thb_set_error("upload of %zu bytes failed", bytes);
+        return 0;
+    }
+    return p;
+}
+
+/* ---- shape rules ---- */
+static int conv_out(int in, int k, int d, int pad) { return (in + 2 * pad - k) / d + 1; }
+/* SpatialMaxPooling.c:196-210 / SpatialAveragePooling.c:120-139 */
+static int pool_out(int in, int k, int d, int pad, int ceil_mode, int any_pad)
+{
+    int o = ceil_mode ? (int)ceilf((float)(in - k + 2 * pad) / d) + 1 : (int)floorf((float)(in - k + 2 * pad) / d) + 1;
+    if (any_pad && (o - 1) * d >= in + pad) --o; /* the last window must start inside the image */
+    return o;
+}
+
+typedef struct {
+    thb_engine *E;
+    instance *I;
+    thb_model *M;
+    value *val;
+    int *uses;      /* consumer count per node (+1 for the output) */
+    int *absorbed;  /* node folded into an earlier launch */
+    int *leader;    /* node index at which the value of node i is produced */
+    int capbufs, capsteps;
+} planner;
+
+static int new_buf(planner *P, size_t bytes)
+{
+    instance *I = P->I;
+    if (I->nbufs == P->capbufs) {
+        P->capbufs = P->capbufs ? P->capbufs * 2 : 64;
+        I->bufs = realloc(I->bufs, P->capbufs * sizeof(abuf));
+    }
+    abuf *b = &I->bufs[I->nbufs];
+    b->bytes = (bytes + 255) & ~(size_t)255;
+    b->offset = 0;
+    b->first = b->last = -1;
+    return I->nbufs++;
+}
+static step *new_step(planner *P, int kind)
+{
+    instance *I = P->I;
+    if (I->nsteps == P->capsteps) {
+        P->capsteps = P->capsteps ? P->capsteps * 2 : 64;
+        I->steps = realloc(I->steps, P->capsteps * sizeof(step));
+    }
+    step *s = &I->steps[I->nsteps++];
+    memset(s, 0, sizeof(*s));
+    s->kind = kind;
+    s->dtype = P->E->dtype;
+    s->out_buf = s->aux_buf = -1;
+    for (int i = 0; i < 8; i++) s->in_buf[i] = -1;
+    s->flops_node = -1;
+    return s;
+}
+static void step_in(step *s, const value *v)
+{
+    s->in_buf[s->nin] = v->buf;
+    s->in_ld[s->nin] = v->ld;
+    s->in_coff[s->nin] = v->coff;
+    s->nin++;
+}
+/* fresh dense activation buffer for a value of shape `sh` */
+static void materialise(planner *P, value *v, shape sh)
+{
+    int al = align_of(P->E->dtype);
+    long pixels = (long)sh.N * sh.H * sh.W;
+    v->s = sh;
+    v->ld = ru(sh.C, al);
+    v->coff = 0;
+    v->buf = new_buf(P, (size_t)pixels * v->ld * esize_of(P->E->dtype));
+}
+static void step_out(step *s, const value *v)
+{
+    s->out_buf = v->buf;
+    s->out_ld = v->ld;
+    s->out_coff = v->coff;
+}
+
+static int sole_consumer(planner *P, int node)
+{
+    if (P->uses[node] != 1 || node == P->M->output) return -1;
+    for (int j = node + 1; j < P->M->nnodes; j++)
+        for (int k = 0; k < P->M->nodes[j].nin; k++)
+            if (P->M->nodes[j].in[k] == node) return j;
+    return -1;
+}
+
+static float *upload_floats(planner *P, const float *src, int n, int padded)
+{
+    float *tmp = calloc(padded, sizeof(float));
+    memcpy(tmp, src, sizeof(float) * n);
+    float *d = dupload(P->I, tmp, sizeof(float) * padded);
+    free(tmp);
+    return d;
+}
+
+static int fill_act(planner *P, thb_act *a, const thb_node *n, int C)
+{
+    a->kind = n->act_kind;
+    a->threshold = n->act_threshold;
+    a->value = n->act_value;
+    a->alpha = n->act_alpha;
+    a->slope = 0;
+    if (n->act_kind == THB_ACT_PRELU) {
+        float *tmp = malloc(sizeof(float) * C);
+        if (n->nslope && n->nslope != C) {
+            free(tmp);
+            thb_set_error("wrong number of input planes for PReLU (%d slopes, %d channels)", n->nslope, C);
+            return -1;
+        }
+        for (int i = 0; i < C; i++) tmp[i] = n->nslope ? n->slope[i] : n->slope[0];
+        a->slope = dupload(P->I, tmp, sizeof(float) * C);
+        free(tmp);
+        if (!a->slope) return -1;
+    }
+    return 0;
+}
+
+/* Emit the launch(es) of a convolution / Linear / transposed convolution and whatever folds into it.
+ * Returns the node whose value the launch produces. */
+static int plan_gemm_group(planner *P, int i)
+{
+    thb_engine *E = P->E;
+    thb_model *M = P->M;
+    thb_node *n = &M->nodes[i];
+    const value *in = &P->val[n->in[0]];
+    const int dtype = E->dtype, al = align_of(dtype);
+    shape is = in->s, os = is;
+    int is_linear = n->op == OP_LINEAR, is_deconv = n->op == OP_DECONV;
+
+    /* ---- geometry ---- */
+    int kH = n->kH, kW = n->kW, Cin = n->Cin, H = is.H, W = is.W, in_ld = in->ld, permute_hw = 0;
+    if (is_linear) {
+        long feat = is.flat ? (long)is.fC * is.fH * is.fW : (long)is.C * is.H * is.W;
+        if (feat != n->Cin) { thb_set_error("Linear expects %d inputs, got %ld", n->Cin, feat); return -1; }
+        if (is.flat || is.H * is.W > 1) {
+            /* the features are an NCHW flatten of a channels-innermost tensor: permute the weight's K axis */
+            int fH = is.flat ? is.fH : is.H, fW = is.flat ? is.fW : is.W;
+            if (in->coff) { thb_set_error("Linear on a channel slice is not supported"); return -1; }
+            permute_hw = fH * fW;
+            Cin = permute_hw * in->ld;
+            in_ld = Cin;
+        }
+        H = W = 1;
+        os.rank = is.N == 1 ? 1 : 2;
+        os.C = n->Cout; os.H = os.W = 1; os.flat = 0;
+    } else if (is_deconv) {
+        if (is.rank < 3) { thb_set_error("3D or 4D (batch mode) tensor is expected"); return -1; }
+        if (is.C != n->Cin) { thb_set_error("input channels and nInputPlane dont match"); return -1; }
+        os.C = n->Cout;
+        os.H = (is.H - 1) * n->dH - 2 * n->padH + n->kH + n->adjH;
+        os.W = (is.W - 1) * n->dW - 2 * n->padW + n->kW + n->adjW;
+    } else {
+        if (is.rank < 3) { thb_set_error("convolution needs a 3D or 4D input"); return -1; }
+        if (is.C != n->Cin) { thb_set_error("nInputPlane %d does not match input planes %d", n->Cin, is.C); return -1; }
+        os.C = n->Cout;
+        os.H = conv_out(is.H, kH, n->dH, n->padH);
+        os.W = conv_out(is.W, kW, n->dW, n->padW);
+        if (os.H < 1 || os.W < 1) { thb_set_error("Given input size: (%dx%dx%d). Output size is too small", is.C, is.H, is.W); return -1; }
+    }
+
+    /* ---- what folds in ---- */
+    int cur = i, bn = -1, comb = -1, act = -1, j;
+    if (dtype != THB_U8 && !is_deconv && (j = sole_consumer(P, cur)) >= 0 && M->nodes[j].op == OP_BN) { bn = j; cur = j; }
+    int res_node = -1;
+    float self_coef = 1.f, res_coef = 0.f;
+    if (dtype != THB_U8 && !is_deconv && (j = sole_consumer(P, cur)) >= 0 && M->nodes[j].op == OP_COMBINE && M->nodes[j].nin == 2) {
+        int pos = M->nodes[j].in[0] == cur ? 0 : 1, other = M->nodes[j].in[1 - pos];
+        if (other != cur && other < i && P->val[other].buf >= 0 && !P->val[other].s.flat &&
+            (long)P->val[other].s.C == os.C && P->val[other].s.H == os.H && P->val[other].s.W == os.W) {
+            comb = j; cur = j; res_node = other;
+            self_coef = M->nodes[j].coef[pos];
+            res_coef = M->nodes[j].coef[1 - pos];
+        }
+    }
+    if ((j = sole_consumer(P, cur)) >= 0 && M->nodes[j].op == OP_ACT &&
+        (dtype != THB_U8 || M->nodes[j].act_kind == THB_ACT_THRESHOLD)) { act = j; cur = j; }
+    for (int k = i + 1; k <= cur; k++)
+        if (k == bn || k == comb || k == act) { P->absorbed[k] = 1; P->leader[k] = i; }
+
+    /* ---- per-channel scale / shift ---- */
+    float *scale = 0, *shift = 0;
+    if (dtype != THB_U8) {
+        int Cp = ru(n->Cout, 64);
+        float *hs = calloc(Cp, sizeof(float)), *hh = calloc(Cp, sizeof(float));
+        for (int c = 0; c < n->Cout; c++) {
+            float b = n->bias ? n->bias[c] : 0.f;
+            hs[c] = bn >= 0 ? M->nodes[bn].scale[c] : 1.f;
+            hh[c] = bn >= 0 ? M->nodes[bn].scale[c] * b + M->nodes[bn].shift[c] : b;
+        }
+        if (bn >= 0 && M->nodes[bn].C != n->Cout) { free(hs); free(hh); thb_set_error("batch-norm width mismatch"); return -1; }
+        if (bn >= 0) scale = dupload(P->I, hs, sizeof(float) * Cp);
+        if ((bn >= 0 || n->bias) && !is_deconv) shift = dupload(P->I, hh, sizeof(float) * Cp);
+        free(hs); free(hh);
+    }
+
+    value *out = &P->val[cur];
+
+    /* ---- small-batch Linear: weight-streaming GEMV ---- */
+    if (is_linear && dtype != THB_U8 && is.N <= 8) {
+        materialise(P, out, os);
+        step *s = new_step(P, ST_GEMV);
+        step_in(s, in);
+        step_out(s, out);
+        /* weight rows are as long as the physical feature vector (channel padding included, zero weights there) */
+        const int Kp = permute_hw ? Cin : in->ld;
+        s->N = is.N; s->K = Kp; s->M = n->Cout; s->in_ld[0] = permute_hw ? in_ld : in->ld;
+        s->scale = scale; s->shift = shift;
+        if (act >= 0 && fill_act(P, &s->act, &M->nodes[act], n->Cout)) return -1;
+        size_t es = esize_of(dtype);
+        unsigned char *hw = calloc((size_t)n->Cout * Kp, es);
+        for (int o = 0; o < n->Cout; o++)
+            for (int k = 0; k < n->Cin; k++) {
+                long dst = k;
+                if (permute_hw) { int c = k / permute_hw, hw_ = k % permute_hw; dst = (long)hw_ * in->ld + c; }
+                float v = n->weight[(size_t)o * n->Cin + k];
+                if (dtype == THB_F32) ((float *)hw)[(size_t)o * Kp + dst] = v;
+                else ((unsigned short *)hw)[(size_t)o * Kp + dst] = thb_float_to_half_bits(v, dtype == THB_BF16);
+            }
+        s->w = dupload(P->I, hw, (size_t)n->Cout * Kp * es);
+        free(hw);
+        if (!s->w) return -1;
+        s->flops_node = i;
+        return cur;
+    }
+
+    /* ---- implicit-GEMM convolution launch ---- */
+    int csum_buf = -1;
+    if (dtype == THB_U8) {
+        /* per-pixel channel sums of the input feed the zero-point correction of the convolution */
+        csum_buf = new_buf(P, sizeof(int) * (size_t)is.N * H * W);
+        step *cs = new_step(P, ST_CSUM);
+        step_in(cs, in);
+        cs->in_ld[0] = in_ld;
+        cs->pixels = (long)is.N * H * W; cs->C = Cin; cs->out_buf = csum_buf;
+    }
+    step *s = new_step(P, ST_CONV);
+    thb_conv_desc *d = &s->conv;
+    s->aux_buf = csum_buf;
+    d->dtype = dtype;
+    d->N = is.N; d->H = H; d->W = W; d->Cin = Cin; d->in_ld = in_ld;
+    d->kH = kH; d->kW = kW; d->dH = n->dH; d->dW = n->dW; d->padH = n->padH; d->padW = n->padW;
+    d->self_coef = 1.f; d->res_coef = 0.f; d->relu_thr = -1;
+    int Cp_out = ru(n->Cout, al);
+    float *w_oihw = n->weight, *w_tmp = 0;
+    if (is_deconv) {
+        /* column matrix [N*H*W][kH*kW*Cp]: column (kh*kW + kw)*Cp + co  <-  W[ci][co][kh][kw] */
+        d->Cout = kH * kW * Cp_out; d->kH = d->kW = 1; d->dH = d->dW = 1; d->padH = d->padW = 0;
+        d->oH = H; d->oW = W;
+        w_tmp = calloc((size_t)d->Cout * Cin, sizeof(float));
+        for (int ci = 0; ci < Cin; ci++)
+            for (int co = 0; co < n->Cout; co++)
+                for (int t = 0; t < kH * kW; t++)
+                    w_tmp[((size_t)t * Cp_out + co) * Cin + ci] = n->weight[((size_t)ci * n->Cout + co) * kH * kW + t];
+        w_oihw = w_tmp;
+    } else if (is_linear) {
+        d->Cout = n->Cout; d->oH = d->oW = 1;
+        if (permute_hw) {
+            w_tmp = calloc((size_t)n->Cout * Cin, sizeof(float));
+            for (int o = 0; o < n->Cout; o++)
+                for (int k = 0; k < n->Cin; k++) {
+                    int c = k / permute_hw, hw_ = k % permute_hw;
+                    w_tmp[(size_t)o * Cin + (size_t)hw_ * in->ld + c] = n->weight[(size_t)o * n->Cin + k];
+                }
+            w_oihw = w_tmp;
+        }
+    } else {
+        d->Cout = n->Cout; d->oH = os.H; d->oW = os.W;
+    }
+    if (thb_conv_geometry(d)) { free(w_tmp); thb_set_error("unsupported convolution geometry %dx%d", kH, kW); return -1; }
+    if (in_ld < d->Cin_pad) { free(w_tmp); thb_set_error("internal: input stride %d below padded channels %d", in_ld, d->Cin_pad); return -1; }
+
+    size_t wbytes = thb_conv_weight_bytes(d), kwords = thb_conv_kinfo_words(d);
+    void *packed = malloc(wbytes);
+    int *kinfo = malloc(kwords * sizeof(int)), *wsat = 0;
+    unsigned char *wq = 0;
+    if (dtype == THB_U8) {
+        /* lowp/lowp_basic.c:156-157: weights and bias quantised over their own ranges */
+        long wn = (long)d->Cout * d->Cin * d->kH * d->kW;
+        wq = malloc(wn);
+        thb_lowp_quantize(w_oihw, wn, wq, &s->w_sub, &s->w_mult);
+        wsat = malloc(sizeof(int) * d->Cout * (d->kH + 1) * (d->kW + 1));
+    }
+    int rc = thb_conv_pack_weights_host(d, dtype == THB_U8 ? 0 : w_oihw, wq, packed, kinfo, wsat);
+    free(w_tmp);
+    if (!rc) {
+        d->w = dupload(P->I, packed, wbytes);
+        d->kinfo = dupload(P->I, kinfo, kwords * sizeof(int));
+        if (wsat) d->wsat = dupload(P->I, wsat, sizeof(int) * d->Cout * (d->kH + 1) * (d->kW + 1));
+    }
+    free(packed); free(kinfo); free(wsat); free(wq);
+    if (rc || !d->w || !d->kinfo) { if (rc) thb_set_error("weight packing failed (%d)", rc); return -1; }
+    if (dtype != THB_F32) {
+        s->tmap = aligned_alloc(64, sizeof(thb_tmap));
+        if (thb_conv_make_tmap(d, s->tmap)) { thb_set_error("TMA descriptor creation failed"); return -1; }
+        d->tmap = s->tmap;
+    }
+    d->status = P->I->d_status;
+    step_in(s, in);
+    s->in_ld[0] = in_ld;
+    s->flops_node = i;
+
+    if (dtype == THB_U8) {
+        if (!n->bias) { thb_set_error("the lowp engine needs a bias on every convolution"); return -1; }
+        unsigned char *bq = malloc(n->Cout);
+        float b_sub, b_mult;
+        thb_lowp_quantize(n->bias, n->Cout, bq, &b_sub, &b_mult);
+        if (b_mult == 0) { free(bq); thb_set_error("an all-zero bias has no quantisation range in the lowp engine"); return -1; }
+        float out_sub = -E->range / 2, out_mult = 255 / E->range; /* lowp_basic.c:137-138 */
+        int *addend = malloc(sizeof(int) * n->Cout);
+        thb_lowp_bias_addends(bq, n->Cout, b_sub, b_mult, out_mult, addend);
+        d->bias_add = dupload(P->I, addend, sizeof(int) * n->Cout);
+        free(addend); free(bq);
+        s->out_sub = out_sub; s->out_mult = out_mult;
+        int ohw = d->oH * d->oW;
+        d->tail_start = ohw - ohw % 8;
+        if (in->q_dyn) s->dyn_quant = 1;
+        else {
+            thb_lowp_gemm_params(s->w_sub, s->w_mult, in->q_sub, in->q_mult, out_sub, out_mult, &d->a_offset, &d->b_offset,
+                                 &d->c_offset, &d->c_mult, &d->c_shift);
+        }
+        if (act >= 0) {
+            /* lowp_Threshold.c:7-8: both bytes scaled with the (conv output) quantisation parameters */
+            d->relu_thr = thb_lowp_scale_float(out_sub, out_mult, M->nodes[act].act_threshold);
+            d->relu_val = thb_lowp_scale_float(out_sub, out_mult, M->nodes[act].act_value);
+        }
+        out->q_sub = out_sub; out->q_mult = out_mult;
+    } else {
+        d->scale = scale; d->shift = shift;
+        if (act >= 0 && !is_deconv && fill_act(P, &d->act, &M->nodes[act], n->Cout)) return -1;
+        if (res_node >= 0) {
+            const value *rv = &P->val[res_node];
+            step_in(s, rv);
+            d->res_ld = rv->ld;
+            d->self_coef = self_coef; d->res_coef = res_coef;
+        }
+    }
+
+    if (is_deconv) {
+        value cols;
+        shape cs = is; cs.C = d->Cout;
+        memset(&cols, 0, sizeof(cols));
+        materialise(P, &cols, cs);
+        s = &P->I->steps[P->I->nsteps - 1];
+        step_out(s, &cols);
+        s->conv.out_ld = cols.ld;
+        materialise(P, out, os);
+        step *g = new_step(P, ST_COL2IM);
+        step_in(g, &cols);
+        step_out(g, out);
+        g->N = is.N; g->H = is.H; g->W = is.W; g->C = n->Cout; g->kH = kH; g->kW = kW; g->dH = n->dH; g->dW = n->dW;
+        g->padH = n->padH; g->padW = n->padW; g->oH = os.H; g->oW = os.W;
+        /* SpatialFullConvolution.c:229-238: the bias GEMM runs with beta = 11 whenever a bias exists */
+        g->beta = E->strict_math ? 1.f : 11.f;
+        if (n->bias) g->bias = upload_floats(P, n->bias, n->Cout, ru(n->Cout, 64));
+        if (act >= 0 && fill_act(P, &g->act, &M->nodes[act], n->Cout)) return -1;
+        return cur;
+    }
+    materialise(P, out, os);
+    s = &P->I->steps[P->I->nsteps - 1];
+    step_out(s, out);
+    s->conv.out_ld = out->ld;
+    return cur;
+}
+
+static int plan_node(planner *P, int i)
+{
+    thb_engine *E = P->E;
+    thb_model *M = P->M;
+    thb_node *n = &M->nodes[i];
+    const int dtype = E->dtype, al = align_of(dtype);
+    value *out = &P->val[i];
+    const value *in = n->nin ? &P->val[n->in[0]] : 0;
+    step *s;
+    int j;
+
+    if (dtype == THB_U8 && n->op != OP_CONV && n->op != OP_LINEAR && n->op != OP_ACT && n->op != OP_MAXPOOL &&
+        n->op != OP_VIEW && n->op != OP_ALIAS) {
+        /* the reference's lowp conversion rejects these module types too (lowp_basic.c:160-208) */
+        thb_set_error("operator %d not supported in Lowp", n->op);
+        return -1;
+    }
+    switch (n->op) {
+    case OP_CONV: case OP_LINEAR: case OP_DECONV:
+        return plan_gemm_group(P, i) < 0 ? -1 : 0;
+    case OP_BN: case OP_ACT: case OP_SCALE: {
+        int act = -1, C = in->s.C;
+        if (in->s.flat) { thb_set_error("elementwise operator on a flattened spatial tensor is not supported"); return -1; }
+        value *dst = out;
+        if (dtype == THB_U8) {
+            if (n->act_kind != THB_ACT_THRESHOLD) { thb_set_error("only Threshold is supported in Lowp"); return -1; }
+            materialise(P, out, in->s);
+            out->q_sub = in->q_sub; out->q_mult = in->q_mult;
+            s = new_step(P, ST_U8THR);
+            step_in(s, in); step_out(s, out);
+            s->pixels = (long)in->s.N * in->s.H * in->s.W; s->C = C;
+            s->thr = thb_lowp_scale_float(in->q_sub, in->q_mult, n->act_threshold);
+            s->val = thb_lowp_scale_float(in->q_sub, in->q_mult, n->act_value);
+            if (in->q_dyn) { thb_set_error("Threshold directly on the network input is not supported in Lowp"); return -1; }
+            return 0;
+        }
+        if (n->op == OP_BN && (j = sole_consumer(P, i)) >= 0 && M->nodes[j].op == OP_ACT) {
+            act = j; P->absorbed[j] = 1; P->leader[j] = i; dst = &P->val[j];
+        }
+        materialise(P, dst, in->s);
+        s = new_step(P, ST_AFFINE);
+        step_in(s, in); step_out(s, dst);
+        s->pixels = (long)in->s.N * in->s.H * in->s.W; s->C = C;
+        if (n->op == OP_BN) {
+            if (n->C != C) { thb_set_error("batch-norm over %d channels applied to %d", n->C, C); return -1; }
+            s->scale = upload_floats(P, n->scale, C, ru(C, 64));
+            s->shift = upload_floats(P, n->shift, C, ru(C, 64));
+            if (act >= 0 && fill_act(P, &s->act, &M->nodes[act], C)) return -1;
+        } else if (n->op == OP_SCALE) {
+            float *f = malloc(sizeof(float) * C);
+            for (int c = 0; c < C; c++) f[c] = n->factor;
+            s->scale = upload_floats(P, f, C, ru(C, 64));
+            free(f);
+        } else if (fill_act(P, &s->act, n, C))
+            return -1;
+        return 0;
+    }
+    case OP_MAXPOOL: case OP_AVGPOOL: {
+        shape os = in->s;
+        int kH = n->kH, kW = n->kW;
+        if (in->s.rank < 3 || in->s.flat) { thb_set_error("3D or 4D (batch mode) tensor expected"); return -1; }
+        if (n->op == OP_AVGPOOL) {
+            if (kW == 0) kW = in->s.W;
+            if (kH == 0) kH = in->s.H;
+            if (!(kW / 2 >= n->padW && kH / 2 >= n->padH)) { thb_set_error("pad should be smaller than half of kernel size"); return -1; }
+        }
+        os.H = pool_out(in->s.H, kH, n->dH, n->padH, n->ceil_mode, n->padH || n->padW);
+        os.W = pool_out(in->s.W, kW, n->dW, n->padW, n->ceil_mode, n->padH || n->padW);
+        if (os.H < 1 || os.W < 1) { thb_set_error("input image smaller than kernel size"); return -1; }
+        materialise(P, out, os);
+        out->q_sub = in->q_sub; out->q_mult = in->q_mult; out->q_dyn = in->q_dyn;
+        s = new_step(P, n->op == OP_MAXPOOL ? ST_MAXPOOL : ST_AVGPOOL);
+        step_in(s, in); step_out(s, out);
+        s->N = in->s.N; s->H = in->s.H; s->W = in->s.W; s->C = in->s.C; s->kH = kH; s->kW = kW; s->dH = n->dH; s->dW = n->dW;
+        s->padH = n->padH; s->padW = n->padW; s->oH = os.H; s->oW = os.W; s->flag = n->count_include_pad;
+        return 0;
+    }
+    case OP_COMBINE: {
+        materialise(P, out, in->s);
+        s = new_step(P, ST_COMBINE);
+        for (int k = 0; k < n->nin; k++) {
+            const value *v = &P->val[n->in[k]];
+            if (v->s.C != in->s.C || v->s.H != in->s.H || v->s.W != in->s.W || v->s.N != in->s.N) {
+                thb_set_error("Sum of tensors of different sizes");
+                return -1;
+            }
+            step_in(s, v);
+            s->coef[k] = n->coef[k];
+        }
+        step_out(s, out);
+        s->pixels = (long)in->s.N * in->s.H * in->s.W; s->C = in->s.C;
+        return 0;
+    }
+    case OP_CONCAT: {
+        /* JoinTable.c:43-44: dimension 1 of a 1-D or 3-D input means dimension 0; only the channel
+         * (feature) dimension is supported here */
+        int dim = n->dim;
+        if (dim == 1 && (in->s.rank == 1 || in->s.rank == 3)) dim--;
+        int chan_dim = (in->s.rank == 4 || in->s.rank == 2) ? 1 : 0;
+        if (dim != chan_dim) { thb_set_error("concatenation along dimension %d is not supported", n->dim); return -1; }
+        shape os = in->s;
+        os.C = 0;
+        for (int k = 0; k < n->nin; k++) {
+            const value *v = &P->val[n->in[k]];
+            if (v->s.rank != in->s.rank) { thb_set_error("Concatenation of tensors of different dimensionality"); return -1; }
+            if (v->s.H != in->s.H || v->s.W != in->s.W || v->s.N != in->s.N || v->s.flat) {
+                thb_set_error("Concatenation of tensors of different sizes");
+                return -1;
+            }
+            if (k < n->nin - 1 && v->s.C % al) {
+                thb_set_error("concatenation of %d channels is not aligned to %d", v->s.C, al);
+                return -1;
+            }
+            os.C += v->s.C;
+        }
+        materialise(P, out, os);
+        int coff = 0;
+        for (int k = 0; k < n->nin; k++) {
+            const value *v = &P->val[n->in[k]];
+            s = new_step(P, ST_COPY);
+            step_in(s, v); step_out(s, out);
+            s->out_coff = coff;
+            s->pixels = (long)os.N * os.H * os.W; s->C = v->s.C;
+            coff += v->s.C;
+        }
+        return 0;
+    }
+    case OP_SOFTMAX: {
+        if (in->s.flat) { thb_set_error("SoftMax on a flattened spatial tensor is not supported"); return -1; }
+        materialise(P, out, in->s);
+        s = new_step(P, ST_SOFTMAX);
+        step_in(s, in); step_out(s, out);
+        s->pixels = (long)in->s.N * in->s.H * in->s.W; s->C = in->s.C;
+        return 0;
+    }
+    case OP_VIEW: {
+        /* View.c:86-97: batch > 1 gives [batch, numElements], otherwise a 1-D tensor */
+        long total = (long)in->s.N * in->s.C * in->s.H * in->s.W, per = n->numElements;
+        long batch = in->s.rank == 4 || in->s.rank == 2 ? in->s.N : 1;
+        if (per == -1) per = total / batch; else batch = total / per;
+        if (batch != in->s.N || per * batch != total) { thb_set_error("View to %d elements does not keep the batch dimension", n->numElements); return -1; }
+        *out = *in;
+        out->s.rank = batch > 1 ? 2 : 1;
+        if (in->s.flat) return 0;
+        if (in->s.H * in->s.W > 1) {
+            /* consumers that are Linear read the channels-innermost data through a permuted weight; anything
+             * else (and the network output) gets the data reordered to the NCHW flatten it expects */
+            int all_linear = i != M->output;
+            for (int k = i + 1; k < M->nnodes && all_linear; k++)
+                for (int q = 0; q < M->nodes[k].nin; q++)
+                    if (M->nodes[k].in[q] == i && M->nodes[k].op != OP_LINEAR) all_linear = 0;
+            if (all_linear && in->coff == 0 && dtype != THB_U8) {
+                out->s.flat = 1; out->s.fC = in->s.C; out->s.fH = in->s.H; out->s.fW = in->s.W;
+                out->s.C = (int)per; out->s.H = out->s.W = 1;
+                return 0;
+            }
+            if (i == M->output) {
+                /* the postprocess kernel emits NCHW order anyway: keep the spatial form, remember the rank */
+                out->s.flat = 2;
+                return 0;
+            }
+            shape os = in->s;
+            os.C = (int)per; os.H = os.W = 1; os.rank = out->s.rank;
+            materialise(P, out, os);
+            out->q_sub = in->q_sub; out->q_mult = in->q_mult; out->q_dyn = in->q_dyn;
+            s = new_step(P, ST_TO_NCHW);
+            step_in(s, in); step_out(s, out);
+            s->N = in->s.N; s->H = in->s.H; s->W = in->s.W; s->C = in->s.C;
+            return 0;
+        }
+        out->s.C = (int)per; out->s.H = out->s.W = 1;
+        return 0;
+    }
+    case OP_ALIAS:
+        *out = *in;
+        return 0;
+    }
+    thb_set_error("internal: unknown operator %d", n->op);
+    return -1;
+}
+
+/* liveness-based packing of the activation buffers into one arena */
+static size_t pack_arena(instance *I)
+{
+    for (int t = 0; t < I->nsteps; t++) {
+        step *s = &I->steps[t];
+        int ids[10], n = 0;
+        for (int k = 0; k < s->nin; k++) ids[n++] = s->in_buf[k];
+        ids[n++] = s->out_buf;
+        ids[n++] = s->aux_buf;
+        for (int k = 0; k < n; k++)
+            if (ids[k] >= 0) {
+                abuf *b = &I->bufs[ids[k]];
+                if (b->first < 0) b->first = t;
+                b->last = t;
+            }
+    }
+    /* the network input lives from the preprocess launch (before step 0); the output until the postprocess */
+    if (I->in_val.buf >= 0) I->bufs[I->in_val.buf].first = -1;
+    if (I->out_val.buf >= 0) I->bufs[I->out_val.buf].last = I->nsteps;
+    size_t top = 0;
+    for (int b = 0; b < I->nbufs; b++) {
+        abuf *B = &I->bufs[b];
+        if (B->last < 0 && b != I->in_val.buf) { B->offset = 0; continue; }
+        size_t off = 0;
+        for (;;) {
+            int moved = 0;
+            for (int o = 0; o < b; o++) {
+                abuf *O = &I->bufs[o];
+                if (O->last < 0 && o != I->in_val.buf) continue;
+                int overlap_time = !(O->last < B->first || B->last < O->first);
+                if (overlap_time && off < O->offset + O->bytes && O->offset < off + B->bytes) {
+                    off = O->offset + O->bytes;
+                    moved = 1;
+                }
+            }
+            if (!moved) break;
+        }
+        B->offset = off;
+        if (off + B->bytes > top) top = off + B->bytes;
+    }
+    return top;
+}
+
+static void instance_free(instance *I)
+{
+    if (!I->allocs && !I->steps) return;
+    cudaSetDevice(I->device);
+    if (I->stream) cudaStreamSynchronize(I->stream);
+    for (int i = 0; i < I->nallocs; i++) cudaFree(I->allocs[i]);
+    for (int i = 0; i < I->nsteps; i++) free(I->steps[i].tmap);
+    if (I->ev0) cudaEventDestroy(I->ev0);
+    if (I->ev1) cudaEventDestroy(I->ev1);
+    if (I->stream) cudaStreamDestroy(I->stream);
+    free(I->allocs); free(I->steps); free(I->bufs);
+    memset(I, 0, sizeof(*I));
+}
+
+static int instance_build(thb_engine *E, instance *I, int device, int slice_off, int slice_n)
+{
+    thb_model *M = E->model;
+    memset(I, 0, sizeof(*I));
+    I->device = device; I->slice_off = slice_off; I->slice_n = slice_n;
+    CU(cudaSetDevice(device));
+    CU(cudaStreamCreateWithFlags(&I->stream, cudaStreamNonBlocking));
+    CU(cudaEventCreate(&I->ev0));
+    CU(cudaEventCreate(&I->ev1));
+    I->d_status = dalloc(I, sizeof(int));
+    I->d_minmax = dalloc(I, 2 * sizeof(float));
+    if (!I->d_status || !I->d_minmax) return -1;
+    CU(cudaMemset(I->d_status, 0, sizeof(int)));
+
+    planner P;
+    memset(&P, 0, sizeof(P));
+    P.E = E; P.I = I; P.M = M;
+    P.val = calloc(M->nnodes, sizeof(value));
+    P.uses = calloc(M->nnodes, sizeof(int));
+    P.absorbed = calloc(M->nnodes, sizeof(int));
+    P.leader = calloc(M->nnodes, sizeof(int));
+    for (int i = 0; i < M->nnodes; i++) {
+        P.val[i].buf = -1;
+        P.leader[i] = i;
+        for (int k = 0; k < M->nodes[i].nin; k++) P.uses[M->nodes[i].in[k]]++;
+    }
+    P.uses[M->output]++;
+
+    shape in = {slice_n, E->C, E->H, E->W, E->rank, 0, 0, 0, 0};
+    materialise(&P, &P.val[0], in);
+    P.val[0].q_dyn = E->dtype == THB_U8;
+    int rc = 0;
+    for (int i = 1; i < M->nnodes && !rc; i++) {
+        if (P.absorbed[i]) continue;
+        rc = plan_node(&P, i);
+    }
+    if (!rc && P.val[M->output].buf < 0) { thb_set_error("internal: the output was not materialised"); rc = -1; }
+    if (!rc) {
+        I->in_val = P.val[0];
+        I->out_val = P.val[M->output];
+        I->out_shape = I->out_val.s;
+        I->out_count = (long)I->out_shape.N * I->out_shape.C * I->out_shape.H * I->out_shape.W;
+        I->arena_bytes = pack_arena(I);
+        I->arena = dalloc(I, I->arena_bytes);
+        size_t in_bytes = (size_t)slice_n * E->C * E->H * E->W * sizeof(float);
+        I->d_in = dalloc(I, in_bytes);
+        I->d_img = dalloc(I, (size_t)slice_n * E->H * E->W * 4);
+        I->d_out = dalloc(I, (size_t)(I->out_count ? I->out_count : 1) * sizeof(float));
+        if (!I->arena || !I->d_in || !I->d_out || !I->d_img) rc = -1;
+        /* padded channels are never read as data, but stale NaN/Inf bit patterns would poison the
+         * zero-weight products: start from a clean arena */
+        if (!rc && cudaMemset(I->arena, 0, I->arena_bytes) != cudaSuccess) { thb_set_error("arena memset failed"); rc = -1; }
+    }
+    free(P.val); free(P.uses); free(P.absorbed); free(P.leader);
+    if (th_debug && !rc)
+        fprintf(stderr, "thb200: device %d: %d launches per forward, arena %.1f MiB, %d buffers\n", device, I->nsteps,
+                I->arena_bytes / 1048576.0, I->nbufs);
+    return rc;
+}
+
+static void *bufptr(instance *I, int buf, int coff, int dtype)
+{
+    return buf < 0 ? 0 : I->arena + I->bufs[buf].offset + (size_t)coff * esize_of(dtype);
+}
+
+static int run_steps(thb_engine *E, instance *I)
+{
+    thb_stream st = I->stream;
+    for (int t = 0; t < I->nsteps; t++) {
+        step *s = &I->steps[t];
+        const int dt = s->dtype;
+        void *x0 = bufptr(I, s->in_buf[0], s->in_coff[0], dt);
+        void *y = bufptr(I, s->out_buf, s->out_coff, dt);
+        int rc = 0;
+        double t0 = 0;
+        if (th_profile) { cudaStreamSynchronize(I->stream); t0 = th_seconds(); }
+        switch (s->kind) {
+        case ST_CONV: {
+            thb_conv_desc *d = &s->conv;
+            if (s->nin > 1) d->res = bufptr(I, s->in_buf[1], s->in_coff[1], dt);
+            if (s->aux_buf >= 0) d->csum = (const int *)bufptr(I, s->aux_buf, 0, THB_U8);
+            rc = thb_conv_fwd(d, x0, y, st);
+            break;
+        }
+        case ST_GEMV:
+            rc = thb_gemv_fwd(dt, x0, s->N, s->K, s->in_ld[0], s->w, s->M, s->scale, s->shift, &s->act, y, s->out_ld, st);
+            break;
+        case ST_MAXPOOL:
+            rc = thb_maxpool(dt, x0, s->N, s->H, s->W, s->C, s->in_ld[0], s->kH, s->kW, s->dH, s->dW, s->padH, s->padW, s->oH,
+                             s->oW, y, s->out_ld, st);
+            break;
+        case ST_AVGPOOL:
+            rc = thb_avgpool(dt, x0, s->N, s->H, s->W, s->C, s->in_ld[0], s->kH, s->kW, s->dH, s->dW, s->padH, s->padW, s->oH,
+                             s->oW, s->flag, y, s->out_ld, st);
+            break;
+        case ST_AFFINE:
+            rc = thb_affine_act(dt, x0, s->pixels, s->C, s->in_ld[0], s->scale, s->shift, &s->act, y, s->out_ld, st);
+            break;
+        case ST_U8THR:
+            rc = thb_u8_threshold(x0, s->pixels, s->C, s->in_ld[0], s->thr, s->val, y, s->out_ld, st);
+            break;
+        case ST_COMBINE: {
+            const void *xs[8];
+            for (int k = 0; k < s->nin; k++) xs[k] = bufptr(I, s->in_buf[k], s->in_coff[k], dt);
+            rc = thb_combine(dt, s->nin, xs, s->in_ld, s->coef, s->pixels, s->C, y, s->out_ld, st);
+            break;
+        }
+        case ST_COPY:
+            rc = thb_copy_channels(dt, x0, s->pixels, s->C, s->in_ld[0], y, s->out_ld, st);
+            break;
+        case ST_SOFTMAX:
+            rc = thb_softmax(dt, x0, s->pixels, s->C, s->in_ld[0], y, s->out_ld, st);
+            break;
+        case ST_COL2IM:
+            rc = thb_col2im(dt, x0, s->N, s->H, s->W, s->C, s->kH, s->kW, s->dH, s->dW, s->padH, s->padW, s->oH, s->oW,
+                            s->in_ld[0], s->beta, s->bias, &s->act, y, s->out_ld, st);
+            break;
+        case ST_CSUM:
+            rc = thb_u8_channel_sum(x0, s->pixels, s->C, s->in_ld[0], (int *)bufptr(I, s->out_buf, 0, THB_U8), st);
+            break;
+        case ST_TO_NCHW:
+            rc = thb_to_nchw(dt, x0, s->N, s->H, s->W, s->C, s->in_ld[0], y, st);
+            break;
+        }
+        if (rc) { thb_set_error("kernel launch %d (kind %d) failed: %d %s", t, s->kind, rc, thb_last_cuda_error()); return -1; }
+        if (th_profile) {
+            /* thapi.c:211-233: wall clock per module, GFLOP/s for convolutions (serialises the stream) */
+            cudaStreamSynchronize(I->stream);
+            double dtm = th_seconds() - t0;
+            if (s->kind == ST_CONV && s->flops_node >= 0) {
+                thb_node *n = &E->model->nodes[s->flops_node];
+                double flops = 2.0 * s->conv.N * s->conv.oH * s->conv.oW * (double)n->Cout * n->Cin * n->kH * n->kW;
+                printf("%f seconds for launch %d, %f Gflops/s\n", dtm, t + 1, flops * 1e-9 / dtm);
+                th_convtot += dtm; th_convflops += flops;
+            } else printf("%f seconds for launch %d\n", dtm, t + 1);
+        }
+    }
+    return 0;
+}
+
+/* ================================================================================================ */
+thb_engine *thb_engine_create(thb_model *model, int mode, float lowp_range, int ngpus)
+{
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev < 1) {
+        thb_set_error("no CUDA device: this library has no CPU engine");
+        return 0;
+    }
+    thb_engine *E = calloc(1, sizeof(*E));
+    E->model = model;
+    model->refs++;
+    E->mode = mode;
+    E->dtype = mode == THB_MODE_F16 ? THB_F16 : mode == THB_MODE_BF16 ? THB_BF16 : mode == THB_MODE_U8 ? THB_U8 : THB_F32;
+    E->range = lowp_range;
+    E->ngpus = ngpus < 1 ? 1 : ngpus > ndev ? ndev : ngpus > 8 ? 8 : ngpus;
+    const char *sm = getenv("THB200_STRICT_MATH");
+    E->strict_math = sm && atoi(sm);
+    const char *g = getenv("THB200_GATHER");
+    E->peer_gather = !(g && !strcmp(g, "host"));
+    return E;
+}
+
+void thb_engine_destroy(thb_engine *E)
+{
+    if (!E) return;
+    for (int g = 0; g < 8; g++) instance_free(&E->inst[g]);
+    thb_host_free_pinned(E->h_out);
+    thb_model_release(E->model);
+    free(E);
+}
+
+static int engine_build(thb_engine *E, int N, int C, int H, int W, int rank, int cp)
+{
+    for (int g = 0; g < 8; g++) instance_free(&E->inst[g]);
+    E->built = 0;
+    E->N = N; E->C = C; E->H = H; E->W = W; E->rank = rank; E->cp = cp;
+    int G = E->ngpus < N ? E->ngpus : N;
+    if (G < 1) G = 1;
+    int base = N / G, extra = N % G, off = 0, dev0 = 0;
+    const char *d0 = getenv("THB200_DEVICE");
+    if (d0) dev0 = atoi(d0);
+    for (int g = 0; g < G; g++) {
+        int n = base + (g < extra ? 1 : 0);
+        if (instance_build(E, &E->inst[g], dev0 + g, off, n)) return -1;
+        off += n;
+    }
+    /* gather target: GPU 0 holds the whole result when peer copies are usable */
+    if (G > 1 && E->peer_gather) {
+        for (int g = 1; g < G; g++) {
+            int can = 0;
+            cudaDeviceCanAccessPeer(&can, E->inst[0].device, E->inst[g].device);
+            if (!can) E->peer_gather = 0;
+        }
+        if (E->peer_gather) {
+            long total = 0;
+            for (int g = 0; g < G; g++) total += E->inst[g].out_count;
+            cudaSetDevice(E->inst[0].device);
+            E->inst[0].d_out = dalloc(&E->inst[0], (size_t)total * sizeof(float));
+            if (!E->inst[0].d_out) return -1;
+        }
+    }
+    E->built = G;
+    return 0;
+}
+
+/* per-forward parameters of a u8 convolution whose input scale is measured on the fly */
+static void set_dynamic_quant(instance *I, float in_sub, float in_mult)
+{
+    for (int t = 0; t < I->nsteps; t++) {
+        step *s = &I->steps[t];
+        if (s->kind == ST_CONV && s->dyn_quant)
+            thb_lowp_gemm_params(s->w_sub, s->w_mult, in_sub, in_mult, s->out_sub, s->out_mult, &s->conv.a_offset,
+                                 &s->conv.b_offset, &s->conv.c_offset, &s->conv.c_mult, &s->conv.c_shift);
+    }
+}
+
+int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stride, int bgr, int cp, int N, int C, int H,
+                       int W, int rank, const float *mean, const float *std, int inplace, thb_result *res)
+{
+    if (N < 1 || C < 1 || H < 1 || W < 1) { thb_set_error("empty input"); return -1; }
+    if (!E->built || E->N != N || E->C != C || E->H != H || E->W != W || E->rank != rank) {
+        if (engine_build(E, N, C, H, W, rank, cp)) return -1;
+    }
+    const int G = E->built;
+    const size_t img_elems = (size_t)C * H * W;
+    float q_sub = 0, q_mult = 0;
+
+    /* stage the input slices */
+    for (int g = 0; g < G; g++) {
+        instance *I = &E->inst[g];
+        CU(cudaSetDevice(I->device));
+        if (x) {
+            CU(cudaMemcpyAsync(I->d_in, x + (size_t)I->slice_off * img_elems, (size_t)I->slice_n * img_elems * sizeof(float),
+                               cudaMemcpyHostToDevice, I->stream));
+        } else {
+            for (int n = 0; n < I->slice_n; n++)
+                CU(cudaMemcpy2DAsync(I->d_img + (size_t)n * H * W * cp, (size_t)W * cp, images[I->slice_off + n], stride,
+                                     (size_t)W * cp, H, cudaMemcpyHostToDevice, I->stream));
+        }
+    }
+    if (E->dtype == THB_U8) {
+        /* lowp_basic.c:15-29: one range over the WHOLE batch tensor, so slices are reduced on the host */
+        if (!x) { thb_set_error("THProcessImages is not supported with Lowp"); return -1; }
+        float lo = 0, hi = 0;
+        for (int g = 0; g < G; g++) {
+            instance *I = &E->inst[g];
+            float mm[2];
+            CU(cudaSetDevice(I->device));
+            if (thb_minmax_normalized(I->d_in, I->slice_n, C, H, W, mean, std, I->d_minmax, I->stream)) return -1;
+            CU(cudaMemcpyAsync(mm, I->d_minmax, sizeof(mm), cudaMemcpyDeviceToHost, I->stream));
+            CU(cudaStreamSynchronize(I->stream));
+            if (mm[0] < lo) lo = mm[0];
+            if (mm[1] > hi) hi = mm[1];
+        }
+        q_sub = lo;
+        q_mult = hi - lo > 0 ? (float)(255.0 / (hi - lo)) : 0;
+        for (int g = 0; g < G; g++) set_dynamic_quant(&E->inst[g], q_sub, q_mult);
+    }
+
+    long total = 0;
+    for (int g = 0; g < G; g++) total += E->inst[g].out_count;
+    if ((size_t)total * sizeof(float) > E->h_out_bytes) {
+        thb_host_free_pinned(E->h_out);
+        E->h_out_bytes = (size_t)total * sizeof(float);
+        E->h_out = thb_host_alloc_pinned(E->h_out_bytes);
+        if (!E->h_out) { thb_set_error("pinned result allocation failed"); return -1; }
+    }
+
+    for (int g = 0; g < G; g++) {
+        instance *I = &E->inst[g];
+        CU(cudaSetDevice(I->device));
+        int rc;
+        void *in_ptr = bufptr(I, I->in_val.buf, 0, E->dtype);
+        if (x)
+            rc = thb_preprocess(I->d_in, inplace ? I->d_in : 0, I->slice_n, C, H, W, mean, std, E->dtype, in_ptr, I->in_val.ld,
+                                q_sub, q_mult, I->stream);
+        else
+            rc = thb_preprocess_images(I->d_img, I->slice_n, H, W, W * cp, cp, bgr, mean, std, E->dtype, in_ptr,
+                                       I->in_val.ld, I->stream);
+        if (rc) { thb_set_error("preprocess launch failed: %s", thb_last_cuda_error()); return -1; }
+        if (x && inplace)
+            CU(cudaMemcpyAsync(x + (size_t)I->slice_off * img_elems, I->d_in, (size_t)I->slice_n * img_elems * sizeof(float),
+                               cudaMemcpyDeviceToHost, I->stream));
+        CU(cudaEventRecord(I->ev0, I->stream));
+        if (run_steps(E, I)) return -1;
+        const value *ov = &I->out_val;
+        float inv = ov->q_mult ? (float)(1.0 / ov->q_mult) : 0;
+        long off = 0;
+        for (int k = 0; k < g; k++) off += E->inst[k].out_count;
+        float *dst_dev = I->d_out;
+        if (thb_postprocess(bufptr(I, ov->buf, ov->coff, E->dtype), E->dtype, ov->s.N, ov->s.H, ov->s.W, ov->s.C, ov->ld,
+                            ov->q_sub, inv, dst_dev, I->stream)) { thb_set_error("postprocess launch failed"); return -1; }
+        CU(cudaEventRecord(I->ev1, I->stream));
+        if (G > 1 && E->peer_gather && g > 0) {
+            /* gather by peer copy into GPU 0's result buffer; GPU 0 sends the whole result to the host */
+            CU(cudaMemcpyPeerAsync(E->inst[0].d_out + off, E->inst[0].device, I->d_out, I->device,
+                                   (size_t)I->out_count * sizeof(float), I->stream));
+        } else if (!(G > 1 && E->peer_gather)) {
+            CU(cudaMemcpyAsync(E->h_out + off, I->d_out, (size_t)I->out_count * sizeof(float), cudaMemcpyDeviceToHost, I->stream));
+        }
+    }
+    float ms_max = 0;
+    for (int g = G - 1; g >= 0; g--) {
+        instance *I = &E->inst[g];
+        CU(cudaSetDevice(I->device));
+        if (g == 0 && G > 1 && E->peer_gather)
+            CU(cudaMemcpyAsync(E->h_out, I->d_out, (size_t)total * sizeof(float), cudaMemcpyDeviceToHost, I->stream));
+        CU(cudaStreamSynchronize(I->stream));
+        float ms = 0;
+        cudaEventElapsedTime(&ms, I->ev0, I->ev1);
+        I->last_ms = ms;
+        if (ms > ms_max) ms_max = ms;
+        int status = 0;
+        CU(cudaMemcpy(&status, I->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+        if (status) {
+            cudaMemset(I->d_status, 0, sizeof(int));
+            thb_set_error("a device-side wait timed out (code %d) on device %d", status, I->device);
+            return -1;
+        }
+    }
+    E->last_ms = ms_max;
+
+    shape os = E->inst[0].out_shape;
+    res->data = E->h_out;
+    res->count = total;
+    int rk = os.rank;
+    if (os.flat == 2) { /* a trailing View over a spatial tensor: rank from the View, data already in NCHW order */
+        res->ndim = rk;
+        if (rk == 2) { res->size[0] = N; res->size[1] = total / N; }
+        else res->size[0] = total;
+        return 0;
+    }
+    res->ndim = rk;
+    switch (rk) {
+    case 4: res->size[0] = N; res->size[1] = os.C; res->size[2] = os.H; res->size[3] = os.W; break;
+    case 3: res->size[0] = os.C; res->size[1] = os.H; res->size[2] = os.W; break;
+    case 2: res->size[0] = N; res->size[1] = os.C; break;
+    default: res->size[0] = os.C; break;
+    }
+    return 0;
+}
+
+float thb_engine_last_ms(thb_engine *E) { return E ? E->last_ms : -1.f; }
+
+/* Device-resident timing loop: the planned launches only (input already staged and preprocessed by the last
+ * forward), `iters` times back to back per GPU, timed with events on the launching stream; max over GPUs. */
+float thb_engine_time_forward(thb_engine *E, int iters)
+{
+    if (!E || !E->built || iters < 1) return -1.f;
+    const int G = E->built;
+    for (int g = 0; g < G; g++) {
+        instance *I = &E->inst[g];
+        if (cudaSetDevice(I->device) != cudaSuccess) return -1.f;
+        cudaEventRecord(I->ev0, I->stream);
+        for (int it = 0; it < iters; it++)
+            if (run_steps(E, I)) return -1.f;
+        cudaEventRecord(I->ev1, I->stream);
+    }
+    float worst = 0;
+    for (int g = 0; g < G; g++) {
+        instance *I = &E->inst[g];
+        cudaSetDevice(I->device);
+        if (cudaStreamSynchronize(I->stream) != cudaSuccess) return -1.f;
+        float ms = 0;
+        cudaEventElapsedTime(&ms, I->ev0, I->ev1);
+        if (ms > worst) worst = ms;
+    }
+    return worst / iters;
+}

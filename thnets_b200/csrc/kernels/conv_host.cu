@@ -107,6 +107,16 @@ extern "C" int thb_conv_pack_weights_host(const thb_conv_desc *d, const float *w
     return THB_OK;
 }
 
+extern "C" unsigned short thb_float_to_half_bits(float v, int bf16)
+{
+    if (bf16) {
+        __nv_bfloat16 h = __float2bfloat16_rn(v);
+        return *reinterpret_cast<unsigned short *>(&h);
+    }
+    __half h = __float2half_rn(v);
+    return *reinterpret_cast<unsigned short *>(&h);
+}
+
 extern "C" int thb_conv_fwd(const thb_conv_desc *d, const void *x, void *y, thb_stream s)
 {
     if (d->in_ld < d->Cin_pad) return THB_ERR_ARG;
