@@ -259,6 +259,12 @@ float THB200_LastDeviceMs(THNETWORK *network);
 /* Device-resident benchmark loop: runs the planned forward `iters` times on the batch uploaded by the last
  * THProcessFloat call and returns the mean device time per forward in milliseconds (< 0 on error). */
 float THB200_TimeForward(THNETWORK *network, int iters);
+/* Per-launch device time (ms, averaged over `iters` passes) of the planned forward on the first GPU; kinds[t] is
+ * 0 for a convolution / Linear-as-convolution launch, 1 for a GEMV, 2 otherwise; flops[t] its algorithmic FLOPs.
+ * Returns the number of launches described (<= max_steps), < 0 on error. */
+int THB200_ProfileForward(THNETWORK *network, int iters, int max_steps, int *kinds, float *ms, double *flops);
+/* the contiguous slice [offset, offset+count) of an N-image batch that GPU g of G processes */
+void THB200_SliceBatch(int N, int G, int g, int *offset, int *count);
 int THB200_KernelLaunches(void);
 /* one text line per operator of the lowered network; returns the length written, < 0 on error */
 int THB200_DescribeNetwork(THNETWORK *network, char *buf, int len);

@@ -81,17 +81,25 @@ class Conv:
             assert lib.thb_conv_make_tmap(C.byref(d), C.byref(self.tmap)) == 0
             d.tmap = C.addressof(self.tmap)
 
+    @staticmethod
+    def _padded(v):
+        """per-channel arrays are read in 16-byte groups: pad to a multiple of 64 floats like the planner does"""
+        v = np.asarray(v, np.float32)
+        out = np.zeros(ru(v.size, 64), np.float32)
+        out[:v.size] = v
+        return out
+
     def set_affine(self, scale, shift):
         if scale is not None:
-            t = dev(np.asarray(scale, np.float32)); self.keep.append(t); self.d.scale = t.data_ptr()
+            t = dev(self._padded(scale)); self.keep.append(t); self.d.scale = t.data_ptr()
         if shift is not None:
-            t = dev(np.asarray(shift, np.float32)); self.keep.append(t); self.d.shift = t.data_ptr()
+            t = dev(self._padded(shift)); self.keep.append(t); self.d.shift = t.data_ptr()
 
     def set_act(self, kind, threshold=0.0, value=0.0, alpha=0.0, slope=None):
         a = self.d.act
         a.kind, a.threshold, a.value, a.alpha = kind, threshold, value, alpha
         if slope is not None:
-            t = dev(np.asarray(slope, np.float32)); self.keep.append(t); a.slope = t.data_ptr()
+            t = dev(self._padded(slope)); self.keep.append(t); a.slope = t.data_ptr()
 
     def set_residual(self, res_t, res_ld, self_coef, res_coef):
         self.keep.append(res_t)

@@ -1,0 +1,144 @@
+"""The CPU oracle against the reference: golden vectors generated from the unmodified reference CPU
+build (tests/golden/make_golden.py), and -- where that build is present on this machine -- the
+reference library itself, operator by operator and network by network.  No GPU needed.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+from oracle.oracle import REF_DIR, ref_lib
+from thnets_b200 import fixtures as fx
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+GOLD = os.path.join(HERE, "golden")
+
+
+def rel_err(a, ref):
+    return float(np.abs(np.asarray(a, np.float64) - np.asarray(ref, np.float64)).max() / max(np.abs(ref).max(), 1e-30))
+
+
+FP32_CASES = {
+    "alexnet_owt": ("alexnet_owt", dict(width=0.25, size=224, classes=50, fc=128), 1),
+    "resnet18": ("resnet18", dict(width=0.25, size=64, classes=10), 4),
+    "resnet50": ("resnet50", dict(width=0.125, size=64, classes=10), 4),
+    "segnet": ("segnet", dict(width=0.5, size=32, classes=21), 4),
+    "segnet_bias": ("segnet", dict(width=0.5, size=32, classes=5, deconv_bias=0.1), 4),
+    "vgg16": ("vgg16", dict(width=0.125, size=32, classes=10, fc=64), 4),
+}
+
+
+@pytest.mark.parametrize("name", list(FP32_CASES))
+def test_fp32_oracle_matches_reference_golden(oracle, name):
+    """Pins the fp32 restatement: the reference's two-input CAddTable subtraction, its x11 transposed-
+    convolution bias, its polynomial softmax and its pooling shape rules all show up in these outputs.
+    The reference differs from itself by a few 1e-6 between build flavours and thread counts."""
+    gold = np.load(os.path.join(GOLD, "fp32_networks.npz"))
+    builder, kw, batch = FP32_CASES[name]
+    g = getattr(fx, builder)(**kw)
+    y = oracle.run(g, g.make_input(batch))
+    assert y.size == gold[name].size
+    assert rel_err(y.ravel(), gold[name]) < 2e-5
+    if y.ndim == 4:
+        assert tuple(gold[name + "_wh"]) == (y.shape[3], y.shape[2])
+
+
+@pytest.mark.parametrize("name,kw,rng", [("vgg16_r8", dict(width=0.125, size=32, classes=10, fc=64), 8.0),
+                                         ("vgg16_r20", dict(width=0.25, size=64, classes=10, fc=64), 20.0),
+                                         ("vgg16_r4", dict(width=0.25, size=32, classes=10, fc=64), 4.0)])
+def test_lowp_oracle_matches_reference_golden_bit_exact(oracle, name, kw, rng):
+    """The uint8 restatement against the reference's own lowp sources (batch 1, first forward) built around
+    the 8-bit GEMM contract: identical dequantised outputs, i.e. identical bytes."""
+    gold = np.load(os.path.join(GOLD, "lowp_networks.npz"))
+    g = fx.vgg16(**kw)
+    y = oracle.run_lowp(g, g.make_input(1), rng, kw["size"])
+    assert np.array_equal(y.ravel(), gold[name])
+
+
+def test_lowp_batch_is_per_image_with_whole_batch_input_scale(oracle):
+    """Batch semantics of the uint8 oracle: image i of a batch equals the batch-1 result of the same image
+    once the input scale is taken over the whole batch."""
+    g = fx.vgg16(width=0.125, size=32, classes=10, fc=64)
+    x = g.make_input(3)
+    full, vals = oracle.run_lowp(g, x, 8.0, 32, keep=True)
+    q, sub, mult = vals[0]
+    xn = oracle.normalize(x, g.mean, g.std)
+    q_all, sub_all, mult_all = oracle.lowp_quantize(xn)
+    assert (sub, mult) == (sub_all, mult_all) and np.array_equal(q, q_all)
+    assert full.shape[0] == 3
+
+
+def test_quirks_are_restated(oracle):
+    a = np.array([[0.003874]], np.float32)
+    b = np.array([[0.526965]], np.float32)
+    assert abs(float(oracle.caddtable([a, b])[0, 0]) - (0.003874 - 0.526965)) < 1e-6       # CAddTable.c:59-69
+    assert abs(float(oracle.caddtable([a, b], is_csub=1)[0, 0]) - (0.003874 + 0.526965)) < 1e-6
+    assert np.allclose(oracle.caddtable([a, b, a]), 3 * a + b)                                # input 0 counted twice
+    # exp(-x) polynomial: exact zero from 13 up, a few percent off at x = 8 (thbasic.c:462-491)
+    assert oracle.lib.orc_exp_minus_approx(13.0) == 0.0
+    assert abs(oracle.lib.orc_exp_minus_approx(8.0) / np.exp(-8.0) - 1) > 1e-2
+    assert abs(oracle.lib.orc_exp_minus_approx(2.0) / np.exp(-2.0) - 1) < 1e-4
+    # transposed convolution with bias: 11 * deconv + bias
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((1, 3, 4, 4)).astype(np.float32)
+    w = rng.standard_normal((3, 2, 4, 4)).astype(np.float32)
+    bias = np.array([100.0, -50.0], np.float32)
+    plain = oracle.fullconv2d(x, w, None, (2, 2), (1, 1), (0, 0))
+    biased = oracle.fullconv2d(x, w, bias, (2, 2), (1, 1), (0, 0))
+    assert rel_err(biased, 11 * plain + bias[None, :, None, None]) < 1e-6
+    # lowp: ReLU threshold byte is 127 for any symmetric range, truncating (lowp_basic.c:214-222)
+    for r in (4.0, 8.0, 20.0):
+        assert oracle.lib.orc_lowp_scale_float(-r / 2, np.float32(255) / np.float32(r), 0.0) == 127
+    # the quantiser can produce 256 -> stored as 0 (two terms rounded separately)
+    v = np.array([-54.5 / 1.0, 200.5], np.float32)
+    q, sub, mult = oracle.lowp_quantize(v)
+    assert mult == 1.0 and q[0] == 0 and q[1] == 0
+
+
+def test_pool_shape_rules(oracle):
+    out = oracle.lib.orc_pool_out
+    assert out(112, 3, 2, 1, 0) == 56
+    assert out(13, 3, 2, 0, 1) == 6 and out(13, 3, 2, 0, 0) == 6
+    assert out(14, 3, 2, 0, 1) == 7 and out(14, 3, 2, 0, 0) == 6
+    assert out(6, 2, 2, 1, 1) == 4          # ceil mode: the window that would start in the padding is dropped
+    assert oracle.lib.orc_conv_out(224, 11, 4, 2) == 55
+
+
+# ------------------------------------------------------------------------------ live reference (when built)
+needs_ref = pytest.mark.skipif(ref_lib() is None, reason="oracle/_ref was not built on this machine")
+
+
+@needs_ref
+@pytest.mark.parametrize("name", ["resnet18", "segnet_bias", "alexnet_owt"])
+def test_fp32_oracle_matches_live_reference(oracle, tmp_path, name):
+    from thnets_b200.capi import THNets
+    ref = THNets(ref_lib())
+    builder, kw, batch = FP32_CASES[name]
+    g = getattr(fx, builder)(**kw)
+    x = g.make_input(batch, seed=99)
+    p = str(tmp_path / "m.net")
+    fx.write_pymodel(g, p)
+    h = ref.load_network(p)
+    ref.set_stats(h, g.mean, g.std)
+    y, _, _ = ref.process_float(h, x)
+    ref.free_network(h)
+    assert rel_err(oracle.run(g, x).ravel(), y) < 2e-5
+
+
+@needs_ref
+def test_lowp_oracle_matches_live_reference(oracle, tmp_path):
+    from thnets_b200.capi import THNets
+    path = os.path.join(REF_DIR, "libthnets_ref_lowp.so")
+    if not os.path.exists(path):
+        pytest.skip("lowp reference build missing")
+    ref = THNets(path)
+    g = fx.vgg16(width=0.125, size=48, classes=7, fc=40)
+    x = g.make_input(1, seed=5)
+    d = str(tmp_path / "vgg")
+    fx.write_torch7(g, d)
+    h = ref.load_network(d)
+    ref.make_spatial(h, 48)
+    hl = ref.create_lowp_network(h, 6.0)
+    y, _, _ = ref.process_float(hl, x)
+    assert np.array_equal(oracle.run_lowp(g, x, 6.0, 48).ravel(), y)

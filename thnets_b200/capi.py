@@ -55,17 +55,19 @@ class THNets:
         lib.THCudaHalfFloat.restype = C.c_int
         lib.THUseSpatialConvolutionMM.argtypes = [C.c_void_p, C.c_int]
         lib.THUseSpatialConvolutionMM.restype = C.c_int
-        lib.THB200_LastErrorString.restype = C.c_char_p
-        lib.THB200_SetPrecision.argtypes = [C.c_int]
-        lib.THB200_SetDevices.argtypes = [C.c_int]
-        lib.THB200_LastDeviceMs.restype = C.c_float
-        lib.THB200_LastDeviceMs.argtypes = [C.c_void_p]
-        lib.THB200_TimeForward.restype = C.c_float
-        lib.THB200_TimeForward.argtypes = [C.c_void_p, C.c_int]
-        lib.THB200_HostAlloc.restype = C.c_void_p
-        lib.THB200_HostAlloc.argtypes = [C.c_size_t]
-        lib.THB200_HostFree.argtypes = [C.c_void_p]
-        lib.THB200_DescribeNetwork.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
+        self.is_b200 = hasattr(lib, "THB200_SetPrecision")  # False for a CPU build of the reference
+        if self.is_b200:
+            lib.THB200_LastErrorString.restype = C.c_char_p
+            lib.THB200_SetPrecision.argtypes = [C.c_int]
+            lib.THB200_SetDevices.argtypes = [C.c_int]
+            lib.THB200_LastDeviceMs.restype = C.c_float
+            lib.THB200_LastDeviceMs.argtypes = [C.c_void_p]
+            lib.THB200_TimeForward.restype = C.c_float
+            lib.THB200_TimeForward.argtypes = [C.c_void_p, C.c_int]
+            lib.THB200_HostAlloc.restype = C.c_void_p
+            lib.THB200_HostAlloc.argtypes = [C.c_size_t]
+            lib.THB200_HostFree.argtypes = [C.c_void_p]
+            lib.THB200_DescribeNetwork.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
         lib.THInit()
 
     # -- network life cycle ----------------------------------------------------

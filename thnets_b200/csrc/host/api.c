@@ -413,5 +413,10 @@ int THB200_DescribeNetwork(THNETWORK *network, char *buf, int len)
     return m ? pos : -1;
 }
 
+int THB200_ProfileForward(THNETWORK *network, int iters, int max_steps, int *kinds, float *ms, double *flops)
+{
+    return thb_engine_profile(netx(network)->engine, iters, max_steps, kinds, ms, flops);
+}
+void THB200_SliceBatch(int N, int G, int g, int *offset, int *count) { thb_slice_batch(N, G, g, offset, count); }
 float THB200_LastDeviceMs(THNETWORK *network) { return thb_engine_last_ms(netx(network)->engine); }
 float THB200_TimeForward(THNETWORK *network, int iters) { return thb_engine_time_forward(netx(network)->engine, iters); }

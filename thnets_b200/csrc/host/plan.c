@@ -828,7 +828,7 @@ static void *bufptr(instance *I, int buf, int coff, int dtype)
     return buf < 0 ? 0 : I->arena + I->bufs[buf].offset + (size_t)coff * esize_of(dtype);
 }
 
-static int run_steps(thb_engine *E, instance *I)
+static int run_steps_ev(thb_engine *E, instance *I, cudaEvent_t *evs)
 {
     thb_stream st = I->stream;
     for (int t = 0; t < I->nsteps; t++) {
@@ -888,6 +888,7 @@ static int run_steps(thb_engine *E, instance *I)
             break;
         }
         if (rc) { thb_set_error("kernel launch %d (kind %d) failed: %d %s", t, s->kind, rc, thb_last_cuda_error()); return -1; }
+        if (evs) cudaEventRecord(evs[t + 1], I->stream);
         if (th_profile) {
             /* thapi.c:211-233: wall clock per module, GFLOP/s for convolutions (serialises the stream) */
             cudaStreamSynchronize(I->stream);
@@ -901,6 +902,47 @@ static int run_steps(thb_engine *E, instance *I)
         }
     }
     return 0;
+}
+
+static int run_steps(thb_engine *E, instance *I) { return run_steps_ev(E, I, 0); }
+
+/* Per-launch device times of the planned forward on the first GPU (events around every launch on the launching
+ * stream, averaged over `iters` passes).  kinds: 0 tensor-core/FFMA convolution, 1 GEMV, 2 everything else.
+ * flops: algorithmic FLOPs of the launch (2 * MACs of the convolution / Linear it computes), 0 otherwise. */
+int thb_engine_profile(thb_engine *E, int iters, int max_steps, int *kinds, float *ms, double *flops)
+{
+    if (!E || !E->built || iters < 1) return -1;
+    instance *I = &E->inst[0];
+    if (cudaSetDevice(I->device) != cudaSuccess) return -1;
+    const int n = I->nsteps < max_steps ? I->nsteps : max_steps;
+    cudaEvent_t *evs = calloc(I->nsteps + 1, sizeof(cudaEvent_t));
+    for (int t = 0; t <= I->nsteps; t++) cudaEventCreate(&evs[t]);
+    for (int t = 0; t < n; t++) ms[t] = 0;
+    int rc = 0;
+    for (int it = 0; it < iters && !rc; it++) {
+        cudaEventRecord(evs[0], I->stream);
+        rc = run_steps_ev(E, I, evs);
+        if (cudaStreamSynchronize(I->stream) != cudaSuccess) rc = -1;
+        for (int t = 0; t < n && !rc; t++) {
+            float m = 0;
+            cudaEventElapsedTime(&m, evs[t], evs[t + 1]);
+            ms[t] += m / iters;
+        }
+    }
+    for (int t = 0; t < n; t++) {
+        step *s = &I->steps[t];
+        kinds[t] = s->kind == ST_CONV ? 0 : s->kind == ST_GEMV ? 1 : 2;
+        flops[t] = 0;
+        if (s->flops_node >= 0) {
+            thb_node *nd = &E->model->nodes[s->flops_node];
+            double pix = s->kind == ST_CONV ? (double)s->conv.N * s->conv.oH * s->conv.oW : (double)s->N;
+            if (nd->op == OP_DECONV) pix = (double)s->conv.N * s->conv.H * s->conv.W;
+            flops[t] = 2.0 * pix * nd->Cout * nd->Cin * nd->kH * nd->kW;
+        }
+    }
+    for (int t = 0; t <= I->nsteps; t++) cudaEventDestroy(evs[t]);
+    free(evs);
+    return rc ? -1 : n;
 }
 
 /* ================================================================================================ */
@@ -934,6 +976,14 @@ void thb_engine_destroy(thb_engine *E)
     free(E);
 }
 
+/* contiguous batch slices, one per GPU; the remainder images go to the lowest ranks */
+void thb_slice_batch(int N, int G, int g, int *offset, int *count)
+{
+    int base = N / G, extra = N % G;
+    *count = base + (g < extra ? 1 : 0);
+    *offset = g * base + (g < extra ? g : extra);
+}
+
 static int engine_build(thb_engine *E, int N, int C, int H, int W, int rank, int cp)
 {
     for (int g = 0; g < 8; g++) instance_free(&E->inst[g]);
@@ -941,13 +991,13 @@ static int engine_build(thb_engine *E, int N, int C, int H, int W, int rank, int
     E->N = N; E->C = C; E->H = H; E->W = W; E->rank = rank; E->cp = cp;
     int G = E->ngpus < N ? E->ngpus : N;
     if (G < 1) G = 1;
-    int base = N / G, extra = N % G, off = 0, dev0 = 0;
+    int dev0 = 0;
     const char *d0 = getenv("THB200_DEVICE");
     if (d0) dev0 = atoi(d0);
     for (int g = 0; g < G; g++) {
-        int n = base + (g < extra ? 1 : 0);
+        int off, n;
+        thb_slice_batch(N, G, g, &off, &n);
         if (instance_build(E, &E->inst[g], dev0 + g, off, n)) return -1;
-        off += n;
     }
     /* gather target: GPU 0 holds the whole result when peer copies are usable */
     if (G > 1 && E->peer_gather) {

@@ -73,15 +73,21 @@ __device__ __forceinline__ uint64_t global_ns()
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-// Bounded wait: gives up after about `limit_ns` and returns false; never spins forever.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint64_t limit_ns = 2000000000ull)
+// Bounded wait: polls the barrier, and once the first polls have failed keeps an eye on the SM cycle counter
+// (cheap, unlike the global nanosecond timer); gives up after `limit_cycles` (about two seconds at 2 GHz) and
+// returns false.  Never spins forever.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, long long limit_cycles = 4000000000ll)
 {
-    if (mbar_try_wait(bar, parity)) return true;
-    uint64_t t0 = global_ns();
+#pragma unroll 1
+    for (int i = 0; i < 16; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+#pragma unroll 1
     for (;;) {
-        for (int i = 0; i < 64; i++)
+#pragma unroll 1
+        for (int i = 0; i < 256; i++)
             if (mbar_try_wait(bar, parity)) return true;
-        if (global_ns() - t0 > limit_ns) return false;
+        if (clock64() - t0 > limit_cycles) return false;
     }
 }
 
@@ -91,6 +97,10 @@ __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.p
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes)
 {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async16_ca(uint32_t dst, const void *src, uint32_t src_bytes)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }

@@ -1,34 +1,38 @@
 // Implicit-GEMM convolution on the 5th-generation tensor cores (tcgen05, accumulators in TMEM).
 //
 // GEMM view: D[pixel][cout] = sum_k A[pixel][k] * Wt[cout][k], k = tap*Cin_pad + c.
-//   * one CTA computes 128 consecutive output pixels (flat over n, oh, ow -- tiles may span rows and
-//     images, so small feature maps waste nothing) times BN output channels;
-//   * A (the im2col rows) is never materialised: four producer warps gather 16-byte channel chunks of
-//     the NHWC activation straight into the 128-byte-swizzled K-major tile layout with zero-filling
-//     cp.async (out-of-image taps and ragged tiles become zeros);
-//   * Wt (packed weights, K-major) arrives by 2-D TMA with SWIZZLE_128B, no multicast;
-//   * one elected thread issues tcgen05.mma (kind::f16 for fp16/bf16 with fp32 accumulation, kind::i8
-//     for u8 x u8 with int32 accumulation), stages are recycled through tcgen05.commit -> mbarrier;
-//   * the producer warps turn into the epilogue: tcgen05.ld the accumulator rows (TMEM lane = pixel),
-//     apply bias/BN scale-shift, residual, activation -- or the exact lowp requantisation -- and store
-//     channels-innermost vectors.
+// One PERSISTENT CTA per SM walks output tiles of 128 consecutive pixels (flat over n, oh, ow: tiles
+// may span rows and images, so small feature maps waste nothing) x BN output channels.  Ten warps:
+//   warps 0-3  A producers: gather 16-byte channel chunks of the NHWC activation straight into the
+//              128-byte-swizzled K-major stage layout with zero-filling cp.async (out-of-image taps and
+//              ragged tiles become zeros; no im2col buffer exists anywhere);
+//   warp  4    B producer: packed weights (K-major) by 2-D TMA with SWIZZLE_128B, no multicast;
+//   warp  5    MMA issuer: one elected thread issues tcgen05.mma (kind::f16: fp16/bf16 -> fp32,
+//              kind::i8: u8 x u8 -> int32) into one of TWO TMEM accumulators, recycles stages through
+//              tcgen05.commit -> mbarrier, and hands a finished accumulator to the epilogue;
+//   warps 6-9  epilogue: tcgen05.ld the accumulator rows (TMEM lane = pixel), release the accumulator,
+//              stage a block of columns in shared memory and write it out as runs of consecutive
+//              16-byte chunks per pixel with bias/BN scale-shift, residual and activation applied -- or
+//              the exact lowp requantisation.  The epilogue of tile i overlaps the main loop of tile i+1.
 // Every wait is bounded: a wait that runs out records a code in *status and the CTA drains and exits.
 #include "common.cuh"
 #include <cuda.h>
 #include <string.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 namespace {
 
-constexpr int BM = 128;          // pixels per CTA tile (= TMEM lanes)
-constexpr int A_STAGE_BYTES = BM * 128;
-constexpr int LAG = 2;           // cp.async groups a producer thread keeps in flight
+constexpr int BM = 128;                  // pixels per tile (= TMEM lanes)
+constexpr int A_STAGE_BYTES = BM * 128;  // 128 rows of one 128-byte K block
+constexpr int NTHREADS = 448;           // 4 producer + 1 TMA + 1 MMA + 2 x 4 epilogue warps
 
 struct ConvTcParams {
     const uint8_t *x;
     uint8_t *y;
     const int *kinfo;
-    int P, H, W, in_ld, oW, oHW, dH, dW, padH, padW, kH, kW, Cin, Cout, out_ld, nkb, n_kchunks;
+    int P, H, W, in_ld, oH, oW, oHW, dH, dW, padH, padW, kH, kW, Cin, Cout, out_ld, nkb, n_kchunks;
+    int m_tiles, n_tiles;
     const float *scale, *shift, *slope;
     const uint8_t *res;
     int res_ld;
@@ -38,11 +42,12 @@ struct ConvTcParams {
     int a_off, b_off, c_off, c_mult, c_shift;
     const int *wsat, *bias_add, *csum;
     int tail_start, relu_thr, relu_val;
+    int use_l1;  // gather through L1: neighbouring taps of one tile re-read the same input pixels
     int *acc_out;
     int *status;
 };
 
-template <int KIND> struct kind_traits;             // 0 = fp16, 1 = bf16, 2 = u8
+template <int KIND> struct kind_traits;  // 0 = fp16, 1 = bf16, 2 = u8
 template <> struct kind_traits<0> { static constexpr int esize = 2; };
 template <> struct kind_traits<1> { static constexpr int esize = 2; };
 template <> struct kind_traits<2> { static constexpr int esize = 1; };
@@ -62,36 +67,97 @@ __device__ __forceinline__ float2 unpack2(uint32_t v, int kind)
     return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&v));
 }
 
-template <int KIND, int BN, int STAGES>
-__global__ void __launch_bounds__(192, 1) conv_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const ConvTcParams p)
+// One 16-byte output chunk (8 channels of one pixel) of the floating-point epilogue:
+//   y = act( self * (acc*scale + shift) + res_coef * residual ), channels >= Cout forced to 0.
+// ACT: 0 none, 1 threshold, 2 anything (leaky / PReLU), 3 plain ReLU (threshold 0, value 0).
+template <int KIND, bool HAS_RES, int ACT, bool CHECK>
+__device__ __forceinline__ uint4 epi_chunk(const float4 &a0, const float4 &a1, const float (&sc)[8], const float (&sh)[8],
+                                           const float (&sl)[8], const uint4 &rv, const ConvTcParams &p, int c0)
 {
+    const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int h = 0; h < 4; h++) {
+        float v0 = fmaf(av[h * 2], sc[h * 2], sh[h * 2]);
+        float v1 = fmaf(av[h * 2 + 1], sc[h * 2 + 1], sh[h * 2 + 1]);
+        if (HAS_RES) {
+            // self_coef is +-1 in every fused CAddTable/CSubTable; the launcher folds it into scale and shift
+            // (exact), so only the residual's own coefficient is left here
+            const float2 rr = unpack2(rw[h], KIND);
+            v0 = fmaf(p.res_coef, rr.x, v0);
+            v1 = fmaf(p.res_coef, rr.y, v1);
+        }
+        if (ACT == 3) {  // x > 0 ? x : 0
+            v0 = fmaxf(v0, 0.f);
+            v1 = fmaxf(v1, 0.f);
+        } else if (ACT == 1) {
+            v0 = v0 > p.act_th ? v0 : p.act_val;
+            v1 = v1 > p.act_th ? v1 : p.act_val;
+        } else if (ACT == 2) {
+            v0 = thb_apply_act(v0, p.act_kind, p.act_th, p.act_val, p.act_alpha, sl[h * 2]);
+            v1 = thb_apply_act(v1, p.act_kind, p.act_th, p.act_val, p.act_alpha, sl[h * 2 + 1]);
+        }
+        if (CHECK) {
+            if (c0 + h * 2 >= p.Cout) v0 = 0.f;
+            if (c0 + h * 2 + 1 >= p.Cout) v1 = 0.f;
+        }
+        ow[h] = pack2(v0, v1, KIND);
+    }
+    return make_uint4(ow[0], ow[1], ow[2], ow[3]);
+}
+
+// shared-memory plan of one CTA
+template <int KIND, int BN, int STAGES> struct Smem {
+    static constexpr int SUBN = BN >= 256 ? 32 : (BN >= 64 ? 64 : BN);           // columns staged at a time
+    static constexpr int B_STAGE_BYTES = BN * 128;
+    static constexpr size_t PIPE = (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
+    static constexpr size_t STAGING = KIND == 2 ? (size_t)BM * (SUBN + 16) : (size_t)BM * (SUBN + 4) * 4;
+    static constexpr size_t STAGING_PAD = (STAGING + 127) / 128 * 128;  // one staging tile per epilogue group
+    static constexpr size_t BARS = (2 * STAGES + 8) * 8 + 16;
+    static constexpr size_t TOTAL = 1024 + PIPE + 2 * STAGING_PAD + BARS + 64;
+};
+
+template <int KIND, int BN, int STAGES>
+__global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const ConvTcParams p)
+{
+    using L = Smem<KIND, BN, STAGES>;
     constexpr int ES = kind_traits<KIND>::esize;
-    constexpr int BKE = 128 / ES;                 // K elements per 128-byte stage row
-    constexpr int B_STAGE_BYTES = BN * 128;
+    constexpr int BKE = 128 / ES;  // K elements per 128-byte stage row
+    constexpr int B_STAGE_BYTES = L::B_STAGE_BYTES;
+    constexpr int SUBN = L::SUBN;
+    constexpr int LAG = STAGES >= 4 ? STAGES - 2 : STAGES - 1;  // cp.async groups a producer thread keeps in flight
     constexpr uint32_t IDESC = make_idesc(KIND == 2 ? 2u : 1u, KIND == 1 ? 1u : 0u, BN);
-    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *sA = smem;
     uint8_t *sB = smem + STAGES * A_STAGE_BYTES;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sB + STAGES * B_STAGE_BYTES);
-    uint64_t *full = bars, *empty = bars + STAGES, *tmem_full = bars + 2 * STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 1);
+    uint8_t *stage_buf = smem + L::PIPE;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(stage_buf + 2 * L::STAGING_PAD);
+    uint64_t *full = bars, *empty = bars + STAGES;
+    uint64_t *acc_full = bars + 2 * STAGES, *acc_empty = acc_full + 2;
+    uint64_t *stg_ready = acc_empty + 2, *stg_free = stg_ready + 2;  // one pair per epilogue group
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(stg_free + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-    float *ep0 = reinterpret_cast<float *>(tmem_slot + 2);   // scale   | wtot (int)
-    float *ep1 = ep0 + BN;                                    // shift   | bias_add (int)
-    float *ep2 = ep1 + BN;                                    // slope
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+    const int total_tiles = p.m_tiles * p.n_tiles;
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(smem_u32(&full[s]), 128 + 1);
             mbar_init(smem_u32(&empty[s]), 1);
         }
-        mbar_init(smem_u32(tmem_full), 1);
+        for (int b = 0; b < 2; b++) {
+            mbar_init(smem_u32(&acc_full[b]), 1);
+            mbar_init(smem_u32(&acc_empty[b]), 128);
+        }
+        for (int g = 0; g < 2; g++) {
+            mbar_init(smem_u32(&stg_ready[g]), 128);
+            mbar_init(smem_u32(&stg_free[g]), 128);
+        }
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
@@ -101,237 +167,330 @@ __global__ void __launch_bounds__(192, 1) conv_tc_kernel(const __grid_constant__
         tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
         tmem_relinquish();
     }
-    if (warp < 4) {
-        for (int i = tid; i < BN; i += 128) {
-            int c = n0 + i;
-            if (KIND == 2) {
-                int tot = 0, ba = 0;
-                if (c < p.Cout) {
-                    tot = p.wsat[(size_t)c * (p.kH + 1) * (p.kW + 1) + (p.kH + 1) * (p.kW + 1) - 1];
-                    ba = p.bias_add ? p.bias_add[c] : 0;
-                }
-                reinterpret_cast<int *>(ep0)[i] = tot;
-                reinterpret_cast<int *>(ep1)[i] = ba;
-            } else {
-                ep0[i] = c < p.Cout ? (p.scale ? p.scale[c] : 1.f) : 0.f;
-                ep1[i] = c < p.Cout ? (p.shift ? p.shift[c] : 0.f) : 0.f;
-                ep2[i] = (c < p.Cout && p.slope) ? p.slope[c] : 0.f;
-            }
-        }
-    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp < 4) {
-        // ------------------------------------------------------------------ A producer
+        // ================================================================== A producer
         const int chunk = lane & 7;
-        int ih0[8], iw0[8], pixbase[8];
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            int r = warp * 32 + j * 4 + (lane >> 3);
-            int pm = m0 + r;
-            if (pm < p.P) {
+        bool alive = true;
+        int it = 0;  // K blocks issued so far by this CTA, over all its tiles
+        for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+            const int m0 = (tile / p.n_tiles) * BM;
+            // this thread's eight rows are 4 pixels apart: decompose the first, then step
+            int ih0[8], iw0[8], pixbase[8];
+            {
+                int pm = m0 + warp * 32 + (lane >> 3);
                 int n = pm / p.oHW, rem = pm - n * p.oHW;
                 int oh = rem / p.oW, ow = rem - oh * p.oW;
-                ih0[j] = oh * p.dH - p.padH;
-                iw0[j] = ow * p.dW - p.padW;
-                pixbase[j] = n * p.H * p.W;
-            } else {
-                ih0[j] = iw0[j] = 0;
-                pixbase[j] = -1;
-            }
-        }
-        bool alive = true;
-        for (int kb = 0; kb < p.nkb && alive; kb++) {
-            const int s = kb % STAGES;
-            const uint32_t ph = (kb / STAGES) & 1;
-            if (!mbar_wait_bounded(smem_u32(&empty[s]), ph ^ 1)) {
-                if (lane == 0) atomicExch(p.status, 1);
-                *abort_flag = 1;
-                alive = false;
-                break;
-            }
-            const int g = kb * 8 + chunk;
-            const int ki = g < p.n_kchunks ? p.kinfo[g] : -1;
-            const int dh = (ki >> 24) & 0x7f, dw = (ki >> 16) & 0xff;
-            const size_t coff = (size_t)(ki & 0xffff) * 16;
-            const uint32_t a_stage = smem_u32(sA + s * A_STAGE_BYTES);
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
-                const int r = warp * 32 + j * 4 + (lane >> 3);
-                const int ih = ih0[j] + dh, iw = iw0[j] + dw;
-                const bool ok = ki >= 0 && pixbase[j] >= 0 && (unsigned)ih < (unsigned)p.H && (unsigned)iw < (unsigned)p.W;
-                const uint8_t *src = ok ? p.x + ((size_t)(pixbase[j] + ih * p.W + iw) * p.in_ld) * ES + coff : p.x;
-                cp_async16(a_stage + r * 128 + ((chunk ^ (r & 7)) << 4), src, ok ? 16u : 0u);
+                for (int j = 0; j < 8; j++) {
+                    if (pm < p.P) {
+                        ih0[j] = oh * p.dH - p.padH;
+                        iw0[j] = ow * p.dW - p.padW;
+                        pixbase[j] = n * p.H * p.W;
+                    } else {
+                        ih0[j] = iw0[j] = 0;
+                        pixbase[j] = -1;
+                    }
+                    pm += 4;
+                    ow += 4;
+                    while (ow >= p.oW) {
+                        ow -= p.oW;
+                        if (++oh == p.oH) { oh = 0; n++; }
+                    }
+                }
             }
-            cp_async_commit();
-            if (kb >= LAG) {
-                cp_async_wait<LAG>();
-                fence_proxy_async_smem();
-                mbar_arrive(smem_u32(&full[(kb - LAG) % STAGES]));
+            int ki_next = chunk < p.n_kchunks ? __ldg(p.kinfo + chunk) : -1;
+            for (int kb = 0; kb < p.nkb; kb++, it++) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                const int ki = ki_next;
+                {
+                    const int g = (kb + 1) * 8 + chunk;
+                    ki_next = (kb + 1 < p.nkb && g < p.n_kchunks) ? __ldg(p.kinfo + g) : -1;
+                }
+                if (!mbar_wait_bounded(smem_u32(&empty[s]), ph ^ 1)) {
+                    if (lane == 0) atomicExch(p.status, 1);
+                    *abort_flag = 1;
+                    alive = false;
+                    break;
+                }
+                const int dh = (ki >> 24) & 0x7f, dw = (ki >> 16) & 0xff;
+                const size_t coff = (size_t)(ki & 0xffff) * 16;
+                const uint32_t a_stage = smem_u32(sA + s * A_STAGE_BYTES);
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const int r = warp * 32 + j * 4 + (lane >> 3);
+                    const int ih = ih0[j] + dh, iw = iw0[j] + dw;
+                    const bool ok = ki >= 0 && pixbase[j] >= 0 && (unsigned)ih < (unsigned)p.H && (unsigned)iw < (unsigned)p.W;
+                    const uint8_t *src = ok ? p.x + ((size_t)(pixbase[j] + ih * p.W + iw) * p.in_ld) * ES + coff : p.x;
+                    const uint32_t dst = a_stage + r * 128 + ((chunk ^ (r & 7)) << 4);
+                    if (p.use_l1) cp_async16_ca(dst, src, ok ? 16u : 0u);
+                    else cp_async16(dst, src, ok ? 16u : 0u);
+                }
+                cp_async_commit();
+                if (it >= LAG) {
+                    cp_async_wait<LAG>();
+                    fence_proxy_async_smem();
+                    mbar_arrive(smem_u32(&full[(it - LAG) % STAGES]));
+                }
             }
         }
         cp_async_wait<0>();
         fence_proxy_async_smem();
         if (alive)
-            for (int kb = (p.nkb > LAG ? p.nkb - LAG : 0); kb < p.nkb; kb++) mbar_arrive(smem_u32(&full[kb % STAGES]));
-
-        // ------------------------------------------------------------------ epilogue
-        const int row = warp * 32 + lane;
-        const int pm = m0 + row;
-        const bool valid = pm < p.P;
-        bool have_acc = alive && !*abort_flag;
-        if (have_acc && !mbar_wait_bounded(smem_u32(tmem_full), 0)) {
-            if (lane == 0) atomicExch(p.status, 2);
-            *abort_flag = 1;
-            have_acc = false;
+            for (int k = (it > LAG ? it - LAG : 0); k < it; k++) mbar_arrive(smem_u32(&full[k % STAGES]));
+    } else if (warp == 4) {
+        // ================================================================== weight (B) TMA producer
+        if (lane == 0) {
+            int it = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+                const int n0 = (tile % p.n_tiles) * BN;
+                for (int kb = 0; kb < p.nkb; kb++, it++) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait_bounded(smem_u32(&empty[s]), ph ^ 1)) {
+                        atomicExch(p.status, 3);
+                        *abort_flag = 1;
+                        alive = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(smem_u32(&full[s]), B_STAGE_BYTES);
+                    tma_load_2d(smem_u32(sB + s * B_STAGE_BYTES), &tmapW, smem_u32(&full[s]), kb * BKE, n0);
+                }
+            }
         }
-        have_acc = __all_sync(0xffffffffu, have_acc);
-        if (have_acc) {
-            tc_fence_after();
+        __syncwarp();
+    } else if (warp == 5) {
+        // ================================================================== MMA issuer
+        if (lane == 0) {
+            int it = 0, lt = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, lt++) {
+                const int b = lt & 1;
+                const uint32_t acc_ph = (lt >> 1) & 1;
+                if (!mbar_wait_bounded(smem_u32(&acc_empty[b]), acc_ph ^ 1)) {
+                    atomicExch(p.status, 6);
+                    *abort_flag = 1;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + b * BN;
+                for (int kb = 0; kb < p.nkb; kb++, it++) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait_bounded(smem_u32(&full[s]), ph)) {
+                        atomicExch(p.status, 4);
+                        *abort_flag = 1;
+                        alive = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    fence_proxy_async_smem();
+                    const uint64_t adesc = make_sw128_kmajor_desc(smem_u32(sA + s * A_STAGE_BYTES));
+                    const uint64_t bdesc = make_sw128_kmajor_desc(smem_u32(sB + s * B_STAGE_BYTES));
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const uint32_t accum = (kb | k) != 0;
+                        if (KIND == 2) tc_mma_i8(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, accum);
+                        else tc_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, accum);
+                    }
+                    tc_commit(smem_u32(&empty[s]));
+                }
+                if (alive) tc_commit(smem_u32(&acc_full[b]));
+            }
+        }
+        __syncwarp();
+    } else {
+        // ================================================================== epilogue (warps 6-13)
+        // Two groups of four warps; group g owns TMEM accumulator g and every second tile of this CTA, so the
+        // write-out of one tile overlaps the accumulator drain of the next.
+        const int grp = (warp - 6) >> 2;
+        const int et = tid - 192 - grp * 128;  // 0..127 within the group
+        const int quad = warp & 3;             // TMEM lane quadrant this warp may read
+        const int row = quad * 32 + lane;      // tile row (= pixel) owned in phase 1
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + grp * BN;
+        uint8_t *stg = stage_buf + grp * L::STAGING_PAD;
+        const uint32_t bar_ready = smem_u32(&stg_ready[grp]), bar_free = smem_u32(&stg_free[grp]);
+        const bool has_res = KIND != 2 && p.res != nullptr;
+        const int act_mode = p.act_kind == THB_ACT_NONE ? 0
+                             : p.act_kind != THB_ACT_THRESHOLD ? 2
+                             : (p.act_th == 0.f && p.act_val == 0.f) ? 3 : 1;
+        bool alive = true;
+        int sub_it = 0;                        // staging blocks this group has processed
+        for (int lt = grp; alive; lt += 2) {
+            const int tile = blockIdx.x + lt * gridDim.x;
+            if (tile >= total_tiles) break;
+            const int m0 = (tile / p.n_tiles) * BM, n0 = (tile % p.n_tiles) * BN;
+            const int pm = m0 + row;
+            const bool valid = pm < p.P;
+            const bool check = n0 + BN > p.Cout;  // the tile reaches beyond the last real channel
             // per-pixel terms of the u8 zero-point correction
             int corr_pix = 0, r0 = 0, r1 = 0, s0 = 0, s1 = 0, plane_pos = 0;
             bool interior = true;
             if (KIND == 2 && valid) {
-                int n = pm / p.oHW, rem = pm - n * p.oHW;
-                int oh = rem / p.oW, ow = rem - oh * p.oW;
+                const int n = pm / p.oHW, rem = pm - n * p.oHW;
+                const int oh = rem / p.oW, ow = rem - oh * p.oW;
                 plane_pos = rem;
-                int ihb = oh * p.dH - p.padH, iwb = ow * p.dW - p.padW;
+                const int ihb = oh * p.dH - p.padH, iwb = ow * p.dW - p.padW;
                 r0 = max(0, -ihb); r1 = min(p.kH, p.H - ihb);
                 s0 = max(0, -iwb); s1 = min(p.kW, p.W - iwb);
                 interior = r0 == 0 && s0 == 0 && r1 == p.kH && s1 == p.kW;
                 int xsum = 0;
                 const int *cs = p.csum + (size_t)n * p.H * p.W;
                 for (int r = r0; r < r1; r++)
-                    for (int s = s0; s < s1; s++) xsum += cs[(ihb + r) * p.W + iwb + s];
-                int nvalid = max(0, r1 - r0) * max(0, s1 - s0);
+                    for (int s = s0; s < s1; s++) xsum += __ldg(cs + (ihb + r) * p.W + iwb + s);
+                const int nvalid = max(0, r1 - r0) * max(0, s1 - s0);
                 corr_pix = p.a_off * (xsum + p.b_off * nvalid * p.Cin);
             }
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+            bool have_acc = false;
 #pragma unroll 1
-            for (int cc = 0; cc < BN / 32; cc++) {
-                uint32_t acc[32];
-                __syncwarp();
-                tmem_ld32(lane_addr + cc * 32, acc);
-                tmem_ld_wait();
-                const int c0 = n0 + cc * 32;
-                if (!valid || c0 >= p.Cout) continue;
-                if (KIND == 2) {
-                    const int *wtot = reinterpret_cast<const int *>(ep0) + cc * 32;
-                    const int *badd = reinterpret_cast<const int *>(ep1) + cc * 32;
-                    const int satw = p.kW + 1, satn = (p.kH + 1) * (p.kW + 1);
-                    uint32_t outw[8];
+            for (int sb = 0; sb < BN / SUBN; sb++, sub_it++) {
+                const int nsub0 = n0 + sb * SUBN;
+                // the residual chunks this thread will need in phase 2: issued now, consumed after the staging
+                // round trip, so their latency hides behind the accumulator drain
+                constexpr int CPRF = SUBN / 8, RPI = 128 / CPRF;
+                const int cg = et % CPRF, rbase = et / CPRF, c0f = nsub0 + cg * 8;
+                uint4 rv[CPRF];
+                if (KIND != 2) {
 #pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        const int c = c0 + i;
-                        int q = 0;
-                        if (c < p.Cout) {
-                            int wv;
-                            if (interior) wv = wtot[i];
-                            else {
+                    for (int u = 0; u < CPRF; u++) {
+                        const int pm2 = m0 + rbase + u * RPI;
+                        rv[u] = make_uint4(0, 0, 0, 0);
+                        if (has_res && pm2 < p.P && c0f < p.Cout)
+                            rv[u] = __ldg(reinterpret_cast<const uint4 *>(p.res + ((size_t)pm2 * p.res_ld + c0f) * 2));
+                    }
+                }
+                if (!have_acc) {
+                    if (!mbar_wait_bounded(smem_u32(&acc_full[grp]), (lt >> 1) & 1)) {
+                        if (lane == 0) atomicExch(p.status, 2);
+                        *abort_flag = 1;
+                        alive = false;
+                    }
+                    alive = __all_sync(0xffffffffu, alive);
+                    if (!alive) break;
+                    tc_fence_after();
+                    have_acc = true;
+                }
+                // ---- phase 1: this thread's pixel row, SUBN accumulator columns -> staging tile
+                if (!mbar_wait_bounded(bar_free, (sub_it & 1) ^ 1)) {
+                    if (lane == 0) atomicExch(p.status, 7);
+                    *abort_flag = 1;
+                    alive = false;
+                }
+                alive = __all_sync(0xffffffffu, alive);
+                if (!alive) break;
+#pragma unroll
+                for (int cc = 0; cc < SUBN / 32; cc++) {
+                    uint32_t acc[32];
+                    __syncwarp();
+                    tmem_ld32(lane_addr + sb * SUBN + cc * 32, acc);
+                    tmem_ld_wait();
+                    if (KIND == 2) {
+                        const int c0 = nsub0 + cc * 32;
+                        const int satw = p.kW + 1, satn = (p.kH + 1) * (p.kW + 1);
+                        uint32_t outw[8];
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            const int c = c0 + i;
+                            int q = 0;
+                            if (valid && c < p.Cout) {
                                 const int *t = p.wsat + (size_t)c * satn;
-                                wv = t[r1 * satw + s1] - t[r0 * satw + s1] - t[r1 * satw + s0] + t[r0 * satw + s0];
+                                int wv;
+                                if (interior) wv = __ldg(t + satn - 1);
+                                else wv = __ldg(t + r1 * satw + s1) - __ldg(t + r0 * satw + s1) - __ldg(t + r1 * satw + s0) + __ldg(t + r0 * satw + s0);
+                                const int a = (int)acc[i] + p.b_off * wv + corr_pix;
+                                if (p.acc_out) p.acc_out[(size_t)pm * p.Cout + c] = a;
+                                uint32_t v = ((uint32_t)a + (uint32_t)p.c_off) * (uint32_t)p.c_mult;
+                                if (p.c_shift >= 1) v += 1u << (p.c_shift - 1);
+                                int sres = (int)v;
+                                if (p.c_shift > 0) sres >>= p.c_shift;
+                                q = min(255, max(0, sres));
+                                int t2 = q + (p.bias_add ? __ldg(p.bias_add + c) : 0);
+                                if (plane_pos < p.tail_start) t2 = min(255, max(0, t2));
+                                else t2 = t2 > 255 ? 255 : (t2 & 255);
+                                q = t2;
+                                if (p.relu_thr >= 0) q = q > p.relu_thr ? q : p.relu_val;
                             }
-                            const int a = (int)acc[i] + p.b_off * wv + corr_pix;
-                            if (p.acc_out) p.acc_out[(size_t)pm * p.Cout + c] = a;
-                            uint32_t v = ((uint32_t)a + (uint32_t)p.c_off) * (uint32_t)p.c_mult;
-                            if (p.c_shift >= 1) v += 1u << (p.c_shift - 1);
-                            int sres = (int)v;
-                            if (p.c_shift > 0) sres >>= p.c_shift;
-                            q = min(255, max(0, sres));
-                            int t2 = q + badd[i];
-                            if (plane_pos < p.tail_start) t2 = min(255, max(0, t2));
-                            else t2 = t2 > 255 ? 255 : (t2 & 255);
-                            q = t2;
-                            if (p.relu_thr >= 0) q = q > p.relu_thr ? q : p.relu_val;
+                            if ((i & 3) == 0) outw[i >> 2] = 0;
+                            outw[i >> 2] |= (uint32_t)q << (8 * (i & 3));
                         }
-                        if ((i & 3) == 0) outw[i >> 2] = 0;
-                        outw[i >> 2] |= (uint32_t)q << (8 * (i & 3));
-                    }
-                    uint8_t *dst = p.y + (size_t)pm * p.out_ld + c0;
+                        uint4 *dst = reinterpret_cast<uint4 *>(stg + row * (SUBN + 16) + cc * 32);
+                        dst[0] = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+                        dst[1] = make_uint4(outw[4], outw[5], outw[6], outw[7]);
+                    } else {
+                        uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<float *>(stg) + row * (SUBN + 4) + cc * 32);
 #pragma unroll
-                    for (int v4 = 0; v4 < 2; v4++)
-                        if (c0 + v4 * 16 < p.Cout)
-                            *reinterpret_cast<uint4 *>(dst + v4 * 16) =
-                                make_uint4(outw[v4 * 4], outw[v4 * 4 + 1], outw[v4 * 4 + 2], outw[v4 * 4 + 3]);
-                } else {
-                    const float *sc = ep0 + cc * 32, *sh = ep1 + cc * 32, *sl = ep2 + cc * 32;
-                    const uint8_t *rsrc = p.res ? p.res + ((size_t)pm * p.res_ld + c0) * 2 : nullptr;
-                    uint8_t *dst = p.y + ((size_t)pm * p.out_ld + c0) * 2;
-#pragma unroll
-                    for (int v8 = 0; v8 < 4; v8++) {
-                        if (c0 + v8 * 8 >= p.Cout) break;
-                        uint4 rv = make_uint4(0, 0, 0, 0);
-                        if (rsrc) rv = *reinterpret_cast<const uint4 *>(rsrc + v8 * 16);
-                        const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-                        uint32_t ow[4];
-#pragma unroll
-                        for (int h = 0; h < 4; h++) {
-                            const int i = v8 * 8 + h * 2;
-                            float v0 = __uint_as_float(acc[i]) * sc[i] + sh[i];
-                            float v1 = __uint_as_float(acc[i + 1]) * sc[i + 1] + sh[i + 1];
-                            if (rsrc) {
-                                float2 rr = unpack2(rw[h], KIND);
-                                v0 = p.self_coef * v0 + p.res_coef * rr.x;
-                                v1 = p.self_coef * v1 + p.res_coef * rr.y;
-                            }
-                            v0 = thb_apply_act(v0, p.act_kind, p.act_th, p.act_val, p.act_alpha, sl[i]);
-                            v1 = thb_apply_act(v1, p.act_kind, p.act_th, p.act_val, p.act_alpha, sl[i + 1]);
-                            if (c0 + i >= p.Cout) v0 = 0.f;
-                            if (c0 + i + 1 >= p.Cout) v1 = 0.f;
-                            ow[h] = pack2(v0, v1, KIND);
-                        }
-                        *reinterpret_cast<uint4 *>(dst + v8 * 16) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                        for (int q = 0; q < 8; q++) dst[q] = make_uint4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
                     }
                 }
-            }
-        }
-    } else if (warp == 4) {
-        // ------------------------------------------------------------------ weight (B) TMA producer
-        if (lane == 0) {
-            for (int kb = 0; kb < p.nkb; kb++) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
-                if (!mbar_wait_bounded(smem_u32(&empty[s]), ph ^ 1)) {
-                    atomicExch(p.status, 3);
-                    *abort_flag = 1;
-                    break;
+                if (sb == BN / SUBN - 1) {
+                    // every column of this accumulator has been read: hand it back to the MMA warp
+                    tc_fence_before();
+                    mbar_arrive(smem_u32(&acc_empty[grp]));
                 }
-                mbar_arrive_expect_tx(smem_u32(&full[s]), B_STAGE_BYTES);
-                tma_load_2d(smem_u32(sB + s * B_STAGE_BYTES), &tmapW, smem_u32(&full[s]), kb * BKE, n0);
-            }
-        }
-        __syncwarp();
-    } else {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            bool ok = true;
-            for (int kb = 0; kb < p.nkb; kb++) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
-                if (!mbar_wait_bounded(smem_u32(&full[s]), ph)) {
-                    atomicExch(p.status, 4);
+                mbar_arrive(bar_ready);
+                if (!mbar_wait_bounded(bar_ready, sub_it & 1)) {
+                    if (lane == 0) atomicExch(p.status, 5);
                     *abort_flag = 1;
-                    ok = false;
-                    break;
+                    alive = false;
                 }
-                tc_fence_after();
-                fence_proxy_async_smem();
-                const uint64_t adesc = make_sw128_kmajor_desc(smem_u32(sA + s * A_STAGE_BYTES));
-                const uint64_t bdesc = make_sw128_kmajor_desc(smem_u32(sB + s * B_STAGE_BYTES));
+                alive = __all_sync(0xffffffffu, alive);
+                if (!alive) break;
+                // ---- phase 2: coalesced write-out of the staged block
+                if (KIND == 2) {
+                    constexpr int CPR = SUBN / 16;
 #pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    const uint32_t accum = (kb | k) != 0;
-                    if (KIND == 2) tc_mma_i8(tmem_base, adesc + 2 * k, bdesc + 2 * k, IDESC, accum);
-                    else tc_mma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, IDESC, accum);
+                    for (int u = 0; u < CPR; u++) {
+                        const int idx = et + u * 128, r = idx / CPR, cg2 = idx - r * CPR;
+                        const int pm2 = m0 + r, c0 = nsub0 + cg2 * 16;
+                        if (pm2 < p.P && c0 < p.Cout)
+                            *reinterpret_cast<uint4 *>(p.y + (size_t)pm2 * p.out_ld + c0) =
+                                *reinterpret_cast<const uint4 *>(stg + r * (SUBN + 16) + cg2 * 16);
+                    }
+                } else if (c0f < p.Cout) {
+                    const float *stage = reinterpret_cast<const float *>(stg);
+                    float sc[8], sh[8], sl[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) { sc[i] = 1.f; sh[i] = 0.f; sl[i] = 0.f; }
+                    if (p.scale) {
+                        const float4 t0 = __ldg(reinterpret_cast<const float4 *>(p.scale + c0f)), t1 = __ldg(reinterpret_cast<const float4 *>(p.scale + c0f + 4));
+                        sc[0] = t0.x; sc[1] = t0.y; sc[2] = t0.z; sc[3] = t0.w; sc[4] = t1.x; sc[5] = t1.y; sc[6] = t1.z; sc[7] = t1.w;
+                    }
+                    if (p.shift) {
+                        const float4 t0 = __ldg(reinterpret_cast<const float4 *>(p.shift + c0f)), t1 = __ldg(reinterpret_cast<const float4 *>(p.shift + c0f + 4));
+                        sh[0] = t0.x; sh[1] = t0.y; sh[2] = t0.z; sh[3] = t0.w; sh[4] = t1.x; sh[5] = t1.y; sh[6] = t1.z; sh[7] = t1.w;
+                    }
+                    if (p.slope) {
+                        const float4 t0 = __ldg(reinterpret_cast<const float4 *>(p.slope + c0f)), t1 = __ldg(reinterpret_cast<const float4 *>(p.slope + c0f + 4));
+                        sl[0] = t0.x; sl[1] = t0.y; sl[2] = t0.z; sl[3] = t0.w; sl[4] = t1.x; sl[5] = t1.y; sl[6] = t1.z; sl[7] = t1.w;
+                    }
+                    if (has_res && p.self_coef != 1.f) {
+#pragma unroll
+                        for (int i = 0; i < 8; i++) { sc[i] *= p.self_coef; sh[i] *= p.self_coef; }
+                    }
+#pragma unroll
+                    for (int u = 0; u < CPRF; u++) {
+                        const int r = rbase + u * RPI, pm2 = m0 + r;
+                        if (pm2 >= p.P) continue;
+                        const float4 a0 = *reinterpret_cast<const float4 *>(stage + r * (SUBN + 4) + cg * 8);
+                        const float4 a1 = *reinterpret_cast<const float4 *>(stage + r * (SUBN + 4) + cg * 8 + 4);
+                        uint4 o;
+                        if (check || act_mode == 2 || act_mode == 1) o = epi_chunk<KIND, true, 2, true>(a0, a1, sc, sh, sl, rv[u], p, c0f);
+                        else if (has_res) o = act_mode ? epi_chunk<KIND, true, 3, false>(a0, a1, sc, sh, sl, rv[u], p, c0f)
+                                                       : epi_chunk<KIND, true, 0, false>(a0, a1, sc, sh, sl, rv[u], p, c0f);
+                        else o = act_mode ? epi_chunk<KIND, false, 3, false>(a0, a1, sc, sh, sl, rv[u], p, c0f)
+                                          : epi_chunk<KIND, false, 0, false>(a0, a1, sc, sh, sl, rv[u], p, c0f);
+                        *reinterpret_cast<uint4 *>(p.y + ((size_t)pm2 * p.out_ld + c0f) * 2) = o;
+                    }
                 }
-                tc_commit(smem_u32(&empty[s]));
+                mbar_arrive(bar_free);
             }
-            if (ok) tc_commit(smem_u32(tmem_full));
         }
-        __syncwarp();
     }
 
     tc_fence_before();
@@ -342,34 +501,45 @@ __global__ void __launch_bounds__(192, 1) conv_tc_kernel(const __grid_constant__
     }
 }
 
-template <int BN, int STAGES> constexpr size_t conv_tc_smem()
+int num_sms()
 {
-    return 1024 + (size_t)STAGES * (A_STAGE_BYTES + BN * 128) + (2 * STAGES + 1) * 8 + 8 + 3 * BN * 4 + 64;
+    static int n[16] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 16) dev = 0;
+    if (!n[dev]) cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
+    return n[dev] > 0 ? n[dev] : 148;
 }
 
 template <int KIND, int BN, int STAGES>
-int launch_tc(const CUtensorMap &tm, const ConvTcParams &p, int gx, int gy, cudaStream_t st)
+int launch_tc(const CUtensorMap &tm, const ConvTcParams &p, cudaStream_t st)
 {
-    static bool configured = false;
+    static bool configured[16] = {false};
     auto kern = conv_tc_kernel<KIND, BN, STAGES>;
-    constexpr size_t smem = conv_tc_smem<BN, STAGES>();
-    if (!configured) {
+    constexpr size_t smem = Smem<KIND, BN, STAGES>::TOTAL;
+    static_assert(smem <= 232448, "shared memory plan exceeds the 227 KB a CTA can have");
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 16) dev = 0;
+    if (!configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return thb_note_launch(e, "conv_tc smem attribute");
-        configured = true;
+        configured[dev] = true;
     }
-    kern<<<dim3(gx, gy), 192, smem, st>>>(tm, p);
+    const int tiles = p.m_tiles * p.n_tiles;
+    const int grid = tiles < num_sms() ? tiles : num_sms();
+    kern<<<grid, NTHREADS, smem, st>>>(tm, p);
     return THB_LAUNCH_CHECK("conv_tc_kernel");
 }
 
 template <int KIND>
-int dispatch_bn(int BN, const CUtensorMap &tm, const ConvTcParams &p, int gx, int gy, cudaStream_t st)
+int dispatch_bn(int BN, const CUtensorMap &tm, const ConvTcParams &p, cudaStream_t st)
 {
     switch (BN) {
-    case 32: return launch_tc<KIND, 32, 4>(tm, p, gx, gy, st);
-    case 64: return launch_tc<KIND, 64, 4>(tm, p, gx, gy, st);
-    case 128: return launch_tc<KIND, 128, 3>(tm, p, gx, gy, st);
-    case 256: return launch_tc<KIND, 256, 4>(tm, p, gx, gy, st);
+    case 32: return launch_tc<KIND, 32, 6>(tm, p, st);
+    case 64: return launch_tc<KIND, 64, 5>(tm, p, st);
+    case 128: return launch_tc<KIND, 128, 4>(tm, p, st);
+    case 256: return launch_tc<KIND, 256, 3>(tm, p, st);
     }
     return THB_ERR_UNSUPPORTED;
 }
@@ -427,7 +597,7 @@ extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, t
     p.y = (uint8_t *)y;
     p.kinfo = d->kinfo;
     p.P = d->N * d->oH * d->oW;
-    p.H = d->H; p.W = d->W; p.in_ld = d->in_ld; p.oW = d->oW; p.oHW = d->oH * d->oW;
+    p.H = d->H; p.W = d->W; p.in_ld = d->in_ld; p.oH = d->oH; p.oW = d->oW; p.oHW = d->oH * d->oW;
     p.dH = d->dH; p.dW = d->dW; p.padH = d->padH; p.padW = d->padW; p.kH = d->kH; p.kW = d->kW;
     p.Cin = d->Cin; p.Cout = d->Cout; p.out_ld = d->out_ld;
     p.nkb = d->Ktot_pad / (128 / es);
@@ -440,17 +610,20 @@ extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, t
     p.wsat = d->wsat; p.bias_add = d->bias_add; p.csum = d->csum;
     p.tail_start = d->tail_start; p.relu_thr = d->relu_thr; p.relu_val = d->relu_val;
     p.acc_out = d->acc_out;
+    p.use_l1 = d->kH * d->kW > 1;
+    if (const char *e = getenv("THB200_CONV_L1")) p.use_l1 = atoi(e);
     p.status = d->status;
     if (!p.status) return THB_ERR_ARG;
     if (d->dtype == THB_U8 && (!p.wsat || !p.csum)) return THB_ERR_ARG;
     if (p.P <= 0) return THB_OK;
-    const int gx = (p.P + BM - 1) / BM, gy = d->Cout_pad / d->BN;
+    p.m_tiles = (p.P + BM - 1) / BM;
+    p.n_tiles = d->Cout_pad / d->BN;
     const CUtensorMap &tm = *reinterpret_cast<const CUtensorMap *>(d->tmap);
     cudaStream_t st = (cudaStream_t)s;
     switch (d->dtype) {
-    case THB_F16: return dispatch_bn<0>(d->BN, tm, p, gx, gy, st);
-    case THB_BF16: return dispatch_bn<1>(d->BN, tm, p, gx, gy, st);
-    case THB_U8: return dispatch_bn<2>(d->BN, tm, p, gx, gy, st);
+    case THB_F16: return dispatch_bn<0>(d->BN, tm, p, st);
+    case THB_BF16: return dispatch_bn<1>(d->BN, tm, p, st);
+    case THB_U8: return dispatch_bn<2>(d->BN, tm, p, st);
     }
     return THB_ERR_UNSUPPORTED;
 }
