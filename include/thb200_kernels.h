@@ -105,6 +105,10 @@ int thb_gemv_fwd(int dtype, const void *x, int N, int K, int x_ld, const void *w
 /* NCHW fp32 -> normalised NHWC dtype; also writes the normalised fp32 values back over `x` when inplace != 0 */
 int thb_preprocess(const float *x_nchw, float *x_inplace, int N, int C, int H, int W, const float *mean3,
                    const float *std3, int dtype, void *y, int y_ld, float q_sub, float q_mult, thb_stream s);
+/* same normalisation, but space-to-depth: output is [N][H/2][W/2][4*C] with channel (ph*2 + pw)*C + c holding pixel
+ * (2h + ph, 2w + pw) of channel c -- the input layout of a stride-2 first convolution rewritten as stride 1 */
+int thb_preprocess_s2d(const float *x_nchw, float *x_inplace, int N, int C, int H, int W, const float *mean3,
+                       const float *std3, int dtype, void *y, int y_ld, thb_stream s);
 /* u8 HWC images (already on the device, row stride `stride`) -> normalised NHWC dtype (thapi.c:20-46) */
 int thb_preprocess_images(const unsigned char *img, int N, int H, int W, int stride, int cp, int bgr,
                           const float *mean3, const float *std3, int dtype, void *y, int y_ld, thb_stream s);

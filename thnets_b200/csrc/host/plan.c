@@ -128,6 +128,7 @@ struct thb_engine {
     /* shape the instances were planned for */
     int N, C, H, W, rank, cp;
     int built;
+    int input_s2d; /* the network input is staged space-to-depth for a stride-2 first convolution */
     instance inst[8];
     float *h_out;
     size_t h_out_bytes;
@@ -289,6 +290,11 @@ static int plan_gemm_group(planner *P, int i)
     const int dtype = E->dtype, al = align_of(dtype);
     shape is = in->s, os = is;
     int is_linear = n->op == OP_LINEAR, is_deconv = n->op == OP_DECONV;
+    /* stride-2 first convolution on a space-to-depth input (see instance_build): rewritten as a stride-1 convolution
+     * over 4*Cin channels.  Input row 2*oh - pad + r is block row oh + floor((r - pad)/2), phase (r - pad) mod 2. */
+    const int s2d = E->input_s2d && n->in[0] == 0 && n->op == OP_CONV;
+    const int s2d_padH = (n->padH + 1) / 2, s2d_padW = (n->padW + 1) / 2;
+    const int s2d_kH = (n->kH - 1 - n->padH) / 2 + s2d_padH + 1, s2d_kW = (n->kW - 1 - n->padW) / 2 + s2d_padW + 1;
 
     /* ---- geometry ---- */
     int kH = n->kH, kW = n->kW, Cin = n->Cin, H = is.H, W = is.W, in_ld = in->ld, permute_hw = 0;
@@ -312,6 +318,13 @@ static int plan_gemm_group(planner *P, int i)
         os.C = n->Cout;
         os.H = (is.H - 1) * n->dH - 2 * n->padH + n->kH + n->adjH;
         os.W = (is.W - 1) * n->dW - 2 * n->padW + n->kW + n->adjW;
+    } else if (s2d) {
+        /* the logical input is still [N, Cin, 2H', 2W']: output size from the original geometry */
+        os.C = n->Cout;
+        os.H = conv_out(E->H, n->kH, 2, n->padH);
+        os.W = conv_out(E->W, n->kW, 2, n->padW);
+        Cin = 4 * n->Cin;
+        kH = s2d_kH; kW = s2d_kW;
     } else {
         if (is.rank < 3) { thb_set_error("convolution needs a 3D or 4D input"); return -1; }
         if (is.C != n->Cin) { thb_set_error("nInputPlane %d does not match input planes %d", n->Cin, is.C); return -1; }
@@ -426,6 +439,21 @@ static int plan_gemm_group(planner *P, int i)
                 }
             w_oihw = w_tmp;
         }
+    } else if (s2d) {
+        d->Cout = n->Cout; d->oH = os.H; d->oW = os.W;
+        d->dH = d->dW = 1; d->padH = s2d_padH; d->padW = s2d_padW;
+        /* W'[co][(ph*2 + pw)*Cin + c][dh][dw] = W[co][c][2*(dh - pad') + ph + pad][...] where that row exists */
+        w_tmp = calloc((size_t)n->Cout * Cin * kH * kW, sizeof(float));
+        for (int co = 0; co < n->Cout; co++)
+            for (int c = 0; c < n->Cin; c++)
+                for (int r = 0; r < n->kH; r++)
+                    for (int q = 0; q < n->kW; q++) {
+                        int tr = r - n->padH + 2 * s2d_padH, tq = q - n->padW + 2 * s2d_padW; /* >= 0 */
+                        int dh = tr / 2, ph = tr % 2, dw = tq / 2, pw = tq % 2;
+                        w_tmp[(((size_t)co * Cin + (ph * 2 + pw) * n->Cin + c) * kH + dh) * kW + dw] =
+                            n->weight[(((size_t)co * n->Cin + c) * n->kH + r) * n->kW + q];
+                    }
+        w_oihw = w_tmp;
     } else {
         d->Cout = n->Cout; d->oH = os.H; d->oW = os.W;
     }
@@ -792,6 +820,17 @@ static int instance_build(thb_engine *E, instance *I, int device, int slice_off,
     P.uses[M->output]++;
 
     shape in = {slice_n, E->C, E->H, E->W, E->rank, 0, 0, 0, 0};
+    {
+        /* a stride-2 convolution on very few channels as the only consumer of the float input: stage the input
+         * space-to-depth so that the gathered 16-byte chunks carry four times as many useful channels */
+        thb_node *c1 = M->nnodes > 1 ? &M->nodes[1] : 0;
+        const char *off = getenv("THB200_NO_S2D");
+        E->input_s2d = c1 && c1->op == OP_CONV && c1->in[0] == 0 && P.uses[0] == 1 && c1->dH == 2 && c1->dW == 2 &&
+                       4 * E->C <= 16 && c1->Cin == E->C && E->H % 2 == 0 && E->W % 2 == 0 && E->rank == 4 && E->cp == 0 &&
+                       (E->dtype == THB_F16 || E->dtype == THB_BF16) && c1->padH <= c1->kH - 1 && c1->padW <= c1->kW - 1 &&
+                       !(off && atoi(off));
+        if (E->input_s2d) { in.C = 4 * E->C; in.H = E->H / 2; in.W = E->W / 2; }
+    }
     materialise(&P, &P.val[0], in);
     P.val[0].q_dyn = E->dtype == THB_U8;
     int rc = 0;
@@ -1033,7 +1072,7 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
                        int W, int rank, const float *mean, const float *std, int inplace, thb_result *res)
 {
     if (N < 1 || C < 1 || H < 1 || W < 1) { thb_set_error("empty input"); return -1; }
-    if (!E->built || E->N != N || E->C != C || E->H != H || E->W != W || E->rank != rank) {
+    if (!E->built || E->N != N || E->C != C || E->H != H || E->W != W || E->rank != rank || E->cp != cp) {
         if (engine_build(E, N, C, H, W, rank, cp)) return -1;
     }
     const int G = E->built;
@@ -1086,7 +1125,10 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
         CU(cudaSetDevice(I->device));
         int rc;
         void *in_ptr = bufptr(I, I->in_val.buf, 0, E->dtype);
-        if (x)
+        if (x && E->input_s2d)
+            rc = thb_preprocess_s2d(I->d_in, inplace ? I->d_in : 0, I->slice_n, C, H, W, mean, std, E->dtype, in_ptr,
+                                    I->in_val.ld, I->stream);
+        else if (x)
             rc = thb_preprocess(I->d_in, inplace ? I->d_in : 0, I->slice_n, C, H, W, mean, std, E->dtype, in_ptr, I->in_val.ld,
                                 q_sub, q_mult, I->stream);
         else
