@@ -42,6 +42,7 @@ struct ConvTcParams {
     int a_off, b_off, c_off, c_mult, c_shift;
     const int *wsat, *bias_add, *csum;
     int tail_start, relu_thr, relu_val;
+    int a_tma;   // 1x1 stride-1 convolution: the activation operand is a plain [pixels][Cin] matrix, loaded by TMA
     int use_l1;  // gather through L1: neighbouring taps of one tile re-read the same input pixels
     int *acc_out;
     int *status;
@@ -114,12 +115,13 @@ template <int KIND, int BN, int STAGES> struct Smem {
     static constexpr size_t PIPE = (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
     static constexpr size_t STAGING = KIND == 2 ? (size_t)BM * (SUBN + 16) : (size_t)BM * (SUBN + 4) * 4;
     static constexpr size_t STAGING_PAD = (STAGING + 127) / 128 * 128;  // one staging tile per epilogue group
-    static constexpr size_t BARS = (2 * STAGES + 8) * 8 + 16;
+    static constexpr size_t BARS = (2 * STAGES + 12) * 8 + 16;
     static constexpr size_t TOTAL = 1024 + PIPE + 2 * STAGING_PAD + BARS + 64;
 };
 
 template <int KIND, int BN, int STAGES>
-__global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const ConvTcParams p)
+__global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_constant__ CUtensorMap tmapA,
+                                                               const ConvTcParams p)
 {
     using L = Smem<KIND, BN, STAGES>;
     constexpr int ES = kind_traits<KIND>::esize;
@@ -128,7 +130,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
     constexpr int SUBN = L::SUBN;
     constexpr int LAG = STAGES >= 4 ? STAGES - 2 : STAGES - 1;  // cp.async groups a producer thread keeps in flight
     constexpr uint32_t IDESC = make_idesc(KIND == 2 ? 2u : 1u, KIND == 1 ? 1u : 0u, BN);
-    constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators
+    constexpr int NACC = BN >= 256 ? 2 : 4;  // TMEM accumulators: the MMA warp runs this many tiles ahead of the epilogue
+    constexpr uint32_t TMEM_COLS = NACC * BN < 32 ? 32 : NACC * BN;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -137,8 +140,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
     uint8_t *stage_buf = smem + L::PIPE;
     uint64_t *bars = reinterpret_cast<uint64_t *>(stage_buf + 2 * L::STAGING_PAD);
     uint64_t *full = bars, *empty = bars + STAGES;
-    uint64_t *acc_full = bars + 2 * STAGES, *acc_empty = acc_full + 2;
-    uint64_t *stg_ready = acc_empty + 2, *stg_free = stg_ready + 2;  // one pair per epilogue group
+    uint64_t *acc_full = bars + 2 * STAGES, *acc_empty = acc_full + 4;
+    uint64_t *stg_ready = acc_empty + 4, *stg_free = stg_ready + 2;  // one pair per epilogue group
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(stg_free + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
@@ -147,10 +150,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(smem_u32(&full[s]), 128 + 1);
+            mbar_init(smem_u32(&full[s]), p.a_tma ? 1 : 128 + 1);
             mbar_init(smem_u32(&empty[s]), 1);
         }
-        for (int b = 0; b < 2; b++) {
+        for (int b = 0; b < NACC; b++) {
             mbar_init(smem_u32(&acc_full[b]), 1);
             mbar_init(smem_u32(&acc_empty[b]), 128);
         }
@@ -162,7 +165,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
         fence_barrier_init();
         fence_proxy_async_smem();
     }
-    if (warp == 4 && lane == 0) tma_prefetch_desc(&tmapW);
+    if (warp == 4 && lane == 0) {
+        tma_prefetch_desc(&tmapW);
+        if (p.a_tma) tma_prefetch_desc(&tmapA);
+    }
     if (warp == 5) {
         tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
         tmem_relinquish();
@@ -173,7 +179,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp < 4) {
-        // ================================================================== A producer
+        // ================================================================== A producer (gather mode)
+        if (p.a_tma) goto done;
         const int chunk = lane & 7;
         bool alive = true;
         int it = 0;  // K blocks issued so far by this CTA, over all its tiles
@@ -259,7 +266,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                         alive = false;
                         break;
                     }
-                    mbar_arrive_expect_tx(smem_u32(&full[s]), B_STAGE_BYTES);
+                    if (p.a_tma) {
+                        mbar_arrive_expect_tx(smem_u32(&full[s]), B_STAGE_BYTES + A_STAGE_BYTES);
+                        tma_load_2d(smem_u32(sA + s * A_STAGE_BYTES), &tmapA, smem_u32(&full[s]), kb * BKE, (tile / p.n_tiles) * BM);
+                    } else
+                        mbar_arrive_expect_tx(smem_u32(&full[s]), B_STAGE_BYTES);
                     tma_load_2d(smem_u32(sB + s * B_STAGE_BYTES), &tmapW, smem_u32(&full[s]), kb * BKE, n0);
                 }
             }
@@ -271,8 +282,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
             int it = 0, lt = 0;
             bool alive = true;
             for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, lt++) {
-                const int b = lt & 1;
-                const uint32_t acc_ph = (lt >> 1) & 1;
+                const int b = lt % NACC;
+                const uint32_t acc_ph = (lt / NACC) & 1;
                 if (!mbar_wait_bounded(smem_u32(&acc_empty[b]), acc_ph ^ 1)) {
                     atomicExch(p.status, 6);
                     *abort_flag = 1;
@@ -313,7 +324,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
         const int et = tid - 192 - grp * 128;  // 0..127 within the group
         const int quad = warp & 3;             // TMEM lane quadrant this warp may read
         const int row = quad * 32 + lane;      // tile row (= pixel) owned in phase 1
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + grp * BN;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
         uint8_t *stg = stage_buf + grp * L::STAGING_PAD;
         const uint32_t bar_ready = smem_u32(&stg_ready[grp]), bar_free = smem_u32(&stg_free[grp]);
         const bool has_res = KIND != 2 && p.res != nullptr;
@@ -326,6 +337,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
             const int tile = blockIdx.x + lt * gridDim.x;
             if (tile >= total_tiles) break;
             const int m0 = (tile / p.n_tiles) * BM, n0 = (tile % p.n_tiles) * BN;
+            const int ab = lt % NACC;  // accumulator holding this tile
+            const uint32_t lane_addr = lane_base + ab * BN;
             const int pm = m0 + row;
             const bool valid = pm < p.P;
             const bool check = n0 + BN > p.Cout;  // the tile reaches beyond the last real channel
@@ -366,7 +379,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     }
                 }
                 if (!have_acc) {
-                    if (!mbar_wait_bounded(smem_u32(&acc_full[grp]), (lt >> 1) & 1)) {
+                    if (!mbar_wait_bounded(smem_u32(&acc_full[ab]), (lt / NACC) & 1)) {
                         if (lane == 0) atomicExch(p.status, 2);
                         *abort_flag = 1;
                         alive = false;
@@ -431,7 +444,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                 if (sb == BN / SUBN - 1) {
                     // every column of this accumulator has been read: hand it back to the MMA warp
                     tc_fence_before();
-                    mbar_arrive(smem_u32(&acc_empty[grp]));
+                    mbar_arrive(smem_u32(&acc_empty[ab]));
                 }
                 mbar_arrive(bar_ready);
                 if (!mbar_wait_bounded(bar_ready, sub_it & 1)) {
@@ -493,6 +506,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
         }
     }
 
+done:
     tc_fence_before();
     __syncthreads();
     if (warp == 5) {
@@ -512,7 +526,7 @@ int num_sms()
 }
 
 template <int KIND, int BN, int STAGES>
-int launch_tc(const CUtensorMap &tm, const ConvTcParams &p, cudaStream_t st)
+int launch_tc(const CUtensorMap &tm, const CUtensorMap &ta, const ConvTcParams &p, cudaStream_t st)
 {
     static bool configured[16] = {false};
     auto kern = conv_tc_kernel<KIND, BN, STAGES>;
@@ -528,18 +542,18 @@ int launch_tc(const CUtensorMap &tm, const ConvTcParams &p, cudaStream_t st)
     }
     const int tiles = p.m_tiles * p.n_tiles;
     const int grid = tiles < num_sms() ? tiles : num_sms();
-    kern<<<grid, NTHREADS, smem, st>>>(tm, p);
+    kern<<<grid, NTHREADS, smem, st>>>(tm, ta, p);
     return THB_LAUNCH_CHECK("conv_tc_kernel");
 }
 
 template <int KIND>
-int dispatch_bn(int BN, const CUtensorMap &tm, const ConvTcParams &p, cudaStream_t st)
+int dispatch_bn(int BN, const CUtensorMap &tm, const CUtensorMap &ta, const ConvTcParams &p, cudaStream_t st)
 {
     switch (BN) {
-    case 32: return launch_tc<KIND, 32, 6>(tm, p, st);
-    case 64: return launch_tc<KIND, 64, 5>(tm, p, st);
-    case 128: return launch_tc<KIND, 128, 4>(tm, p, st);
-    case 256: return launch_tc<KIND, 256, 3>(tm, p, st);
+    case 32: return launch_tc<KIND, 32, 6>(tm, ta, p, st);
+    case 64: return launch_tc<KIND, 64, 5>(tm, ta, p, st);
+    case 128: return launch_tc<KIND, 128, 4>(tm, ta, p, st);
+    case 256: return launch_tc<KIND, 256, 3>(tm, ta, p, st);
     }
     return THB_ERR_UNSUPPORTED;
 }
@@ -559,6 +573,39 @@ encode_tiled_fn get_encode_fn()
             fn = reinterpret_cast<encode_tiled_fn>(sym);
     }
     return fn;
+}
+
+// TMA descriptors of activation matrices, keyed by what they encode (built once per buffer and shape)
+struct ATmapEntry {
+    const void *x;
+    int P, cin_pad, in_ld, dtype;
+    alignas(64) CUtensorMap map;
+};
+const CUtensorMap *activation_tmap(const thb_conv_desc *d, const void *x, int P)
+{
+    static ATmapEntry cache[512];
+    static int used = 0, next = 0;
+    for (int i = 0; i < used; i++) {
+        ATmapEntry &e = cache[i];
+        if (e.x == x && e.P == P && e.cin_pad == d->Cin_pad && e.in_ld == d->in_ld && e.dtype == d->dtype) return &e.map;
+    }
+    encode_tiled_fn enc = get_encode_fn();
+    if (!enc) return nullptr;
+    ATmapEntry &e = cache[used < 512 ? used++ : (next++ % 512)];
+    const int es = d->dtype == THB_U8 ? 1 : 2;
+    CUtensorMapDataType t = d->dtype == THB_U8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                            : d->dtype == THB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    cuuint64_t dims[2] = {(cuuint64_t)d->Cin_pad, (cuuint64_t)P};
+    cuuint64_t strides[1] = {(cuuint64_t)d->in_ld * es};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / es), (cuuint32_t)BM};
+    cuuint32_t estr[2] = {1, 1};
+    if (enc(&e.map, t, 2, const_cast<void *>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+        e.x = nullptr;
+        return nullptr;
+    }
+    e.x = x; e.P = P; e.cin_pad = d->Cin_pad; e.in_ld = d->in_ld; e.dtype = d->dtype;
+    return &e.map;
 }
 
 }  // namespace
@@ -619,11 +666,20 @@ extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, t
     p.m_tiles = (p.P + BM - 1) / BM;
     p.n_tiles = d->Cout_pad / d->BN;
     const CUtensorMap &tm = *reinterpret_cast<const CUtensorMap *>(d->tmap);
+    const CUtensorMap *ta = &tm;
+    // a 1x1 stride-1 unpadded convolution (and every Linear) reads a plain [pixels][Cin] matrix: TMA loads it
+    p.a_tma = d->kH == 1 && d->kW == 1 && d->dH == 1 && d->dW == 1 && d->padH == 0 && d->padW == 0 &&
+              d->oH == d->H && d->oW == d->W;
+    if (const char *e = getenv("THB200_A_TMA")) p.a_tma = p.a_tma && atoi(e);
+    if (p.a_tma) {
+        ta = activation_tmap(d, x, p.P);
+        if (!ta) p.a_tma = 0, ta = &tm;
+    }
     cudaStream_t st = (cudaStream_t)s;
     switch (d->dtype) {
-    case THB_F16: return dispatch_bn<0>(d->BN, tm, p, st);
-    case THB_BF16: return dispatch_bn<1>(d->BN, tm, p, st);
-    case THB_U8: return dispatch_bn<2>(d->BN, tm, p, st);
+    case THB_F16: return dispatch_bn<0>(d->BN, tm, *ta, p, st);
+    case THB_BF16: return dispatch_bn<1>(d->BN, tm, *ta, p, st);
+    case THB_U8: return dispatch_bn<2>(d->BN, tm, *ta, p, st);
     }
     return THB_ERR_UNSUPPORTED;
 }
