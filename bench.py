@@ -175,6 +175,9 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl != "reference" and world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("--gpus N > 1 must be launched with one process per GPU: python -m torch.distributed.run "
+                         "--nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 bench.py --gpus N ...")
     _, dbatch, ddtype, _ = WORKLOADS[args.workload]
     batch = args.batch or dbatch
     dtype = args.dtype or ddtype
@@ -200,12 +203,8 @@ def main():
 
     # ---------------------------------------------------------------- B200 arm
     os.environ["THB200_DEVICE"] = str(local_rank)
-    dist = None
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    from thnets_b200.distributed import Ranks
+    ranks = Ranks("nccl" if world > 1 else None)
     from thnets_b200.capi import THNets
     th = THNets()
     lib = th.lib
@@ -242,17 +241,7 @@ def main():
             raise SystemExit("THProcessFloat failed: %s" % lib.THB200_LastErrorString())
         return n
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-
-    def max_over_ranks(v):
-        if dist is None:
-            return v
-        import torch
-        t = torch.tensor([v], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    barrier, max_over_ranks = ranks.barrier, ranks.max
 
     out_count = forward_e2e()          # plans the network, uploads the weights, stages the batch
     for _ in range(warmup):
@@ -317,8 +306,7 @@ def main():
         print(json.dumps(out))
     lib.THB200_HostFree(hptr)
     th.free_network(net)
-    if dist is not None:
-        dist.destroy_process_group()
+    ranks.close()
 
 
 if __name__ == "__main__":

@@ -89,8 +89,7 @@ int thb_channel_align(int dtype);               /* 4 (F32), 8 (F16/BF16), 16 (U8
 int thb_conv_geometry(thb_conv_desc *d);        /* fills Cin_pad, Ktot_pad, Cout_pad, BN from the shape */
 size_t thb_conv_weight_bytes(const thb_conv_desc *d);
 size_t thb_conv_kinfo_words(const thb_conv_desc *d);
-/* host-side packing of OIHW fp32 weights (or pre-quantised u8 weights) into the kernel layout;
- * chan_perm_hw > 0 reorders Cin from an NCHW flatten of [Cin/hw, hw] to channels-innermost (View -> Linear) */
+/* host-side packing of OIHW fp32 weights (or pre-quantised u8 weights) into the kernel layout */
 int thb_conv_pack_weights_host(const thb_conv_desc *d, const float *w_oihw, const unsigned char *wq_oihw,
                                void *packed_host, int *kinfo_host, int *wsat_host);
 int thb_conv_make_tmap(const thb_conv_desc *d, thb_tmap *out);

@@ -1,0 +1,221 @@
+"""Host-side logic that needs no GPU: loaders, graph lowering, THMakeSpatial, error conventions,
+struct ABI, and that the shared library exports every symbol its headers declare.
+No compute entry point is called here."""
+import ctypes as C
+import os
+import re
+import shutil
+import subprocess
+
+import numpy as np
+import pytest
+
+from thnets_b200 import fixtures as fx
+from thnets_b200.capi import DEFAULT_LIB, THNets, THNetworkStruct
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+os.environ.setdefault("THB200_NO_EXIT", "1")
+
+pytestmark = pytest.mark.skipif(not os.path.exists(DEFAULT_LIB), reason="libthnets.so not built")
+
+
+@pytest.fixture(scope="module")
+def th():
+    return THNets()
+
+
+def describe(th, h):
+    buf = C.create_string_buffer(1 << 18)
+    n = th.lib.THB200_DescribeNetwork(h, buf, len(buf))
+    assert n > 0, buf.value
+    return [line for line in buf.value.decode().split("\n") if line]
+
+
+def test_every_declared_symbol_is_exported():
+    lib = C.CDLL(DEFAULT_LIB)
+    names = set()
+    for hdr in ("thnets.h", "thb200_kernels.h"):
+        text = open(os.path.join(ROOT, "include", hdr)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names |= set(re.findall(r"\b((?:TH|thb_|THB200_)\w+|loadtorch|freeobject|freenetwork|Module2Network|loadpytorch|"
+                                r"freepynet|th_seconds)\s*\(", text))
+    names -= {"THB_"}
+    assert len(names) > 60
+    missing = [n for n in sorted(names) if not hasattr(lib, n)]
+    assert not missing, missing
+    for var in ("th_debug", "th_profile", "th_minmax", "th_convtot", "th_convflops"):
+        C.c_int.in_dll(lib, var)
+
+
+EXPECTED_ABI = {
+    "sizeof(THFloatTensor)": 88, "sizeof(THFloatStorage)": 16, "sizeof(struct module)": 208, "sizeof(struct network)": 16,
+    "sizeof(THNETWORK)": 72, "sizeof(struct thobject)": 24, "sizeof(struct pyelement)": 248,
+    "offsetof(struct module, updateOutput)": 8, "offsetof(struct module, output)": 24,
+    "offsetof(struct module, SpatialConvolution)": 128, "offsetof(struct module, SpatialConvolution.nOutputPlane)": 180,
+    "offsetof(struct module, SpatialBatchNormalization.eps)": 160, "offsetof(THNETWORK, net)": 16,
+    "offsetof(THNETWORK, mean)": 48, "offsetof(THNETWORK, std)": 60, "offsetof(struct network, modules)": 8,
+    "offsetof(THFloatTensor, storage)": 72, "MT_CSubTable": 22, "MT_Transpose": 36, "ENGINE_LOWP": 4,
+}
+
+
+@pytest.mark.skipif(shutil.which("gcc") is None, reason="needs gcc")
+def test_struct_layout_matches_the_reference_header(tmp_path):
+    """sizes / offsets measured on the reference's own thnets.h (CPU build, x86-64) are pinned above; when the
+    reference tree is present the two headers are also compared directly."""
+    def probe(include):
+        exe = str(tmp_path / ("abi_" + str(abs(hash(include)))))
+        subprocess.check_call(["gcc", "-I", include, "-o", exe, os.path.join(ROOT, "tests", "abi_probe.c")])
+        out = subprocess.check_output([exe], text=True)
+        return dict((k, int(v)) for k, v in (line.rsplit("=", 1) for line in out.split("\n") if line))
+    mine = probe(os.path.join(ROOT, "include"))
+    for k, v in EXPECTED_ABI.items():
+        assert mine[k] == v, (k, mine[k], v)
+    if os.path.exists("/root/reference/thnets.h"):
+        assert probe("/root/reference") == mine
+
+
+def test_torch7_loader_and_lowering(th, tmp_path):
+    g = fx.alexnet_owt(width=0.25, size=224, classes=50, fc=128)
+    d = str(tmp_path / "alex")
+    fx.write_torch7(g, d)
+    h = th.load_network(d)
+    s = THNetworkStruct.from_address(h)
+    assert s.net and not s.pynet
+    assert np.allclose(list(s.mean), 0.45) and np.allclose(list(s.std), 0.225)   # stat.t7
+    lines = describe(th, h)
+    ops = [line.split()[1] for line in lines]
+    assert ops == ["input", "conv", "act", "maxpool", "conv", "act", "maxpool", "conv", "act", "conv", "act", "conv", "act",
+                   "maxpool", "view", "linear", "act", "linear", "act", "linear", "softmax"]
+    assert "3->16 k11x11 s4,4 p2,2 bias=1" in lines[1]
+    assert lines[-1].endswith("<- output")
+    th.free_network(h)
+
+
+def test_torch7_containers_and_caddtable_signs(th, tmp_path):
+    """nn.Sequential { conv, ConcatTable { Sequential{conv,bn}, Identity }, CAddTable, ReLU, Concat{conv|conv}, JoinTable-free }"""
+    rng = np.random.default_rng(0)
+    conv = lambda ci, co, k, p: ("nn.SpatialConvolutionMM", dict(  # noqa: E731
+        padW=p, padH=p, dW=1, dH=1, kW=k, kH=k, nInputPlane=ci, nOutputPlane=co,
+        weight=rng.standard_normal((co, ci * k * k)).astype(np.float32), bias=rng.standard_normal(co).astype(np.float32)))
+    bn = ("nn.SpatialBatchNormalization", dict(running_mean=np.zeros(8, np.float32), running_var=np.ones(8, np.float32),
+                                               weight=np.ones(8, np.float32), bias=np.zeros(8, np.float32), eps=1e-5))
+    spec = ("nn.Sequential", [
+        conv(3, 8, 3, 1),
+        ("nn.ConcatTable", [("nn.Sequential", [conv(8, 8, 3, 1), bn]), ("nn.Identity", {})]),
+        ("nn.CAddTable", {}),
+        ("nn.ReLU", dict(threshold=0.0, val=0.0, inplace=False)),
+        ("nn.Concat", [conv(8, 8, 1, 0), conv(8, 16, 1, 0)], dict(dimension=2)),
+    ])
+    d = str(tmp_path / "branchy")
+    fx.write_torch7(spec, d)
+    h = th.load_network(d)
+    lines = describe(th, h)
+    ops = [line.split()[1] for line in lines]
+    assert ops == ["input", "conv", "conv", "bn", "alias", "combine", "act", "conv", "conv", "concat"]
+    comb = lines[5]
+    assert "in=3,4" in comb and "+1 -1" in comb       # two-input CAddTable: first minus second
+    assert "dim=1" in lines[9]
+    th.free_network(h)
+
+
+def test_pytorch_dump_loader_shares_referenced_nodes(th, tmp_path):
+    g = fx.resnet18(width=0.25, size=64, classes=10)
+    p = str(tmp_path / "r18.net")
+    fx.write_pymodel(g, p)
+    h = th.load_network(p)
+    s = THNetworkStruct.from_address(h)
+    assert s.pynet and not s.net                        # as in the reference, no struct network on this route
+    lines = describe(th, h)
+    combines = [line for line in lines if " combine " in line]
+    assert len(combines) == 8 and all("+1 -1" in c for c in combines)
+    # the shortcut of the first block is the max-pool output, consumed twice (second time by reference)
+    assert "in=9,4" in combines[0]
+    assert sum(" conv " in line for line in lines) == 20
+    th.free_network(h)
+    # a directory holding pymodel.net loads the same way
+    d = tmp_path / "dir"
+    d.mkdir()
+    shutil.copy(p, d / "pymodel.net")
+    h = th.load_network(str(d))
+    assert len(describe(th, h)) == len(lines)
+    th.free_network(h)
+
+
+def test_make_spatial_rewrites_the_classifier(th, tmp_path):
+    g = fx.vgg16(width=0.125, size=32, classes=10, fc=64)
+    d = str(tmp_path / "vgg")
+    fx.write_torch7(g, d)
+    h = th.load_network(d)
+    before = describe(th, h)
+    assert any(" view " in x for x in before) and sum(" linear " in x for x in before) == 3
+    th.make_spatial(h, 32)
+    after = describe(th, h)
+    assert not any(" view " in x or " linear " in x for x in after)
+    convs = [x for x in after if " conv " in x]
+    assert len(convs) == 16
+    assert "64->64 k1x1" in convs[-3] and "64->64 k1x1" in convs[-2] and "64->10 k1x1" in convs[-1]   # 32/2^5 = 1
+    th.free_network(h)
+    # a 64x64 classifier: the first Linear becomes a 2x2 convolution
+    g = fx.vgg16(width=0.125, size=64, classes=10, fc=64)
+    d = str(tmp_path / "vgg64")
+    fx.write_torch7(g, d)
+    h = th.load_network(d)
+    th.make_spatial(h, 64)
+    assert "k2x2" in [x for x in describe(th, h) if " conv " in x][-3]
+    th.free_network(h)
+
+
+def test_error_conventions(th, tmp_path):
+    lib = th.lib
+    assert not lib.THLoadNetwork(str(tmp_path / "missing").encode())
+    assert lib.THLastError() == -1                       # ERR_OPENFILE
+    d = tmp_path / "corrupt"
+    d.mkdir()
+    (d / "model.net").write_bytes(b"\x09\x00\x00\x00garbage")
+    assert not lib.THLoadNetwork(str(d).encode())
+    assert lib.THLastError() == -4                       # ERR_CORRUPTED
+    (d / "model.net").write_bytes(b"\x01\x00\x00\x00" + b"\x00" * 8)   # a bare number, not a module
+    assert not lib.THLoadNetwork(str(d).encode())
+    assert lib.THLastError() == -5                       # ERR_WRONGOBJECT
+    (d / "model.net").write_bytes(b"\x04\x00")
+    assert not lib.THLoadNetwork(str(d).encode())
+    assert lib.THLastError() == -2                       # ERR_READFILE
+    assert lib.THOpenCLHalfFloat(1) == -3 and not lib.THCreateOpenCLNetwork(None)
+    assert lib.THCudaHalfFloat(1) == 0 and lib.THCudaHalfFloat(0) == 0
+
+
+def test_unsupported_module_is_reported(th, tmp_path):
+    spec = ("nn.Sequential", [("nn.SpatialConvolutionMM", dict(
+        padW=0, padH=0, dW=1, dH=1, kW=1, kH=1, nInputPlane=3, nOutputPlane=4,
+        weight=np.zeros((4, 3), np.float32), bias=np.zeros(4, np.float32))), ("nn.LogSoftMax", {})])
+    d = str(tmp_path / "ls")
+    fx.write_torch7(spec, d)
+    # unknown module types are fatal in the reference's loader (thload.c:777-778): run in a child process
+    code = ("import os, sys; sys.path.insert(0, %r); from thnets_b200.capi import THNets; THNets().lib.THLoadNetwork(%r)"
+            % (ROOT, d.encode()))
+    r = subprocess.run([os.sys.executable, "-c", code], capture_output=True, text=True)
+    assert r.returncode != 0 and "Unknown module type nn.LogSoftMax" in r.stderr
+
+
+def test_batch_slicing(th):
+    off, cnt = C.c_int(), C.c_int()
+    for n in (1, 7, 256, 250):
+        for g in (1, 2, 4, 8):
+            covered = []
+            for r in range(g):
+                th.lib.THB200_SliceBatch(n, g, r, C.byref(off), C.byref(cnt))
+                covered += list(range(off.value, off.value + cnt.value))
+                assert cnt.value in (n // g, n // g + 1)
+            assert covered == list(range(n))
+
+
+def test_fixture_writers_round_trip_through_the_reference_formats(tmp_path):
+    """the .t7 writer emits objects with strictly increasing indices and float tensors with 1-based offsets"""
+    g = fx.vgg16(width=0.125, size=32, classes=10, fc=64)
+    d = str(tmp_path / "vgg")
+    fx.write_torch7(g, d)
+    raw = open(os.path.join(d, "model.net"), "rb").read()
+    assert raw[:4] == (4).to_bytes(4, "little") and b"nn.Sequential" in raw[:64] and b"torch.FloatStorage" in raw
+    p = str(tmp_path / "m.net")
+    fx.write_pymodel(g, p)
+    assert open(p, "rb").read(24) == b"PyTorch Graph Dump 1.00\0"
