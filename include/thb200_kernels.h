@@ -146,6 +146,16 @@ int thb_u8_channel_sum(const void *x, long pixels, int C, int x_ld, int *csum, t
 /* channels-innermost -> plain NCHW flatten order of the same dtype (View feeding anything but a Linear) */
 int thb_to_nchw(int dtype, const void *x, int N, int H, int W, int C, int x_ld, void *y, thb_stream s);
 
+/* ---- no counterpart in the reference ----
+ * thb_conv_fwd for THB_U8 that allocates nothing and needs no caller-provided d->csum: the per-pixel channel sums
+ * go into a fixed array of THB_STATIC_CSUM_MAX_PIXELS int32 that is part of the library's device image
+ * (d->csum is ignored).  N*H*W input pixels beyond that limit are refused with THB_ERR_ARG and a message in
+ * thb_last_cuda_error().  The first call on each device looks the array's address up and caches it; make that call
+ * before starting a stream capture.  All calls on a device share the array: nothing in it needs to start at zero
+ * (each call rewrites the entries it reads, in stream order), but calls that may execute concurrently race on it. */
+#define THB_STATIC_CSUM_MAX_PIXELS 1048576
+int thb_conv_u8_fwd_static(const thb_conv_desc *d, const void *x, void *y, thb_stream s);
+
 const char *thb_last_cuda_error(void);
 int thb_kernel_launch_count(void); /* launches issued through this ABI since load (bench bookkeeping) */
 
