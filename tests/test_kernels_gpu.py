@@ -38,6 +38,12 @@ CONV_CASES = [
     (2, 40, 7, 7, 136, 5, 1, 2),
     (5, 128, 7, 7, 72, 3, 1, 1),
     (1, 8, 30, 30, 300, 1, 2, 0),
+    # whole 128-byte channel slabs per tap: the activation operand comes in by im2col-mode TMA
+    (3, 64, 19, 23, 40, 3, 2, 1),
+    (2, 128, 14, 14, 64, 1, 2, 0),
+    (2, 64, 30, 17, 96, 5, 1, 2),
+    (1, 192, 13, 13, 48, 3, 1, 0),
+    (2, 256, 9, 11, 32, 2, 2, 0),
 ]
 
 

@@ -117,6 +117,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, uint
         "l"(tmap), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
 }
+// 4-D im2col TMA load over a channels-innermost activation tensor {C, W, H, N} (no multicast): starting at the
+// input position (w, h, n) of the tile's first output pixel for filter tap (0, 0), the copy engine walks the
+// descriptor's pixels-per-column output pixels in W, H, N order with the descriptor's traversal strides, adds the
+// tap offset (off_w, off_h) to each and fetches its channels-per-pixel channels from c on; positions outside the
+// image read as zeros.  The result is one 128-byte-swizzled row per output pixel.
+__device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const void *tmap, uint32_t bar, int c, int w, int h, int n,
+                                                   uint16_t off_w, uint16_t off_h)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], "
+        "{%7, %8};" ::"r"(dst),
+        "l"(tmap), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h)
+        : "memory");
+}
 
 // ---- tcgen05 / tensor memory ----
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols)

@@ -42,7 +42,9 @@ struct ConvTcParams {
     int a_off, b_off, c_off, c_mult, c_shift;
     const int *wsat, *bias_add, *csum;
     int tail_start, relu_thr, relu_val;
-    int a_tma;   // 1x1 stride-1 convolution: the activation operand is a plain [pixels][Cin] matrix, loaded by TMA
+    int a_tma;   // 1: 1x1 stride-1 convolution, the activation operand is a plain [pixels][Cin] matrix loaded by 2-D TMA;
+                 // 2: whole 128-byte channel slabs per tap, loaded by im2col-mode TMA (any kernel size, stride, padding)
+    int slabs;   // a_tma == 2: 128-byte channel slabs per tap (K block kb = tap * slabs + slab)
     int use_l1;  // gather through L1: neighbouring taps of one tile re-read the same input pixels
     int *acc_out;
     int *status;
@@ -257,6 +259,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
             bool alive = true;
             for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
                 const int n0 = (tile % p.n_tiles) * BN;
+                const int m0 = (tile / p.n_tiles) * BM;
+                // im2col mode: input position of the tile's first output pixel for tap (0, 0)
+                int iw = 0, ih = 0, in = 0, tap_w = 0, tap_h = 0, slab = 0;
+                if (p.a_tma == 2) {
+                    in = m0 / p.oHW;
+                    const int rem = m0 - in * p.oHW;
+                    const int oh = rem / p.oW;
+                    ih = oh * p.dH - p.padH;
+                    iw = (rem - oh * p.oW) * p.dW - p.padW;
+                }
                 for (int kb = 0; kb < p.nkb; kb++, it++) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
@@ -266,9 +278,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                         alive = false;
                         break;
                     }
-                    if (p.a_tma) {
+                    if (p.a_tma == 1) {
                         mbar_arrive_expect_tx(smem_u32(&full[s]), B_STAGE_BYTES + A_STAGE_BYTES);
-                        tma_load_2d(smem_u32(sA + s * A_STAGE_BYTES), &tmapA, smem_u32(&full[s]), kb * BKE, (tile / p.n_tiles) * BM);
+                        tma_load_2d(smem_u32(sA + s * A_STAGE_BYTES), &tmapA, smem_u32(&full[s]), kb * BKE, m0);
+                    } else if (p.a_tma == 2) {
+                        mbar_arrive_expect_tx(smem_u32(&full[s]), B_STAGE_BYTES + A_STAGE_BYTES);
+                        tma_load_im2col_4d(smem_u32(sA + s * A_STAGE_BYTES), &tmapA, smem_u32(&full[s]), slab * BKE, iw, ih, in,
+                                           (uint16_t)tap_w, (uint16_t)tap_h);
+                        if (++slab == p.slabs) {
+                            slab = 0;
+                            if (++tap_w == p.kW) { tap_w = 0; tap_h++; }
+                        }
                     } else
                         mbar_arrive_expect_tx(smem_u32(&full[s]), B_STAGE_BYTES);
                     tma_load_2d(smem_u32(sB + s * B_STAGE_BYTES), &tmapW, smem_u32(&full[s]), kb * BKE, n0);
@@ -575,36 +595,80 @@ encode_tiled_fn get_encode_fn()
     return fn;
 }
 
-// TMA descriptors of activation matrices, keyed by what they encode (built once per buffer and shape)
+typedef CUresult (*encode_im2col_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                     const cuuint64_t *, const int *, const int *, cuuint32_t, cuuint32_t, const cuuint32_t *,
+                                     CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+encode_im2col_fn get_encode_im2col_fn()
+{
+    static encode_im2col_fn fn = nullptr;
+    if (!fn) {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<encode_im2col_fn>(sym);
+    }
+    return fn;
+}
+
+// TMA descriptors of activation operands, keyed by what they encode (built once per buffer and shape).
+// mode 1: the plain [pixels][Cin] matrix of a 1x1 stride-1 convolution; mode 2: im2col over {C, W, H, N}.
 struct ATmapEntry {
     const void *x;
-    int P, cin_pad, in_ld, dtype;
+    int mode, N, H, W, cin_pad, in_ld, dtype, geom[6];
     alignas(64) CUtensorMap map;
 };
-const CUtensorMap *activation_tmap(const thb_conv_desc *d, const void *x, int P)
+const CUtensorMap *activation_tmap(const thb_conv_desc *d, const void *x, int mode)
 {
     static ATmapEntry cache[512];
     static int used = 0, next = 0;
+    const int geom[6] = {d->kH, d->kW, d->dH, d->dW, d->padH, d->padW};
     for (int i = 0; i < used; i++) {
         ATmapEntry &e = cache[i];
-        if (e.x == x && e.P == P && e.cin_pad == d->Cin_pad && e.in_ld == d->in_ld && e.dtype == d->dtype) return &e.map;
+        if (e.x == x && e.mode == mode && e.N == d->N && e.H == d->H && e.W == d->W && e.cin_pad == d->Cin_pad &&
+            e.in_ld == d->in_ld && e.dtype == d->dtype && (mode == 1 || !memcmp(e.geom, geom, sizeof(geom))))
+            return &e.map;
     }
-    encode_tiled_fn enc = get_encode_fn();
-    if (!enc) return nullptr;
     ATmapEntry &e = cache[used < 512 ? used++ : (next++ % 512)];
+    e.x = nullptr;
     const int es = d->dtype == THB_U8 ? 1 : 2;
     CUtensorMapDataType t = d->dtype == THB_U8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                             : d->dtype == THB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-    cuuint64_t dims[2] = {(cuuint64_t)d->Cin_pad, (cuuint64_t)P};
-    cuuint64_t strides[1] = {(cuuint64_t)d->in_ld * es};
-    cuuint32_t box[2] = {(cuuint32_t)(128 / es), (cuuint32_t)BM};
-    cuuint32_t estr[2] = {1, 1};
-    if (enc(&e.map, t, 2, const_cast<void *>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
-        e.x = nullptr;
-        return nullptr;
+    if (mode == 1) {
+        encode_tiled_fn enc = get_encode_fn();
+        if (!enc) return nullptr;
+        cuuint64_t dims[2] = {(cuuint64_t)d->Cin_pad, (cuuint64_t)d->N * d->H * d->W};
+        cuuint64_t strides[1] = {(cuuint64_t)d->in_ld * es};
+        cuuint32_t box[2] = {(cuuint32_t)(128 / es), (cuuint32_t)BM};
+        cuuint32_t estr[2] = {1, 1};
+        if (enc(&e.map, t, 2, const_cast<void *>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return nullptr;
+    } else {
+        encode_im2col_fn enc = get_encode_im2col_fn();
+        if (!enc) return nullptr;
+        // The bounding box that base pixels (tap (0,0) positions) live in: from -pad to dim + pad - (k - 1), so that
+        // stepping by the convolution stride visits exactly oW x oH positions per image.
+        cuuint64_t dims[4] = {(cuuint64_t)d->Cin_pad, (cuuint64_t)d->W, (cuuint64_t)d->H, (cuuint64_t)d->N};
+        cuuint64_t strides[3] = {(cuuint64_t)d->in_ld * es, (cuuint64_t)d->W * d->in_ld * es,
+                                 (cuuint64_t)d->H * d->W * d->in_ld * es};
+        int lower[2] = {-d->padW, -d->padH};
+        int upper[2] = {d->padW - (d->kW - 1), d->padH - (d->kH - 1)};
+        cuuint32_t estr[4] = {1, (cuuint32_t)d->dW, (cuuint32_t)d->dH, 1};
+        if (enc(&e.map, t, 4, const_cast<void *>(x), dims, strides, lower, upper, (cuuint32_t)(128 / es), (cuuint32_t)BM, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return nullptr;
+        // Drivers up to CUDA 13.1 encode im2col descriptors of tensors smaller than 128 KiB with a flag (bit 21 of
+        // the second 64-bit word) that makes the load misbehave; CUTLASS clears it for those drivers, and so do we.
+        int drv = 0;
+        if (cudaDriverGetVersion(&drv) == cudaSuccess && drv <= 13010 &&
+            (size_t)d->N * d->H * d->W * d->in_ld * es < 131072)
+            reinterpret_cast<uint64_t *>(&e.map)[1] &= ~(1ull << 21);
     }
-    e.x = x; e.P = P; e.cin_pad = d->Cin_pad; e.in_ld = d->in_ld; e.dtype = d->dtype;
+    e.x = x; e.mode = mode; e.N = d->N; e.H = d->H; e.W = d->W; e.cin_pad = d->Cin_pad; e.in_ld = d->in_ld; e.dtype = d->dtype;
+    memcpy(e.geom, geom, sizeof(geom));
     return &e.map;
 }
 
@@ -670,9 +734,21 @@ extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, t
     // a 1x1 stride-1 unpadded convolution (and every Linear) reads a plain [pixels][Cin] matrix: TMA loads it
     p.a_tma = d->kH == 1 && d->kW == 1 && d->dH == 1 && d->dW == 1 && d->padH == 0 && d->padW == 0 &&
               d->oH == d->H && d->oW == d->W;
-    if (const char *e = getenv("THB200_A_TMA")) p.a_tma = p.a_tma && atoi(e);
+    // anything else whose taps are whole 128-byte channel slabs goes through im2col-mode TMA, within the limits of
+    // a rank-4 descriptor: box corners in [-128, 127], traversal strides up to 8, tap offsets below 256
+    const int bke = 128 / es;
+    if (!p.a_tma && d->Cin_pad % bke == 0 && d->Ktot_pad == d->kH * d->kW * d->Cin_pad && d->dH <= 8 && d->dW <= 8 &&
+        d->padH <= 127 && d->padW <= 127 && d->kH - 1 - d->padH <= 128 && d->kW - 1 - d->padW <= 128 && d->kH <= 256 &&
+        d->kW <= 256 && d->H + 2 * d->padH >= d->kH && d->W + 2 * d->padW >= d->kW &&
+        d->oH == (d->H + 2 * d->padH - d->kH) / d->dH + 1 && d->oW == (d->W + 2 * d->padW - d->kW) / d->dW + 1)
+        p.a_tma = 2;
+    p.slabs = d->Cin_pad / bke;
+    if (const char *e = getenv("THB200_A_TMA")) {
+        const int allow = atoi(e);  // 0: gather only, 1: plain-matrix TMA only, 2 (default): im2col too
+        if (p.a_tma > allow) p.a_tma = 0;
+    }
     if (p.a_tma) {
-        ta = activation_tmap(d, x, p.P);
+        ta = activation_tmap(d, x, p.a_tma);
         if (!ta) p.a_tma = 0, ta = &tm;
     }
     cudaStream_t st = (cudaStream_t)s;
