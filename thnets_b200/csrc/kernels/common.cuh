@@ -117,6 +117,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, uint
         "l"(tmap), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
 }
+// 2-D tiled TMA store of a shared-memory tile (rows and columns beyond the tensor's extent are clipped), as one
+// bulk async-group of the issuing thread.
+__device__ __forceinline__ void tma_store_2d(const void *tmap, uint32_t src, int c0, int c1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap), "r"(src), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// wait until at most N of this thread's most recent bulk groups still have to READ their shared-memory source
+template <int N> __device__ __forceinline__ void bulk_wait_group_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_group() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
+
 // 4-D im2col TMA load over a channels-innermost activation tensor {C, W, H, N} (no multicast): starting at the
 // input position (w, h, n) of the tile's first output pixel for filter tap (0, 0), the copy engine walks the
 // descriptor's pixels-per-column output pixels in W, H, N order with the descriptor's traversal strides, adds the
@@ -192,6 +204,18 @@ __device__ __forceinline__ uint64_t make_sw128_kmajor_desc(uint32_t smem_addr)
     d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset between 8-row groups, bits [32,46)
     d |= (uint64_t)1 << 46;                        // descriptor version for sm_100
     d |= (uint64_t)2 << 61;                        // layout type: SWIZZLE_128B
+    return d;
+}
+// The same for rows of 64 or 32 bytes stored with the swizzle of that width (a SWIZZLE_64B / SWIZZLE_32B TMA box):
+// 8-row groups 8 * row_bytes apart.
+__device__ __forceinline__ uint64_t make_kmajor_desc(uint32_t smem_addr, int row_bytes)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)((8 * row_bytes) >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)(row_bytes == 128 ? 2 : row_bytes == 64 ? 4 : 6) << 61;
     return d;
 }
 // Instruction descriptor: dense, K-major A and B, M = 128, N = n.

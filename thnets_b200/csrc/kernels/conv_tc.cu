@@ -2,19 +2,25 @@
 //
 // GEMM view: D[pixel][cout] = sum_k A[pixel][k] * Wt[cout][k], k = tap*Cin_pad + c.
 // One PERSISTENT CTA per SM walks output tiles of 128 consecutive pixels (flat over n, oh, ow: tiles
-// may span rows and images, so small feature maps waste nothing) x BN output channels.  Ten warps:
-//   warps 0-3  A producers: gather 16-byte channel chunks of the NHWC activation straight into the
-//              128-byte-swizzled K-major stage layout with zero-filling cp.async (out-of-image taps and
-//              ragged tiles become zeros; no im2col buffer exists anywhere);
-//   warp  4    B producer: packed weights (K-major) by 2-D TMA with SWIZZLE_128B, no multicast;
+// may span rows and images, so small feature maps waste nothing) x BN output channels.  Fourteen warps:
+//   warp  4    TMA producer: packed weights (K-major, SWIZZLE_128B, no multicast) and -- whenever a K block is
+//              one whole 128-byte channel slab of one tap -- the activation operand too: a plain 2-D load for
+//              1x1 stride-1 convolutions, an im2col-mode load (the copy engine walks the 128 output pixels,
+//              applies stride, tap offset and zero padding) for everything else;
+//   warps 0-3  otherwise (few input channels, e.g. a first layer) gather 16-byte channel chunks of the NHWC
+//              activation into the swizzled stage layout with zero-filling cp.async; in the TMA modes they
+//              are a third epilogue group;
 //   warp  5    MMA issuer: one elected thread issues tcgen05.mma (kind::f16: fp16/bf16 -> fp32,
-//              kind::i8: u8 x u8 -> int32) into one of TWO TMEM accumulators, recycles stages through
-//              tcgen05.commit -> mbarrier, and hands a finished accumulator to the epilogue;
-//   warps 6-9  epilogue: tcgen05.ld the accumulator rows (TMEM lane = pixel), release the accumulator,
-//              stage a block of columns in shared memory and write it out as runs of consecutive
-//              16-byte chunks per pixel with bias/BN scale-shift, residual and activation applied -- or
-//              the exact lowp requantisation.  The epilogue of tile i overlaps the main loop of tile i+1.
-// Every wait is bounded: a wait that runs out records a code in *status and the CTA drains and exits.
+//              kind::i8: u8 x u8 -> int32) into one of 2-4 TMEM accumulators, recycles stages through
+//              tcgen05.commit -> mbarrier, and hands finished accumulators to the epilogue;
+//   warps 6-13 two epilogue groups; a group drains its tile's accumulator 64 columns at a time with
+//              tcgen05.ld (TMEM lane = pixel), applies bias/BN scale-shift, residual and activation, and
+//              leaves the fp16/bf16 rows in a swizzled shared-memory tile that one thread hands to a TMA
+//              store; the residual tile is prefetched into that same shared-memory tile by TMA two blocks
+//              ahead, so no epilogue thread ever waits on global memory.  The uint8 path (exact lowp
+//              requantisation) and BN = 32 stage through shared memory and write out with plain stores.
+// No im2col buffer exists anywhere.  Every wait is bounded: a wait that runs out records a code in
+// *status and the CTA drains and exits.
 #include "common.cuh"
 #include <cuda.h>
 #include <string.h>
@@ -25,7 +31,8 @@ namespace {
 
 constexpr int BM = 128;                  // pixels per tile (= TMEM lanes)
 constexpr int A_STAGE_BYTES = BM * 128;  // 128 rows of one 128-byte K block
-constexpr int NTHREADS = 448;           // 4 producer + 1 TMA + 1 MMA + 2 x 4 epilogue warps
+constexpr int NTHREADS = 448;           // 4 producer/epilogue + 1 TMA + 1 MMA + 2 x 4 epilogue warps
+constexpr int EPI_TILE_BYTES = BM * 128;  // one 128-row x 64-column fp16 tile of the TMA epilogue
 
 struct ConvTcParams {
     const uint8_t *x;
@@ -44,6 +51,10 @@ struct ConvTcParams {
     int tail_start, relu_thr, relu_val;
     int a_tma;   // 1: 1x1 stride-1 convolution, the activation operand is a plain [pixels][Cin] matrix loaded by 2-D TMA;
                  // 2: whole 128-byte channel slabs per tap, loaded by im2col-mode TMA (any kernel size, stride, padding)
+    int epi_groups, epi_bufs;  // TMA epilogue: groups at work (2 or 3) and 16 KB tiles each of them cycles through
+                 // 3: 16 or 32 channels (32 or 64 bytes) per tap: one im2col-mode TMA load per tap into a sub-tile of
+                 //    that row width, 4 or 2 taps per K block
+    int tap_bytes, taps;  // a_tma == 3: bytes of one pixel's channels, kH * kW
     int slabs;   // a_tma == 2: 128-byte channel slabs per tap (K block kb = tap * slabs + slab)
     int use_l1;  // gather through L1: neighbouring taps of one tile re-read the same input pixels
     int *acc_out;
@@ -110,19 +121,203 @@ __device__ __forceinline__ uint4 epi_chunk(const float4 &a0, const float4 &a1, c
     return make_uint4(ow[0], ow[1], ow[2], ow[3]);
 }
 
+// One pixel row of a 64-channel block of the TMA epilogue: the thread's 64 accumulator columns -> eight 16-byte chunks
+// of its row of the swizzled shared-memory tile, which holds the residual row on entry when HAS_RES.  One variant is
+// chosen per block, so that only the code of that variant is fetched.
+template <int KIND, bool HAS_RES, int ACT, bool CHECK>
+__device__ __forceinline__ void epi_block(const uint32_t (&acc0)[32], const uint32_t (&acc1)[32], uint8_t *row_smem, int rsw,
+                                          int nsub0, const ConvTcParams &p)
+{
+    const float *scale = p.scale, *shift = p.shift, *slope = ACT == 2 ? p.slope : nullptr;
+    const int cout = p.Cout;
+    const float self = HAS_RES ? p.self_coef : 1.f;
+#pragma unroll
+    for (int cj = 0; cj < 8; cj++) {
+        const int c0 = nsub0 + cj * 8;
+        uint4 *slot = reinterpret_cast<uint4 *>(row_smem + ((cj ^ rsw) << 4));
+        uint4 o = make_uint4(0, 0, 0, 0);
+        if (!CHECK || c0 < cout) {
+            float sc[8], sh[8], sl[8];
+            const float4 one = make_float4(self, self, self, self), zero = make_float4(0.f, 0.f, 0.f, 0.f);
+            float4 t0 = one, t1 = one;
+            if (scale) {
+                t0 = __ldg(reinterpret_cast<const float4 *>(scale + c0));
+                t1 = __ldg(reinterpret_cast<const float4 *>(scale + c0 + 4));
+                if (HAS_RES) { t0.x *= self; t0.y *= self; t0.z *= self; t0.w *= self; t1.x *= self; t1.y *= self; t1.z *= self; t1.w *= self; }
+            }
+            sc[0] = t0.x; sc[1] = t0.y; sc[2] = t0.z; sc[3] = t0.w; sc[4] = t1.x; sc[5] = t1.y; sc[6] = t1.z; sc[7] = t1.w;
+            t0 = zero; t1 = zero;
+            if (shift) {
+                t0 = __ldg(reinterpret_cast<const float4 *>(shift + c0));
+                t1 = __ldg(reinterpret_cast<const float4 *>(shift + c0 + 4));
+                if (HAS_RES) { t0.x *= self; t0.y *= self; t0.z *= self; t0.w *= self; t1.x *= self; t1.y *= self; t1.z *= self; t1.w *= self; }
+            }
+            sh[0] = t0.x; sh[1] = t0.y; sh[2] = t0.z; sh[3] = t0.w; sh[4] = t1.x; sh[5] = t1.y; sh[6] = t1.z; sh[7] = t1.w;
+            t0 = zero; t1 = zero;
+            if (ACT == 2 && slope) {
+                t0 = __ldg(reinterpret_cast<const float4 *>(slope + c0));
+                t1 = __ldg(reinterpret_cast<const float4 *>(slope + c0 + 4));
+            }
+            sl[0] = t0.x; sl[1] = t0.y; sl[2] = t0.z; sl[3] = t0.w; sl[4] = t1.x; sl[5] = t1.y; sl[6] = t1.z; sl[7] = t1.w;
+            const uint32_t *a = cj < 4 ? acc0 + cj * 8 : acc1 + (cj - 4) * 8;
+            const float4 a0 = make_float4(__uint_as_float(a[0]), __uint_as_float(a[1]), __uint_as_float(a[2]), __uint_as_float(a[3]));
+            const float4 a1 = make_float4(__uint_as_float(a[4]), __uint_as_float(a[5]), __uint_as_float(a[6]), __uint_as_float(a[7]));
+            const uint4 rv = HAS_RES ? *slot : make_uint4(0, 0, 0, 0);
+            o = epi_chunk<KIND, HAS_RES, ACT, CHECK>(a0, a1, sc, sh, sl, rv, p, c0);
+        }
+        *slot = o;
+    }
+}
+
 // shared-memory plan of one CTA
 template <int KIND, int BN, int STAGES> struct Smem {
-    static constexpr int SUBN = BN >= 256 ? 32 : (BN >= 64 ? 64 : BN);           // columns staged at a time
+    static constexpr bool TMA_EPI = KIND != 2 && BN >= 64;                        // epilogue through TMA loads/stores
+    static constexpr int SUBN = BN >= 256 ? 32 : (BN >= 64 ? 64 : BN);           // staged epilogue: columns at a time
     static constexpr int B_STAGE_BYTES = BN * 128;
     static constexpr size_t PIPE = (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
     static constexpr size_t STAGING = KIND == 2 ? (size_t)BM * (SUBN + 16) : (size_t)BM * (SUBN + 4) * 4;
     static constexpr size_t STAGING_PAD = (STAGING + 127) / 128 * 128;  // one staging tile per epilogue group
-    static constexpr size_t BARS = (2 * STAGES + 12) * 8 + 16;
-    static constexpr size_t TOTAL = 1024 + PIPE + 2 * STAGING_PAD + BARS + 64;
+    static constexpr int EPI_TILES = BN >= 256 ? 4 : 6;                 // TMA epilogue: 16 KB tiles shared out to the groups
+    static constexpr size_t EPI = TMA_EPI ? (size_t)EPI_TILES * EPI_TILE_BYTES : 2 * STAGING_PAD;
+    static constexpr size_t BARS = (2 * STAGES + 24) * 8 + 16;
+    static constexpr size_t TOTAL = 1024 + PIPE + EPI + BARS + 64;
 };
+
+// position of an epilogue group in its sequence of 64-column blocks
+struct EpiCursor {
+    int j, sb;  // j-th tile of this group, block sb of that tile
+};
+
+// The TMA epilogue of one group of four warps (fp16 / bf16, BN >= 64).  The group owns every ngrp-th tile of this
+// CTA and walks it in blocks of 64 output channels through `nbuf` shared-memory tiles of 128 rows x 128 bytes
+// (SWIZZLE_128B).  Per block: the residual tile (if any) arrives by a TMA load that the group's leader issued two
+// blocks earlier; each thread owns one pixel row: it reads its 64 accumulator columns from TMEM, combines them with
+// its residual row in place and leaves the converted row in the tile; after a group barrier the leader hands the
+// tile to a TMA store (which clips rows and channels beyond the tensor) and prefetches the residual of the block
+// two ahead into the tile whose store has finished reading.
+template <int KIND, int BN, int NACC>
+__device__ __forceinline__ void epilogue_tma(const ConvTcParams &p, const CUtensorMap *tmY, const CUtensorMap *tmR, int grp,
+                                             int et, int warp, int lane, uint32_t tmem_base, uint8_t *tiles,
+                                             uint64_t *acc_full, uint64_t *acc_empty, uint64_t *sync_bar_p,
+                                             uint64_t *res_full, volatile int *abort_flag, int total_tiles)
+{
+    constexpr int NSB = BN / 64;
+    const int ngrp = p.epi_groups, nbuf = p.epi_bufs;
+    const int quad = warp & 3, row = quad * 32 + lane;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t sync_bar = smem_u32(sync_bar_p);
+    const bool has_res = p.res != nullptr, leader = et == 0;
+    const int act_mode = p.act_kind == THB_ACT_NONE ? 0
+                         : p.act_kind != THB_ACT_THRESHOLD ? 2
+                         : (p.act_th == 0.f && p.act_val == 0.f) ? 3 : 1;
+    const int cout8 = (p.Cout + 7) & ~7;
+    const int first = blockIdx.x + grp * gridDim.x, step = gridDim.x * ngrp;
+    const int my_tiles = first < total_tiles ? (total_tiles - 1 - first) / step + 1 : 0;
+    auto blocks_of = [&](int j) {  // 64-column blocks of the group's j-th tile that hold real channels
+        const int n0 = ((first + j * step) % p.n_tiles) * BN;
+        return min(NSB, (cout8 - n0 + 63) >> 6);
+    };
+    auto advance = [&](EpiCursor &c) {
+        if (++c.sb == blocks_of(c.j)) { c.sb = 0; c.j++; }
+    };
+    auto load_residual = [&](const EpiCursor &c, int q) {  // leader only
+        const int tile = first + c.j * step;
+        const int b = q % nbuf;
+        mbar_arrive_expect_tx(smem_u32(&res_full[b]), EPI_TILE_BYTES);
+        tma_load_2d(smem_u32(tiles + b * EPI_TILE_BYTES), tmR, smem_u32(&res_full[b]), (tile % p.n_tiles) * BN + c.sb * 64,
+                    (tile / p.n_tiles) * BM);
+    };
+    EpiCursor cur = {0, 0}, pre = {0, 0};  // block being processed / next block whose residual has not been requested
+    int q_pre = 0;
+    if (leader && has_res)
+        for (; q_pre < 2 && pre.j < my_tiles; q_pre++) {
+            load_residual(pre, q_pre);
+            advance(pre);
+        }
+    bool alive = true;
+    int q = 0;
+    for (; cur.j < my_tiles && alive; q++) {
+        const int lt = grp + cur.j * ngrp, tile = first + cur.j * step;
+        const int m0 = (tile / p.n_tiles) * BM, n0 = (tile % p.n_tiles) * BN, nsub0 = n0 + cur.sb * 64;
+        const int ab = lt % NACC;
+        const bool last_block = cur.sb == blocks_of(cur.j) - 1;
+        uint8_t *tile_smem = tiles + (q % nbuf) * EPI_TILE_BYTES;
+        if (cur.sb == 0) {
+            if (!mbar_wait_bounded(smem_u32(&acc_full[ab]), (lt / NACC) & 1)) {
+                if (lane == 0) atomicExch(p.status, 2);
+                *abort_flag = 1;
+                alive = false;
+            }
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) break;
+            tc_fence_after();
+        }
+        uint32_t acc0[32], acc1[32];
+        __syncwarp();
+        tmem_ld32(lane_base + ab * BN + cur.sb * 64, acc0);
+        tmem_ld32(lane_base + ab * BN + cur.sb * 64 + 32, acc1);
+        tmem_ld_wait();
+        if (last_block) {  // every column of this accumulator has been read: hand it back to the MMA warp
+            tc_fence_before();
+            mbar_arrive(smem_u32(&acc_empty[ab]));
+        }
+        if (has_res) {
+            if (!mbar_wait_bounded(smem_u32(&res_full[q % nbuf]), (q / nbuf) & 1)) {
+                if (lane == 0) atomicExch(p.status, 8);
+                *abort_flag = 1;
+                alive = false;
+            }
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) break;
+        }
+        {
+            uint8_t *row_smem = tile_smem + row * 128;
+            const int rsw = row & 7;
+            if (nsub0 + 64 > p.Cout || act_mode == 2 || act_mode == 1) {  // ragged channel edge or a general activation
+                if (has_res) epi_block<KIND, true, 2, true>(acc0, acc1, row_smem, rsw, nsub0, p);
+                else epi_block<KIND, false, 2, true>(acc0, acc1, row_smem, rsw, nsub0, p);
+            } else if (has_res) {
+                if (act_mode) epi_block<KIND, true, 3, false>(acc0, acc1, row_smem, rsw, nsub0, p);
+                else epi_block<KIND, true, 0, false>(acc0, acc1, row_smem, rsw, nsub0, p);
+            } else {
+                if (act_mode) epi_block<KIND, false, 3, false>(acc0, acc1, row_smem, rsw, nsub0, p);
+                else epi_block<KIND, false, 0, false>(acc0, acc1, row_smem, rsw, nsub0, p);
+            }
+        }
+        fence_proxy_async_smem();  // this thread's rows must be visible to the copy engine
+        mbar_arrive(sync_bar);
+        if (!mbar_wait_bounded(sync_bar, q & 1)) {
+            if (lane == 0) atomicExch(p.status, 5);
+            *abort_flag = 1;
+            alive = false;
+        }
+        alive = __all_sync(0xffffffffu, alive);
+        if (!alive) break;
+        if (leader) {
+            tma_store_2d(tmY, smem_u32(tile_smem), nsub0, m0);
+            bulk_commit_group();
+            // the tile that block q + 2 will use must have been read out by its previous store (block q + 2 - nbuf)
+            if (nbuf >= 3) bulk_wait_group_read<1>();
+            else bulk_wait_group_read<0>();
+            if (has_res && pre.j < my_tiles) {
+                load_residual(pre, q_pre++);
+                advance(pre);
+            }
+        }
+        __syncwarp();
+        advance(cur);
+    }
+    if (leader) {
+        bulk_wait_group<0>();
+        // residual loads still in flight after an early exit must land before the CTA may leave
+        if (has_res)
+            for (int k = alive ? q_pre : q; k < q_pre; k++) mbar_wait_bounded(smem_u32(&res_full[k % nbuf]), (k / nbuf) & 1);
+    }
+}
 
 template <int KIND, int BN, int STAGES>
 __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_constant__ CUtensorMap tmapA,
+                                                               const __grid_constant__ CUtensorMap tmapY, const __grid_constant__ CUtensorMap tmapR,
                                                                const ConvTcParams p)
 {
     using L = Smem<KIND, BN, STAGES>;
@@ -140,11 +335,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
     uint8_t *sA = smem;
     uint8_t *sB = smem + STAGES * A_STAGE_BYTES;
     uint8_t *stage_buf = smem + L::PIPE;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(stage_buf + 2 * L::STAGING_PAD);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(stage_buf + L::EPI);
     uint64_t *full = bars, *empty = bars + STAGES;
     uint64_t *acc_full = bars + 2 * STAGES, *acc_empty = acc_full + 4;
-    uint64_t *stg_ready = acc_empty + 4, *stg_free = stg_ready + 2;  // one pair per epilogue group
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(stg_free + 2);
+    uint64_t *stg_ready = acc_empty + 4, *stg_free = stg_ready + 3;  // one pair per epilogue group (staged epilogue)
+    uint64_t *res_full = stg_free + 3;                               // TMA epilogue: one per residual tile in flight
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(res_full + 9);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -159,10 +355,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
             mbar_init(smem_u32(&acc_full[b]), 1);
             mbar_init(smem_u32(&acc_empty[b]), 128);
         }
-        for (int g = 0; g < 2; g++) {
+        for (int g = 0; g < 3; g++) {
             mbar_init(smem_u32(&stg_ready[g]), 128);
             mbar_init(smem_u32(&stg_free[g]), 128);
         }
+        for (int g = 0; g < 9; g++) mbar_init(smem_u32(&res_full[g]), 1);
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
@@ -170,6 +367,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
     if (warp == 4 && lane == 0) {
         tma_prefetch_desc(&tmapW);
         if (p.a_tma) tma_prefetch_desc(&tmapA);
+        if (L::TMA_EPI) {
+            tma_prefetch_desc(&tmapY);
+            if (p.res) tma_prefetch_desc(&tmapR);
+        }
     }
     if (warp == 5) {
         tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
@@ -182,7 +383,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
 
     if (warp < 4) {
         // ================================================================== A producer (gather mode)
-        if (p.a_tma) goto done;
+        if (p.a_tma) {
+            // nothing to gather: these four warps are the third epilogue group
+            if constexpr (L::TMA_EPI)
+                if (p.epi_groups == 3)
+                    epilogue_tma<KIND, BN, NACC>(p, &tmapY, &tmapR, 2, tid, warp, lane, tmem_base,
+                                                 stage_buf + 2 * p.epi_bufs * EPI_TILE_BYTES, acc_full, acc_empty, &stg_ready[2],
+                                                 res_full + 6, abort_flag, total_tiles);
+            goto done;
+        }
         const int chunk = lane & 7;
         bool alive = true;
         int it = 0;  // K blocks issued so far by this CTA, over all its tiles
@@ -262,7 +471,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                 const int m0 = (tile / p.n_tiles) * BM;
                 // im2col mode: input position of the tile's first output pixel for tap (0, 0)
                 int iw = 0, ih = 0, in = 0, tap_w = 0, tap_h = 0, slab = 0;
-                if (p.a_tma == 2) {
+                if (p.a_tma >= 2) {
                     in = m0 / p.oHW;
                     const int rem = m0 - in * p.oHW;
                     const int oh = rem / p.oW;
@@ -288,6 +497,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                         if (++slab == p.slabs) {
                             slab = 0;
                             if (++tap_w == p.kW) { tap_w = 0; tap_h++; }
+                        }
+                    } else if (p.a_tma == 3) {
+                        mbar_arrive_expect_tx(smem_u32(&full[s]), B_STAGE_BYTES + A_STAGE_BYTES);
+                        const int tps = 128 / p.tap_bytes;  // taps per K block
+                        for (int t = 0; t < tps; t++) {
+                            // taps beyond the kernel (K padding) meet zero weights: any finite data will do
+                            const int tap = kb * tps + t < p.taps ? kb * tps + t : 0;
+                            const int th = tap / p.kW;
+                            tma_load_im2col_4d(smem_u32(sA + s * A_STAGE_BYTES + t * BM * p.tap_bytes), &tmapA, smem_u32(&full[s]), 0,
+                                               iw, ih, in, (uint16_t)(tap - th * p.kW), (uint16_t)th);
                         }
                     } else
                         mbar_arrive_expect_tx(smem_u32(&full[s]), B_STAGE_BYTES);
@@ -322,13 +541,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     }
                     tc_fence_after();
                     fence_proxy_async_smem();
-                    const uint64_t adesc = make_sw128_kmajor_desc(smem_u32(sA + s * A_STAGE_BYTES));
+                    const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
+                    const uint64_t adesc = make_sw128_kmajor_desc(a_addr);
                     const uint64_t bdesc = make_sw128_kmajor_desc(smem_u32(sB + s * B_STAGE_BYTES));
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
                         const uint32_t accum = (kb | k) != 0;
-                        if (KIND == 2) tc_mma_i8(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, accum);
-                        else tc_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, accum);
+                        // per-tap sub-tiles: 32-byte step k lies in sub-tile k*32/tap_bytes, at k*32 % tap_bytes of its rows
+                        const uint64_t ad = p.a_tma != 3 ? adesc + 2 * k
+                                                         : make_kmajor_desc(a_addr + (k * 32 / p.tap_bytes) * BM * p.tap_bytes +
+                                                                                (k * 32) % p.tap_bytes, p.tap_bytes);
+                        if (KIND == 2) tc_mma_i8(d_tmem, ad, bdesc + 2 * k, IDESC, accum);
+                        else tc_mma_f16(d_tmem, ad, bdesc + 2 * k, IDESC, accum);
                     }
                     tc_commit(smem_u32(&empty[s]));
                 }
@@ -342,6 +566,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
         // write-out of one tile overlaps the accumulator drain of the next.
         const int grp = (warp - 6) >> 2;
         const int et = tid - 192 - grp * 128;  // 0..127 within the group
+        if constexpr (L::TMA_EPI) {
+            epilogue_tma<KIND, BN, NACC>(p, &tmapY, &tmapR, grp, et, warp, lane, tmem_base,
+                                         stage_buf + grp * p.epi_bufs * EPI_TILE_BYTES, acc_full, acc_empty, &stg_ready[grp],
+                                         res_full + grp * 3, abort_flag, total_tiles);
+            goto done;
+        }
         const int quad = warp & 3;             // TMEM lane quadrant this warp may read
         const int row = quad * 32 + lane;      // tile row (= pixel) owned in phase 1
         const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
@@ -545,8 +775,12 @@ int num_sms()
     return n[dev] > 0 ? n[dev] : 148;
 }
 
+struct ConvTmaps {
+    const CUtensorMap *w, *a, *y, *r;  // weights, activation operand, output, residual (unused ones alias w)
+};
+
 template <int KIND, int BN, int STAGES>
-int launch_tc(const CUtensorMap &tm, const CUtensorMap &ta, const ConvTcParams &p, cudaStream_t st)
+int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
 {
     static bool configured[16] = {false};
     auto kern = conv_tc_kernel<KIND, BN, STAGES>;
@@ -562,18 +796,25 @@ int launch_tc(const CUtensorMap &tm, const CUtensorMap &ta, const ConvTcParams &
     }
     const int tiles = p.m_tiles * p.n_tiles;
     const int grid = tiles < num_sms() ? tiles : num_sms();
-    kern<<<grid, NTHREADS, smem, st>>>(tm, ta, p);
+    using L = Smem<KIND, BN, STAGES>;
+    if (L::TMA_EPI) {
+        if (!tm.y || (p.res && !tm.r)) return thb_note_launch(cudaErrorUnknown, "conv_tc: output tensor map");
+        // warps 0-3 join the epilogue when they have nothing to gather and a third accumulator exists for them
+        p.epi_groups = p.a_tma && L::EPI_TILES >= 6 ? 3 : 2;
+        p.epi_bufs = L::EPI_TILES / p.epi_groups;
+    }
+    kern<<<grid, NTHREADS, smem, st>>>(*tm.w, *tm.a, tm.y ? *tm.y : *tm.w, tm.r ? *tm.r : *tm.w, p);
     return THB_LAUNCH_CHECK("conv_tc_kernel");
 }
 
 template <int KIND>
-int dispatch_bn(int BN, const CUtensorMap &tm, const CUtensorMap &ta, const ConvTcParams &p, cudaStream_t st)
+int dispatch_bn(int BN, const ConvTmaps &tm, const ConvTcParams &p, cudaStream_t st)
 {
     switch (BN) {
-    case 32: return launch_tc<KIND, 32, 6>(tm, ta, p, st);
-    case 64: return launch_tc<KIND, 64, 5>(tm, ta, p, st);
-    case 128: return launch_tc<KIND, 128, 4>(tm, ta, p, st);
-    case 256: return launch_tc<KIND, 256, 3>(tm, ta, p, st);
+    case 32: return launch_tc<KIND, 32, 6>(tm, p, st);
+    case 64: return launch_tc<KIND, 64, 5>(tm, p, st);
+    case 128: return launch_tc<KIND, 128, 4>(tm, p, st);
+    case 256: return launch_tc<KIND, 256, 3>(tm, p, st);
     }
     return THB_ERR_UNSUPPORTED;
 }
@@ -612,6 +853,40 @@ encode_im2col_fn get_encode_im2col_fn()
     return fn;
 }
 
+// TMA descriptors of plain row-major matrices [rows][cols] with a row pitch (activation operand of a 1x1
+// convolution, output and residual tensors), keyed by what they encode and built once per buffer and shape.
+struct MTmapEntry {
+    const void *x;
+    long rows;
+    int cols, ld, dtype, box_cols;
+    alignas(64) CUtensorMap map;
+};
+const CUtensorMap *matrix_tmap(const void *x, long rows, int cols, int ld, int dtype, int box_cols)
+{
+    static MTmapEntry cache[1024];
+    static int used = 0, next = 0;
+    for (int i = 0; i < used; i++) {
+        MTmapEntry &e = cache[i];
+        if (e.x == x && e.rows == rows && e.cols == cols && e.ld == ld && e.dtype == dtype && e.box_cols == box_cols) return &e.map;
+    }
+    encode_tiled_fn enc = get_encode_fn();
+    if (!enc) return nullptr;
+    MTmapEntry &e = cache[used < 1024 ? used++ : (next++ % 1024)];
+    e.x = nullptr;
+    const int es = dtype == THB_U8 ? 1 : 2;
+    CUtensorMapDataType t = dtype == THB_U8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                            : dtype == THB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * es};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)BM};
+    cuuint32_t estr[2] = {1, 1};
+    if (enc(&e.map, t, 2, const_cast<void *>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return nullptr;
+    e.x = x; e.rows = rows; e.cols = cols; e.ld = ld; e.dtype = dtype; e.box_cols = box_cols;
+    return &e.map;
+}
+
 // TMA descriptors of activation operands, keyed by what they encode (built once per buffer and shape).
 // mode 1: the plain [pixels][Cin] matrix of a 1x1 stride-1 convolution; mode 2: im2col over {C, W, H, N}.
 struct ATmapEntry {
@@ -621,6 +896,8 @@ struct ATmapEntry {
 };
 const CUtensorMap *activation_tmap(const thb_conv_desc *d, const void *x, int mode)
 {
+    if (mode == 1)
+        return matrix_tmap(x, (long)d->N * d->H * d->W, d->Cin_pad, d->in_ld, d->dtype, d->dtype == THB_U8 ? 128 : 64);
     static ATmapEntry cache[512];
     static int used = 0, next = 0;
     const int geom[6] = {d->kH, d->kW, d->dH, d->dW, d->padH, d->padW};
@@ -635,17 +912,7 @@ const CUtensorMap *activation_tmap(const thb_conv_desc *d, const void *x, int mo
     const int es = d->dtype == THB_U8 ? 1 : 2;
     CUtensorMapDataType t = d->dtype == THB_U8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                             : d->dtype == THB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-    if (mode == 1) {
-        encode_tiled_fn enc = get_encode_fn();
-        if (!enc) return nullptr;
-        cuuint64_t dims[2] = {(cuuint64_t)d->Cin_pad, (cuuint64_t)d->N * d->H * d->W};
-        cuuint64_t strides[1] = {(cuuint64_t)d->in_ld * es};
-        cuuint32_t box[2] = {(cuuint32_t)(128 / es), (cuuint32_t)BM};
-        cuuint32_t estr[2] = {1, 1};
-        if (enc(&e.map, t, 2, const_cast<void *>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-            return nullptr;
-    } else {
+    {
         encode_im2col_fn enc = get_encode_im2col_fn();
         if (!enc) return nullptr;
         // The bounding box that base pixels (tap (0,0) positions) live in: from -pad to dim + pad - (k - 1), so that
@@ -656,8 +923,12 @@ const CUtensorMap *activation_tmap(const thb_conv_desc *d, const void *x, int mo
         int lower[2] = {-d->padW, -d->padH};
         int upper[2] = {d->padW - (d->kW - 1), d->padH - (d->kH - 1)};
         cuuint32_t estr[4] = {1, (cuuint32_t)d->dW, (cuuint32_t)d->dH, 1};
-        if (enc(&e.map, t, 4, const_cast<void *>(x), dims, strides, lower, upper, (cuuint32_t)(128 / es), (cuuint32_t)BM, estr,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        // mode 2 fetches 128-byte channel slabs; mode 3 a pixel's 32 or 64 bytes of channels, swizzled at that width
+        const int row_bytes = mode == 3 ? d->Cin_pad * es : 128;
+        const CUtensorMapSwizzle swz = row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                       : row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+        if (enc(&e.map, t, 4, const_cast<void *>(x), dims, strides, lower, upper, (cuuint32_t)(row_bytes / es), (cuuint32_t)BM, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return nullptr;
         // Drivers up to CUDA 13.1 encode im2col descriptors of tensors smaller than 128 KiB with a flag (bit 21 of
@@ -737,25 +1008,36 @@ extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, t
     // anything else whose taps are whole 128-byte channel slabs goes through im2col-mode TMA, within the limits of
     // a rank-4 descriptor: box corners in [-128, 127], traversal strides up to 8, tap offsets below 256
     const int bke = 128 / es;
-    if (!p.a_tma && d->Cin_pad % bke == 0 && d->Ktot_pad == d->kH * d->kW * d->Cin_pad && d->dH <= 8 && d->dW <= 8 &&
-        d->padH <= 127 && d->padW <= 127 && d->kH - 1 - d->padH <= 128 && d->kW - 1 - d->padW <= 128 && d->kH <= 256 &&
-        d->kW <= 256 && d->H + 2 * d->padH >= d->kH && d->W + 2 * d->padW >= d->kW &&
-        d->oH == (d->H + 2 * d->padH - d->kH) / d->dH + 1 && d->oW == (d->W + 2 * d->padW - d->kW) / d->dW + 1)
-        p.a_tma = 2;
+    const bool im2col_ok = !p.a_tma && d->dH <= 8 && d->dW <= 8 && d->padH <= 127 && d->padW <= 127 &&
+                           d->kH - 1 - d->padH <= 128 && d->kW - 1 - d->padW <= 128 && d->kH <= 256 && d->kW <= 256 &&
+                           d->H + 2 * d->padH >= d->kH && d->W + 2 * d->padW >= d->kW &&
+                           d->oH == (d->H + 2 * d->padH - d->kH) / d->dH + 1 && d->oW == (d->W + 2 * d->padW - d->kW) / d->dW + 1;
+    if (im2col_ok && d->Cin_pad % bke == 0 && d->Ktot_pad == d->kH * d->kW * d->Cin_pad) p.a_tma = 2;
+    // a pixel's channels fill exactly 32 or 64 bytes (e.g. a first layer after space-to-depth): one load per tap
+    else if (im2col_ok && (d->Cin_pad * es == 32 || d->Cin_pad * es == 64)) p.a_tma = 3;
     p.slabs = d->Cin_pad / bke;
+    p.tap_bytes = d->Cin_pad * es;
+    p.taps = d->kH * d->kW;
     if (const char *e = getenv("THB200_A_TMA")) {
-        const int allow = atoi(e);  // 0: gather only, 1: plain-matrix TMA only, 2 (default): im2col too
+        const int allow = atoi(e);  // 0: gather only, 1: plain-matrix TMA only, 2: + channel-slab im2col, 3 (default): all
         if (p.a_tma > allow) p.a_tma = 0;
     }
     if (p.a_tma) {
         ta = activation_tmap(d, x, p.a_tma);
         if (!ta) p.a_tma = 0, ta = &tm;
     }
+    ConvTmaps maps = {&tm, ta, nullptr, nullptr};
+    if (d->dtype != THB_U8 && d->BN >= 64) {
+        // output and residual go through TMA: [pixels][channels rounded up to 8] matrices with their own pitch
+        const int c8 = (d->Cout + 7) & ~7;
+        maps.y = matrix_tmap(y, p.P, c8, d->out_ld, d->dtype, 64);
+        if (d->res) maps.r = matrix_tmap(d->res, p.P, c8, d->res_ld, d->dtype, 64);
+    }
     cudaStream_t st = (cudaStream_t)s;
     switch (d->dtype) {
-    case THB_F16: return dispatch_bn<0>(d->BN, tm, *ta, p, st);
-    case THB_BF16: return dispatch_bn<1>(d->BN, tm, *ta, p, st);
-    case THB_U8: return dispatch_bn<2>(d->BN, tm, *ta, p, st);
+    case THB_F16: return dispatch_bn<0>(d->BN, maps, p, st);
+    case THB_BF16: return dispatch_bn<1>(d->BN, maps, p, st);
+    case THB_U8: return dispatch_bn<2>(d->BN, maps, p, st);
     }
     return THB_ERR_UNSUPPORTED;
 }
