@@ -44,7 +44,7 @@ CONV_CASES = [
     (2, 64, 30, 17, 96, 5, 1, 2),
     (1, 192, 13, 13, 48, 3, 1, 0),
     (2, 256, 9, 11, 32, 2, 2, 0),
-    # 32 or 64 bytes of channels per pixel: one im2col-mode load per tap, several taps per K block (K padding: 49 taps)
+    # few channels per pixel: several taps per K block, gathered (K padding: 49 taps)
     (2, 32, 15, 15, 64, 3, 1, 1),
     (1, 16, 20, 22, 64, 7, 2, 3),
     (2, 12, 23, 23, 72, 4, 1, 2),

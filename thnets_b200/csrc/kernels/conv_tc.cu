@@ -51,10 +51,8 @@ struct ConvTcParams {
     int tail_start, relu_thr, relu_val;
     int a_tma;   // 1: 1x1 stride-1 convolution, the activation operand is a plain [pixels][Cin] matrix loaded by 2-D TMA;
                  // 2: whole 128-byte channel slabs per tap, loaded by im2col-mode TMA (any kernel size, stride, padding)
+    int stages;                // TMA epilogue: pipeline stages (the launcher sizes them against the epilogue tiles)
     int epi_groups, epi_bufs;  // TMA epilogue: groups at work (2 or 3) and 16 KB tiles each of them cycles through
-                 // 3: 16 or 32 channels (32 or 64 bytes) per tap: one im2col-mode TMA load per tap into a sub-tile of
-                 //    that row width, 4 or 2 taps per K block
-    int tap_bytes, taps;  // a_tma == 3: bytes of one pixel's channels, kH * kW
     int slabs;   // a_tma == 2: 128-byte channel slabs per tap (K block kb = tap * slabs + slab)
     int use_l1;  // gather through L1: neighbouring taps of one tile re-read the same input pixels
     int *acc_out;
@@ -174,14 +172,17 @@ template <int KIND, int BN, int STAGES> struct Smem {
     static constexpr bool TMA_EPI = KIND != 2 && BN >= 64;                        // epilogue through TMA loads/stores
     static constexpr int SUBN = BN >= 256 ? 32 : (BN >= 64 ? 64 : BN);           // staged epilogue: columns at a time
     static constexpr int B_STAGE_BYTES = BN * 128;
-    static constexpr size_t PIPE = (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
+    static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
     static constexpr size_t STAGING = KIND == 2 ? (size_t)BM * (SUBN + 16) : (size_t)BM * (SUBN + 4) * 4;
     static constexpr size_t STAGING_PAD = (STAGING + 127) / 128 * 128;  // one staging tile per epilogue group
-    static constexpr int EPI_TILES = BN >= 256 ? 4 : 6;                 // TMA epilogue: 16 KB tiles shared out to the groups
-    static constexpr size_t EPI = TMA_EPI ? (size_t)EPI_TILES * EPI_TILE_BYTES : 2 * STAGING_PAD;
-    static constexpr size_t BARS = (2 * STAGES + 24) * 8 + 16;
-    static constexpr size_t TOTAL = 1024 + PIPE + EPI + BARS + 64;
+    static constexpr size_t BAR_BYTES = 1024;                           // mbarriers and the TMEM slot, ahead of the tiles
+    // The TMA epilogue takes the whole 227 KB: the launcher splits what the barriers leave between pipeline stages
+    // (at least STAGES of them) and 16 KB epilogue tiles.  The staged epilogue has STAGES stages and two staging tiles.
+    static constexpr size_t AVAIL = 232448 - 1024 - BAR_BYTES;
+    static constexpr size_t TOTAL = TMA_EPI ? 232448 : 1024 + BAR_BYTES + (size_t)STAGES * STAGE_BYTES + 2 * STAGING_PAD;
+    static_assert(TOTAL <= 232448, "shared memory plan exceeds the 227 KB a CTA can have");
 };
+constexpr int MAX_STAGES = 12;
 
 // position of an epilogue group in its sequence of 64-column blocks
 struct EpiCursor {
@@ -199,7 +200,7 @@ template <int KIND, int BN, int NACC>
 __device__ __forceinline__ void epilogue_tma(const ConvTcParams &p, const CUtensorMap *tmY, const CUtensorMap *tmR, int grp,
                                              int et, int warp, int lane, uint32_t tmem_base, uint8_t *tiles,
                                              uint64_t *acc_full, uint64_t *acc_empty, uint64_t *sync_bar_p,
-                                             uint64_t *res_full, volatile int *abort_flag, int total_tiles)
+                                             uint64_t *sync2_bar_p, uint64_t *res_full, volatile int *abort_flag, int total_tiles)
 {
     constexpr int NSB = BN / 64;
     const int ngrp = p.epi_groups, nbuf = p.epi_bufs;
@@ -229,8 +230,9 @@ __device__ __forceinline__ void epilogue_tma(const ConvTcParams &p, const CUtens
     };
     EpiCursor cur = {0, 0}, pre = {0, 0};  // block being processed / next block whose residual has not been requested
     int q_pre = 0;
+    const uint32_t sync2_bar = smem_u32(sync2_bar_p);
     if (leader && has_res)
-        for (; q_pre < 2 && pre.j < my_tiles; q_pre++) {
+        for (; q_pre < min(2, nbuf) && pre.j < my_tiles; q_pre++) {
             load_residual(pre, q_pre);
             advance(pre);
         }
@@ -296,7 +298,7 @@ __device__ __forceinline__ void epilogue_tma(const ConvTcParams &p, const CUtens
         if (leader) {
             tma_store_2d(tmY, smem_u32(tile_smem), nsub0, m0);
             bulk_commit_group();
-            // the tile that block q + 2 will use must have been read out by its previous store (block q + 2 - nbuf)
+            // the tile that the next prefetched block will use must have been read out by its previous store
             if (nbuf >= 3) bulk_wait_group_read<1>();
             else bulk_wait_group_read<0>();
             if (has_res && pre.j < my_tiles) {
@@ -305,6 +307,17 @@ __device__ __forceinline__ void epilogue_tma(const ConvTcParams &p, const CUtens
             }
         }
         __syncwarp();
+        if (nbuf == 1) {
+            // a single tile: nobody may write the next block into it before the leader has seen this store read it out
+            mbar_arrive(sync2_bar);
+            if (!mbar_wait_bounded(sync2_bar, q & 1)) {
+                if (lane == 0) atomicExch(p.status, 7);
+                *abort_flag = 1;
+                alive = false;
+            }
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) break;
+        }
         advance(cur);
     }
     if (leader) {
@@ -332,12 +345,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t *sA = smem;
-    uint8_t *sB = smem + STAGES * A_STAGE_BYTES;
-    uint8_t *stage_buf = smem + L::PIPE;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(stage_buf + L::EPI);
-    uint64_t *full = bars, *empty = bars + STAGES;
-    uint64_t *acc_full = bars + 2 * STAGES, *acc_empty = acc_full + 4;
+    const int nst = L::TMA_EPI ? p.stages : STAGES;  // pipeline stages in use
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
+    uint8_t *sA = smem + L::BAR_BYTES;
+    uint8_t *sB = sA + nst * A_STAGE_BYTES;
+    uint8_t *stage_buf = sA + nst * L::STAGE_BYTES;
+    uint64_t *full = bars, *empty = bars + MAX_STAGES;
+    uint64_t *acc_full = bars + 2 * MAX_STAGES, *acc_empty = acc_full + 4;
     uint64_t *stg_ready = acc_empty + 4, *stg_free = stg_ready + 3;  // one pair per epilogue group (staged epilogue)
     uint64_t *res_full = stg_free + 3;                               // TMA epilogue: one per residual tile in flight
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(res_full + 9);
@@ -347,7 +361,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
     const int total_tiles = p.m_tiles * p.n_tiles;
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; s++) {
+        for (int s = 0; s < nst; s++) {
             mbar_init(smem_u32(&full[s]), p.a_tma ? 1 : 128 + 1);
             mbar_init(smem_u32(&empty[s]), 1);
         }
@@ -389,7 +403,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                 if (p.epi_groups == 3)
                     epilogue_tma<KIND, BN, NACC>(p, &tmapY, &tmapR, 2, tid, warp, lane, tmem_base,
                                                  stage_buf + 2 * p.epi_bufs * EPI_TILE_BYTES, acc_full, acc_empty, &stg_ready[2],
-                                                 res_full + 6, abort_flag, total_tiles);
+                                                 &stg_free[2], res_full + 6, abort_flag, total_tiles);
             goto done;
         }
         const int chunk = lane & 7;
@@ -464,14 +478,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
     } else if (warp == 4) {
         // ================================================================== weight (B) TMA producer
         if (lane == 0) {
-            int it = 0;
+            int it = 0, ring_s = 0;  // stage and phase of K block `it` in the ring of nst stages
+            uint32_t ring_ph = 0;
             bool alive = true;
             for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
                 const int n0 = (tile % p.n_tiles) * BN;
                 const int m0 = (tile / p.n_tiles) * BM;
                 // im2col mode: input position of the tile's first output pixel for tap (0, 0)
                 int iw = 0, ih = 0, in = 0, tap_w = 0, tap_h = 0, slab = 0;
-                if (p.a_tma >= 2) {
+                if (p.a_tma == 2) {
                     in = m0 / p.oHW;
                     const int rem = m0 - in * p.oHW;
                     const int oh = rem / p.oW;
@@ -479,8 +494,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     iw = (rem - oh * p.oW) * p.dW - p.padW;
                 }
                 for (int kb = 0; kb < p.nkb; kb++, it++) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
+                    const int s = ring_s;
+                    const uint32_t ph = ring_ph;
+                    if (++ring_s == nst) { ring_s = 0; ring_ph ^= 1; }
                     if (!mbar_wait_bounded(smem_u32(&empty[s]), ph ^ 1)) {
                         atomicExch(p.status, 3);
                         *abort_flag = 1;
@@ -498,16 +514,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                             slab = 0;
                             if (++tap_w == p.kW) { tap_w = 0; tap_h++; }
                         }
-                    } else if (p.a_tma == 3) {
-                        mbar_arrive_expect_tx(smem_u32(&full[s]), B_STAGE_BYTES + A_STAGE_BYTES);
-                        const int tps = 128 / p.tap_bytes;  // taps per K block
-                        for (int t = 0; t < tps; t++) {
-                            // taps beyond the kernel (K padding) meet zero weights: any finite data will do
-                            const int tap = kb * tps + t < p.taps ? kb * tps + t : 0;
-                            const int th = tap / p.kW;
-                            tma_load_im2col_4d(smem_u32(sA + s * A_STAGE_BYTES + t * BM * p.tap_bytes), &tmapA, smem_u32(&full[s]), 0,
-                                               iw, ih, in, (uint16_t)(tap - th * p.kW), (uint16_t)th);
-                        }
                     } else
                         mbar_arrive_expect_tx(smem_u32(&full[s]), B_STAGE_BYTES);
                     tma_load_2d(smem_u32(sB + s * B_STAGE_BYTES), &tmapW, smem_u32(&full[s]), kb * BKE, n0);
@@ -518,7 +524,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
     } else if (warp == 5) {
         // ================================================================== MMA issuer
         if (lane == 0) {
-            int it = 0, lt = 0;
+            int it = 0, lt = 0, ring_s = 0;
+            uint32_t ring_ph = 0;
             bool alive = true;
             for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, lt++) {
                 const int b = lt % NACC;
@@ -531,8 +538,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + b * BN;
                 for (int kb = 0; kb < p.nkb; kb++, it++) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
+                    const int s = ring_s;
+                    const uint32_t ph = ring_ph;
+                    if (++ring_s == nst) { ring_s = 0; ring_ph ^= 1; }
                     if (!mbar_wait_bounded(smem_u32(&full[s]), ph)) {
                         atomicExch(p.status, 4);
                         *abort_flag = 1;
@@ -541,18 +549,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     }
                     tc_fence_after();
                     fence_proxy_async_smem();
-                    const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
-                    const uint64_t adesc = make_sw128_kmajor_desc(a_addr);
+                    const uint64_t adesc = make_sw128_kmajor_desc(smem_u32(sA + s * A_STAGE_BYTES));
                     const uint64_t bdesc = make_sw128_kmajor_desc(smem_u32(sB + s * B_STAGE_BYTES));
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
                         const uint32_t accum = (kb | k) != 0;
-                        // per-tap sub-tiles: 32-byte step k lies in sub-tile k*32/tap_bytes, at k*32 % tap_bytes of its rows
-                        const uint64_t ad = p.a_tma != 3 ? adesc + 2 * k
-                                                         : make_kmajor_desc(a_addr + (k * 32 / p.tap_bytes) * BM * p.tap_bytes +
-                                                                                (k * 32) % p.tap_bytes, p.tap_bytes);
-                        if (KIND == 2) tc_mma_i8(d_tmem, ad, bdesc + 2 * k, IDESC, accum);
-                        else tc_mma_f16(d_tmem, ad, bdesc + 2 * k, IDESC, accum);
+                        if (KIND == 2) tc_mma_i8(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, accum);
+                        else tc_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, accum);
                     }
                     tc_commit(smem_u32(&empty[s]));
                 }
@@ -569,7 +572,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
         if constexpr (L::TMA_EPI) {
             epilogue_tma<KIND, BN, NACC>(p, &tmapY, &tmapR, grp, et, warp, lane, tmem_base,
                                          stage_buf + grp * p.epi_bufs * EPI_TILE_BYTES, acc_full, acc_empty, &stg_ready[grp],
-                                         res_full + grp * 3, abort_flag, total_tiles);
+                                         &stg_free[grp], res_full + grp * 3, abort_flag, total_tiles);
             goto done;
         }
         const int quad = warp & 3;             // TMEM lane quadrant this warp may read
@@ -800,8 +803,17 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
     if (L::TMA_EPI) {
         if (!tm.y || (p.res && !tm.r)) return thb_note_launch(cudaErrorUnknown, "conv_tc: output tensor map");
         // warps 0-3 join the epilogue when they have nothing to gather and a third accumulator exists for them
-        p.epi_groups = p.a_tma && L::EPI_TILES >= 6 ? 3 : 2;
-        p.epi_bufs = L::EPI_TILES / p.epi_groups;
+        p.epi_groups = p.a_tma && BN < 256 ? 3 : 2;
+        // Short reductions live off their epilogue: two tiles per group (three when only two groups run), so that
+        // residual prefetch and store overlap the arithmetic.  Long reductions live off loads in flight: one tile per
+        // group and every remaining byte in pipeline stages.
+        p.epi_bufs = p.nkb >= 6 ? 1 : (p.epi_groups == 2 && BN < 256 ? 3 : 2);
+        if (const char *e = getenv("THB200_EPI_BUFS")) p.epi_bufs = atoi(e) < 1 ? 1 : atoi(e) > 3 ? 3 : atoi(e);
+        while ((size_t)STAGES * L::STAGE_BYTES + (size_t)p.epi_groups * p.epi_bufs * EPI_TILE_BYTES > L::AVAIL) p.epi_bufs--;
+        if (p.epi_bufs < 1) return thb_note_launch(cudaErrorUnknown, "conv_tc: shared-memory plan");
+        p.stages = (int)((L::AVAIL - (size_t)p.epi_groups * p.epi_bufs * EPI_TILE_BYTES) / L::STAGE_BYTES);
+        if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
+        if (!p.a_tma) p.stages = STAGES;  // the gather's cp.async depth is tied to the compile-time count
     }
     kern<<<grid, NTHREADS, smem, st>>>(*tm.w, *tm.a, tm.y ? *tm.y : *tm.w, tm.r ? *tm.r : *tm.w, p);
     return THB_LAUNCH_CHECK("conv_tc_kernel");
@@ -915,20 +927,17 @@ const CUtensorMap *activation_tmap(const thb_conv_desc *d, const void *x, int mo
     {
         encode_im2col_fn enc = get_encode_im2col_fn();
         if (!enc) return nullptr;
-        // The bounding box that base pixels (tap (0,0) positions) live in: from -pad to dim + pad - (k - 1), so that
-        // stepping by the convolution stride visits exactly oW x oH positions per image.
+        // The bounding box that base pixels (tap (0,0) positions) live in: from -pad up to the position of the last
+        // output pixel (dim + pad - (k - 1) for a full convolution), so that stepping by the convolution stride visits
+        // exactly oW x oH positions per image.
         cuuint64_t dims[4] = {(cuuint64_t)d->Cin_pad, (cuuint64_t)d->W, (cuuint64_t)d->H, (cuuint64_t)d->N};
         cuuint64_t strides[3] = {(cuuint64_t)d->in_ld * es, (cuuint64_t)d->W * d->in_ld * es,
                                  (cuuint64_t)d->H * d->W * d->in_ld * es};
         int lower[2] = {-d->padW, -d->padH};
-        int upper[2] = {d->padW - (d->kW - 1), d->padH - (d->kH - 1)};
+        int upper[2] = {(d->oW - 1) * d->dW + 1 - d->W - d->padW, (d->oH - 1) * d->dH + 1 - d->H - d->padH};
         cuuint32_t estr[4] = {1, (cuuint32_t)d->dW, (cuuint32_t)d->dH, 1};
-        // mode 2 fetches 128-byte channel slabs; mode 3 a pixel's 32 or 64 bytes of channels, swizzled at that width
-        const int row_bytes = mode == 3 ? d->Cin_pad * es : 128;
-        const CUtensorMapSwizzle swz = row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
-                                       : row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
-        if (enc(&e.map, t, 4, const_cast<void *>(x), dims, strides, lower, upper, (cuuint32_t)(row_bytes / es), (cuuint32_t)BM, estr,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        if (enc(&e.map, t, 4, const_cast<void *>(x), dims, strides, lower, upper, (cuuint32_t)(128 / es), (cuuint32_t)BM, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return nullptr;
         // Drivers up to CUDA 13.1 encode im2col descriptors of tensors smaller than 128 KiB with a flag (bit 21 of
@@ -967,6 +976,9 @@ extern "C" int thb_conv_make_tmap(const thb_conv_desc *d, thb_tmap *out)
     }
     return THB_OK;
 }
+
+// upper corner of the im2col bounding box: representable, and leaving a box of at least one position
+static bool box_corner_ok(int upper, int dim_plus_pad) { return upper >= -128 && upper <= 127 && dim_plus_pad + upper >= 1; }
 
 extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, thb_stream s)
 {
@@ -1009,17 +1021,13 @@ extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, t
     // a rank-4 descriptor: box corners in [-128, 127], traversal strides up to 8, tap offsets below 256
     const int bke = 128 / es;
     const bool im2col_ok = !p.a_tma && d->dH <= 8 && d->dW <= 8 && d->padH <= 127 && d->padW <= 127 &&
-                           d->kH - 1 - d->padH <= 128 && d->kW - 1 - d->padW <= 128 && d->kH <= 256 && d->kW <= 256 &&
-                           d->H + 2 * d->padH >= d->kH && d->W + 2 * d->padW >= d->kW &&
-                           d->oH == (d->H + 2 * d->padH - d->kH) / d->dH + 1 && d->oW == (d->W + 2 * d->padW - d->kW) / d->dW + 1;
+                           d->kH <= 256 && d->kW <= 256 && d->oH >= 1 && d->oW >= 1 &&
+                           box_corner_ok((d->oH - 1) * d->dH + 1 - d->H - d->padH, d->H + d->padH) &&
+                           box_corner_ok((d->oW - 1) * d->dW + 1 - d->W - d->padW, d->W + d->padW);
     if (im2col_ok && d->Cin_pad % bke == 0 && d->Ktot_pad == d->kH * d->kW * d->Cin_pad) p.a_tma = 2;
-    // a pixel's channels fill exactly 32 or 64 bytes (e.g. a first layer after space-to-depth): one load per tap
-    else if (im2col_ok && (d->Cin_pad * es == 32 || d->Cin_pad * es == 64)) p.a_tma = 3;
     p.slabs = d->Cin_pad / bke;
-    p.tap_bytes = d->Cin_pad * es;
-    p.taps = d->kH * d->kW;
     if (const char *e = getenv("THB200_A_TMA")) {
-        const int allow = atoi(e);  // 0: gather only, 1: plain-matrix TMA only, 2: + channel-slab im2col, 3 (default): all
+        const int allow = atoi(e);  // 0: gather only, 1: plain-matrix TMA only, 2 (default): im2col too
         if (p.a_tma > allow) p.a_tma = 0;
     }
     if (p.a_tma) {
