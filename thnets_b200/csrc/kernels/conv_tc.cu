@@ -31,7 +31,7 @@ namespace {
 
 constexpr int BM = 128;                  // pixels per tile (= TMEM lanes)
 constexpr int A_STAGE_BYTES = BM * 128;  // 128 rows of one 128-byte K block
-constexpr int NTHREADS = 448;           // 4 producer/epilogue + 1 TMA + 1 MMA + 2 x 4 epilogue warps
+constexpr int NTHREADS = 480;           // 4 producer/epilogue + 1 TMA + 1 MMA + 2 x 4 epilogue warps + 1 warp of agents
 constexpr int EPI_TILE_BYTES = BM * 128;  // one 128-row x 64-column fp16 tile of the TMA epilogue
 
 struct ConvTcParams {
@@ -189,61 +189,55 @@ struct EpiCursor {
     int j, sb;  // j-th tile of this group, block sb of that tile
 };
 
-// The TMA epilogue of one group of four warps (fp16 / bf16, BN >= 64).  The group owns every ngrp-th tile of this
-// CTA and walks it in blocks of 64 output channels through `nbuf` shared-memory tiles of 128 rows x 128 bytes
-// (SWIZZLE_128B).  Per block: the residual tile (if any) arrives by a TMA load that the group's leader issued two
-// blocks earlier; each thread owns one pixel row: it reads its 64 accumulator columns from TMEM, combines them with
-// its residual row in place and leaves the converted row in the tile; after a group barrier the leader hands the
-// tile to a TMA store (which clips rows and channels beyond the tensor) and prefetches the residual of the block
-// two ahead into the tile whose store has finished reading.
+// The sequence of 64-channel blocks an epilogue group walks: every ngrp-th tile of this CTA, and of each tile the
+// blocks that hold real channels.
+template <int BN> struct EpiWalk {
+    int first, step, my_tiles, n_tiles, cout8;
+    __device__ EpiWalk(const ConvTcParams &p, int grp, int total_tiles)
+    {
+        first = blockIdx.x + grp * gridDim.x;
+        step = gridDim.x * p.epi_groups;
+        my_tiles = first < total_tiles ? (total_tiles - 1 - first) / step + 1 : 0;
+        n_tiles = p.n_tiles;
+        cout8 = (p.Cout + 7) & ~7;
+    }
+    __device__ int tile(int j) const { return first + j * step; }
+    __device__ int blocks_of(int j) const { return min(BN / 64, (cout8 - (tile(j) % n_tiles) * BN + 63) >> 6); }
+    __device__ void advance(EpiCursor &c) const
+    {
+        if (++c.sb == blocks_of(c.j)) { c.sb = 0; c.j++; }
+    }
+};
+
+// The TMA epilogue of one group of four warps (fp16 / bf16, BN >= 64).  The group walks its tiles in blocks of 64
+// output channels through `nbuf` shared-memory tiles of 128 rows x 128 bytes (SWIZZLE_128B).  Each thread owns one
+// pixel row and never waits on another thread of its group or on global memory: it waits until the block's tile is
+// available (for a fused residual that is the arrival of the residual tile, loaded by the group's agent), reads its 64
+// accumulator columns from TMEM, combines them with its residual row in place, leaves the converted row in the tile
+// and arrives on the tile's rows_ready barrier.  The agent (epilogue_agent) does the rest.
 template <int KIND, int BN, int NACC>
-__device__ __forceinline__ void epilogue_tma(const ConvTcParams &p, const CUtensorMap *tmY, const CUtensorMap *tmR, int grp,
-                                             int et, int warp, int lane, uint32_t tmem_base, uint8_t *tiles,
-                                             uint64_t *acc_full, uint64_t *acc_empty, uint64_t *sync_bar_p,
-                                             uint64_t *sync2_bar_p, uint64_t *res_full, volatile int *abort_flag, int total_tiles)
+__device__ __forceinline__ void epilogue_tma(const ConvTcParams &p, int grp, int warp, int lane, uint32_t tmem_base,
+                                             uint8_t *tiles, uint64_t *acc_full, uint64_t *acc_empty, uint64_t *rows_ready,
+                                             uint64_t *avail, volatile int *abort_flag, int total_tiles)
 {
-    constexpr int NSB = BN / 64;
     const int ngrp = p.epi_groups, nbuf = p.epi_bufs;
     const int quad = warp & 3, row = quad * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
-    const uint32_t sync_bar = smem_u32(sync_bar_p);
-    const bool has_res = p.res != nullptr, leader = et == 0;
+    const bool has_res = p.res != nullptr;
     const int act_mode = p.act_kind == THB_ACT_NONE ? 0
                          : p.act_kind != THB_ACT_THRESHOLD ? 2
                          : (p.act_th == 0.f && p.act_val == 0.f) ? 3 : 1;
-    const int cout8 = (p.Cout + 7) & ~7;
-    const int first = blockIdx.x + grp * gridDim.x, step = gridDim.x * ngrp;
-    const int my_tiles = first < total_tiles ? (total_tiles - 1 - first) / step + 1 : 0;
-    auto blocks_of = [&](int j) {  // 64-column blocks of the group's j-th tile that hold real channels
-        const int n0 = ((first + j * step) % p.n_tiles) * BN;
-        return min(NSB, (cout8 - n0 + 63) >> 6);
-    };
-    auto advance = [&](EpiCursor &c) {
-        if (++c.sb == blocks_of(c.j)) { c.sb = 0; c.j++; }
-    };
-    auto load_residual = [&](const EpiCursor &c, int q) {  // leader only
-        const int tile = first + c.j * step;
-        const int b = q % nbuf;
-        mbar_arrive_expect_tx(smem_u32(&res_full[b]), EPI_TILE_BYTES);
-        tma_load_2d(smem_u32(tiles + b * EPI_TILE_BYTES), tmR, smem_u32(&res_full[b]), (tile % p.n_tiles) * BN + c.sb * 64,
-                    (tile / p.n_tiles) * BM);
-    };
-    EpiCursor cur = {0, 0}, pre = {0, 0};  // block being processed / next block whose residual has not been requested
-    int q_pre = 0;
-    const uint32_t sync2_bar = smem_u32(sync2_bar_p);
-    if (leader && has_res)
-        for (; q_pre < min(2, nbuf) && pre.j < my_tiles; q_pre++) {
-            load_residual(pre, q_pre);
-            advance(pre);
-        }
+    const EpiWalk<BN> walk(p, grp, total_tiles);
+    EpiCursor cur = {0, 0};
+    int b = 0;            // tile of the current block, and how often the ring of tiles has wrapped
+    uint32_t wrap = 0;
     bool alive = true;
-    int q = 0;
-    for (; cur.j < my_tiles && alive; q++) {
-        const int lt = grp + cur.j * ngrp, tile = first + cur.j * step;
-        const int m0 = (tile / p.n_tiles) * BM, n0 = (tile % p.n_tiles) * BN, nsub0 = n0 + cur.sb * 64;
+    while (cur.j < walk.my_tiles) {
+        const int lt = grp + cur.j * ngrp, tile = walk.tile(cur.j);
+        const int n0 = (tile % p.n_tiles) * BN, nsub0 = n0 + cur.sb * 64;
         const int ab = lt % NACC;
-        const bool last_block = cur.sb == blocks_of(cur.j) - 1;
-        uint8_t *tile_smem = tiles + (q % nbuf) * EPI_TILE_BYTES;
+        const bool last_block = cur.sb == walk.blocks_of(cur.j) - 1;
+        uint8_t *tile_smem = tiles + b * EPI_TILE_BYTES;
         if (cur.sb == 0) {
             if (!mbar_wait_bounded(smem_u32(&acc_full[ab]), (lt / NACC) & 1)) {
                 if (lane == 0) atomicExch(p.status, 2);
@@ -263,15 +257,14 @@ __device__ __forceinline__ void epilogue_tma(const ConvTcParams &p, const CUtens
             tc_fence_before();
             mbar_arrive(smem_u32(&acc_empty[ab]));
         }
-        if (has_res) {
-            if (!mbar_wait_bounded(smem_u32(&res_full[q % nbuf]), (q / nbuf) & 1)) {
-                if (lane == 0) atomicExch(p.status, 8);
-                *abort_flag = 1;
-                alive = false;
-            }
-            alive = __all_sync(0xffffffffu, alive);
-            if (!alive) break;
+        // the tile is ours once its previous store has read it out and, with a residual, the residual rows are in it
+        if (!mbar_wait_bounded(smem_u32(&avail[b]), wrap & 1)) {
+            if (lane == 0) atomicExch(p.status, 8);
+            *abort_flag = 1;
+            alive = false;
         }
+        alive = __all_sync(0xffffffffu, alive);
+        if (!alive) break;
         {
             uint8_t *row_smem = tile_smem + row * 128;
             const int rsw = row & 7;
@@ -286,46 +279,66 @@ __device__ __forceinline__ void epilogue_tma(const ConvTcParams &p, const CUtens
                 else epi_block<KIND, false, 0, false>(acc0, acc1, row_smem, rsw, nsub0, p);
             }
         }
-        fence_proxy_async_smem();  // this thread's rows must be visible to the copy engine
-        mbar_arrive(sync_bar);
-        if (!mbar_wait_bounded(sync_bar, q & 1)) {
-            if (lane == 0) atomicExch(p.status, 5);
+        fence_proxy_async_smem();  // this thread's row must be visible to the copy engine
+        mbar_arrive(smem_u32(&rows_ready[b]));
+        if (++b == nbuf) { b = 0; wrap++; }
+        walk.advance(cur);
+    }
+}
+
+// The agent of an epilogue group: one thread that owns the group's global-memory traffic.  It makes a tile available
+// to the group (arming the tile's barrier with the TMA load of the residual tile when one is fused), waits until all
+// 128 rows of a block are in its tile, hands the tile to a TMA store (which clips rows and channels beyond the tensor),
+// waits until the store has read the tile out and makes it available for the block nbuf ahead.
+template <int BN>
+__device__ __forceinline__ void epilogue_agent(const ConvTcParams &p, const CUtensorMap *tmY, const CUtensorMap *tmR, int grp,
+                                               uint8_t *tiles, uint64_t *rows_ready, uint64_t *avail,
+                                               volatile int *abort_flag, int total_tiles)
+{
+    const int nbuf = p.epi_bufs;
+    const bool has_res = p.res != nullptr;
+    const EpiWalk<BN> walk(p, grp, total_tiles);
+    auto make_available = [&](const EpiCursor &c, int b) {
+        if (has_res) {
+            const int tile = walk.tile(c.j);
+            mbar_arrive_expect_tx(smem_u32(&avail[b]), EPI_TILE_BYTES);
+            tma_load_2d(smem_u32(tiles + b * EPI_TILE_BYTES), tmR, smem_u32(&avail[b]), (tile % p.n_tiles) * BN + c.sb * 64,
+                        (tile / p.n_tiles) * BM);
+        } else
+            mbar_arrive(smem_u32(&avail[b]));
+    };
+    EpiCursor cur = {0, 0}, pre = {0, 0};  // block whose rows are awaited / next block to make a tile available for
+    int q_pre = 0;
+    for (; q_pre < nbuf && pre.j < walk.my_tiles; q_pre++) {
+        make_available(pre, q_pre);
+        walk.advance(pre);
+    }
+    int b = 0, q = 0;
+    uint32_t wrap = 0;
+    bool alive = true;
+    for (; cur.j < walk.my_tiles; q++) {
+        const int tile = walk.tile(cur.j);
+        if (!mbar_wait_bounded(smem_u32(&rows_ready[b]), wrap & 1)) {
+            atomicExch(p.status, 5);
             *abort_flag = 1;
             alive = false;
+            break;
         }
-        alive = __all_sync(0xffffffffu, alive);
-        if (!alive) break;
-        if (leader) {
-            tma_store_2d(tmY, smem_u32(tile_smem), nsub0, m0);
-            bulk_commit_group();
-            // the tile that the next prefetched block will use must have been read out by its previous store
-            if (nbuf >= 3) bulk_wait_group_read<1>();
-            else bulk_wait_group_read<0>();
-            if (has_res && pre.j < my_tiles) {
-                load_residual(pre, q_pre++);
-                advance(pre);
-            }
+        tma_store_2d(tmY, smem_u32(tiles + b * EPI_TILE_BYTES), (tile % p.n_tiles) * BN + cur.sb * 64, (tile / p.n_tiles) * BM);
+        bulk_commit_group();
+        bulk_wait_group_read<0>();
+        if (pre.j < walk.my_tiles) {
+            make_available(pre, b);
+            walk.advance(pre);
+            q_pre++;
         }
-        __syncwarp();
-        if (nbuf == 1) {
-            // a single tile: nobody may write the next block into it before the leader has seen this store read it out
-            mbar_arrive(sync2_bar);
-            if (!mbar_wait_bounded(sync2_bar, q & 1)) {
-                if (lane == 0) atomicExch(p.status, 7);
-                *abort_flag = 1;
-                alive = false;
-            }
-            alive = __all_sync(0xffffffffu, alive);
-            if (!alive) break;
-        }
-        advance(cur);
+        if (++b == nbuf) { b = 0; wrap++; }
+        walk.advance(cur);
     }
-    if (leader) {
-        bulk_wait_group<0>();
-        // residual loads still in flight after an early exit must land before the CTA may leave
-        if (has_res)
-            for (int k = alive ? q_pre : q; k < q_pre; k++) mbar_wait_bounded(smem_u32(&res_full[k % nbuf]), (k / nbuf) & 1);
-    }
+    bulk_wait_group<0>();
+    // after an early exit, residual loads still in flight must land before the CTA may leave
+    if (!alive && has_res)
+        for (int k = q; k < q_pre; k++) mbar_wait_bounded(smem_u32(&avail[k % nbuf]), (k / nbuf) & 1);
 }
 
 template <int KIND, int BN, int STAGES>
@@ -352,9 +365,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
     uint8_t *stage_buf = sA + nst * L::STAGE_BYTES;
     uint64_t *full = bars, *empty = bars + MAX_STAGES;
     uint64_t *acc_full = bars + 2 * MAX_STAGES, *acc_empty = acc_full + 4;
-    uint64_t *stg_ready = acc_empty + 4, *stg_free = stg_ready + 3;  // one pair per epilogue group (staged epilogue)
-    uint64_t *res_full = stg_free + 3;                               // TMA epilogue: one per residual tile in flight
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(res_full + 9);
+    uint64_t *rows_ready = acc_empty + 4, *avail = rows_ready + 9;   // TMA epilogue: a pair per group and tile
+    uint64_t *stg_ready = rows_ready, *stg_free = rows_ready + 3;    // staged epilogue: a pair per group
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(avail + 9);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -369,11 +382,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
             mbar_init(smem_u32(&acc_full[b]), 1);
             mbar_init(smem_u32(&acc_empty[b]), 128);
         }
-        for (int g = 0; g < 3; g++) {
-            mbar_init(smem_u32(&stg_ready[g]), 128);
-            mbar_init(smem_u32(&stg_free[g]), 128);
+        for (int g = 0; g < 9; g++) {
+            mbar_init(smem_u32(&rows_ready[g]), 128);
+            mbar_init(smem_u32(&avail[g]), 1);
         }
-        for (int g = 0; g < 9; g++) mbar_init(smem_u32(&res_full[g]), 1);
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
@@ -395,15 +407,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp < 4) {
+    if (warp == 14) {
+        // ================================================================== epilogue agents (TMA epilogue only)
+        if constexpr (L::TMA_EPI)
+            if (lane < p.epi_groups)
+                epilogue_agent<BN>(p, &tmapY, &tmapR, lane, stage_buf + lane * p.epi_bufs * EPI_TILE_BYTES, rows_ready + lane * 3,
+                                   avail + lane * 3, abort_flag, total_tiles);
+        __syncwarp();
+    } else if (warp < 4) {
         // ================================================================== A producer (gather mode)
         if (p.a_tma) {
             // nothing to gather: these four warps are the third epilogue group
             if constexpr (L::TMA_EPI)
                 if (p.epi_groups == 3)
-                    epilogue_tma<KIND, BN, NACC>(p, &tmapY, &tmapR, 2, tid, warp, lane, tmem_base,
-                                                 stage_buf + 2 * p.epi_bufs * EPI_TILE_BYTES, acc_full, acc_empty, &stg_ready[2],
-                                                 &stg_free[2], res_full + 6, abort_flag, total_tiles);
+                    epilogue_tma<KIND, BN, NACC>(p, 2, warp, lane, tmem_base, stage_buf + 2 * p.epi_bufs * EPI_TILE_BYTES,
+                                                 acc_full, acc_empty, rows_ready + 6, avail + 6, abort_flag, total_tiles);
             goto done;
         }
         const int chunk = lane & 7;
@@ -570,9 +588,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
         const int grp = (warp - 6) >> 2;
         const int et = tid - 192 - grp * 128;  // 0..127 within the group
         if constexpr (L::TMA_EPI) {
-            epilogue_tma<KIND, BN, NACC>(p, &tmapY, &tmapR, grp, et, warp, lane, tmem_base,
-                                         stage_buf + grp * p.epi_bufs * EPI_TILE_BYTES, acc_full, acc_empty, &stg_ready[grp],
-                                         &stg_free[grp], res_full + grp * 3, abort_flag, total_tiles);
+            epilogue_tma<KIND, BN, NACC>(p, grp, warp, lane, tmem_base, stage_buf + grp * p.epi_bufs * EPI_TILE_BYTES, acc_full,
+                                         acc_empty, rows_ready + grp * 3, avail + grp * 3, abort_flag, total_tiles);
             goto done;
         }
         const int quad = warp & 3;             // TMEM lane quadrant this warp may read
