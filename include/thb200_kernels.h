@@ -158,6 +158,7 @@ int thb_conv_u8_fwd_static(const thb_conv_desc *d, const void *x, void *y, thb_s
 
 const char *thb_last_cuda_error(void);
 int thb_kernel_launch_count(void); /* launches issued through this ABI since load (bench bookkeeping) */
+void thb_count_launches(int n);    /* add launches that were replayed from a captured graph of calls to this ABI */
 
 #ifdef __cplusplus
 }

@@ -251,6 +251,9 @@ void THFloatTensor_set(THFloatTensor *tdst, THFloatTensor *tsrc);
 int THB200_SetPrecision(int mode);
 /* number of GPUs a converted network shards its batch over (1..8); read when a network is converted */
 int THB200_SetDevices(int ngpus);
+/* THProcessFloat cuts each GPU's batch slice into sub-batches so that the host-to-device copy of one runs under the
+ * kernels of the one before; 0 = chosen from the input size (default, also THB200_CHUNKS), 1 = off, up to 4 */
+int THB200_SetPipelineChunks(int chunks);
 /* pinned host memory for input batches, so that THProcessFloat's copies run at full PCIe speed */
 void *THB200_HostAlloc(size_t bytes);
 void THB200_HostFree(void *p);

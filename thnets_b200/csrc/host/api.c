@@ -63,6 +63,12 @@ int THB200_SetPrecision(int mode)
     g_half_mode = mode;
     return 0;
 }
+int THB200_SetPipelineChunks(int chunks)
+{
+    thb_set_pipeline_chunks(chunks);
+    return 0;
+}
+
 int THB200_SetDevices(int ngpus)
 {
     if (ngpus < 1 || ngpus > 8) return ERR_NOTIMPLEMENTED;

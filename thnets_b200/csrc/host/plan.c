@@ -118,6 +118,10 @@ typedef struct instance {
     shape out_shape;
     long out_count;
     float last_ms;
+    /* the planned launches as one CUDA graph: captured from the second forward on (the first runs them directly,
+     * which also sets every kernel's attributes), replayed with a single launch afterwards */
+    cudaGraphExec_t graph;
+    int runs, graph_state; /* graph_state: 0 not tried, 1 usable, -1 capture failed or switched off */
 } instance;
 
 struct thb_engine {
@@ -130,6 +134,11 @@ struct thb_engine {
     int built;
     int input_s2d; /* the network input is staged space-to-depth for a stride-2 first convolution */
     instance inst[8];
+    /* Host-input forwards are pipelined: the batch slice of each GPU is cut into `chunks` sub-batches, each with its own
+     * plan instance and stream on that GPU, so that the host-to-device copy of one sub-batch runs under the kernels of
+     * the one before it.  Built on the first such forward; chunk c of GPU g is pipe[g * chunks + c]. */
+    instance pipe[32];
+    int chunks, pipe_built, pipe_chunks;
     float *h_out;
     size_t h_out_bytes;
     float last_ms;
@@ -784,6 +793,7 @@ static void instance_free(instance *I)
     if (I->stream) cudaStreamSynchronize(I->stream);
     for (int i = 0; i < I->nallocs; i++) cudaFree(I->allocs[i]);
     for (int i = 0; i < I->nsteps; i++) free(I->steps[i].tmap);
+    if (I->graph) cudaGraphExecDestroy(I->graph);
     if (I->ev0) cudaEventDestroy(I->ev0);
     if (I->ev1) cudaEventDestroy(I->ev1);
     if (I->stream) cudaStreamDestroy(I->stream);
@@ -943,7 +953,36 @@ static int run_steps_ev(thb_engine *E, instance *I, cudaEvent_t *evs)
     return 0;
 }
 
-static int run_steps(thb_engine *E, instance *I) { return run_steps_ev(E, I, 0); }
+/* The launches of one forward on the instance's stream: directly the first time, from then on as a replay of the
+ * graph captured from them.  The uint8 engine changes kernel arguments every forward (dynamic input quantisation), so
+ * it always launches directly; so does THB200_NO_GRAPH=1 and the per-module profile mode. */
+static int run_steps(thb_engine *E, instance *I)
+{
+    if (I->graph_state == 0 && I->runs >= 1) {
+        const char *ng = getenv("THB200_NO_GRAPH");
+        I->graph_state = -1;
+        if (E->dtype != THB_U8 && !(ng && atoi(ng)) && !th_profile) {
+            cudaGraph_t g = 0;
+            if (cudaStreamBeginCapture(I->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+                const int rc = run_steps_ev(E, I, 0);
+                const cudaError_t ce = cudaStreamEndCapture(I->stream, &g);
+                if (!rc && ce == cudaSuccess && g && cudaGraphInstantiate(&I->graph, g, 0) == cudaSuccess) I->graph_state = 1;
+                if (g) cudaGraphDestroy(g);
+                cudaGetLastError();
+            }
+        }
+    }
+    I->runs++;
+    if (I->graph_state == 1 && !th_profile) {
+        if (cudaGraphLaunch(I->graph, I->stream) == cudaSuccess) {
+            thb_count_launches(I->nsteps);
+            return 0;
+        }
+        thb_set_error("graph launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        return -1;
+    }
+    return run_steps_ev(E, I, 0);
+}
 
 /* Per-launch device times of the planned forward on the first GPU (events around every launch on the launching
  * stream, averaged over `iters` passes).  kinds: 0 tensor-core/FFMA convolution, 1 GEMV, 2 everything else.
@@ -1010,6 +1049,7 @@ void thb_engine_destroy(thb_engine *E)
 {
     if (!E) return;
     for (int g = 0; g < 8; g++) instance_free(&E->inst[g]);
+    for (int g = 0; g < 32; g++) instance_free(&E->pipe[g]);
     thb_host_free_pinned(E->h_out);
     thb_model_release(E->model);
     free(E);
@@ -1026,7 +1066,9 @@ void thb_slice_batch(int N, int G, int g, int *offset, int *count)
 static int engine_build(thb_engine *E, int N, int C, int H, int W, int rank, int cp)
 {
     for (int g = 0; g < 8; g++) instance_free(&E->inst[g]);
+    for (int g = 0; g < 32; g++) instance_free(&E->pipe[g]);
     E->built = 0;
+    E->pipe_built = 0;
     E->N = N; E->C = C; E->H = H; E->W = W; E->rank = rank; E->cp = cp;
     int G = E->ngpus < N ? E->ngpus : N;
     if (G < 1) G = 1;
@@ -1054,6 +1096,34 @@ static int engine_build(thb_engine *E, int N, int C, int H, int W, int rank, int
         }
     }
     E->built = G;
+    /* sub-batches per GPU for pipelined host-input forwards: worth it once a slice's input copy takes about a
+     * millisecond; the uint8 engine needs the input range of the whole batch before any kernel can start */
+    const int per_gpu = N / G;
+    const double in_mb = (double)per_gpu * C * H * W * 4 / 1e6;
+    E->chunks = E->dtype == THB_U8 || in_mb < 32 ? 1 : per_gpu >= 128 ? 4 : per_gpu >= 32 ? 2 : 1;
+    const char *ce = getenv("THB200_CHUNKS");
+    if (ce) E->chunks = atoi(ce) < 1 || E->dtype == THB_U8 ? 1 : atoi(ce) > 4 ? 4 : atoi(ce);
+    if (E->chunks > per_gpu) E->chunks = 1;
+    return 0;
+}
+
+static int g_chunks_override; /* 0 = the engine's own choice */
+void thb_set_pipeline_chunks(int n) { g_chunks_override = n < 0 ? 0 : n > 4 ? 4 : n; }
+
+/* plan instances of the sub-batches (first pipelined forward of this shape with S sub-batches per GPU) */
+static int pipe_build(thb_engine *E, int S)
+{
+    const int G = E->built;
+    for (int g = 0; g < 32; g++) instance_free(&E->pipe[g]);
+    E->pipe_built = 0;
+    for (int g = 0; g < G; g++)
+        for (int c = 0; c < S; c++) {
+            int off, n;
+            thb_slice_batch(E->inst[g].slice_n, S, c, &off, &n);
+            if (instance_build(E, &E->pipe[g * S + c], E->inst[g].device, E->inst[g].slice_off + off, n)) return -1;
+        }
+    E->pipe_built = G * S;
+    E->pipe_chunks = S;
     return 0;
 }
 
@@ -1075,13 +1145,24 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
     if (!E->built || E->N != N || E->C != C || E->H != H || E->W != W || E->rank != rank || E->cp != cp) {
         if (engine_build(E, N, C, H, W, rank, cp)) return -1;
     }
-    const int G = E->built;
+    /* host float input: run the sub-batch instances so that copies and kernels overlap */
+    instance *set = E->inst;
+    int G = E->built;
+    int peer_gather = E->peer_gather;
+    int S = g_chunks_override ? g_chunks_override : E->chunks;
+    if (E->dtype == THB_U8 || S > E->inst[0].slice_n) S = 1;
+    if (x && S > 1) {
+        if ((!E->pipe_built || E->pipe_chunks != S) && pipe_build(E, S)) return -1;
+        set = E->pipe;
+        G = E->pipe_built;
+        peer_gather = 0;
+    }
     const size_t img_elems = (size_t)C * H * W;
     float q_sub = 0, q_mult = 0;
 
     /* stage the input slices */
     for (int g = 0; g < G; g++) {
-        instance *I = &E->inst[g];
+        instance *I = &set[g];
         CU(cudaSetDevice(I->device));
         if (x) {
             CU(cudaMemcpyAsync(I->d_in, x + (size_t)I->slice_off * img_elems, (size_t)I->slice_n * img_elems * sizeof(float),
@@ -1097,7 +1178,7 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
         if (!x) { thb_set_error("THProcessImages is not supported with Lowp"); return -1; }
         float lo = 0, hi = 0;
         for (int g = 0; g < G; g++) {
-            instance *I = &E->inst[g];
+            instance *I = &set[g];
             float mm[2];
             CU(cudaSetDevice(I->device));
             if (thb_minmax_normalized(I->d_in, I->slice_n, C, H, W, mean, std, I->d_minmax, I->stream)) return -1;
@@ -1108,11 +1189,11 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
         }
         q_sub = lo;
         q_mult = hi - lo > 0 ? (float)(255.0 / (hi - lo)) : 0;
-        for (int g = 0; g < G; g++) set_dynamic_quant(&E->inst[g], q_sub, q_mult);
+        for (int g = 0; g < G; g++) set_dynamic_quant(&set[g], q_sub, q_mult);
     }
 
     long total = 0;
-    for (int g = 0; g < G; g++) total += E->inst[g].out_count;
+    for (int g = 0; g < G; g++) total += set[g].out_count;
     if ((size_t)total * sizeof(float) > E->h_out_bytes) {
         thb_host_free_pinned(E->h_out);
         E->h_out_bytes = (size_t)total * sizeof(float);
@@ -1121,7 +1202,7 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
     }
 
     for (int g = 0; g < G; g++) {
-        instance *I = &E->inst[g];
+        instance *I = &set[g];
         CU(cudaSetDevice(I->device));
         int rc;
         void *in_ptr = bufptr(I, I->in_val.buf, 0, E->dtype);
@@ -1143,24 +1224,24 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
         const value *ov = &I->out_val;
         float inv = ov->q_mult ? (float)(1.0 / ov->q_mult) : 0;
         long off = 0;
-        for (int k = 0; k < g; k++) off += E->inst[k].out_count;
+        for (int k = 0; k < g; k++) off += set[k].out_count;
         float *dst_dev = I->d_out;
         if (thb_postprocess(bufptr(I, ov->buf, ov->coff, E->dtype), E->dtype, ov->s.N, ov->s.H, ov->s.W, ov->s.C, ov->ld,
                             ov->q_sub, inv, dst_dev, I->stream)) { thb_set_error("postprocess launch failed"); return -1; }
         CU(cudaEventRecord(I->ev1, I->stream));
-        if (G > 1 && E->peer_gather && g > 0) {
+        if (G > 1 && peer_gather && g > 0) {
             /* gather by peer copy into GPU 0's result buffer; GPU 0 sends the whole result to the host */
-            CU(cudaMemcpyPeerAsync(E->inst[0].d_out + off, E->inst[0].device, I->d_out, I->device,
+            CU(cudaMemcpyPeerAsync(set[0].d_out + off, set[0].device, I->d_out, I->device,
                                    (size_t)I->out_count * sizeof(float), I->stream));
-        } else if (!(G > 1 && E->peer_gather)) {
+        } else if (!(G > 1 && peer_gather)) {
             CU(cudaMemcpyAsync(E->h_out + off, I->d_out, (size_t)I->out_count * sizeof(float), cudaMemcpyDeviceToHost, I->stream));
         }
     }
     float ms_max = 0;
     for (int g = G - 1; g >= 0; g--) {
-        instance *I = &E->inst[g];
+        instance *I = &set[g];
         CU(cudaSetDevice(I->device));
-        if (g == 0 && G > 1 && E->peer_gather)
+        if (g == 0 && G > 1 && peer_gather)
             CU(cudaMemcpyAsync(E->h_out, I->d_out, (size_t)total * sizeof(float), cudaMemcpyDeviceToHost, I->stream));
         CU(cudaStreamSynchronize(I->stream));
         float ms = 0;
@@ -1177,7 +1258,7 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
     }
     E->last_ms = ms_max;
 
-    shape os = E->inst[0].out_shape;
+    shape os = set[0].out_shape;
     res->data = E->h_out;
     res->count = total;
     int rk = os.rank;

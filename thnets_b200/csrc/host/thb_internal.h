@@ -70,6 +70,7 @@ typedef struct thb_result {
     int ndim;
     long size[4];
 } thb_result;
+void thb_set_pipeline_chunks(int n);
 int thb_engine_forward(thb_engine *e, float *x, unsigned char **images, int stride, int bgr, int cp, int N, int C,
                        int H, int W, int input_rank, const float *mean, const float *std, int inplace, thb_result *res);
 float thb_engine_last_ms(thb_engine *e);

@@ -24,6 +24,8 @@ extern "C" int thb_note_launch(cudaError_t e, const char *what)
 }
 extern "C" const char *thb_last_cuda_error(void) { return g_last_error; }
 extern "C" int thb_kernel_launch_count(void) { return g_launches; }
+// launches replayed through a captured graph are counted by whoever replays it
+extern "C" void thb_count_launches(int n) { g_launches += n; }
 
 static inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 

@@ -1037,15 +1037,16 @@ extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, t
     // anything else whose taps are whole 128-byte channel slabs goes through im2col-mode TMA, within the limits of
     // a rank-4 descriptor: box corners in [-128, 127], traversal strides up to 8, tap offsets below 256
     const int bke = 128 / es;
-    const bool im2col_ok = !p.a_tma && d->dH <= 8 && d->dW <= 8 && d->padH <= 127 && d->padW <= 127 &&
+    const bool im2col_ok = d->dH <= 8 && d->dW <= 8 && d->padH <= 127 && d->padW <= 127 &&
                            d->kH <= 256 && d->kW <= 256 && d->oH >= 1 && d->oW >= 1 &&
                            box_corner_ok((d->oH - 1) * d->dH + 1 - d->H - d->padH, d->H + d->padH) &&
                            box_corner_ok((d->oW - 1) * d->dW + 1 - d->W - d->padW, d->W + d->padW);
-    if (im2col_ok && d->Cin_pad % bke == 0 && d->Ktot_pad == d->kH * d->kW * d->Cin_pad) p.a_tma = 2;
+    if (!p.a_tma && im2col_ok && d->Cin_pad % bke == 0 && d->Ktot_pad == d->kH * d->kW * d->Cin_pad) p.a_tma = 2;
     p.slabs = d->Cin_pad / bke;
     if (const char *e = getenv("THB200_A_TMA")) {
         const int allow = atoi(e);  // 0: gather only, 1: plain-matrix TMA only, 2 (default): im2col too
         if (p.a_tma > allow) p.a_tma = 0;
+        if (allow == 22 && p.a_tma == 1) p.a_tma = 2;  // experiment: im2col mode for a plain matrix too
     }
     if (p.a_tma) {
         ta = activation_tmap(d, x, p.a_tma);
