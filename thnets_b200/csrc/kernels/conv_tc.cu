@@ -51,6 +51,7 @@ struct ConvTcParams {
     int tail_start, relu_thr, relu_val;
     int a_tma;   // 1: 1x1 stride-1 convolution, the activation operand is a plain [pixels][Cin] matrix loaded by 2-D TMA;
                  // 2: whole 128-byte channel slabs per tap, loaded by im2col-mode TMA (any kernel size, stride, padding)
+    int pdl;                   // launched with programmatic stream serialisation
     int stages;                // TMA epilogue: pipeline stages (the launcher sizes them against the epilogue tiles)
     int epi_groups, epi_bufs;  // TMA epilogue: groups at work (2 or 3) and 16 KB tiles each of them cycles through
     int slabs;   // a_tma == 2: 128-byte channel slabs per tap (K block kb = tap * slabs + slab)
@@ -406,6 +407,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Programmatic dependent launch: this grid may have been started while the previous kernel of the stream was
+    // still draining, so that the set-up above overlaps its tail.  Nothing before this point touches memory that
+    // kernel could write or read; from here on it must have finished.  The next kernel may start its own set-up as
+    // soon as this grid's CTAs leave their SMs.
+    if (p.pdl) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
 
     if (warp == 14) {
         // ================================================================== epilogue agents (TMA epilogue only)
@@ -832,8 +841,24 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
         if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
         if (!p.a_tma) p.stages = STAGES;  // the gather's cp.async depth is tied to the compile-time count
     }
-    kern<<<grid, NTHREADS, smem, st>>>(*tm.w, *tm.a, tm.y ? *tm.y : *tm.w, tm.r ? *tm.r : *tm.w, p);
-    return THB_LAUNCH_CHECK("conv_tc_kernel");
+    static int use_pdl = -1;
+    if (use_pdl < 0) {
+        const char *e = getenv("THB200_PDL");
+        use_pdl = e ? atoi(e) : 1;
+    }
+    p.pdl = use_pdl;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NTHREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl ? 1 : 0;
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, kern, *tm.w, *tm.a, tm.y ? *tm.y : *tm.w, tm.r ? *tm.r : *tm.w, p);
+    return thb_note_launch(le != cudaSuccess ? le : cudaGetLastError(), "conv_tc_kernel");
 }
 
 template <int KIND>
