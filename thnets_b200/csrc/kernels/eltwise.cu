@@ -284,6 +284,55 @@ __global__ void pool_kernel(const T *x, int N, int H, int W, int C, int x_ld, in
     Vec<T>::store(y + (size_t)opix * y_ld + cv * VN, acc);
 }
 
+// 3x3 stride-2 max pooling of a 16-bit type, without a conversion and with each input row reduced once: a thread owns one
+// output column of one 8-channel group and walks down a strip of output rows; of the three input rows of a window the
+// first is the last one of the window above, so every step reads two new rows of three pixels, takes their
+// horizontal maxima, and combines them with the carried one.  Neighbouring threads read neighbouring pixels, so the
+// shared column of adjacent windows is served by L1.
+template <typename T2> __device__ __forceinline__ uint4 max8(const uint4 &a, const uint4 &b)
+{
+    uint4 r;
+    const T2 *pa = reinterpret_cast<const T2 *>(&a), *pb = reinterpret_cast<const T2 *>(&b);
+    T2 *pr = reinterpret_cast<T2 *>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; i++) pr[i] = __hmax2(pa[i], pb[i]);
+    return r;
+}
+template <typename T2>
+__global__ void maxpool3s2_kernel(const uint4 *__restrict__ x, int N, int H, int W, int cvecs, int x_ld8, int padH, int padW,
+                                  int oH, int oW, int strip, int nstrips, uint32_t neg_inf2, uint4 *__restrict__ y, int y_ld8)
+{
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)N * nstrips * oW * cvecs) return;
+    const int cv = (int)(idx % cvecs);
+    long r = idx / cvecs;
+    const int ow = (int)(r % oW);
+    r /= oW;
+    const int st = (int)(r % nstrips);
+    const long n = r / nstrips;
+    const uint4 ninf = make_uint4(neg_inf2, neg_inf2, neg_inf2, neg_inf2);
+    const int iw0 = ow * 2 - padW;
+    const uint4 *img = x + (size_t)n * H * W * x_ld8 + cv;
+    auto hrow = [&](int ih) {
+        uint4 m = ninf;
+        if ((unsigned)ih < (unsigned)H) {
+            const uint4 *row = img + (size_t)ih * W * x_ld8;
+#pragma unroll
+            for (int k = 0; k < 3; k++)
+                if ((unsigned)(iw0 + k) < (unsigned)W) m = max8<T2>(m, __ldg(row + (size_t)(iw0 + k) * x_ld8));
+        }
+        return m;
+    };
+    const int oh0 = st * strip, oh1 = min(oH, oh0 + strip);
+    uint4 carried = hrow(oh0 * 2 - padH);
+    uint4 *out = y + ((size_t)n * oH * oW + ow) * y_ld8 + cv;
+    for (int oh = oh0; oh < oh1; oh++) {
+        const uint4 r1 = hrow(oh * 2 - padH + 1), r2 = hrow(oh * 2 - padH + 2);
+        out[(size_t)oh * oW * y_ld8] = max8<T2>(max8<T2>(carried, r1), r2);
+        carried = r2;
+    }
+}
+
 // ---- y = act(x*scale[c] + shift[c]) ----------------------------------------------------------------------
 template <typename T>
 __global__ void affine_act_kernel(const T *x, long pixels, int C, int x_ld, const float *scale, const float *shift,
@@ -541,6 +590,21 @@ int thb_maxpool(int dtype, const void *x, int N, int H, int W, int C, int x_ld, 
     const int al = thb_channel_align(dtype);
     const long total = (long)N * oH * oW * ((C + al - 1) / al);
     if (total == 0) return THB_OK;
+    if ((dtype == THB_F16 || dtype == THB_BF16) && kH == 3 && kW == 3 && dH == 2 && dW == 2 && x_ld % 8 == 0 && y_ld % 8 == 0) {
+        const int cvecs = (C + 7) / 8;
+        // strips of output rows: long enough to amortise the carried row, short enough to fill the GPU
+        int strip = oH;
+        while (strip > 4 && (long)N * ((oH + strip - 1) / strip) * oW * cvecs < 8L * 148 * 256) strip = (strip + 1) / 2;
+        const int nstrips = (oH + strip - 1) / strip;
+        const long items = (long)N * nstrips * oW * cvecs;
+        if (dtype == THB_F16)
+            maxpool3s2_kernel<__half2><<<nblocks(items), 256, 0, (cudaStream_t)s>>>(
+                (const uint4 *)x, N, H, W, cvecs, x_ld / 8, padH, padW, oH, oW, strip, nstrips, 0xFC00FC00u, (uint4 *)y, y_ld / 8);
+        else
+            maxpool3s2_kernel<__nv_bfloat162><<<nblocks(items), 256, 0, (cudaStream_t)s>>>(
+                (const uint4 *)x, N, H, W, cvecs, x_ld / 8, padH, padW, oH, oW, strip, nstrips, 0xFF80FF80u, (uint4 *)y, y_ld / 8);
+        return THB_LAUNCH_CHECK("maxpool3s2_kernel");
+    }
     DISPATCH_ANY_DTYPE(dtype, (pool_kernel<T, true><<<nblocks(total), 256, 0, (cudaStream_t)s>>>(
                                   (const T *)x, N, H, W, C, x_ld, kH, kW, dH, dW, padH, padW, oH, oW, 0, (T *)y, y_ld)));
     return THB_LAUNCH_CHECK("pool_kernel<max>");
