@@ -83,6 +83,11 @@ typedef struct thb_conv_desc {
     const thb_tmap *tmap; /* tensor-core dtypes: TMA descriptor of w (host pointer) */
     int Cin_pad, Ktot_pad, Cout_pad, BN;
     int *status;          /* device word: set non-zero when a bounded wait gave up */
+    /* Rows stored with their horizontal zero padding (0, 0: plain [N][H][W][ld] input).  in_row_pitch > 0: row h of
+     * image n starts at pixel (n*H + h)*in_row_pitch of x and holds in_pad_left zero pixels, the W real pixels, then
+     * at least kW - 1 - padW zero pixels; in_pad_left must equal padW.  When a row's kW taps then fill exactly
+     * 128 bytes (kW * Cin_pad elements) and dW is 1, the tensor-core path fetches all of them with one copy. */
+    int in_row_pitch, in_pad_left;
 } thb_conv_desc;
 
 int thb_channel_align(int dtype);               /* 4 (F32), 8 (F16/BF16), 16 (U8) */
@@ -108,6 +113,12 @@ int thb_preprocess(const float *x_nchw, float *x_inplace, int N, int C, int H, i
  * (2h + ph, 2w + pw) of channel c -- the input layout of a stride-2 first convolution rewritten as stride 1 */
 int thb_preprocess_s2d(const float *x_nchw, float *x_inplace, int N, int C, int H, int W, const float *mean3,
                        const float *std3, int dtype, void *y, int y_ld, thb_stream s);
+/* the same into rows of row_pitch >= pad_left + W/2 pixels that start with pad_left zero pixels and end in zero
+ * pixels (the layout thb_conv_desc.in_row_pitch describes); every pixel of y, padding included, is written */
+int thb_preprocess_s2d_padded(const float *x_nchw, float *x_inplace, int N, int C, int H, int W, const float *mean3,
+                              const float *std3, int dtype, void *y, int y_ld, int row_pitch, int pad_left, thb_stream s);
+/* 1 when the device and driver accept the single-copy row fetch described at thb_conv_desc.in_row_pitch */
+int thb_conv_padded_rows_supported(int dtype);
 /* u8 HWC images (already on the device, row stride `stride`) -> normalised NHWC dtype (thapi.c:20-46) */
 int thb_preprocess_images(const unsigned char *img, int N, int H, int W, int stride, int cp, int bgr,
                           const float *mean3, const float *std3, int dtype, void *y, int y_ld, thb_stream s);

@@ -80,6 +80,36 @@ def test_conv_plain(lib, G, oracle, dtype, case):
     assert pad.numel() == 0 or float(pad.float().abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("gather_only", [False, True])
+@pytest.mark.parametrize("crop", [0, 1])
+def test_conv_f16_rows_stored_with_padding(lib, G, oracle, gather_only, crop, monkeypatch):
+    """Input rows stored with their horizontal zero padding (thb_conv_desc.in_row_pitch): four taps of 16 channels fill
+    one 128-byte K block, so one copy fetches a kernel row.  crop = 1 drops the last output row and column, as the
+    space-to-depth rewrite of a stride-2 first layer does.  The gather path must read the same layout."""
+    case = (3, 12, 21, 19, 72, 4, 1, 2)
+    n, cin, h, w, cout, k, s, p = case
+    x, wt = _conv_inputs(case, 9, True)
+    bias = np.random.default_rng(2).standard_normal(cout).astype(np.float32)
+    ref = oracle.conv2d(x, wt, bias, (s, s), (p, p))
+    if crop:
+        ref = ref[:, :, :-1, :-1]
+    assert lib.thb_conv_padded_rows_supported(K.THB_F16) == 1
+    if gather_only:
+        monkeypatch.setenv("THB200_A_TMA", "0")
+    conv = G.Conv(lib, K.THB_F16, x.shape, wt, (s, s), (p, p))
+    conv.set_affine(None, bias)
+    d = conv.d
+    d.oH, d.oW = ref.shape[2], ref.shape[3]
+    pitch = p + w + (k - 1 - p) + 2
+    ld = d.in_ld
+    buf = np.zeros((n, h, pitch, ld), np.float32)
+    buf[:, :, p:p + w, :cin] = np.transpose(x, (0, 2, 3, 1))
+    xt = torch.from_numpy(buf).cuda().half()
+    d.in_row_pitch, d.in_pad_left = pitch, p
+    got = G.from_nhwc(conv.run(xt, fill=3.0), cout)
+    assert G.rel_err(got, ref) < 1e-2, G.rel_err(got, ref)
+
+
 @pytest.mark.parametrize("bn_tile", [32, 64, 128, 256])
 def test_conv_f16_all_tile_widths(lib, G, oracle, bn_tile):
     case = (2, 72, 14, 14, 264, 3, 1, 1)

@@ -63,6 +63,7 @@ typedef struct {
     shape s;
     float q_sub, q_mult; /* u8 mode */
     int q_dyn;           /* u8 mode: the scale is measured per forward (network input) */
+    int row_pitch, pad_left; /* rows stored with horizontal zero padding (the staged network input only), else 0 */
 } value;
 
 typedef struct {
@@ -423,6 +424,7 @@ static int plan_gemm_group(planner *P, int i)
     s->aux_buf = csum_buf;
     d->dtype = dtype;
     d->N = is.N; d->H = H; d->W = W; d->Cin = Cin; d->in_ld = in_ld;
+    d->in_row_pitch = in->row_pitch; d->in_pad_left = in->pad_left;
     d->kH = kH; d->kW = kW; d->dH = n->dH; d->dW = n->dW; d->padH = n->padH; d->padW = n->padW;
     d->self_coef = 1.f; d->res_coef = 0.f; d->relu_thr = -1;
     int Cp_out = ru(n->Cout, al);
@@ -842,6 +844,20 @@ static int instance_build(thb_engine *E, instance *I, int device, int slice_off,
         if (E->input_s2d) { in.C = 4 * E->C; in.H = E->H / 2; in.W = E->W / 2; }
     }
     materialise(&P, &P.val[0], in);
+    if (E->input_s2d) {
+        /* When the rewritten convolution's kernel row fills one 128-byte K block, store the staged rows with their
+         * zero padding: one copy then fetches a whole kernel row of an output pixel (thb_conv_desc.in_row_pitch). */
+        thb_node *c1 = &M->nodes[1];
+        const int padW = (c1->padW + 1) / 2, kW = (c1->kW - 1 - c1->padW) / 2 + padW + 1;
+        const char *off = getenv("THB200_NO_PADDED_ROWS");
+        value *v = &P.val[0];
+        if (kW * v->ld * esize_of(E->dtype) == 128 && thb_conv_padded_rows_supported(E->dtype) && !(off && atoi(off))) {
+            v->pad_left = padW;
+            v->row_pitch = (padW + in.W + kW - 1 + 3) & ~3;
+            I->nbufs--; /* re-create the buffer at its padded size */
+            v->buf = new_buf(&P, (size_t)in.N * in.H * v->row_pitch * v->ld * esize_of(E->dtype));
+        }
+    }
     P.val[0].q_dyn = E->dtype == THB_U8;
     int rc = 0;
     for (int i = 1; i < M->nnodes && !rc; i++) {
@@ -1207,8 +1223,9 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
         int rc;
         void *in_ptr = bufptr(I, I->in_val.buf, 0, E->dtype);
         if (x && E->input_s2d)
-            rc = thb_preprocess_s2d(I->d_in, inplace ? I->d_in : 0, I->slice_n, C, H, W, mean, std, E->dtype, in_ptr,
-                                    I->in_val.ld, I->stream);
+            rc = thb_preprocess_s2d_padded(I->d_in, inplace ? I->d_in : 0, I->slice_n, C, H, W, mean, std, E->dtype, in_ptr,
+                                           I->in_val.ld, I->in_val.row_pitch ? I->in_val.row_pitch : W / 2,
+                                           I->in_val.pad_left, I->stream);
         else if (x)
             rc = thb_preprocess(I->d_in, inplace ? I->d_in : 0, I->slice_n, C, H, W, mean, std, E->dtype, in_ptr, I->in_val.ld,
                                 q_sub, q_mult, I->stream);

@@ -123,6 +123,11 @@ extern "C" unsigned short thb_float_to_half_bits(float v, int bf16)
 extern "C" int thb_conv_fwd(const thb_conv_desc *d, const void *x, void *y, thb_stream s)
 {
     if (d->in_ld < d->Cin_pad) return THB_ERR_ARG;
+    if (d->in_row_pitch) {
+        // rows stored with their padding: tensor-core dtypes only
+        if (d->dtype == THB_F32) return THB_ERR_UNSUPPORTED;
+        if (d->in_pad_left != d->padW || d->in_row_pitch < d->W + d->kW - 1) return THB_ERR_ARG;
+    }
     if (d->dtype == THB_F32) return thb_conv_fwd_simt(d, x, y, s);
     return thb_conv_fwd_tc(d, x, y, s);
 }

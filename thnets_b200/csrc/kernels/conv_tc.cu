@@ -54,6 +54,9 @@ struct ConvTcParams {
     int pdl;                   // launched with programmatic stream serialisation
     int stages;                // TMA epilogue: pipeline stages (the launcher sizes them against the epilogue tiles)
     int epi_groups, epi_bufs;  // TMA epilogue: groups at work (2 or 3) and 16 KB tiles each of them cycles through
+    int row_pitch, pad_left;  // gather: pixels between input rows, zero pixels in front of each row (W, 0 when plain)
+    int tma_kw, tma_padw;     // a_tma == 2: taps per kernel row that need a load of their own, and the padding the
+                              // descriptor's coordinates see (1, 0 when one copy fetches a padded row's kW taps)
     int slabs;   // a_tma == 2: 128-byte channel slabs per tap (K block kb = tap * slabs + slab)
     int use_l1;  // gather through L1: neighbouring taps of one tile re-read the same input pixels
     int *acc_out;
@@ -449,7 +452,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     if (pm < p.P) {
                         ih0[j] = oh * p.dH - p.padH;
                         iw0[j] = ow * p.dW - p.padW;
-                        pixbase[j] = n * p.H * p.W;
+                        pixbase[j] = n * p.H * p.row_pitch + p.pad_left;
                     } else {
                         ih0[j] = iw0[j] = 0;
                         pixbase[j] = -1;
@@ -485,7 +488,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     const int r = warp * 32 + j * 4 + (lane >> 3);
                     const int ih = ih0[j] + dh, iw = iw0[j] + dw;
                     const bool ok = ki >= 0 && pixbase[j] >= 0 && (unsigned)ih < (unsigned)p.H && (unsigned)iw < (unsigned)p.W;
-                    const uint8_t *src = ok ? p.x + ((size_t)(pixbase[j] + ih * p.W + iw) * p.in_ld) * ES + coff : p.x;
+                    const uint8_t *src = ok ? p.x + ((size_t)(pixbase[j] + ih * p.row_pitch + iw) * p.in_ld) * ES + coff : p.x;
                     const uint32_t dst = a_stage + r * 128 + ((chunk ^ (r & 7)) << 4);
                     if (p.use_l1) cp_async16_ca(dst, src, ok ? 16u : 0u);
                     else cp_async16(dst, src, ok ? 16u : 0u);
@@ -518,7 +521,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     const int rem = m0 - in * p.oHW;
                     const int oh = rem / p.oW;
                     ih = oh * p.dH - p.padH;
-                    iw = (rem - oh * p.oW) * p.dW - p.padW;
+                    iw = (rem - oh * p.oW) * p.dW - p.tma_padw;
                 }
                 for (int kb = 0; kb < p.nkb; kb++, it++) {
                     const int s = ring_s;
@@ -539,7 +542,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                                            (uint16_t)tap_w, (uint16_t)tap_h);
                         if (++slab == p.slabs) {
                             slab = 0;
-                            if (++tap_w == p.kW) { tap_w = 0; tap_h++; }
+                            if (++tap_w == p.tma_kw) { tap_w = 0; tap_h++; }
                         }
                     } else
                         mbar_arrive_expect_tx(smem_u32(&full[s]), B_STAGE_BYTES);
@@ -945,7 +948,7 @@ const CUtensorMap *matrix_tmap(const void *x, long rows, int cols, int ld, int d
 // mode 1: the plain [pixels][Cin] matrix of a 1x1 stride-1 convolution; mode 2: im2col over {C, W, H, N}.
 struct ATmapEntry {
     const void *x;
-    int mode, N, H, W, cin_pad, in_ld, dtype, geom[6];
+    int mode, N, H, W, cin_pad, in_ld, dtype, geom[8];
     alignas(64) CUtensorMap map;
 };
 const CUtensorMap *activation_tmap(const thb_conv_desc *d, const void *x, int mode)
@@ -954,7 +957,7 @@ const CUtensorMap *activation_tmap(const thb_conv_desc *d, const void *x, int mo
         return matrix_tmap(x, (long)d->N * d->H * d->W, d->Cin_pad, d->in_ld, d->dtype, d->dtype == THB_U8 ? 128 : 64);
     static ATmapEntry cache[512];
     static int used = 0, next = 0;
-    const int geom[6] = {d->kH, d->kW, d->dH, d->dW, d->padH, d->padW};
+    const int geom[8] = {d->kH, d->kW, d->dH, d->dW, d->padH, mode == 3 ? d->in_row_pitch : d->padW, d->oH, d->oW};
     for (int i = 0; i < used; i++) {
         ATmapEntry &e = cache[i];
         if (e.x == x && e.mode == mode && e.N == d->N && e.H == d->H && e.W == d->W && e.cin_pad == d->Cin_pad &&
@@ -977,6 +980,18 @@ const CUtensorMap *activation_tmap(const thb_conv_desc *d, const void *x, int mo
                                  (cuuint64_t)d->H * d->W * d->in_ld * es};
         int lower[2] = {-d->padW, -d->padH};
         int upper[2] = {(d->oW - 1) * d->dW + 1 - d->W - d->padW, (d->oH - 1) * d->dH + 1 - d->H - d->padH};
+        if (mode == 3) {
+            // Rows stored with their zero padding, kW taps = 128 bytes, stride 1: "pixel" w of this tensor is the
+            // 128-byte window that starts at stored pixel w, i.e. the kW taps of output column w.  Windows overlap
+            // (the pixel stride is smaller than the window), there are oW of them per row, and no horizontal
+            // padding is left for the copy engine to supply.
+            dims[0] = (cuuint64_t)(128 / es);
+            dims[1] = (cuuint64_t)d->oW;
+            strides[1] = (cuuint64_t)d->in_row_pitch * d->in_ld * es;
+            strides[2] = (cuuint64_t)d->H * d->in_row_pitch * d->in_ld * es;
+            lower[0] = 0;
+            upper[0] = 0;
+        }
         cuuint32_t estr[4] = {1, (cuuint32_t)d->dW, (cuuint32_t)d->dH, 1};
         if (enc(&e.map, t, 4, const_cast<void *>(x), dims, strides, lower, upper, (cuuint32_t)(128 / es), (cuuint32_t)BM, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -986,7 +1001,7 @@ const CUtensorMap *activation_tmap(const thb_conv_desc *d, const void *x, int mo
         // the second 64-bit word) that makes the load misbehave; CUTLASS clears it for those drivers, and so do we.
         int drv = 0;
         if (cudaDriverGetVersion(&drv) == cudaSuccess && drv <= 13010 &&
-            (size_t)d->N * d->H * d->W * d->in_ld * es < 131072)
+            (size_t)d->N * d->H * (mode == 3 ? d->in_row_pitch : d->W) * d->in_ld * es < 131072)
             reinterpret_cast<uint64_t *>(&e.map)[1] &= ~(1ull << 21);
     }
     e.x = x; e.mode = mode; e.N = d->N; e.H = d->H; e.W = d->W; e.cin_pad = d->Cin_pad; e.in_ld = d->in_ld; e.dtype = d->dtype;
@@ -1021,6 +1036,25 @@ extern "C" int thb_conv_make_tmap(const thb_conv_desc *d, thb_tmap *out)
 
 // upper corner of the im2col bounding box: representable, and leaving a box of at least one position
 static bool box_corner_ok(int upper, int dim_plus_pad) { return upper >= -128 && upper <= 127 && dim_plus_pad + upper >= 1; }
+
+extern "C" int thb_conv_padded_rows_supported(int dtype)
+{
+    if (dtype != THB_F16 && dtype != THB_BF16 && dtype != THB_U8) return 0;
+    static int ok[4] = {-1, -1, -1, -1};
+    if (ok[dtype] < 0) {
+        // encode a descriptor of the overlapping-window kind over a dummy address: only the encoder's checks matter
+        if (cudaFree(0) != cudaSuccess) return 0;  // the encoder needs an initialised driver
+        thb_conv_desc d;
+        memset(&d, 0, sizeof(d));
+        const int es = dtype == THB_U8 ? 1 : 2;
+        d.dtype = dtype;
+        d.N = 2; d.H = 8; d.W = 8; d.kH = d.kW = 4; d.dH = d.dW = 1; d.padH = d.padW = 2; d.oH = d.oW = 8;
+        d.Cin_pad = d.in_ld = 32 / es;
+        d.in_row_pitch = 12; d.in_pad_left = 2;
+        ok[dtype] = activation_tmap(&d, reinterpret_cast<const void *>(uintptr_t(1) << 20), 3) != nullptr;
+    }
+    return ok[dtype];
+}
 
 extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, thb_stream s)
 {
@@ -1068,13 +1102,30 @@ extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, t
                            box_corner_ok((d->oW - 1) * d->dW + 1 - d->W - d->padW, d->W + d->padW);
     if (!p.a_tma && im2col_ok && d->Cin_pad % bke == 0 && d->Ktot_pad == d->kH * d->kW * d->Cin_pad) p.a_tma = 2;
     p.slabs = d->Cin_pad / bke;
+    p.tma_kw = d->kW;
+    p.tma_padw = d->padW;
+    p.row_pitch = d->in_row_pitch ? d->in_row_pitch : d->W;
+    p.pad_left = d->in_row_pitch ? d->in_pad_left : 0;
+    int tmap_mode = p.a_tma;
+    if (d->in_row_pitch) {
+        // padded rows: the plain-matrix and per-tap descriptors do not describe this layout; the single-copy row
+        // fetch does when a row's taps fill one 128-byte K block
+        p.a_tma = 0;
+        if (im2col_ok && d->dW == 1 && d->kW * d->Cin_pad == bke && d->Ktot_pad == d->kH * bke) {
+            p.a_tma = 2;
+            tmap_mode = 3;
+            p.slabs = 1;
+            p.tma_kw = 1;
+            p.tma_padw = 0;
+        }
+    }
     if (const char *e = getenv("THB200_A_TMA")) {
         const int allow = atoi(e);  // 0: gather only, 1: plain-matrix TMA only, 2 (default): im2col too
         if (p.a_tma > allow) p.a_tma = 0;
         if (allow == 22 && p.a_tma == 1) p.a_tma = 2;  // experiment: im2col mode for a plain matrix too
     }
     if (p.a_tma) {
-        ta = activation_tmap(d, x, p.a_tma);
+        ta = activation_tmap(d, x, tmap_mode);
         if (!ta) p.a_tma = 0, ta = &tm;
     }
     ConvTmaps maps = {&tm, ta, nullptr, nullptr};

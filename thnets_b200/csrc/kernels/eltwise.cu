@@ -135,16 +135,19 @@ __global__ void preprocess_kernel(const float *x, float *x_inplace, int N, int C
 // Space-to-depth variant for a stride-2 first convolution on very few channels: the 2x2 pixel block
 // (ph, pw) of channel c becomes channel (ph*2 + pw)*C + c of a half-resolution tensor, so the convolution
 // turns into a stride-1 one over 4*C channels whose gathered 16-byte chunks are fully used.
+// Rows may be stored row_pitch pixels apart with pad_left zero pixels in front (and zeros behind): every pixel of such
+// a row is written here, the padding as zeros.
 template <typename T>
 __global__ void preprocess_s2d_kernel(const float *x, float *x_inplace, int N, int C, int H, int W, float3 mean,
-                                      float3 std_, T *y, int y_ld)
+                                      float3 std_, T *y, int y_ld, int row_pitch, int pad_left)
 {
     constexpr int VN = Vec<T>::N;
     const int H2 = H / 2, W2 = W / 2;
-    const long pix = (long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (pix >= (long)N * H2 * W2) return;
-    const long n = pix / ((long)H2 * W2);
-    const int rem = (int)(pix - n * (long)H2 * W2), bh = rem / W2, bw = rem - bh * W2;
+    const long pix = (long)blockIdx.x * blockDim.x + threadIdx.x;  // over the stored (padded) pixels
+    if (pix >= (long)N * H2 * row_pitch) return;
+    const long n = pix / ((long)H2 * row_pitch);
+    const int rem = (int)(pix - n * (long)H2 * row_pitch), bh = rem / row_pitch, bw = rem - bh * row_pitch - pad_left;
+    const bool real = bw >= 0 && bw < W2;
     const float m[3] = {mean.x, mean.y, mean.z}, sd[3] = {std_.x, std_.y, std_.z};
     const int Cs = 4 * C, Cpad = (Cs + VN - 1) / VN * VN;
     for (int c0 = 0; c0 < Cpad; c0 += VN) {
@@ -153,7 +156,7 @@ __global__ void preprocess_s2d_kernel(const float *x, float *x_inplace, int N, i
         for (int i = 0; i < VN; i++) {
             const int cs = c0 + i;
             float val = 0.f;
-            if (cs < Cs) {
+            if (real && cs < Cs) {
                 const int blk = cs / C, c = cs - blk * C;
                 const long idx = ((n * C + c) * H + (2 * bh + (blk >> 1))) * W + 2 * bw + (blk & 1);
                 val = x[idx];
@@ -524,16 +527,22 @@ int thb_preprocess(const float *x, float *x_inplace, int N, int C, int H, int W,
     return THB_LAUNCH_CHECK("preprocess_kernel");
 }
 
-int thb_preprocess_s2d(const float *x, float *x_inplace, int N, int C, int H, int W, const float *mean3,
-                       const float *std3, int dtype, void *y, int y_ld, thb_stream s)
+int thb_preprocess_s2d_padded(const float *x, float *x_inplace, int N, int C, int H, int W, const float *mean3,
+                              const float *std3, int dtype, void *y, int y_ld, int row_pitch, int pad_left, thb_stream s)
 {
-    if ((H | W) & 1) return THB_ERR_ARG;
-    const long pix = (long)N * (H / 2) * (W / 2);
+    if (((H | W) & 1) || pad_left < 0 || row_pitch < pad_left + W / 2) return THB_ERR_ARG;
+    const long pix = (long)N * (H / 2) * row_pitch;
     if (pix == 0) return THB_OK;
     float3 m = make_float3(mean3[0], mean3[1], mean3[2]), sd = make_float3(std3[0], std3[1], std3[2]);
     DISPATCH_FLOAT_DTYPE(dtype, (preprocess_s2d_kernel<T><<<nblocks(pix), 256, 0, (cudaStream_t)s>>>(
-                                    x, x_inplace, N, C, H, W, m, sd, (T *)y, y_ld)));
+                                    x, x_inplace, N, C, H, W, m, sd, (T *)y, y_ld, row_pitch, pad_left)));
     return THB_LAUNCH_CHECK("preprocess_s2d_kernel");
+}
+
+int thb_preprocess_s2d(const float *x, float *x_inplace, int N, int C, int H, int W, const float *mean3,
+                       const float *std3, int dtype, void *y, int y_ld, thb_stream s)
+{
+    return thb_preprocess_s2d_padded(x, x_inplace, N, C, H, W, mean3, std3, dtype, y, y_ld, W / 2, 0, s);
 }
 
 int thb_preprocess_images(const unsigned char *img, int N, int H, int W, int stride, int cp, int bgr, const float *mean3,

@@ -46,6 +46,7 @@ class ConvDesc(C.Structure):
         ("w", C.c_void_p), ("kinfo", C.c_void_p), ("tmap", C.c_void_p),
         ("Cin_pad", C.c_int), ("Ktot_pad", C.c_int), ("Cout_pad", C.c_int), ("BN", C.c_int),
         ("status", C.c_void_p),
+        ("in_row_pitch", C.c_int), ("in_pad_left", C.c_int),
     ]
 
 
