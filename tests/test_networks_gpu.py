@@ -142,3 +142,65 @@ def test_process_images_matches_float_path(th, oracle, tmp_path):
         ref = oracle.run(plain, dst)
         assert rel_err(out, ref.ravel()) < 1e-4
     th.free_network(h)
+
+
+def _convert(th, g, kind, tmp_path, name, mode):
+    h = _load(th, g, kind, tmp_path, name)
+    th.lib.THB200_SetPrecision(mode)
+    hc = th.lib.THCreateCudaNetwork(h)
+    th.lib.THB200_SetPrecision(0)
+    assert hc, th.lib.THB200_LastErrorString()
+    th.free_network(h)
+    return hc
+
+
+@pytest.mark.parametrize("chunks", [2, 3, 4])
+def test_pipelined_sub_batches_give_the_same_result(th, oracle, tmp_path, chunks):
+    """THProcessFloat may cut the batch into sub-batches whose copies overlap the kernels of the previous one: every
+    image is computed by the same kernels in the same order, so the result is identical bit for bit."""
+    g = fx.resnet18(width=0.25, size=64, classes=10)
+    x = g.make_input(9)
+    hc = _convert(th, g, "py", tmp_path, "r18p", 1)
+    try:
+        th.lib.THB200_SetPipelineChunks(1)
+        whole, _, _ = th.process_float(hc, x)
+        th.lib.THB200_SetPipelineChunks(chunks)
+        for _ in range(3):   # direct launches, then graph capture, then graph replay
+            cut, _, _ = th.process_float(hc, x)
+            assert np.array_equal(whole, cut)
+    finally:
+        th.lib.THB200_SetPipelineChunks(0)
+    assert rel_err(whole, oracle.run(g, x).ravel()) < TOL[1]
+    th.free_network(hc)
+
+
+def test_graph_replay_matches_direct_launches(th, tmp_path):
+    g = fx.resnet50(width=0.125, size=64, classes=10)
+    x = g.make_input(3)
+    hc = _convert(th, g, "py", tmp_path, "r50g", 1)
+    outs = [th.process_float(hc, x)[0].copy() for _ in range(4)]   # 1st: direct; 2nd: captured; then replays
+    for o in outs[1:]:
+        assert np.array_equal(outs[0], o)
+    th.free_network(hc)
+
+
+def test_batch_sharded_over_two_gpus(th, oracle, tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    g = fx.resnet18(width=0.25, size=64, classes=10)
+    x = g.make_input(9)
+    one = _convert(th, g, "py", tmp_path, "r18one", 1)
+    ref, _, _ = th.process_float(one, x)
+    th.free_network(one)
+    for gather in ("peer", "host"):
+        os.environ["THB200_GATHER"] = gather
+        th.lib.THB200_SetDevices(2)
+        try:
+            two = _convert(th, g, "py", tmp_path, "r18two" + gather, 1)
+        finally:
+            th.lib.THB200_SetDevices(1)
+            os.environ.pop("THB200_GATHER", None)
+        out, _, _ = th.process_float(two, x)
+        assert np.array_equal(out, ref), gather
+        th.free_network(two)
