@@ -48,6 +48,11 @@ WORKLOADS = {
 LOWP_RANGE = 20.0
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the convolution launches of ONE forward, from the ncu capture whose
+# summary is kept under profiles/ (captured at batch 128, activations scaled to batch 256, weights once)
+NCU_DRAM_BYTES_PER_STEP = {("resnet50", "fp16", 256): 10.32e9}
+
+
 def read_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -292,7 +297,7 @@ def main():
         roof = {"bound": "tensor", "kernel": "conv_tc_kernel" if dtype != "fp32" else "conv_simt_kernel",
                 "achieved": ach, "peak": peaks["tflops"] if dtype != "int8" else peaks["tflops"] * 2, "unit": "TFLOP/s",
                 "frac": ach / (peaks["tflops"] * (2 if dtype == "int8" else 1)), "peak_source": "of " + peaks["src"],
-                "traffic": None, "launches_per_step": nconv, "kernel_ms_per_step": conv_ms, "share_of_step": conv_ms / tot_ms if tot_ms else None,
+                "traffic": NCU_DRAM_BYTES_PER_STEP.get((args.workload, dtype, batch)), "launches_per_step": nconv, "kernel_ms_per_step": conv_ms, "share_of_step": conv_ms / tot_ms if tot_ms else None,
                 "flops_per_step": conv_fl}
 
     if rank == 0:
