@@ -50,8 +50,8 @@ extern "C" int thb_conv_geometry(thb_conv_desc *d)
         if (d->Cout <= 32) d->BN = 32;
         else if (d->Cout <= 64) d->BN = 64;
         else if (d->Cout <= 128) d->BN = 128;
-        else if (d->Ktot_pad / bke >= 8 && mtiles * ((d->Cout + 255) / 256) >= 2 * 148 &&
-                 round_up(d->Cout, 256) == round_up(d->Cout, 128)) d->BN = 256; /* wide tiles only pay on long K loops */
+        else if (d->Ktot_pad / bke >= 4 && mtiles * ((d->Cout + 255) / 256) >= 148 &&
+                 round_up(d->Cout, 256) == round_up(d->Cout, 128)) d->BN = 256; /* wide tiles pay once the K loop outweighs the epilogue and every SM gets a tile */
         else d->BN = 128;
     }
     d->Cout_pad = round_up(d->Cout, d->BN);
