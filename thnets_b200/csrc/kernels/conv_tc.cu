@@ -679,45 +679,68 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                 }
                 alive = __all_sync(0xffffffffu, alive);
                 if (!alive) break;
+                if (KIND == 2) {
+                    // Eight columns at a time in a rolled loop (compact code: the unrolled 32-column form was bound by
+                    // instruction fetch).  Per-channel constants are loaded once per group; only rows whose window is
+                    // clipped by the image border look their own tap rectangle up in the summed-area table.
+                    const int satw = p.kW + 1, satn = (p.kH + 1) * (p.kW + 1);
+                    const bool clipped = valid && !interior;
+                    const uint32_t rnd = p.c_shift >= 1 ? 1u << (p.c_shift - 1) : 0u;
+                    const int cmax = p.Cout - 1;
+#pragma unroll 1
+                    for (int c8 = 0; c8 < SUBN / 8; c8++) {
+                        uint32_t a8[8];
+                        __syncwarp();
+                        tmem_ld8(lane_addr + sb * SUBN + c8 * 8, a8);
+                        tmem_ld_wait();
+                        const int c0 = nsub0 + c8 * 8;
+                        uint32_t lo = 0, hi = 0;
+                        if (c0 < p.Cout) {
+                            int wv[8], badd[8];
 #pragma unroll
-                for (int cc = 0; cc < SUBN / 32; cc++) {
-                    uint32_t acc[32];
-                    __syncwarp();
-                    tmem_ld32(lane_addr + sb * SUBN + cc * 32, acc);
-                    tmem_ld_wait();
-                    if (KIND == 2) {
-                        const int c0 = nsub0 + cc * 32;
-                        const int satw = p.kW + 1, satn = (p.kH + 1) * (p.kW + 1);
-                        uint32_t outw[8];
-#pragma unroll
-                        for (int i = 0; i < 32; i++) {
-                            const int c = c0 + i;
-                            int q = 0;
-                            if (valid && c < p.Cout) {
-                                const int *t = p.wsat + (size_t)c * satn;
-                                int wv;
-                                if (interior) wv = __ldg(t + satn - 1);
-                                else wv = __ldg(t + r1 * satw + s1) - __ldg(t + r0 * satw + s1) - __ldg(t + r1 * satw + s0) + __ldg(t + r0 * satw + s0);
-                                const int a = (int)acc[i] + p.b_off * wv + corr_pix;
-                                if (p.acc_out) p.acc_out[(size_t)pm * p.Cout + c] = a;
-                                uint32_t v = ((uint32_t)a + (uint32_t)p.c_off) * (uint32_t)p.c_mult;
-                                if (p.c_shift >= 1) v += 1u << (p.c_shift - 1);
-                                int sres = (int)v;
-                                if (p.c_shift > 0) sres >>= p.c_shift;
-                                q = min(255, max(0, sres));
-                                int t2 = q + (p.bias_add ? __ldg(p.bias_add + c) : 0);
-                                if (plane_pos < p.tail_start) t2 = min(255, max(0, t2));
-                                else t2 = t2 > 255 ? 255 : (t2 & 255);
-                                q = t2;
-                                if (p.relu_thr >= 0) q = q > p.relu_thr ? q : p.relu_val;
+                            for (int i = 0; i < 8; i++) {
+                                const int c = min(c0 + i, cmax);
+                                wv[i] = __ldg(p.wsat + (size_t)c * satn + satn - 1);
+                                badd[i] = p.bias_add ? __ldg(p.bias_add + c) : 0;
                             }
-                            if ((i & 3) == 0) outw[i >> 2] = 0;
-                            outw[i >> 2] |= (uint32_t)q << (8 * (i & 3));
+                            if (clipped) {
+#pragma unroll
+                                for (int i = 0; i < 8; i++) {
+                                    const int *t = p.wsat + (size_t)min(c0 + i, cmax) * satn;
+                                    wv[i] = __ldg(t + r1 * satw + s1) - __ldg(t + r0 * satw + s1) - __ldg(t + r1 * satw + s0) +
+                                            __ldg(t + r0 * satw + s0);
+                                }
+                            }
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                const int c = c0 + i;
+                                int q = 0;
+                                if (valid && c < p.Cout) {
+                                    const int a = (int)a8[i] + p.b_off * wv[i] + corr_pix;
+                                    if (p.acc_out) p.acc_out[(size_t)pm * p.Cout + c] = a;
+                                    const uint32_t v = ((uint32_t)a + (uint32_t)p.c_off) * (uint32_t)p.c_mult + rnd;
+                                    int sres = (int)v;
+                                    if (p.c_shift > 0) sres >>= p.c_shift;
+                                    q = min(255, max(0, sres));
+                                    int t2 = q + badd[i];
+                                    if (plane_pos < p.tail_start) t2 = min(255, max(0, t2));
+                                    else t2 = t2 > 255 ? 255 : (t2 & 255);
+                                    q = t2;
+                                    if (p.relu_thr >= 0) q = q > p.relu_thr ? q : p.relu_val;
+                                }
+                                if (i < 4) lo |= (uint32_t)q << (8 * i);
+                                else hi |= (uint32_t)q << (8 * (i - 4));
+                            }
                         }
-                        uint4 *dst = reinterpret_cast<uint4 *>(stg + row * (SUBN + 16) + cc * 32);
-                        dst[0] = make_uint4(outw[0], outw[1], outw[2], outw[3]);
-                        dst[1] = make_uint4(outw[4], outw[5], outw[6], outw[7]);
-                    } else {
+                        *reinterpret_cast<uint2 *>(stg + row * (SUBN + 16) + c8 * 8) = make_uint2(lo, hi);
+                    }
+                } else {
+#pragma unroll
+                    for (int cc = 0; cc < SUBN / 32; cc++) {
+                        uint32_t acc[32];
+                        __syncwarp();
+                        tmem_ld32(lane_addr + sb * SUBN + cc * 32, acc);
+                        tmem_ld_wait();
                         uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<float *>(stg) + row * (SUBN + 4) + cc * 32);
 #pragma unroll
                         for (int q = 0; q < 8; q++) dst[q] = make_uint4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
