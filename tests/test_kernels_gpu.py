@@ -438,3 +438,16 @@ def test_pre_and_postprocess(lib, G, oracle, dtype):
         assert np.array_equal(out.cpu().numpy(), oracle.lowp_dequantize(refq, rsub, rmult))
     else:
         assert np.array_equal(out.cpu().numpy(), got)
+
+
+@pytest.mark.parametrize("shape", [(37, 40), (5, 2500), (300, 64), (3, 25088)])
+def test_u8_channel_sum(lib, G, shape):
+    """per-pixel sum of the first C bytes (both the thread-per-pixel and the block-per-pixel kernel)"""
+    pixels, c = shape
+    ld = G.ru(c, 16) + 16
+    x = np.random.default_rng(40).integers(0, 256, (pixels, ld), dtype=np.uint8)
+    xt = G.dev(x)
+    out = G.dzeros(pixels, torch.int32)
+    assert lib.thb_u8_channel_sum(G.ptr(xt), pixels, c, ld, G.ptr(out), None) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), x[:, :c].astype(np.int64).sum(axis=1))

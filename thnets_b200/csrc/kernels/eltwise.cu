@@ -509,6 +509,30 @@ __global__ void u8_channel_sum_kernel(const uint8_t *x, long pixels, int C, int 
     csum[pix] = s;
 }
 
+// the same with a whole block per pixel, for the few-pixel, many-channel inputs of Linear layers
+__global__ void u8_channel_sum_wide_kernel(const uint8_t *x, int C, int x_ld, int *csum)
+{
+    const uint8_t *p = x + (size_t)blockIdx.x * x_ld;
+    int s = 0;
+    for (int c0 = threadIdx.x * 16; c0 < C; c0 += blockDim.x * 16) {
+        const uint4 t = *reinterpret_cast<const uint4 *>(p + c0);
+        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int i = 0; i < 16; i++)
+            if (c0 + i < C) s += (w[i >> 2] >> ((i & 3) * 8)) & 0xff;
+    }
+    __shared__ int part[8];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int tot = 0;
+        for (int i = 0; i < (int)(blockDim.x >> 5); i++) tot += part[i];
+        csum[blockIdx.x] = tot;
+    }
+}
+
 }  // namespace
 
 // =================================================================================================
@@ -709,6 +733,10 @@ int thb_col2im(int dtype, const void *cols, int N, int H, int W, int Cout, int k
 int thb_u8_channel_sum(const void *x, long pixels, int C, int x_ld, int *csum, thb_stream s)
 {
     if (pixels == 0) return THB_OK;
+    if (C >= 2048 && pixels <= 65535) {
+        u8_channel_sum_wide_kernel<<<(unsigned)pixels, 256, 0, (cudaStream_t)s>>>((const uint8_t *)x, C, x_ld, csum);
+        return THB_LAUNCH_CHECK("u8_channel_sum_wide_kernel");
+    }
     u8_channel_sum_kernel<<<nblocks(pixels), 256, 0, (cudaStream_t)s>>>((const uint8_t *)x, pixels, C, x_ld, csum);
     return THB_LAUNCH_CHECK("u8_channel_sum_kernel");
 }
