@@ -122,6 +122,10 @@ int thb_conv_padded_rows_supported(int dtype);
 /* u8 HWC images (already on the device, row stride `stride`) -> normalised NHWC dtype (thapi.c:20-46) */
 int thb_preprocess_images(const unsigned char *img, int N, int H, int W, int stride, int cp, int bgr,
                           const float *mean3, const float *std3, int dtype, void *y, int y_ld, thb_stream s);
+/* u8 HWC RGB images -> quantised NHWC u8 with the static input range the lowp image loader derives from mean/std
+ * (lowp/lowp_basic.c:82-131); returns that range as *q_sub, *q_mult (host) */
+int thb_preprocess_images_lowp(const unsigned char *img, int N, int H, int W, int stride, int bgr, const float *mean3,
+                               const float *std3, void *y, int y_ld, float *q_sub_host, float *q_mult_host, thb_stream s);
 /* min and max (both seeded with 0) of the normalised input, for the dynamic input quantisation */
 int thb_minmax_normalized(const float *x_nchw, int N, int C, int H, int W, const float *mean3,
                           const float *std3, float *minmax2, thb_stream s);

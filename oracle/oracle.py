@@ -285,7 +285,21 @@ class Oracle:
         self.lib.orc_lowp_threshold(_up(xq), xq.size, t, v, _up(y))
         return y
 
-    def run_lowp(self, graph, batch, rng, spatial_size, keep=False):
+    def lowp_images(self, images, mean, std, bgr=0):
+        """lowp_basic.c:60-131: list of uint8 [H,W,3] images -> (planar uint8 [N,3,H,W], sub, mult)."""
+        n = len(images)
+        imgs = [np.ascontiguousarray(i, np.uint8) for i in images]
+        h, w = imgs[0].shape[:2]
+        ptrs = (C.POINTER(C.c_ubyte) * n)(*[i.ctypes.data_as(C.POINTER(C.c_ubyte)) for i in imgs])
+        dst = np.empty((n, 3, h, w), np.uint8)
+        sub, mult = C.c_float(), C.c_float()
+        mean = np.ascontiguousarray(mean, np.float32)
+        std = np.ascontiguousarray(std, np.float32)
+        self.lib.orc_lowp_images(ptrs, n, w, h, imgs[0].strides[0], mean.ctypes.data_as(C.POINTER(C.c_float)),
+                                 std.ctypes.data_as(C.POINTER(C.c_float)), bgr, _up(dst), C.byref(sub), C.byref(mult))
+        return dst, float(sub.value), float(mult.value)
+
+    def run_lowp(self, graph, batch, rng, spatial_size, keep=False, quantised_input=None):
         """uint8 forward of a sequential conv/linear/relu/maxpool graph.
 
         The input is quantised over the WHOLE batch tensor (lowp_basic.c:15-35); every
@@ -293,8 +307,11 @@ class Oracle:
         convolution runs per image.  View nodes vanish and Linear nodes become k x k
         convolutions exactly as THMakeSpatial does.
         """
-        x = self.normalize(batch, graph.mean, graph.std)
-        q, sub, mult = self.lowp_quantize(x)
+        if quantised_input is not None:      # the image loader's static range instead of the measured one
+            q, sub, mult = quantised_input
+        else:
+            x = self.normalize(batch, graph.mean, graph.std)
+            q, sub, mult = self.lowp_quantize(x)
         osub, omult = np.float32(-rng / 2), np.float32(np.float32(255) / np.float32(rng))
         size = spatial_size
         vals = {0: (q, sub, mult)}

@@ -204,3 +204,24 @@ def test_batch_sharded_over_two_gpus(th, oracle, tmp_path):
         out, _, _ = th.process_float(two, x)
         assert np.array_equal(out, ref), gather
         th.free_network(two)
+
+
+@pytest.mark.parametrize("bgr", [0, 1])
+@pytest.mark.parametrize("batch", [1, 3])
+def test_lowp_images_bit_exact(th, oracle, tmp_path, batch, bgr):
+    """THProcessImages on the uint8 engine: the image loader's static input range (lowp_basic.c:82-131), then the same
+    network as test_lowp_vgg_bit_exact; every output byte equals the oracle's."""
+    size, rng = 32, 8.0
+    g = fx.vgg16(width=0.125, size=size, classes=10, fc=64)
+    g.mean, g.std = np.array([0.45, 0.42, 0.40], np.float32), np.array([0.225, 0.23, 0.22], np.float32)
+    r = np.random.default_rng(17)
+    imgs = [r.integers(0, 256, (size, size, 3)).astype(np.uint8) for _ in range(batch)]
+    ref = oracle.run_lowp(g, None, rng, size, quantised_input=oracle.lowp_images(imgs, g.mean, g.std, bgr))
+    h = _load(th, g, "t7", tmp_path, "vggi")
+    th.make_spatial(h, size)
+    hl = th.create_lowp_network(h, rng)
+    th.free_network(h)
+    out, ow, oh = th.process_images(hl, imgs, bgr=bgr)
+    assert (ow, oh) == (1, 1)
+    assert np.array_equal(out, ref.ravel()), np.abs(out - ref.ravel()).max()
+    th.free_network(hl)

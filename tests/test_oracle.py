@@ -142,3 +142,25 @@ def test_lowp_oracle_matches_live_reference(oracle, tmp_path):
     hl = ref.create_lowp_network(h, 6.0)
     y, _, _ = ref.process_float(hl, x)
     assert np.array_equal(oracle.run_lowp(g, x, 6.0, 48).ravel(), y)
+
+
+@pytest.mark.parametrize("bgr", [0, 1])
+def test_lowp_image_loader_matches_live_reference(oracle, tmp_path, bgr):
+    """THProcessImages on the reference's lowp engine (Lowp_LoadImages, lowp/lowp_basic.c:82-131) against the restated
+    loader feeding the restated network, batch 1 (the reference's lowp engine is only sound at batch 1)."""
+    from thnets_b200.capi import THNets
+    path = os.path.join(REF_DIR, "libthnets_ref_lowp.so")
+    if not os.path.exists(path):
+        pytest.skip("lowp reference build missing")
+    ref = THNets(path)
+    g = fx.vgg16(width=0.125, size=48, classes=7, fc=40)
+    g.mean, g.std = np.array([0.45, 0.42, 0.40], np.float32), np.array([0.225, 0.23, 0.22], np.float32)
+    img = np.random.default_rng(8).integers(0, 256, (48, 48, 3)).astype(np.uint8)
+    d = str(tmp_path / "vggi")
+    fx.write_torch7(g, d)
+    h = ref.load_network(d)
+    ref.make_spatial(h, 48)
+    hl = ref.create_lowp_network(h, 6.0)
+    y, _, _ = ref.process_images(hl, [img], bgr=bgr)
+    mine = oracle.run_lowp(g, None, 6.0, 48, quantised_input=oracle.lowp_images([img], g.mean, g.std, bgr))
+    assert np.array_equal(mine.ravel(), y)

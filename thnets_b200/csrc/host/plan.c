@@ -1158,6 +1158,7 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
                        int W, int rank, const float *mean, const float *std, int inplace, thb_result *res)
 {
     if (N < 1 || C < 1 || H < 1 || W < 1) { thb_set_error("empty input"); return -1; }
+    if (E->dtype == THB_U8 && !x) rank = 4; /* the lowp image loader always builds a 4-D tensor (lowp_basic.c:87-92) */
     if (!E->built || E->N != N || E->C != C || E->H != H || E->W != W || E->rank != rank || E->cp != cp) {
         if (engine_build(E, N, C, H, W, rank, cp)) return -1;
     }
@@ -1191,8 +1192,13 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
     }
     if (E->dtype == THB_U8) {
         /* lowp_basic.c:15-29: one range over the WHOLE batch tensor, so slices are reduced on the host */
-        if (!x) { thb_set_error("THProcessImages is not supported with Lowp"); return -1; }
         float lo = 0, hi = 0;
+        if (!x) {
+            /* lowp_basic.c:82-131: the image loader quantises straight from the bytes with a static range derived
+             * from mean/std, so nothing has to be measured; the kernel call below reports that range */
+            if (cp != 3) { thb_set_error("the lowp image loader takes 3-plane images"); return -1; }
+            goto lowp_range_done;
+        }
         for (int g = 0; g < G; g++) {
             instance *I = &set[g];
             float mm[2];
@@ -1206,6 +1212,7 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
         q_sub = lo;
         q_mult = hi - lo > 0 ? (float)(255.0 / (hi - lo)) : 0;
         for (int g = 0; g < G; g++) set_dynamic_quant(&set[g], q_sub, q_mult);
+    lowp_range_done:;
     }
 
     long total = 0;
@@ -1229,7 +1236,11 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
         else if (x)
             rc = thb_preprocess(I->d_in, inplace ? I->d_in : 0, I->slice_n, C, H, W, mean, std, E->dtype, in_ptr, I->in_val.ld,
                                 q_sub, q_mult, I->stream);
-        else
+        else if (E->dtype == THB_U8) {
+            rc = thb_preprocess_images_lowp(I->d_img, I->slice_n, H, W, W * cp, bgr, mean, std, in_ptr, I->in_val.ld, &q_sub,
+                                            &q_mult, I->stream);
+            set_dynamic_quant(I, q_sub, q_mult);
+        } else
             rc = thb_preprocess_images(I->d_img, I->slice_n, H, W, W * cp, cp, bgr, mean, std, E->dtype, in_ptr,
                                        I->in_val.ld, I->stream);
         if (rc) { thb_set_error("preprocess launch failed: %s", thb_last_cuda_error()); return -1; }

@@ -194,6 +194,28 @@ __global__ void preprocess_images_kernel(const uint8_t *img, int N, int H, int W
     Vec<T>::store(y + pix * y_ld, v);
 }
 
+// u8 HWC images -> quantised NHWC u8 with the static input range of the lowp image loader
+// (lowp/lowp_basic.c:82-131, lowp/lowp_images.c): q = (unsigned char)(int)roundf((px - sub[c]) * mult[c])
+__global__ void preprocess_images_u8_kernel(const uint8_t *img, int N, int H, int W, int stride, int bgr, int3 sub, float3 mult,
+                                            uint8_t *y, int y_ld)
+{
+    const long pix = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (pix >= (long)N * H * W) return;
+    const long n = pix / ((long)H * W);
+    const int hw = (int)(pix - n * (long)H * W), h = hw / W, w = hw - h * W;
+    const uint8_t *src = img + ((size_t)n * H + h) * stride + (size_t)w * 3;
+    const int sb[3] = {sub.x, sub.y, sub.z};
+    const float ml[3] = {mult.x, mult.y, mult.z};
+    uint32_t word = 0;
+#pragma unroll
+    for (int c = 0; c < 3; c++) {
+        const int sc = bgr ? 2 - c : c;
+        const int q = (int)roundf(__fmul_rn((float)((int)src[sc] - sb[c]), ml[c]));
+        word |= (uint32_t)(q & 0xff) << (8 * c);
+    }
+    *reinterpret_cast<uint4 *>(y + pix * y_ld) = make_uint4(word, 0, 0, 0);
+}
+
 __global__ void minmax_kernel(const float *x, int C, long HW, long total, float3 mean, float3 std_, float *minmax)
 {
     const float m[3] = {mean.x, mean.y, mean.z}, sd[3] = {std_.x, std_.y, std_.z};
@@ -580,6 +602,32 @@ int thb_preprocess_images(const unsigned char *img, int N, int H, int W, int str
     DISPATCH_FLOAT_DTYPE(dtype, (preprocess_images_kernel<T><<<nblocks(pix), 256, 0, (cudaStream_t)s>>>(
                                     img, N, H, W, stride, cp, bgr, m, is, (T *)y, y_ld)));
     return THB_LAUNCH_CHECK("preprocess_images_kernel");
+}
+
+int thb_preprocess_images_lowp(const unsigned char *img, int N, int H, int W, int stride, int bgr, const float *mean3,
+                               const float *std3, void *y, int y_ld, float *q_sub, float *q_mult, thb_stream s)
+{
+    if (y_ld % 16) return THB_ERR_ARG;
+    // the loader's float expressions, in its order (lowp_basic.c:102-119)
+    float mn = 1e30f, mx = -1e30f, m;
+    for (int i = 0; i < 3; i++) {
+        if (-mean3[i] / std3[i] < mn) mn = -mean3[i] / std3[i];
+        if ((1 - mean3[i]) / std3[i] > mx) mx = (1 - mean3[i]) / std3[i];
+    }
+    m = (mx - mn) ? 255 / (mx - mn) : 0;
+    int sub[3];
+    float mul[3];
+    for (int i = 0; i < 3; i++) {
+        sub[i] = (int)roundf(255 * (mean3[i] + std3[i] * mn));
+        mul[i] = m / (255 * std3[i]);
+    }
+    *q_sub = mn;
+    *q_mult = m;
+    const long pix = (long)N * H * W;
+    if (pix == 0) return THB_OK;
+    preprocess_images_u8_kernel<<<nblocks(pix), 256, 0, (cudaStream_t)s>>>(img, N, H, W, stride, bgr, make_int3(sub[0], sub[1], sub[2]),
+                                                                            make_float3(mul[0], mul[1], mul[2]), (uint8_t *)y, y_ld);
+    return THB_LAUNCH_CHECK("preprocess_images_u8_kernel");
 }
 
 int thb_minmax_normalized(const float *x, int N, int C, int H, int W, const float *mean3, const float *std3,
