@@ -44,6 +44,10 @@ CONV_CASES = [
     (2, 64, 30, 17, 96, 5, 1, 2),
     (1, 192, 13, 13, 48, 3, 1, 0),
     (2, 256, 9, 11, 32, 2, 2, 0),
+    # stride 1, same padding, whole channel slabs, tiles that span several image rows and images
+    (2, 64, 20, 24, 64, 3, 1, 1),
+    (3, 128, 21, 22, 128, 3, 1, 1),
+    (1, 64, 33, 20, 64, 5, 1, 2),
     # few channels per pixel: several taps per K block, gathered (K padding: 49 taps)
     (2, 32, 15, 15, 64, 3, 1, 1),
     (1, 16, 20, 22, 64, 7, 2, 3),
