@@ -62,16 +62,19 @@ def read_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons, sampled every 50 ms from before the warm-up on; the samples that fall
+    inside the timed region are reported (or, if the region was too short to hold three, those since the warm-up began:
+    the GPU runs the same forward throughout)."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
         self.rows, self.proc, self.gpu = [], None, gpu_index
+        self.t0 = self.t1 = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                                           "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -80,21 +83,32 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
+
+    def mark_begin(self):
+        self.t0 = time.perf_counter()
+
+    def mark_end(self):
+        self.t1 = time.perf_counter()
 
     def stop(self):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
         self.t.join(timeout=2)
-        sm = sorted(float(r[1]) for r in self.rows if len(r) > 8 and r[1].replace(".", "").isdigit())
-        mx = [float(r[2]) for r in self.rows if len(r) > 8 and r[2].replace(".", "").isdigit()]
+        good = [(ts, r) for ts, r in self.rows if len(r) > 8 and r[1].replace(".", "").isdigit()]
+        inside = [r for ts, r in good if self.t0 is not None and self.t0 <= ts <= (self.t1 or ts)]
+        window = "timed region"
+        if len(inside) < 3:
+            inside, window = [r for ts, r in good], "warm-up + timed region"
+        sm = sorted(float(r[1]) for r in inside)
+        mx = [float(r[2]) for r in inside if r[2].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) > 8 and r[5 + i].lower().startswith("active") for r in self.rows)]
+        reasons = [n for i, n in enumerate(names) if any(r[5 + i].lower().startswith("active") for r in inside)]
         # the busiest half of the samples = the clock under load
         load = sm[len(sm) // 2:] if sm else []
         return {"sm_mhz": load[len(load) // 2] if load else None, "sm_max_mhz": mx[0] if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+                "reasons": reasons, "samples": len(sm), "window": window}
 
 
 def build_fixture(workload, tmpdir):
@@ -248,6 +262,9 @@ def main():
 
     barrier, max_over_ranks = ranks.barrier, ranks.max
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     # The device-resident loop runs the whole-batch plan, so stage the batch into it with the copy/compute pipelining of
     # THProcessFloat switched off once; the end-to-end loop below runs with the library's default (pipelined sub-batches).
     lib.THB200_SetPipelineChunks(1)
@@ -258,11 +275,9 @@ def main():
     if lib.THB200_TimeForward(net, warmup) < 0:
         raise SystemExit("THB200_TimeForward failed: %s" % lib.THB200_LastErrorString())
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     # --- device-resident: K forwards, events on the launching stream
     barrier()
+    sampler.mark_begin()
     l0 = lib.THB200_KernelLaunches()
     ms_step = lib.THB200_TimeForward(net, args.steps)
     launches = lib.THB200_KernelLaunches() - l0
@@ -278,6 +293,7 @@ def main():
     e2e_s = (time.perf_counter() - t0) / args.steps
     barrier()
     e2e_s = max_over_ranks(e2e_s)
+    sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
 
     # --- per-launch profile for the roofline of the dominant kernel
