@@ -114,6 +114,35 @@ def test_conv_f16_rows_stored_with_padding(lib, G, oracle, gather_only, crop, mo
     assert G.rel_err(got, ref) < 1e-2, G.rel_err(got, ref)
 
 
+@pytest.mark.parametrize("case", [(3, 64, 19, 23, 40, 3, 2, 1), (2, 64, 30, 17, 96, 5, 1, 2), (3, 128, 21, 22, 128, 3, 1, 1),
+                                  (3, 64, 9, 9, 64, 1, 1, 0), (5, 128, 7, 7, 72, 3, 1, 1), (2, 128, 14, 14, 64, 1, 2, 0)])
+@pytest.mark.parametrize("residual", [False, True])
+def test_conv_f16_two_tiles_per_cta(lib, G, oracle, case, residual, monkeypatch):
+    """Pair mode (two vertically adjacent pixel tiles per CTA sharing one weight tile per K block), forced on shapes
+    small enough for the oracle: odd and even tile counts, ragged last tiles, with and without a fused residual."""
+    monkeypatch.setenv("THB200_PAIR_MIN_UNITS", "1")
+    monkeypatch.setenv("THB200_PAIR_MIN_KB", "1")
+    n, cin, h, w, cout, k, s, p = case
+    x, wt = _conv_inputs(case, 21, True)
+    rng = np.random.default_rng(22)
+    scale = rng.uniform(0.5, 1.5, cout).astype(np.float32)
+    shift = rng.standard_normal(cout).astype(np.float32)
+    y0 = oracle.conv2d(x, wt, None, (s, s), (p, p)) * scale[None, :, None, None] + shift[None, :, None, None]
+    conv = G.Conv(lib, K.THB_F16, x.shape, wt, (s, s), (p, p))
+    conv.set_affine(scale, shift)
+    if residual:
+        res = rng.standard_normal(y0.shape).astype(np.float16).astype(np.float32)
+        rt, rld = G.to_nhwc(res, K.THB_F16)
+        conv.set_residual(rt, rld, 1.0, -1.0)
+        conv.set_act(K.ACT_THRESHOLD)
+        ref = np.maximum(y0 - res, 0)
+    else:
+        ref = y0
+    xt, _ = G.to_nhwc(x, K.THB_F16)
+    got = G.from_nhwc(conv.run(xt, fill=5.0), cout)
+    assert G.rel_err(got, ref) < 1e-2, (case, residual, G.rel_err(got, ref))
+
+
 @pytest.mark.parametrize("bn_tile", [32, 64, 128, 256])
 def test_conv_f16_all_tile_widths(lib, G, oracle, bn_tile):
     case = (2, 72, 14, 14, 264, 3, 1, 1)

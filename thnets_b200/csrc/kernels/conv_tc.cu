@@ -52,6 +52,10 @@ struct ConvTcParams {
     int a_tma;   // 1: 1x1 stride-1 convolution, the activation operand is a plain [pixels][Cin] matrix loaded by 2-D TMA;
                  // 2: whole 128-byte channel slabs per tap, loaded by im2col-mode TMA (any kernel size, stride, padding)
     int pdl;                   // launched with programmatic stream serialisation
+    int pair;                  // TMA modes, BN <= 128: the CTA works on two vertically adjacent 128-pixel tiles at once.  Every
+                               // pipeline stage carries both activation tiles and ONE weight tile, and the MMA thread feeds two
+                               // accumulators per barrier round: that round costs the thread ~250 cycles whatever it carries,
+                               // which a single narrow tile (192-256 tensor cycles per K block) cannot hide.
     int stages;                // TMA epilogue: pipeline stages (the launcher sizes them against the epilogue tiles)
     int epi_groups, epi_bufs;  // TMA epilogue: groups at work (2 or 3) and 16 KB tiles each of them cycles through
     int row_pitch, pad_left;  // gather: pixels between input rows, zero pixels in front of each row (W, 0 when plain)
@@ -193,20 +197,48 @@ struct EpiCursor {
     int j, sb;  // j-th tile of this group, block sb of that tile
 };
 
-// The sequence of 64-channel blocks an epilogue group walks: every ngrp-th tile of this CTA, and of each tile the
-// blocks that hold real channels.
-template <int BN> struct EpiWalk {
-    int first, step, my_tiles, n_tiles, cout8;
-    __device__ EpiWalk(const ConvTcParams &p, int grp, int total_tiles)
+// The CTA's own sequence of 128-pixel tiles ("local tiles" 0, 1, 2, ...).  Plain mode: global tile blockIdx.x +
+// lt*gridDim.x of the (pixel tile, column tile) grid.  Pair mode: the CTA takes UNITS of two vertically adjacent pixel
+// tiles with the same column tile; local tiles 2i and 2i+1 are the halves of its i-th unit.  A second half beyond
+// the last pixel tile (odd tile count) is a phantom: it is computed from zero-filled loads and never stored.
+template <int BN> struct TileMap {
+    int pair, n_tiles, n_local;
+    __device__ TileMap(const ConvTcParams &p)
     {
-        first = blockIdx.x + grp * gridDim.x;
-        step = gridDim.x * p.epi_groups;
-        my_tiles = first < total_tiles ? (total_tiles - 1 - first) / step + 1 : 0;
+        pair = p.pair;
         n_tiles = p.n_tiles;
+        const int units = (pair ? (p.m_tiles + 1) >> 1 : p.m_tiles) * n_tiles;
+        const int mine = (int)blockIdx.x < units ? (units - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+        n_local = pair ? 2 * mine : mine;
+    }
+    __device__ void coords(int lt, int &m0, int &n0) const
+    {
+        const int u = blockIdx.x + (pair ? lt >> 1 : lt) * gridDim.x;
+        const int um = u / n_tiles;
+        n0 = (u - um * n_tiles) * BN;
+        m0 = (pair ? 2 * um + (lt & 1) : um) * BM;
+    }
+};
+
+// The sequence of 64-channel blocks an epilogue group walks: every ngrp-th local tile of this CTA, and of each tile
+// the blocks that hold real channels.
+template <int BN> struct EpiWalk {
+    TileMap<BN> map;
+    int grp, ngrp, my_tiles, cout8;
+    __device__ EpiWalk(const ConvTcParams &p, int g) : map(p)
+    {
+        grp = g;
+        ngrp = p.epi_groups;
+        my_tiles = map.n_local > grp ? (map.n_local - 1 - grp) / ngrp + 1 : 0;
         cout8 = (p.Cout + 7) & ~7;
     }
-    __device__ int tile(int j) const { return first + j * step; }
-    __device__ int blocks_of(int j) const { return min(BN / 64, (cout8 - (tile(j) % n_tiles) * BN + 63) >> 6); }
+    __device__ int local(int j) const { return grp + j * ngrp; }
+    __device__ int blocks_of(int j) const
+    {
+        int m0, n0;
+        map.coords(local(j), m0, n0);
+        return min(BN / 64, (cout8 - n0 + 63) >> 6);
+    }
     __device__ void advance(EpiCursor &c) const
     {
         if (++c.sb == blocks_of(c.j)) { c.sb = 0; c.j++; }
@@ -222,7 +254,7 @@ template <int BN> struct EpiWalk {
 template <int KIND, int BN, int NACC>
 __device__ __forceinline__ void epilogue_tma(const ConvTcParams &p, int grp, int warp, int lane, uint32_t tmem_base,
                                              uint8_t *tiles, uint64_t *acc_full, uint64_t *acc_empty, uint64_t *rows_ready,
-                                             uint64_t *avail, volatile int *abort_flag, int total_tiles)
+                                             uint64_t *avail, volatile int *abort_flag)
 {
     const int ngrp = p.epi_groups, nbuf = p.epi_bufs;
     const int quad = warp & 3, row = quad * 32 + lane;
@@ -231,14 +263,16 @@ __device__ __forceinline__ void epilogue_tma(const ConvTcParams &p, int grp, int
     const int act_mode = p.act_kind == THB_ACT_NONE ? 0
                          : p.act_kind != THB_ACT_THRESHOLD ? 2
                          : (p.act_th == 0.f && p.act_val == 0.f) ? 3 : 1;
-    const EpiWalk<BN> walk(p, grp, total_tiles);
+    const EpiWalk<BN> walk(p, grp);
     EpiCursor cur = {0, 0};
     int b = 0;            // tile of the current block, and how often the ring of tiles has wrapped
     uint32_t wrap = 0;
     bool alive = true;
     while (cur.j < walk.my_tiles) {
-        const int lt = grp + cur.j * ngrp, tile = walk.tile(cur.j);
-        const int n0 = (tile % p.n_tiles) * BN, nsub0 = n0 + cur.sb * 64;
+        const int lt = grp + cur.j * ngrp;
+        int m0, n0;
+        walk.map.coords(lt, m0, n0);
+        const int nsub0 = n0 + cur.sb * 64;
         const int ab = lt % NACC;
         const bool last_block = cur.sb == walk.blocks_of(cur.j) - 1;
         uint8_t *tile_smem = tiles + b * EPI_TILE_BYTES;
@@ -297,17 +331,17 @@ __device__ __forceinline__ void epilogue_tma(const ConvTcParams &p, int grp, int
 template <int BN>
 __device__ __forceinline__ void epilogue_agent(const ConvTcParams &p, const CUtensorMap *tmY, const CUtensorMap *tmR, int grp,
                                                uint8_t *tiles, uint64_t *rows_ready, uint64_t *avail,
-                                               volatile int *abort_flag, int total_tiles)
+                                               volatile int *abort_flag)
 {
     const int nbuf = p.epi_bufs;
     const bool has_res = p.res != nullptr;
-    const EpiWalk<BN> walk(p, grp, total_tiles);
+    const EpiWalk<BN> walk(p, grp);
     auto make_available = [&](const EpiCursor &c, int b) {
-        if (has_res) {
-            const int tile = walk.tile(c.j);
+        int m0, n0;
+        walk.map.coords(walk.local(c.j), m0, n0);
+        if (has_res && m0 < p.P) {  // (a phantom half tile has no residual rows)
             mbar_arrive_expect_tx(smem_u32(&avail[b]), EPI_TILE_BYTES);
-            tma_load_2d(smem_u32(tiles + b * EPI_TILE_BYTES), tmR, smem_u32(&avail[b]), (tile % p.n_tiles) * BN + c.sb * 64,
-                        (tile / p.n_tiles) * BM);
+            tma_load_2d(smem_u32(tiles + b * EPI_TILE_BYTES), tmR, smem_u32(&avail[b]), n0 + c.sb * 64, m0);
         } else
             mbar_arrive(smem_u32(&avail[b]));
     };
@@ -321,14 +355,15 @@ __device__ __forceinline__ void epilogue_agent(const ConvTcParams &p, const CUte
     uint32_t wrap = 0;
     bool alive = true;
     for (; cur.j < walk.my_tiles; q++) {
-        const int tile = walk.tile(cur.j);
+        int m0, n0;
+        walk.map.coords(walk.local(cur.j), m0, n0);
         if (!mbar_wait_bounded(smem_u32(&rows_ready[b]), wrap & 1)) {
             atomicExch(p.status, 5);
             *abort_flag = 1;
             alive = false;
             break;
         }
-        tma_store_2d(tmY, smem_u32(tiles + b * EPI_TILE_BYTES), (tile % p.n_tiles) * BN + cur.sb * 64, (tile / p.n_tiles) * BM);
+        if (m0 < p.P) tma_store_2d(tmY, smem_u32(tiles + b * EPI_TILE_BYTES), n0 + cur.sb * 64, m0);
         bulk_commit_group();
         bulk_wait_group_read<0>();
         if (pre.j < walk.my_tiles) {
@@ -364,9 +399,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int nst = L::TMA_EPI ? p.stages : STAGES;  // pipeline stages in use
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
+    const bool pair = L::TMA_EPI && p.pair;
+    const int a_stage_bytes = pair ? 2 * A_STAGE_BYTES : A_STAGE_BYTES;  // pair mode: both halves' activation tiles
     uint8_t *sA = smem + L::BAR_BYTES;
-    uint8_t *sB = sA + nst * A_STAGE_BYTES;
-    uint8_t *stage_buf = sA + nst * L::STAGE_BYTES;
+    uint8_t *sB = sA + nst * a_stage_bytes;
+    uint8_t *stage_buf = sB + nst * B_STAGE_BYTES;
     uint64_t *full = bars, *empty = bars + MAX_STAGES;
     uint64_t *acc_full = bars + 2 * MAX_STAGES, *acc_empty = acc_full + 4;
     uint64_t *rows_ready = acc_empty + 4, *avail = rows_ready + 9;   // TMA epilogue: a pair per group and tile
@@ -424,7 +461,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
         if constexpr (L::TMA_EPI)
             if (lane < p.epi_groups)
                 epilogue_agent<BN>(p, &tmapY, &tmapR, lane, stage_buf + lane * p.epi_bufs * EPI_TILE_BYTES, rows_ready + lane * 3,
-                                   avail + lane * 3, abort_flag, total_tiles);
+                                   avail + lane * 3, abort_flag);
         __syncwarp();
     } else if (warp < 4) {
         // ================================================================== A producer (gather mode)
@@ -433,7 +470,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
             if constexpr (L::TMA_EPI)
                 if (p.epi_groups == 3)
                     epilogue_tma<KIND, BN, NACC>(p, 2, warp, lane, tmem_base, stage_buf + 2 * p.epi_bufs * EPI_TILE_BYTES,
-                                                 acc_full, acc_empty, rows_ready + 6, avail + 6, abort_flag, total_tiles);
+                                                 acc_full, acc_empty, rows_ready + 6, avail + 6, abort_flag);
             goto done;
         }
         const int chunk = lane & 7;
@@ -506,24 +543,29 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
         if (alive)
             for (int k = (it > LAG ? it - LAG : 0); k < it; k++) mbar_arrive(smem_u32(&full[k % STAGES]));
     } else if (warp == 4) {
-        // ================================================================== weight (B) TMA producer
+        // ================================================================== TMA producer: per K block the weight tile
+        // and, in the TMA modes, the activation tile (both halves' tiles in pair mode)
         if (lane == 0) {
-            int it = 0, ring_s = 0;  // stage and phase of K block `it` in the ring of nst stages
+            const TileMap<BN> map(p);
+            const int halves = pair ? 2 : 1;
+            int ring_s = 0;  // stage and phase in the ring of nst stages
             uint32_t ring_ph = 0;
             bool alive = true;
-            for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-                const int n0 = (tile % p.n_tiles) * BN;
-                const int m0 = (tile / p.n_tiles) * BM;
-                // im2col mode: input position of the tile's first output pixel for tap (0, 0)
-                int iw = 0, ih = 0, in = 0, tap_w = 0, tap_h = 0, slab = 0;
-                if (p.a_tma == 2) {
-                    in = m0 / p.oHW;
-                    const int rem = m0 - in * p.oHW;
-                    const int oh = rem / p.oW;
-                    ih = oh * p.dH - p.padH;
-                    iw = (rem - oh * p.oW) * p.dW - p.tma_padw;
-                }
-                for (int kb = 0; kb < p.nkb; kb++, it++) {
+            for (int lt = 0; lt < map.n_local && alive; lt += halves) {
+                int m0, n0;
+                map.coords(lt, m0, n0);
+                // im2col mode: input position of each half's first output pixel for tap (0, 0)
+                int iw[2] = {0, 0}, ih[2] = {0, 0}, in[2] = {0, 0}, tap_w = 0, tap_h = 0, slab = 0;
+                if (p.a_tma == 2)
+                    for (int h = 0; h < halves; h++) {
+                        const int m = m0 + h * BM;
+                        in[h] = m / p.oHW;
+                        const int rem = m - in[h] * p.oHW;
+                        const int oh = rem / p.oW;
+                        ih[h] = oh * p.dH - p.padH;
+                        iw[h] = (rem - oh * p.oW) * p.dW - p.tma_padw;
+                    }
+                for (int kb = 0; kb < p.nkb; kb++) {
                     const int s = ring_s;
                     const uint32_t ph = ring_ph;
                     if (++ring_s == nst) { ring_s = 0; ring_ph ^= 1; }
@@ -533,20 +575,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                         alive = false;
                         break;
                     }
+                    const uint32_t bar = smem_u32(&full[s]);
+                    mbar_arrive_expect_tx(bar, (uint32_t)(B_STAGE_BYTES + (p.a_tma ? a_stage_bytes : 0)));
                     if (p.a_tma == 1) {
-                        mbar_arrive_expect_tx(smem_u32(&full[s]), B_STAGE_BYTES + A_STAGE_BYTES);
-                        tma_load_2d(smem_u32(sA + s * A_STAGE_BYTES), &tmapA, smem_u32(&full[s]), kb * BKE, m0);
+                        for (int h = 0; h < halves; h++)
+                            tma_load_2d(smem_u32(sA + s * a_stage_bytes + h * A_STAGE_BYTES), &tmapA, bar, kb * BKE, m0 + h * BM);
                     } else if (p.a_tma == 2) {
-                        mbar_arrive_expect_tx(smem_u32(&full[s]), B_STAGE_BYTES + A_STAGE_BYTES);
-                        tma_load_im2col_4d(smem_u32(sA + s * A_STAGE_BYTES), &tmapA, smem_u32(&full[s]), slab * BKE, iw, ih, in,
-                                           (uint16_t)tap_w, (uint16_t)tap_h);
+                        for (int h = 0; h < halves; h++)
+                            tma_load_im2col_4d(smem_u32(sA + s * a_stage_bytes + h * A_STAGE_BYTES), &tmapA, bar, slab * BKE, iw[h],
+                                               ih[h], in[h], (uint16_t)tap_w, (uint16_t)tap_h);
                         if (++slab == p.slabs) {
                             slab = 0;
                             if (++tap_w == p.tma_kw) { tap_w = 0; tap_h++; }
                         }
-                    } else
-                        mbar_arrive_expect_tx(smem_u32(&full[s]), B_STAGE_BYTES);
-                    tma_load_2d(smem_u32(sB + s * B_STAGE_BYTES), &tmapW, smem_u32(&full[s]), kb * BKE, n0);
+                    }
+                    tma_load_2d(smem_u32(sB + s * B_STAGE_BYTES), &tmapW, bar, kb * BKE, n0);
                 }
             }
         }
@@ -554,20 +597,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
     } else if (warp == 5) {
         // ================================================================== MMA issuer
         if (lane == 0) {
-            int it = 0, lt = 0, ring_s = 0;
+            const TileMap<BN> map(p);
+            const int halves = pair ? 2 : 1;
+            int ring_s = 0;
             uint32_t ring_ph = 0;
             bool alive = true;
-            for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, lt++) {
-                const int b = lt % NACC;
-                const uint32_t acc_ph = (lt / NACC) & 1;
-                if (!mbar_wait_bounded(smem_u32(&acc_empty[b]), acc_ph ^ 1)) {
-                    atomicExch(p.status, 6);
-                    *abort_flag = 1;
-                    break;
-                }
+            for (int lt = 0; lt < map.n_local && alive; lt += halves) {
+                // the accumulators of this unit's local tiles (two in pair mode) must have been drained
+                for (int h = 0; h < halves && alive; h++)
+                    if (!mbar_wait_bounded(smem_u32(&acc_empty[(lt + h) % NACC]), (((lt + h) / NACC) & 1) ^ 1)) {
+                        atomicExch(p.status, 6);
+                        *abort_flag = 1;
+                        alive = false;
+                    }
+                if (!alive) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + b * BN;
-                for (int kb = 0; kb < p.nkb; kb++, it++) {
+                const uint32_t d0 = tmem_base + (lt % NACC) * BN, d1 = tmem_base + ((lt + 1) % NACC) * BN;
+                for (int kb = 0; kb < p.nkb; kb++) {
                     const int s = ring_s;
                     const uint32_t ph = ring_ph;
                     if (++ring_s == nst) { ring_s = 0; ring_ph ^= 1; }
@@ -579,17 +625,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     }
                     tc_fence_after();
                     fence_proxy_async_smem();
-                    const uint64_t adesc = make_sw128_kmajor_desc(smem_u32(sA + s * A_STAGE_BYTES));
+                    const uint64_t adesc = make_sw128_kmajor_desc(smem_u32(sA + s * a_stage_bytes));
                     const uint64_t bdesc = make_sw128_kmajor_desc(smem_u32(sB + s * B_STAGE_BYTES));
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
                         const uint32_t accum = (kb | k) != 0;
-                        if (KIND == 2) tc_mma_i8(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, accum);
-                        else tc_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, accum);
+                        if (KIND == 2) tc_mma_i8(d0, adesc + 2 * k, bdesc + 2 * k, IDESC, accum);
+                        else tc_mma_f16(d0, adesc + 2 * k, bdesc + 2 * k, IDESC, accum);
+                    }
+                    if (pair) {
+                        // the second half's tile lies A_STAGE_BYTES further on (1024 in the descriptor's 16-byte units)
+#pragma unroll
+                        for (int k = 0; k < 4; k++)
+                            tc_mma_f16(d1, adesc + (A_STAGE_BYTES >> 4) + 2 * k, bdesc + 2 * k, IDESC, (uint32_t)((kb | k) != 0));
                     }
                     tc_commit(smem_u32(&empty[s]));
                 }
-                if (alive) tc_commit(smem_u32(&acc_full[b]));
+                if (alive)
+                    for (int h = 0; h < halves; h++) tc_commit(smem_u32(&acc_full[(lt + h) % NACC]));
             }
         }
         __syncwarp();
@@ -601,7 +654,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
         const int et = tid - 192 - grp * 128;  // 0..127 within the group
         if constexpr (L::TMA_EPI) {
             epilogue_tma<KIND, BN, NACC>(p, grp, warp, lane, tmem_base, stage_buf + grp * p.epi_bufs * EPI_TILE_BYTES, acc_full,
-                                         acc_empty, rows_ready + grp * 3, avail + grp * 3, abort_flag, total_tiles);
+                                         acc_empty, rows_ready + grp * 3, avail + grp * 3, abort_flag);
             goto done;
         }
         const int quad = warp & 3;             // TMEM lane quadrant this warp may read
@@ -849,9 +902,16 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
         if (e != cudaSuccess) return thb_note_launch(e, "conv_tc smem attribute");
         configured[dev] = true;
     }
-    const int tiles = p.m_tiles * p.n_tiles;
-    const int grid = tiles < num_sms() ? tiles : num_sms();
     using L = Smem<KIND, BN, STAGES>;
+    // Pair mode (see ConvTcParams::pair): narrow tiles with a K loop long enough to be bound by the MMA thread's barrier
+    // rounds, and at least two units of work per SM.
+    int pair_min_kb = 2;
+    if (const char *e = getenv("THB200_PAIR_MIN_KB")) pair_min_kb = atoi(e);
+    long pair_min_units = 2L * num_sms();
+    if (const char *e = getenv("THB200_PAIR_MIN_UNITS")) pair_min_units = atol(e);  // (tests exercise the mode on small shapes)
+    p.pair = L::TMA_EPI && p.a_tma && BN <= 128 && p.nkb >= pair_min_kb && (long)(p.m_tiles / 2) * p.n_tiles >= pair_min_units;
+    const int tiles = (p.pair ? (p.m_tiles + 1) / 2 : p.m_tiles) * p.n_tiles;  // units of work
+    const int grid = tiles < num_sms() ? tiles : num_sms();
     if (L::TMA_EPI) {
         if (!tm.y || (p.res && !tm.r)) return thb_note_launch(cudaErrorUnknown, "conv_tc: output tensor map");
         // warps 0-3 join the epilogue when they have nothing to gather and a third accumulator exists for them
@@ -861,9 +921,11 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
         // group and every remaining byte in pipeline stages.
         p.epi_bufs = p.nkb >= 6 ? 1 : (p.epi_groups == 2 && BN < 256 ? 3 : 2);
         if (const char *e = getenv("THB200_EPI_BUFS")) p.epi_bufs = atoi(e) < 1 ? 1 : atoi(e) > 3 ? 3 : atoi(e);
-        while ((size_t)STAGES * L::STAGE_BYTES + (size_t)p.epi_groups * p.epi_bufs * EPI_TILE_BYTES > L::AVAIL) p.epi_bufs--;
+        const size_t stage_bytes = L::STAGE_BYTES + (p.pair ? A_STAGE_BYTES : 0);
+        const int min_stages = p.pair ? 2 : STAGES;
+        while (min_stages * stage_bytes + (size_t)p.epi_groups * p.epi_bufs * EPI_TILE_BYTES > L::AVAIL) p.epi_bufs--;
         if (p.epi_bufs < 1) return thb_note_launch(cudaErrorUnknown, "conv_tc: shared-memory plan");
-        p.stages = (int)((L::AVAIL - (size_t)p.epi_groups * p.epi_bufs * EPI_TILE_BYTES) / L::STAGE_BYTES);
+        p.stages = (int)((L::AVAIL - (size_t)p.epi_groups * p.epi_bufs * EPI_TILE_BYTES) / stage_bytes);
         if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
         if (!p.a_tma) p.stages = STAGES;  // the gather's cp.async depth is tied to the compile-time count
     }
