@@ -905,7 +905,7 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
     using L = Smem<KIND, BN, STAGES>;
     // Pair mode (see ConvTcParams::pair): narrow tiles with a K loop long enough to be bound by the MMA thread's barrier
     // rounds, and at least two units of work per SM.
-    int pair_min_kb = 2;
+    int pair_min_kb = 1;
     if (const char *e = getenv("THB200_PAIR_MIN_KB")) pair_min_kb = atoi(e);
     long pair_min_units = 2L * num_sms();
     if (const char *e = getenv("THB200_PAIR_MIN_UNITS")) pair_min_units = atol(e);  // (tests exercise the mode on small shapes)
