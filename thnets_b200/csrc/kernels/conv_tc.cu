@@ -2,7 +2,7 @@
 //
 // GEMM view: D[pixel][cout] = sum_k A[pixel][k] * Wt[cout][k], k = tap*Cin_pad + c.
 // One PERSISTENT CTA per SM walks output tiles of 128 consecutive pixels (flat over n, oh, ow: tiles
-// may span rows and images, so small feature maps waste nothing) x BN output channels.  Fourteen warps:
+// may span rows and images, so small feature maps waste nothing) x BN output channels.  Fifteen warps:
 //   warp  4    TMA producer: packed weights (K-major, SWIZZLE_128B, no multicast) and -- whenever a K block is
 //              one whole 128-byte channel slab of one tap -- the activation operand too: a plain 2-D load for
 //              1x1 stride-1 convolutions, an im2col-mode load (the copy engine walks the 128 output pixels,
@@ -12,13 +12,16 @@
 //              are a third epilogue group;
 //   warp  5    MMA issuer: one elected thread issues tcgen05.mma (kind::f16: fp16/bf16 -> fp32,
 //              kind::i8: u8 x u8 -> int32) into one of 2-4 TMEM accumulators, recycles stages through
-//              tcgen05.commit -> mbarrier, and hands finished accumulators to the epilogue;
-//   warps 6-13 two epilogue groups; a group drains its tile's accumulator 64 columns at a time with
-//              tcgen05.ld (TMEM lane = pixel), applies bias/BN scale-shift, residual and activation, and
-//              leaves the fp16/bf16 rows in a swizzled shared-memory tile that one thread hands to a TMA
-//              store; the residual tile is prefetched into that same shared-memory tile by TMA two blocks
-//              ahead, so no epilogue thread ever waits on global memory.  The uint8 path (exact lowp
-//              requantisation) and BN = 32 stage through shared memory and write out with plain stores.
+//              tcgen05.commit -> mbarrier, and hands finished accumulators to the epilogue.  With narrow
+//              tiles it works on two pixel tiles at once (pair mode), which share every weight tile and
+//              every barrier round;
+//   warps 6-13 two epilogue groups; a thread owns one pixel row (TMEM lane): it reads 64 accumulator
+//              columns with tcgen05.ld, applies bias/BN scale-shift, residual and activation, and leaves the
+//              fp16/bf16 row in a swizzled shared-memory tile.  It never waits on global memory or on the
+//              other threads of its group.  The uint8 path (exact lowp requantisation) and BN = 32 stage
+//              through shared memory and write out with plain stores;
+//   warp 14    epilogue agents, one thread per group: TMA load of the fused residual tile into the group's
+//              shared-memory tile, TMA store of the finished tile, recycling of the tile.
 // No im2col buffer exists anywhere.  Every wait is bounded: a wait that runs out records a code in
 // *status and the CTA drains and exits.
 #include "common.cuh"
