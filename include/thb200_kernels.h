@@ -13,6 +13,11 @@
  *
  * Each entry point names the reference operator it replaces (file:line within the
  * reference project).
+ *
+ * Threading: the launch functions keep small host-side caches (TMA descriptors by buffer
+ * and shape, per-device kernel attributes) without locks, as the reference's engines
+ * keep their state: call them from one host thread at a time.  Everything they enqueue
+ * goes to the stream they are given; nothing synchronises the device.
  */
 #ifndef THB200_KERNELS_H
 #define THB200_KERNELS_H

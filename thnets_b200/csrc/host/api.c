@@ -14,6 +14,7 @@
  * (fp32 mode) and for PyTorch-dump networks, which the reference cannot convert at all.
  */
 #include <math.h>
+#include <stdarg.h>
 #include <stdio.h>
 #include <string.h>
 #include <strings.h>
@@ -390,33 +391,46 @@ THFloatTensor *thb_module_updateOutput(struct module *m, THFloatTensor *in)
 }
 
 /* Text dump of the lowered operator list (one line per node): used by host-side tests and for debugging. */
+/* bounded formatted append: never writes past buf[len - 1]; returns the new length (at most len - 1) */
+static int describe_append(char *buf, int len, int pos, const char *fmt, ...)
+{
+    if (pos >= len - 1) return len - 1;
+    va_list ap;
+    va_start(ap, fmt);
+    int w = vsnprintf(buf + pos, (size_t)(len - pos), fmt, ap);
+    va_end(ap);
+    if (w < 0) return pos;
+    return pos + w >= len ? len - 1 : pos + w;
+}
+
 int THB200_DescribeNetwork(THNETWORK *network, char *buf, int len)
 {
     static const char *names[] = {"input", "conv", "deconv", "linear", "bn", "act", "maxpool", "avgpool", "combine",
                                   "concat", "softmax", "view", "alias", "scale"};
     char err[256] = "";
+    if (!buf || len < 2) return -1;
     thb_model *m = thb_model_from_network(network, err, sizeof(err));
     if (!m) { snprintf(buf, len, "error: %s", err); return -1; }
     int pos = 0;
-    for (int i = 0; i < m->nnodes && pos < len - 1; i++) {
+    buf[0] = 0;
+    for (int i = 0; i < m->nnodes; i++) {
         thb_node *n = &m->nodes[i];
-        pos += snprintf(buf + pos, len - pos, "%d %s in=", i, names[n->op]);
-        for (int k = 0; k < n->nin && pos < len - 1; k++) pos += snprintf(buf + pos, len - pos, "%s%d", k ? "," : "", n->in[k]);
-        if (pos >= len - 1) break;
+        pos = describe_append(buf, len, pos, "%d %s in=", i, names[n->op]);
+        for (int k = 0; k < n->nin; k++) pos = describe_append(buf, len, pos, "%s%d", k ? "," : "", n->in[k]);
         if (n->op == OP_CONV || n->op == OP_DECONV || n->op == OP_LINEAR)
-            pos += snprintf(buf + pos, len - pos, " %d->%d k%dx%d s%d,%d p%d,%d bias=%d", n->Cin, n->Cout, n->kH, n->kW, n->dH,
-                            n->dW, n->padH, n->padW, n->bias != 0);
+            pos = describe_append(buf, len, pos, " %d->%d k%dx%d s%d,%d p%d,%d bias=%d", n->Cin, n->Cout, n->kH, n->kW, n->dH, n->dW,
+                                  n->padH, n->padW, n->bias != 0);
         else if (n->op == OP_MAXPOOL || n->op == OP_AVGPOOL)
-            pos += snprintf(buf + pos, len - pos, " k%dx%d s%d,%d p%d,%d ceil=%d", n->kH, n->kW, n->dH, n->dW, n->padH, n->padW, n->ceil_mode);
+            pos = describe_append(buf, len, pos, " k%dx%d s%d,%d p%d,%d ceil=%d", n->kH, n->kW, n->dH, n->dW, n->padH, n->padW, n->ceil_mode);
         else if (n->op == OP_COMBINE)
-            for (int k = 0; k < n->nin && pos < len - 1; k++) pos += snprintf(buf + pos, len - pos, " %+g", n->coef[k]);
-        else if (n->op == OP_VIEW) pos += snprintf(buf + pos, len - pos, " %d", n->numElements);
-        else if (n->op == OP_ACT) pos += snprintf(buf + pos, len - pos, " kind=%d th=%g val=%g", n->act_kind, n->act_threshold, n->act_value);
-        else if (n->op == OP_CONCAT) pos += snprintf(buf + pos, len - pos, " dim=%d", n->dim);
-        if (pos < len - 1) pos += snprintf(buf + pos, len - pos, "%s\n", i == m->output ? " <- output" : "");
+            for (int k = 0; k < n->nin; k++) pos = describe_append(buf, len, pos, " %+g", n->coef[k]);
+        else if (n->op == OP_VIEW) pos = describe_append(buf, len, pos, " %d", n->numElements);
+        else if (n->op == OP_ACT) pos = describe_append(buf, len, pos, " kind=%d th=%g val=%g", n->act_kind, n->act_threshold, n->act_value);
+        else if (n->op == OP_CONCAT) pos = describe_append(buf, len, pos, " dim=%d", n->dim);
+        pos = describe_append(buf, len, pos, "%s\n", i == m->output ? " <- output" : "");
     }
     thb_model_release(m);
-    return m ? pos : -1;
+    return pos;
 }
 
 int THB200_ProfileForward(THNETWORK *network, int iters, int max_steps, int *kinds, float *ms, double *flops)
