@@ -228,6 +228,7 @@ def main():
     th = THNets()
     lib = th.lib
     lib.THB200_ProfileForward.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.THB200_ProfileForwardBytes.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
     lib.THB200_KernelLaunches.restype = C.c_int
 
     tmp = tempfile.TemporaryDirectory()
@@ -315,6 +316,15 @@ def main():
                 "frac": ach / (peaks["tflops"] * (2 if dtype == "int8" else 1)), "peak_source": "of " + peaks["src"],
                 "traffic": NCU_DRAM_BYTES_PER_STEP.get((args.workload, dtype, batch)), "launches_per_step": nconv, "kernel_ms_per_step": conv_ms, "share_of_step": conv_ms / tot_ms if tot_ms else None,
                 "flops_per_step": conv_fl}
+        # the bound a forward of this network cannot beat when every launch ran at the slower of its two roofs
+        # (algorithmic FLOPs / measured tensor peak, algorithmic bytes / measured HBM copy bandwidth)
+        by = (C.c_double * maxs)()
+        if lib.THB200_ProfileForwardBytes(net, maxs, by) == nst and peaks["hbm"]:
+            tpk = peaks["tflops"] * 1e12 * (2 if dtype == "int8" else 1)
+            bound_ms = sum(max(fl[i] / tpk, by[i] / (peaks["hbm"] * 1e9)) for i in range(nst) if kinds[i] == 0) * 1e3
+            hbm_launches = sum(1 for i in range(nst) if kinds[i] == 0 and by[i] / (peaks["hbm"] * 1e9) > fl[i] / tpk)
+            roof["two_roof_bound"] = {"kernel_ms_per_step": bound_ms, "frac": bound_ms / conv_ms if conv_ms else None,
+                                      "hbm_bound_launches": hbm_launches, "bytes_per_step": sum(by[i] for i in range(nst) if kinds[i] == 0)}
 
     if rank == 0:
         out = {"metric": "images_per_second", "value": world * batch / (ms_step * 1e-3), "unit": "images/s", "n_gpus": world,

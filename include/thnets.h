@@ -266,6 +266,9 @@ float THB200_TimeForward(THNETWORK *network, int iters);
  * 0 for a convolution / Linear-as-convolution launch, 1 for a GEMV, 2 otherwise; flops[t] its algorithmic FLOPs.
  * Returns the number of launches described (<= max_steps), < 0 on error. */
 int THB200_ProfileForward(THNETWORK *network, int iters, int max_steps, int *kinds, float *ms, double *flops);
+/* bytes[t]: algorithmic bytes of launch t of the same list (input, output, residual and weights counted once each at the
+ * storage type's size) for convolution and GEMV launches, 0 for the others.  Returns the number described. */
+int THB200_ProfileForwardBytes(THNETWORK *network, int max_steps, double *bytes);
 /* the contiguous slice [offset, offset+count) of an N-image batch that GPU g of G processes */
 void THB200_SliceBatch(int N, int G, int g, int *offset, int *count);
 int THB200_KernelLaunches(void);

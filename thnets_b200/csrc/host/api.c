@@ -437,6 +437,10 @@ int THB200_ProfileForward(THNETWORK *network, int iters, int max_steps, int *kin
 {
     return thb_engine_profile(netx(network)->engine, iters, max_steps, kinds, ms, flops);
 }
+int THB200_ProfileForwardBytes(THNETWORK *network, int max_steps, double *bytes)
+{
+    return thb_engine_profile_bytes(netx(network)->engine, max_steps, bytes);
+}
 void THB200_SliceBatch(int N, int G, int g, int *offset, int *count) { thb_slice_batch(N, G, g, offset, count); }
 float THB200_LastDeviceMs(THNETWORK *network) { return thb_engine_last_ms(netx(network)->engine); }
 float THB200_TimeForward(THNETWORK *network, int iters) { return thb_engine_time_forward(netx(network)->engine, iters); }

@@ -1039,6 +1039,30 @@ int thb_engine_profile(thb_engine *E, int iters, int max_steps, int *kinds, floa
     return rc ? -1 : n;
 }
 
+/* Algorithmic bytes of each planned launch on the first GPU: every tensor the launch names counted once (input, output,
+ * residual, weights) at the storage type's size; 0 for launches that are neither a convolution nor a GEMV.  The
+ * companion of thb_engine_profile's flops for a per-launch "slower of the two roofs" bound. */
+int thb_engine_profile_bytes(thb_engine *E, int max_steps, double *bytes)
+{
+    if (!E || !E->built) return -1;
+    instance *I = &E->inst[0];
+    const int n = I->nsteps < max_steps ? I->nsteps : max_steps;
+    for (int t = 0; t < n; t++) {
+        step *s = &I->steps[t];
+        const double el = s->dtype == THB_F32 ? 4 : s->dtype == THB_U8 ? 1 : 2;
+        bytes[t] = 0;
+        if (s->kind == ST_CONV) {
+            const thb_conv_desc *d = &s->conv;
+            const double out = (double)d->N * d->oH * d->oW * d->Cout;
+            bytes[t] = el * ((double)d->N * d->H * d->W * d->Cin + out * (d->res ? 2 : 1) +
+                             (double)d->Cout * d->Cin * d->kH * d->kW);
+        } else if (s->kind == ST_GEMV) {
+            bytes[t] = el * ((double)s->M * s->K + (double)s->N * (s->K + s->M));
+        }
+    }
+    return n;
+}
+
 /* ================================================================================================ */
 thb_engine *thb_engine_create(thb_model *model, int mode, float lowp_range, int ngpus)
 {

@@ -76,6 +76,7 @@ int thb_engine_forward(thb_engine *e, float *x, unsigned char **images, int stri
 float thb_engine_last_ms(thb_engine *e);
 float thb_engine_time_forward(thb_engine *e, int iters);
 int thb_engine_profile(thb_engine *e, int iters, int max_steps, int *kinds, float *ms, double *flops);
+int thb_engine_profile_bytes(thb_engine *e, int max_steps, double *bytes);
 void thb_slice_batch(int N, int G, int g, int *offset, int *count);
 const char *thb_engine_error(void);
 void thb_set_error(const char *fmt, ...);

@@ -1,6 +1,6 @@
 // Batch-small Linear (N <= 8 rows of x): y[n][m] = act((sum_k W[m][k] x[n][k]) * scale[m] + shift[m]).
-// HBM-bound on the weight matrix: one warp per output row streams W[m][:] once with 16-byte loads
-// (four in flight per lane), keeps the x rows in L1/L2, accumulates in fp32 and reduces by shuffles.
+// HBM-bound on the weight matrix: W is streamed once with 16-byte loads (four to eight in flight per thread), the x rows
+// stay in L1/L2, sums are fp32.
 #include "common.cuh"
 
 namespace {
@@ -38,52 +38,97 @@ template <> struct V16<__nv_bfloat16> {
     }
 };
 
+// One CTA per weight row at a time, rows taken with a grid stride by a grid that is resident all at once.  Each thread owns
+// the vectors tid, tid+256, ... of a row in batches of U; the batch after the one being accumulated is already in flight
+// (two register buffers, running on into the CTA's next row), so the stream of loads never drains at a row's end.
 template <typename T, int NB>
-__global__ void __launch_bounds__(256) gemv_kernel(const T *x, int K, int x_ld, const T *w, int M, const float *scale,
-                                                   const float *shift, thb_act act, T *y, int y_ld)
-{
-    constexpr int VN = V16<T>::N;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m = blockIdx.x * 8 + warp;
-    if (m >= M) {
-        // channels of the padded tail of y are kept at exact zero
-        if (m < (M + VN - 1) / VN * VN && m < y_ld && lane == 0)
-            for (int n = 0; n < NB; n++) dt<T>::st(y + (size_t)n * y_ld + m, 0.f);
-        return;
+struct GemvWalk {
+    static constexpr int VN = V16<T>::N, U = 4;
+    const uint4 *w;
+    int nvec, nbatch, M, stride;
+    int row, b;  // next batch to load: row and batch index inside the row
+    __device__ __forceinline__ void load(uint4 (&buf)[U])
+    {
+        if (row >= M) return;
+        const uint4 *wr = w + (size_t)row * nvec;
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int v = (b * U + u) * 256 + threadIdx.x;
+            buf[u] = v < nvec ? __ldcs(wr + v) : make_uint4(0, 0, 0, 0);
+        }
+        if (++b == nbatch) { b = 0; row += stride; }
     }
-    const uint4 *wr = reinterpret_cast<const uint4 *>(w + (size_t)m * K);
+};
+
+template <typename T, int NB>
+__global__ void __launch_bounds__(256, 4) gemv_kernel(const T *x, int K, int x_ld, const T *w, int M, const float *scale,
+                                                      const float *shift, thb_act act, T *y, int y_ld)
+{
+    constexpr int VN = V16<T>::N, U = GemvWalk<T, NB>::U;
+    __shared__ float part[2][8][NB];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (blockIdx.x == 0) {
+        // channels of the padded tail of y are kept at exact zero
+        const int m = M + threadIdx.x;
+        if (m < (M + VN - 1) / VN * VN && m < y_ld)
+            for (int n = 0; n < NB; n++) dt<T>::st(y + (size_t)n * y_ld + m, 0.f);
+    }
     const int nvec = K / VN;
+    GemvWalk<T, NB> walk{reinterpret_cast<const uint4 *>(w), nvec, (nvec + U * 256 - 1) / (U * 256), M, (int)gridDim.x,
+                         (int)blockIdx.x, 0};
+    uint4 buf0[U], buf1[U];
     float acc[NB];
 #pragma unroll
     for (int n = 0; n < NB; n++) acc[n] = 0.f;
-    for (int v0 = lane; v0 < nvec; v0 += 128) {
-        uint4 wv[4];
+    int crow = blockIdx.x, cb = 0, parity = 0;
+
+    auto consume = [&](const uint4 (&buf)[U]) {
 #pragma unroll
-        for (int u = 0; u < 4; u++)
-            wv[u] = (v0 + u * 32 < nvec) ? __ldcs(wr + v0 + u * 32) : make_uint4(0, 0, 0, 0);
+        for (int u = 0; u < U; u++) {
+            const int v = (cb * U + u) * 256 + threadIdx.x;
+            if (v < nvec) {
+                float wf[VN];
+                V16<T>::unpack(buf[u], wf);
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
-            if (v0 + u * 32 >= nvec) break;
-            float wf[VN];
-            V16<T>::unpack(wv[u], wf);
+                for (int n = 0; n < NB; n++) {
+                    float xf[VN];
+                    V16<T>::unpack(*reinterpret_cast<const uint4 *>(x + (size_t)n * x_ld + (size_t)v * VN), xf);
 #pragma unroll
-            for (int n = 0; n < NB; n++) {
-                float xf[VN];
-                V16<T>::unpack(*reinterpret_cast<const uint4 *>(x + (size_t)n * x_ld + (size_t)(v0 + u * 32) * VN), xf);
-#pragma unroll
-                for (int i = 0; i < VN; i++) acc[n] = fmaf(wf[i], xf[i], acc[n]);
+                    for (int i = 0; i < VN; i++) acc[n] = fmaf(wf[i], xf[i], acc[n]);
+                }
             }
         }
-    }
+        if (++cb < walk.nbatch) return;
+        // the row is complete: warp sums, then warp 0 adds the eight partial sums (buffers alternate between rows, so
+        // one barrier per row is enough)
 #pragma unroll
-    for (int n = 0; n < NB; n++)
-        for (int o = 16; o > 0; o >>= 1) acc[n] += __shfl_xor_sync(0xffffffffu, acc[n], o);
-    if (lane == 0) {
-        const float sc = scale ? scale[m] : 1.f, sh = shift ? shift[m] : 0.f;
-        const float sl = act.kind == THB_ACT_PRELU ? act.slope[m] : 0.f;
+        for (int n = 0; n < NB; n++) {
+            for (int o = 16; o > 0; o >>= 1) acc[n] += __shfl_xor_sync(0xffffffffu, acc[n], o);
+            if (lane == 0) part[parity][warp][n] = acc[n];
+            acc[n] = 0.f;
+        }
+        __syncthreads();
+        if (threadIdx.x < NB) {
+            const int n = threadIdx.x, m = crow;
+            float s = 0.f;
 #pragma unroll
-        for (int n = 0; n < NB; n++)
-            dt<T>::st(y + (size_t)n * y_ld + m, thb_apply_act(acc[n] * sc + sh, act.kind, act.threshold, act.value, act.alpha, sl));
+            for (int q = 0; q < 8; q++) s += part[parity][q][n];
+            const float sc = scale ? scale[m] : 1.f, sh = shift ? shift[m] : 0.f;
+            const float sl = act.kind == THB_ACT_PRELU ? act.slope[m] : 0.f;
+            dt<T>::st(y + (size_t)n * y_ld + m, thb_apply_act(s * sc + sh, act.kind, act.threshold, act.value, act.alpha, sl));
+        }
+        parity ^= 1;
+        cb = 0;
+        crow += gridDim.x;
+    };
+
+    walk.load(buf0);
+    while (crow < M) {
+        walk.load(buf1);
+        consume(buf0);
+        if (crow >= M) break;
+        walk.load(buf0);
+        consume(buf1);
     }
 }
 
@@ -91,7 +136,14 @@ template <typename T>
 int launch_gemv(const void *x, int N, int K, int x_ld, const void *w, int M, const float *scale, const float *shift,
                 thb_act a, void *y, int y_ld, cudaStream_t st)
 {
-    const int grid = (M + 7) / 8 + 1;
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    const int grid = M < 4 * sms ? M : 4 * sms;
 #define GEMV_CASE(NB)                                                                                                   \
     case NB:                                                                                                            \
         gemv_kernel<T, NB><<<grid, 256, 0, st>>>((const T *)x, K, x_ld, (const T *)w, M, scale, shift, a, (T *)y, y_ld); \
