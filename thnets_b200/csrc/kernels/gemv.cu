@@ -43,7 +43,7 @@ template <> struct V16<__nv_bfloat16> {
 // (two register buffers, running on into the CTA's next row), so the stream of loads never drains at a row's end.
 template <typename T, int NB>
 struct GemvWalk {
-    static constexpr int VN = V16<T>::N, U = 4;
+    static constexpr int U = 4;
     const uint4 *w;
     int nvec, nbatch, M, stride;
     int row, b;  // next batch to load: row and batch index inside the row
