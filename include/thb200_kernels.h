@@ -149,6 +149,11 @@ int thb_affine_act(int dtype, const void *x, long pixels, int C, int x_ld, const
                    const thb_act *act, void *y, int y_ld, thb_stream s);
 /* u8 threshold: q > thr ? q : val (lowp/lowp_Threshold.c:3-28) */
 int thb_u8_threshold(const void *x, long pixels, int C, int x_ld, int thr, int val, void *y, int y_ld, thb_stream s);
+/* uint8 ca*a + cb*b (ca, cb = +1 or -1) of tensors on the static quantisation sub = -range/2, mult = 255/range, then an
+ * optional Threshold (thr < 0: none): y = sat_u8(floor(ca*qa + cb*qb - (ca + cb - 1)*127.5)).  No counterpart in the
+ * reference (its lowp engine converts no CAddTable, lowp/lowp_basic.c:150-208); an extension for residual networks. */
+int thb_u8_combine(const void *a, int a_ld, const void *b, int b_ld, int ca, int cb, int thr, int val, long pixels, int C,
+                   void *y, int y_ld, thb_stream s);
 /* y = sum_i coef[i]*x[i], evaluated left to right (CAddTable.c:32-86) */
 int thb_combine(int dtype, int nin, const void *const *x_host, const int *ld_host, const float *coef_host,
                 long pixels, int C, void *y, int y_ld, thb_stream s);

@@ -300,12 +300,24 @@ class Oracle:
         return dst, float(sub.value), float(mult.value)
 
     def run_lowp(self, graph, batch, rng, spatial_size, keep=False, quantised_input=None):
-        """uint8 forward of a sequential conv/linear/relu/maxpool graph.
+        """uint8 forward of a conv/linear/relu/maxpool graph.
 
         The input is quantised over the WHOLE batch tensor (lowp_basic.c:15-35); every
         module output uses sub = -range/2, mult = 255/range (lowp_basic.c:137-148); the
         convolution runs per image.  View nodes vanish and Linear nodes become k x k
         convolutions exactly as THMakeSpatial does.
+
+        Beyond what the reference's lowp engine converts (it refuses batch normalisation, average
+        pooling and has no CAddTable, lowp_basic.c:150-208) three rules of this project's own let a
+        residual network run; they have no reference counterpart and are pinned by nothing but this
+        restatement:
+          * conv -> bn: the normalisation is folded into weights and bias BEFORE they are quantised,
+            w' = w*scale, b' = b*scale + shift with scale = gamma/sqrt(var+eps) (double, then float),
+            shift = beta - mean*scale (the algebra of onnx.cc:537-548);
+          * add of two tensors on the static quantisation (CAddTable with two inputs is a - b,
+            CAddTable.c:59-69): sat_u8(qa - qb + 127), the byte the dequantise -> subtract ->
+            THLowp_ScaleFloat chain gives in exact arithmetic (sub*mult = -127.5, truncation);
+          * unpadded average pooling: floor(sum of bytes / window size).
         """
         if quantised_input is not None:      # the image loader's static range instead of the measured one
             q, sub, mult = quantised_input
@@ -313,37 +325,84 @@ class Oracle:
             x = self.normalize(batch, graph.mean, graph.std)
             q, sub, mult = self.lowp_quantize(x)
         osub, omult = np.float32(-rng / 2), np.float32(np.float32(255) / np.float32(rng))
-        size = spatial_size
+        users = {}
+        for i, node in enumerate(graph.nodes):
+            for j in node.inputs:
+                users.setdefault(j, []).append(i)
         vals = {0: (q, sub, mult)}
-        cur = (q, sub, mult)
+
+        def conv_like(node, src, scale=None, shift=None):
+            a = node.attrs
+            ts = [t for _, t in node.tensors]
+            q, sub, mult = src
+            w, b = ts[0], (ts[1] if len(ts) > 1 else None)
+            if scale is not None:
+                w = (w * scale.reshape(-1, *([1] * (w.ndim - 1)))).astype(np.float32)
+                b = ((b * scale if b is not None else np.zeros_like(shift)) + shift).astype(np.float32)
+            if node.op == "linear":
+                cin = q.shape[1]
+                k = int(round((w.shape[1] / cin) ** 0.5))
+                w = w.reshape(w.shape[0], cin, k, k)
+                stride, pad = (1, 1), (0, 0)
+            else:
+                stride, pad = a["stride"], a["padding"]
+            wq, wsub, wmult = self.lowp_quantize(w)
+            bq, bsub, bmult = self.lowp_quantize(b)
+            y = self.lowp_conv(q, sub, mult, wq, wsub, wmult, bq, bsub, bmult, stride, pad, float(osub), float(omult))
+            return (y, float(osub), float(omult))
+
+        cur = vals[0]
         for i, node in enumerate(graph.nodes):
             if i == 0:
                 continue
             a = node.attrs
             ts = [t for _, t in node.tensors]
-            q, sub, mult = cur
+            src = vals[node.inputs[0]]
             if node.op in ("conv", "linear"):
-                w, b = ts[0], ts[1]
-                if node.op == "linear":
-                    cin = q.shape[1]
-                    k = int(round((w.shape[1] / cin) ** 0.5))
-                    w = w.reshape(w.shape[0], cin, k, k)
-                    stride, pad = (1, 1), (0, 0)
+                u = users.get(i, [])
+                if len(u) == 1 and graph.nodes[u[0]].op == "bn":
+                    cur = None           # computed at the batch-norm node, folded
                 else:
-                    stride, pad = a["stride"], a["padding"]
-                wq, wsub, wmult = self.lowp_quantize(w)
-                bq, bsub, bmult = self.lowp_quantize(b)
-                y = self.lowp_conv(q, sub, mult, wq, wsub, wmult, bq, bsub, bmult, stride, pad, float(osub), float(omult))
-                cur = (y, float(osub), float(omult))
+                    cur = conv_like(node, src)
+            elif node.op == "bn":
+                prod = graph.nodes[node.inputs[0]]
+                if prod.op != "conv" or vals[node.inputs[0]] is not None:
+                    raise ValueError("lowp engine folds a batch-norm only into the convolution before it")
+                gamma, beta, mean, var = ts[0], ts[1], ts[2], ts[3]
+                invstd = (1.0 / np.sqrt(var.astype(np.float64) + a["eps"])).astype(np.float32)
+                scale = (invstd * gamma).astype(np.float32)
+                shift = (beta - (mean * scale).astype(np.float32)).astype(np.float32)
+                cur = conv_like(prod, vals[prod.inputs[0]], scale, shift)
             elif node.op == "threshold":
+                q, sub, mult = src
                 cur = (self.lowp_threshold(q, sub, mult, a["threshold"], a["value"]), sub, mult)
             elif node.op == "maxpool":
+                q, sub, mult = src
                 cur = (self.lowp_maxpool(q, a["kernel_size"], a["stride"], a["padding"], a["ceil_mode"]), sub, mult)
+            elif node.op == "avgpool":
+                q, sub, mult = src
+                (kh, kw), (sh, sw) = a["kernel_size"], a["stride"]
+                if tuple(a["padding"]) != (0, 0):
+                    raise ValueError("lowp engine has no padded average pooling")
+                n, c, h, w_ = q.shape
+                oh, ow = (h - kh) // sh + 1, (w_ - kw) // sw + 1
+                y = np.empty((n, c, oh, ow), np.uint8)
+                for r in range(oh):
+                    for t in range(ow):
+                        win = q[:, :, r * sh:r * sh + kh, t * sw:t * sw + kw].astype(np.int64)
+                        y[:, :, r, t] = win.sum(axis=(2, 3)) // (kh * kw)
+                cur = (y, sub, mult)
+            elif node.op == "add":
+                if len(node.inputs) != 2:
+                    raise ValueError("lowp engine adds two tensors")
+                (qa, sa, ma), (qb, sb, mb) = vals[node.inputs[0]], vals[node.inputs[1]]
+                if (sa, ma) != (sb, mb) or sa != float(osub):
+                    raise ValueError("lowp add needs the static output quantisation on both inputs")
+                cur = (np.clip(qa.astype(np.int32) - qb.astype(np.int32) + 127, 0, 255).astype(np.uint8), sa, ma)
             elif node.op in ("view", "dropout"):
-                pass
+                cur = src
             else:
                 raise ValueError("lowp engine has no " + node.op)
             vals[i] = cur
-        _ = size
         out = self.lowp_dequantize(*cur)
         return (out, vals) if keep else out

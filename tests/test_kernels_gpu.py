@@ -473,6 +473,44 @@ def test_pre_and_postprocess(lib, G, oracle, dtype):
         assert np.array_equal(out.cpu().numpy(), got)
 
 
+@pytest.mark.parametrize("coefs", [(1, -1), (1, 1), (-1, 1)])
+@pytest.mark.parametrize("thr", [-1, 127])
+def test_u8_combine(lib, G, coefs, thr):
+    """The uint8 CAddTable of residual networks (no reference counterpart): sat(floor(ca*qa + cb*qb - (ca+cb-1)*127.5)),
+    then the Threshold bytes; padded channels stay zero."""
+    rng = np.random.default_rng(61)
+    n, c, h, w = 2, 20, 5, 7
+    a = rng.integers(0, 256, (n, c, h, w)).astype(np.uint8)
+    b = rng.integers(0, 256, (n, c, h, w)).astype(np.uint8)
+    ca, cb = coefs
+    ref = np.floor(ca * a.astype(np.float64) + cb * b.astype(np.float64) - (ca + cb - 1) * 127.5)
+    ref = np.clip(ref, 0, 255)
+    if thr >= 0:
+        ref = np.where(ref > thr, ref, 127)
+    at, ld = G.to_nhwc(a, K.THB_U8)
+    bt, _ = G.to_nhwc(b, K.THB_U8)
+    y = torch.full((n, h, w, ld), 9, dtype=torch.uint8, device="cuda")
+    rc = lib.thb_u8_combine(G.ptr(at), ld, G.ptr(bt), ld, ca, cb, thr, 127, n * h * w, c, G.ptr(y), ld, None)
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert np.array_equal(G.from_nhwc(y, c), ref.astype(np.uint8))
+    assert int(y[..., c:].max()) == 0
+
+
+def test_u8_avgpool(lib, G):
+    """Unpadded uint8 average pooling = floor(sum / window) (extension for residual networks)."""
+    rng = np.random.default_rng(62)
+    n, c, h, w, k = 3, 40, 7, 7, 7
+    x = rng.integers(0, 256, (n, c, h, w)).astype(np.uint8)
+    ref = (x.astype(np.int64).sum(axis=(2, 3)) // (k * k)).astype(np.uint8).reshape(n, c, 1, 1)
+    xt, ld = G.to_nhwc(x, K.THB_U8)
+    y = torch.zeros((n, 1, 1, ld), dtype=torch.uint8, device="cuda")
+    rc = lib.thb_avgpool(K.THB_U8, G.ptr(xt), n, h, w, c, ld, k, k, k, k, 0, 0, 1, 1, 0, G.ptr(y), ld, None)
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert np.array_equal(G.from_nhwc(y, c), ref)
+
+
 @pytest.mark.parametrize("shape", [(37, 40), (5, 2500), (300, 64), (3, 25088)])
 def test_u8_channel_sum(lib, G, shape):
     """per-pixel sum of the first C bytes (both the thread-per-pixel and the block-per-pixel kernel)"""

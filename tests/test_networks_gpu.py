@@ -110,19 +110,39 @@ def test_lowp_vgg_bit_exact(th, oracle, tmp_path, batch):
 
 
 def test_lowp_rejects_what_the_reference_rejects(th, tmp_path):
-    g = fx.resnet18(width=0.25, size=64, classes=10)
-    h = _load(th, g, "py", tmp_path, "r18")
+    """SpatialFullConvolution and JoinTable have no lowp implementation (lowp_basic.c:197-208)."""
+    g = fx.segnet(width=0.25, size=32, classes=5)
+    h = _load(th, g, "py", tmp_path, "seg")
     hl = th.lib.THCreateLowpNetwork(h, 8.0)
     if hl:
         x = g.make_input(1)
-        n = th.lib.THProcessFloat  # forward must fail: BatchNorm has no lowp implementation
+        n = th.lib.THProcessFloat
         import ctypes as C
         res = C.POINTER(C.c_float)()
         ow, oh = C.c_int(), C.c_int()
-        assert n(hl, x.ctypes.data_as(C.c_void_p), 1, 64, 64, 3, C.byref(res), C.byref(ow), C.byref(oh)) == 0
+        assert n(hl, x.ctypes.data_as(C.c_void_p), 1, 32, 32, 3, C.byref(res), C.byref(ow), C.byref(oh)) == 0
         assert b"lowp" in th.lib.THB200_LastErrorString().lower()
         th.free_network(hl)
     th.free_network(h)
+
+
+@pytest.mark.parametrize("arch,width", [("resnet18", 0.25), ("resnet50", 0.125)])
+@pytest.mark.parametrize("batch", [1, 3])
+def test_lowp_residual_network_bit_exact(th, oracle, tmp_path, arch, width, batch):
+    """uint8 residual networks: an extension with no reference counterpart (the reference's lowp engine refuses batch
+    normalisation and average pooling and converts no CAddTable).  Folded batch-norm, the uint8 a - b of CAddTable and
+    the floor-mean pooling follow the rules stated in oracle.run_lowp; every output byte equals that restatement's."""
+    size, rng = 64, 20.0
+    g = getattr(fx, arch)(width=width, size=size, classes=10, fc_bias=0.05)
+    x = g.make_input(batch)
+    ref = oracle.run_lowp(g, x, rng, size)
+    h = _load(th, g, "py", tmp_path, arch)
+    hl = th.create_lowp_network(h, rng)
+    th.free_network(h)
+    out, _, _ = th.process_float(hl, x)
+    assert np.array_equal(out, ref.ravel()), np.abs(out - ref.ravel()).max()
+    assert len(np.unique(out)) > 3          # the logits are not a saturated constant
+    th.free_network(hl)
 
 
 def test_process_images_matches_float_path(th, oracle, tmp_path):

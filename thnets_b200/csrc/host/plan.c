@@ -72,7 +72,7 @@ typedef struct {
 } abuf;
 
 enum step_kind {
-    ST_CONV, ST_GEMV, ST_MAXPOOL, ST_AVGPOOL, ST_AFFINE, ST_U8THR, ST_COMBINE, ST_COPY, ST_SOFTMAX, ST_COL2IM,
+    ST_CONV, ST_GEMV, ST_MAXPOOL, ST_AVGPOOL, ST_AFFINE, ST_U8THR, ST_U8COMBINE, ST_COMBINE, ST_COPY, ST_SOFTMAX, ST_COL2IM,
     ST_CSUM, ST_TO_NCHW
 };
 
@@ -346,7 +346,11 @@ static int plan_gemm_group(planner *P, int i)
 
     /* ---- what folds in ---- */
     int cur = i, bn = -1, comb = -1, act = -1, j;
-    if (dtype != THB_U8 && !is_deconv && (j = sole_consumer(P, cur)) >= 0 && M->nodes[j].op == OP_BN) { bn = j; cur = j; }
+    /* In uint8 mode a batch normalisation that follows is folded into the weights and the bias BEFORE they are
+     * quantised (w' = w * scale[co], b' = b * scale[co] + shift[co], the algebra of the reference's ONNX loader,
+     * onnx.cc:537-548): the reference's lowp engine itself refuses the module (lowp/lowp_basic.c:194-196). */
+    if (!is_deconv && (j = sole_consumer(P, cur)) >= 0 && M->nodes[j].op == OP_BN) { bn = j; cur = j; }
+    if (bn >= 0 && M->nodes[bn].C != n->Cout) { thb_set_error("batch-norm width mismatch"); return -1; }
     int res_node = -1;
     float self_coef = 1.f, res_coef = 0.f;
     if (dtype != THB_U8 && !is_deconv && (j = sole_consumer(P, cur)) >= 0 && M->nodes[j].op == OP_COMBINE && M->nodes[j].nin == 2) {
@@ -429,6 +433,20 @@ static int plan_gemm_group(planner *P, int i)
     d->self_coef = 1.f; d->res_coef = 0.f; d->relu_thr = -1;
     int Cp_out = ru(n->Cout, al);
     float *w_oihw = n->weight, *w_tmp = 0;
+    float *w_fold = 0, *b_fold = 0; /* uint8: weights and bias with the batch normalisation folded in */
+    const float *bias_eff = n->bias;
+    if (dtype == THB_U8 && bn >= 0) {
+        const size_t per = (size_t)n->Cin * n->kH * n->kW;
+        w_fold = malloc(sizeof(float) * per * n->Cout);
+        b_fold = malloc(sizeof(float) * n->Cout);
+        for (int co = 0; co < n->Cout; co++) {
+            const float sc = M->nodes[bn].scale[co];
+            for (size_t k = 0; k < per; k++) w_fold[co * per + k] = n->weight[co * per + k] * sc;
+            b_fold[co] = (n->bias ? n->bias[co] * sc : 0.f) + M->nodes[bn].shift[co];
+        }
+        w_oihw = w_fold;
+        bias_eff = b_fold;
+    }
     if (is_deconv) {
         /* column matrix [N*H*W][kH*kW*Cp]: column (kh*kW + kw)*Cp + co  <-  W[ci][co][kh][kw] */
         d->Cout = kH * kW * Cp_out; d->kH = d->kW = 1; d->dH = d->dW = 1; d->padH = d->padW = 0;
@@ -441,6 +459,7 @@ static int plan_gemm_group(planner *P, int i)
         w_oihw = w_tmp;
     } else if (is_linear) {
         d->Cout = n->Cout; d->oH = d->oW = 1;
+        if (permute_hw && w_fold) { free(w_fold); free(b_fold); thb_set_error("batch-norm after a flattened Linear is not supported in Lowp"); return -1; }
         if (permute_hw) {
             w_tmp = calloc((size_t)n->Cout * Cin, sizeof(float));
             for (int o = 0; o < n->Cout; o++)
@@ -483,7 +502,7 @@ static int plan_gemm_group(planner *P, int i)
         wsat = malloc(sizeof(int) * d->Cout * (d->kH + 1) * (d->kW + 1));
     }
     int rc = thb_conv_pack_weights_host(d, dtype == THB_U8 ? 0 : w_oihw, wq, packed, kinfo, wsat);
-    free(w_tmp);
+    free(w_tmp); free(w_fold);
     if (!rc) {
         d->w = dupload(P->I, packed, wbytes);
         d->kinfo = dupload(P->I, kinfo, kwords * sizeof(int));
@@ -502,10 +521,11 @@ static int plan_gemm_group(planner *P, int i)
     s->flops_node = i;
 
     if (dtype == THB_U8) {
-        if (!n->bias) { thb_set_error("the lowp engine needs a bias on every convolution"); return -1; }
+        if (!bias_eff) { thb_set_error("the lowp engine needs a bias on every convolution"); return -1; }
         unsigned char *bq = malloc(n->Cout);
         float b_sub, b_mult;
-        thb_lowp_quantize(n->bias, n->Cout, bq, &b_sub, &b_mult);
+        thb_lowp_quantize(bias_eff, n->Cout, bq, &b_sub, &b_mult);
+        free(b_fold);
         if (b_mult == 0) { free(bq); thb_set_error("an all-zero bias has no quantisation range in the lowp engine"); return -1; }
         float out_sub = -E->range / 2, out_mult = 255 / E->range; /* lowp_basic.c:137-138 */
         int *addend = malloc(sizeof(int) * n->Cout);
@@ -576,8 +596,10 @@ static int plan_node(planner *P, int i)
     int j;
 
     if (dtype == THB_U8 && n->op != OP_CONV && n->op != OP_LINEAR && n->op != OP_ACT && n->op != OP_MAXPOOL &&
-        n->op != OP_VIEW && n->op != OP_ALIAS) {
-        /* the reference's lowp conversion rejects these module types too (lowp_basic.c:160-208) */
+        n->op != OP_VIEW && n->op != OP_ALIAS && n->op != OP_AVGPOOL && !(n->op == OP_COMBINE && n->nin == 2)) {
+        /* the reference's lowp conversion rejects these module types too (lowp_basic.c:160-208); beyond it, this engine
+         * takes what a residual network needs: a batch normalisation folded into the convolution before it, the
+         * two-input CAddTable / CSubTable and the average pooling, each on the static output quantisation */
         thb_set_error("operator %d not supported in Lowp", n->op);
         return -1;
     }
@@ -630,6 +652,10 @@ static int plan_node(planner *P, int i)
             if (kH == 0) kH = in->s.H;
             if (!(kW / 2 >= n->padW && kH / 2 >= n->padH)) { thb_set_error("pad should be smaller than half of kernel size"); return -1; }
         }
+        if (dtype == THB_U8 && n->op == OP_AVGPOOL && (n->padH || n->padW || in->q_dyn)) {
+            thb_set_error("padded average pooling is not supported in Lowp");
+            return -1;
+        }
         os.H = pool_out(in->s.H, kH, n->dH, n->padH, n->ceil_mode, n->padH || n->padW);
         os.W = pool_out(in->s.W, kW, n->dW, n->padW, n->ceil_mode, n->padH || n->padW);
         if (os.H < 1 || os.W < 1) { thb_set_error("input image smaller than kernel size"); return -1; }
@@ -642,6 +668,39 @@ static int plan_node(planner *P, int i)
         return 0;
     }
     case OP_COMBINE: {
+        if (dtype == THB_U8) {
+            const value *b = &P->val[n->in[1]];
+            int act = -1;
+            if (in->q_dyn || b->q_dyn || in->q_sub != b->q_sub || in->q_mult != b->q_mult ||
+                in->q_sub != -E->range / 2 || in->s.flat || b->s.flat) {
+                thb_set_error("CAddTable in Lowp needs two tensors on the static output quantisation");
+                return -1;
+            }
+            if (b->s.C != in->s.C || b->s.H != in->s.H || b->s.W != in->s.W || b->s.N != in->s.N) {
+                thb_set_error("Sum of tensors of different sizes");
+                return -1;
+            }
+            if ((n->coef[0] != 1.f && n->coef[0] != -1.f) || (n->coef[1] != 1.f && n->coef[1] != -1.f)) {
+                thb_set_error("only sums and differences are supported in Lowp");
+                return -1;
+            }
+            value *dst = out;
+            if ((j = sole_consumer(P, i)) >= 0 && M->nodes[j].op == OP_ACT && M->nodes[j].act_kind == THB_ACT_THRESHOLD) {
+                act = j; P->absorbed[j] = 1; P->leader[j] = i; dst = &P->val[j];
+            }
+            materialise(P, dst, in->s);
+            dst->q_sub = in->q_sub; dst->q_mult = in->q_mult;
+            s = new_step(P, ST_U8COMBINE);
+            step_in(s, in); step_in(s, b); step_out(s, dst);
+            s->coef[0] = n->coef[0]; s->coef[1] = n->coef[1];
+            s->pixels = (long)in->s.N * in->s.H * in->s.W; s->C = in->s.C;
+            s->thr = -1; s->val = 0;
+            if (act >= 0) {
+                s->thr = thb_lowp_scale_float(in->q_sub, in->q_mult, M->nodes[act].act_threshold);
+                s->val = thb_lowp_scale_float(in->q_sub, in->q_mult, M->nodes[act].act_value);
+            }
+            return 0;
+        }
         materialise(P, out, in->s);
         s = new_step(P, ST_COMBINE);
         for (int k = 0; k < n->nin; k++) {
@@ -925,6 +984,10 @@ static int run_steps_ev(thb_engine *E, instance *I, cudaEvent_t *evs)
             break;
         case ST_AFFINE:
             rc = thb_affine_act(dt, x0, s->pixels, s->C, s->in_ld[0], s->scale, s->shift, &s->act, y, s->out_ld, st);
+            break;
+        case ST_U8COMBINE:
+            rc = thb_u8_combine(x0, s->in_ld[0], bufptr(I, s->in_buf[1], s->in_coff[1], THB_U8), s->in_ld[1], (int)s->coef[0],
+                                (int)s->coef[1], s->thr, s->val, s->pixels, s->C, y, s->out_ld, st);
             break;
         case ST_U8THR:
             rc = thb_u8_threshold(x0, s->pixels, s->C, s->in_ld[0], s->thr, s->val, y, s->out_ld, st);

@@ -29,6 +29,17 @@ extern "C" void thb_count_launches(int n) { g_launches += n; }
 
 static inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
+/* K blocks from which a 256-channel tile is preferred to two 128-channel ones (diagnostic override: THB200_BN256_MIN_KB) */
+static int bn256_min_kb()
+{
+    static int v = 0;
+    if (!v) {
+        const char *e = getenv("THB200_BN256_MIN_KB");
+        v = e && atoi(e) > 0 ? atoi(e) : 4;
+    }
+    return v;
+}
+
 extern "C" int thb_conv_geometry(thb_conv_desc *d)
 {
     if (d->kH < 1 || d->kW < 1 || d->kH > 127 || d->kW > 255 || d->dH < 1 || d->dW < 1 || d->Cin < 1 || d->Cout < 1)
@@ -50,7 +61,7 @@ extern "C" int thb_conv_geometry(thb_conv_desc *d)
         if (d->Cout <= 32) d->BN = 32;
         else if (d->Cout <= 64) d->BN = 64;
         else if (d->Cout <= 128) d->BN = 128;
-        else if (d->Ktot_pad / bke >= 4 && mtiles * ((d->Cout + 255) / 256) >= 148 &&
+        else if (d->Ktot_pad / bke >= bn256_min_kb() && mtiles * ((d->Cout + 255) / 256) >= 148 &&
                  round_up(d->Cout, 256) == round_up(d->Cout, 128)) d->BN = 256; /* wide tiles pay once the K loop outweighs the epilogue and every SM gets a tile */
         else d->BN = 128;
     }

@@ -59,6 +59,8 @@ struct ConvTcParams {
                                // pipeline stage carries both activation tiles and ONE weight tile, and the MMA thread feeds two
                                // accumulators per barrier round: that round costs the thread ~250 cycles whatever it carries,
                                // which a single narrow tile (192-256 tensor cycles per K block) cannot hide.
+    int reverse;               // TMA modes with the TMA epilogue: pixel tiles are walked from the tensor's end, so that a layer
+                               // starts on what the layer before it wrote last and the L2 still holds
     int stages;                // TMA epilogue: pipeline stages (the launcher sizes them against the epilogue tiles)
     int epi_groups, epi_bufs;  // TMA epilogue: groups at work (2 or 3) and 16 KB tiles each of them cycles through
     int row_pitch, pad_left;  // gather: pixels between input rows, zero pixels in front of each row (W, 0 when plain)
@@ -205,11 +207,12 @@ struct EpiCursor {
 // tiles with the same column tile; local tiles 2i and 2i+1 are the halves of its i-th unit.  A second half beyond
 // the last pixel tile (odd tile count) is a phantom: it is computed from zero-filled loads and never stored.
 template <int BN> struct TileMap {
-    int pair, n_tiles, n_local;
+    int pair, n_tiles, n_local, last_um;
     __device__ TileMap(const ConvTcParams &p)
     {
         pair = p.pair;
         n_tiles = p.n_tiles;
+        last_um = p.reverse ? (pair ? (p.m_tiles + 1) >> 1 : p.m_tiles) - 1 : -1;
         const int units = (pair ? (p.m_tiles + 1) >> 1 : p.m_tiles) * n_tiles;
         const int mine = (int)blockIdx.x < units ? (units - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
         n_local = pair ? 2 * mine : mine;
@@ -217,8 +220,9 @@ template <int BN> struct TileMap {
     __device__ void coords(int lt, int &m0, int &n0) const
     {
         const int u = blockIdx.x + (pair ? lt >> 1 : lt) * gridDim.x;
-        const int um = u / n_tiles;
+        int um = u / n_tiles;
         n0 = (u - um * n_tiles) * BN;
+        if (last_um >= 0) um = last_um - um;  // walk the pixel tiles from the end of the tensor
         m0 = (pair ? 2 * um + (lt & 1) : um) * BM;
     }
 };
@@ -913,6 +917,18 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
     long pair_min_units = 2L * num_sms();
     if (const char *e = getenv("THB200_PAIR_MIN_UNITS")) pair_min_units = atol(e);  // (tests exercise the mode on small shapes)
     p.pair = L::TMA_EPI && p.a_tma && BN <= 128 && p.nkb >= pair_min_kb && (long)(p.m_tiles / 2) * p.n_tiles >= pair_min_units;
+    {
+        // Every second convolution launch of a host thread walks its pixel tiles backwards: consecutive layers then
+        // start on the end of the tensor the layer before has just written, which the L2 still holds (1.3 % of a
+        // ResNet-50 forward).  THB200_REVERSE=0 switches it off, 2 reverses every launch.
+        static int rev_mode = -1;
+        static thread_local unsigned flip = 0;
+        if (rev_mode < 0) {
+            const char *e = getenv("THB200_REVERSE");
+            rev_mode = e ? atoi(e) : 1;
+        }
+        p.reverse = L::TMA_EPI && p.a_tma && (rev_mode == 1 ? (flip++ & 1) : rev_mode == 2);
+    }
     const int tiles = (p.pair ? (p.m_tiles + 1) / 2 : p.m_tiles) * p.n_tiles;  // units of work
     const int grid = tiles < num_sms() ? tiles : num_sms();
     if (L::TMA_EPI) {

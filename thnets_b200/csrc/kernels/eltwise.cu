@@ -399,6 +399,34 @@ __global__ void u8_threshold_kernel(const uint8_t *x, long pixels, int C, int x_
     *reinterpret_cast<uint4 *>(y + pix * y_ld + cv * 16) = t;
 }
 
+// uint8 a*ca + b*cb with ca, cb in {+1, -1}, both inputs and the output on the same static quantisation
+// (sub = -range/2, mult = 255/range, so sub*mult = -127.5): the byte a dequantise -> float combine -> requantise chain
+// gives in exact arithmetic, floor(ca*qa + cb*qb - (ca + cb - 1)*127.5) saturated to [0, 255] = `add2`/2 folded into an
+// integer addend; an optional Threshold (bytes thr, val; thr < 0: none) follows.  No counterpart in the reference, whose
+// lowp engine has no CAddTable.
+__global__ void u8_combine_kernel(const uint8_t *a, int a_ld, const uint8_t *b, int b_ld, int ca, int cb, int addend,
+                                  int thr, int val, long pixels, int C, uint8_t *y, int y_ld)
+{
+    const int cvecs = (C + 15) / 16;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= pixels * cvecs) return;
+    const int cv = (int)(idx % cvecs);
+    const long pix = idx / cvecs;
+    uint4 ta = __ldg(reinterpret_cast<const uint4 *>(a + pix * a_ld + cv * 16));
+    uint4 tb = __ldg(reinterpret_cast<const uint4 *>(b + pix * b_ld + cv * 16));
+    const uint8_t *pa = reinterpret_cast<const uint8_t *>(&ta), *pb = reinterpret_cast<const uint8_t *>(&tb);
+    uint4 t;
+    uint8_t *o = reinterpret_cast<uint8_t *>(&t);
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        int v = ca * (int)pa[i] + cb * (int)pb[i] + addend;
+        v = min(255, max(0, v));
+        if (thr >= 0) v = v > thr ? v : val;
+        o[i] = (cv * 16 + i < C) ? (uint8_t)v : 0;
+    }
+    *reinterpret_cast<uint4 *>(y + pix * y_ld + cv * 16) = t;
+}
+
 struct CombineArgs {
     const void *x[8];
     int ld[8];
@@ -697,7 +725,7 @@ int thb_avgpool(int dtype, const void *x, int N, int H, int W, int C, int x_ld, 
     const int al = thb_channel_align(dtype);
     const long total = (long)N * oH * oW * ((C + al - 1) / al);
     if (total == 0) return THB_OK;
-    DISPATCH_FLOAT_DTYPE(dtype, (pool_kernel<T, false><<<nblocks(total), 256, 0, (cudaStream_t)s>>>(
+    DISPATCH_ANY_DTYPE(dtype, (pool_kernel<T, false><<<nblocks(total), 256, 0, (cudaStream_t)s>>>(
                                     (const T *)x, N, H, W, C, x_ld, kH, kW, dH, dW, padH, padW, oH, oW,
                                     count_include_pad, (T *)y, y_ld)));
     return THB_LAUNCH_CHECK("pool_kernel<avg>");
@@ -723,6 +751,20 @@ int thb_u8_threshold(const void *x, long pixels, int C, int x_ld, int thr, int v
     u8_threshold_kernel<<<nblocks(total), 256, 0, (cudaStream_t)s>>>((const uint8_t *)x, pixels, C, x_ld, thr, val,
                                                                      (uint8_t *)y, y_ld);
     return THB_LAUNCH_CHECK("u8_threshold_kernel");
+}
+
+int thb_u8_combine(const void *a, int a_ld, const void *b, int b_ld, int ca, int cb, int thr, int val, long pixels, int C,
+                   void *y, int y_ld, thb_stream s)
+{
+    if ((ca != 1 && ca != -1) || (cb != 1 && cb != -1)) return THB_ERR_UNSUPPORTED;
+    const long total = pixels * ((C + 15) / 16);
+    if (total == 0) return THB_OK;
+    /* floor(-(ca + cb - 1) * 127.5): +1+1 -> -128, +1-1 -> +127, -1-1 -> +382 */
+    const int twice = -(ca + cb - 1) * 255;
+    const int addend = twice >= 0 ? twice / 2 : -((-twice + 1) / 2);
+    u8_combine_kernel<<<nblocks(total), 256, 0, (cudaStream_t)s>>>((const uint8_t *)a, a_ld, (const uint8_t *)b, b_ld, ca, cb,
+                                                                   addend, thr, val, pixels, C, (uint8_t *)y, y_ld);
+    return THB_LAUNCH_CHECK("u8_combine_kernel");
 }
 
 int thb_combine(int dtype, int nin, const void *const *x_host, const int *ld_host, const float *coef_host, long pixels,

@@ -448,7 +448,7 @@ def _bottleneck(g, x, cin, mid, stride):
     return g.relu(g.add(y, sc))
 
 
-def _resnet(seed, blocks, bottleneck, width, size, classes):
+def _resnet(seed, blocks, bottleneck, width, size, classes, fc_bias="zero"):
     g = Graph(seed)
     g.input_shape, g.input_dist = (3, size, size), "normal"
     base = max(8, int(round(64 * width)))
@@ -470,16 +470,17 @@ def _resnet(seed, blocks, bottleneck, width, size, classes):
                 s = (s + 2 - 3) // 2 + 1
     x = g.avgpool(x, s, s)
     x = g.view(x, cin)
-    g.linear(x, cin, classes)
+    g.linear(x, cin, classes, bias=fc_bias)
     return g
 
 
-def resnet18(seed=1, width=1.0, size=224, classes=1000):
-    return _resnet(seed, [2, 2, 2, 2], False, width, size, classes)
+def resnet18(seed=1, width=1.0, size=224, classes=1000, fc_bias="zero"):
+    """fc_bias: "zero", or the standard deviation of a random bias (the uint8 engine cannot quantise an all-zero one)."""
+    return _resnet(seed, [2, 2, 2, 2], False, width, size, classes, fc_bias)
 
 
-def resnet50(seed=4, width=1.0, size=224, classes=1000):
-    return _resnet(seed, [3, 4, 6, 3], True, width, size, classes)
+def resnet50(seed=4, width=1.0, size=224, classes=1000, fc_bias="zero"):
+    return _resnet(seed, [3, 4, 6, 3], True, width, size, classes, fc_bias)
 
 
 def segnet(seed=3, width=1.0, size=512, classes=21, deconv_bias=None):

@@ -81,6 +81,7 @@ def load(libpath: str | None = None):
     lib.thb_avgpool.argtypes = [ci, vp] + [ci] * 14 + [vp, ci, vp]
     lib.thb_affine_act.argtypes = [ci, vp, cl, ci, ci, vp, vp, C.POINTER(Act), vp, ci, vp]
     lib.thb_u8_threshold.argtypes = [vp, cl, ci, ci, ci, ci, vp, ci, vp]
+    lib.thb_u8_combine.argtypes = [vp, ci, vp, ci, ci, ci, ci, ci, cl, ci, vp, ci, vp]
     lib.thb_combine.argtypes = [ci, ci, C.POINTER(vp), C.POINTER(ci), C.POINTER(cf), cl, ci, vp, ci, vp]
     lib.thb_copy_channels.argtypes = [ci, vp, cl, ci, ci, vp, ci, vp]
     lib.thb_softmax.argtypes = [ci, vp, cl, ci, ci, vp, ci, vp]
