@@ -59,6 +59,8 @@ struct ConvTcParams {
                                // pipeline stage carries both activation tiles and ONE weight tile, and the MMA thread feeds two
                                // accumulators per barrier round: that round costs the thread ~250 cycles whatever it carries,
                                // which a single narrow tile (192-256 tensor cycles per K block) cannot hide.
+    int u8_classes;            // uint8: > 0 when the border classes of the kernel window ((1 + 2 padH) x (1 + 2 padW) of them)
+                               // fit the epilogue's shared-memory table; 0: every row looks its window up in global memory
     int reverse;               // TMA modes with the TMA epilogue: pixel tiles are walked from the tensor's end, so that a layer
                                // starts on what the layer before it wrote last and the L2 still holds
     int stages;                // TMA epilogue: pipeline stages (the launcher sizes them against the epilogue tiles)
@@ -192,7 +194,12 @@ template <int KIND, int BN, int STAGES> struct Smem {
     // The TMA epilogue takes the whole 227 KB: the launcher splits what the barriers leave between pipeline stages
     // (at least STAGES of them) and 16 KB epilogue tiles.  The staged epilogue has STAGES stages and two staging tiles.
     static constexpr size_t AVAIL = 232448 - 1024 - BAR_BYTES;
-    static constexpr size_t TOTAL = TMA_EPI ? 232448 : 1024 + BAR_BYTES + (size_t)STAGES * STAGE_BYTES + 2 * STAGING_PAD;
+    // uint8: per epilogue group a table of zero-point correction terms per (border class, channel) and the bias addends
+    static constexpr int TBL_ROW = BN + 4;                                 // ints between the rows of two classes
+    static constexpr int TBL_CAP = 3400;                                   // ints the class table may take
+    static constexpr size_t TBL_BYTES = KIND == 2 ? (size_t)(TBL_CAP + 256) * 4 + 64 : 0;
+    static constexpr size_t TOTAL =
+        TMA_EPI ? 232448 : 1024 + BAR_BYTES + (size_t)STAGES * STAGE_BYTES + 2 * STAGING_PAD + 2 * TBL_BYTES;
     static_assert(TOTAL <= 232448, "shared memory plan exceeds the 227 KB a CTA can have");
 };
 constexpr int MAX_STAGES = 12;
@@ -675,6 +682,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                              : (p.act_th == 0.f && p.act_val == 0.f) ? 3 : 1;
         bool alive = true;
         int sub_it = 0;                        // staging blocks this group has processed
+        int *tbl = reinterpret_cast<int *>(stage_buf + 2 * L::STAGING_PAD + grp * L::TBL_BYTES);  // uint8 only
+        const uint32_t bar_tbl = smem_u32(&rows_ready[6 + grp]);
+        int tbl_n0 = -1;
+        uint32_t tbl_phase = 0;
         for (int lt = grp; alive; lt += 2) {
             const int tile = blockIdx.x + lt * gridDim.x;
             if (tile >= total_tiles) break;
@@ -701,6 +712,53 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     for (int s = s0; s < s1; s++) xsum += __ldg(cs + (ihb + r) * p.W + iwb + s);
                 const int nvalid = max(0, r1 - r0) * max(0, s1 - s0);
                 corr_pix = p.a_off * (xsum + p.b_off * nvalid * p.Cin);
+            }
+            // uint8 fast path: the window's border class of this row selects a row of the group's table
+            // T[class][channel] = b_off * (sum of the weights of channel `channel` over the taps inside the image)
+            int cls = 0;
+            bool fast = KIND == 2 && p.u8_classes > 0;
+            if (KIND == 2 && fast) {
+                if (valid) {
+                    const int ct = r0, cb = p.kH - r1, cl = s0, cr = p.kW - s1;  // taps clipped at each side
+                    if ((ct > 0 && cb > 0) || (cl > 0 && cr > 0) || ct > p.padH || cb > p.padH || cl > p.padW || cr > p.padW ||
+                        r1 <= r0 || s1 <= s0)
+                        fast = false;  // clipped on two opposite sides (image smaller than the kernel): no class for that
+                    else
+                        cls = (ct > 0 ? ct : cb > 0 ? p.padH + cb : 0) * (1 + 2 * p.padW) + (cl > 0 ? cl : cr > 0 ? p.padW + cr : 0);
+                }
+                fast = __all_sync(0xffffffffu, fast);
+                if (n0 != tbl_n0) {
+                    // (re)build the table for this tile's channels: all four warps of the group, between two group barriers
+                    bool ok = true;
+                    mbar_arrive(bar_tbl);
+                    ok = mbar_wait_bounded(bar_tbl, tbl_phase & 1);
+                    tbl_phase++;
+                    if (ok) {
+                        const int ncc = 1 + 2 * p.padW, satw = p.kW + 1, satn = (p.kH + 1) * (p.kW + 1);
+                        for (int idx = et; idx < p.u8_classes * BN; idx += 128) {
+                            const int k = idx / BN, col = idx - k * BN;
+                            const int rc = k / ncc, cc = k - rc * ncc;
+                            const int tr0 = rc >= 1 && rc <= p.padH ? rc : 0, tr1 = rc > p.padH ? p.kH - (rc - p.padH) : p.kH;
+                            const int ts0 = cc >= 1 && cc <= p.padW ? cc : 0, ts1 = cc > p.padW ? p.kW - (cc - p.padW) : p.kW;
+                            const int *t = p.wsat + (size_t)min(n0 + col, p.Cout - 1) * satn;
+                            tbl[k * L::TBL_ROW + col] = p.b_off * (__ldg(t + tr1 * satw + ts1) - __ldg(t + tr0 * satw + ts1) -
+                                                                   __ldg(t + tr1 * satw + ts0) + __ldg(t + tr0 * satw + ts0));
+                        }
+                        for (int col = et; col < BN; col += 128)
+                            tbl[L::TBL_CAP + col] = p.bias_add ? __ldg(p.bias_add + min(n0 + col, p.Cout - 1)) : 0;
+                        mbar_arrive(bar_tbl);
+                        ok = mbar_wait_bounded(bar_tbl, tbl_phase & 1);
+                        tbl_phase++;
+                    }
+                    if (!ok) {
+                        if (lane == 0) atomicExch(p.status, 8);
+                        *abort_flag = 1;
+                        alive = false;
+                    }
+                    alive = __all_sync(0xffffffffu, alive);
+                    if (!alive) break;
+                    tbl_n0 = n0;
+                }
             }
             bool have_acc = false;
 #pragma unroll 1
@@ -739,7 +797,50 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                 }
                 alive = __all_sync(0xffffffffu, alive);
                 if (!alive) break;
-                if (KIND == 2) {
+                if (KIND == 2 && fast) {
+                    // 32 accumulator columns per TMEM load; per column one table word (the row's border class) and one bias
+                    // addend from shared memory, then integer arithmetic only.
+                    const int *trow = tbl + cls * L::TBL_ROW + sb * SUBN;
+                    const int *brow = tbl + L::TBL_CAP + sb * SUBN;
+                    const uint32_t rnd = p.c_shift >= 1 ? 1u << (p.c_shift - 1) : 0u;
+                    const int tailmask = plane_pos < p.tail_start ? 0 : 255;  // the reference's tail adds without the lower clamp
+                    const int thr = p.relu_thr, rval = p.relu_val;             // thr < 0: every byte passes
+                    const uint32_t rowmask = valid ? 0xffffffffu : 0u;
+#pragma unroll 1
+                    for (int cc = 0; cc < SUBN / 32; cc++) {
+                        uint32_t acc[32];
+                        __syncwarp();
+                        tmem_ld32(lane_addr + sb * SUBN + cc * 32, acc);
+                        tmem_ld_wait();
+                        uint32_t words[8];
+#pragma unroll
+                        for (int g4 = 0; g4 < 8; g4++) {
+                            const int4 t4 = *reinterpret_cast<const int4 *>(trow + cc * 32 + g4 * 4);
+                            const int4 b4 = *reinterpret_cast<const int4 *>(brow + cc * 32 + g4 * 4);
+                            const int tv[4] = {t4.x, t4.y, t4.z, t4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+                            const int cfirst = nsub0 + cc * 32 + g4 * 4;
+                            uint32_t w = 0;
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+                                const int a = (int)acc[g4 * 4 + i] + tv[i] + corr_pix;
+                                if (p.acc_out && valid && cfirst + i < p.Cout) p.acc_out[(size_t)pm * p.Cout + cfirst + i] = a;
+                                int sres = (int)(((uint32_t)a + (uint32_t)p.c_off) * (uint32_t)p.c_mult + rnd);
+                                if (p.c_shift > 0) sres >>= p.c_shift;
+                                int q = min(255, max(0, sres));
+                                const int t2 = q + bv[i];
+                                q = min(255, max(t2, t2 & tailmask));
+                                q = q > thr ? q : rval;
+                                w |= (uint32_t)q << (8 * i);
+                            }
+                            const int nreal = p.Cout - cfirst;  // channels of this word that exist
+                            const uint32_t cmask = nreal >= 4 ? 0xffffffffu : nreal <= 0 ? 0u : (1u << (8 * nreal)) - 1u;
+                            words[g4] = w & cmask & rowmask;
+                        }
+                        uint4 *dst = reinterpret_cast<uint4 *>(stg + row * (SUBN + 16) + cc * 32);
+                        dst[0] = make_uint4(words[0], words[1], words[2], words[3]);
+                        dst[1] = make_uint4(words[4], words[5], words[6], words[7]);
+                    }
+                } else if (KIND == 2) {
                     // Eight columns at a time in a rolled loop (compact code: the unrolled 32-column form was bound by
                     // instruction fetch).  Per-channel constants are loaded once per group; only rows whose window is
                     // clipped by the image border look their own tap rectangle up in the summed-area table.
@@ -916,6 +1017,16 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
     if (const char *e = getenv("THB200_PAIR_MIN_KB")) pair_min_kb = atoi(e);
     long pair_min_units = 2L * num_sms();
     if (const char *e = getenv("THB200_PAIR_MIN_UNITS")) pair_min_units = atol(e);  // (tests exercise the mode on small shapes)
+    p.u8_classes = 0;
+    if (KIND == 2) {
+        static int fast_mode = -1;
+        if (fast_mode < 0) {
+            const char *e = getenv("THB200_U8_FAST");
+            fast_mode = e ? atoi(e) : 1;
+        }
+        const int ncls = (1 + 2 * p.padH) * (1 + 2 * p.padW);
+        if (fast_mode && p.wsat && p.padH < p.kH && p.padW < p.kW && ncls * L::TBL_ROW <= L::TBL_CAP) p.u8_classes = ncls;
+    }
     p.pair = L::TMA_EPI && p.a_tma && BN <= 128 && p.nkb >= pair_min_kb && (long)(p.m_tiles / 2) * p.n_tiles >= pair_min_units;
     {
         // Every second convolution launch of a host thread walks its pixel tiles backwards: consecutive layers then
