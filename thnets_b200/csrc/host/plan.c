@@ -353,9 +353,17 @@ static int plan_gemm_group(planner *P, int i)
     if (bn >= 0 && M->nodes[bn].C != n->Cout) { thb_set_error("batch-norm width mismatch"); return -1; }
     int res_node = -1;
     float self_coef = 1.f, res_coef = 0.f;
-    if (dtype != THB_U8 && !is_deconv && (j = sole_consumer(P, cur)) >= 0 && M->nodes[j].op == OP_COMBINE && M->nodes[j].nin == 2) {
+    /* uint8: the fused residual needs what thb_u8_combine needs (two tensors on the static range, coefficients +-1)
+     * and the table-driven epilogue (at most 13 border classes, the image at least as large as the kernel) */
+    const char *nofuse = getenv("THB200_U8_NO_FUSED_RESIDUAL");
+    const int u8_res_ok = dtype == THB_U8 && !in->q_dyn && (1 + 2 * n->padH) * (1 + 2 * n->padW) <= 13 && H >= kH && W >= kW &&
+                          n->padH < kH && n->padW < kW && !is_linear && !(nofuse && atoi(nofuse));
+    if ((dtype != THB_U8 || u8_res_ok) && !is_deconv && (j = sole_consumer(P, cur)) >= 0 && M->nodes[j].op == OP_COMBINE && M->nodes[j].nin == 2) {
         int pos = M->nodes[j].in[0] == cur ? 0 : 1, other = M->nodes[j].in[1 - pos];
-        if (other != cur && other < i && P->val[other].buf >= 0 && !P->val[other].s.flat &&
+        const float c0 = M->nodes[j].coef[0], c1 = M->nodes[j].coef[1];
+        const int u8_ok = dtype != THB_U8 || ((c0 == 1.f || c0 == -1.f) && (c1 == 1.f || c1 == -1.f) && !P->val[other].q_dyn &&
+                                              P->val[other].q_sub == -E->range / 2 && P->val[other].q_mult == 255 / E->range);
+        if (u8_ok && other != cur && other < i && P->val[other].buf >= 0 && !P->val[other].s.flat &&
             (long)P->val[other].s.C == os.C && P->val[other].s.H == os.H && P->val[other].s.W == os.W) {
             comb = j; cur = j; res_node = other;
             self_coef = M->nodes[j].coef[pos];
@@ -546,6 +554,12 @@ static int plan_gemm_group(planner *P, int i)
             d->relu_val = thb_lowp_scale_float(out_sub, out_mult, M->nodes[act].act_value);
         }
         out->q_sub = out_sub; out->q_mult = out_mult;
+        if (res_node >= 0) {
+            const value *rv = &P->val[res_node];
+            step_in(s, rv);
+            d->res_ld = rv->ld;
+            d->self_coef = self_coef; d->res_coef = res_coef;
+        }
     } else {
         d->scale = scale; d->shift = shift;
         if (act >= 0 && !is_deconv && fill_act(P, &d->act, &M->nodes[act], n->Cout)) return -1;

@@ -59,6 +59,7 @@ struct ConvTcParams {
                                // pipeline stage carries both activation tiles and ONE weight tile, and the MMA thread feeds two
                                // accumulators per barrier round: that round costs the thread ~250 cycles whatever it carries,
                                // which a single narrow tile (192-256 tensor cycles per K block) cannot hide.
+    int res_addend;            // uint8 fused residual: the constant of ca*q + cb*r + addend (see thb_u8_combine)
     int u8_classes;            // uint8: > 0 when the border classes of the kernel window ((1 + 2 padH) x (1 + 2 padW) of them)
                                // fit the epilogue's shared-memory table; 0: every row looks its window up in global memory
     int reverse;               // TMA modes with the TMA epilogue: pixel tiles are walked from the tensor's end, so that a layer
@@ -258,6 +259,53 @@ template <int BN> struct EpiWalk {
         if (++c.sb == blocks_of(c.j)) { c.sb = 0; c.j++; }
     }
 };
+
+// uint8 epilogue arithmetic of one pixel row over 32 accumulator columns (the table-driven path).  Per column: zero-point
+// correction (table word of the row's border class + the row's own term, with c_offset folded in), gemmlowp
+// requantisation ((x * c_mult + round) >> c_shift, saturated), the reference's saturating bias add, an optional fused
+// residual ca*q + cb*r + addend (saturated) and the Threshold.  GENERAL = false assumes what almost every warp sees: no
+// row in the image plane's tail (where the reference's bias add wraps instead of clamping at 0) and a Threshold whose
+// replacement byte equals its threshold (max suffices); the integer pipe is what bounds this loop.
+struct U8Epi {
+    int corr;        // corr_pix + c_offset of this row
+    uint32_t mult, rnd;
+    int shift, tailmask, thr, rval, ca, cb, addend;
+};
+template <bool GENERAL, bool HAS_RES>
+__device__ __forceinline__ void u8_chunk32(const uint32_t (&acc)[32], const int *trow, const int *brow, const U8Epi &e,
+                                           const uint4 &res0, const uint4 &res1, uint32_t (&words)[8])
+{
+    const uint32_t rw[8] = {res0.x, res0.y, res0.z, res0.w, res1.x, res1.y, res1.z, res1.w};
+#pragma unroll
+    for (int g4 = 0; g4 < 8; g4++) {
+        const int4 t4 = *reinterpret_cast<const int4 *>(trow + g4 * 4);
+        const int4 b4 = *reinterpret_cast<const int4 *>(brow + g4 * 4);
+        const int tv[4] = {t4.x, t4.y, t4.z, t4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+        int q[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int a = (int)acc[g4 * 4 + i] + tv[i] + e.corr;
+            const int sres = (int)((uint32_t)a * e.mult + e.rnd) >> e.shift;
+            const int q1 = __vimin_s32_relu(sres, 255);
+            int v;
+            if (GENERAL) {
+                const int t2 = q1 + bv[i];
+                v = max(__vimin_s32_relu(t2, 255), t2 & e.tailmask);
+            } else {
+                v = __viaddmin_s32_relu(q1, bv[i], 255);
+            }
+            if (HAS_RES) {
+                const int r = (int)((rw[g4] >> (8 * i)) & 255u);
+                v = __vimin_s32_relu(e.ca * v + e.cb * r + e.addend, 255);
+            }
+            if (GENERAL) v = v > e.thr ? v : e.rval;
+            else v = max(v, e.rval);
+            q[i] = v;
+        }
+        const uint32_t lo = __byte_perm((uint32_t)q[0], (uint32_t)q[1], 0x0040), hi = __byte_perm((uint32_t)q[2], (uint32_t)q[3], 0x0040);
+        words[g4] = __byte_perm(lo, hi, 0x5410);
+    }
+}
 
 // The TMA epilogue of one group of four warps (fp16 / bf16, BN >= 64).  The group walks its tiles in blocks of 64
 // output channels through `nbuf` shared-memory tiles of 128 rows x 128 bytes (SWIZZLE_128B).  Each thread owns one
@@ -799,48 +847,64 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                 if (!alive) break;
                 if (KIND == 2 && fast) {
                     // 32 accumulator columns per TMEM load; per column one table word (the row's border class) and one bias
-                    // addend from shared memory, then integer arithmetic only.
+                    // addend from shared memory, then integer arithmetic only (u8_chunk32).
                     const int *trow = tbl + cls * L::TBL_ROW + sb * SUBN;
                     const int *brow = tbl + L::TBL_CAP + sb * SUBN;
-                    const uint32_t rnd = p.c_shift >= 1 ? 1u << (p.c_shift - 1) : 0u;
-                    const int tailmask = plane_pos < p.tail_start ? 0 : 255;  // the reference's tail adds without the lower clamp
-                    const int thr = p.relu_thr, rval = p.relu_val;             // thr < 0: every byte passes
-                    const uint32_t rowmask = valid ? 0xffffffffu : 0u;
+                    U8Epi e;
+                    e.corr = corr_pix + p.c_off;
+                    e.mult = (uint32_t)p.c_mult;
+                    e.rnd = p.c_shift >= 1 ? 1u << (p.c_shift - 1) : 0u;
+                    e.shift = p.c_shift > 0 ? p.c_shift : 0;
+                    e.tailmask = plane_pos < p.tail_start ? 0 : 255;  // the reference's tail adds without the lower clamp
+                    e.thr = p.relu_thr;                               // < 0: every byte passes
+                    e.rval = p.relu_thr < 0 ? 0 : p.relu_val;
+                    e.ca = (int)p.self_coef; e.cb = (int)p.res_coef; e.addend = p.res_addend;
+                    const bool u8res = p.res != nullptr;
+                    // the common case per warp: no tail row, Threshold replaces by its own threshold byte (or none)
+                    const bool general = __any_sync(0xffffffffu, e.tailmask != 0) || (p.relu_thr >= 0 && p.relu_val != p.relu_thr);
+                    const uint8_t *rrow = p.res + (size_t)(valid ? pm : 0) * p.res_ld + nsub0;
 #pragma unroll 1
                     for (int cc = 0; cc < SUBN / 32; cc++) {
                         uint32_t acc[32];
+                        uint4 res0 = make_uint4(0, 0, 0, 0), res1 = res0;
+                        if (u8res && nsub0 + cc * 32 < p.res_ld) {
+                            // residual bytes of this row: issued before the accumulator wait
+                            res0 = __ldg(reinterpret_cast<const uint4 *>(rrow + cc * 32));
+                            if (nsub0 + cc * 32 + 16 < p.res_ld) res1 = __ldg(reinterpret_cast<const uint4 *>(rrow + cc * 32 + 16));
+                        }
                         __syncwarp();
                         tmem_ld32(lane_addr + sb * SUBN + cc * 32, acc);
                         tmem_ld_wait();
-                        uint32_t words[8];
+                        if (p.acc_out && valid) {
+                            // raw corrected accumulators (tests only)
 #pragma unroll
-                        for (int g4 = 0; g4 < 8; g4++) {
-                            const int4 t4 = *reinterpret_cast<const int4 *>(trow + cc * 32 + g4 * 4);
-                            const int4 b4 = *reinterpret_cast<const int4 *>(brow + cc * 32 + g4 * 4);
-                            const int tv[4] = {t4.x, t4.y, t4.z, t4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
-                            const int cfirst = nsub0 + cc * 32 + g4 * 4;
-                            uint32_t w = 0;
-#pragma unroll
-                            for (int i = 0; i < 4; i++) {
-                                const int a = (int)acc[g4 * 4 + i] + tv[i] + corr_pix;
-                                if (p.acc_out && valid && cfirst + i < p.Cout) p.acc_out[(size_t)pm * p.Cout + cfirst + i] = a;
-                                int sres = (int)(((uint32_t)a + (uint32_t)p.c_off) * (uint32_t)p.c_mult + rnd);
-                                if (p.c_shift > 0) sres >>= p.c_shift;
-                                int q = min(255, max(0, sres));
-                                const int t2 = q + bv[i];
-                                q = min(255, max(t2, t2 & tailmask));
-                                q = q > thr ? q : rval;
-                                w |= (uint32_t)q << (8 * i);
+                            for (int i = 0; i < 32; i++) {
+                                const int c = nsub0 + cc * 32 + i;
+                                if (c < p.Cout) p.acc_out[(size_t)pm * p.Cout + c] = (int)acc[i] + trow[cc * 32 + i] + corr_pix;
                             }
-                            const int nreal = p.Cout - cfirst;  // channels of this word that exist
-                            const uint32_t cmask = nreal >= 4 ? 0xffffffffu : nreal <= 0 ? 0u : (1u << (8 * nreal)) - 1u;
-                            words[g4] = w & cmask & rowmask;
+                        }
+                        uint32_t words[8];
+                        if (u8res) {
+                            if (general) u8_chunk32<true, true>(acc, trow + cc * 32, brow + cc * 32, e, res0, res1, words);
+                            else u8_chunk32<false, true>(acc, trow + cc * 32, brow + cc * 32, e, res0, res1, words);
+                        } else {
+                            if (general) u8_chunk32<true, false>(acc, trow + cc * 32, brow + cc * 32, e, res0, res1, words);
+                            else u8_chunk32<false, false>(acc, trow + cc * 32, brow + cc * 32, e, res0, res1, words);
+                        }
+                        if (check) {
+                            // channels beyond the last real one are stored as zero bytes
+#pragma unroll
+                            for (int g4 = 0; g4 < 8; g4++) {
+                                const int nreal = p.Cout - (nsub0 + cc * 32 + g4 * 4);
+                                words[g4] &= nreal >= 4 ? 0xffffffffu : nreal <= 0 ? 0u : (1u << (8 * nreal)) - 1u;
+                            }
                         }
                         uint4 *dst = reinterpret_cast<uint4 *>(stg + row * (SUBN + 16) + cc * 32);
                         dst[0] = make_uint4(words[0], words[1], words[2], words[3]);
                         dst[1] = make_uint4(words[4], words[5], words[6], words[7]);
                     }
                 } else if (KIND == 2) {
+                    if (p.res && lane == 0) atomicExch(p.status, 9);  // a fused residual exists on the table-driven path only
                     // Eight columns at a time in a rolled loop (compact code: the unrolled 32-column form was bound by
                     // instruction fetch).  Per-channel constants are loaded once per group; only rows whose window is
                     // clipped by the image border look their own tap rectangle up in the summed-area table.
@@ -1026,6 +1090,8 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
         }
         const int ncls = (1 + 2 * p.padH) * (1 + 2 * p.padW);
         if (fast_mode && p.wsat && p.padH < p.kH && p.padW < p.kW && ncls * L::TBL_ROW <= L::TBL_CAP) p.u8_classes = ncls;
+        // a fused residual exists on the table-driven path only, and that path needs windows clipped on one side at most
+        if (p.res && (!p.u8_classes || p.H < p.kH || p.W < p.kW)) return thb_note_launch(cudaErrorInvalidValue, "conv_tc: uint8 residual");
     }
     p.pair = L::TMA_EPI && p.a_tma && BN <= 128 && p.nkb >= pair_min_kb && (long)(p.m_tiles / 2) * p.n_tiles >= pair_min_units;
     {
@@ -1296,6 +1362,12 @@ extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, t
     p.act_kind = d->act.kind; p.act_th = d->act.threshold; p.act_val = d->act.value; p.act_alpha = d->act.alpha;
     p.a_off = d->a_offset; p.b_off = d->b_offset; p.c_off = d->c_offset; p.c_mult = d->c_mult; p.c_shift = d->c_shift;
     p.wsat = d->wsat; p.bias_add = d->bias_add; p.csum = d->csum;
+    if (d->dtype == THB_U8 && d->res) {
+        const int ca = (int)d->self_coef, cb = (int)d->res_coef;
+        if ((ca != 1 && ca != -1) || (cb != 1 && cb != -1) || (float)ca != d->self_coef || (float)cb != d->res_coef) return THB_ERR_UNSUPPORTED;
+        const int twice = -(ca + cb - 1) * 255;  // floor(-(ca + cb - 1) * 127.5), as thb_u8_combine
+        p.res_addend = twice >= 0 ? twice / 2 : -((-twice + 1) / 2);
+    }
     p.tail_start = d->tail_start; p.relu_thr = d->relu_thr; p.relu_val = d->relu_val;
     p.acc_out = d->acc_out;
     p.use_l1 = d->kH * d->kW > 1;
