@@ -838,13 +838,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     have_acc = true;
                 }
                 // ---- phase 1: this thread's pixel row, SUBN accumulator columns -> staging tile
-                if (!mbar_wait_bounded(bar_free, (sub_it & 1) ^ 1)) {
-                    if (lane == 0) atomicExch(p.status, 7);
-                    *abort_flag = 1;
-                    alive = false;
+                // (uint8: a warp stages and writes out its own 32 rows, so it synchronises with nobody but itself)
+                if (KIND != 2) {
+                    if (!mbar_wait_bounded(bar_free, (sub_it & 1) ^ 1)) {
+                        if (lane == 0) atomicExch(p.status, 7);
+                        *abort_flag = 1;
+                        alive = false;
+                    }
+                    alive = __all_sync(0xffffffffu, alive);
+                    if (!alive) break;
                 }
-                alive = __all_sync(0xffffffffu, alive);
-                if (!alive) break;
                 if (KIND == 2 && fast) {
                     // 32 accumulator columns per TMEM load; per column one table word (the row's border class) and one bias
                     // addend from shared memory, then integer arithmetic only (u8_chunk32).
@@ -976,25 +979,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     tc_fence_before();
                     mbar_arrive(smem_u32(&acc_empty[ab]));
                 }
-                mbar_arrive(bar_ready);
-                if (!mbar_wait_bounded(bar_ready, sub_it & 1)) {
-                    if (lane == 0) atomicExch(p.status, 5);
-                    *abort_flag = 1;
-                    alive = false;
+                if (KIND == 2) {
+                    __syncwarp();
+                } else {
+                    mbar_arrive(bar_ready);
+                    if (!mbar_wait_bounded(bar_ready, sub_it & 1)) {
+                        if (lane == 0) atomicExch(p.status, 5);
+                        *abort_flag = 1;
+                        alive = false;
+                    }
+                    alive = __all_sync(0xffffffffu, alive);
+                    if (!alive) break;
                 }
-                alive = __all_sync(0xffffffffu, alive);
-                if (!alive) break;
                 // ---- phase 2: coalesced write-out of the staged block
                 if (KIND == 2) {
+                    // the warp's own 32 rows, 16-byte chunks: each instruction stores whole rows' worth of contiguous bytes
                     constexpr int CPR = SUBN / 16;
 #pragma unroll
                     for (int u = 0; u < CPR; u++) {
-                        const int idx = et + u * 128, r = idx / CPR, cg2 = idx - r * CPR;
+                        const int idx = lane + u * 32, r = quad * 32 + idx / CPR, cg2 = idx % CPR;
                         const int pm2 = m0 + r, c0 = nsub0 + cg2 * 16;
                         if (pm2 < p.P && c0 < p.Cout)
                             *reinterpret_cast<uint4 *>(p.y + (size_t)pm2 * p.out_ld + c0) =
                                 *reinterpret_cast<const uint4 *>(stg + r * (SUBN + 16) + cg2 * 16);
                     }
+                    __syncwarp();
                 } else if (c0f < p.Cout) {
                     const float *stage = reinterpret_cast<const float *>(stg);
                     float sc[8], sh[8], sl[8];
@@ -1031,7 +1040,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                         *reinterpret_cast<uint4 *>(p.y + ((size_t)pm2 * p.out_ld + c0f) * 2) = o;
                     }
                 }
-                mbar_arrive(bar_free);
+                if (KIND != 2) mbar_arrive(bar_free);
             }
         }
     }
