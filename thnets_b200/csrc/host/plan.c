@@ -61,6 +61,7 @@ typedef struct {
     int ld;    /* pixel stride in elements */
     int coff;  /* channel offset inside the buffer */
     shape s;
+    int csum_buf;        /* u8 mode: 1 + the buffer holding this tensor's per-pixel channel sums once a convolution asked for them; 0: none yet */
     float q_sub, q_mult; /* u8 mode */
     int q_dyn;           /* u8 mode: the scale is measured per forward (network input) */
     int row_pitch, pad_left; /* rows stored with horizontal zero padding (the staged network input only), else 0 */
@@ -425,11 +426,17 @@ static int plan_gemm_group(planner *P, int i)
     int csum_buf = -1;
     if (dtype == THB_U8) {
         /* per-pixel channel sums of the input feed the zero-point correction of the convolution */
-        csum_buf = new_buf(P, sizeof(int) * (size_t)is.N * H * W);
-        step *cs = new_step(P, ST_CSUM);
-        step_in(cs, in);
-        cs->in_ld[0] = in_ld;
-        cs->pixels = (long)is.N * H * W; cs->C = Cin; cs->out_buf = csum_buf;
+        /* (several convolutions reading one tensor share one pass; csum_buf holds buffer index + 1, 0 = none yet) */
+        value *inw = &P->val[n->in[0]];
+        if (inw->csum_buf > 0 && !is_linear) csum_buf = inw->csum_buf - 1;
+        else {
+            csum_buf = new_buf(P, sizeof(int) * (size_t)is.N * H * W);
+            step *cs = new_step(P, ST_CSUM);
+            step_in(cs, in);
+            cs->in_ld[0] = in_ld;
+            cs->pixels = (long)is.N * H * W; cs->C = Cin; cs->out_buf = csum_buf;
+            if (!is_linear) inw->csum_buf = csum_buf + 1;
+        }
     }
     step *s = new_step(P, ST_CONV);
     thb_conv_desc *d = &s->conv;

@@ -543,20 +543,35 @@ __global__ void col2im_kernel(const T *cols, int N, int H, int W, int Cout, int 
     Vec<T>::store(y + (size_t)opix * y_ld + cv * VN, acc);
 }
 
+// G lanes per pixel (a power of two up to 32): neighbouring lanes read neighbouring 16-byte chunks, so a warp's load covers
+// whole pixels' contiguous bytes; bytes are summed four at a time (dp4a against ones) and the G partial sums by shuffles.
+template <int G>
 __global__ void u8_channel_sum_kernel(const uint8_t *x, long pixels, int C, int x_ld, int *csum)
 {
-    const long pix = (long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (pix >= pixels) return;
-    const uint8_t *p = x + pix * x_ld;
+    const long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long pix = t / G;
+    const int g = (int)(t % G);
     int s = 0;
-    for (int c0 = 0; c0 < C; c0 += 16) {
-        uint4 t = *reinterpret_cast<const uint4 *>(p + c0);
-        const uint8_t *b = reinterpret_cast<const uint8_t *>(&t);
+    if (pix < pixels) {
+        const uint8_t *p = x + pix * x_ld;
+        for (int c0 = g * 16; c0 < C; c0 += G * 16) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p + c0));
+            uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            if (c0 + 16 > C) {
+                // the last chunk: bytes beyond channel C do not count
 #pragma unroll
-        for (int i = 0; i < 16; i++)
-            if (c0 + i < C) s += b[i];
+                for (int i = 0; i < 4; i++) {
+                    const int nreal = C - c0 - 4 * i;
+                    w[i] &= nreal >= 4 ? 0xffffffffu : nreal <= 0 ? 0u : (1u << (8 * nreal)) - 1u;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) s = (int)__dp4a(w[i], 0x01010101u, (uint32_t)s);
+        }
     }
-    csum[pix] = s;
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (pix < pixels && g == 0) csum[pix] = s;
 }
 
 // the same with a whole block per pixel, for the few-pixel, many-channel inputs of Linear layers
@@ -827,7 +842,16 @@ int thb_u8_channel_sum(const void *x, long pixels, int C, int x_ld, int *csum, t
         u8_channel_sum_wide_kernel<<<(unsigned)pixels, 256, 0, (cudaStream_t)s>>>((const uint8_t *)x, C, x_ld, csum);
         return THB_LAUNCH_CHECK("u8_channel_sum_wide_kernel");
     }
-    u8_channel_sum_kernel<<<nblocks(pixels), 256, 0, (cudaStream_t)s>>>((const uint8_t *)x, pixels, C, x_ld, csum);
+    const int chunks = (C + 15) / 16;
+#define CSUM_CASE(G)                                                                                                      \
+    u8_channel_sum_kernel<G><<<nblocks(pixels * G), 256, 0, (cudaStream_t)s>>>((const uint8_t *)x, pixels, C, x_ld, csum)
+    if (chunks <= 1) CSUM_CASE(1);
+    else if (chunks <= 2) CSUM_CASE(2);
+    else if (chunks <= 4) CSUM_CASE(4);
+    else if (chunks <= 8) CSUM_CASE(8);
+    else if (chunks <= 16) CSUM_CASE(16);
+    else CSUM_CASE(32);
+#undef CSUM_CASE
     return THB_LAUNCH_CHECK("u8_channel_sum_kernel");
 }
 
