@@ -213,6 +213,17 @@ __device__ __forceinline__ uint64_t make_sw128_kmajor_desc(uint32_t smem_addr)
     d |= (uint64_t)2 << 61;                        // layout type: SWIZZLE_128B
     return d;
 }
+// The same for rows of 64 bytes with the 64-byte swizzle (a SWIZZLE_64B TMA box 64 bytes wide): 8-row groups 512 bytes apart.
+__device__ __forceinline__ uint64_t make_sw64_kmajor_desc(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(512 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)4 << 61;                        // layout type: SWIZZLE_64B
+    return d;
+}
 // Instruction descriptor: dense, K-major A and B, M = 128, N = n.
 // c_format: 1 = F32, 2 = S32.  ab_format: f16 kinds 0 = F16, 1 = BF16; i8 kind 0 = U8, 1 = S8.
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t c_format, uint32_t ab_format, uint32_t n)

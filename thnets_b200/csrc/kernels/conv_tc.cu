@@ -70,6 +70,8 @@ struct ConvTcParams {
     int tma_kw, tma_padw;     // a_tma == 2: taps per kernel row that need a load of their own, and the padding the
                               // descriptor's coordinates see (1, 0 when one copy fetches a padded row's kW taps)
     int slabs;   // a_tma == 2: 128-byte channel slabs per tap (K block kb = tap * slabs + slab)
+    int half, ntaps;  // a_tma == 2, half: a tap is 64 bytes of channels; a K block holds two taps as two tiles of 64-byte rows
+                      // (SWIZZLE_64B), each loaded by its own activation and weight copy and fed to two MMAs of K = 32 bytes
     int use_l1;  // gather through L1: neighbouring taps of one tile re-read the same input pixels
     int *acc_out;
     int *status;
@@ -638,6 +640,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                         break;
                     }
                     const uint32_t bar = smem_u32(&full[s]);
+                    if (p.half) {
+                        const int nh = 2 * kb + 1 < p.ntaps ? 2 : 1;
+                        mbar_arrive_expect_tx(bar, (uint32_t)(nh * (A_STAGE_BYTES / 2 + B_STAGE_BYTES / 2)));
+                        for (int h = 0; h < nh; h++) {
+                            tma_load_im2col_4d(smem_u32(sA + s * a_stage_bytes + h * (A_STAGE_BYTES / 2)), &tmapA, bar, 0, iw[0], ih[0],
+                                               in[0], (uint16_t)tap_w, (uint16_t)tap_h);
+                            tma_load_2d(smem_u32(sB + s * B_STAGE_BYTES + h * (B_STAGE_BYTES / 2)), &tmapW, bar, (2 * kb + h) * (BKE / 2), n0);
+                            if (++tap_w == p.tma_kw) { tap_w = 0; tap_h++; }
+                        }
+                        continue;
+                    }
                     mbar_arrive_expect_tx(bar, (uint32_t)(B_STAGE_BYTES + (p.a_tma ? a_stage_bytes : 0)));
                     if (p.a_tma == 1) {
                         for (int h = 0; h < halves; h++)
@@ -687,6 +700,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     }
                     tc_fence_after();
                     fence_proxy_async_smem();
+                    if (p.half) {
+                        const int nh = 2 * kb + 1 < p.ntaps ? 2 : 1;
+                        for (int h = 0; h < nh; h++) {
+                            const uint64_t ad = make_sw64_kmajor_desc(smem_u32(sA + s * a_stage_bytes + h * (A_STAGE_BYTES / 2)));
+                            const uint64_t bd = make_sw64_kmajor_desc(smem_u32(sB + s * B_STAGE_BYTES + h * (B_STAGE_BYTES / 2)));
+#pragma unroll
+                            for (int k = 0; k < 2; k++) {
+                                const uint32_t accum = (kb | h | k) != 0;
+                                if (KIND == 2) tc_mma_i8(d0, ad + 2 * k, bd + 2 * k, IDESC, accum);
+                                else tc_mma_f16(d0, ad + 2 * k, bd + 2 * k, IDESC, accum);
+                            }
+                        }
+                        tc_commit(smem_u32(&empty[s]));
+                        continue;
+                    }
                     const uint64_t adesc = make_sw128_kmajor_desc(smem_u32(sA + s * a_stage_bytes));
                     const uint64_t bdesc = make_sw128_kmajor_desc(smem_u32(sB + s * B_STAGE_BYTES));
 #pragma unroll
@@ -1286,8 +1314,10 @@ const CUtensorMap *activation_tmap(const thb_conv_desc *d, const void *x, int mo
             upper[0] = 0;
         }
         cuuint32_t estr[4] = {1, (cuuint32_t)d->dW, (cuuint32_t)d->dH, 1};
-        if (enc(&e.map, t, 4, const_cast<void *>(x), dims, strides, lower, upper, (cuuint32_t)(128 / es), (cuuint32_t)BM, estr,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        // mode 4: a tap is 64 bytes of channels; the box is 64 bytes wide and lands as rows of 64 bytes with the 64-byte swizzle
+        if (enc(&e.map, t, 4, const_cast<void *>(x), dims, strides, lower, upper, (cuuint32_t)((mode == 4 ? 64 : 128) / es),
+                (cuuint32_t)BM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                mode == 4 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return nullptr;
         // Drivers up to CUDA 13.1 encode im2col descriptors of tensors smaller than 128 KiB with a flag (bit 21 of
@@ -1299,6 +1329,38 @@ const CUtensorMap *activation_tmap(const thb_conv_desc *d, const void *x, int mo
     }
     e.x = x; e.mode = mode; e.N = d->N; e.H = d->H; e.W = d->W; e.cin_pad = d->Cin_pad; e.in_ld = d->in_ld; e.dtype = d->dtype;
     memcpy(e.geom, geom, sizeof(geom));
+    return &e.map;
+}
+
+// Descriptor of the packed weights read in boxes 64 bytes wide (SWIZZLE_64B), for convolutions whose taps are 64 bytes.
+struct WHalfEntry {
+    const void *w;
+    int ktot, cout_pad, bn, dtype;
+    alignas(64) CUtensorMap map;
+};
+const CUtensorMap *weights_half_tmap(const thb_conv_desc *d)
+{
+    static WHalfEntry cache[256];
+    static int used = 0, next = 0;
+    for (int i = 0; i < used; i++) {
+        WHalfEntry &e = cache[i];
+        if (e.w == d->w && e.ktot == d->Ktot_pad && e.cout_pad == d->Cout_pad && e.bn == d->BN && e.dtype == d->dtype) return &e.map;
+    }
+    encode_tiled_fn enc = get_encode_fn();
+    if (!enc) return nullptr;
+    WHalfEntry &e = cache[used < 256 ? used++ : (next++ % 256)];
+    e.w = nullptr;
+    const int es = d->dtype == THB_U8 ? 1 : 2;
+    CUtensorMapDataType t = d->dtype == THB_U8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                            : d->dtype == THB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    cuuint64_t dims[2] = {(cuuint64_t)d->Ktot_pad, (cuuint64_t)d->Cout_pad};
+    cuuint64_t strides[1] = {(cuuint64_t)d->Ktot_pad * es};
+    cuuint32_t box[2] = {(cuuint32_t)(64 / es), (cuuint32_t)d->BN};
+    cuuint32_t estr[2] = {1, 1};
+    if (enc(&e.map, t, 2, const_cast<void *>(d->w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return nullptr;
+    e.w = d->w; e.ktot = d->Ktot_pad; e.cout_pad = d->Cout_pad; e.bn = d->BN; e.dtype = d->dtype;
     return &e.map;
 }
 
@@ -1400,6 +1462,11 @@ extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, t
                            box_corner_ok((d->oH - 1) * d->dH + 1 - d->H - d->padH, d->H + d->padH) &&
                            box_corner_ok((d->oW - 1) * d->dW + 1 - d->W - d->padW, d->W + d->padW);
     if (!p.a_tma && im2col_ok && d->Cin_pad % bke == 0 && d->Ktot_pad == d->kH * d->kW * d->Cin_pad) p.a_tma = 2;
+    // uint8 with 64 channels: a tap is half a K block; two taps per block, each as its own 64-byte-wide copy
+    p.ntaps = d->kH * d->kW;
+    const bool half_ok = d->dtype == THB_U8 && !p.a_tma && im2col_ok && d->Cin_pad * 2 == bke && !d->in_row_pitch &&
+                         d->Ktot_pad == (p.ntaps * d->Cin_pad + bke - 1) / bke * bke;
+    if (half_ok) p.a_tma = 2, p.half = 1;
     p.slabs = d->Cin_pad / bke;
     p.tma_kw = d->kW;
     p.tma_padw = d->padW;
@@ -1418,16 +1485,26 @@ extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, t
             p.tma_padw = 0;
         }
     }
+    if (p.half) {
+        tmap_mode = 4;
+        p.slabs = 1;
+        if (const char *e = getenv("THB200_HALF_TAPS"))
+            if (!atoi(e)) p.half = 0, p.a_tma = 0;
+    }
     if (const char *e = getenv("THB200_A_TMA")) {
         const int allow = atoi(e);  // 0: gather only, 1: plain-matrix TMA only, 2 (default): im2col too
-        if (p.a_tma > allow) p.a_tma = 0;
+        if (p.a_tma > allow) p.a_tma = 0, p.half = 0;
         if (allow == 22 && p.a_tma == 1) p.a_tma = 2;  // experiment: im2col mode for a plain matrix too
     }
     if (p.a_tma) {
         ta = activation_tmap(d, x, tmap_mode);
-        if (!ta) p.a_tma = 0, ta = &tm;
+        if (!ta) p.a_tma = 0, p.half = 0, ta = &tm;
     }
     ConvTmaps maps = {&tm, ta, nullptr, nullptr};
+    if (p.half) {
+        maps.w = weights_half_tmap(d);
+        if (!maps.w) return thb_note_launch(cudaErrorUnknown, "conv_tc: weight tensor map");
+    }
     if (d->dtype != THB_U8 && d->BN >= 64) {
         // output and residual go through TMA: [pixels][channels rounded up to 8] matrices with their own pitch
         const int c8 = (d->Cout + 7) & ~7;
