@@ -202,7 +202,7 @@ template <int KIND, int BN, int STAGES> struct Smem {
     static constexpr int TBL_CAP = 3400;                                   // ints the class table may take
     static constexpr size_t TBL_BYTES = KIND == 2 ? (size_t)(TBL_CAP + 256) * 4 + 64 : 0;
     static constexpr size_t TOTAL =
-        TMA_EPI ? 232448 : 1024 + BAR_BYTES + (size_t)STAGES * STAGE_BYTES + 2 * STAGING_PAD + 2 * TBL_BYTES;
+        TMA_EPI ? 232448 : 1024 + BAR_BYTES + (size_t)STAGES * STAGE_BYTES + 3 * STAGING_PAD + 3 * TBL_BYTES;
     static_assert(TOTAL <= 232448, "shared memory plan exceeds the 227 KB a CTA can have");
 };
 constexpr int MAX_STAGES = 12;
@@ -527,8 +527,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                 epilogue_agent<BN>(p, &tmapY, &tmapR, lane, stage_buf + lane * p.epi_bufs * EPI_TILE_BYTES, rows_ready + lane * 3,
                                    avail + lane * 3, abort_flag);
         __syncwarp();
-    } else if (warp < 4) {
+    } else if (warp < 4 && !(!L::TMA_EPI && p.a_tma && p.epi_groups == 3)) {
         // ================================================================== A producer (gather mode)
+        // (with the staged epilogue and nothing to gather, these warps are its third group: the last branch below)
         if (p.a_tma) {
             // nothing to gather: these four warps are the third epilogue group
             if constexpr (L::TMA_EPI)
@@ -740,8 +741,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
         // ================================================================== epilogue (warps 6-13)
         // Two groups of four warps; group g owns TMEM accumulator g and every second tile of this CTA, so the
         // write-out of one tile overlaps the accumulator drain of the next.
-        const int grp = (warp - 6) >> 2;
-        const int et = tid - 192 - grp * 128;  // 0..127 within the group
+        const int grp = warp < 4 ? 2 : (warp - 6) >> 2;
+        const int et = warp < 4 ? tid : tid - 192 - grp * 128;  // 0..127 within the group
+        const int ngrp = L::TMA_EPI ? 2 : (p.epi_groups == 3 ? 3 : 2);  // groups sharing the staged epilogue's tiles
         if constexpr (L::TMA_EPI) {
             epilogue_tma<KIND, BN, NACC>(p, grp, warp, lane, tmem_base, stage_buf + grp * p.epi_bufs * EPI_TILE_BYTES, acc_full,
                                          acc_empty, rows_ready + grp * 3, avail + grp * 3, abort_flag);
@@ -758,11 +760,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                              : (p.act_th == 0.f && p.act_val == 0.f) ? 3 : 1;
         bool alive = true;
         int sub_it = 0;                        // staging blocks this group has processed
-        int *tbl = reinterpret_cast<int *>(stage_buf + 2 * L::STAGING_PAD + grp * L::TBL_BYTES);  // uint8 only
+        int *tbl = reinterpret_cast<int *>(stage_buf + 3 * L::STAGING_PAD + grp * L::TBL_BYTES);  // uint8 only
         const uint32_t bar_tbl = smem_u32(&rows_ready[6 + grp]);
         int tbl_n0 = -1;
         uint32_t tbl_phase = 0;
-        for (int lt = grp; alive; lt += 2) {
+        for (int lt = grp; alive; lt += ngrp) {
             const int tile = blockIdx.x + lt * gridDim.x;
             if (tile >= total_tiles) break;
             const int m0 = (tile / p.n_tiles) * BM, n0 = (tile % p.n_tiles) * BN;
@@ -1145,6 +1147,11 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
     }
     const int tiles = (p.pair ? (p.m_tiles + 1) / 2 : p.m_tiles) * p.n_tiles;  // units of work
     const int grid = tiles < num_sms() ? tiles : num_sms();
+    if (!L::TMA_EPI) {
+        // staged epilogue: uint8 with nothing to gather runs a third group on warps 0-3 (a fourth accumulator exists below 256 columns)
+        p.epi_groups = KIND == 2 && p.a_tma && BN < 256 ? 3 : 2;
+        if (const char *e = getenv("THB200_EPI_GROUPS")) p.epi_groups = atoi(e) == 3 && KIND == 2 && p.a_tma && BN < 256 ? 3 : 2;
+    }
     if (L::TMA_EPI) {
         if (!tm.y || (p.res && !tm.r)) return thb_note_launch(cudaErrorUnknown, "conv_tc: output tensor map");
         // Shared memory is split between pipeline stages and the epilogue's 16 KB tiles (groups x tiles per group); which
