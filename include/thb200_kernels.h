@@ -122,6 +122,12 @@ int thb_preprocess_s2d(const float *x_nchw, float *x_inplace, int N, int C, int 
  * pixels (the layout thb_conv_desc.in_row_pitch describes); every pixel of y, padding included, is written */
 int thb_preprocess_s2d_padded(const float *x_nchw, float *x_inplace, int N, int C, int H, int W, const float *mean3,
                               const float *std3, int dtype, void *y, int y_ld, int row_pitch, int pad_left, thb_stream s);
+/* the same for the uint8 engine: normalise, quantise with the batch's measured range exactly as thb_preprocess does
+ * (lowp/lowp_basic.c:15-35), store space-to-depth.  Zero weights quantise to the weights' zero point, whose products
+ * vanish exactly (lowp_basic.c:310-320: the offsets are the rounded zero points), so the rewritten stride-1 convolution
+ * gives the accumulators of the stride-2 one bit for bit. */
+int thb_preprocess_s2d_u8(const float *x_nchw, float *x_inplace, int N, int C, int H, int W, const float *mean3,
+                          const float *std3, void *y, int y_ld, float q_sub, float q_mult, thb_stream s);
 /* 1 when the device and driver accept the single-copy row fetch described at thb_conv_desc.in_row_pitch */
 int thb_conv_padded_rows_supported(int dtype);
 /* u8 HWC images (already on the device, row stride `stride`) -> normalised NHWC dtype (thapi.c:20-46) */

@@ -496,7 +496,7 @@ static int plan_gemm_group(planner *P, int i)
                         int tr = r - n->padH + 2 * s2d_padH, tq = q - n->padW + 2 * s2d_padW; /* >= 0 */
                         int dh = tr / 2, ph = tr % 2, dw = tq / 2, pw = tq % 2;
                         w_tmp[(((size_t)co * Cin + (ph * 2 + pw) * n->Cin + c) * kH + dh) * kW + dw] =
-                            n->weight[(((size_t)co * n->Cin + c) * n->kH + r) * n->kW + q];
+                            (w_fold ? w_fold : n->weight)[(((size_t)co * n->Cin + c) * n->kH + r) * n->kW + q];
                     }
         w_oihw = w_tmp;
     } else {
@@ -916,10 +916,11 @@ static int instance_build(thb_engine *E, instance *I, int device, int slice_off,
         /* a stride-2 convolution on very few channels as the only consumer of the float input: stage the input
          * space-to-depth so that the gathered 16-byte chunks carry four times as many useful channels */
         thb_node *c1 = M->nnodes > 1 ? &M->nodes[1] : 0;
-        const char *off = getenv("THB200_NO_S2D");
+        const char *off = getenv("THB200_NO_S2D"), *u8off = getenv("THB200_NO_S2D_U8");
         E->input_s2d = c1 && c1->op == OP_CONV && c1->in[0] == 0 && P.uses[0] == 1 && c1->dH == 2 && c1->dW == 2 &&
                        4 * E->C <= 16 && c1->Cin == E->C && E->H % 2 == 0 && E->W % 2 == 0 && E->rank == 4 && E->cp == 0 &&
-                       (E->dtype == THB_F16 || E->dtype == THB_BF16) && c1->padH <= c1->kH - 1 && c1->padW <= c1->kW - 1 &&
+                       (E->dtype == THB_F16 || E->dtype == THB_BF16 || (E->dtype == THB_U8 && !(u8off && atoi(u8off)))) &&
+                       c1->padH <= c1->kH - 1 && c1->padW <= c1->kW - 1 &&
                        !(off && atoi(off));
         if (E->input_s2d) { in.C = 4 * E->C; in.H = E->H / 2; in.W = E->W / 2; }
     }
@@ -1337,7 +1338,10 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
         CU(cudaSetDevice(I->device));
         int rc;
         void *in_ptr = bufptr(I, I->in_val.buf, 0, E->dtype);
-        if (x && E->input_s2d)
+        if (x && E->input_s2d && E->dtype == THB_U8)
+            rc = thb_preprocess_s2d_u8(I->d_in, inplace ? I->d_in : 0, I->slice_n, C, H, W, mean, std, in_ptr, I->in_val.ld, q_sub,
+                                       q_mult, I->stream);
+        else if (x && E->input_s2d)
             rc = thb_preprocess_s2d_padded(I->d_in, inplace ? I->d_in : 0, I->slice_n, C, H, W, mean, std, E->dtype, in_ptr,
                                            I->in_val.ld, I->in_val.row_pitch ? I->in_val.row_pitch : W / 2,
                                            I->in_val.pad_left, I->stream);

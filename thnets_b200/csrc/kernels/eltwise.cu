@@ -139,8 +139,9 @@ __global__ void preprocess_kernel(const float *x, float *x_inplace, int N, int C
 // a row is written here, the padding as zeros.
 template <typename T>
 __global__ void preprocess_s2d_kernel(const float *x, float *x_inplace, int N, int C, int H, int W, float3 mean,
-                                      float3 std_, T *y, int y_ld, int row_pitch, int pad_left)
+                                      float3 std_, T *y, int y_ld, int row_pitch, int pad_left, float q_min, float q_mult)
 {
+    const float zr = roundf(q_min * q_mult);  // uint8 only: the quantisation of preprocess_kernel
     constexpr int VN = Vec<T>::N;
     const int H2 = H / 2, W2 = W / 2;
     const long pix = (long)blockIdx.x * blockDim.x + threadIdx.x;  // over the stored (padded) pixels
@@ -162,6 +163,7 @@ __global__ void preprocess_s2d_kernel(const float *x, float *x_inplace, int N, i
                 val = x[idx];
                 if (c < 3) val = __fdiv_rn(__fsub_rn(val, m[c]), sd[c]);
                 if (x_inplace) x_inplace[idx] = val;
+                if (sizeof(T) == 1) val = (float)(((int)(roundf(val * q_mult) - zr)) & 255);
             }
             v[i] = val;
         }
@@ -624,8 +626,20 @@ int thb_preprocess_s2d_padded(const float *x, float *x_inplace, int N, int C, in
     if (pix == 0) return THB_OK;
     float3 m = make_float3(mean3[0], mean3[1], mean3[2]), sd = make_float3(std3[0], std3[1], std3[2]);
     DISPATCH_FLOAT_DTYPE(dtype, (preprocess_s2d_kernel<T><<<nblocks(pix), 256, 0, (cudaStream_t)s>>>(
-                                    x, x_inplace, N, C, H, W, m, sd, (T *)y, y_ld, row_pitch, pad_left)));
+                                    x, x_inplace, N, C, H, W, m, sd, (T *)y, y_ld, row_pitch, pad_left, 0.f, 0.f)));
     return THB_LAUNCH_CHECK("preprocess_s2d_kernel");
+}
+
+int thb_preprocess_s2d_u8(const float *x, float *x_inplace, int N, int C, int H, int W, const float *mean3, const float *std3,
+                          void *y, int y_ld, float q_sub, float q_mult, thb_stream s)
+{
+    if ((H | W) & 1) return THB_ERR_ARG;
+    const long pix = (long)N * (H / 2) * (W / 2);
+    if (pix == 0) return THB_OK;
+    float3 m = make_float3(mean3[0], mean3[1], mean3[2]), sd = make_float3(std3[0], std3[1], std3[2]);
+    preprocess_s2d_kernel<uint8_t><<<nblocks(pix), 256, 0, (cudaStream_t)s>>>(x, x_inplace, N, C, H, W, m, sd, (uint8_t *)y, y_ld,
+                                                                              W / 2, 0, q_sub, q_mult);
+    return THB_LAUNCH_CHECK("preprocess_s2d_kernel<u8>");
 }
 
 int thb_preprocess_s2d(const float *x, float *x_inplace, int N, int C, int H, int W, const float *mean3,
