@@ -325,6 +325,11 @@ template <typename T2> __device__ __forceinline__ uint4 max8(const uint4 &a, con
     for (int i = 0; i < 4; i++) pr[i] = __hmax2(pa[i], pb[i]);
     return r;
 }
+struct U8x4 {};  // sixteen uint8 channels per 16-byte vector, maxima by __vmaxu4
+template <> __device__ __forceinline__ uint4 max8<U8x4>(const uint4 &a, const uint4 &b)
+{
+    return make_uint4(__vmaxu4(a.x, b.x), __vmaxu4(a.y, b.y), __vmaxu4(a.z, b.z), __vmaxu4(a.w, b.w));
+}
 template <typename T2>
 __global__ void maxpool3s2_kernel(const uint4 *__restrict__ x, int N, int H, int W, int cvecs, int x_ld8, int padH, int padW,
                                   int oH, int oW, int strip, int nstrips, uint32_t neg_inf2, uint4 *__restrict__ y, int y_ld8)
@@ -741,6 +746,17 @@ int thb_maxpool(int dtype, const void *x, int N, int H, int W, int C, int x_ld, 
         else
             maxpool3s2_kernel<__nv_bfloat162><<<nblocks(items), 256, 0, (cudaStream_t)s>>>(
                 (const uint4 *)x, N, H, W, cvecs, x_ld / 8, padH, padW, oH, oW, strip, nstrips, 0xFF80FF80u, (uint4 *)y, y_ld / 8);
+        return THB_LAUNCH_CHECK("maxpool3s2_kernel");
+    }
+    if (dtype == THB_U8 && kH == 3 && kW == 3 && dH == 2 && dW == 2 && x_ld % 16 == 0 && y_ld % 16 == 0) {
+        // the same kernel on 16-channel vectors; the maximum starts from byte 0 as lowp_SpatialMaxPooling.c does
+        const int cvecs = (C + 15) / 16;
+        int strip = oH;
+        while (strip > 4 && (long)N * ((oH + strip - 1) / strip) * oW * cvecs < 8L * 148 * 256) strip = (strip + 1) / 2;
+        const int nstrips = (oH + strip - 1) / strip;
+        const long items = (long)N * nstrips * oW * cvecs;
+        maxpool3s2_kernel<U8x4><<<nblocks(items), 256, 0, (cudaStream_t)s>>>(
+            (const uint4 *)x, N, H, W, cvecs, x_ld / 16, padH, padW, oH, oW, strip, nstrips, 0u, (uint4 *)y, y_ld / 16);
         return THB_LAUNCH_CHECK("maxpool3s2_kernel");
     }
     DISPATCH_ANY_DTYPE(dtype, (pool_kernel<T, true><<<nblocks(total), 256, 0, (cudaStream_t)s>>>(
