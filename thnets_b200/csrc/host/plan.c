@@ -1225,7 +1225,7 @@ static int engine_build(thb_engine *E, int N, int C, int H, int W, int rank, int
      * millisecond; the uint8 engine needs the input range of the whole batch before any kernel can start */
     const int per_gpu = N / G;
     const double in_mb = (double)per_gpu * C * H * W * 4 / 1e6;
-    E->chunks = E->dtype == THB_U8 || in_mb < 32 ? 1 : per_gpu >= 128 ? 4 : per_gpu >= 32 ? 2 : 1;
+    E->chunks = E->dtype == THB_U8 || in_mb < 32 ? 1 : per_gpu >= 32 ? 2 : 1;
     const char *ce = getenv("THB200_CHUNKS");
     if (ce) E->chunks = atoi(ce) < 1 || E->dtype == THB_U8 ? 1 : atoi(ce) > 4 ? 4 : atoi(ce);
     if (E->chunks > per_gpu) E->chunks = 1;
