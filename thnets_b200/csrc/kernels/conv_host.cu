@@ -64,6 +64,8 @@ extern "C" int thb_conv_geometry(thb_conv_desc *d)
         else if (d->Ktot_pad / bke >= bn256_min_kb() && mtiles * ((d->Cout + 255) / 256) >= 148 &&
                  round_up(d->Cout, 256) == round_up(d->Cout, 128)) d->BN = 256; /* wide tiles pay once the K loop outweighs the epilogue and every SM gets a tile */
         else d->BN = 128;
+        /* a launch of a few tiles only (a Linear on a batch of pixels): narrower tiles give more SMs a share of the weights */
+        if (d->BN == 128 && mtiles * ((d->Cout + 127) / 128) * 4 <= 148) d->BN = 64;
     }
     d->Cout_pad = round_up(d->Cout, d->BN);
     return THB_OK;

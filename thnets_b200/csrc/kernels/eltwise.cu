@@ -295,7 +295,8 @@ __global__ void pool_kernel(const T *x, int N, int H, int W, int C, int x_ld, in
         for (int i = 0; i < VN; i++) acc[i] = 0.f;
     }
     for (int h = hs; h < he; h++)
-        for (int w = ws; w < we; w++) {
+#pragma unroll 4
+        for (int w = ws; w < we; w++) {  // (unrolled: four independent loads in flight; a 7x7 global pool is latency-bound)
             float v[VN];
             Vec<T>::load(x + ((size_t)(n * H + h) * W + w) * x_ld + cv * VN, v);
 #pragma unroll
