@@ -141,6 +141,58 @@ def test_pytorch_dump_loader_shares_referenced_nodes(th, tmp_path):
     th.free_network(h)
 
 
+def test_onnx_reader_builds_the_same_graph(th, tmp_path):
+    """The protobuf-free ONNX reader (onnx.cc:572-834 without protoc): batch normalisations are absorbed into their
+    convolutions, a bias written as Add-of-a-constant and a padding written as a Pad node fold back, shared tensors are
+    referenced, and what comes out is the node tree of the PyTorch-dump route."""
+    g = fx.resnet18(width=0.25, size=64, classes=10)
+    ref_lines = None
+    for variant in ({}, {"bias_as_add": True, "pad_nodes": True}):
+        p = str(tmp_path / "r18.onnx")
+        fx.write_onnx(g, p, **variant)
+        h = th.load_network(p)
+        s = THNetworkStruct.from_address(h)
+        assert s.pynet and not s.net
+        lines = describe(th, h)
+        assert sum(" conv " in line for line in lines) == 20
+        assert not any(" bn " in line for line in lines)           # absorb_bn (onnx.cc:472-570)
+        combines = [line for line in lines if " combine " in line]
+        assert len(combines) == 8 and all("+1 -1" in c for c in combines)   # ONNX Add is CAddTable too (onnx.cc:46)
+        assert sum("p3,3" in line for line in lines) == 1          # the stem's padding, Pad node or attribute
+        if ref_lines is None:
+            ref_lines = lines
+        assert len(lines) == len(ref_lines)
+        th.free_network(h)
+    # VGG (biases everywhere) and the encoder-decoder (ConvTranspose, Concat)
+    for build in (lambda: fx.vgg16(width=0.125, size=32, classes=10, fc=64), lambda: fx.segnet(width=0.25, size=32, classes=5)):
+        g2 = build()
+        p = str(tmp_path / "m.onnx")
+        fx.write_onnx(g2, p, bias_as_add=True)
+        h = th.load_network(p)
+        lines = describe(th, h)
+        assert sum((" conv " in line) or (" deconv " in line) or (" linear " in line) for line in lines) == \
+            sum(n.op in ("conv", "deconv", "linear") for n in g2.nodes)
+        th.free_network(h)
+
+
+def test_onnx_reader_rejects_what_it_cannot_read(th, tmp_path):
+    bad = tmp_path / "bad.onnx"
+    bad.write_bytes(b"\x3a\x05hello")                   # field 7 (graph) holding garbage
+    assert not th.lib.THLoadNetwork(str(bad).encode())
+    # an operator outside the supported set is an error, not a silent Dropout
+    g = fx.Graph(0)
+    g.input_shape = (3, 8, 8)
+    x = g.conv(0, 3, 4, 3, 1, 1)
+    g.softmax(x)
+    p = str(tmp_path / "ok.onnx")
+    fx.write_onnx(g, p)
+    raw = open(p, "rb").read()
+    assert raw.count(b"Softmax") == 1
+    open(p, "wb").write(raw.replace(b"Softmax", b"Softmin"))
+    assert not th.lib.THLoadNetwork(p.encode())
+    assert b"Unsupported node type Softmin" in th.lib.THB200_LastErrorString()
+
+
 def test_make_spatial_rewrites_the_classifier(th, tmp_path):
     g = fx.vgg16(width=0.125, size=32, classes=10, fc=64)
     d = str(tmp_path / "vgg")

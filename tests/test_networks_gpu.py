@@ -78,6 +78,28 @@ def test_network_parity(th, oracle, tmp_path, name, mode):
     th.free_network(hc)
 
 
+@pytest.mark.parametrize("name", ["alexnet_owt_b5", "resnet18", "resnet50", "segnet_bias", "vgg16"])
+@pytest.mark.parametrize("variant", [{}, {"bias_as_add": True, "pad_nodes": True}], ids=["plain", "add_pad"])
+def test_onnx_network_parity(th, oracle, tmp_path, name, variant):
+    """The same networks through the ONNX reader (batch-norm absorbed into the convolutions in fp32 as absorb_bn does,
+    onnx.cc:472-570): fp32 results within 1e-4 of the CPU oracle."""
+    build, batch, _ = NETS[name]
+    g = build()
+    x = g.make_input(batch)
+    ref = oracle.run(g, x)
+    p = str(tmp_path / (name + ".onnx"))
+    fx.write_onnx(g, p, **variant)
+    h = th.load_network(p)
+    th.set_stats(h, g.mean, g.std)
+    hc = th.lib.THCreateCudaNetwork(h)
+    assert hc, th.lib.THB200_LastErrorString()
+    th.free_network(h)
+    out, _, _ = th.process_float(hc, x)
+    assert out.size == ref.size
+    assert rel_err(out, ref.ravel()) < 1e-4
+    th.free_network(hc)
+
+
 def test_unconverted_network_runs_on_gpu_fp32(th, oracle, tmp_path):
     g = fx.alexnet_owt(width=0.25, size=224, classes=50, fc=128)
     x = g.make_input(1)

@@ -92,8 +92,20 @@ THNETWORK *THLoadNetwork(const char *path)
     for (int i = 0; i < 3; i++) net->std[i] = 1;
     lasterror = 0;
 
-    /* 1. a PyTorch graph dump, either the file itself or <path>/pymodel.net (thapi.c:264-271) */
     net->allpynodes = calloc(MAXPYNODES, sizeof(*net->allpynodes));
+    /* 0. an ONNX model, by the file name's ending (thapi.c:254-262); the result is held as a graph-dump network */
+    {
+        size_t n = strlen(path);
+        if ((n > 3 && !strcasecmp(path + n - 3, ".pb")) || (n > 6 && !strcasecmp(path + n - 6, ".proto")) ||
+            (n > 5 && !strcasecmp(path + n - 5, ".onnx"))) {
+            char why[256] = "";
+            net->pynet = loadonnx(path, net->allpynodes, why, sizeof(why));
+            if (net->pynet) return net;
+            if (*why) thb_set_error("%s: %s", path, why);
+            memset(net->allpynodes, 0, MAXPYNODES * sizeof(*net->allpynodes));
+        }
+    }
+    /* 1. a PyTorch graph dump, either the file itself or <path>/pymodel.net (thapi.c:264-271) */
     net->pynet = loadpytorch(path, net->allpynodes);
     if (!net->pynet) {
         snprintf(tmp, sizeof(tmp), "%s/pymodel.net", path);

@@ -283,7 +283,7 @@ static float fval(struct elemlist *l, const char *name, float dflt)
     return (e && e->type == ELTYPE_FLOAT) ? e->fvalue : dflt;
 }
 
-static void build_py_module(const char *fname, struct pyfunction *f)
+void thb_build_py_module(const char *fname, struct pyfunction *f)
 {
     const char *op = strrchr(fname, '.');
     op = op ? op + 1 : fname;
@@ -358,6 +358,8 @@ static void build_py_module(const char *fname, struct pyfunction *f)
         if (e && e->type == ELTYPE_INTVECT) m->View.numElements = e->ivect[1];
     } else if (!strcmp(op, "Add")) {
         m->type = MT_CAddTable;
+    } else if (!strcmp(op, "Sub")) { /* only the ONNX reader produces it (onnx.cc:45) */
+        m->type = MT_CSubTable;
     } else if (!strcmp(op, "Concat")) {
         m->type = MT_JoinTable;
         m->JoinTable.dimension = ival(p, "dim", 0);
@@ -419,7 +421,7 @@ static struct pyelement *rd_element(FILE *fp, struct pyelement **nodes)
             } else
                 append(&e->function.params, child);
         }
-        build_py_module(name, &e->function);
+        thb_build_py_module(name, &e->function);
         return e;
     }
     }

@@ -106,4 +106,9 @@ typedef struct thb_netx {
 } thb_netx;
 #define THB_NETX_MAGIC 0xB2000001u
 
+/* fills f->module from the operator name and the parameter list of a graph function (PyTorch-dump names) */
+void thb_build_py_module(const char *fname, struct pyfunction *f);
+/* ONNX file -> the same node tree (onnx_reader.c); NULL on failure with a message in err */
+struct pyelement *loadonnx(const char *path, struct pyelement **allpynodes, char *err, size_t errlen);
+
 #endif

@@ -510,3 +510,118 @@ BUILDERS = {"alexnet_owt": alexnet_owt, "resnet18": resnet18, "vgg16": vgg16, "s
 # algorithmic GFLOP per image at full size (2 * MACs of conv / deconv / linear layers)
 GFLOP_PER_IMAGE = {"alexnet_owt": 1.428, "resnet18": 3.628, "vgg16": 30.94, "segnet": 18.97,
                    "resnet50": 8.178}
+
+
+# ---------------------------------------------------------------------------------------------- ONNX
+def _pb_varint(v):
+    v &= (1 << 64) - 1
+    out = bytearray()
+    while True:
+        b = v & 0x7F
+        v >>= 7
+        if v:
+            out.append(b | 0x80)
+        else:
+            out.append(b)
+            return bytes(out)
+
+
+def _pb_len(field, payload):
+    return _pb_varint(field << 3 | 2) + _pb_varint(len(payload)) + payload
+
+
+def _pb_int(field, v):
+    return _pb_varint(field << 3) + _pb_varint(int(v))
+
+
+def _onnx_tensor(name, a):
+    """TensorProto: dims = 1, data_type = 2, name = 8, raw_data = 9 (float32 -> 1, int64 -> 7)."""
+    a = np.ascontiguousarray(a)
+    dt = 7 if a.dtype == np.int64 else 1
+    if dt == 1:
+        a = a.astype(np.float32)
+    return b"".join(_pb_int(1, d) for d in a.shape) + _pb_int(2, dt) + _pb_len(8, name.encode()) + _pb_len(9, a.tobytes())
+
+
+def _onnx_attr(name, v):
+    """AttributeProto: name = 1, f = 2, i = 3, s = 4, ints = 8 (one by one), type = 20."""
+    out = _pb_len(1, name.encode())
+    if isinstance(v, float):
+        return out + _pb_varint(2 << 3 | 5) + struct.pack("<f", v) + _pb_int(20, 1)
+    if isinstance(v, int):
+        return out + _pb_int(3, v) + _pb_int(20, 2)
+    if isinstance(v, str):
+        return out + _pb_len(4, v.encode()) + _pb_int(20, 3)
+    return out + b"".join(_pb_int(8, i) for i in v) + _pb_int(20, 7)
+
+
+def write_onnx(graph: Graph, path: str, bias_as_add=False, pad_nodes=False):
+    """Serialise `graph` as an ONNX ModelProto with a hand-written protobuf encoder (no onnx package needed).
+
+    conv -> Conv, deconv -> ConvTranspose, linear -> Gemm(transB=1), bn -> BatchNormalization, threshold(0, 0) -> Relu,
+    maxpool -> MaxPool, avgpool -> AveragePool, view -> Flatten, add -> Add, concat -> Concat, softmax -> Softmax,
+    dropout -> Dropout.  bias_as_add writes a convolution's bias as a separate Add of a constant; pad_nodes writes its
+    padding as a Pad node in front of it (two shapes the reference's loader folds back, onnx.cc:605-700).
+    """
+    nodes, inits = [], []
+
+    def node(op, ins, out, **attrs):
+        body = b"".join(_pb_len(1, i.encode()) for i in ins) + _pb_len(2, out.encode()) + _pb_len(3, ("n_" + out).encode())
+        body += _pb_len(4, op.encode()) + b"".join(_pb_len(5, _onnx_attr(k, v)) for k, v in attrs.items())
+        nodes.append(_pb_len(1, body))
+
+    def init(name, a):
+        inits.append(_pb_len(5, _onnx_tensor(name, a)))
+        return name
+
+    name = {0: "input"}
+    for i, nd in enumerate(graph.nodes):
+        if i == 0:
+            continue
+        a, ts = nd.attrs, [t for _, t in nd.tensors]
+        ins, out = [name[j] for j in nd.inputs], "v%d" % i
+        name[i] = out
+        if nd.op in ("conv", "deconv"):
+            src, pads = ins[0], list(a["padding"]) * 2
+            if pad_nodes and nd.op == "conv" and any(pads):
+                node("Pad", [src], out + "_pad", mode="constant", pads=[0, 0, pads[0], pads[1], 0, 0, pads[2], pads[3]])
+                src, pads = out + "_pad", [0, 0, 0, 0]
+            cin = [src, init(out + "_w", ts[0])]
+            split_bias = bias_as_add and len(ts) > 1
+            if len(ts) > 1 and not split_bias:
+                cin.append(init(out + "_b", ts[1]))
+            extra = dict(output_padding=list(a["output_padding"])) if nd.op == "deconv" else {}
+            node("Conv" if nd.op == "conv" else "ConvTranspose", cin, out + "_c" if split_bias else out,
+                 kernel_shape=list(ts[0].shape[2:]), strides=list(a["stride"]), pads=pads, **extra)
+            if split_bias:
+                node("Add", [out + "_c", init(out + "_b", ts[1])], out)
+        elif nd.op == "linear":
+            node("Gemm", [ins[0], init(out + "_w", ts[0]), init(out + "_b", ts[1])], out, alpha=1.0, beta=1.0, transB=1)
+        elif nd.op == "bn":
+            node("BatchNormalization", [ins[0]] + [init("%s_%d" % (out, k), t) for k, t in enumerate(ts)], out, epsilon=float(a["eps"]))
+        elif nd.op == "threshold":
+            if a["threshold"] != 0 or a["value"] != 0:
+                raise ValueError("only ReLU maps onto ONNX here")
+            node("Relu", ins, out)
+        elif nd.op in ("maxpool", "avgpool"):
+            extra = dict(ceil_mode=int(a["ceil_mode"])) if a["ceil_mode"] else {}
+            node("MaxPool" if nd.op == "maxpool" else "AveragePool", ins, out, kernel_shape=list(a["kernel_size"]),
+                 strides=list(a["stride"]), pads=list(a["padding"]) * 2, **extra)
+        elif nd.op == "view":
+            node("Flatten", ins, out, axis=1)
+        elif nd.op == "dropout":
+            node("Dropout", ins, out)
+        elif nd.op == "softmax":
+            node("Softmax", ins, out, axis=1)
+        elif nd.op == "add":
+            node("Add", ins, out)
+        elif nd.op == "concat":
+            node("Concat", ins, out, axis=int(a["dim"]))
+        else:
+            raise ValueError("no ONNX form for " + nd.op)
+    value_info = lambda n: _pb_len(1, n.encode())
+    g = b"".join(nodes) + _pb_len(2, b"thnets_b200_fixture") + b"".join(inits)
+    g += _pb_len(11, value_info("input")) + _pb_len(12, value_info(name[graph.output]))
+    model = _pb_int(1, 3) + _pb_len(2, b"thnets_b200") + _pb_len(7, g)
+    with open(path, "wb") as f:
+        f.write(model)
