@@ -216,6 +216,24 @@ def test_pipelined_sub_batches_give_the_same_result(th, oracle, tmp_path, chunks
     th.free_network(hc)
 
 
+def test_pipelined_images_give_the_same_result(th, tmp_path):
+    """THProcessImages pipelines sub-batches the same way (device-side conversion of each sub-batch's bytes)."""
+    g = fx.resnet18(width=0.25, size=64, classes=10)
+    hc = _convert(th, g, "py", tmp_path, "r18i", 1)
+    rng = np.random.default_rng(5)
+    imgs = [rng.integers(0, 256, (64, 64, 3)).astype(np.uint8) for _ in range(7)]
+    try:
+        th.lib.THB200_SetPipelineChunks(1)
+        whole = th.process_images(hc, imgs, bgr=0)[0].copy()
+        for chunks in (2, 3):
+            th.lib.THB200_SetPipelineChunks(chunks)
+            for _ in range(3):
+                assert np.array_equal(whole, th.process_images(hc, imgs, bgr=0)[0])
+    finally:
+        th.lib.THB200_SetPipelineChunks(0)
+    th.free_network(hc)
+
+
 def test_graph_replay_matches_direct_launches(th, tmp_path):
     g = fx.resnet50(width=0.125, size=64, classes=10)
     x = g.make_input(3)

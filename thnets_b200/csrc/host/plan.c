@@ -1271,13 +1271,13 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
     if (!E->built || E->N != N || E->C != C || E->H != H || E->W != W || E->rank != rank || E->cp != cp) {
         if (engine_build(E, N, C, H, W, rank, cp)) return -1;
     }
-    /* host float input: run the sub-batch instances so that copies and kernels overlap */
+    /* host input (a float batch or byte images): run the sub-batch instances so that copies and kernels overlap */
     instance *set = E->inst;
     int G = E->built;
     int peer_gather = E->peer_gather;
     int S = g_chunks_override ? g_chunks_override : E->chunks;
     if (E->dtype == THB_U8 || S > E->inst[0].slice_n) S = 1;
-    if (x && S > 1) {
+    if (S > 1) {
         if ((!E->pipe_built || E->pipe_chunks != S) && pipe_build(E, S)) return -1;
         set = E->pipe;
         G = E->pipe_built;
