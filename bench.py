@@ -15,7 +15,10 @@ JSON line (rank 0):
   e2e      the same through THProcessFloat with a pinned HOST batch: H2D of the fp32 input and D2H of the
            logits inside the timed region (wall clock, max over ranks);
   roofline the dominant kernel (implicit-GEMM convolution): algorithmic FLOPs of all its launches in one
-           forward / their summed event-timed durations, against the measured bf16 GEMM peak;
+           forward / their summed event-timed durations, against the measured bf16 GEMM peak (twice that for
+           uint8); roofline.two_roof_bound: the time those launches would take if each ran at the slower of its
+           two roofs (FLOPs / tensor peak, algorithmic bytes / measured HBM bandwidth) and its ratio to the
+           measured time -- many layers of a residual network are HBM-bound;
   cpu_baseline the unmodified reference CPU build timed on this box's host cores on a bounded sample.
 `--impl reference` times only that CPU reference and prints the same line with "impl": "reference".
 """
