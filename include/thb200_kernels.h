@@ -39,7 +39,11 @@ typedef enum {
 typedef void *thb_stream; /* cudaStream_t */
 
 /* fused activation, applied last.  Threshold.c:38-63, PReLU.c:32-92 */
-typedef enum { THB_ACT_NONE = 0, THB_ACT_THRESHOLD = 1, THB_ACT_LEAKY = 2, THB_ACT_PRELU = 3 } thb_act_kind;
+typedef enum {
+    THB_ACT_NONE = 0, THB_ACT_THRESHOLD = 1, THB_ACT_LEAKY = 2, THB_ACT_PRELU = 3,
+    THB_ACT_SIGMOID = 4, /* 1/(1 + expf(-x)), modules/Sigmoid.c:24 */
+    THB_ACT_TANH = 5     /* tanhf(x), modules/Tanh.c */
+} thb_act_kind;
 typedef struct thb_act {
     int kind;
     float threshold, value, alpha; /* x > threshold ? x : value   |   x >= 0 ? x : alpha*x */

@@ -216,6 +216,10 @@ class Oracle:
                 y = x
             elif node.op == "softmax":
                 y = self.softmax(x)
+            elif node.op == "sigmoid":      # modules/Sigmoid.c:24, float arithmetic
+                y = (np.float32(1) / (np.float32(1) + np.exp(-x.astype(np.float32)))).astype(np.float32)
+            elif node.op == "tanh":         # modules/Tanh.c
+                y = np.tanh(x.astype(np.float32)).astype(np.float32)
             elif node.op == "add":
                 y = self.caddtable(xin)
             elif node.op == "concat":

@@ -100,6 +100,32 @@ def test_onnx_network_parity(th, oracle, tmp_path, name, variant):
     th.free_network(hc)
 
 
+@pytest.mark.parametrize("mode", [0, 1], ids=["fp32", "fp16"])
+def test_onnx_sigmoid_tanh(th, oracle, tmp_path, mode):
+    """Sigmoid and Tanh exist on the ONNX route only, as in the reference (onnx.cc:59-60, modules/Sigmoid.c, Tanh.c):
+    fused into the convolution before them or run as a kernel of their own (after the pooling)."""
+    g = fx.Graph(7)
+    g.input_shape = (3, 20, 20)
+    x = g.sigmoid(g.conv(0, 3, 12, 3, 1, 1, bias=0.1))
+    x = g.tanh(g.maxpool(x, 2, 2))
+    x = g.tanh(g.conv(x, 12, 20, 3, 1, 1, bias=0.1))
+    x = g.view(x, 20 * 10 * 10)
+    g.sigmoid(g.linear(x, 20 * 10 * 10, 7, bias=0.1))
+    xin = g.make_input(3)
+    ref = oracle.run(g, xin)
+    p = str(tmp_path / "st.onnx")
+    fx.write_onnx(g, p)
+    h = th.load_network(p)
+    th.lib.THB200_SetPrecision(mode)
+    hc = th.lib.THCreateCudaNetwork(h)
+    th.lib.THB200_SetPrecision(0)
+    assert hc, th.lib.THB200_LastErrorString()
+    th.free_network(h)
+    out, _, _ = th.process_float(hc, xin)
+    assert rel_err(out, ref.ravel()) < TOL[mode]
+    th.free_network(hc)
+
+
 def test_unconverted_network_runs_on_gpu_fp32(th, oracle, tmp_path):
     g = fx.alexnet_owt(width=0.25, size=224, classes=50, fc=128)
     x = g.make_input(1)

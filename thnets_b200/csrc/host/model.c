@@ -138,6 +138,10 @@ static int lower_leaf(builder *b, struct module *m, val in, val *out)
         if (m->Threshold.alpha) { n->act_kind = THB_ACT_LEAKY; n->act_alpha = m->Threshold.alpha; }
         else { n->act_kind = THB_ACT_THRESHOLD; n->act_threshold = m->Threshold.threshold; n->act_value = m->Threshold.val; }
         break;
+    case MT_Sigmoid: case MT_Tanh: /* reachable through the ONNX reader only, as in the reference (onnx.cc:59-60) */
+        n = new_node(b, OP_ACT, 1, in.id);
+        n->act_kind = m->type == MT_Sigmoid ? THB_ACT_SIGMOID : THB_ACT_TANH;
+        break;
     case MT_PReLU:
         n = new_node(b, OP_ACT, 1, in.id);
         n->act_kind = THB_ACT_PRELU;

@@ -358,6 +358,10 @@ void thb_build_py_module(const char *fname, struct pyfunction *f)
         if (e && e->type == ELTYPE_INTVECT) m->View.numElements = e->ivect[1];
     } else if (!strcmp(op, "Add")) {
         m->type = MT_CAddTable;
+    } else if (!strcmp(op, "Sigmoid")) { /* these two: the ONNX reader only (onnx.cc:59-60) */
+        m->type = MT_Sigmoid;
+    } else if (!strcmp(op, "Tanh")) {
+        m->type = MT_Tanh;
     } else if (!strcmp(op, "Sub")) { /* only the ONNX reader produces it (onnx.cc:45) */
         m->type = MT_CSubTable;
     } else if (!strcmp(op, "Concat")) {

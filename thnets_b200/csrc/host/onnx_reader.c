@@ -593,8 +593,8 @@ static struct pyelement *ox_value(ox_build *b, const char *name)
         par_int(&e->function, "inplace", 0);
     } else if (!strcmp(op, "Dropout") || !strcmp(op, "Identity"))
         e = ox_function(b, idx, "Dropout", (const char *const *)&n->in[0], 1);
-    else if (!strcmp(op, "Softmax"))
-        e = ox_function(b, idx, "Softmax", (const char *const *)&n->in[0], 1);
+    else if (!strcmp(op, "Softmax") || !strcmp(op, "Sigmoid") || !strcmp(op, "Tanh"))
+        e = ox_function(b, idx, op, (const char *const *)&n->in[0], 1);
     else if (!strcmp(op, "Flatten") || !strcmp(op, "Reshape")) {
         /* View.c: the batch dimension stays, everything else becomes one dimension */
         if (!strcmp(op, "Reshape")) {

@@ -34,6 +34,8 @@ __device__ __forceinline__ float thb_apply_act(float v, int kind, float th, floa
     if (kind == THB_ACT_THRESHOLD) return v > th ? v : val;
     if (kind == THB_ACT_LEAKY) return v >= 0.f ? v : v * alpha;
     if (kind == THB_ACT_PRELU) return v > 0.f ? v : slope * v;
+    if (kind == THB_ACT_SIGMOID) return 1.0f / (1.0f + expf(-v));
+    if (kind == THB_ACT_TANH) return tanhf(v);
     return v;
 }
 

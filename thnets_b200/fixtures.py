@@ -115,6 +115,12 @@ class Graph:
     def softmax(self, x):
         return self._add("softmax", [x])
 
+    def sigmoid(self, x):
+        return self._add("sigmoid", [x])
+
+    def tanh(self, x):
+        return self._add("tanh", [x])
+
     def add(self, a, b):
         """Reference semantics for two inputs: a - b (CAddTable.c:59-69)."""
         return self._add("add", [a, b])
@@ -613,6 +619,8 @@ def write_onnx(graph: Graph, path: str, bias_as_add=False, pad_nodes=False):
             node("Dropout", ins, out)
         elif nd.op == "softmax":
             node("Softmax", ins, out, axis=1)
+        elif nd.op in ("sigmoid", "tanh"):
+            node(nd.op.capitalize(), ins, out)
         elif nd.op == "add":
             node("Add", ins, out)
         elif nd.op == "concat":

@@ -11,7 +11,7 @@ import os
 import numpy as np
 
 THB_F32, THB_F16, THB_BF16, THB_U8 = 0, 1, 2, 3
-ACT_NONE, ACT_THRESHOLD, ACT_LEAKY, ACT_PRELU = 0, 1, 2, 3
+ACT_NONE, ACT_THRESHOLD, ACT_LEAKY, ACT_PRELU, ACT_SIGMOID, ACT_TANH = 0, 1, 2, 3, 4, 5
 ESIZE = {THB_F32: 4, THB_F16: 2, THB_BF16: 2, THB_U8: 1}
 ALIGN = {THB_F32: 4, THB_F16: 8, THB_BF16: 8, THB_U8: 16}
 
