@@ -97,6 +97,14 @@ typedef struct thb_conv_desc {
      * at least kW - 1 - padW zero pixels; in_pad_left must equal padW.  When a row's kW taps then fill exactly
      * 128 bytes (kW * Cin_pad elements) and dW is 1, the tensor-core path fetches all of them with one copy. */
     int in_row_pitch, in_pad_left;
+    /* Second activation operand (NULL: none; fp16 / bf16 only).  A 1x1 stride-1 unpadded convolution whose Cin input
+     * channels come from TWO tensors: the first cin1 from x, the remaining Cin - cin1 from x2, an [N][x2_H][x2_W][x2_ld]
+     * tensor sampled with stride x2_d (x2_H, x2_W must give the same oH x oW).  With the weights of two 1x1
+     * convolutions side by side along K this computes their sum in one accumulator: a bottleneck block's last
+     * convolution and its projection shortcut, without writing either addend.  cin1 and Cin - cin1 are multiples of 64.
+     * No counterpart in the reference, which runs the two convolutions and a CAddTable. */
+    const void *x2;
+    int x2_ld, x2_H, x2_W, x2_d, cin1;
 } thb_conv_desc;
 
 int thb_channel_align(int dtype);               /* 4 (F32), 8 (F16/BF16), 16 (U8) */

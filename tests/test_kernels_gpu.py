@@ -221,6 +221,35 @@ def test_conv_strided_views(lib, G, oracle, dtype):
     assert float((y[..., cout:].float() - 9.0).abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("geom", [(3, 64, 128, 12, 12, 1, 256), (2, 128, 64, 14, 10, 2, 136), (5, 64, 64, 7, 7, 2, 64)])
+def test_conv_f16_two_activation_operands(lib, G, oracle, geom):
+    """A 1x1 convolution whose input channels come from two tensors (thb_conv_desc.x2): the sum of a 1x1 convolution of x
+    and a strided 1x1 convolution of x2 in one accumulator, as a bottleneck block's last convolution and its projection
+    shortcut are run.  No reference counterpart as one operator; the oracle adds the two convolutions."""
+    n, c1, c2, oh, ow, d2, cout = geom
+    rng = np.random.default_rng(71)
+    half = lambda a: a.astype(np.float16).astype(np.float32)
+    h2, w2 = (oh - 1) * d2 + 1 + (d2 - 1), (ow - 1) * d2 + 1     # trailing rows the stride never reaches are allowed
+    x1 = half(rng.standard_normal((n, c1, oh, ow)).astype(np.float32))
+    x2 = half(rng.standard_normal((n, c2, h2, w2)).astype(np.float32))
+    w1 = half((rng.standard_normal((cout, c1, 1, 1)) * 0.1).astype(np.float32))
+    w2_ = half((rng.standard_normal((cout, c2, 1, 1)) * 0.1).astype(np.float32))
+    shift = rng.standard_normal(cout).astype(np.float32)
+    ref = oracle.conv2d(x1, w1, None, (1, 1), (0, 0)) + oracle.conv2d(x2, w2_, None, (d2, d2), (0, 0)) + shift.reshape(1, -1, 1, 1)
+    ref = np.maximum(ref, 0)
+    conv = G.Conv(lib, K.THB_F16, (n, c1 + c2, oh, ow), np.concatenate([w1, w2_], axis=1))
+    conv.set_affine(None, shift)
+    conv.set_act(K.ACT_THRESHOLD, 0.0, 0.0)
+    d = conv.d
+    xt1, ld1 = G.to_nhwc(x1, K.THB_F16)
+    xt2, ld2 = G.to_nhwc(x2, K.THB_F16)
+    conv.keep.append(xt2)
+    d.in_ld, d.cin1 = ld1, c1
+    d.x2, d.x2_ld, d.x2_H, d.x2_W, d.x2_d = xt2.data_ptr(), ld2, h2, w2, d2
+    y = conv.run(xt1)
+    assert G.rel_err(G.from_nhwc(y, cout), ref) < TOL[K.THB_F16]
+
+
 # ---------------------------------------------------------------------------------------------- uint8
 def _lowp_case(oracle, G, case, seed, rng_range=8.0):
     n, cin, h, w, cout, k, s, p = case

@@ -97,6 +97,8 @@ typedef struct {
     /* u8 conv constants needed to derive the per-forward parameters */
     float w_sub, w_mult, out_sub, out_mult;
     int flops_node; /* model node index of the conv (profiling) */
+    int dual;       /* convolution with a second activation operand (in_buf[1]) instead of a residual */
+    double flops_extra; /* FLOPs of the second convolution computed by the same launch */
 } step;
 
 typedef struct instance {
@@ -371,10 +373,40 @@ static int plan_gemm_group(planner *P, int i)
             res_coef = M->nodes[j].coef[1 - pos];
         }
     }
+    /* Two 1x1 convolutions whose (batch-normalised) outputs meet in a two-input sum -- a bottleneck block's last
+     * convolution and its projection shortcut -- run as ONE convolution over both inputs: the weights side by side
+     * along K (each scaled by its batch-norm and its coefficient of the sum), one accumulator, neither addend written.
+     * 16-bit tensor-core modes only; the second convolution must not have been planned yet and must be used nowhere else. */
+    int dual_conv = -1, dual_bn = -1;
+    {
+        const char *nodual = getenv("THB200_NO_DUAL");
+        if (comb < 0 && (dtype == THB_F16 || dtype == THB_BF16) && !is_deconv && !is_linear && !s2d && n->kH == 1 && n->kW == 1 &&
+            n->dH == 1 && n->dW == 1 && n->padH == 0 && n->padW == 0 && n->Cin % 64 == 0 && n->Cout >= 64 && !in->row_pitch &&
+            in->coff == 0 && !(nodual && atoi(nodual)) && (j = sole_consumer(P, cur)) >= 0 && M->nodes[j].op == OP_COMBINE &&
+            M->nodes[j].nin == 2) {
+            const int pos = M->nodes[j].in[0] == cur ? 0 : 1, other = M->nodes[j].in[1 - pos];
+            int ob = -1, oc = other;
+            if (other > cur && other < j && M->nodes[other].op == OP_BN && P->uses[other] == 1) { ob = other; oc = M->nodes[other].in[0]; }
+            if (oc > cur && oc < j && P->uses[oc] == 1 && M->nodes[oc].op == OP_CONV && oc != M->output && other != M->output) {
+                const thb_node *c2 = &M->nodes[oc];
+                const value *v2 = &P->val[c2->in[0]];
+                if (c2->kH == 1 && c2->kW == 1 && c2->padH == 0 && c2->padW == 0 && c2->dH == c2->dW && c2->dH >= 1 && c2->dH <= 8 &&
+                    c2->Cout == n->Cout && c2->Cin % 64 == 0 && c2->in[0] <= i && v2->buf >= 0 && !v2->s.flat && v2->s.rank >= 3 &&
+                    v2->s.C == c2->Cin && v2->coff == 0 && !v2->row_pitch && v2->s.N == is.N &&
+                    conv_out(v2->s.H, 1, c2->dH, 0) == os.H && conv_out(v2->s.W, 1, c2->dW, 0) == os.W &&
+                    (ob < 0 || M->nodes[ob].C == n->Cout)) {
+                    dual_conv = oc; dual_bn = ob;
+                    comb = j; cur = j;
+                    self_coef = M->nodes[j].coef[pos];
+                    res_coef = M->nodes[j].coef[1 - pos];
+                }
+            }
+        }
+    }
     if ((j = sole_consumer(P, cur)) >= 0 && M->nodes[j].op == OP_ACT &&
         (dtype != THB_U8 || M->nodes[j].act_kind == THB_ACT_THRESHOLD)) { act = j; cur = j; }
     for (int k = i + 1; k <= cur; k++)
-        if (k == bn || k == comb || k == act) { P->absorbed[k] = 1; P->leader[k] = i; }
+        if (k == bn || k == comb || k == act || k == dual_conv || k == dual_bn) { P->absorbed[k] = 1; P->leader[k] = i; }
 
     /* ---- per-channel scale / shift ---- */
     float *scale = 0, *shift = 0;
@@ -387,8 +419,18 @@ static int plan_gemm_group(planner *P, int i)
             hh[c] = bn >= 0 ? M->nodes[bn].scale[c] * b + M->nodes[bn].shift[c] : b;
         }
         if (bn >= 0 && M->nodes[bn].C != n->Cout) { free(hs); free(hh); thb_set_error("batch-norm width mismatch"); return -1; }
-        if (bn >= 0) scale = dupload(P->I, hs, sizeof(float) * Cp);
-        if ((bn >= 0 || n->bias) && !is_deconv) shift = dupload(P->I, hh, sizeof(float) * Cp);
+        if (dual_conv >= 0) {
+            /* both scales go into the weights (below); what is left is the sum of the two shifts */
+            const thb_node *c2 = &M->nodes[dual_conv];
+            for (int c = 0; c < n->Cout; c++) {
+                const float b2 = c2->bias ? c2->bias[c] : 0.f;
+                const float h2 = dual_bn >= 0 ? M->nodes[dual_bn].scale[c] * b2 + M->nodes[dual_bn].shift[c] : b2;
+                hh[c] = self_coef * hh[c] + res_coef * h2;
+                hs[c] = 1.f;
+            }
+        }
+        if (bn >= 0 && dual_conv < 0) scale = dupload(P->I, hs, sizeof(float) * Cp);
+        if ((dual_conv >= 0 || bn >= 0 || n->bias) && !is_deconv) shift = dupload(P->I, hh, sizeof(float) * Cp);
         free(hs); free(hh);
     }
 
@@ -502,8 +544,26 @@ static int plan_gemm_group(planner *P, int i)
     } else {
         d->Cout = n->Cout; d->oH = os.H; d->oW = os.W;
     }
+    if (dual_conv >= 0) {
+        /* [Cout][cin1 + cin2] weights: each convolution's rows scaled by its batch-norm and its coefficient of the sum */
+        const thb_node *c2 = &M->nodes[dual_conv];
+        const value *v2 = &P->val[c2->in[0]];
+        const int c1n = n->Cin, c2n = c2->Cin;
+        w_tmp = malloc(sizeof(float) * (size_t)n->Cout * (c1n + c2n));
+        for (int co = 0; co < n->Cout; co++) {
+            const float s1 = self_coef * (bn >= 0 ? M->nodes[bn].scale[co] : 1.f);
+            const float s2 = res_coef * (dual_bn >= 0 ? M->nodes[dual_bn].scale[co] : 1.f);
+            float *row = w_tmp + (size_t)co * (c1n + c2n);
+            for (int ci = 0; ci < c1n; ci++) row[ci] = s1 * n->weight[(size_t)co * c1n + ci];
+            for (int ci = 0; ci < c2n; ci++) row[c1n + ci] = s2 * c2->weight[(size_t)co * c2n + ci];
+        }
+        w_oihw = w_tmp;
+        d->Cin = c1n + c2n;
+        d->cin1 = c1n;
+        d->x2_ld = v2->ld; d->x2_H = v2->s.H; d->x2_W = v2->s.W; d->x2_d = c2->dH;
+    }
     if (thb_conv_geometry(d)) { free(w_tmp); thb_set_error("unsupported convolution geometry %dx%d", kH, kW); return -1; }
-    if (in_ld < d->Cin_pad) { free(w_tmp); thb_set_error("internal: input stride %d below padded channels %d", in_ld, d->Cin_pad); return -1; }
+    if (dual_conv < 0 && in_ld < d->Cin_pad) { free(w_tmp); thb_set_error("internal: input stride %d below padded channels %d", in_ld, d->Cin_pad); return -1; }
 
     size_t wbytes = thb_conv_weight_bytes(d), kwords = thb_conv_kinfo_words(d);
     void *packed = malloc(wbytes);
@@ -534,6 +594,11 @@ static int plan_gemm_group(planner *P, int i)
     step_in(s, in);
     s->in_ld[0] = in_ld;
     s->flops_node = i;
+    if (dual_conv >= 0) {
+        step_in(s, &P->val[M->nodes[dual_conv].in[0]]);
+        s->dual = 1;
+        s->flops_extra = 2.0 * is.N * os.H * os.W * (double)n->Cout * M->nodes[dual_conv].Cin;
+    }
 
     if (dtype == THB_U8) {
         if (!bias_eff) { thb_set_error("the lowp engine needs a bias on every convolution"); return -1; }
@@ -988,7 +1053,8 @@ static int run_steps_ev(thb_engine *E, instance *I, cudaEvent_t *evs)
         switch (s->kind) {
         case ST_CONV: {
             thb_conv_desc *d = &s->conv;
-            if (s->nin > 1) d->res = bufptr(I, s->in_buf[1], s->in_coff[1], dt);
+            if (s->dual) d->x2 = bufptr(I, s->in_buf[1], s->in_coff[1], dt);
+            else if (s->nin > 1) d->res = bufptr(I, s->in_buf[1], s->in_coff[1], dt);
             if (s->aux_buf >= 0) d->csum = (const int *)bufptr(I, s->aux_buf, 0, THB_U8);
             rc = thb_conv_fwd(d, x0, y, st);
             break;
@@ -1116,7 +1182,7 @@ int thb_engine_profile(thb_engine *E, int iters, int max_steps, int *kinds, floa
             thb_node *nd = &E->model->nodes[s->flops_node];
             double pix = s->kind == ST_CONV ? (double)s->conv.N * s->conv.oH * s->conv.oW : (double)s->N;
             if (nd->op == OP_DECONV) pix = (double)s->conv.N * s->conv.H * s->conv.W;
-            flops[t] = 2.0 * pix * nd->Cout * nd->Cin * nd->kH * nd->kW;
+            flops[t] = 2.0 * pix * nd->Cout * nd->Cin * nd->kH * nd->kW + s->flops_extra;
         }
     }
     for (int t = 0; t <= I->nsteps; t++) cudaEventDestroy(evs[t]);
@@ -1139,8 +1205,9 @@ int thb_engine_profile_bytes(thb_engine *E, int max_steps, double *bytes)
         if (s->kind == ST_CONV) {
             const thb_conv_desc *d = &s->conv;
             const double out = (double)d->N * d->oH * d->oW * d->Cout;
-            bytes[t] = el * ((double)d->N * d->H * d->W * d->Cin + out * (d->res ? 2 : 1) +
-                             (double)d->Cout * d->Cin * d->kH * d->kW);
+            const double in_elems = s->dual ? (double)d->N * d->H * d->W * d->cin1 + (double)d->N * d->x2_H * d->x2_W * (d->Cin - d->cin1)
+                                            : (double)d->N * d->H * d->W * d->Cin;
+            bytes[t] = el * (in_elems + out * (d->res ? 2 : 1) + (double)d->Cout * d->Cin * d->kH * d->kW);
         } else if (s->kind == ST_GEMV) {
             bytes[t] = el * ((double)s->M * s->K + (double)s->N * (s->K + s->M));
         }

@@ -135,6 +135,11 @@ extern "C" unsigned short thb_float_to_half_bits(float v, int bf16)
 
 extern "C" int thb_conv_fwd(const thb_conv_desc *d, const void *x, void *y, thb_stream s)
 {
+    if (d->x2) {
+        if (d->dtype != THB_F16 && d->dtype != THB_BF16) return THB_ERR_UNSUPPORTED;
+        if (d->in_ld < d->cin1 || d->x2_ld < d->Cin - d->cin1) return THB_ERR_ARG;
+        return thb_conv_fwd_tc(d, x, y, s);
+    }
     if (d->in_ld < d->Cin_pad) return THB_ERR_ARG;
     if (d->in_row_pitch) {
         // rows stored with their padding: tensor-core dtypes only

@@ -70,6 +70,8 @@ struct ConvTcParams {
     int tma_kw, tma_padw;     // a_tma == 2: taps per kernel row that need a load of their own, and the padding the
                               // descriptor's coordinates see (1, 0 when one copy fetches a padded row's kW taps)
     int slabs;   // a_tma == 2: 128-byte channel slabs per tap (K block kb = tap * slabs + slab)
+    int nkb1, a2_mode, a2_d;  // second activation operand (a_tma == 1 only): K blocks nkb1.. come from it, through the fourth
+                              // tensor map (no residual then); a2_mode 1: plain matrix, 2: 1x1 im2col sampling with stride a2_d
     int half, ntaps;  // a_tma == 2, half: a tap is 64 bytes of channels; a K block holds two taps as two tiles of 64-byte rows
                       // (SWIZZLE_64B), each loaded by its own activation and weight copy and fed to two MMAs of K = 32 bytes
     int use_l1;  // gather through L1: neighbouring taps of one tile re-read the same input pixels
@@ -500,7 +502,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
         if (p.a_tma) tma_prefetch_desc(&tmapA);
         if (L::TMA_EPI) {
             tma_prefetch_desc(&tmapY);
-            if (p.res) tma_prefetch_desc(&tmapR);
+            if (p.res || p.nkb1) tma_prefetch_desc(&tmapR);
         }
     }
     if (warp == 5) {
@@ -621,6 +623,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                 map.coords(lt, m0, n0);
                 // im2col mode: input position of each half's first output pixel for tap (0, 0)
                 int iw[2] = {0, 0}, ih[2] = {0, 0}, in[2] = {0, 0}, tap_w = 0, tap_h = 0, slab = 0;
+                if (p.nkb1 && p.a2_mode == 2)
+                    for (int h = 0; h < halves; h++) {   // where the second operand is sampled for each half's first pixel
+                        const int m = m0 + h * BM;
+                        in[h] = m / p.oHW;
+                        const int rem = m - in[h] * p.oHW;
+                        const int oh = rem / p.oW;
+                        ih[h] = oh * p.a2_d;
+                        iw[h] = (rem - oh * p.oW) * p.a2_d;
+                    }
                 if (p.a_tma == 2)
                     for (int h = 0; h < halves; h++) {
                         const int m = m0 + h * BM;
@@ -653,7 +664,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                         continue;
                     }
                     mbar_arrive_expect_tx(bar, (uint32_t)(B_STAGE_BYTES + (p.a_tma ? a_stage_bytes : 0)));
-                    if (p.a_tma == 1) {
+                    if (p.a_tma == 1 && p.nkb1 && kb >= p.nkb1) {
+                        for (int h = 0; h < halves; h++) {
+                            const uint32_t dst = smem_u32(sA + s * a_stage_bytes + h * A_STAGE_BYTES);
+                            if (p.a2_mode == 1) tma_load_2d(dst, &tmapR, bar, (kb - p.nkb1) * BKE, m0 + h * BM);
+                            else tma_load_im2col_4d(dst, &tmapR, bar, (kb - p.nkb1) * BKE, iw[h], ih[h], in[h], 0, 0);
+                        }
+                    } else if (p.a_tma == 1) {
                         for (int h = 0; h < halves; h++)
                             tma_load_2d(smem_u32(sA + s * a_stage_bytes + h * A_STAGE_BYTES), &tmapA, bar, kb * BKE, m0 + h * BM);
                     } else if (p.a_tma == 2) {
@@ -1517,7 +1534,31 @@ extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, t
         const int c8 = (d->Cout + 7) & ~7;
         maps.y = matrix_tmap(y, p.P, c8, d->out_ld, d->dtype, 64);
         if (d->res) maps.r = matrix_tmap(d->res, p.P, c8, d->res_ld, d->dtype, 64);
+        if (d->x2) {
+            // second activation operand: its descriptor travels in the residual's slot (there is no residual then)
+            const int cin2 = d->Cin - d->cin1;
+            if (d->res || p.a_tma != 1 || d->in_row_pitch || d->cin1 <= 0 || d->cin1 % 64 || cin2 <= 0 || cin2 % 64 || d->x2_d < 1 ||
+                d->x2_d > 8 || d->Cin_pad != d->Cin || (d->x2_H - 1) / d->x2_d + 1 != d->oH || (d->x2_W - 1) / d->x2_d + 1 != d->oW)
+                return THB_ERR_UNSUPPORTED;
+            p.nkb1 = d->cin1 / 64;
+            p.a2_d = d->x2_d;
+            maps.a = matrix_tmap(x, p.P, d->cin1, d->in_ld, d->dtype, 64);
+            if (d->x2_d == 1) {
+                p.a2_mode = 1;
+                maps.r = matrix_tmap(d->x2, p.P, cin2, d->x2_ld, d->dtype, 64);
+            } else {
+                thb_conv_desc d2;
+                memset(&d2, 0, sizeof(d2));
+                d2.dtype = d->dtype;
+                d2.N = d->N; d2.H = d->x2_H; d2.W = d->x2_W; d2.Cin = d2.Cin_pad = cin2; d2.in_ld = d->x2_ld;
+                d2.kH = d2.kW = 1; d2.dH = d2.dW = d->x2_d; d2.oH = d->oH; d2.oW = d->oW;
+                p.a2_mode = 2;
+                maps.r = activation_tmap(&d2, d->x2, 2);
+            }
+            if (!maps.a || !maps.r) return thb_note_launch(cudaErrorUnknown, "conv_tc: second operand tensor map");
+        }
     }
+    if (d->x2 && !p.nkb1) return THB_ERR_UNSUPPORTED;  // (narrow tiles and uint8 have no second operand)
     cudaStream_t st = (cudaStream_t)s;
     switch (d->dtype) {
     case THB_F16: return dispatch_bn<0>(d->BN, maps, p, st);

@@ -47,6 +47,7 @@ class ConvDesc(C.Structure):
         ("Cin_pad", C.c_int), ("Ktot_pad", C.c_int), ("Cout_pad", C.c_int), ("BN", C.c_int),
         ("status", C.c_void_p),
         ("in_row_pitch", C.c_int), ("in_pad_left", C.c_int),
+        ("x2", C.c_void_p), ("x2_ld", C.c_int), ("x2_H", C.c_int), ("x2_W", C.c_int), ("x2_d", C.c_int), ("cin1", C.c_int),
     ]
 
 
