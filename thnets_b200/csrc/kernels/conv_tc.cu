@@ -1172,14 +1172,15 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
     if (L::TMA_EPI) {
         if (!tm.y || (p.res && !tm.r)) return thb_note_launch(cudaErrorUnknown, "conv_tc: output tensor map");
         // Shared memory is split between pipeline stages and the epilogue's 16 KB tiles (groups x tiles per group); which
-        // split wins was measured per layer shape.  A reduction of one or two K blocks lives off its epilogue: three
-        // groups (warps 0-3 join when they have nothing to gather) of two tiles, or, when a residual is read, two groups
-        // of three tiles, whose deeper ring keeps residual loads and stores in flight.  Up to eight K blocks: two groups of
-        // two tiles.  Longer reductions live off loads in flight: one tile per group, the rest in stages.
+        // split wins was measured per layer shape.  A single K block with 128 output channels per tile lives off its
+        // epilogue: three groups (warps 0-3 join when they have nothing to gather) of two tiles.  One or two K blocks with
+        // a residual, and a single K block on 64-channel tiles: two groups of three tiles, whose deeper ring keeps
+        // residual loads and stores in flight.  Up to eight K blocks: two groups of two tiles.  Longer reductions live
+        // off loads in flight: one tile per group, the rest in stages.
         const bool short_k = p.nkb <= 2;
-        p.epi_groups = p.a_tma && BN < 256 && short_k && !p.res ? 3 : 2;
+        p.epi_groups = p.a_tma && BN >= 128 && BN < 256 && p.nkb == 1 && !p.res ? 3 : 2;
         if (const char *e = getenv("THB200_EPI_GROUPS")) p.epi_groups = atoi(e) == 3 && p.a_tma && BN < 256 ? 3 : 2;
-        p.epi_bufs = p.epi_groups == 3 ? 2 : (short_k && p.res && BN < 256) ? 3 : p.nkb <= 8 ? 2 : 1;
+        p.epi_bufs = p.epi_groups == 3 ? 2 : ((short_k && p.res) || p.nkb == 1) && BN < 256 ? 3 : p.nkb <= 8 ? 2 : 1;
         if (const char *e = getenv("THB200_EPI_BUFS")) p.epi_bufs = atoi(e) < 1 ? 1 : atoi(e) > 3 ? 3 : atoi(e);
         const size_t stage_bytes = L::STAGE_BYTES + (p.pair ? A_STAGE_BYTES : 0);
         const int min_stages = p.pair ? 2 : STAGES;
