@@ -299,6 +299,41 @@ def test_conv_u8_bit_exact(lib, G, oracle, case, relu):
     assert np.array_equal(got, ref), ("requantised outputs differ", int(np.abs(got.astype(int) - ref.astype(int)).max()))
 
 
+@pytest.mark.parametrize("case", [(2, 64, 12, 12, 72, 1, 1, 0), (3, 128, 9, 11, 64, 3, 1, 1), (2, 64, 15, 15, 40, 3, 2, 1)])
+@pytest.mark.parametrize("coefs", [(1.0, -1.0), (1.0, 1.0)])
+def test_conv_u8_fused_residual(lib, G, oracle, case, coefs):
+    """uint8 convolution with the residual add fused into its epilogue (an extension, see thb_u8_combine): the bytes equal
+    those of the plain convolution followed by sat(floor(ca*q + cb*r - (ca+cb-1)*127.5)) and the Threshold."""
+    n, cin, h, w, cout, k, s, p = case
+    (xq, xs, xm), (wq, ws, wm), (bq, bs, bm), (osub, omult) = _lowp_case(oracle, G, case, 13)
+    conv_ref = oracle.lowp_conv(xq, xs, xm, wq, ws, wm, bq, bs, bm, (s, s), (p, p), osub, omult)
+    rng = np.random.default_rng(14)
+    res = rng.integers(0, 256, conv_ref.shape).astype(np.uint8)
+    ca, cb = coefs
+    ref = np.clip(np.floor(ca * conv_ref.astype(np.float64) + cb * res.astype(np.float64) - (ca + cb - 1) * 127.5), 0, 255)
+    thr = oracle.lib.orc_lowp_scale_float(osub, omult, 0.0)
+    ref = np.where(ref > thr, ref, thr).astype(np.uint8)
+    a_off, b_off, c_off, c_mult, c_shift = oracle.lowp_gemm_params(ws, wm, xs, xm, osub, omult)
+    conv = G.Conv(lib, K.THB_U8, xq.shape, None, (s, s), (p, p), wq=wq)
+    d = conv.d
+    d.a_offset, d.b_offset, d.c_offset, d.c_mult, d.c_shift = a_off, b_off, c_off, c_mult, c_shift
+    add = int(np.round(np.float32(bs) * np.float32(omult)))
+    mul = np.float32(omult) / np.float32(bm)
+    badd = np.array([int(np.round(np.float32(q) * mul)) + add for q in bq], np.int32)
+    ohw = d.oH * d.oW
+    d.tail_start = ohw - ohw % 8
+    d.relu_thr, d.relu_val = thr, thr
+    xt, _ = G.to_nhwc(xq, K.THB_U8)
+    rt, rld = G.to_nhwc(res, K.THB_U8)
+    csum = G.dzeros(n * h * w, torch.int32)
+    tb = G.dev(badd)
+    d.bias_add, d.csum = tb.data_ptr(), csum.data_ptr()
+    conv.set_residual(rt, rld, ca, cb)
+    assert lib.thb_u8_channel_sum(G.ptr(xt), n * h * w, cin, d.in_ld, G.ptr(csum), None) == 0
+    y = conv.run(xt)
+    assert np.array_equal(G.from_nhwc(y, cout), ref)
+
+
 # ---------------------------------------------------------------------------------------- other kernels
 @pytest.mark.parametrize("dtype", [K.THB_F32, K.THB_F16])
 @pytest.mark.parametrize("n", [1, 3, 8])
