@@ -1149,7 +1149,7 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
         // a fused residual exists on the table-driven path only, and that path needs windows clipped on one side at most
         if (p.res && (!p.u8_classes || p.H < p.kH || p.W < p.kW)) return thb_note_launch(cudaErrorInvalidValue, "conv_tc: uint8 residual");
     }
-    p.pair = L::TMA_EPI && p.a_tma && BN <= 128 && p.nkb >= pair_min_kb && (long)(p.m_tiles / 2) * p.n_tiles >= pair_min_units;
+    p.pair = L::TMA_EPI && p.a_tma && !p.half && BN <= 128 && p.nkb >= pair_min_kb && (long)(p.m_tiles / 2) * p.n_tiles >= pair_min_units;
     {
         // Every second convolution launch of a host thread walks its pixel tiles backwards: consecutive layers then
         // start on the end of the tensor the layer before has just written, which the L2 still holds (1.3 % of a
@@ -1487,9 +1487,10 @@ extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, t
                            box_corner_ok((d->oH - 1) * d->dH + 1 - d->H - d->padH, d->H + d->padH) &&
                            box_corner_ok((d->oW - 1) * d->dW + 1 - d->W - d->padW, d->W + d->padW);
     if (!p.a_tma && im2col_ok && d->Cin_pad % bke == 0 && d->Ktot_pad == d->kH * d->kW * d->Cin_pad) p.a_tma = 2;
-    // uint8 with 64 channels: a tap is half a K block; two taps per block, each as its own 64-byte-wide copy
+    // taps of 64 bytes (uint8 with 64 channels, 16-bit types with 32): half a K block; two taps per block, each as its own
+    // 64-byte-wide copy
     p.ntaps = d->kH * d->kW;
-    const bool half_ok = d->dtype == THB_U8 && !p.a_tma && im2col_ok && d->Cin_pad * 2 == bke && !d->in_row_pitch &&
+    const bool half_ok = !p.a_tma && im2col_ok && d->Cin_pad * 2 == bke && !d->in_row_pitch &&
                          d->Ktot_pad == (p.ntaps * d->Cin_pad + bke - 1) / bke * bke;
     if (half_ok) p.a_tma = 2, p.half = 1;
     p.slabs = d->Cin_pad / bke;
