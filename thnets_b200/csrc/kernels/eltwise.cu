@@ -312,6 +312,43 @@ __global__ void pool_kernel(const T *x, int N, int H, int W, int C, int x_ld, in
     Vec<T>::store(y + (size_t)opix * y_ld + cv * VN, acc);
 }
 
+// Global average pooling (the window is the whole map): the generic kernel would walk the map's pixels one after the
+// other in each thread, a chain of dependent load latencies.  Here a block owns one image and 32 channel vectors; its
+// eight warps take every eighth pixel (independent loads in flight) and their partial sums meet in shared memory.
+template <typename T>
+__global__ void __launch_bounds__(256) global_avgpool_kernel(const T *x, int HW, int C, int x_ld, T *y, int y_ld)
+{
+    constexpr int VN = Vec<T>::N;
+    __shared__ float part[8][32][VN + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int cvecs = (C + VN - 1) / VN, cv = blockIdx.y * 32 + lane;
+    const long n = blockIdx.x;
+    float acc[VN];
+#pragma unroll
+    for (int i = 0; i < VN; i++) acc[i] = 0.f;
+    if (cv < cvecs)
+        for (int p = warp; p < HW; p += 8) {
+            float v[VN];
+            Vec<T>::load(x + ((size_t)n * HW + p) * x_ld + cv * VN, v);
+#pragma unroll
+            for (int i = 0; i < VN; i++) acc[i] += v[i];
+        }
+#pragma unroll
+    for (int i = 0; i < VN; i++) part[warp][lane][i] = acc[i];
+    __syncthreads();
+    if (warp == 0 && cv < cvecs) {
+        float out[VN];
+#pragma unroll
+        for (int i = 0; i < VN; i++) {
+            float s = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; w++) s += part[w][lane][i];
+            out[i] = s / (float)HW;
+        }
+        Vec<T>::store(y + (size_t)n * y_ld + cv * VN, out);
+    }
+}
+
 // 3x3 stride-2 max pooling of a 16-bit type, without a conversion and with each input row reduced once: a thread owns one
 // output column of one 8-channel group and walks down a strip of output rows; of the three input rows of a window the
 // first is the last one of the window above, so every step reads two new rows of three pixels, takes their
@@ -772,6 +809,11 @@ int thb_avgpool(int dtype, const void *x, int N, int H, int W, int C, int x_ld, 
     const int al = thb_channel_align(dtype);
     const long total = (long)N * oH * oW * ((C + al - 1) / al);
     if (total == 0) return THB_OK;
+    if (kH == H && kW == W && padH == 0 && padW == 0 && oH == 1 && oW == 1 && x_ld % al == 0 && y_ld % al == 0) {
+        const dim3 grid((unsigned)N, (unsigned)(((C + al - 1) / al + 31) / 32));
+        DISPATCH_ANY_DTYPE(dtype, (global_avgpool_kernel<T><<<grid, 256, 0, (cudaStream_t)s>>>((const T *)x, H * W, C, x_ld, (T *)y, y_ld)));
+        return THB_LAUNCH_CHECK("global_avgpool_kernel");
+    }
     DISPATCH_ANY_DTYPE(dtype, (pool_kernel<T, false><<<nblocks(total), 256, 0, (cudaStream_t)s>>>(
                                     (const T *)x, N, H, W, C, x_ld, kH, kW, dH, dW, padH, padW, oH, oW,
                                     count_include_pad, (T *)y, y_ld)));
