@@ -1312,6 +1312,13 @@ static int pipe_build(thb_engine *E, int S)
         for (int c = 0; c < S; c++) {
             int off, n;
             thb_slice_batch(E->inst[g].slice_n, S, c, &off, &n);
+            if (S == 2 && E->inst[g].slice_n >= 8) {
+                /* two sub-batches: a smaller first one (3/8) starts the kernels sooner, and the copy of the larger second
+                 * one still ends before they do (ResNet-50 batch 256: 96 + 160 images) */
+                const int first = (E->inst[g].slice_n * 3 + 4) / 8;
+                off = c ? first : 0;
+                n = c ? E->inst[g].slice_n - first : first;
+            }
             if (instance_build(E, &E->pipe[g * S + c], E->inst[g].device, E->inst[g].slice_off + off, n)) return -1;
         }
     E->pipe_built = G * S;
