@@ -105,6 +105,9 @@ typedef struct thb_conv_desc {
      * No counterpart in the reference, which runs the two convolutions and a CAddTable. */
     const void *x2;
     int x2_ld, x2_H, x2_W, x2_d, cin1;
+    /* uint8, optional, only when one tile covers all output channels (Cout_pad == BN): the convolution also stores, per
+     * output pixel, the sum of its Cout output bytes -- what thb_u8_channel_sum would compute for the next convolution */
+    int *csum_out;
 } thb_conv_desc;
 
 int thb_channel_align(int dtype);               /* 4 (F32), 8 (F16/BF16), 16 (U8) */

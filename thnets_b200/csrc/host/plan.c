@@ -82,6 +82,7 @@ typedef struct {
     int nin, in_buf[8], in_ld[8], in_coff[8];
     int out_buf, out_ld, out_coff;
     int aux_buf; /* csum scratch (conv u8) */
+    int aux2_buf; /* conv u8: channel sums of its OUTPUT, written by the convolution itself for the next one (-1: none) */
     float coef[8];
     int N, H, W, C, oH, oW, kH, kW, dH, dW, padH, padW, flag;
     long pixels;
@@ -223,7 +224,7 @@ static step *new_step(planner *P, int kind)
     memset(s, 0, sizeof(*s));
     s->kind = kind;
     s->dtype = P->E->dtype;
-    s->out_buf = s->aux_buf = -1;
+    s->out_buf = s->aux_buf = s->aux2_buf = -1;
     for (int i = 0; i < 8; i++) s->in_buf[i] = -1;
     s->flops_node = -1;
     return s;
@@ -626,6 +627,12 @@ static int plan_gemm_group(planner *P, int i)
             d->relu_val = thb_lowp_scale_float(out_sub, out_mult, M->nodes[act].act_value);
         }
         out->q_sub = out_sub; out->q_mult = out_mult;
+        /* one column tile: the epilogue sees every output byte of a pixel and leaves their sum for the next convolution */
+        const char *nocs = getenv("THB200_U8_NO_CSUM_OUT");
+        if (!is_linear && d->Cout_pad == d->BN && !(nocs && atoi(nocs))) {
+            s->aux2_buf = new_buf(P, sizeof(int) * (size_t)is.N * os.H * os.W);
+            out->csum_buf = s->aux2_buf + 1;
+        }
         if (res_node >= 0) {
             const value *rv = &P->val[res_node];
             step_in(s, rv);
@@ -895,10 +902,11 @@ static size_t pack_arena(instance *I)
 {
     for (int t = 0; t < I->nsteps; t++) {
         step *s = &I->steps[t];
-        int ids[10], n = 0;
+        int ids[12], n = 0;
         for (int k = 0; k < s->nin; k++) ids[n++] = s->in_buf[k];
         ids[n++] = s->out_buf;
         ids[n++] = s->aux_buf;
+        ids[n++] = s->aux2_buf;
         for (int k = 0; k < n; k++)
             if (ids[k] >= 0) {
                 abuf *b = &I->bufs[ids[k]];
@@ -1056,6 +1064,7 @@ static int run_steps_ev(thb_engine *E, instance *I, cudaEvent_t *evs)
             if (s->dual) d->x2 = bufptr(I, s->in_buf[1], s->in_coff[1], dt);
             else if (s->nin > 1) d->res = bufptr(I, s->in_buf[1], s->in_coff[1], dt);
             if (s->aux_buf >= 0) d->csum = (const int *)bufptr(I, s->aux_buf, 0, THB_U8);
+            if (s->aux2_buf >= 0) d->csum_out = (int *)bufptr(I, s->aux2_buf, 0, THB_U8);
             rc = thb_conv_fwd(d, x0, y, st);
             break;
         }

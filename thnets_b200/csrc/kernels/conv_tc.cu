@@ -59,6 +59,7 @@ struct ConvTcParams {
                                // pipeline stage carries both activation tiles and ONE weight tile, and the MMA thread feeds two
                                // accumulators per barrier round: that round costs the thread ~250 cycles whatever it carries,
                                // which a single narrow tile (192-256 tensor cycles per K block) cannot hide.
+    int *csum_out;             // uint8, one column tile: per output pixel the sum of its output bytes (the next layer's channel sums)
     int res_addend;            // uint8 fused residual: the constant of ca*q + cb*r + addend (see thb_u8_combine)
     int u8_classes;            // uint8: > 0 when the border classes of the kernel window ((1 + 2 padH) x (1 + 2 padW) of them)
                                // fit the epilogue's shared-memory table; 0: every row looks its window up in global memory
@@ -856,6 +857,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                 }
             }
             bool have_acc = false;
+            uint32_t rowsum = 0;  // uint8: sum of this row's output bytes over the tile's columns
 #pragma unroll 1
             for (int sb = 0; sb < BN / SUBN; sb++, sub_it++) {
                 const int nsub0 = n0 + sb * SUBN;
@@ -949,6 +951,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                                 words[g4] &= nreal >= 4 ? 0xffffffffu : nreal <= 0 ? 0u : (1u << (8 * nreal)) - 1u;
                             }
                         }
+#pragma unroll
+                        for (int g4 = 0; g4 < 8; g4++) rowsum = __dp4a(words[g4], 0x01010101u, rowsum);
                         uint4 *dst = reinterpret_cast<uint4 *>(stg + row * (SUBN + 16) + cc * 32);
                         dst[0] = make_uint4(words[0], words[1], words[2], words[3]);
                         dst[1] = make_uint4(words[4], words[5], words[6], words[7]);
@@ -1007,6 +1011,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                                 else hi |= (uint32_t)q << (8 * (i - 4));
                             }
                         }
+                        rowsum = __dp4a(hi, 0x01010101u, __dp4a(lo, 0x01010101u, rowsum));
                         *reinterpret_cast<uint2 *>(stg + row * (SUBN + 16) + c8 * 8) = make_uint2(lo, hi);
                     }
                 } else {
@@ -1089,6 +1094,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                 }
                 if (KIND != 2) mbar_arrive(bar_free);
             }
+            if (KIND == 2 && alive && p.csum_out && valid) p.csum_out[pm] = (int)rowsum;
         }
     }
 
@@ -1458,6 +1464,10 @@ extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, t
     p.act_kind = d->act.kind; p.act_th = d->act.threshold; p.act_val = d->act.value; p.act_alpha = d->act.alpha;
     p.a_off = d->a_offset; p.b_off = d->b_offset; p.c_off = d->c_offset; p.c_mult = d->c_mult; p.c_shift = d->c_shift;
     p.wsat = d->wsat; p.bias_add = d->bias_add; p.csum = d->csum;
+    if (d->csum_out) {
+        if (d->dtype != THB_U8 || d->Cout_pad != d->BN) return THB_ERR_UNSUPPORTED;
+        p.csum_out = d->csum_out;
+    }
     if (d->dtype == THB_U8 && d->res) {
         const int ca = (int)d->self_coef, cb = (int)d->res_coef;
         if ((ca != 1 && ca != -1) || (cb != 1 && cb != -1) || (float)ca != d->self_coef || (float)cb != d->res_coef) return THB_ERR_UNSUPPORTED;
