@@ -105,8 +105,10 @@ typedef struct thb_conv_desc {
      * No counterpart in the reference, which runs the two convolutions and a CAddTable. */
     const void *x2;
     int x2_ld, x2_H, x2_W, x2_d, cin1;
-    /* uint8, optional, only when one tile covers all output channels (Cout_pad == BN): the convolution also stores, per
-     * output pixel, the sum of its Cout output bytes -- what thb_u8_channel_sum would compute for the next convolution */
+    /* uint8, optional: the convolution also leaves, per output pixel, the sum of its Cout output bytes -- what
+     * thb_u8_channel_sum would compute for the next convolution.  When one tile covers all output channels
+     * (Cout_pad == BN) the sums are stored; otherwise each column tile ADDS its part, and the caller clears the buffer
+     * before the launch. */
     int *csum_out;
 } thb_conv_desc;
 

@@ -74,7 +74,7 @@ typedef struct {
 
 enum step_kind {
     ST_CONV, ST_GEMV, ST_MAXPOOL, ST_AVGPOOL, ST_AFFINE, ST_U8THR, ST_U8COMBINE, ST_COMBINE, ST_COPY, ST_SOFTMAX, ST_COL2IM,
-    ST_CSUM, ST_TO_NCHW
+    ST_CSUM, ST_TO_NCHW, ST_ZERO
 };
 
 typedef struct {
@@ -481,6 +481,13 @@ static int plan_gemm_group(planner *P, int i)
             if (!is_linear) inw->csum_buf = csum_buf + 1;
         }
     }
+    /* uint8: a place-holder launch in front of the convolution; it becomes the clearing of the output's channel-sum
+     * buffer when the convolution has several column tiles, which then add their partial sums into it */
+    int zero_step = -1;
+    if (dtype == THB_U8 && !is_linear) {
+        new_step(P, ST_ZERO)->pixels = 0;
+        zero_step = P->I->nsteps - 1;
+    }
     step *s = new_step(P, ST_CONV);
     thb_conv_desc *d = &s->conv;
     s->aux_buf = csum_buf;
@@ -629,9 +636,14 @@ static int plan_gemm_group(planner *P, int i)
         out->q_sub = out_sub; out->q_mult = out_mult;
         /* one column tile: the epilogue sees every output byte of a pixel and leaves their sum for the next convolution */
         const char *nocs = getenv("THB200_U8_NO_CSUM_OUT");
-        if (!is_linear && d->Cout_pad == d->BN && !(nocs && atoi(nocs))) {
+        if (!is_linear && zero_step >= 0 && !(nocs && atoi(nocs) == 1) && (d->Cout_pad == d->BN || !(nocs && atoi(nocs) == 2))) {
             s->aux2_buf = new_buf(P, sizeof(int) * (size_t)is.N * os.H * os.W);
             out->csum_buf = s->aux2_buf + 1;
+            if (d->Cout_pad != d->BN) {
+                step *z = &P->I->steps[zero_step];
+                z->out_buf = s->aux2_buf;
+                z->pixels = (long)is.N * os.H * os.W;
+            }
         }
         if (res_node >= 0) {
             const value *rv = &P->val[res_node];
@@ -1104,6 +1116,9 @@ static int run_steps_ev(thb_engine *E, instance *I, cudaEvent_t *evs)
         case ST_COL2IM:
             rc = thb_col2im(dt, x0, s->N, s->H, s->W, s->C, s->kH, s->kW, s->dH, s->dW, s->padH, s->padW, s->oH, s->oW,
                             s->in_ld[0], s->beta, s->bias, &s->act, y, s->out_ld, st);
+            break;
+        case ST_ZERO:
+            if (s->pixels > 0 && cudaMemsetAsync(bufptr(I, s->out_buf, 0, THB_U8), 0, sizeof(int) * (size_t)s->pixels, (cudaStream_t)st) != cudaSuccess) rc = -1;
             break;
         case ST_CSUM:
             rc = thb_u8_channel_sum(x0, s->pixels, s->C, s->in_ld[0], (int *)bufptr(I, s->out_buf, 0, THB_U8), st);

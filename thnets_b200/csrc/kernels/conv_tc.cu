@@ -1094,7 +1094,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                 }
                 if (KIND != 2) mbar_arrive(bar_free);
             }
-            if (KIND == 2 && alive && p.csum_out && valid) p.csum_out[pm] = (int)rowsum;
+            if (KIND == 2 && alive && p.csum_out && valid) {
+                if (p.n_tiles == 1) p.csum_out[pm] = (int)rowsum;
+                else atomicAdd(p.csum_out + pm, (int)rowsum);  // several column tiles: the buffer was cleared before the launch
+            }
         }
     }
 
@@ -1465,7 +1468,7 @@ extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, t
     p.a_off = d->a_offset; p.b_off = d->b_offset; p.c_off = d->c_offset; p.c_mult = d->c_mult; p.c_shift = d->c_shift;
     p.wsat = d->wsat; p.bias_add = d->bias_add; p.csum = d->csum;
     if (d->csum_out) {
-        if (d->dtype != THB_U8 || d->Cout_pad != d->BN) return THB_ERR_UNSUPPORTED;
+        if (d->dtype != THB_U8) return THB_ERR_UNSUPPORTED;
         p.csum_out = d->csum_out;
     }
     if (d->dtype == THB_U8 && d->res) {
