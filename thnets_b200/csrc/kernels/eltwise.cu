@@ -218,23 +218,41 @@ __global__ void preprocess_images_u8_kernel(const uint8_t *img, int N, int H, in
     *reinterpret_cast<uint4 *>(y + pix * y_ld) = make_uint4(word, 0, 0, 0);
 }
 
-__global__ void minmax_kernel(const float *x, int C, long HW, long total, float3 mean, float3 std_, float *minmax)
+// Range of the normalised input (lowp_basic.c:15-29 starts both ends at 0).  A block scans a piece of one (image, channel)
+// plane for its raw extremes with 16-byte loads and normalises only those two: subtraction and division by a positive
+// deviation are monotone, so the extremes of the normalised values are the normalised extremes, bit for bit.
+__global__ void __launch_bounds__(256) minmax_kernel(const float *x, int C, long HW, int pieces, float3 mean, float3 std_, float *minmax)
 {
-    const float m[3] = {mean.x, mean.y, mean.z}, sd[3] = {std_.x, std_.y, std_.z};
-    float mn = 0.f, mx = 0.f;
-    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
-        const int c = (int)((i / HW) % C);
-        float v = x[i];
-        if (c < 3) v = __fdiv_rn(__fsub_rn(v, m[c]), sd[c]);
-        mn = fminf(mn, v);
-        mx = fmaxf(mx, v);
+    const long plane = blockIdx.x / pieces;
+    const int piece = blockIdx.x % pieces, c = (int)(plane % C);
+    const long per = (HW + pieces - 1) / pieces, i0 = piece * per, i1 = min(HW, i0 + per);
+    const float *p = x + plane * HW;
+    float mn = INFINITY, mx = -INFINITY;
+    if (((HW | per) & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        for (long i = i0 + threadIdx.x * 4; i < i1; i += 1024) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(p + i));
+            mn = fminf(fminf(mn, fminf(v.x, v.y)), fminf(v.z, v.w));
+            mx = fmaxf(fmaxf(mx, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+        }
+    } else {
+        for (long i = i0 + threadIdx.x; i < i1; i += 256) {
+            const float v = p[i];
+            mn = fminf(mn, v);
+            mx = fmaxf(mx, v);
+        }
     }
     for (int o = 16; o > 0; o >>= 1) {
         mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     }
-    if ((threadIdx.x & 31) == 0) {
-        // mn <= 0 <= mx: negative floats order like their unsigned bit patterns, non-negative like signed ints
+    if ((threadIdx.x & 31) == 0 && mn <= mx) {
+        if (c < 3) {
+            const float m = c == 0 ? mean.x : c == 1 ? mean.y : mean.z, sd = c == 0 ? std_.x : c == 1 ? std_.y : std_.z;
+            const float a = __fdiv_rn(__fsub_rn(mn, m), sd), b = __fdiv_rn(__fsub_rn(mx, m), sd);
+            mn = fminf(a, b);
+            mx = fmaxf(a, b);
+        }
+        // mn <= 0 <= mx is all that matters: negative floats order like their unsigned bit patterns, non-negative like signed ints
         if (mn < 0.f) atomicMax(reinterpret_cast<unsigned int *>(minmax), __float_as_uint(mn));
         if (mx > 0.f) atomicMax(reinterpret_cast<int *>(minmax + 1), __float_as_int(mx));
     }
@@ -738,9 +756,13 @@ int thb_minmax_normalized(const float *x, int N, int C, int H, int W, const floa
     if (e != cudaSuccess) return thb_note_launch(e, "minmax memset");
     if (total == 0) return THB_OK;
     float3 m = make_float3(mean3[0], mean3[1], mean3[2]), sd = make_float3(std3[0], std3[1], std3[2]);
-    int blocks = nblocks(total);
-    if (blocks > 148 * 8) blocks = 148 * 8;
-    minmax_kernel<<<blocks, 256, 0, (cudaStream_t)s>>>(x, C, HW, total, m, sd, minmax2);
+    // pieces of a plane per block: enough blocks for a few waves, pieces a multiple of four elements long where possible
+    const long planes = (long)N * C;
+    int pieces = (int)((148L * 16 + planes - 1) / planes);
+    if (pieces < 1) pieces = 1;
+    while (pieces > 1 && ((HW + pieces - 1) / pieces < 4096 || (HW % (4L * pieces)))) pieces--;
+    if (planes * pieces > 0x7fffffffL) return THB_ERR_UNSUPPORTED;
+    minmax_kernel<<<(unsigned)(planes * pieces), 256, 0, (cudaStream_t)s>>>(x, C, HW, pieces, m, sd, minmax2);
     return THB_LAUNCH_CHECK("minmax_kernel");
 }
 
