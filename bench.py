@@ -60,8 +60,9 @@ def read_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         d = json.load(open(p))
-        return {"tflops": d.get("bf16_tflops_sustained", d.get("bf16_tflops")), "hbm": d.get("hbm_gbs"), "src": "measured"}
-    return {"tflops": 1590.0, "hbm": 6650.0, "src": "fallback"}
+        return {"tflops": d.get("bf16_tflops_sustained", d.get("bf16_tflops")), "tflops_burst": d.get("bf16_tflops"),
+                "hbm": d.get("hbm_gbs"), "src": "measured"}
+    return {"tflops": 1400.0, "tflops_burst": 1590.0, "hbm": 6650.0, "src": "fallback"}
 
 
 class ClockSampler:
@@ -127,21 +128,64 @@ def build_fixture(workload, tmpdir, dtype=None):
     return g, path
 
 
+def usable_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except (AttributeError, OSError):
+        return os.cpu_count() or 1
+
+
 def omp_threads_for(batch):
     """The reference's batch-parallel GEMM deadlocks unless the OpenMP team divides the batch, and its scratch
     tables hold 32 threads (OpenBLAS-stripped/sgemm.c:967-980, blas.h:1)."""
-    cores = min(os.cpu_count() or 1, 32)
+    cores = min(usable_cores(), 32)
     if batch < 4:
         return cores
     return max(d for d in range(1, cores + 1) if batch % d == 0)
 
 
+def available_host_gb():
+    """Memory this process may still take: the smaller of what the machine reports free and the cgroup's limit."""
+    avail = None
+    try:
+        for line in open("/proc/meminfo"):
+            if line.startswith("MemAvailable:"):
+                avail = int(line.split()[1]) / 1e6
+    except OSError:
+        pass
+    try:
+        lim = open("/sys/fs/cgroup/memory.max").read().strip()
+        cur = int(open("/sys/fs/cgroup/memory.current").read().strip())
+        if lim != "max":
+            room = (int(lim) - cur) / 1e9
+            avail = room if avail is None else min(avail, room)
+    except (OSError, ValueError):
+        pass
+    return avail if avail is not None else 16.0
+
+
+# host memory the reference takes per image of a forward (it keeps every module's output and an im2col buffer per
+# thread): measured on ResNet-50, 0.16 GB; the other networks' figures are scaled by their activation sizes
+REF_GB_PER_IMAGE = {"resnet50": 0.16, "resnet18": 0.05, "vgg16": 0.25, "alexnet_owt": 0.02, "segnet": 0.5}
+
+
+def reference_batch(workload, full_batch):
+    """The configuration's own batch when the host has room for it (with a margin of two), else the largest
+    halving of it that fits."""
+    room = available_host_gb() / 2
+    b = full_batch
+    while b > 1 and b * REF_GB_PER_IMAGE[workload] + 1.0 > room:
+        b //= 2
+    return max(b, 1)
+
+
 def reference_child(args):
-    """Runs in a fresh process (OMP_NUM_THREADS must be set before the reference library loads)."""
+    """Runs in a fresh process (OMP_NUM_THREADS must be set before the reference library loads): the unmodified reference
+    through its own THLoadNetwork / THProcessFloat on the first `ref_batch` images of the benchmark batch.  Saves the
+    first forward's output for the parity record of the GPU arm."""
     from oracle.oracle import ref_lib
     from thnets_b200.capi import THNets
     lib = ref_lib()
-    kind = "reference"
     if lib is None:
         raise SystemExit("reference library not built (oracle/_ref)")
     with tempfile.TemporaryDirectory() as tmp:
@@ -149,32 +193,248 @@ def reference_child(args):
         th = THNets(lib)
         h = th.load_network(path)
         th.set_stats(h, g.mean, g.std)
-        x = g.make_input(args.ref_batch)
+        x = g.make_input(args.batch, seed=1234)[:args.ref_batch]
         times = []
         for i in range(args.warmup_ref + args.steps_ref):
             t0 = time.perf_counter()
-            th.process_float(h, x)
+            out, _, _ = th.process_float(h, x)
             times.append(time.perf_counter() - t0)
+            if i == 0 and args.ref_out:
+                np.save(args.ref_out, out.reshape(args.ref_batch, -1))
         t = sum(times[args.warmup_ref:]) / args.steps_ref
-    print(json.dumps({"images_per_s": args.ref_batch / t, "ms_per_step": t * 1e3, "kind": kind,
-                      "lib": os.path.basename(lib)}))
+    print(json.dumps({"images_per_s": args.ref_batch / t, "ms_per_step": t * 1e3, "kind": "reference",
+                      "lib": os.path.basename(lib), "first_forward_s": times[0]}))
 
 
-def run_reference(args, steps, warmup):
-    """The reference's own CPU implementation on this box's host cores, on a bounded sample of the workload."""
-    _, batch, dtype, _ = WORKLOADS[args.workload]
-    sample = {"resnet50": 16, "resnet18": 32, "vgg16": 4, "alexnet_owt": 1, "segnet": 2}[args.workload]
+def run_reference(args, steps, warmup, ref_out=None):
+    """The reference's own CPU implementation on this box's host cores: the workload's network in fp32 (the reference's
+    only CPU precision) at the configuration's batch when host memory allows, `warmup` + `steps` forwards."""
+    _, dbatch, _, _ = WORKLOADS[args.workload]
+    batch = args.batch or dbatch
+    sample = reference_batch(args.workload, batch)
     threads = omp_threads_for(sample)
     env = dict(os.environ, OMP_NUM_THREADS=str(threads))
-    cmd = [sys.executable, os.path.abspath(__file__), "--_ref_child", "--workload", args.workload, "--ref-batch", str(sample),
-           "--steps-ref", str(steps), "--warmup-ref", str(warmup)]
-    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    cmd = [sys.executable, os.path.abspath(__file__), "--_ref_child", "--workload", args.workload, "--batch", str(batch),
+           "--ref-batch", str(sample), "--steps-ref", str(steps), "--warmup-ref", str(warmup)]
+    if ref_out:
+        cmd += ["--ref-out", ref_out]
+    try:
+        out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=1500)
+    except subprocess.TimeoutExpired:
+        return None, "reference run exceeded 1500 s"
     if out.returncode != 0:
         return None, f"reference run failed: {out.stderr.strip()[-200:]}"
     r = json.loads(out.stdout.strip().splitlines()[-1])
-    return {"value": r["images_per_s"], "unit": "images/s", "cores": threads, "kind": r["kind"],
-            "sample": f"{args.workload} fp32, batch {sample}, THProcessFloat of {r['lib']}, {warmup} warm-up + {steps} timed forwards",
+    return {"value": r["images_per_s"], "unit": "images/s", "cores": threads, "kind": r["kind"], "batch": sample,
+            "steps": steps, "warmup": warmup,
+            "sample": f"{args.workload} fp32, batch {sample} of {batch}, THProcessFloat of {r['lib']}, {threads} OpenMP threads "
+                      f"on {usable_cores()} usable cores, {warmup} warm-up + {steps} timed forwards",
             "ms_per_step": r["ms_per_step"]}, None
+
+
+class Arm:
+    """One converted network on this rank's GPU and the host batch it is measured on."""
+
+    def __init__(self, th, workload, dtype, batch, rank, tmpdir):
+        self.th, self.lib = th, th.lib
+        self.workload, self.dtype, self.batch = workload, dtype, batch
+        lib = self.lib
+        self.g, path = build_fixture(workload, tmpdir, dtype)
+        h = th.load_network(path)
+        th.set_stats(h, self.g.mean, self.g.std)
+        if dtype == "int8":
+            if workload == "vgg16":
+                th.make_spatial(h, self.g.input_shape[1])
+            self.net = th.create_lowp_network(h, LOWP_RANGE)
+        else:
+            lib.THB200_SetPrecision({"fp32": 0, "fp16": 1, "bf16": 2}[dtype])
+            self.net = lib.THCreateCudaNetwork(h)
+            lib.THB200_SetPrecision(0)
+            if not self.net:
+                raise SystemExit("THCreateCudaNetwork failed: %s" % lib.THB200_LastErrorString())
+        th.free_network(h)
+        c, hh, ww = self.g.input_shape
+        self.shape = (batch, c, hh, ww)
+        self.nbytes = batch * c * hh * ww * 4
+        self.hptr = lib.THB200_HostAlloc(self.nbytes)          # pinned host batch
+        self.host = np.ctypeslib.as_array(C.cast(self.hptr, C.POINTER(C.c_float)), shape=self.shape)
+        self.host[...] = self.g.make_input(batch, seed=1234 + rank)
+        self.res = C.POINTER(C.c_float)()
+        self.ow, self.oh = C.c_int(), C.c_int()
+        self.out_count = 0
+
+    def forward(self, ptr=None):
+        """THProcessFloat on the host batch (H2D of the batch and D2H of the result inside the call)."""
+        b, c, hh, ww = self.shape
+        n = self.lib.THProcessFloat(self.net, ptr or self.hptr, b, ww, hh, c, C.byref(self.res), C.byref(self.ow), C.byref(self.oh))
+        if n <= 0:
+            raise SystemExit("THProcessFloat failed: %s" % self.lib.THB200_LastErrorString())
+        self.out_count = n
+        return n
+
+    def output(self):
+        return np.ctypeslib.as_array(self.res, shape=(self.out_count,)).reshape(self.batch, -1).copy()
+
+    def close(self):
+        self.lib.THB200_HostFree(self.hptr)
+        self.th.free_network(self.net)
+
+
+def time_loop(fn, steps, barrier, max_over_ranks):
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        fn()
+    dt = (time.perf_counter() - t0) / steps
+    barrier()
+    return max_over_ranks(dt)
+
+
+def measure(arm, steps, warmup, world, barrier, max_over_ranks, peaks):
+    """Device-resident value, end-to-end figures and the roofline of the convolution kernel for one converted network."""
+    lib, batch = arm.lib, arm.batch
+    # The device-resident loop runs the whole-batch plan, so stage the batch into it with the copy/compute pipelining of
+    # THProcessFloat switched off once; the end-to-end loops run with the library's default (pipelined sub-batches).
+    lib.THB200_SetPipelineChunks(1)
+    arm.forward()                      # plans the network, uploads the weights, stages the batch
+    first_out = arm.output()           # (later calls re-normalise the host batch in place when mean/std are not the identity)
+    lib.THB200_SetPipelineChunks(0)
+    for _ in range(warmup):
+        arm.forward()
+    if lib.THB200_TimeForward(arm.net, warmup) < 0:
+        raise SystemExit("THB200_TimeForward failed: %s" % lib.THB200_LastErrorString())
+    # --- device-resident: K forwards from the fp32 batch in HBM to the fp32 result in HBM, events on the launching stream
+    barrier()
+    l0 = lib.THB200_KernelLaunches()
+    ms_step = lib.THB200_TimeForward(arm.net, steps)
+    launches = lib.THB200_KernelLaunches() - l0
+    barrier()
+    if ms_step < 0:
+        raise SystemExit("THB200_TimeForward failed: %s" % lib.THB200_LastErrorString())
+    ms_step = max_over_ranks(ms_step)
+    # --- end to end through the public API: pinned host batch, then an ordinary pageable one
+    e2e_s = time_loop(arm.forward, steps, barrier, max_over_ranks)
+    pageable = np.array(arm.host, copy=True)
+    pp = pageable.ctypes.data_as(C.c_void_p)
+    arm.forward(pp)
+    e2e_pageable_s = time_loop(lambda: arm.forward(pp), max(2, steps // 4), barrier, max_over_ranks)
+    del pageable
+    out = {"value": world * batch / (ms_step * 1e-3), "ms_per_step": ms_step, "gpu_launches": launches,
+           "e2e": {"value": world * batch / e2e_s, "unit": "images/s", "h2d_bytes_per_step": arm.nbytes,
+                   "d2h_bytes_per_step": arm.out_count * 4, "ms_per_step": e2e_s * 1e3, "entry": "THProcessFloat",
+                   "host_buffer": "pinned (THB200_HostAlloc)", "h2d_gbs_per_gpu": arm.nbytes / e2e_s / 1e9,
+                   "pageable_host_buffer": {"value": world * batch / e2e_pageable_s, "ms_per_step": e2e_pageable_s * 1e3}}}
+    # --- per-launch profile -> roofline of the dominant kernel
+    maxs = 4096
+    kinds, ms, fl, by = (C.c_int * maxs)(), (C.c_float * maxs)(), (C.c_double * maxs)(), (C.c_double * maxs)()
+    nst = lib.THB200_ProfileForward(arm.net, 5, maxs, kinds, ms, fl)
+    if nst > 0:
+        u8 = arm.dtype == "int8"
+        conv_prof = sum(ms[i] for i in range(nst) if kinds[i] == 0)
+        conv_fl = sum(fl[i] for i in range(nst) if kinds[i] == 0)
+        tot_prof = sum(ms[i] for i in range(nst))
+        nconv = sum(1 for i in range(nst) if kinds[i] == 0)
+        # Events between launches switch off the overlap of one kernel's tail with the next one's set-up, so the
+        # per-launch times add up to more than a step.  The convolution kernel's time per step is its SHARE of the
+        # profile applied to the step as timed above: it cannot exceed the step.
+        share = conv_prof / tot_prof if tot_prof else 0.0
+        conv_ms = ms_step * share
+        # The timed region is far shorter than the seconds it takes a B200 to settle under its power cap: the burst
+        # GEMM peak is the denominator (the sustained figure is given beside it).
+        peak = peaks["tflops_burst"] * (2 if u8 else 1)
+        ach = conv_fl / (conv_ms * 1e-3) / 1e12 if conv_ms > 0 else 0.0
+        roof = {"bound": "tensor", "kernel": "conv_tc_kernel" if arm.dtype != "fp32" else "conv_simt_kernel",
+                "achieved": ach, "peak": peak, "unit": "TFLOP/s" if not u8 else "TOP/s", "frac": ach / peak,
+                "peak_source": "of " + peaks["src"] + (": bf16_tflops (burst)" if not u8 else ": 2 x bf16_tflops (burst)"),
+                "frac_of_sustained_peak": ach / (peaks["tflops"] * (2 if u8 else 1)),
+                "traffic": NCU_DRAM_BYTES_PER_STEP.get((arm.workload, arm.dtype, batch)),
+                "launches_per_step": nconv, "kernel_ms_per_step": conv_ms, "share_of_step": share,
+                "profile_ms": {"convolutions": conv_prof, "all_launches": tot_prof,
+                               "boundary_kernels": sum(ms[i] for i in range(nst) if kinds[i] == 3)},
+                "flops_per_step": conv_fl}
+        # the bound a forward of this network cannot beat when every launch ran at the slower of its two roofs
+        # (algorithmic FLOPs / measured tensor peak, algorithmic bytes / measured HBM copy bandwidth)
+        if lib.THB200_ProfileForwardBytes(arm.net, maxs, by) == nst and peaks["hbm"]:
+            tpk = peak * 1e12
+            bound_ms = sum(max(fl[i] / tpk, by[i] / (peaks["hbm"] * 1e9)) for i in range(nst) if kinds[i] == 0) * 1e3
+            hbm_launches = sum(1 for i in range(nst) if kinds[i] == 0 and by[i] / (peaks["hbm"] * 1e9) > fl[i] / tpk)
+            roof["two_roof_bound"] = {"kernel_ms_per_step": bound_ms, "frac": bound_ms / conv_ms if conv_ms else None,
+                                      "hbm_bound_launches": hbm_launches,
+                                      "bytes_per_step": sum(by[i] for i in range(nst) if kinds[i] == 0)}
+        out["roofline"] = roof
+    return out, first_out
+
+
+def measure_images(arm, steps, world, barrier, max_over_ranks):
+    """End to end through THProcessImages: HWC byte images in host memory (a quarter of the fp32 batch's bytes), converted
+    and normalised on the GPU."""
+    lib = arm.lib
+    b, c, hh, ww = arm.shape
+    nbytes = b * hh * ww * 3
+    hptr = lib.THB200_HostAlloc(nbytes)
+    img = np.ctypeslib.as_array(C.cast(hptr, C.POINTER(C.c_ubyte)), shape=(b, hh, ww, 3))
+    img[...] = np.random.default_rng(99).integers(0, 256, img.shape, dtype=np.uint8)
+    ptrs = (C.c_void_p * b)(*[hptr + i * hh * ww * 3 for i in range(b)])
+    res, ow, oh = C.POINTER(C.c_float)(), C.c_int(), C.c_int()
+
+    def fwd():
+        n = lib.THProcessImages(arm.net, ptrs, b, ww, hh, ww * 3, C.byref(res), C.byref(ow), C.byref(oh), 0)
+        if n <= 0:
+            raise SystemExit("THProcessImages failed: %s" % lib.THB200_LastErrorString())
+        return n
+
+    for _ in range(3):
+        n = fwd()
+    dt = time_loop(fwd, steps, barrier, max_over_ranks)
+    lib.THB200_HostFree(hptr)
+    return {"value": world * b / dt, "unit": "images/s", "ms_per_step": dt * 1e3, "entry": "THProcessImages",
+            "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": n * 4, "host_buffer": "pinned (THB200_HostAlloc)"}
+
+
+def measure_strong(th, workload, dtype, batch, ngpus, steps, warmup, tmpdir, one_gpu_out):
+    """One batch of `batch` images sharded over `ngpus` GPUs by the library itself (contiguous slices, whole network and
+    resident weights on every GPU, results gathered into GPU 0 by peer copies): device-resident and end-to-end rates,
+    and whether the result equals the single-GPU result of the same batch bit for bit."""
+    lib = th.lib
+    lib.THB200_SetDevices(ngpus)
+    try:
+        arm = Arm(th, workload, dtype, batch, 0, tmpdir)
+    finally:
+        lib.THB200_SetDevices(1)
+    arm.forward()
+    same = bool(np.array_equal(arm.output(), one_gpu_out))
+    for _ in range(warmup):
+        arm.forward()
+    noop = lambda: None
+    ident = lambda v: v
+    e2e_s = time_loop(arm.forward, steps, noop, ident)
+    lib.THB200_SetPipelineChunks(1)
+    arm.forward()
+    lib.THB200_SetPipelineChunks(0)
+    lib.THB200_TimeForward(arm.net, warmup)
+    ms = lib.THB200_TimeForward(arm.net, steps)
+    rec = {"scaling": "strong", "n_gpus": ngpus, "global_batch": batch, "images_per_gpu": batch / ngpus,
+           "value": batch / (ms * 1e-3) if ms > 0 else None, "unit": "images/s", "ms_per_step": ms,
+           "e2e": {"value": batch / e2e_s, "ms_per_step": e2e_s * 1e3, "entry": "THProcessFloat",
+                   "gather": "cudaMemcpyPeerAsync into GPU 0, one copy to the host"},
+           "bit_identical_to_1gpu": same}
+    arm.close()
+    return rec
+
+
+def parity_record(gpu_out, ref_path, tol):
+    """The GPU arm's first forward against the reference's output on the same images (max-abs error / max-abs reference)."""
+    try:
+        ref = np.load(ref_path)
+    except OSError:
+        return None
+    n = min(len(ref), len(gpu_out))
+    a, r = gpu_out[:n].astype(np.float64), ref[:n].astype(np.float64)
+    rel = float(np.abs(a - r).max() / max(np.abs(r).max(), 1e-30))
+    rec = {"images": n, "rel_err": rel, "tol": tol, "ok": bool(rel < tol), "against": "the reference CPU forward of the same images"}
+    if r.shape[1] > 1:
+        rec["argmax_agree"] = float((a.argmax(1) == r.argmax(1)).mean())
+    return rec
 
 
 def main():
@@ -187,10 +447,12 @@ def main():
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sub-records", action="store_true", help="headline measurement only (no int8 / THProcessImages records)")
     ap.add_argument("--_ref_child", action="store_true")
     ap.add_argument("--ref-batch", type=int, default=8)
-    ap.add_argument("--steps-ref", type=int, default=3)
+    ap.add_argument("--steps-ref", type=int, default=2)
     ap.add_argument("--warmup-ref", type=int, default=1)
+    ap.add_argument("--ref-out", default=None)
     args = ap.parse_args()
     if args._ref_child:
         return reference_child(args)
@@ -213,12 +475,17 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return
-        ref, why = run_reference(args, max(2, min(args.steps, 5)), 1)
+        rsteps = max(1, min(args.steps, 2))
+        ref, why = run_reference(args, rsteps, 1)
         if ref is None:
             print(json.dumps({"impl": "reference", "unavailable": why}))
             return
+        config["workload"] = f"{args.workload}_fp32_b{ref['batch']}"
+        config["batch_per_gpu"] = ref["batch"]
+        config["parallelism"] = "host cores only"
         print(json.dumps({"impl": "reference", "metric": "images_per_second", "value": ref["value"], "unit": "images/s",
-                          "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ref["ms_per_step"],
+                          "n_gpus": args.gpus, "steps": ref["steps"], "warmup": ref["warmup"], "requested_steps": args.steps,
+                          "requested_warmup": args.warmup, "ms_per_step": ref["ms_per_step"],
                           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                           "config": config, "cpu_baseline": {k: ref[k] for k in ("value", "unit", "cores", "kind", "sample")},
                           "e2e": {"value": ref["value"], "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
@@ -234,117 +501,69 @@ def main():
     lib.THB200_ProfileForward.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.THB200_ProfileForwardBytes.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
     lib.THB200_KernelLaunches.restype = C.c_int
-
-    tmp = tempfile.TemporaryDirectory()
-    g, path = build_fixture(args.workload, tmp.name, dtype)
-    h = th.load_network(path)
-    th.set_stats(h, g.mean, g.std)
-    if dtype == "int8":
-        if args.workload == "vgg16":
-            th.make_spatial(h, g.input_shape[1])
-        net = th.create_lowp_network(h, LOWP_RANGE)
-    else:
-        lib.THB200_SetPrecision({"fp32": 0, "fp16": 1, "bf16": 2}[dtype])
-        net = lib.THCreateCudaNetwork(h)
-        if not net:
-            raise SystemExit("THCreateCudaNetwork failed: %s" % lib.THB200_LastErrorString())
-    th.free_network(h)
-
-    # pinned host batch (the e2e path copies it to the device every step)
-    c, hh, ww = g.input_shape
-    nbytes = batch * c * hh * ww * 4
-    hptr = lib.THB200_HostAlloc(nbytes)
-    host = np.ctypeslib.as_array(C.cast(hptr, C.POINTER(C.c_float)), shape=(batch, c, hh, ww))
-    host[...] = g.make_input(batch, seed=1234 + rank)
-    res = C.POINTER(C.c_float)()
-    ow, oh = C.c_int(), C.c_int()
-
-    def forward_e2e():
-        n = lib.THProcessFloat(net, hptr, batch, ww, hh, c, C.byref(res), C.byref(ow), C.byref(oh))
-        if n <= 0:
-            raise SystemExit("THProcessFloat failed: %s" % lib.THB200_LastErrorString())
-        return n
-
+    lib.THB200_HostAlloc.restype = C.c_void_p
     barrier, max_over_ranks = ranks.barrier, ranks.max
+    peaks = read_peaks()
+    tmp = tempfile.TemporaryDirectory()
+
+    # the reference CPU forward runs after the GPU measurements (rank 0 of a single-GPU run only)
+    ref_out = os.path.join(tmp.name, "ref_logits.npy")
+    want_ref = rank == 0 and world == 1 and not args.no_cpu_baseline
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    # The device-resident loop runs the whole-batch plan, so stage the batch into it with the copy/compute pipelining of
-    # THProcessFloat switched off once; the end-to-end loop below runs with the library's default (pipelined sub-batches).
-    lib.THB200_SetPipelineChunks(1)
-    out_count = forward_e2e()          # plans the network, uploads the weights, stages the batch
-    lib.THB200_SetPipelineChunks(0)
-    for _ in range(warmup):
-        forward_e2e()
-    if lib.THB200_TimeForward(net, warmup) < 0:
-        raise SystemExit("THB200_TimeForward failed: %s" % lib.THB200_LastErrorString())
-
-    # --- device-resident: K forwards, events on the launching stream
-    barrier()
+    arm = Arm(th, args.workload, dtype, batch, rank, tmp.name)
     sampler.mark_begin()
-    l0 = lib.THB200_KernelLaunches()
-    ms_step = lib.THB200_TimeForward(net, args.steps)
-    launches = lib.THB200_KernelLaunches() - l0
-    barrier()
-    if ms_step < 0:
-        raise SystemExit("THB200_TimeForward failed: %s" % lib.THB200_LastErrorString())
-    ms_step = max_over_ranks(ms_step)
-    # --- end to end through the public API with host buffers
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        forward_e2e()
-    e2e_s = (time.perf_counter() - t0) / args.steps
-    barrier()
-    e2e_s = max_over_ranks(e2e_s)
+    head, first_out = measure(arm, args.steps, warmup, world, barrier, max_over_ranks, peaks)
     sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
 
-    # --- per-launch profile for the roofline of the dominant kernel
-    maxs = 4096
-    kinds = (C.c_int * maxs)()
-    ms = (C.c_float * maxs)()
-    fl = (C.c_double * maxs)()
-    nst = lib.THB200_ProfileForward(net, 5, maxs, kinds, ms, fl)
-    roof = None
-    peaks = read_peaks()
-    if nst > 0:
-        conv_ms = sum(ms[i] for i in range(nst) if kinds[i] == 0)
-        conv_fl = sum(fl[i] for i in range(nst) if kinds[i] == 0)
-        tot_ms = sum(ms[i] for i in range(nst))
-        nconv = sum(1 for i in range(nst) if kinds[i] == 0)
-        ach = conv_fl / (conv_ms * 1e-3) / 1e12 if conv_ms > 0 else 0.0
-        roof = {"bound": "tensor", "kernel": "conv_tc_kernel" if dtype != "fp32" else "conv_simt_kernel",
-                "achieved": ach, "peak": peaks["tflops"] if dtype != "int8" else peaks["tflops"] * 2, "unit": "TFLOP/s",
-                "frac": ach / (peaks["tflops"] * (2 if dtype == "int8" else 1)), "peak_source": "of " + peaks["src"],
-                "traffic": NCU_DRAM_BYTES_PER_STEP.get((args.workload, dtype, batch)), "launches_per_step": nconv, "kernel_ms_per_step": conv_ms, "share_of_step": conv_ms / tot_ms if tot_ms else None,
-                "flops_per_step": conv_fl}
-        # the bound a forward of this network cannot beat when every launch ran at the slower of its two roofs
-        # (algorithmic FLOPs / measured tensor peak, algorithmic bytes / measured HBM copy bandwidth)
-        by = (C.c_double * maxs)()
-        if lib.THB200_ProfileForwardBytes(net, maxs, by) == nst and peaks["hbm"]:
-            tpk = peaks["tflops"] * 1e12 * (2 if dtype == "int8" else 1)
-            bound_ms = sum(max(fl[i] / tpk, by[i] / (peaks["hbm"] * 1e9)) for i in range(nst) if kinds[i] == 0) * 1e3
-            hbm_launches = sum(1 for i in range(nst) if kinds[i] == 0 and by[i] / (peaks["hbm"] * 1e9) > fl[i] / tpk)
-            roof["two_roof_bound"] = {"kernel_ms_per_step": bound_ms, "frac": bound_ms / conv_ms if conv_ms else None,
-                                      "hbm_bound_launches": hbm_launches, "bytes_per_step": sum(by[i] for i in range(nst) if kinds[i] == 0)}
-
+    out = None
     if rank == 0:
-        out = {"metric": "images_per_second", "value": world * batch / (ms_step * 1e-3), "unit": "images/s", "n_gpus": world,
-               "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        out = {"metric": "images_per_second", "value": head["value"], "unit": "images/s", "n_gpus": world,
+               "steps": args.steps, "warmup": warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak",
                "vs_baseline": None, "dtype": {"fp16": "f16", "fp32": "f32", "bf16": "bf16", "int8": "u8"}[dtype], "data": "synthetic",
-               "config": config,
-               "e2e": {"value": world * batch / e2e_s, "unit": "images/s", "h2d_bytes_per_step": nbytes,
-                       "d2h_bytes_per_step": out_count * 4, "ms_per_step": e2e_s * 1e3},
-               "gpu_launches": launches, "clocks": clocks, "roofline": roof}
-        if world == 1 and not args.no_cpu_baseline:
-            ref, why = run_reference(args, 3, 1)
+               "config": config, "e2e": head["e2e"], "gpu_launches": head["gpu_launches"], "clocks": clocks,
+               "roofline": head.get("roofline"),
+               "timed_region": "value: boundary kernels (fp32 NCHW <-> the engine's layout) and every planned launch, batch and "
+                               "result resident in HBM; e2e: the THProcessFloat call with host buffers"}
+    # ---- sub-records measured in the same run: the byte-image entry point and the uint8 engine
+    if not args.no_sub_records:
+        images = measure_images(arm, args.steps, world, barrier, max_over_ranks)
+        if rank == 0:
+            out["e2e_images"] = images
+    arm.close()
+    if not args.no_sub_records and dtype != "int8" and args.workload in ("resnet50", "resnet18", "vgg16"):
+        arm8 = Arm(th, args.workload, "int8", batch, rank, tmp.name)
+        sub, _ = measure(arm8, args.steps, warmup, world, barrier, max_over_ranks, peaks)
+        arm8.close()
+        if rank == 0:
+            out["int8"] = {"config": f"{args.workload}_int8_b{batch} (uint8 lowp engine, range {LOWP_RANGE:g})", "value": sub["value"],
+                           "unit": "images/s", "ms_per_step": sub["ms_per_step"], "e2e": sub["e2e"], "gpu_launches": sub["gpu_launches"],
+                           "roofline": sub.get("roofline")}
+    # ---- strong scaling inside the library: ONE batch over the N GPUs of this box (rank 0 alone drives them; the other
+    # ranks hold no work and wait on the host, through the rendezvous store, so that no kernel of theirs sits on a GPU)
+    if world > 1 and not args.no_sub_records:
+        import torch
+        torch.cuda.synchronize()
+        barrier()
+        if rank == 0:
+            try:
+                out["strong"] = measure_strong(th, args.workload, dtype, batch, world, args.steps, warmup, tmp.name, first_out)
+            except (SystemExit, RuntimeError) as e:
+                out["strong"] = {"unavailable": str(e)[:200]}
+            ranks.host_signal("strong_done")
+        else:
+            ranks.host_wait("strong_done")
+    if rank == 0:
+        if want_ref:
+            ref, why = run_reference(args, 2, 1, ref_out)
             out["cpu_baseline"] = ({k: ref[k] for k in ("value", "unit", "cores", "kind", "sample")} if ref
                                    else {"value": None, "unit": "images/s", "cores": 0, "kind": "reference", "sample": why})
+            if ref and dtype != "int8":
+                out["parity"] = parity_record(first_out, ref_out, {"fp32": 1e-4, "fp16": 1e-2, "bf16": 6e-2}[dtype])
         print(json.dumps(out))
-    lib.THB200_HostFree(hptr)
-    th.free_network(net)
     ranks.close()
 
 

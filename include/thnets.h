@@ -259,14 +259,17 @@ void *THB200_HostAlloc(size_t bytes);
 void THB200_HostFree(void *p);
 /* device time in milliseconds of the last forward (kernels only, between the input and output copies) */
 float THB200_LastDeviceMs(THNETWORK *network);
-/* Device-resident benchmark loop: runs the planned forward `iters` times on the batch uploaded by the last
- * THProcessFloat call and returns the mean device time per forward in milliseconds (< 0 on error). */
+/* Device-resident benchmark loop: the whole forward from the batch the last THProcessFloat / THProcessImages call
+ * left in device memory (NCHW fp32, or HWC bytes) to the NCHW fp32 result in device memory -- the boundary kernels at
+ * both ends, the uint8 engine's input-range pass and the planned launches -- `iters` times back to back; returns the
+ * mean device time per forward in milliseconds (< 0 on error).  No host<->device copy of batch or result is inside. */
 float THB200_TimeForward(THNETWORK *network, int iters);
-/* Per-launch device time (ms, averaged over `iters` passes) of the planned forward on the first GPU; kinds[t] is
- * 0 for a convolution / Linear-as-convolution launch, 1 for a GEMV, 2 otherwise; flops[t] its algorithmic FLOPs.
- * Returns the number of launches described (<= max_steps), < 0 on error. */
+/* Per-launch device time (ms, averaged over `iters` passes) of the same forward on the first GPU.  Entry 0 is the
+ * boundary kernel in, the last entry the boundary kernel out, the planned launches lie between.  kinds[t] is 0 for a
+ * convolution / Linear-as-convolution launch, 1 for a GEMV, 2 for another planned launch, 3 for a boundary kernel;
+ * flops[t] its algorithmic FLOPs.  Returns the number of entries described (<= max_steps), < 0 on error. */
 int THB200_ProfileForward(THNETWORK *network, int iters, int max_steps, int *kinds, float *ms, double *flops);
-/* bytes[t]: algorithmic bytes of launch t of the same list (input, output, residual and weights counted once each at the
+/* bytes[t]: algorithmic bytes of entry t of the same list (input, output, residual and weights counted once each at the
  * storage type's size) for convolution and GEMV launches, 0 for the others.  Returns the number described. */
 int THB200_ProfileForwardBytes(THNETWORK *network, int max_steps, double *bytes);
 /* the contiguous slice [offset, offset+count) of an N-image batch that GPU g of G processes */

@@ -24,10 +24,17 @@ _f = C.POINTER(C.c_float)
 _u8 = C.POINTER(C.c_ubyte)
 
 
-def build(ref_root="/root/reference"):
+def reference_root():
+    """Root of a checkout of the reference: $THNETS_REFERENCE, else a directory `reference` beside the repository."""
+    cand = os.environ.get("THNETS_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.isfile(os.path.join(cand, "thnets.h")) else None
+
+
+def build(ref_root=None):
     """Compile the C restatement and, when the reference tree is present, the reference itself."""
     subprocess.check_call(["make", "-s", "-C", _HERE, "port"])
-    if os.path.isdir(ref_root):
+    ref_root = ref_root or reference_root()
+    if ref_root and os.path.isdir(ref_root):
         subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "reflowp", f"REF={ref_root}"])
 
 

@@ -16,14 +16,24 @@ worst = r.max(10.0 + r.rank)          # rank 1 is "slower"
 total = r.sum(256)                    # every rank processed 256 images (weak scaling)
 off, cnt = r.shard(251)
 r.barrier()
+# host-side hand-over: rank 1 blocks on the store (no collective in flight) until rank 0 has done its solo work
+import time
+if r.rank == 0:
+    time.sleep(0.5)
+    open(os.path.join(%r, "solo_done"), "w").write("x")
+    r.host_signal("solo")
+else:
+    r.host_wait("solo", 60)
+    assert os.path.exists(os.path.join(%r, "solo_done"))
+r.barrier()
 print(json.dumps(dict(rank=r.rank, world=r.world, worst=worst, total=total, off=off, cnt=cnt)))
 r.close()
-""" % ROOT
+"""
 
 
 def test_two_ranks_gloo(tmp_path):
     script = tmp_path / "child.py"
-    script.write_text(CHILD)
+    script.write_text(CHILD % (ROOT, str(tmp_path), str(tmp_path)))
     port = 29500 + os.getpid() % 2000
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE="2", OMP_NUM_THREADS="1")
     procs = [subprocess.Popen([sys.executable, str(script)], env=dict(env, RANK=str(i), LOCAL_RANK=str(i)),

@@ -70,8 +70,9 @@ def test_struct_layout_matches_the_reference_header(tmp_path):
     mine = probe(os.path.join(ROOT, "include"))
     for k, v in EXPECTED_ABI.items():
         assert mine[k] == v, (k, mine[k], v)
-    if os.path.exists("/root/reference/thnets.h"):
-        assert probe("/root/reference") == mine
+    from oracle.oracle import reference_root
+    if reference_root():
+        assert probe(reference_root()) == mine
 
 
 def test_torch7_loader_and_lowering(th, tmp_path):
@@ -271,3 +272,31 @@ def test_fixture_writers_round_trip_through_the_reference_formats(tmp_path):
     p = str(tmp_path / "m.net")
     fx.write_pymodel(g, p)
     assert open(p, "rb").read(24) == b"PyTorch Graph Dump 1.00\0"
+
+
+def test_static_scratch_entry_validates_before_any_launch():
+    """thb_conv_u8_fwd_static must answer a descriptor its channel-sum pass cannot digest with an error code, before any
+    CUDA call: every case below returns without touching a device (this test runs where there is none)."""
+    from thnets_b200 import kernels_abi as K
+    lib = K.load()
+    lib.thb_conv_u8_fwd_static.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    fake = C.c_void_p(1 << 20)          # never dereferenced: each call is refused first
+
+    def desc(**kw):
+        d = K.ConvDesc()
+        d.dtype = K.THB_U8
+        d.N, d.H, d.W, d.Cin, d.Cout, d.in_ld = 2, 8, 8, 24, 16, 32
+        d.w = d.kinfo = d.tmap = d.wsat = d.status = 1 << 20
+        for k, v in kw.items():
+            setattr(d, k, v)
+        return d
+
+    ARG, UNSUP = -4, -1
+    cases = [(desc(dtype=K.THB_F16), fake, ARG), (desc(N=-2, H=-8), fake, ARG), (desc(N=0), fake, ARG),
+             (desc(Cin=0), fake, ARG), (desc(in_ld=24), fake, ARG), (desc(in_ld=16), fake, ARG),
+             (desc(), C.c_void_p((1 << 20) + 4), ARG), (desc(wsat=None), fake, ARG), (desc(status=None), fake, ARG),
+             (desc(tmap=None), fake, ARG), (desc(in_row_pitch=12, in_pad_left=1), fake, UNSUP),
+             (desc(N=64, H=512, W=512), fake, ARG)]
+    for d, x, want in cases:
+        assert lib.thb_conv_u8_fwd_static(C.byref(d), x, fake, None) == want
+    assert lib.thb_conv_u8_fwd_static(None, fake, fake, None) == ARG

@@ -311,3 +311,83 @@ def test_lowp_images_bit_exact(th, oracle, tmp_path, batch, bgr):
     assert (ow, oh) == (1, 1)
     assert np.array_equal(out, ref.ravel()), np.abs(out - ref.ravel()).max()
     th.free_network(hl)
+
+
+# ------------------------------------------------------------------------------------------ full-width networks
+# The benchmark architectures at their real channel widths and input sizes (small batches, so that the CPU oracle
+# finishes in seconds): every layer runs with the tile shapes, pipeline depths and fusions the benchmark uses.
+FULL = {
+    "resnet50": (lambda: fx.resnet50(), 4, "py"),
+    "resnet18": (lambda: fx.resnet18(), 4, "py"),
+    "alexnet_owt": (lambda: fx.alexnet_owt(), 1, "t7"),
+    "vgg16": (lambda: fx.vgg16(fc=512), 1, "t7"),
+    "segnet": (lambda: fx.segnet(size=256), 2, "py"),
+}
+
+
+@pytest.mark.parametrize("name,mode", [("resnet50", 1), ("resnet50", 0), ("resnet18", 1), ("alexnet_owt", 0), ("vgg16", 1),
+                                       ("segnet", 1)])
+def test_full_width_network_parity(th, oracle, tmp_path, name, mode):
+    build, batch, kind = FULL[name]
+    g = build()
+    x = g.make_input(batch)
+    ref = oracle.run(g, x)
+    hc = _convert(th, g, kind, tmp_path, name + "_full", mode)
+    out, _, _ = th.process_float(hc, x)
+    assert out.size == ref.size
+    err = rel_err(out, ref.ravel())
+    assert err < TOL[mode], (name, mode, err)
+    if ref.ndim == 2:
+        agree = float((out.reshape(ref.shape).argmax(1) == ref.argmax(1)).mean())
+        assert agree == 1.0, (name, "arg-max agreement", agree)
+    th.free_network(hc)
+
+
+def test_full_width_resnet50_uint8_bit_exact(th, oracle, tmp_path):
+    """ResNet-50 at full width and 224 x 224 through the uint8 engine, range 20 (the benchmark's int8 configuration at
+    batch 2): every output byte equals the restatement's (see test_lowp_residual_network_bit_exact for its rules)."""
+    g = fx.resnet50(fc_bias=0.01)
+    x = g.make_input(2)
+    ref = oracle.run_lowp(g, x, 20.0, 224)
+    h = _load(th, g, "py", tmp_path, "r50u8")
+    hl = th.create_lowp_network(h, 20.0)
+    th.free_network(h)
+    out, _, _ = th.process_float(hl, x)
+    assert np.array_equal(out, ref.ravel()), np.abs(out - ref.ravel()).max()
+    assert len(np.unique(out)) > 3
+    th.free_network(hl)
+
+
+def test_full_width_vgg16_uint8_bit_exact(th, oracle, tmp_path):
+    """VGG-16 at full width and 224 x 224 through THMakeSpatial + THCreateLowpNetwork, range 20, batch 2 (the hidden
+    classifier layers narrowed to 512 to keep the fixture file small): bit-exact."""
+    g = fx.vgg16(fc=512)
+    x = g.make_input(2)
+    ref = oracle.run_lowp(g, x, 20.0, 224)
+    h = _load(th, g, "t7", tmp_path, "vggu8")
+    th.make_spatial(h, 224)
+    hl = th.create_lowp_network(h, 20.0)
+    th.free_network(h)
+    out, _, _ = th.process_float(hl, x)
+    assert np.array_equal(out, ref.ravel()), np.abs(out - ref.ravel()).max()
+    th.free_network(hl)
+
+
+def test_lowp_first_convolution_15x15_stride_2(th, oracle, tmp_path):
+    """A uint8 network whose first convolution is 15x15 / stride 2 / pad 7 on three channels: after the space-to-depth
+    rewrite its kernel row is 8 taps of 16 bytes, the shape for which 16-bit types store the staged rows with padding.
+    The uint8 loader and channel sums use dense rows, and the result must be bit-exact all the same."""
+    g = fx.Graph(11)
+    g.input_shape, g.input_dist = (3, 48, 48), "uniform"
+    x = g.relu(g.conv(0, 3, 24, 15, 2, 7, bias=0.05))
+    x = g.maxpool(x, 2, 2)
+    x = g.relu(g.conv(x, 24, 32, 3, 1, 1, bias=0.05))
+    g.conv(x, 32, 10, 12, 1, 0, bias=0.05)
+    xin = g.make_input(3)
+    ref = oracle.run_lowp(g, xin, 8.0, 48)
+    h = _load(th, g, "t7", tmp_path, "first15")
+    hl = th.create_lowp_network(h, 8.0)
+    th.free_network(h)
+    out, _, _ = th.process_float(hl, xin)
+    assert np.array_equal(out, ref.ravel()), np.abs(out - ref.ravel()).max()
+    th.free_network(hl)

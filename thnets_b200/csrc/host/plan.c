@@ -114,6 +114,7 @@ typedef struct instance {
     unsigned char *d_img; /* staged u8 HWC images */
     float *d_out;         /* NCHW fp32 result */
     float *d_minmax;
+    float h_minmax[2];    /* host copy of the slice's input extremes (uint8 engine) */
     int *d_status;
     abuf *bufs;
     int nbufs;
@@ -148,6 +149,9 @@ struct thb_engine {
     size_t h_out_bytes;
     float last_ms;
     int peer_gather;
+    /* arguments of the last forward, for the device-resident timing loop */
+    int last_has_x, last_cp, last_bgr;
+    float last_mean[3], last_std[3];
 };
 
 static int align_of(int dtype) { return thb_channel_align(dtype); }
@@ -1017,7 +1021,9 @@ static int instance_build(thb_engine *E, instance *I, int device, int slice_off,
         const int padW = (c1->padW + 1) / 2, kW = (c1->kW - 1 - c1->padW) / 2 + padW + 1;
         const char *off = getenv("THB200_NO_PADDED_ROWS");
         value *v = &P.val[0];
-        if (kW * v->ld * esize_of(E->dtype) == 128 && thb_conv_padded_rows_supported(E->dtype) && !(off && atoi(off))) {
+        /* (16-bit types only: the uint8 loader and the channel-sum pass write and read dense rows) */
+        if (E->dtype != THB_U8 && kW * v->ld * esize_of(E->dtype) == 128 && thb_conv_padded_rows_supported(E->dtype) &&
+            !(off && atoi(off))) {
             v->pad_left = padW;
             v->row_pitch = (padW + in.W + kW - 1 + 3) & ~3;
             I->nbufs--; /* re-create the buffer at its padded size */
@@ -1175,22 +1181,37 @@ static int run_steps(thb_engine *E, instance *I)
     return run_steps_ev(E, I, 0);
 }
 
-/* Per-launch device times of the planned forward on the first GPU (events around every launch on the launching
- * stream, averaged over `iters` passes).  kinds: 0 tensor-core/FFMA convolution, 1 GEMV, 2 everything else.
+static int lowp_input_range(thb_engine *E, instance *set, int G, int has_x, int cp, int C, int H, int W, const float *mean,
+                            const float *std, float *q_sub, float *q_mult);
+static int boundary_in(thb_engine *E, instance *I, int has_x, int inplace, int cp, int bgr, int C, int H, int W,
+                       const float *mean, const float *std, float q_sub, float q_mult);
+static int boundary_out(thb_engine *E, instance *I, float *dst);
+
+/* Per-launch device times of one forward on the first GPU from the batch staged by the last THProcess* call (events
+ * around every launch on the launching stream, averaged over `iters` passes).  Entry 0 is the boundary kernel in
+ * (NCHW fp32 or HWC bytes -> the engine's layout), entries 1..n the planned launches, entry n+1 the boundary kernel
+ * out.  kinds: 0 tensor-core/FFMA convolution, 1 GEMV, 2 any other planned launch, 3 boundary kernel.
  * flops: algorithmic FLOPs of the launch (2 * MACs of the convolution / Linear it computes), 0 otherwise. */
 int thb_engine_profile(thb_engine *E, int iters, int max_steps, int *kinds, float *ms, double *flops)
 {
-    if (!E || !E->built || iters < 1) return -1;
+    if (!E || !E->built || iters < 1 || (!E->last_has_x && !E->last_cp)) return -1;
     instance *I = &E->inst[0];
     if (cudaSetDevice(I->device) != cudaSuccess) return -1;
-    const int n = I->nsteps < max_steps ? I->nsteps : max_steps;
-    cudaEvent_t *evs = calloc(I->nsteps + 1, sizeof(cudaEvent_t));
-    for (int t = 0; t <= I->nsteps; t++) cudaEventCreate(&evs[t]);
+    const int total = I->nsteps + 2;
+    const int n = total < max_steps ? total : max_steps;
+    cudaEvent_t *evs = calloc(total + 1, sizeof(cudaEvent_t));
+    for (int t = 0; t <= total; t++) cudaEventCreate(&evs[t]);
     for (int t = 0; t < n; t++) ms[t] = 0;
     int rc = 0;
     for (int it = 0; it < iters && !rc; it++) {
+        float q_sub = 0, q_mult = 0;
+        rc = lowp_input_range(E, E->inst, 1, E->last_has_x, E->last_cp, E->C, E->H, E->W, E->last_mean, E->last_std, &q_sub, &q_mult);
         cudaEventRecord(evs[0], I->stream);
-        rc = run_steps_ev(E, I, evs);
+        if (!rc) rc = boundary_in(E, I, E->last_has_x, 0, E->last_cp, E->last_bgr, E->C, E->H, E->W, E->last_mean, E->last_std, q_sub, q_mult);
+        cudaEventRecord(evs[1], I->stream);
+        if (!rc) rc = run_steps_ev(E, I, evs + 1);
+        if (!rc) rc = boundary_out(E, I, I->d_out);
+        cudaEventRecord(evs[total], I->stream);
         if (cudaStreamSynchronize(I->stream) != cudaSuccess) rc = -1;
         for (int t = 0; t < n && !rc; t++) {
             float m = 0;
@@ -1199,9 +1220,11 @@ int thb_engine_profile(thb_engine *E, int iters, int max_steps, int *kinds, floa
         }
     }
     for (int t = 0; t < n; t++) {
-        step *s = &I->steps[t];
-        kinds[t] = s->kind == ST_CONV ? 0 : s->kind == ST_GEMV ? 1 : 2;
+        kinds[t] = 3;
         flops[t] = 0;
+        if (t == 0 || t == total - 1) continue;
+        step *s = &I->steps[t - 1];
+        kinds[t] = s->kind == ST_CONV ? 0 : s->kind == ST_GEMV ? 1 : 2;
         if (s->flops_node >= 0) {
             thb_node *nd = &E->model->nodes[s->flops_node];
             double pix = s->kind == ST_CONV ? (double)s->conv.N * s->conv.oH * s->conv.oW : (double)s->N;
@@ -1209,23 +1232,25 @@ int thb_engine_profile(thb_engine *E, int iters, int max_steps, int *kinds, floa
             flops[t] = 2.0 * pix * nd->Cout * nd->Cin * nd->kH * nd->kW + s->flops_extra;
         }
     }
-    for (int t = 0; t <= I->nsteps; t++) cudaEventDestroy(evs[t]);
+    for (int t = 0; t <= total; t++) cudaEventDestroy(evs[t]);
     free(evs);
     return rc ? -1 : n;
 }
 
-/* Algorithmic bytes of each planned launch on the first GPU: every tensor the launch names counted once (input, output,
+/* Algorithmic bytes of each entry of thb_engine_profile: every tensor the launch names counted once (input, output,
  * residual, weights) at the storage type's size; 0 for launches that are neither a convolution nor a GEMV.  The
  * companion of thb_engine_profile's flops for a per-launch "slower of the two roofs" bound. */
 int thb_engine_profile_bytes(thb_engine *E, int max_steps, double *bytes)
 {
     if (!E || !E->built) return -1;
     instance *I = &E->inst[0];
-    const int n = I->nsteps < max_steps ? I->nsteps : max_steps;
+    const int total = I->nsteps + 2;
+    const int n = total < max_steps ? total : max_steps;
     for (int t = 0; t < n; t++) {
-        step *s = &I->steps[t];
-        const double el = s->dtype == THB_F32 ? 4 : s->dtype == THB_U8 ? 1 : 2;
         bytes[t] = 0;
+        if (t == 0 || t == total - 1) continue;
+        step *s = &I->steps[t - 1];
+        const double el = s->dtype == THB_F32 ? 4 : s->dtype == THB_U8 ? 1 : 2;
         if (s->kind == ST_CONV) {
             const thb_conv_desc *d = &s->conv;
             const double out = (double)d->N * d->oH * d->oW * d->Cout;
@@ -1304,6 +1329,16 @@ static int engine_build(thb_engine *E, int N, int C, int H, int W, int rank, int
             if (!can) E->peer_gather = 0;
         }
         if (E->peer_gather) {
+            /* direct copies over NVLink need the access switched on from the sending GPU's side (a second request is
+             * answered with cudaErrorPeerAccessAlreadyEnabled, which is fine) */
+            for (int g = 1; g < G; g++) {
+                cudaSetDevice(E->inst[g].device);
+                const cudaError_t pe = cudaDeviceEnablePeerAccess(E->inst[0].device, 0);
+                if (pe != cudaSuccess && pe != cudaErrorPeerAccessAlreadyEnabled) E->peer_gather = 0;
+                cudaGetLastError();
+            }
+        }
+        if (E->peer_gather) {
             long total = 0;
             for (int g = 0; g < G; g++) total += E->inst[g].out_count;
             cudaSetDevice(E->inst[0].device);
@@ -1361,6 +1396,91 @@ static void set_dynamic_quant(instance *I, float in_sub, float in_mult)
     }
 }
 
+/* The uint8 engine's input range.  A float batch: lowp_basic.c:15-29 takes one range over the WHOLE batch tensor, so
+ * the slices' extremes are reduced on the host (one 8-byte read-back per GPU) and every instance's first convolution
+ * gets the parameters that follow from it.  Byte images: the loader's range is static (lowp_basic.c:82-131), nothing
+ * is measured here. */
+static int lowp_input_range(thb_engine *E, instance *set, int G, int has_x, int cp, int C, int H, int W, const float *mean,
+                            const float *std, float *q_sub, float *q_mult)
+{
+    *q_sub = *q_mult = 0;
+    if (E->dtype != THB_U8) return 0;
+    if (!has_x) {
+        if (cp != 3) { thb_set_error("the lowp image loader takes 3-plane images"); return -1; }
+        return 0;
+    }
+    float lo = 0, hi = 0;
+    for (int g = 0; g < G; g++) {
+        instance *I = &set[g];
+        CU(cudaSetDevice(I->device));
+        if (thb_minmax_normalized(I->d_in, I->slice_n, C, H, W, mean, std, I->d_minmax, I->stream)) return -1;
+        CU(cudaMemcpyAsync(I->h_minmax, I->d_minmax, 2 * sizeof(float), cudaMemcpyDeviceToHost, I->stream));
+    }
+    for (int g = 0; g < G; g++) {
+        instance *I = &set[g];
+        CU(cudaSetDevice(I->device));
+        CU(cudaStreamSynchronize(I->stream));
+        if (I->h_minmax[0] < lo) lo = I->h_minmax[0];
+        if (I->h_minmax[1] > hi) hi = I->h_minmax[1];
+    }
+    *q_sub = lo;
+    *q_mult = hi - lo > 0 ? (float)(255.0 / (hi - lo)) : 0;
+    for (int g = 0; g < G; g++) set_dynamic_quant(&set[g], *q_sub, *q_mult);
+    return 0;
+}
+
+/* The boundary kernel in: the staged input (I->d_in: NCHW fp32, or I->d_img: HWC bytes) -> the engine's layout and type. */
+static int boundary_in(thb_engine *E, instance *I, int has_x, int inplace, int cp, int bgr, int C, int H, int W,
+                       const float *mean, const float *std, float q_sub, float q_mult)
+{
+    int rc;
+    void *in_ptr = bufptr(I, I->in_val.buf, 0, E->dtype);
+    if (has_x && E->input_s2d && E->dtype == THB_U8)
+        rc = thb_preprocess_s2d_u8(I->d_in, inplace ? I->d_in : 0, I->slice_n, C, H, W, mean, std, in_ptr, I->in_val.ld, q_sub,
+                                   q_mult, I->stream);
+    else if (has_x && E->input_s2d)
+        rc = thb_preprocess_s2d_padded(I->d_in, inplace ? I->d_in : 0, I->slice_n, C, H, W, mean, std, E->dtype, in_ptr,
+                                       I->in_val.ld, I->in_val.row_pitch ? I->in_val.row_pitch : W / 2,
+                                       I->in_val.pad_left, I->stream);
+    else if (has_x)
+        rc = thb_preprocess(I->d_in, inplace ? I->d_in : 0, I->slice_n, C, H, W, mean, std, E->dtype, in_ptr, I->in_val.ld,
+                            q_sub, q_mult, I->stream);
+    else if (E->dtype == THB_U8) {
+        rc = thb_preprocess_images_lowp(I->d_img, I->slice_n, H, W, W * cp, bgr, mean, std, in_ptr, I->in_val.ld, &q_sub,
+                                        &q_mult, I->stream);
+        set_dynamic_quant(I, q_sub, q_mult);
+    } else
+        rc = thb_preprocess_images(I->d_img, I->slice_n, H, W, W * cp, cp, bgr, mean, std, E->dtype, in_ptr,
+                                   I->in_val.ld, I->stream);
+    if (rc) { thb_set_error("preprocess launch failed: %s", thb_last_cuda_error()); return -1; }
+    return 0;
+}
+
+/* The boundary kernel out: the network's last tensor -> NCHW fp32 at `dst`. */
+static int boundary_out(thb_engine *E, instance *I, float *dst)
+{
+    const value *ov = &I->out_val;
+    float inv = ov->q_mult ? (float)(1.0 / ov->q_mult) : 0;
+    if (thb_postprocess(bufptr(I, ov->buf, ov->coff, E->dtype), E->dtype, ov->s.N, ov->s.H, ov->s.W, ov->s.C, ov->ld,
+                        ov->q_sub, inv, dst, I->stream)) { thb_set_error("postprocess launch failed"); return -1; }
+    return 0;
+}
+
+/* Everything one GPU does between its staged input and its NCHW fp32 result, on the instance's stream: the boundary
+ * kernel in, the planned launches, the boundary kernel out.  ev0 marks the start of the planned launches.
+ * `writeback`: host address the normalised input slice is copied back to (THProcessFloat's in-place side effect), or
+ * NULL; `dst`: where the result goes (I->d_out, or this GPU's part of the gathered result). */
+static int device_forward(thb_engine *E, instance *I, int has_x, int inplace, int cp, int bgr, int C, int H, int W,
+                          const float *mean, const float *std, float q_sub, float q_mult, float *writeback, float *dst)
+{
+    if (boundary_in(E, I, has_x, inplace, cp, bgr, C, H, W, mean, std, q_sub, q_mult)) return -1;
+    if (writeback)
+        CU(cudaMemcpyAsync(writeback, I->d_in, (size_t)I->slice_n * C * H * W * sizeof(float), cudaMemcpyDeviceToHost, I->stream));
+    CU(cudaEventRecord(I->ev0, I->stream));
+    if (run_steps(E, I)) return -1;
+    return boundary_out(E, I, dst);
+}
+
 int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stride, int bgr, int cp, int N, int C, int H,
                        int W, int rank, const float *mean, const float *std, int inplace, thb_result *res)
 {
@@ -1379,8 +1499,12 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
         if ((!E->pipe_built || E->pipe_chunks != S) && pipe_build(E, S)) return -1;
         set = E->pipe;
         G = E->pipe_built;
-        peer_gather = 0;
     }
+    /* Peer gather: every GPU's part of the result ends up in GPU 0's result buffer (the first instance's, sized for the
+     * whole batch), which goes to the host in one copy.  Instances on GPU 0 write their part there directly; the others
+     * send theirs with cudaMemcpyPeerAsync on their own stream -- also when a GPU's slice runs as pipelined sub-batches. */
+    float *gather = E->built > 1 && peer_gather ? E->inst[0].d_out : 0;
+    const int dev0 = E->inst[0].device;
     const size_t img_elems = (size_t)C * H * W;
     float q_sub = 0, q_mult = 0;
 
@@ -1397,30 +1521,10 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
                                      (size_t)W * cp, H, cudaMemcpyHostToDevice, I->stream));
         }
     }
-    if (E->dtype == THB_U8) {
-        /* lowp_basic.c:15-29: one range over the WHOLE batch tensor, so slices are reduced on the host */
-        float lo = 0, hi = 0;
-        if (!x) {
-            /* lowp_basic.c:82-131: the image loader quantises straight from the bytes with a static range derived
-             * from mean/std, so nothing has to be measured; the kernel call below reports that range */
-            if (cp != 3) { thb_set_error("the lowp image loader takes 3-plane images"); return -1; }
-            goto lowp_range_done;
-        }
-        for (int g = 0; g < G; g++) {
-            instance *I = &set[g];
-            float mm[2];
-            CU(cudaSetDevice(I->device));
-            if (thb_minmax_normalized(I->d_in, I->slice_n, C, H, W, mean, std, I->d_minmax, I->stream)) return -1;
-            CU(cudaMemcpyAsync(mm, I->d_minmax, sizeof(mm), cudaMemcpyDeviceToHost, I->stream));
-            CU(cudaStreamSynchronize(I->stream));
-            if (mm[0] < lo) lo = mm[0];
-            if (mm[1] > hi) hi = mm[1];
-        }
-        q_sub = lo;
-        q_mult = hi - lo > 0 ? (float)(255.0 / (hi - lo)) : 0;
-        for (int g = 0; g < G; g++) set_dynamic_quant(&set[g], q_sub, q_mult);
-    lowp_range_done:;
-    }
+    if (lowp_input_range(E, set, G, x != 0, cp, C, H, W, mean, std, &q_sub, &q_mult)) return -1;
+    /* what the device-resident timing loop needs to repeat this forward from the staged input */
+    E->last_has_x = x != 0; E->last_cp = cp; E->last_bgr = bgr;
+    for (int k = 0; k < 3; k++) { E->last_mean[k] = mean[k]; E->last_std[k] = std[k]; }
 
     long total = 0;
     for (int g = 0; g < G; g++) total += set[g].out_count;
@@ -1434,53 +1538,25 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
     for (int g = 0; g < G; g++) {
         instance *I = &set[g];
         CU(cudaSetDevice(I->device));
-        int rc;
-        void *in_ptr = bufptr(I, I->in_val.buf, 0, E->dtype);
-        if (x && E->input_s2d && E->dtype == THB_U8)
-            rc = thb_preprocess_s2d_u8(I->d_in, inplace ? I->d_in : 0, I->slice_n, C, H, W, mean, std, in_ptr, I->in_val.ld, q_sub,
-                                       q_mult, I->stream);
-        else if (x && E->input_s2d)
-            rc = thb_preprocess_s2d_padded(I->d_in, inplace ? I->d_in : 0, I->slice_n, C, H, W, mean, std, E->dtype, in_ptr,
-                                           I->in_val.ld, I->in_val.row_pitch ? I->in_val.row_pitch : W / 2,
-                                           I->in_val.pad_left, I->stream);
-        else if (x)
-            rc = thb_preprocess(I->d_in, inplace ? I->d_in : 0, I->slice_n, C, H, W, mean, std, E->dtype, in_ptr, I->in_val.ld,
-                                q_sub, q_mult, I->stream);
-        else if (E->dtype == THB_U8) {
-            rc = thb_preprocess_images_lowp(I->d_img, I->slice_n, H, W, W * cp, bgr, mean, std, in_ptr, I->in_val.ld, &q_sub,
-                                            &q_mult, I->stream);
-            set_dynamic_quant(I, q_sub, q_mult);
-        } else
-            rc = thb_preprocess_images(I->d_img, I->slice_n, H, W, W * cp, cp, bgr, mean, std, E->dtype, in_ptr,
-                                       I->in_val.ld, I->stream);
-        if (rc) { thb_set_error("preprocess launch failed: %s", thb_last_cuda_error()); return -1; }
-        if (x && inplace)
-            CU(cudaMemcpyAsync(x + (size_t)I->slice_off * img_elems, I->d_in, (size_t)I->slice_n * img_elems * sizeof(float),
-                               cudaMemcpyDeviceToHost, I->stream));
-        CU(cudaEventRecord(I->ev0, I->stream));
-        if (run_steps(E, I)) return -1;
-        const value *ov = &I->out_val;
-        float inv = ov->q_mult ? (float)(1.0 / ov->q_mult) : 0;
         long off = 0;
         for (int k = 0; k < g; k++) off += set[k].out_count;
-        float *dst_dev = I->d_out;
-        if (thb_postprocess(bufptr(I, ov->buf, ov->coff, E->dtype), E->dtype, ov->s.N, ov->s.H, ov->s.W, ov->s.C, ov->ld,
-                            ov->q_sub, inv, dst_dev, I->stream)) { thb_set_error("postprocess launch failed"); return -1; }
+        float *dst = gather && I->device == dev0 ? gather + off : I->d_out;
+        if (device_forward(E, I, x != 0, inplace, cp, bgr, C, H, W, mean, std, q_sub, q_mult,
+                           x && inplace ? x + (size_t)I->slice_off * img_elems : 0, dst)) return -1;
         CU(cudaEventRecord(I->ev1, I->stream));
-        if (G > 1 && peer_gather && g > 0) {
-            /* gather by peer copy into GPU 0's result buffer; GPU 0 sends the whole result to the host */
-            CU(cudaMemcpyPeerAsync(set[0].d_out + off, set[0].device, I->d_out, I->device,
-                                   (size_t)I->out_count * sizeof(float), I->stream));
-        } else if (!(G > 1 && peer_gather)) {
+        if (gather) {
+            if (I->device != dev0)
+                CU(cudaMemcpyPeerAsync(gather + off, dev0, I->d_out, I->device, (size_t)I->out_count * sizeof(float), I->stream));
+        } else
             CU(cudaMemcpyAsync(E->h_out + off, I->d_out, (size_t)I->out_count * sizeof(float), cudaMemcpyDeviceToHost, I->stream));
-        }
     }
     float ms_max = 0;
     for (int g = G - 1; g >= 0; g--) {
         instance *I = &set[g];
         CU(cudaSetDevice(I->device));
-        if (g == 0 && G > 1 && peer_gather)
-            CU(cudaMemcpyAsync(E->h_out, I->d_out, (size_t)total * sizeof(float), cudaMemcpyDeviceToHost, I->stream));
+        /* every other stream has been waited for by now: the gathered result is complete */
+        if (g == 0 && gather)
+            CU(cudaMemcpyAsync(E->h_out, gather, (size_t)total * sizeof(float), cudaMemcpyDeviceToHost, I->stream));
         CU(cudaStreamSynchronize(I->stream));
         float ms = 0;
         cudaEventElapsedTime(&ms, I->ev0, I->ev1);
@@ -1518,28 +1594,43 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
 
 float thb_engine_last_ms(thb_engine *E) { return E ? E->last_ms : -1.f; }
 
-/* Device-resident timing loop: the planned launches only (input already staged and preprocessed by the last
- * forward), `iters` times back to back per GPU, timed with events on the launching stream; max over GPUs. */
+/* Device-resident timing loop: the whole forward from the batch staged in device memory by the last THProcess* call
+ * (NCHW fp32 or HWC bytes) to the NCHW fp32 result in device memory -- boundary kernels, the uint8 engine's input
+ * range (with its 8-byte read-back) and the planned launches -- `iters` times back to back per GPU, timed with events
+ * on the launching stream; max over GPUs.  No host<->device copy of the batch or the result is inside. */
 float thb_engine_time_forward(thb_engine *E, int iters)
 {
-    if (!E || !E->built || iters < 1) return -1.f;
+    if (!E || !E->built || iters < 1 || (!E->last_has_x && !E->last_cp)) return -1.f;
     const int G = E->built;
+    cudaEvent_t t0[8], t1[8];
     for (int g = 0; g < G; g++) {
-        instance *I = &E->inst[g];
-        if (cudaSetDevice(I->device) != cudaSuccess) return -1.f;
-        cudaEventRecord(I->ev0, I->stream);
-        for (int it = 0; it < iters; it++)
-            if (run_steps(E, I)) return -1.f;
-        cudaEventRecord(I->ev1, I->stream);
+        if (cudaSetDevice(E->inst[g].device) != cudaSuccess) return -1.f;
+        cudaEventCreate(&t0[g]);
+        cudaEventCreate(&t1[g]);
+        cudaEventRecord(t0[g], E->inst[g].stream);
+    }
+    int rc = 0;
+    for (int it = 0; it < iters && !rc; it++) {
+        float q_sub = 0, q_mult = 0;
+        rc = lowp_input_range(E, E->inst, G, E->last_has_x, E->last_cp, E->C, E->H, E->W, E->last_mean, E->last_std, &q_sub, &q_mult);
+        for (int g = 0; g < G && !rc; g++) {
+            instance *I = &E->inst[g];
+            if (cudaSetDevice(I->device) != cudaSuccess) rc = -1;
+            else rc = device_forward(E, I, E->last_has_x, 0, E->last_cp, E->last_bgr, E->C, E->H, E->W, E->last_mean, E->last_std,
+                                     q_sub, q_mult, 0, I->d_out);
+        }
     }
     float worst = 0;
     for (int g = 0; g < G; g++) {
         instance *I = &E->inst[g];
         cudaSetDevice(I->device);
-        if (cudaStreamSynchronize(I->stream) != cudaSuccess) return -1.f;
+        cudaEventRecord(t1[g], I->stream);
+        if (cudaStreamSynchronize(I->stream) != cudaSuccess) rc = -1;
         float ms = 0;
-        cudaEventElapsedTime(&ms, I->ev0, I->ev1);
+        if (!rc) cudaEventElapsedTime(&ms, t0[g], t1[g]);
         if (ms > worst) worst = ms;
+        cudaEventDestroy(t0[g]);
+        cudaEventDestroy(t1[g]);
     }
-    return worst / iters;
+    return rc ? -1.f : worst / iters;
 }

@@ -23,66 +23,56 @@
 /* THB_STATIC_CSUM_MAX_PIXELS (thb200_kernels.h) = 1048576 entries: 4 MiB of int32, e.g. 20 images of 224x224 */
 static __device__ __align__(256) int g_csum_scratch[THB_STATIC_CSUM_MAX_PIXELS];
 
+extern "C" int thb_conv_fwd(const thb_conv_desc *d, const void *x, void *y, thb_stream s);
+extern "C" int thb_u8_channel_sum(const void *x, long pixels, int C, int x_ld, int *csum, thb_stream s);
+
 namespace {
 
 #define THB_MAX_DEVICES 64
 int *g_scratch_addr[THB_MAX_DEVICES]; /* device address of g_csum_scratch, per device ordinal; NULL = not looked up yet */
 
-// per input pixel: sum of its first C bytes, written to the static array
-__global__ void u8_channel_sum_static_kernel(const uint8_t *__restrict__ x, int pixels, int C, int x_ld)
+int refuse(int code, const char *why)
 {
-    const int pix = blockIdx.x * blockDim.x + threadIdx.x;
-    if (pix >= pixels) return;
-    const uint4 *p = reinterpret_cast<const uint4 *>(x + (size_t)pix * x_ld);
-    int s = 0;
-    for (int c0 = 0; c0 < C; c0 += 16) {
-        const uint4 t = p[c0 >> 4];
-        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-        for (int i = 0; i < 16; i++)
-            if (c0 + i < C) s += (w[i >> 2] >> ((i & 3) * 8)) & 0xff;
-    }
-    g_csum_scratch[pix] = s;
+    thb_note_launch(cudaErrorInvalidValue, why);
+    return code;
 }
-
-int fail(cudaError_t e, const char *what) { return thb_note_launch(e, what); }
 
 }  // namespace
 
 extern "C" int thb_conv_u8_fwd_static(const thb_conv_desc *d, const void *x, void *y, thb_stream s)
 {
+    // Everything is checked before the first launch: the channel-sum kernels read whole 16-byte vectors of every pixel,
+    // so a descriptor they cannot digest must come back as an error code, not as a device fault.
     if (!d || !x || !y) return THB_ERR_ARG;
-    if (d->dtype != THB_U8) {
-        fail(cudaErrorInvalidValue, "thb_conv_u8_fwd_static: descriptor dtype is not THB_U8");
-        return THB_ERR_ARG;
-    }
+    if (d->dtype != THB_U8) return refuse(THB_ERR_ARG, "thb_conv_u8_fwd_static: descriptor dtype is not THB_U8");
+    if (d->N < 1 || d->H < 1 || d->W < 1 || d->Cin < 1 || d->Cout < 1)
+        return refuse(THB_ERR_ARG, "thb_conv_u8_fwd_static: N, H, W, Cin and Cout must be positive");
+    if (d->in_ld % 16 || d->in_ld < ((d->Cin + 15) & ~15) || (reinterpret_cast<uintptr_t>(x) & 15))
+        return refuse(THB_ERR_ARG, "thb_conv_u8_fwd_static: input needs a 16-byte aligned base and in_ld = multiple of 16 >= Cin rounded up to 16");
+    if (!d->w || !d->kinfo || !d->tmap || !d->wsat || !d->status)
+        return refuse(THB_ERR_ARG, "thb_conv_u8_fwd_static: w, kinfo, tmap, wsat and status must be set");
+    // Rows stored with their horizontal padding are not summed here: the sums are indexed densely as [n][H][W].
+    if (d->in_row_pitch) return refuse(THB_ERR_UNSUPPORTED, "thb_conv_u8_fwd_static: in_row_pitch (rows stored with padding) is not supported");
     const long long pixels = (long long)d->N * d->H * d->W;
-    if (pixels < 0 || pixels > THB_STATIC_CSUM_MAX_PIXELS) {
+    if (pixels > THB_STATIC_CSUM_MAX_PIXELS) {
         char msg[160];
         snprintf(msg, sizeof(msg), "thb_conv_u8_fwd_static: N*H*W = %lld input pixels exceeds the static scratch of %d",
                  pixels, THB_STATIC_CSUM_MAX_PIXELS);
-        fail(cudaErrorInvalidValue, msg);
-        return THB_ERR_ARG;
+        return refuse(THB_ERR_ARG, msg);
     }
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return fail(e, "thb_conv_u8_fwd_static: cudaGetDevice");
-    if (dev < 0 || dev >= THB_MAX_DEVICES) {
-        fail(cudaErrorInvalidDevice, "thb_conv_u8_fwd_static: device ordinal beyond the address cache");
-        return THB_ERR_ARG;
-    }
+    if (e != cudaSuccess) return thb_note_launch(e, "thb_conv_u8_fwd_static: cudaGetDevice");
+    if (dev < 0 || dev >= THB_MAX_DEVICES) return refuse(THB_ERR_ARG, "thb_conv_u8_fwd_static: device ordinal beyond the address cache");
     int *scratch = g_scratch_addr[dev];
     if (!scratch) {
         e = cudaGetSymbolAddress((void **)&scratch, g_csum_scratch);
-        if (e != cudaSuccess) return fail(e, "thb_conv_u8_fwd_static: cudaGetSymbolAddress(g_csum_scratch)");
-        if (!scratch) return fail(cudaErrorInvalidSymbol, "thb_conv_u8_fwd_static: g_csum_scratch has no device address");
+        if (e != cudaSuccess) return thb_note_launch(e, "thb_conv_u8_fwd_static: cudaGetSymbolAddress(g_csum_scratch)");
+        if (!scratch) return thb_note_launch(cudaErrorInvalidSymbol, "thb_conv_u8_fwd_static: g_csum_scratch has no device address");
         g_scratch_addr[dev] = scratch;
     }
-    if (pixels == 0) return THB_OK;
-    const int threads = 256;
-    u8_channel_sum_static_kernel<<<(unsigned)((pixels + threads - 1) / threads), threads, 0, (cudaStream_t)s>>>(
-        (const uint8_t *)x, (int)pixels, d->Cin, d->in_ld);
-    int rc = THB_LAUNCH_CHECK("u8_channel_sum_static_kernel");
+    // the same channel-sum kernels as the ordinary route, writing into the static array (no allocation on either)
+    int rc = thb_u8_channel_sum(x, (long)pixels, d->Cin, d->in_ld, scratch, s);
     if (rc) return rc;
     thb_conv_desc local = *d;
     local.csum = scratch;

@@ -50,6 +50,22 @@ class Ranks:
         self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
         return float(t.item())
 
+    def host_signal(self, key: str):
+        """Set a key in the rendezvous store: a message to ranks blocked in host_wait.  No GPU work is involved, so a
+        rank can wait for another one while its GPU stays idle (a collective would park a kernel on it)."""
+        if self.dist is not None:
+            self._store().set(key, "1")
+
+    def host_wait(self, key: str, timeout_s: float = 900.0):
+        """Block on the host until some rank has set `key`."""
+        if self.dist is not None:
+            import datetime
+            self._store().wait([key], datetime.timedelta(seconds=timeout_s))
+
+    def _store(self):
+        from torch.distributed import distributed_c10d
+        return distributed_c10d._get_default_store()
+
     def shard(self, total: int):
         """contiguous slice [offset, offset+count) of `total` units for this rank; remainder to the lowest ranks"""
         base, extra = divmod(total, self.world)
