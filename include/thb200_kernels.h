@@ -122,6 +122,17 @@ int thb_conv_pack_weights_host(const thb_conv_desc *d, const float *w_oihw, cons
 int thb_conv_make_tmap(const thb_conv_desc *d, thb_tmap *out);
 int thb_conv_fwd(const thb_conv_desc *d, const void *x, void *y, thb_stream s);
 
+/* Convolution + epilogue as above (no residual) + max pooling with a pk x pk window (2 or 3), stride 2 and padding ppad
+ * in ONE launch: the convolution's own output is never written, only the [N][pH][pW][y_ld] pooled tensor.  Replaces
+ * nn_SpatialConvolutionMM_updateOutput followed by nn_SpatialMaxPooling_updateOutput (modules/SpatialMaxPooling.c:168-247:
+ * windows clipped to the image, maximum from the smallest value).  F16 / BF16, Cout <= 64 with BN = 64, stride-1
+ * convolution whose K blocks are whole 128-byte channel slabs (Cin_pad a multiple of 64) or, with d->in_row_pitch, whole
+ * kernel rows.  pH, pW: the pooled size the caller derived (every window must start inside the convolution output).
+ * thb_conv_maxpool_supported answers whether a descriptor qualifies (THB200_NO_CONV_POOL=1 makes it answer 0). */
+int thb_conv_maxpool_supported(const thb_conv_desc *d, int pk, int ps, int ppad);
+int thb_conv_maxpool_fwd(const thb_conv_desc *d, int pk, int ps, int ppad, int pH, int pW, const void *x, void *y, int y_ld,
+                         thb_stream s);
+
 /* Batch-small Linear: y[n][m] = sum_k W[m][k]*x[n][k] (+ epilogue as above), N <= 8, weights read once.
  * Replaces nn_Linear_updateOutput's addmv path (modules/Linear.c:86-90, OpenBLAS-stripped/sgemv.c:48-105). */
 int thb_gemv_fwd(int dtype, const void *x, int N, int K, int x_ld, const void *w /*[M][K]*/, int M,

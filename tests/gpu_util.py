@@ -120,6 +120,22 @@ class Conv:
         return y
 
 
+    def run_pooled(self, x_t, pk, ppad, ph, pw, fill=None):
+        """the convolution and the pk x pk / stride 2 max pooling after it in one launch (thb_conv_maxpool_fwd)"""
+        d = self.d
+        y = torch.zeros((d.N, ph, pw, d.out_ld), dtype=_TORCH[self.dtype], device="cuda")
+        if fill is not None:
+            y.fill_(fill)
+        self.lib.thb_conv_maxpool_fwd.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                                  C.c_void_p, C.c_int, C.c_void_p]
+        rc = self.lib.thb_conv_maxpool_fwd(C.byref(d), pk, 2, ppad, ph, pw, ptr(x_t), ptr(y), d.out_ld, None)
+        torch.cuda.synchronize()
+        assert rc == 0, (rc, self.lib.thb_last_cuda_error())
+        status = int(self.keep[3].cpu()[0])
+        assert status == 0, f"kernel status word = {status} (a bounded wait gave up)"
+        return y
+
+
 def rel_err(a, ref):
     a = np.asarray(a, np.float64)
     ref = np.asarray(ref, np.float64)

@@ -110,7 +110,7 @@ def test_conv_f16_two_operands_many_tiles(lib, G, oracle, geom):
     ref = oracle.conv2d(x1, w1, None, (1, 1), (0, 0)) + oracle.conv2d(x2, w2_, None, (d2, d2), (0, 0)) + shift.reshape(1, -1, 1, 1)
     ref = np.maximum(ref, 0)
     conv = G.Conv(lib, K.THB_F16, (n, c1 + c2, oh, ow), np.concatenate([w1, w2_], axis=1))
-    assert _units(lib, conv) > 3 * SMS
+    assert _units(lib, conv) > 2 * SMS
     conv.set_affine(None, shift)
     conv.set_act(K.ACT_THRESHOLD, 0.0, 0.0)
     d = conv.d
@@ -145,6 +145,34 @@ def test_conv_f16_stem_rows_stored_with_padding_many_tiles(lib, G, oracle):
     d.in_row_pitch, d.in_pad_left = pitch, p
     for launch in range(2):
         err = G.rel_err(G.from_nhwc(conv.run(xt, fill=3.0), cout), ref)
+        assert err < 1e-2, (launch, err)
+
+
+def test_stem_and_max_pooling_in_one_launch_many_tiles(lib, G, oracle):
+    """The ResNet stem (after the space-to-depth rewrite) + bias + ReLU + 3x3/s2/p1 max pooling as ONE launch
+    (thb_conv_maxpool_fwd) at batch 6: 336 pooled tiles on 148 CTAs, every CTA walks two or three."""
+    case = (6, 12, 112, 112, 64, 4, 1, 2, False)
+    n, cin, h, w, cout, k, s, p, _ = case
+    rng, x, wt = _inputs(case, 109)
+    shift = (rng.standard_normal(cout) * 0.2).astype(np.float32)
+    y0 = np.maximum(oracle.conv2d(x, wt, shift, (s, s), (p, p))[:, :, :-1, :-1], 0)
+    ref = oracle.maxpool(np.ascontiguousarray(y0), (3, 3), (2, 2), (1, 1), 0)
+    conv = G.Conv(lib, K.THB_F16, x.shape, wt, (s, s), (p, p), bn_tile=64)
+    conv.set_affine(None, shift)
+    conv.set_act(K.ACT_THRESHOLD)
+    d = conv.d
+    d.oH, d.oW = y0.shape[2], y0.shape[3]
+    pitch = (p + w + (k - 1 - p) + 3) & ~3
+    buf = np.zeros((n, h, pitch, d.in_ld), np.float32)
+    buf[:, :, p:p + w, :cin] = np.transpose(x, (0, 2, 3, 1))
+    xt = torch.from_numpy(buf).cuda().half()
+    d.in_row_pitch, d.in_pad_left = pitch, p
+    lib.thb_conv_maxpool_supported.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
+    if lib.thb_conv_maxpool_supported(C.byref(d), 3, 2, 1) != 1:
+        pytest.skip("the driver refuses the overlapping-window descriptor; the planner then keeps the two launches")
+    assert ref.shape[2:] == (56, 56)
+    for launch in range(2):
+        err = G.rel_err(G.from_nhwc(conv.run_pooled(xt, 3, 1, 56, 56, fill=3.0), cout), ref)
         assert err < 1e-2, (launch, err)
 
 

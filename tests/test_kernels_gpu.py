@@ -206,6 +206,72 @@ def test_conv_fused_epilogue(lib, G, oracle, dtype):
     assert G.rel_err(G.from_nhwc(conv.run(xt), cout), oracle.threshold(base, 0.5, -1.0)) < TOL[dtype]
 
 
+@pytest.mark.parametrize("pool", [(3, 1, 0), (2, 0, 0), (3, 0, 1), (2, 0, 1)], ids=["3s2p1", "2s2", "3s2ceil", "2s2ceil"])
+@pytest.mark.parametrize("case", [(2, 64, 20, 24, 40, 3, 1, 1), (3, 128, 17, 15, 64, 3, 1, 1), (1, 64, 33, 37, 24, 5, 1, 2),
+                                  (2, 64, 9, 9, 64, 1, 1, 0)])
+def test_conv_maxpool_fused(lib, G, oracle, case, pool):
+    """Convolution + bias + ReLU + stride-2 max pooling in one launch (thb_conv_maxpool_fwd) against the oracle's
+    convolution, Threshold and SpatialMaxPooling (windows clipped to the image, ceil and floor output sizes): maps that
+    are not multiples of the pooled tile, several tiles per image, channels below 64."""
+    n, cin, h, w, cout, k, s, p = case
+    pk, ppad, ceil_mode = pool
+    x, wt = _conv_inputs(case, 41, True)
+    rng = np.random.default_rng(42)
+    scale = rng.uniform(0.5, 1.5, cout).astype(np.float32)
+    shift = rng.standard_normal(cout).astype(np.float32)
+    y0 = np.maximum(oracle.conv2d(x, wt, None, (s, s), (p, p)) * scale[None, :, None, None] + shift[None, :, None, None], 0)
+    ref = oracle.maxpool(y0, (pk, pk), (2, 2), (ppad, ppad), ceil_mode)
+    conv = G.Conv(lib, K.THB_F16, x.shape, wt, (s, s), (p, p), bn_tile=64)
+    conv.set_affine(scale, shift)
+    conv.set_act(K.ACT_THRESHOLD)
+    lib.thb_conv_maxpool_supported.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
+    assert lib.thb_conv_maxpool_supported(C.byref(conv.d), pk, 2, ppad) == 1
+    xt, _ = G.to_nhwc(x, K.THB_F16)
+    y = conv.run_pooled(xt, pk, ppad, ref.shape[2], ref.shape[3], fill=9.0)
+    assert G.rel_err(G.from_nhwc(y, cout), ref) < 1e-2, (case, pool, G.rel_err(G.from_nhwc(y, cout), ref))
+    pad = y[..., cout:G.ru(cout, 8)]
+    assert pad.numel() == 0 or float(pad.float().abs().max()) == 0.0
+    # bit-identical to the two launches it replaces
+    two = torch.zeros_like(y)
+    assert lib.thb_maxpool(K.THB_F16, G.ptr(conv.run(xt)), n, y0.shape[2], y0.shape[3], cout, conv.d.out_ld, pk, pk, 2, 2, ppad, ppad,
+                           ref.shape[2], ref.shape[3], G.ptr(two), conv.d.out_ld, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(y[..., :cout], two[..., :cout])
+
+
+@pytest.mark.parametrize("prelu", [False, True])
+def test_conv_maxpool_fused_rows_stored_with_padding(lib, G, oracle, prelu):
+    """The same through the kernel-row-per-copy path of a space-to-depth first layer (input rows stored with their
+    zero padding, thb_conv_desc.in_row_pitch), cropped output as the stride-2 rewrite produces, then 3x3/s2/p1 pooling."""
+    case = (3, 12, 21, 19, 56, 4, 1, 2)
+    n, cin, h, w, cout, k, s, p = case
+    x, wt = _conv_inputs(case, 43, True)
+    rng = np.random.default_rng(44)
+    shift = rng.standard_normal(cout).astype(np.float32)
+    slope = rng.uniform(0.1, 0.3, cout).astype(np.float32)
+    y0 = oracle.conv2d(x, wt, shift, (s, s), (p, p))[:, :, :-1, :-1]
+    y0 = oracle.prelu(np.ascontiguousarray(y0), slope, cout) if prelu else np.maximum(y0, 0)
+    ref = oracle.maxpool(np.ascontiguousarray(y0), (3, 3), (2, 2), (1, 1), 0)
+    conv = G.Conv(lib, K.THB_F16, x.shape, wt, (s, s), (p, p), bn_tile=64)
+    conv.set_affine(None, shift)
+    if prelu:
+        conv.set_act(K.ACT_PRELU, slope=slope)
+    else:
+        conv.set_act(K.ACT_THRESHOLD)
+    d = conv.d
+    d.oH, d.oW = y0.shape[2], y0.shape[3]
+    pitch = (p + w + (k - 1 - p) + 3) & ~3
+    buf = np.zeros((n, h, pitch, d.in_ld), np.float32)
+    buf[:, :, p:p + w, :cin] = np.transpose(x, (0, 2, 3, 1))
+    xt = torch.from_numpy(buf).cuda().half()
+    d.in_row_pitch, d.in_pad_left = pitch, p
+    lib.thb_conv_maxpool_supported.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
+    if lib.thb_conv_maxpool_supported(C.byref(d), 3, 2, 1) != 1:
+        pytest.skip("the driver refuses the overlapping-window descriptor; the planner then keeps the two launches")
+    y = conv.run_pooled(xt, 3, 1, ref.shape[2], ref.shape[3], fill=4.0)
+    assert G.rel_err(G.from_nhwc(y, cout), ref) < 1e-2
+
+
 @pytest.mark.parametrize("dtype", [K.THB_F32, K.THB_F16])
 def test_conv_strided_views(lib, G, oracle, dtype):
     """Input read from, and output written into, channel slices of wider buffers."""

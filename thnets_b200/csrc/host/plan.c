@@ -99,6 +99,7 @@ typedef struct {
     float w_sub, w_mult, out_sub, out_mult;
     int flops_node; /* model node index of the conv (profiling) */
     int dual;       /* convolution with a second activation operand (in_buf[1]) instead of a residual */
+    int pool_k, pool_pad, pool_oH, pool_oW; /* pool_k > 0: the max pooling that follows runs inside the convolution launch */
     double flops_extra; /* FLOPs of the second convolution computed by the same launch */
 } step;
 
@@ -412,6 +413,15 @@ static int plan_gemm_group(planner *P, int i)
         (dtype != THB_U8 || M->nodes[j].act_kind == THB_ACT_THRESHOLD)) { act = j; cur = j; }
     for (int k = i + 1; k <= cur; k++)
         if (k == bn || k == comb || k == act || k == dual_conv || k == dual_bn) { P->absorbed[k] = 1; P->leader[k] = i; }
+    /* A stride-2 max pooling as the only consumer of this convolution (after its batch-norm and activation) can run
+     * inside the convolution's launch, which then stores the pooled tensor only: decided below, once the kernel
+     * geometry is known (16-bit types, at most 64 output channels, stride-1 convolution). */
+    int pool = -1;
+    if ((dtype == THB_F16 || dtype == THB_BF16) && !is_linear && !is_deconv && comb < 0 && dual_conv < 0 && n->Cout <= 64 &&
+        (j = sole_consumer(P, cur)) >= 0 && M->nodes[j].op == OP_MAXPOOL) {
+        const thb_node *pn = &M->nodes[j];
+        if (pn->kH == pn->kW && pn->dH == 2 && pn->dW == 2 && pn->padH == pn->padW) pool = j;
+    }
 
     /* ---- per-channel scale / shift ---- */
     float *scale = 0, *shift = 0;
@@ -574,7 +584,13 @@ static int plan_gemm_group(planner *P, int i)
         d->cin1 = c1n;
         d->x2_ld = v2->ld; d->x2_H = v2->s.H; d->x2_W = v2->s.W; d->x2_d = c2->dH;
     }
+    if (pool >= 0) d->BN = 64;
     if (thb_conv_geometry(d)) { free(w_tmp); thb_set_error("unsupported convolution geometry %dx%d", kH, kW); return -1; }
+    if (pool >= 0 && !thb_conv_maxpool_supported(d, M->nodes[pool].kH, 2, M->nodes[pool].padH)) {
+        pool = -1;
+        d->BN = 0;
+        thb_conv_geometry(d);
+    }
     if (dual_conv < 0 && in_ld < d->Cin_pad) { free(w_tmp); thb_set_error("internal: input stride %d below padded channels %d", in_ld, d->Cin_pad); return -1; }
 
     size_t wbytes = thb_conv_weight_bytes(d), kwords = thb_conv_kinfo_words(d);
@@ -686,10 +702,25 @@ static int plan_gemm_group(planner *P, int i)
         if (act >= 0 && fill_act(P, &g->act, &M->nodes[act], n->Cout)) return -1;
         return cur;
     }
+    if (pool >= 0) {
+        const thb_node *pn = &M->nodes[pool];
+        shape ps = os;
+        ps.H = pool_out(os.H, pn->kH, 2, pn->padH, pn->ceil_mode, pn->padH || pn->padW);
+        ps.W = pool_out(os.W, pn->kW, 2, pn->padW, pn->ceil_mode, pn->padH || pn->padW);
+        if (ps.H < 1 || ps.W < 1) { thb_set_error("input image smaller than kernel size"); return -1; }
+        P->absorbed[pool] = 1;
+        P->leader[pool] = i;
+        out = &P->val[pool];
+        os = ps;
+        cur = pool;
+    }
     materialise(P, out, os);
     s = &P->I->steps[P->I->nsteps - 1];
     step_out(s, out);
     s->conv.out_ld = out->ld;
+    if (pool >= 0) {
+        s->pool_k = M->nodes[pool].kH; s->pool_pad = M->nodes[pool].padH; s->pool_oH = os.H; s->pool_oW = os.W;
+    }
     return cur;
 }
 
@@ -1083,7 +1114,8 @@ static int run_steps_ev(thb_engine *E, instance *I, cudaEvent_t *evs)
             else if (s->nin > 1) d->res = bufptr(I, s->in_buf[1], s->in_coff[1], dt);
             if (s->aux_buf >= 0) d->csum = (const int *)bufptr(I, s->aux_buf, 0, THB_U8);
             if (s->aux2_buf >= 0) d->csum_out = (int *)bufptr(I, s->aux2_buf, 0, THB_U8);
-            rc = thb_conv_fwd(d, x0, y, st);
+            rc = s->pool_k ? thb_conv_maxpool_fwd(d, s->pool_k, 2, s->pool_pad, s->pool_oH, s->pool_oW, x0, y, s->out_ld, st)
+                           : thb_conv_fwd(d, x0, y, st);
             break;
         }
         case ST_GEMV:
@@ -1253,7 +1285,7 @@ int thb_engine_profile_bytes(thb_engine *E, int max_steps, double *bytes)
         const double el = s->dtype == THB_F32 ? 4 : s->dtype == THB_U8 ? 1 : 2;
         if (s->kind == ST_CONV) {
             const thb_conv_desc *d = &s->conv;
-            const double out = (double)d->N * d->oH * d->oW * d->Cout;
+            const double out = s->pool_k ? (double)d->N * s->pool_oH * s->pool_oW * d->Cout : (double)d->N * d->oH * d->oW * d->Cout;
             const double in_elems = s->dual ? (double)d->N * d->H * d->W * d->cin1 + (double)d->N * d->x2_H * d->x2_W * (d->Cin - d->cin1)
                                             : (double)d->N * d->H * d->W * d->Cin;
             bytes[t] = el * (in_elems + out * (d->res ? 2 : 1) + (double)d->Cout * d->Cin * d->kH * d->kW);
