@@ -126,12 +126,18 @@ int thb_conv_fwd(const thb_conv_desc *d, const void *x, void *y, thb_stream s);
  * in ONE launch: the convolution's own output is never written, only the [N][pH][pW][y_ld] pooled tensor.  Replaces
  * nn_SpatialConvolutionMM_updateOutput followed by nn_SpatialMaxPooling_updateOutput (modules/SpatialMaxPooling.c:168-247:
  * windows clipped to the image, maximum from the smallest value).  F16 / BF16, Cout <= 64 with BN = 64, stride-1
- * convolution whose K blocks are whole 128-byte channel slabs (Cin_pad a multiple of 64) or, with d->in_row_pitch, whole
- * kernel rows.  pH, pW: the pooled size the caller derived (every window must start inside the convolution output).
+ * convolution on 16 or 64 (padded) input channels with a kernel of at most 8 x 8.  pH, pW: the pooled size the caller
+ * derived (every window must start inside the convolution output).
  * thb_conv_maxpool_supported answers whether a descriptor qualifies (THB200_NO_CONV_POOL=1 makes it answer 0). */
 int thb_conv_maxpool_supported(const thb_conv_desc *d, int pk, int ps, int ppad);
 int thb_conv_maxpool_fwd(const thb_conv_desc *d, int pk, int ps, int ppad, int pH, int pW, const void *x, void *y, int y_ld,
                          thb_stream s);
+
+/* The patch kernel behind both: thb_conv_fwd itself takes this route for the same class of convolutions (kernel larger
+ * than 1 x 1, no residual) -- the raw input patch of a rectangle of outputs is loaded once and every tap reads it in place.
+ * THB200_NO_PATCH=1 switches the route off. */
+int thb_conv_patch_supported(const thb_conv_desc *d);
+int thb_conv_patch_fwd(const thb_conv_desc *d, const void *x, void *y, thb_stream s);
 
 /* Batch-small Linear: y[n][m] = sum_k W[m][k]*x[n][k] (+ epilogue as above), N <= 8, weights read once.
  * Replaces nn_Linear_updateOutput's addmv path (modules/Linear.c:86-90, OpenBLAS-stripped/sgemv.c:48-105). */

@@ -206,6 +206,30 @@ def test_conv_fused_epilogue(lib, G, oracle, dtype):
     assert G.rel_err(G.from_nhwc(conv.run(xt), cout), oracle.threshold(base, 0.5, -1.0)) < TOL[dtype]
 
 
+@pytest.mark.parametrize("case", [(2, 64, 20, 24, 64, 3, 1, 1), (3, 64, 9, 7, 24, 3, 1, 0), (1, 64, 57, 61, 40, 3, 1, 1), (2, 64, 30, 18, 64, 2, 1, 1),
+                                  (2, 16, 21, 19, 56, 4, 1, 2), (3, 12, 15, 33, 64, 5, 1, 2), (1, 16, 40, 40, 48, 3, 1, 1),
+                                  (2, 64, 5, 300, 64, 3, 1, 1), (2, 16, 300, 6, 64, 3, 1, 1)])
+def test_conv_patch_path(lib, G, oracle, case):
+    """Stride-1 convolutions on 16 or 64 channels per pixel with at most 64 output channels take the patch kernel (one raw
+    input patch per unit, every tap reads it in place): maps narrower and wider than a patch row, odd sizes, every
+    padding, Cout below 64, several patches per image.  The descriptor must qualify, so a silent fall-back cannot pass."""
+    n, cin, h, w, cout, k, s, p = case
+    x, wt = _conv_inputs(case, 51, True)
+    rng = np.random.default_rng(52)
+    scale = rng.uniform(0.5, 1.5, cout).astype(np.float32)
+    shift = rng.standard_normal(cout).astype(np.float32)
+    ref = oracle.conv2d(x, wt, None, (s, s), (p, p)) * scale[None, :, None, None] + shift[None, :, None, None]
+    conv = G.Conv(lib, K.THB_F16, x.shape, wt, (s, s), (p, p), bn_tile=64)
+    conv.set_affine(scale, shift)
+    lib.thb_conv_patch_supported.argtypes = [C.c_void_p]
+    assert lib.thb_conv_patch_supported(C.byref(conv.d)) == 1, "the case must qualify for the patch kernel"
+    xt, _ = G.to_nhwc(x, K.THB_F16)
+    y = conv.run(xt, fill=7.0)
+    assert G.rel_err(G.from_nhwc(y, cout), ref) < 1e-2, (case, G.rel_err(G.from_nhwc(y, cout), ref))
+    pad = y[..., cout:G.ru(cout, 8)]
+    assert pad.numel() == 0 or float(pad.float().abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("pool", [(3, 1, 0), (2, 0, 0), (3, 0, 1), (2, 0, 1)], ids=["3s2p1", "2s2", "3s2ceil", "2s2ceil"])
 @pytest.mark.parametrize("case", [(2, 64, 20, 24, 40, 3, 1, 1), (3, 128, 17, 15, 64, 3, 1, 1), (1, 64, 33, 37, 24, 5, 1, 2),
                                   (2, 64, 9, 9, 64, 1, 1, 0)])

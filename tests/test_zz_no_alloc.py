@@ -120,11 +120,12 @@ def test_static_scratch_channel_counts_and_capacity(lib, case):
 def test_static_scratch_refuses_oversized_inputs(lib):
     d = K.ConvDesc()
     d.dtype = K.THB_U8
-    d.N, d.H, d.W, d.Cin = 64, 512, 512, 16          # 16.8M pixels > the array's 1M entries
+    d.N, d.H, d.W, d.Cin, d.Cout, d.in_ld = 64, 512, 512, 16, 16, 16          # 16.8M pixels > the array's 1M entries
+    d.w = d.kinfo = d.tmap = d.wsat = d.status = 1 << 20                     # (never dereferenced: the call is refused first)
     dummy = torch.zeros(16, dtype=torch.uint8, device="cuda")
     rc = lib.thb_conv_u8_fwd_static(C.byref(d), C.c_void_p(dummy.data_ptr()), C.c_void_p(dummy.data_ptr()), None)
     assert rc == -4                                   # THB_ERR_ARG
-    assert b"exceeds the static scratch" in lib.thb_last_cuda_error()
+    assert b"exceeds the static scratch" in lib.thb_last_cuda_error()  # (a complete descriptor otherwise: the size check is what refuses)
     d.dtype = K.THB_F16
     d.N = 1
     assert lib.thb_conv_u8_fwd_static(C.byref(d), C.c_void_p(dummy.data_ptr()), C.c_void_p(dummy.data_ptr()), None) == -4

@@ -8,6 +8,8 @@
 
 extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, thb_stream s);
 extern "C" int thb_conv_fwd_simt(const thb_conv_desc *d, const void *x, void *y, thb_stream s);
+extern "C" int thb_conv_patch_supported(const thb_conv_desc *d);
+extern "C" int thb_conv_patch_fwd(const thb_conv_desc *d, const void *x, void *y, thb_stream s);
 
 static char g_last_error[256] = "";
 static int g_launches = 0;
@@ -147,5 +149,8 @@ extern "C" int thb_conv_fwd(const thb_conv_desc *d, const void *x, void *y, thb_
         if (d->in_pad_left != d->padW || d->in_row_pitch < d->W + d->kW - 1) return THB_ERR_ARG;
     }
     if (d->dtype == THB_F32) return thb_conv_fwd_simt(d, x, y, s);
+    // stride-1 layers with 16 or 64 channels per pixel and a kernel larger than 1x1: the raw input patch is loaded once
+    // and every tap reads it in place (conv_patch_tc.cu)
+    if (d->kH * d->kW > 1 && thb_conv_patch_supported(d)) return thb_conv_patch_fwd(d, x, y, s);
     return thb_conv_fwd_tc(d, x, y, s);
 }
