@@ -221,6 +221,8 @@ int thb_to_nchw(int dtype, const void *x, int N, int H, int W, int C, int x_ld, 
 #define THB_STATIC_CSUM_MAX_PIXELS 1048576
 int thb_conv_u8_fwd_static(const thb_conv_desc *d, const void *x, void *y, thb_stream s);
 
+/* the launchers read their diagnostic THB200_* environment switches once; this re-reads them */
+void thb_conv_reload_knobs(void);
 const char *thb_last_cuda_error(void);
 int thb_kernel_launch_count(void); /* launches issued through this ABI since load (bench bookkeeping) */
 void thb_count_launches(int n);    /* add launches that were replayed from a captured graph of calls to this ABI */

@@ -27,7 +27,7 @@
 
 namespace {
 
-constexpr int PT_THREADS = 320;
+constexpr int PT_THREADS = 640;        // warps: 0 copy producer, 1-2 MMA issuers, 3 idle, 4-19 epilogue
 constexpr int PT_MAX_STAGES = 4;
 constexpr int PT_CT_BYTES = 256 * 128;  // activated outputs of one patch, one 128-byte row each
 constexpr int PT_PT_BYTES = 64 * 128;   // pooled tile (at most 64 pooled pixels)
@@ -42,13 +42,16 @@ struct PatchParams {
     int xoff;               // zero pixels stored in front of each input row
     int stage_bytes, nst;   // raw patch buffers
     int w_bytes;            // resident weights: kH*kW tiles of 64 rows x px_bytes
+    int ct_bufs;            // output tiles without pooling: 2, or 1 when shared memory is short
     int Cout;
     int kp, pp, PR, PC;     // max pooling fused behind the convolution (kp = 0: none): window, padding, pooled tile
-    const float *scale, *shift, *slope;
+    const float *slope;
+    float cscale[64], cshift[64];   // per-channel epilogue constants, read straight from the kernel-parameter bank
     int act_kind;
     float act_th, act_val, act_alpha;
     int kind;               // 0 fp16, 1 bf16
     int pdl;
+    int debug;              // timing experiments: 1 one tap only, 2 no epilogue work, 4 no patch copies, 8 no activation pass, 16 no pooling pass, 32 tap offsets rounded to 8 rows
     int *status;
 };
 
@@ -65,8 +68,8 @@ __device__ __forceinline__ void tma_store_4d(const void *tmap, uint32_t src, int
                  "r"(c0), "r"(c1), "r"(c2), "r"(c3)
                  : "memory");
 }
-// barrier among the 256 epilogue threads only
-__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+// barrier among the 512 epilogue threads only
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
 
 // K-major operand whose rows are `row_bytes` (32 or 128) long and consecutive, swizzled with the pattern of that width:
 // 8-row groups 8*row_bytes apart.  The start address may be any multiple of 16 bytes; the pattern follows the address.
@@ -121,6 +124,74 @@ __device__ __forceinline__ Unit unit_of(const PatchParams &p, int u)
     return q;
 }
 
+// All tcgen05.mma of ONE tap into one accumulator (KSTEPS instructions of K = 16 elements), descriptors given as
+// (low word, high word).  An issuing thread is a single thread whose instruction latency is the kernel's critical
+// path: the low word (the 14-bit start-address field, in 16-byte units) is advanced with adds, nothing else is
+// recomputed, and the statement carries no memory clobber so that the compiler may fetch the next tap's offset early
+// (the operands were made visible by the mbarrier wait and the fence before the loop).
+template <int KSTEPS>
+__device__ __forceinline__ void mma_tap(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc, uint32_t accumulate)
+{
+    if (KSTEPS == 1) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "setp.ne.b32 p, %5, 0;\n\t"
+            "mov.b64 da, {%1, %3};\n\t"
+            "mov.b64 db, {%2, %3};\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
+            "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate));
+    } else {
+        // four K steps along a 128-byte row: 32 bytes = 2 address units each; `hi` is never zero, so q is always true
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
+            "setp.ne.b32 p, %5, 0;\n\t"
+            "setp.ne.b32 q, %3, 0;\n\t"
+            "mov.b64 da, {%1, %3};\n\t"
+            "mov.b64 db, {%2, %3};\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+            "add.s64 da, da, 2;\n\t"
+            "add.s64 db, db, 2;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, q;\n\t"
+            "add.s64 da, da, 2;\n\t"
+            "add.s64 db, db, 2;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, q;\n\t"
+            "add.s64 da, da, 2;\n\t"
+            "add.s64 db, db, 2;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, q;\n\t}" ::"r"(d_tmem),
+            "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate));
+    }
+}
+
+// One thread's 32 accumulator columns (channels CH*32 .. CH*32+31 of its output pixel) -> four 16-byte chunks:
+// y = act(acc * scale[c] + shift[c]).  CH is a template argument so that every index into the constants is known at
+// compile time: they are then operands of the FFMA itself (kernel-parameter bank), not loads.
+template <int CH>
+__device__ __forceinline__ void activate_half(const uint32_t (&acc)[32], const PatchParams &p, int act_mode, const float *s_slope,
+                                              uint4 (&o)[4])
+{
+#pragma unroll
+    for (int cj = 0; cj < 4; cj++) {
+        uint32_t ow[4];
+#pragma unroll
+        for (int h = 0; h < 4; h++) {
+            const int c = CH * 32 + cj * 8 + h * 2;
+            float v0 = fmaf(__uint_as_float(acc[cj * 8 + h * 2]), p.cscale[c], p.cshift[c]);
+            float v1 = fmaf(__uint_as_float(acc[cj * 8 + h * 2 + 1]), p.cscale[c + 1], p.cshift[c + 1]);
+            if (act_mode == 3) {
+                v0 = fmaxf(v0, 0.f);
+                v1 = fmaxf(v1, 0.f);
+            } else if (act_mode != 0) {
+                v0 = c < p.Cout ? thb_apply_act(v0, p.act_kind, p.act_th, p.act_val, p.act_alpha, s_slope[c]) : 0.f;
+                v1 = c + 1 < p.Cout ? thb_apply_act(v1, p.act_kind, p.act_th, p.act_val, p.act_alpha, s_slope[c + 1]) : 0.f;
+            }
+            ow[h] = pack_pair(v0, v1, p.kind);
+        }
+        o[cj] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
+// PX: bytes per input pixel in shared memory (32 or 128); KP: pooling window fused behind the convolution (0: none)
+template <int PX, int KP>
 __global__ void __launch_bounds__(PT_THREADS, 1)
 conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_constant__ CUtensorMap tmapA,
                      const __grid_constant__ CUtensorMap tmapY, const PatchParams p)
@@ -131,11 +202,12 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
     uint64_t *acc_full = empty + PT_MAX_STAGES, *acc_empty = acc_full + 2, *w_full = acc_empty + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(w_full + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-    float *s_scale = reinterpret_cast<float *>(smem + 256), *s_shift = s_scale + 64, *s_slope = s_shift + 64;
-    uint8_t *sW = smem + 1024;                          // resident weights: tap t at sW + t * 64 * px_bytes
+    uint32_t *s_tapoff = reinterpret_cast<uint32_t *>(smem + 128);   // per tap: (r*P + s) pixel rows, in 16-byte units (at most 64 taps)
+    float *s_slope = reinterpret_cast<float *>(smem + 384);
+    uint8_t *sW = smem + 2048;                          // resident weights: tap t at sW + t * 64 * PX
     uint8_t *sP = sW + p.w_bytes;                       // raw patch buffers
     uint8_t *ct = sP + p.nst * p.stage_bytes;           // output tile(s): one with pooling, two without
-    uint8_t *pt = ct + PT_CT_BYTES;                     // pooled tiles (pooling only)
+    uint8_t *pt = ct + p.ct_bufs * PT_CT_BYTES;         // pooled tiles (pooling only)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int units = p.N * p.tiles_r * p.tiles_c;
@@ -146,22 +218,26 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
     if (tid == 0) {
         for (int s = 0; s < p.nst; s++) {
             mbar_init(smem_u32(&full[s]), 1);
-            mbar_init(smem_u32(&empty[s]), 1);
+            mbar_init(smem_u32(&empty[s]), 2);            // one commit per MMA issuer
         }
         for (int b = 0; b < 2; b++) {
-            mbar_init(smem_u32(&acc_full[b]), 1);
-            mbar_init(smem_u32(&acc_empty[b]), 256);
+            mbar_init(smem_u32(&acc_full[b]), 2);          // one commit per MMA issuer
+            mbar_init(smem_u32(&acc_empty[b]), 16);        // one arrival per epilogue warp
         }
         mbar_init(smem_u32(w_full), 1);
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
     }
+    if (tid >= 128 && tid < 192) {
+        const int t = tid - 128;
+        int rows = (t / p.kW) * p.P + t % p.kW;
+        if (p.debug & 32) rows &= ~7;
+        s_tapoff[t] = t < taps ? (uint32_t)(rows * (PX / 16)) : 0u;
+    }
     if (tid < 64) {
         // per-channel epilogue constants (uploaded when the network was planned: no kernel of this stream writes them)
         const bool real = tid < p.Cout;
-        s_scale[tid] = real ? (p.scale ? p.scale[tid] : 1.f) : 0.f;
-        s_shift[tid] = real ? (p.shift ? p.shift[tid] : 0.f) : 0.f;
         s_slope[tid] = real && p.slope ? p.slope[tid] : 0.f;
     }
     if (warp == 0 && lane == 0) {
@@ -180,8 +256,7 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
     // the weights do not depend on the kernel before this one: fetch them while it drains
     if (warp == 0 && lane == 0 && mine > 0) {
         mbar_arrive_expect_tx(smem_u32(w_full), (uint32_t)p.w_bytes);
-        const int px_elems = p.px_bytes / 2;
-        for (int t = 0; t < taps; t++) tma_load_2d(smem_u32(sW + t * 64 * p.px_bytes), &tmapW, smem_u32(w_full), t * px_elems, 0);
+        for (int t = 0; t < taps; t++) tma_load_2d(smem_u32(sW + t * 64 * PX), &tmapW, smem_u32(w_full), t * (PX / 2), 0);
     }
     if (p.pdl) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -193,7 +268,7 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
         if (lane == 0) {
             int ring_s = 0;
             uint32_t ring_ph = 0;
-            const uint32_t box_bytes = (uint32_t)((p.CR + p.kH - 1) * p.P * p.px_bytes);
+            const uint32_t box_bytes = (uint32_t)((p.CR + p.kH - 1) * p.P * PX);
             for (int u = 0; u < mine; u++) {
                 const Unit q = unit_of(p, blockIdx.x + u * gridDim.x);
                 const int s = ring_s;
@@ -205,17 +280,26 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
                     break;
                 }
                 const uint32_t bar = smem_u32(&full[s]);
+                if (p.debug & 4) { mbar_arrive(bar); continue; }
                 mbar_arrive_expect_tx(bar, box_bytes);
                 tma_load_4d(smem_u32(sP + s * p.stage_bytes), &tmapA, bar, 0, q.c0 - p.padW + p.xoff, q.r0 - p.padH, q.n);
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
-        // ================================================================== MMA issuer
+    } else if (warp == 1 || warp == 2) {
+        // ================================================================== MMA issuers: warp 1 feeds the accumulator of GEMM
+        // rows 0..127, warp 2 that of rows 128..255 (an instruction of N = 64 takes the tensor pipe 48 cycles, which
+        // one issuing thread cannot sustain)
         if (lane == 0 && mine > 0) {
             constexpr uint32_t IDESC_F16 = make_idesc(1u, 0u, 64), IDESC_BF16 = make_idesc(1u, 1u, 64);
             const uint32_t idesc = p.kind == 1 ? IDESC_BF16 : IDESC_F16;
-            const int ksteps = p.px_bytes / 32;  // tcgen05.mma of K = 16 elements per tap
+            constexpr int KSTEPS = PX / 32;      // tcgen05.mma of K = 16 elements per tap
+            constexpr uint32_t HALF = 128u * PX / 16, BSTEP = 64u * PX / 16;   // descriptor steps: second accumulator's rows, next tap's weights
+            const int hsel = warp - 1;
+            const uint64_t proto = make_rows_desc(0u, PX);
+            const uint32_t hi = (uint32_t)(proto >> 32), lo_flags = (uint32_t)proto;
+            const uint32_t b_lo0 = lo_flags | ((smem_u32(sW) >> 4) & 0x3FFFu);
+            const int ntaps = (p.debug & 1) ? 1 : taps;
             int ring_s = 0;
             uint32_t ring_ph = 0;
             bool alive = mbar_wait_bounded(smem_u32(w_full), 0);
@@ -239,41 +323,42 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
                     break;
                 }
                 tc_fence_after();
-                const uint32_t d0 = tmem_base + ab * 128, d1 = d0 + 64;
-                const uint32_t patch = smem_u32(sP + s * p.stage_bytes), wbase = smem_u32(sW);
-                int r = 0, sx = 0;
-                for (int t = 0; t < taps; t++) {
-                    const uint32_t a_addr = patch + (uint32_t)((r * p.P + sx) * p.px_bytes);
-                    const uint64_t a0 = make_rows_desc(a_addr, p.px_bytes);
-                    const uint64_t a1 = make_rows_desc(a_addr + 128u * (uint32_t)p.px_bytes, p.px_bytes);
-                    const uint64_t b = make_rows_desc(wbase + (uint32_t)(t * 64 * p.px_bytes), p.px_bytes);
-                    for (int k = 0; k < ksteps; k++) {
-                        const uint32_t accum = (uint32_t)((t | k) != 0);
-                        tc_mma_f16(d0, a0 + 2 * k, b + 2 * k, idesc, accum);
-                        tc_mma_f16(d1, a1 + 2 * k, b + 2 * k, idesc, accum);
-                    }
-                    if (++sx == p.kW) { sx = 0; r++; }
+                const uint32_t d = tmem_base + ab * 128 + hsel * 64;
+                const uint32_t a_lo0 = (lo_flags | ((smem_u32(sP + s * p.stage_bytes) >> 4) & 0x3FFFu)) + hsel * HALF;
+                uint32_t b_lo = b_lo0;
+                mma_tap<KSTEPS>(d, a_lo0 + s_tapoff[0], b_lo, hi, idesc, 0u);   // first tap: the accumulator starts from zero
+#pragma unroll 4
+                for (int t = 1; t < ntaps; t++) {
+                    b_lo += BSTEP;
+                    mma_tap<KSTEPS>(d, a_lo0 + s_tapoff[t], b_lo, hi, idesc, 1u);
                 }
                 tc_commit(smem_u32(&empty[s]));
                 tc_commit(smem_u32(&acc_full[ab]));
             }
         }
         __syncwarp();
-    } else {
+    } else if (warp >= 4) {
         // ================================================================== epilogue: activate, (pool,) store
-        const int et = tid - 64;                 // 0..255
+        // 16 warps: a thread owns one GEMM row (TMEM lane) and 32 of its 64 output channels
+        const int et = tid - 128;                // 0..511
+        const int e = warp - 4;
         const int quad = warp & 3;               // TMEM lane quadrant this warp may read
-        const int half = (warp - 2) >> 2;        // accumulator half: GEMM rows 0..127 / 128..255
+        const int half = (e >> 2) & 1;           // accumulator half: GEMM rows 0..127 / 128..255
+        const int ch = e >> 3;                   // channels 0..31 / 32..63
         const int m = half * 128 + quad * 32 + lane;
         const int cr = m / p.P, cc = m - cr * p.P;
         const bool valid = cr < p.CR && cc < p.CC;
         const int ci = cr * p.CC + cc;           // row of the output tile (valid rows only)
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + half * 64;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + half * 64 + ch * 32;
         const int act_mode = p.act_kind == THB_ACT_NONE ? 0
                              : p.act_kind != THB_ACT_THRESHOLD ? 2
                              : (p.act_th == 0.f && p.act_val == 0.f) ? 3 : 1;
-        const int items = p.PR * p.PC * 8;       // pooling: (pooled pixel, 16-byte channel chunk)
         const uint32_t neg_inf2 = p.kind == 0 ? 0xFC00FC00u : 0xFF80FF80u;
+        const int kind = p.kind;
+        // pooling: this thread's (pooled pixel, 16-byte channel chunk) item; its patch coordinates never change
+        const int items = KP ? p.PR * p.PC * 8 : 0;
+        const int it_px = et >> 3, it_j = et & 7;
+        const int it_pr = KP ? it_px / p.PC : 0, it_pc = it_px - it_pr * p.PC;
         for (int u = 0; u < mine; u++) {
             const int ab = u & 1;
             const Unit q = unit_of(p, blockIdx.x + u * gridDim.x);
@@ -282,42 +367,31 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
                 *abort_flag = 1;
             }
             tc_fence_after();
-            uint32_t acc0[32], acc1[32];
+            uint32_t acc[32];
             __syncwarp();
-            tmem_ld32(lane_addr + ab * 128, acc0);
-            tmem_ld32(lane_addr + ab * 128 + 32, acc1);
+            tmem_ld32(lane_addr + ab * 128, acc);
             tmem_ld_wait();
             tc_fence_before();
-            mbar_arrive(smem_u32(&acc_empty[ab]));
-            // the tile about to be written was the source of the store two units ago
-            if (et == 0) bulk_wait_group_read<1>();
-            uint8_t *tile = p.kp ? ct : ct + (u & 1) * PT_CT_BYTES;
-            if (!p.kp) epi_bar_sync();
-            if (valid) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&acc_empty[ab]));
+            if (p.debug & 2) continue;
+            // the tile about to be written was the source of the store two units ago (of the last one with a single tile)
+            if (et == 0) {
+                if (!KP && p.ct_bufs == 1) bulk_wait_group_read<0>();
+                else bulk_wait_group_read<1>();
+            }
+            uint8_t *tile = KP || p.ct_bufs == 1 ? ct : ct + (u & 1) * PT_CT_BYTES;
+            if (!KP) epi_bar_sync();
+            if (valid && !(p.debug & 8)) {
+                uint4 o[4];
+                if (ch == 0) activate_half<0>(acc, p, act_mode, s_slope, o);
+                else activate_half<1>(acc, p, act_mode, s_slope, o);
                 uint8_t *row_smem = tile + ci * 128;
                 const int rsw = ci & 7;
 #pragma unroll
-                for (int cj = 0; cj < 8; cj++) {
-                    const uint32_t *a = cj < 4 ? acc0 + cj * 8 : acc1 + (cj - 4) * 8;
-                    uint32_t ow[4];
-#pragma unroll
-                    for (int h = 0; h < 4; h++) {
-                        const int c = cj * 8 + h * 2;
-                        float v0 = fmaf(__uint_as_float(a[h * 2]), s_scale[c], s_shift[c]);
-                        float v1 = fmaf(__uint_as_float(a[h * 2 + 1]), s_scale[c + 1], s_shift[c + 1]);
-                        if (act_mode == 3) {
-                            v0 = fmaxf(v0, 0.f);
-                            v1 = fmaxf(v1, 0.f);
-                        } else if (act_mode != 0) {
-                            v0 = c < p.Cout ? thb_apply_act(v0, p.act_kind, p.act_th, p.act_val, p.act_alpha, s_slope[c]) : 0.f;
-                            v1 = c + 1 < p.Cout ? thb_apply_act(v1, p.act_kind, p.act_th, p.act_val, p.act_alpha, s_slope[c + 1]) : 0.f;
-                        }
-                        ow[h] = pack_pair(v0, v1, p.kind);
-                    }
-                    *reinterpret_cast<uint4 *>(row_smem + ((cj ^ rsw) << 4)) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-                }
+                for (int cj = 0; cj < 4; cj++) *reinterpret_cast<uint4 *>(row_smem + (((ch * 4 + cj) ^ rsw) << 4)) = o[cj];
             }
-            if (!p.kp) {
+            if (!KP) {
                 fence_proxy_async_smem();         // the rows must be visible to the copy engine
                 epi_bar_sync();                   // the tile is complete
                 if (*abort_flag) break;           // (read after the barrier: every thread sees the same value)
@@ -330,25 +404,27 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
             epi_bar_sync();                       // the activated patch is complete
             if (*abort_flag) break;
             uint8_t *ptile = pt + (u & 1) * PT_PT_BYTES;
-            for (int it = et; it < items; it += 256) {
-                const int px = it >> 3, j = it & 7;
-                const int pr = px / p.PC, pc = px - pr * p.PC;
-                // window of this pooled pixel, clipped to the convolution output
-                const int gr0 = q.r0 + 2 * pr, gc0 = q.c0 + 2 * pc;
+            if (et < items && !(p.debug & 16)) {
+                // window of this thread's pooled pixel, clipped to the convolution output
+                const int gr0 = q.r0 + 2 * it_pr, gc0 = q.c0 + 2 * it_pc;
                 uint32_t mx[4] = {neg_inf2, neg_inf2, neg_inf2, neg_inf2};
-                for (int dr = 0; dr < p.kp; dr++) {
-                    if ((unsigned)(gr0 + dr) >= (unsigned)p.oH) continue;
-                    for (int dc = 0; dc < p.kp; dc++) {
-                        if ((unsigned)(gc0 + dc) >= (unsigned)p.oW) continue;
-                        const int mm = (2 * pr + dr) * p.CC + 2 * pc + dc;
-                        const uint4 v = *reinterpret_cast<const uint4 *>(ct + mm * 128 + ((j ^ (mm & 7)) << 4));
-                        mx[0] = max_pair(mx[0], v.x, p.kind);
-                        mx[1] = max_pair(mx[1], v.y, p.kind);
-                        mx[2] = max_pair(mx[2], v.z, p.kind);
-                        mx[3] = max_pair(mx[3], v.w, p.kind);
+                const int m00 = 2 * it_pr * p.CC + 2 * it_pc;
+#pragma unroll
+                for (int dr = 0; dr < KP; dr++) {
+                    const bool rok = (unsigned)(gr0 + dr) < (unsigned)p.oH;
+#pragma unroll
+                    for (int dc = 0; dc < KP; dc++) {
+                        const int mm = m00 + dr * p.CC + dc;
+                        const uint4 v = *reinterpret_cast<const uint4 *>(ct + mm * 128 + ((it_j ^ (mm & 7)) << 4));
+                        if (rok && (unsigned)(gc0 + dc) < (unsigned)p.oW) {
+                            mx[0] = max_pair(mx[0], v.x, kind);
+                            mx[1] = max_pair(mx[1], v.y, kind);
+                            mx[2] = max_pair(mx[2], v.z, kind);
+                            mx[3] = max_pair(mx[3], v.w, kind);
+                        }
                     }
                 }
-                *reinterpret_cast<uint4 *>(ptile + px * 128 + j * 16) = make_uint4(mx[0], mx[1], mx[2], mx[3]);
+                *reinterpret_cast<uint4 *>(ptile + it_px * 128 + it_j * 16) = make_uint4(mx[0], mx[1], mx[2], mx[3]);
             }
             fence_proxy_async_smem();
             epi_bar_sync();                       // pooled tile complete; the patch tile may be overwritten
@@ -386,40 +462,66 @@ encode_tiled_fn pt_encode_fn()
 
 struct Geometry {
     int CR, CC, P, tiles_r, tiles_c, PR, PC;
+    int stage_bytes, nst, ct_bufs, w_bytes;
+    size_t smem;
 };
+
+// shared-memory plan of a candidate patch: resident weights, raw patch buffers, output tile(s), pooled tiles
+bool plan_smem(int kH, int kW, int px_bytes, int kp, Geometry *g)
+{
+    g->w_bytes = (kH * kW * 64 * px_bytes + 1023) & ~1023;
+    // a patch buffer holds the copied pixels and whatever the 256 GEMM rows of the last tap reach beyond them
+    const int box_px = (g->CR + kH - 1) * g->P, reach_px = (kH - 1) * g->P + kW - 1 + 256;
+    g->stage_bytes = ((box_px > reach_px ? box_px : reach_px) * px_bytes + 1023) & ~1023;
+    // without pooling the output tile is the source of an asynchronous store: two of them when room allows
+    for (g->ct_bufs = kp ? 1 : 2; g->ct_bufs >= 1; g->ct_bufs--) {
+        const size_t fixed = 1024 + 2048 + (size_t)g->w_bytes + (size_t)g->ct_bufs * PT_CT_BYTES + (kp ? 2 * PT_PT_BYTES : 0);
+        if (fixed + 2 * (size_t)g->stage_bytes > PT_SMEM_MAX) continue;
+        g->nst = (int)((PT_SMEM_MAX - fixed) / g->stage_bytes);
+        if (g->nst > PT_MAX_STAGES) g->nst = PT_MAX_STAGES;
+        if (g->nst < 3 && g->ct_bufs == 2) continue;   // a third patch in flight is worth more than a second output tile
+        g->smem = fixed + (size_t)g->nst * g->stage_bytes;
+        return true;
+    }
+    return false;
+}
 
 // The patch that covers the map with the fewest units: CR output rows x CC output columns with CR * (CC + kW - 1) <= 256
 // GEMM rows; with a pooling behind the convolution the patch is made of whole windows (CR = 2(PR-1)+kp, CC likewise).
-bool choose_patch(int oH, int oW, int kW, int kp, int pH, int pW, Geometry *g)
+bool choose_patch(int oH, int oW, int kH, int kW, int px_bytes, int kp, int pH, int pW, Geometry *best)
 {
-    long best = -1;
+    long best_tiles = -1;
     for (int a = 1; a <= 64; a++) {
-        const int CR = kp ? 2 * (a - 1) + kp : a;
-        int CC, PC = 0;
+        Geometry g;
+        memset(&g, 0, sizeof(g));
+        g.CR = kp ? 2 * (a - 1) + kp : a;
+        if (g.CR > 256) break;
         if (kp) {
             // largest PC with CR * (2(PC-1) + kp + kW - 1) <= 256, at most 64 pooled pixels per tile
-            PC = ((256 / CR) - (kW - 1) - kp) / 2 + 1;
-            if (PC > pW) PC = pW;
-            if (a * PC > 64) PC = 64 / a;
-            if (PC < 1) continue;
-            CC = 2 * (PC - 1) + kp;
+            g.PR = a;
+            g.PC = ((256 / g.CR) - (kW - 1) - kp) / 2 + 1;
+            if (g.PC > pW) g.PC = pW;
+            if (a * g.PC > 64) g.PC = 64 / a;
+            if (g.PC < 1) continue;
+            g.CC = 2 * (g.PC - 1) + kp;
         } else {
-            CC = 256 / CR - (kW - 1);
-            if (CC > oW) CC = oW;
-            if (CC > 256) CC = 256;
-            if (CC < 1) continue;
+            g.CC = 256 / g.CR - (kW - 1);
+            if (g.CC > oW) g.CC = oW;
+            if (g.CC < 1) continue;
         }
-        if (CR > 256 || CR * (CC + kW - 1) > 256) continue;
-        const int tr = kp ? (pH + a - 1) / a : (oH + CR - 1) / CR;
-        const int tc = kp ? (pW + PC - 1) / PC : (oW + CC - 1) / CC;
-        const long tiles = (long)tr * tc;
-        if (best < 0 || tiles < best) {
-            best = tiles;
-            g->CR = CR; g->CC = CC; g->P = CC + kW - 1; g->tiles_r = tr; g->tiles_c = tc; g->PR = kp ? a : 0; g->PC = PC;
+        g.P = g.CC + kW - 1;
+        if (g.P > 256 || g.CR + kH - 1 > 256 || g.CR * g.P > 256) continue;
+        g.tiles_r = kp ? (pH + a - 1) / a : (oH + g.CR - 1) / g.CR;
+        g.tiles_c = kp ? (pW + g.PC - 1) / g.PC : (oW + g.CC - 1) / g.CC;
+        if (!plan_smem(kH, kW, px_bytes, kp, &g)) continue;
+        const long tiles = (long)g.tiles_r * g.tiles_c;
+        if (best_tiles < 0 || tiles < best_tiles || (tiles == best_tiles && g.nst > best->nst)) {
+            best_tiles = tiles;
+            *best = g;
         }
-        if ((kp ? a >= pH : CR >= oH)) break;
+        if ((kp ? a >= pH : g.CR >= oH)) break;
     }
-    return best > 0;
+    return best_tiles > 0;
 }
 
 bool patch_geometry_ok(const thb_conv_desc *d, int pk, int ps, int ppad)
@@ -438,7 +540,8 @@ bool patch_geometry_ok(const thb_conv_desc *d, int pk, int ps, int ppad)
 }
 
 struct PtMapEntry {
-    const void *x, *y;
+    const void *x, *y, *wptr, *scale, *shift;
+    float cscale[64], cshift[64];   // host copies of the per-channel constants (they travel as kernel parameters)
     int key[20];
     alignas(64) CUtensorMap w, a, y_map;
 };
@@ -450,7 +553,7 @@ int patch_launch(const thb_conv_desc *d, int pk, int ppad, int pH, int pW, const
     PatchParams p;
     memset(&p, 0, sizeof(p));
     Geometry g;
-    if (!choose_patch(d->oH, d->oW, d->kW, pk, pH, pW, &g)) return THB_ERR_UNSUPPORTED;
+    if (!choose_patch(d->oH, d->oW, d->kH, d->kW, d->Cin_pad * 2, pk, pH, pW, &g)) return THB_ERR_UNSUPPORTED;
     p.N = d->N; p.oH = d->oH; p.oW = d->oW;
     p.CR = g.CR; p.CC = g.CC; p.P = g.P; p.tiles_r = g.tiles_r; p.tiles_c = g.tiles_c; p.PR = g.PR; p.PC = g.PC;
     p.kH = d->kH; p.kW = d->kW; p.padH = d->padH; p.padW = d->padW;
@@ -458,20 +561,12 @@ int patch_launch(const thb_conv_desc *d, int pk, int ppad, int pH, int pW, const
     p.xoff = d->in_row_pitch ? d->in_pad_left : 0;
     p.kp = pk; p.pp = ppad;
     p.Cout = d->Cout;
-    p.scale = d->scale; p.shift = d->shift; p.slope = d->act.kind == THB_ACT_PRELU ? d->act.slope : nullptr;
+    p.slope = d->act.kind == THB_ACT_PRELU ? d->act.slope : nullptr;
     p.act_kind = d->act.kind; p.act_th = d->act.threshold; p.act_val = d->act.value; p.act_alpha = d->act.alpha;
     p.kind = d->dtype == THB_BF16 ? 1 : 0;
     p.status = d->status;
-    const int taps = d->kH * d->kW;
-    p.w_bytes = (taps * 64 * p.px_bytes + 1023) & ~1023;
-    // a patch buffer holds the copied pixels and whatever the 256 GEMM rows of the last tap reach beyond them
-    const int box_px = (p.CR + p.kH - 1) * p.P, reach_px = (p.kH - 1) * p.P + p.kW - 1 + 256;
-    p.stage_bytes = ((box_px > reach_px ? box_px : reach_px) * p.px_bytes + 1023) & ~1023;
-    const size_t fixed = 1024 + 1024 + (size_t)p.w_bytes + (pk ? PT_CT_BYTES + 2 * PT_PT_BYTES : 2 * PT_CT_BYTES);
-    p.nst = (int)((PT_SMEM_MAX - fixed) / p.stage_bytes);
-    if (p.nst > PT_MAX_STAGES) p.nst = PT_MAX_STAGES;
-    if (p.nst < 2) return THB_ERR_UNSUPPORTED;
-    const size_t smem = fixed + (size_t)p.nst * p.stage_bytes;
+    p.w_bytes = g.w_bytes; p.stage_bytes = g.stage_bytes; p.nst = g.nst; p.ct_bufs = g.ct_bufs;
+    const size_t smem = g.smem;
 
     // tensor maps of the weights (one tap per box), the input (patch box) and the output (tile box), cached by buffer and shape
     static PtMapEntry cache[128];
@@ -480,7 +575,7 @@ int patch_launch(const thb_conv_desc *d, int pk, int ppad, int pH, int pW, const
                          p.CR, p.CC, p.PR, p.PC, d->kH, d->kW, d->Ktot_pad};
     PtMapEntry *e = nullptr;
     for (int i = 0; i < used; i++)
-        if (cache[i].x == x && cache[i].y == y && !memcmp(cache[i].key, key, sizeof(key))) { e = &cache[i]; break; }
+        if (cache[i].x == x && cache[i].y == y && cache[i].wptr == d->w && cache[i].scale == d->scale && cache[i].shift == d->shift && !memcmp(cache[i].key, key, sizeof(key))) { e = &cache[i]; break; }
     if (!e) {
         e = &cache[used < 128 ? used++ : (next++ % 128)];
         e->x = nullptr;
@@ -516,19 +611,34 @@ int patch_launch(const thb_conv_desc *d, int pk, int ppad, int pH, int pW, const
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
                 return thb_note_launch(cudaErrorInvalidValue, "conv_patch: output tensor map");
         }
-        e->x = x; e->y = y;
+        // The per-channel constants are fetched from the device once per layer (a blocking copy: the first forward of a
+        // plan launches directly, before any stream capture, so this never runs inside one).
+        for (int c = 0; c < 64; c++) { e->cscale[c] = c < d->Cout ? 1.f : 0.f; e->cshift[c] = 0.f; }
+        if (d->scale && cudaMemcpy(e->cscale, d->scale, sizeof(float) * d->Cout, cudaMemcpyDeviceToHost) != cudaSuccess)
+            return thb_note_launch(cudaGetLastError(), "conv_patch: reading the scale constants");
+        if (d->shift && cudaMemcpy(e->cshift, d->shift, sizeof(float) * d->Cout, cudaMemcpyDeviceToHost) != cudaSuccess)
+            return thb_note_launch(cudaGetLastError(), "conv_patch: reading the shift constants");
+        e->x = x; e->y = y; e->wptr = d->w; e->scale = d->scale; e->shift = d->shift;
         memcpy(e->key, key, sizeof(key));
     }
 
+    memcpy(p.cscale, e->cscale, sizeof(p.cscale));
+    memcpy(p.cshift, e->cshift, sizeof(p.cshift));
     static bool configured[16] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 16) dev = 0;
+    typedef void (*kern_t)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const PatchParams);
+    static const kern_t kerns[6] = {conv_patch_tc_kernel<32, 0>,  conv_patch_tc_kernel<32, 2>,  conv_patch_tc_kernel<32, 3>,
+                                    conv_patch_tc_kernel<128, 0>, conv_patch_tc_kernel<128, 2>, conv_patch_tc_kernel<128, 3>};
     if (!configured[dev]) {
-        cudaError_t ce = cudaFuncSetAttribute(conv_patch_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PT_SMEM_MAX);
-        if (ce != cudaSuccess) return thb_note_launch(ce, "conv_patch smem attribute");
+        for (int i = 0; i < 6; i++) {
+            cudaError_t ce = cudaFuncSetAttribute(kerns[i], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PT_SMEM_MAX);
+            if (ce != cudaSuccess) return thb_note_launch(ce, "conv_patch smem attribute");
+        }
         configured[dev] = true;
     }
+    const kern_t kern = kerns[(p.px_bytes == 128 ? 3 : 0) + (pk == 0 ? 0 : pk == 2 ? 1 : 2)];
     static int sms[16] = {0};
     if (!sms[dev]) cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
     const int units = p.N * p.tiles_r * p.tiles_c;
@@ -540,6 +650,7 @@ int patch_launch(const thb_conv_desc *d, int pk, int ppad, int pH, int pW, const
         use_pdl = ev ? atoi(ev) : 1;
     }
     p.pdl = use_pdl;
+    if (const char *dv = getenv("THB200_PATCH_DEBUG")) p.debug = atoi(dv);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(PT_THREADS);
@@ -550,7 +661,7 @@ int patch_launch(const thb_conv_desc *d, int pk, int ppad, int pH, int pW, const
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = use_pdl ? 1 : 0;
-    const cudaError_t le = cudaLaunchKernelEx(&cfg, conv_patch_tc_kernel, e->w, e->a, e->y_map, p);
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, kern, e->w, e->a, e->y_map, p);
     return thb_note_launch(le != cudaSuccess ? le : cudaGetLastError(), "conv_patch_tc_kernel");
 }
 
@@ -569,7 +680,9 @@ bool patch_disabled()
 // 1 when the patch kernel can run this convolution (plain store of its output)
 extern "C" int thb_conv_patch_supported(const thb_conv_desc *d)
 {
-    return !patch_disabled() && patch_geometry_ok(d, 0, 0, 0) ? 1 : 0;
+    Geometry g;
+    return !patch_disabled() && patch_geometry_ok(d, 0, 0, 0) &&
+           choose_patch(d->oH, d->oW, d->kH, d->kW, d->Cin_pad * 2, 0, 0, 0, &g) ? 1 : 0;
 }
 
 extern "C" int thb_conv_patch_fwd(const thb_conv_desc *d, const void *x, void *y, thb_stream s)
@@ -588,7 +701,9 @@ extern "C" int thb_conv_maxpool_supported(const thb_conv_desc *d, int pk, int ps
         const char *e = getenv("THB200_NO_CONV_POOL");
         disabled = e && atoi(e) ? 1 : 0;
     }
-    return !disabled && !patch_disabled() && pk > 0 && patch_geometry_ok(d, pk, ps, ppad) ? 1 : 0;
+    Geometry g;
+    return !disabled && !patch_disabled() && pk > 0 && patch_geometry_ok(d, pk, ps, ppad) &&
+           choose_patch(d->oH, d->oW, d->kH, d->kW, d->Cin_pad * 2, pk, d->oH / 2 + 1, d->oW / 2 + 1, &g) ? 1 : 0;
 }
 
 extern "C" int thb_conv_maxpool_fwd(const thb_conv_desc *d, int pk, int ps, int ppad, int pH, int pW, const void *x, void *y,

@@ -1110,6 +1110,40 @@ done:
     }
 }
 
+// Diagnostic launcher switches (THB200_* environment variables), read ONCE: a launch costs no getenv call.
+// thb_conv_reload_knobs() re-reads them (the tests change them between cases).  -1 = not set.
+struct ConvKnobs {
+    int pair_min_kb, u8_fast, reverse, epi_groups, epi_bufs, pdl, conv_l1, half_taps, a_tma;
+    long pair_min_units;
+};
+ConvKnobs g_knobs;
+bool g_knobs_read = false;
+int env_int(const char *name, int unset)
+{
+    const char *e = getenv(name);
+    return e ? atoi(e) : unset;
+}
+void read_knobs()
+{
+    g_knobs.pair_min_kb = env_int("THB200_PAIR_MIN_KB", -1);
+    const char *u = getenv("THB200_PAIR_MIN_UNITS");
+    g_knobs.pair_min_units = u ? atol(u) : -1;
+    g_knobs.u8_fast = env_int("THB200_U8_FAST", 1);
+    g_knobs.reverse = env_int("THB200_REVERSE", 1);
+    g_knobs.epi_groups = env_int("THB200_EPI_GROUPS", -1);
+    g_knobs.epi_bufs = env_int("THB200_EPI_BUFS", -1);
+    g_knobs.pdl = env_int("THB200_PDL", 1);
+    g_knobs.conv_l1 = env_int("THB200_CONV_L1", -1);
+    g_knobs.half_taps = env_int("THB200_HALF_TAPS", -1);
+    g_knobs.a_tma = env_int("THB200_A_TMA", -1);
+    g_knobs_read = true;
+}
+const ConvKnobs &knobs()
+{
+    if (!g_knobs_read) read_knobs();
+    return g_knobs;
+}
+
 int num_sms()
 {
     static int n[16] = {0};
@@ -1142,17 +1176,12 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
     using L = Smem<KIND, BN, STAGES>;
     // Pair mode (see ConvTcParams::pair): narrow tiles with a K loop long enough to be bound by the MMA thread's barrier
     // rounds, and at least two units of work per SM.
-    int pair_min_kb = 1;
-    if (const char *e = getenv("THB200_PAIR_MIN_KB")) pair_min_kb = atoi(e);
-    long pair_min_units = 2L * num_sms();
-    if (const char *e = getenv("THB200_PAIR_MIN_UNITS")) pair_min_units = atol(e);  // (tests exercise the mode on small shapes)
+    const ConvKnobs &kn = knobs();
+    const int pair_min_kb = kn.pair_min_kb >= 0 ? kn.pair_min_kb : 1;
+    const long pair_min_units = kn.pair_min_units >= 0 ? kn.pair_min_units : 2L * num_sms();  // (tests exercise the mode on small shapes)
     p.u8_classes = 0;
     if (KIND == 2) {
-        static int fast_mode = -1;
-        if (fast_mode < 0) {
-            const char *e = getenv("THB200_U8_FAST");
-            fast_mode = e ? atoi(e) : 1;
-        }
+        const int fast_mode = kn.u8_fast;
         const int ncls = (1 + 2 * p.padH) * (1 + 2 * p.padW);
         if (fast_mode && p.wsat && p.padH < p.kH && p.padW < p.kW && ncls * L::TBL_ROW <= L::TBL_CAP) p.u8_classes = ncls;
         // a fused residual exists on the table-driven path only, and that path needs windows clipped on one side at most
@@ -1163,12 +1192,8 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
         // Every second convolution launch of a host thread walks its pixel tiles backwards: consecutive layers then
         // start on the end of the tensor the layer before has just written, which the L2 still holds (1.3 % of a
         // ResNet-50 forward).  THB200_REVERSE=0 switches it off, 2 reverses every launch.
-        static int rev_mode = -1;
         static thread_local unsigned flip = 0;
-        if (rev_mode < 0) {
-            const char *e = getenv("THB200_REVERSE");
-            rev_mode = e ? atoi(e) : 1;
-        }
+        const int rev_mode = kn.reverse;
         p.reverse = L::TMA_EPI && p.a_tma && (rev_mode == 1 ? (flip++ & 1) : rev_mode == 2);
     }
     const int tiles = (p.pair ? (p.m_tiles + 1) / 2 : p.m_tiles) * p.n_tiles;  // units of work
@@ -1176,7 +1201,7 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
     if (!L::TMA_EPI) {
         // staged epilogue: uint8 with nothing to gather runs a third group on warps 0-3 (a fourth accumulator exists below 256 columns)
         p.epi_groups = KIND == 2 && p.a_tma && BN < 256 ? 3 : 2;
-        if (const char *e = getenv("THB200_EPI_GROUPS")) p.epi_groups = atoi(e) == 3 && KIND == 2 && p.a_tma && BN < 256 ? 3 : 2;
+        if (kn.epi_groups >= 0) p.epi_groups = kn.epi_groups == 3 && KIND == 2 && p.a_tma && BN < 256 ? 3 : 2;
     }
     if (L::TMA_EPI) {
         if (!tm.y || (p.res && !tm.r)) return thb_note_launch(cudaErrorUnknown, "conv_tc: output tensor map");
@@ -1188,9 +1213,9 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
         // off loads in flight: one tile per group, the rest in stages.
         const bool short_k = p.nkb <= 2;
         p.epi_groups = p.a_tma && BN >= 128 && BN < 256 && p.nkb == 1 && !p.res ? 3 : 2;
-        if (const char *e = getenv("THB200_EPI_GROUPS")) p.epi_groups = atoi(e) == 3 && p.a_tma && BN < 256 ? 3 : 2;
+        if (kn.epi_groups >= 0) p.epi_groups = kn.epi_groups == 3 && p.a_tma && BN < 256 ? 3 : 2;
         p.epi_bufs = p.epi_groups == 3 ? 2 : ((short_k && p.res) || p.nkb == 1) && BN < 256 ? 3 : p.nkb <= 8 ? 2 : 1;
-        if (const char *e = getenv("THB200_EPI_BUFS")) p.epi_bufs = atoi(e) < 1 ? 1 : atoi(e) > 3 ? 3 : atoi(e);
+        if (kn.epi_bufs >= 0) p.epi_bufs = kn.epi_bufs < 1 ? 1 : kn.epi_bufs > 3 ? 3 : kn.epi_bufs;
         const size_t stage_bytes = L::STAGE_BYTES + (p.pair ? A_STAGE_BYTES : 0);
         const int min_stages = p.pair ? 2 : STAGES;
         while (min_stages * stage_bytes + (size_t)p.epi_groups * p.epi_bufs * EPI_TILE_BYTES > L::AVAIL) p.epi_bufs--;
@@ -1199,11 +1224,7 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
         if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
         if (!p.a_tma) p.stages = STAGES;  // the gather's cp.async depth is tied to the compile-time count
     }
-    static int use_pdl = -1;
-    if (use_pdl < 0) {
-        const char *e = getenv("THB200_PDL");
-        use_pdl = e ? atoi(e) : 1;
-    }
+    const int use_pdl = kn.pdl;
     p.pdl = use_pdl;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
@@ -1400,6 +1421,8 @@ const CUtensorMap *weights_half_tmap(const thb_conv_desc *d)
 
 }  // namespace
 
+extern "C" void thb_conv_reload_knobs(void) { read_knobs(); }
+
 extern "C" int thb_conv_make_tmap(const thb_conv_desc *d, thb_tmap *out)
 {
     if (d->dtype == THB_F32) return THB_ERR_ARG;
@@ -1480,7 +1503,8 @@ extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, t
     p.tail_start = d->tail_start; p.relu_thr = d->relu_thr; p.relu_val = d->relu_val;
     p.acc_out = d->acc_out;
     p.use_l1 = d->kH * d->kW > 1;
-    if (const char *e = getenv("THB200_CONV_L1")) p.use_l1 = atoi(e);
+    const ConvKnobs &kn = knobs();
+    if (kn.conv_l1 >= 0) p.use_l1 = kn.conv_l1;
     p.status = d->status;
     if (!p.status) return THB_ERR_ARG;
     if (d->dtype == THB_U8 && (!p.wsat || !p.csum)) return THB_ERR_ARG;
@@ -1527,11 +1551,10 @@ extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, t
     if (p.half) {
         tmap_mode = 4;
         p.slabs = 1;
-        if (const char *e = getenv("THB200_HALF_TAPS"))
-            if (!atoi(e)) p.half = 0, p.a_tma = 0;
+        if (kn.half_taps == 0) p.half = 0, p.a_tma = 0;
     }
-    if (const char *e = getenv("THB200_A_TMA")) {
-        const int allow = atoi(e);  // 0: gather only, 1: plain-matrix TMA only, 2 (default): im2col too
+    if (kn.a_tma >= 0) {
+        const int allow = kn.a_tma;  // 0: gather only, 1: plain-matrix TMA only, 2 (default): im2col too
         if (p.a_tma > allow) p.a_tma = 0, p.half = 0;
         if (allow == 22 && p.a_tma == 1) p.a_tma = 2;  // experiment: im2col mode for a plain matrix too
     }
