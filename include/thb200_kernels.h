@@ -206,6 +206,29 @@ int thb_softmax(int dtype, const void *x, long pixels, int C, int x_ld, void *y,
 int thb_col2im(int dtype, const void *cols, int N, int H, int W, int Cout, int kH, int kW, int dH, int dW, int padH,
                int padW, int oH, int oW, int cols_ld, float beta, const float *bias, const thb_act *act, void *y,
                int y_ld, thb_stream s);
+/* ---- operators outside the benchmark networks (fp32 / fp16 / bf16) ---- */
+/* 2x nearest-neighbour upsampling (modules/Upsample.c:18-63): y is [N][2H][2W][y_ld] */
+int thb_upsample2x(int dtype, const void *x, int N, int H, int W, int C, int x_ld, void *y, int y_ld, thb_stream s);
+/* zero padding by pad_l/r/t/b pixels, negative values crop (modules/SpatialZeroPadding.c:17-60, as intended: the
+ * reference's own loop strides rows by the height and leaves the right padding unwritten): y is [N][H+pad_t+pad_b][W+pad_l+pad_r][y_ld] */
+int thb_zero_pad(int dtype, const void *x, int N, int H, int W, int C, int x_ld, int pad_l, int pad_r, int pad_t, int pad_b, void *y,
+                 int y_ld, thb_stream s);
+/* channels [from, from + C) of every pixel of x -> y (modules/Slice.c:34-39 along the channel dimension, any `from`) */
+int thb_slice_channels(int dtype, const void *x, long pixels, int from, int C, int x_ld, void *y, int y_ld, thb_stream s);
+/* elementwise maximum of up to 8 tensors of one shape (modules/Cmax.c:20-68) */
+int thb_cmax(int dtype, int nin, const void *const *x_host, const int *ld_host, long pixels, int C, void *y, int y_ld, thb_stream s);
+/* log-softmax over the channels of each pixel (modules/LogSoftMax.c:19-81).  first_frame_quirk = 1 reproduces the
+ * reference's last loop, which subtracts each position's log-sum from the values at the START of the input (:77) */
+int thb_logsoftmax(int dtype, const void *x, long pixels, int C, int x_ld, void *y, int y_ld, int first_frame_quirk, thb_stream s);
+/* x / ||x||_2 over each of `rows` contiguous rows of row_len elements (per_row = 1: a 2-D tensor) or over all of them
+ * together (modules/Normalize.c:12-44); scratch_rows: `rows` floats of device scratch; y may be x */
+int thb_l2_normalize(int dtype, const void *x, long rows, long row_len, int per_row, float *scratch_rows, void *y, thb_stream s);
+/* max unpooling (modules/SpatialMaxUnpooling.c:14-121): v holds one value per pooling window ([N][oH][oW][v_ld]), pool_in is
+ * the tensor that pooling read ([N][H][W][x_ld]); y ([N][H][W][y_ld]) gets each value at the position of its window's
+ * maximum (the index SpatialMaxPooling.c:95-112 records) and zero elsewhere; later windows win where windows overlap */
+int thb_max_unpool(int dtype, const void *v, int v_ld, const void *pool_in, int x_ld, int N, int H, int W, int C, int kH, int kW, int dH,
+                   int dW, int padH, int padW, int oH, int oW, void *y, int y_ld, thb_stream s);
+
 /* per-pixel sum of the first C bytes (zero-point correction term of the u8 convolution) */
 int thb_u8_channel_sum(const void *x, long pixels, int C, int x_ld, int *csum, thb_stream s);
 /* channels-innermost -> plain NCHW flatten order of the same dtype (View feeding anything but a Linear) */

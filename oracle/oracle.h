@@ -69,6 +69,16 @@ void lowpgemm(const int is_a_transposed, const int is_b_transposed, const int is
               const int b_offset, const int c_offset, const int c_mult, const int c_shift);
 unsigned char orc_lowp_requant(int acc, int c_offset, int c_mult, int c_shift);
 
+/* ---- the remaining operators (oracle_shape.c) ---- */
+void orc_upsample2x(const float *x, int N, int C, int H, int W, float *y);
+void orc_zero_pad(const float *x, int N, int C, int H, int W, int pad_l, int pad_r, int pad_t, int pad_b, float *y);
+void orc_slice(const float *x, const long *size, int ndim, int axis, long from, long to, float *y);
+void orc_cmax(const float *const *ins, int nin, long n, float *y);
+void orc_logsoftmax(const float *x, long nframe, long dim, long stride, int first_frame_quirk, float *y);
+void orc_l2_normalize(const float *x, long rows, long row_len, int per_row, float *y);
+void orc_max_unpool(const float *v, const float *pool_in, int N, int C, int H, int W, int kH, int kW, int dH, int dW, int padH,
+                    int padW, int oH, int oW, float *y);
+
 #ifdef __cplusplus
 }
 #endif

@@ -191,6 +191,71 @@ class Oracle:
         self.lib.orc_normalize(_fp(x), n, c, h, w, _fp(mean), _fp(std))
         return x
 
+    # ---- the remaining operators (oracle_shape.c) -----------------------------
+    def upsample2x(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        lead = x.shape[:-2]
+        h, w = x.shape[-2:]
+        y = np.empty(lead + (2 * h, 2 * w), np.float32)
+        self.lib.orc_upsample2x(_fp(x), 1, int(np.prod(lead)), h, w, _fp(y))
+        return y
+
+    def zero_pad(self, x, pad_l, pad_r, pad_t, pad_b):
+        x = np.ascontiguousarray(x, np.float32)
+        lead = x.shape[:-2]
+        h, w = x.shape[-2:]
+        y = np.empty(lead + (h + pad_t + pad_b, w + pad_l + pad_r), np.float32)
+        self.lib.orc_zero_pad(_fp(x), 1, int(np.prod(lead)), h, w, pad_l, pad_r, pad_t, pad_b, _fp(y))
+        return y
+
+    def slice(self, x, axis, start, stop):
+        x = np.ascontiguousarray(x, np.float32)
+        shape = list(x.shape)
+        shape[axis] = stop - start
+        y = np.empty(shape, np.float32)
+        size = (C.c_long * x.ndim)(*x.shape)
+        self.lib.orc_slice.argtypes = [_f, C.POINTER(C.c_long), C.c_int, C.c_int, C.c_long, C.c_long, _f]
+        self.lib.orc_slice(_fp(x), size, x.ndim, axis, start, stop, _fp(y))
+        return y
+
+    def cmax(self, ins):
+        ins = [np.ascontiguousarray(i, np.float32) for i in ins]
+        y = np.empty_like(ins[0])
+        ptrs = (_f * len(ins))(*[_fp(i) for i in ins])
+        self.lib.orc_cmax.argtypes = [C.POINTER(_f), C.c_int, C.c_long, _f]
+        self.lib.orc_cmax(ptrs, len(ins), ins[0].size, _fp(y))
+        return y
+
+    def logsoftmax(self, x, first_frame_quirk=1):
+        """LogSoftMax.c over dimension 1 of [N,C] / [N,C,H,W], dimension 0 of [C] / [C,H,W]."""
+        x = np.ascontiguousarray(x, np.float32)
+        y = np.empty_like(x)
+        if x.ndim in (1, 3):
+            nframe, dim, stride = 1, x.shape[0], int(np.prod(x.shape[1:]))
+        else:
+            nframe, dim, stride = x.shape[0], x.shape[1], int(np.prod(x.shape[2:]))
+        self.lib.orc_logsoftmax.argtypes = [_f, C.c_long, C.c_long, C.c_long, C.c_int, _f]
+        self.lib.orc_logsoftmax(_fp(x), nframe, dim, stride, first_frame_quirk, _fp(y))
+        return y
+
+    def l2_normalize(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        y = np.empty_like(x)
+        per_row = 1 if x.ndim == 2 else 0
+        rows = x.shape[0] if x.ndim == 2 else 1
+        self.lib.orc_l2_normalize.argtypes = [_f, C.c_long, C.c_long, C.c_int, _f]
+        self.lib.orc_l2_normalize(_fp(x), rows, x.size // rows, per_row, _fp(y))
+        return y
+
+    def max_unpool(self, v, pool_in, k, stride, pad, ceil_mode=0):
+        v = np.ascontiguousarray(v, np.float32)
+        pool_in = np.ascontiguousarray(pool_in, np.float32)
+        n, c, h, w = pool_in.shape
+        oh, ow = v.shape[2:]
+        y = np.empty_like(pool_in)
+        self.lib.orc_max_unpool(_fp(v), _fp(pool_in), n, c, h, w, k[0], k[1], stride[0], stride[1], pad[0], pad[1], oh, ow, _fp(y))
+        return y
+
     # ---- graph execution -------------------------------------------------------
     def run(self, graph, batch, keep=False, strict_bias=0):
         """fp32 forward of `graph` on a raw [N,C,H,W] batch (normalised here first)."""
@@ -230,7 +295,23 @@ class Oracle:
             elif node.op == "add":
                 y = self.caddtable(xin)
             elif node.op == "concat":
-                y = self.join(xin)
+                y = self.join(xin) if a.get("dim", 1) == 1 else np.concatenate(xin, axis=a["dim"])
+            elif node.op == "upsample":
+                y = self.upsample2x(x)
+            elif node.op == "zeropad":
+                y = self.zero_pad(x, a["pad_l"], a["pad_r"], a["pad_t"], a["pad_b"])
+            elif node.op == "slice":
+                y = self.slice(x, a["axis"], a["start"], a["stop"])
+            elif node.op == "cmax":
+                y = self.cmax(xin)
+            elif node.op == "logsoftmax":
+                y = self.logsoftmax(x)
+            elif node.op == "l2normalize":
+                y = self.l2_normalize(x)
+            elif node.op == "unpool":
+                pool = graph.nodes[a["pool"]]
+                pa = pool.attrs
+                y = self.max_unpool(x, vals[pool.inputs[0]], pa["kernel_size"], pa["stride"], pa["padding"], pa["ceil_mode"])
             else:
                 raise ValueError(node.op)
             vals[i] = y

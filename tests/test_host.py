@@ -240,14 +240,14 @@ def test_error_conventions(th, tmp_path):
 def test_unsupported_module_is_reported(th, tmp_path):
     spec = ("nn.Sequential", [("nn.SpatialConvolutionMM", dict(
         padW=0, padH=0, dW=1, dH=1, kW=1, kH=1, nInputPlane=3, nOutputPlane=4,
-        weight=np.zeros((4, 3), np.float32), bias=np.zeros(4, np.float32))), ("nn.LogSoftMax", {})])
+        weight=np.zeros((4, 3), np.float32), bias=np.zeros(4, np.float32))), ("nn.SpatialSubtractiveNormalization", {})])
     d = str(tmp_path / "ls")
     fx.write_torch7(spec, d)
     # unknown module types are fatal in the reference's loader (thload.c:777-778): run in a child process
     code = ("import os, sys; sys.path.insert(0, %r); from thnets_b200.capi import THNets; THNets().lib.THLoadNetwork(%r)"
             % (ROOT, d.encode()))
     r = subprocess.run([os.sys.executable, "-c", code], capture_output=True, text=True)
-    assert r.returncode != 0 and "Unknown module type nn.LogSoftMax" in r.stderr
+    assert r.returncode != 0 and "Unknown module type nn.SpatialSubtractiveNormalization" in r.stderr
 
 
 def test_batch_slicing(th):
@@ -300,3 +300,35 @@ def test_static_scratch_entry_validates_before_any_launch():
     for d, x, want in cases:
         assert lib.thb_conv_u8_fwd_static(C.byref(d), x, fake, None) == want
     assert lib.thb_conv_u8_fwd_static(None, fake, fake, None) == ARG
+
+
+def test_loaders_accept_the_remaining_operators(th, tmp_path):
+    """SpatialZeroPadding / SpatialMaxUnpooling (with its reference to the pooling module) / LogSoftMax / Normalize from
+    Torch7 files, Cmax / Slice from a graph dump, Upsample / Max / Slice / LogSoftmax from ONNX: loaded and lowered."""
+    g = fx.unpool_net()
+    d = str(tmp_path / "unpool")
+    fx.write_torch7(g, d)
+    h = th.load_network(d)
+    lines = describe(th, h)
+    assert any("unpool" in l.lower() for l in lines) and any("pad" in l.lower() for l in lines), lines
+    th.free_network(h)
+    g = fx.normalize_net()
+    d = str(tmp_path / "norm")
+    fx.write_torch7(g, d)
+    h = th.load_network(d)
+    assert len(describe(th, h)) >= 5
+    th.free_network(h)
+    g = fx.cmax_slice_net()
+    p = str(tmp_path / "cmax.net")
+    fx.write_pymodel(g, p)
+    h = th.load_network(p)
+    lines = describe(th, h)
+    assert any("max" in l.lower() for l in lines) and any("slice" in l.lower() for l in lines), lines
+    th.free_network(h)
+    g = fx.onnx_ops_net()
+    p = str(tmp_path / "ops.onnx")
+    fx.write_onnx(g, p)
+    h = th.load_network(p)
+    lines = describe(th, h)
+    assert any("upsample" in l.lower() for l in lines), lines
+    th.free_network(h)

@@ -391,3 +391,62 @@ def test_lowp_first_convolution_15x15_stride_2(th, oracle, tmp_path):
     out, _, _ = th.process_float(hl, xin)
     assert np.array_equal(out, ref.ravel()), np.abs(out - ref.ravel()).max()
     th.free_network(hl)
+
+
+# ------------------------------------------------------------------------- operators outside the benchmark networks
+@pytest.mark.parametrize("case", [("unpool_zeropad_b1", lambda: fx.unpool_net(), "t7", 1, 0),
+                                  ("unpool_b3", lambda: fx.unpool_net(zeropad=False), "t7", 3, 0),
+                                  ("unpool_zeropad_b3", lambda: fx.unpool_net(), "t7", 3, 0),
+                                  ("normalize_b1", lambda: fx.normalize_net(), "t7", 1, 0),
+                                  ("normalize_b4", lambda: fx.normalize_net(), "t7", 4, 0),
+                                  ("normalize_b4_fp16", lambda: fx.normalize_net(), "t7", 4, 1),
+                                  ("cmax_slice_b4", lambda: fx.cmax_slice_net(), "py", 4, 0),
+                                  ("cmax_slice_b4_fp16", lambda: fx.cmax_slice_net(), "py", 4, 1),
+                                  ("onnx_ops_b3", lambda: fx.onnx_ops_net(), "onnx", 3, 0),
+                                  ("onnx_ops_b1", lambda: fx.onnx_ops_net(), "onnx", 1, 0)], ids=lambda c: c[0])
+def test_remaining_operators(th, oracle, tmp_path, case):
+    """SpatialZeroPadding, SpatialMaxUnpooling (positions recomputed from the pooling's input), LogSoftMax (with the
+    reference's first-frame quirk), Normalize, Cmax, Slice along every dimension and Upsample, through the three loaders,
+    against the oracle functions that are pinned to the live reference."""
+    name, build, kind, batch, mode = case
+    g = build()
+    x = g.make_input(batch)
+    ref = oracle.run(g, x)
+    if name == "normalize_b1":
+        ref = oracle.l2_normalize(oracle.run(g, x, keep=True)[len(g.nodes) - 2].ravel())   # View gives a 1-D tensor at batch 1
+    if kind == "onnx":
+        p = str(tmp_path / (name + ".onnx"))
+        fx.write_onnx(g, p)
+        h = th.load_network(p)
+        th.set_stats(h, g.mean, g.std)
+    else:
+        h = _load(th, g, kind, tmp_path, name)
+    th.lib.THB200_SetPrecision(mode)
+    hc = th.lib.THCreateCudaNetwork(h)
+    th.lib.THB200_SetPrecision(0)
+    assert hc, th.lib.THB200_LastErrorString()
+    th.free_network(h)
+    out, _, _ = th.process_float(hc, x)
+    assert out.size == ref.size, (out.size, ref.shape)
+    err = rel_err(out, ref.ravel())
+    assert err < (1e-4 if mode == 0 else 2e-2), (name, err)
+    th.free_network(hc)
+
+
+def test_concat_along_the_batch_dimension(th, oracle, tmp_path):
+    """JoinTable along dimension 0 of 4-D tensors (JoinTable.c:46-57): the inputs' images one after the other."""
+    g = fx.Graph(9)
+    g.input_shape = (3, 10, 10)
+    x = g.relu(g.conv(0, 3, 8, 3, 1, 1, bias=0.1))
+    a = g.conv(x, 8, 6, 3, 1, 1, bias=0.1)
+    b = g.conv(x, 8, 6, 1, 1, 0, bias=0.1)
+    j = g.concat([a, b], 0)
+    g.conv(j, 6, 4, 3, 1, 1, bias=0.1)
+    xin = g.make_input(3)
+    ref = oracle.run(g, xin)
+    assert ref.shape[0] == 6
+    hc = _convert(th, g, "py", tmp_path, "cat0", 0)
+    out, _, _ = th.process_float(hc, xin)
+    assert out.size == ref.size
+    assert rel_err(out, ref.ravel()) < 1e-4
+    th.free_network(hc)

@@ -164,3 +164,73 @@ def test_lowp_image_loader_matches_live_reference(oracle, tmp_path, bgr):
     y, _, _ = ref.process_images(hl, [img], bgr=bgr)
     mine = oracle.run_lowp(g, None, 6.0, 48, quantised_input=oracle.lowp_images([img], g.mean, g.std, bgr))
     assert np.array_equal(mine.ravel(), y)
+
+
+@pytest.mark.parametrize("batch,zeropad", [(1, True), (3, False)])
+def test_unpool_zeropad_logsoftmax_against_the_live_reference(oracle, tmp_path, batch, zeropad):
+    """The restatements of SpatialZeroPadding, SpatialMaxPooling's indices + SpatialMaxUnpooling and LogSoftMax (with its
+    first-frame quirk at batch 3) against the unmodified reference run on the same Torch7 file.  The zero padding is
+    compared where the reference's own loop is sound: a square map, no right padding, and ONE image -- its batch loop
+    shares the plane and row counters between OpenMP threads (SpatialZeroPadding.c:39-41), so larger batches race."""
+    from oracle.oracle import ref_lib
+    from thnets_b200 import fixtures as fx
+    from thnets_b200.capi import THNets
+    if ref_lib() is None:
+        pytest.skip("reference library not built")
+    g = fx.unpool_net(zeropad=zeropad)
+    d = str(tmp_path / "unpool")
+    fx.write_torch7(g, d)
+    th = THNets(ref_lib())
+    h = th.load_network(d)
+    x = g.make_input(batch)
+    out, _, _ = th.process_float(h, x)
+    ref = oracle.run(g, x)
+    assert out.size == ref.size
+    assert np.abs(out - ref.ravel()).max() / np.abs(ref).max() < 2e-5
+
+
+@pytest.mark.parametrize("batch", [1, 4])
+def test_normalize_against_the_live_reference(oracle, tmp_path, batch):
+    from oracle.oracle import ref_lib
+    from thnets_b200 import fixtures as fx
+    from thnets_b200.capi import THNets
+    if ref_lib() is None:
+        pytest.skip("reference library not built")
+    g = fx.normalize_net()
+    d = str(tmp_path / "norm")
+    fx.write_torch7(g, d)
+    th = THNets(ref_lib())
+    h = th.load_network(d)
+    x = g.make_input(batch)
+    out, _, _ = th.process_float(h, x)
+    ref = oracle.run(g, x)
+    if batch == 1:
+        ref = oracle.l2_normalize(oracle.run(g, x, keep=True)[len(g.nodes) - 2].ravel())   # View gives a 1-D tensor at batch 1
+    assert np.abs(out - ref.ravel()).max() / np.abs(ref).max() < 2e-5
+
+
+def test_cmax_slice_against_the_live_reference(oracle, tmp_path):
+    from oracle.oracle import ref_lib
+    from thnets_b200 import fixtures as fx
+    from thnets_b200.capi import THNets
+    if ref_lib() is None:
+        pytest.skip("reference library not built")
+    g = fx.cmax_slice_net()
+    p = str(tmp_path / "cmax.net")
+    fx.write_pymodel(g, p)
+    th = THNets(ref_lib())
+    h = th.load_network(p)
+    x = g.make_input(4)
+    out, _, _ = th.process_float(h, x)
+    ref = oracle.run(g, x)
+    assert ref.shape[0] == 2 and out.size == ref.size
+    assert np.abs(out - ref.ravel()).max() / np.abs(ref).max() < 2e-5
+
+
+def test_upsample_restatement():
+    """Upsample has an ONNX loader only in the reference, which cannot be built here; the restatement of its loop
+    (Upsample.c:55-61) is checked against NumPy's repeat."""
+    from oracle.oracle import Oracle
+    o = Oracle()
+    x = np.random.default_rng(3).standard_normal((2, 3, 4, 5)).astype(np.float32)
+    assert np.array_equal(o.upsample2x(x), x.repeat(2, axis=2).repeat(2, axis=3))

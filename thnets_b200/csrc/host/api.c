@@ -418,7 +418,8 @@ static int describe_append(char *buf, int len, int pos, const char *fmt, ...)
 int THB200_DescribeNetwork(THNETWORK *network, char *buf, int len)
 {
     static const char *names[] = {"input", "conv", "deconv", "linear", "bn", "act", "maxpool", "avgpool", "combine",
-                                  "concat", "softmax", "view", "alias", "scale"};
+                                  "concat", "softmax", "view", "alias", "scale", "upsample", "zeropad", "slice", "cmax",
+                                  "logsoftmax", "normalize", "unpool"};
     char err[256] = "";
     if (!buf || len < 2) return -1;
     thb_model *m = thb_model_from_network(network, err, sizeof(err));
@@ -439,6 +440,8 @@ int THB200_DescribeNetwork(THNETWORK *network, char *buf, int len)
         else if (n->op == OP_VIEW) pos = describe_append(buf, len, pos, " %d", n->numElements);
         else if (n->op == OP_ACT) pos = describe_append(buf, len, pos, " kind=%d th=%g val=%g", n->act_kind, n->act_threshold, n->act_value);
         else if (n->op == OP_CONCAT) pos = describe_append(buf, len, pos, " dim=%d", n->dim);
+        else if (n->op == OP_ZEROPAD) pos = describe_append(buf, len, pos, " l%d r%d t%d b%d", n->pad_l, n->pad_r, n->pad_t, n->pad_b);
+        else if (n->op == OP_SLICE) pos = describe_append(buf, len, pos, " axis=%d [%d,%d)", n->slice_axis, n->slice_from, n->slice_to);
         pos = describe_append(buf, len, pos, "%s\n", i == m->output ? " <- output" : "");
     }
     thb_model_release(m);

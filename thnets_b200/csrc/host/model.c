@@ -21,6 +21,9 @@ typedef struct {
     char *err;
     size_t errlen;
     int memo[MAXPYNODES];
+    /* max-pooling modules lowered so far (Torch7 route): an unpooling finds the pooling it undoes by identity */
+    struct nnmodule *pool_mod[64];
+    int pool_node[64], npools;
 } builder;
 
 static int fail(builder *b, const char *fmt, ...)
@@ -73,7 +76,7 @@ static int lower_leaf(builder *b, struct module *m, val in, val *out)
     long cnt;
     out->n = 1;
     out->is_table = 0;
-    if (in.is_table && m->type != MT_JoinTable && m->type != MT_CAddTable && m->type != MT_CSubTable)
+    if (in.is_table && m->type != MT_JoinTable && m->type != MT_CAddTable && m->type != MT_CSubTable && m->type != MT_Cmax)
         return fail(b, "module type %d cannot take a table of tensors", m->type);
     switch (m->type) {
     case MT_SpatialConvolution: case MT_SpatialConvolutionMM: case MT_SpatialConvolutionVirtMM: {
@@ -206,9 +209,45 @@ static int lower_leaf(builder *b, struct module *m, val in, val *out)
         }
         break;
     }
+    case MT_Upsample:
+        if (m->Upsample.height_scale != 2 || m->Upsample.width_scale != 2) return fail(b, "Only 2x upsampling is supported");
+        new_node(b, OP_UPSAMPLE, 1, in.id);
+        break;
+    case MT_SpatialZeroPadding:
+        n = new_node(b, OP_ZEROPAD, 1, in.id);
+        n->pad_l = m->SpatialZeroPadding.pad_l; n->pad_r = m->SpatialZeroPadding.pad_r;
+        n->pad_t = m->SpatialZeroPadding.pad_t; n->pad_b = m->SpatialZeroPadding.pad_b;
+        break;
+    case MT_Slice:
+        n = new_node(b, OP_SLICE, 1, in.id);
+        n->slice_axis = m->Slice.axis; n->slice_from = m->Slice.from; n->slice_to = m->Slice.to;
+        break;
+    case MT_Cmax:
+        if (!in.is_table || in.n < 1) return fail(b, "Cmax needs a table of tensors");
+        new_node(b, OP_CMAX, in.n, in.id);
+        break;
+    case MT_LogSoftMax: new_node(b, OP_LOGSOFTMAX, 1, in.id); break;
+    case MT_Normalize: new_node(b, OP_NORMALIZE, 1, in.id); break;
+    case MT_SpatialMaxUnpooling: {
+        /* SpatialMaxUnpooling.c:60-71: the pooling module it undoes is found by identity among the modules seen so far;
+         * the unpooling reads that pooling's input again to locate each window's maximum */
+        int pool = -1;
+        for (int k = 0; k < b->npools; k++)
+            if (b->pool_mod[k] == m->SpatialMaxUnpooling.pooling) pool = b->pool_node[k];
+        if (pool < 0 || !m->SpatialMaxUnpooling.pooling) return fail(b, "SpatialMaxUnpooling refers to no SpatialMaxPooling of this network");
+        int ids[2] = {in.id[0], b->m->nodes[pool].in[0]};
+        const thb_node pn = b->m->nodes[pool];
+        n = new_node(b, OP_UNPOOL, 2, ids);
+        n->kH = pn.kH; n->kW = pn.kW; n->dH = pn.dH; n->dW = pn.dW; n->padH = pn.padH; n->padW = pn.padW; n->ceil_mode = pn.ceil_mode;
+        break;
+    }
     default: return fail(b, "module type %d is not supported by the B200 engine", m->type);
     }
     out->id[0] = last_id(b);
+    if (m->type == MT_SpatialMaxPooling && m->nnmodule && b->npools < 64) {
+        b->pool_mod[b->npools] = m->nnmodule;
+        b->pool_node[b->npools++] = out->id[0];
+    }
     return 0;
 }
 
@@ -264,7 +303,7 @@ static int lower_py(builder *b, struct pyelement *e, int *id)
         in.n++;
     }
     int t = e->function.module.type;
-    in.is_table = (t == MT_CAddTable || t == MT_CSubTable || t == MT_JoinTable);
+    in.is_table = (t == MT_CAddTable || t == MT_CSubTable || t == MT_JoinTable || t == MT_Cmax);
     if (!in.is_table && in.n != 1) return fail(b, "function %s has %d inputs", e->name, in.n);
     if (lower_leaf(b, &e->function.module, in, &out)) return -1;
     b->memo[e->function.id] = out.id[0];

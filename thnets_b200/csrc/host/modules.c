@@ -166,6 +166,19 @@ static int build_torch_module(struct module *m, struct nnmodule *n)
         m->type = MT_PReLU;
         m->PReLU.nOutputPlane = thb_t7_number(t, "nOutputPlane");
         m->PReLU.weight = thb_t7_tensor(t, "weight");
+    } else if (!strcmp(cls, "nn.SpatialZeroPadding")) { /* SpatialZeroPadding.c:4-15 */
+        m->type = MT_SpatialZeroPadding;
+        m->SpatialZeroPadding.pad_l = thb_t7_number(t, "pad_l");
+        m->SpatialZeroPadding.pad_r = thb_t7_number(t, "pad_r");
+        m->SpatialZeroPadding.pad_t = thb_t7_number(t, "pad_t");
+        m->SpatialZeroPadding.pad_b = thb_t7_number(t, "pad_b");
+    } else if (!strcmp(cls, "nn.Normalize") || !strcmp(cls, "nn.L2Normalize")) { /* thload.c:729-730 */
+        m->type = MT_Normalize;
+    } else if (!strcmp(cls, "nn.LogSoftMax")) {
+        m->type = MT_LogSoftMax;
+    } else if (!strcmp(cls, "nn.SpatialMaxUnpooling")) { /* SpatialMaxUnpooling.c:4-12 */
+        m->type = MT_SpatialMaxUnpooling;
+        m->SpatialMaxUnpooling.pooling = thb_t7_nnmodule(t, "pooling");
     } else
         return -1;
     return 0;
@@ -367,6 +380,20 @@ void thb_build_py_module(const char *fname, struct pyfunction *f)
     } else if (!strcmp(op, "Concat")) {
         m->type = MT_JoinTable;
         m->JoinTable.dimension = ival(p, "dim", 0);
+    } else if (!strcmp(op, "Slice")) {
+        /* Slice.c:3-14: the graph dump carries "index" = {from, to} and no axis (dimension 0); the ONNX reader passes all three */
+        struct pyelement *e = param(p, "index", 0);
+        m->type = MT_Slice;
+        if (e && e->type == ELTYPE_INTVECT) { m->Slice.from = e->ivect[0]; m->Slice.to = e->ivect[1]; }
+        else { m->Slice.axis = ival(p, "axis", 0); m->Slice.from = ival(p, "from", 0); m->Slice.to = ival(p, "to", 0); }
+    } else if (!strcmp(op, "Cmax")) {
+        m->type = MT_Cmax;
+    } else if (!strcmp(op, "LogSoftmax")) { /* ONNX reader only (onnx.cc:41) */
+        m->type = MT_LogSoftMax;
+    } else if (!strcmp(op, "Upsample")) {   /* ONNX reader only (onnx.cc:54, Upsample.c:4-16) */
+        m->type = MT_Upsample;
+        m->Upsample.width_scale = fval(p, "width_scale", 0);
+        m->Upsample.height_scale = fval(p, "height_scale", 0);
     } else
         THError("Unsupported function %s", fname);
 }

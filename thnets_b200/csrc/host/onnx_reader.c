@@ -89,9 +89,9 @@ typedef struct {
 
 typedef struct {
     char *name;
-    int has_i, has_f, nints;
+    int has_i, has_f, nints, nfloats;
     int64_t i, ints[OX_MAXINTS];
-    float f;
+    float f, floats[OX_MAXINTS];
     char *s;
     ox_tensor *t;
 } ox_attr;
@@ -198,6 +198,14 @@ static int ox_parse_attr(pbuf m, ox_attr *a)
         else if (field == 3 && wt == 0) { a->i = (int64_t)v; a->has_i = 1; }
         else if (field == 4 && wt == 2) { free(a->s); a->s = pb_strdup(&sub); }
         else if (field == 5 && wt == 2) { ox_tensor_free(a->t); a->t = ox_parse_tensor(sub); if (!a->t) return -1; }
+        else if (field == 7) { /* floats: packed or one by one */
+            if (wt == 2) {
+                while (sub.end - sub.p >= 4) {
+                    if (a->nfloats < OX_MAXINTS) memcpy(&a->floats[a->nfloats++], sub.p, 4);
+                    sub.p += 4;
+                }
+            } else if (wt == 5 && a->nfloats < OX_MAXINTS) { uint32_t u = (uint32_t)v; memcpy(&a->floats[a->nfloats++], &u, 4); }
+        }
         else if (field == 8) { /* ints: packed or one by one */
             if (wt == 2) {
                 while (sub.p < sub.end) {
@@ -593,8 +601,29 @@ static struct pyelement *ox_value(ox_build *b, const char *name)
         par_int(&e->function, "inplace", 0);
     } else if (!strcmp(op, "Dropout") || !strcmp(op, "Identity"))
         e = ox_function(b, idx, "Dropout", (const char *const *)&n->in[0], 1);
-    else if (!strcmp(op, "Softmax") || !strcmp(op, "Sigmoid") || !strcmp(op, "Tanh"))
+    else if (!strcmp(op, "Softmax") || !strcmp(op, "Sigmoid") || !strcmp(op, "Tanh") || !strcmp(op, "LogSoftmax"))
         e = ox_function(b, idx, op, (const char *const *)&n->in[0], 1);
+    else if (!strcmp(op, "Max"))            /* onnx.cc:52: elementwise maximum of all inputs */
+        e = ox_function(b, idx, "Cmax", (const char *const *)n->in, n->nin);
+    else if (!strcmp(op, "Slice")) {        /* Slice.c:17-32: first entry of axes / starts / ends */
+        int ax = 0, from = 0, to = 0, unused = 0;
+        ox_ints2(n, "axes", 0, 0, &ax, &unused);
+        ox_ints2(n, "starts", 0, 0, &from, &unused);
+        ox_ints2(n, "ends", 0, 0, &to, &unused);
+        if (!(e = ox_function(b, idx, "Slice", (const char *const *)&n->in[0], 1))) return 0;
+        par_int(&e->function, "axis", ax);
+        par_int(&e->function, "from", from);
+        par_int(&e->function, "to", to);
+    } else if (!strcmp(op, "Upsample")) {   /* Upsample.c:4-16: width_scale / height_scale, else scales[3] / scales[2] */
+        float ws = ox_float(n, "width_scale", 0.f), hs = ox_float(n, "height_scale", 0.f);
+        if (ws == 0.f && hs == 0.f) {
+            const ox_attr *sa = ox_attr_of(n, "scales");
+            if (sa && sa->nfloats >= 4) { hs = sa->floats[2]; ws = sa->floats[3]; }
+        }
+        if (!(e = ox_function(b, idx, "Upsample", (const char *const *)&n->in[0], 1))) return 0;
+        par_float(&e->function, "width_scale", ws);
+        par_float(&e->function, "height_scale", hs);
+    }
     else if (!strcmp(op, "Flatten") || !strcmp(op, "Reshape")) {
         /* View.c: the batch dimension stays, everything else becomes one dimension */
         if (!strcmp(op, "Reshape")) {

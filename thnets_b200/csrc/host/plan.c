@@ -74,7 +74,7 @@ typedef struct {
 
 enum step_kind {
     ST_CONV, ST_GEMV, ST_MAXPOOL, ST_AVGPOOL, ST_AFFINE, ST_U8THR, ST_U8COMBINE, ST_COMBINE, ST_COPY, ST_SOFTMAX, ST_COL2IM,
-    ST_CSUM, ST_TO_NCHW, ST_ZERO
+    ST_CSUM, ST_TO_NCHW, ST_ZERO, ST_UPSAMPLE, ST_ZEROPAD, ST_SLICEC, ST_CMAX, ST_LOGSOFTMAX, ST_NORMALIZE, ST_UNPOOL
 };
 
 typedef struct {
@@ -99,6 +99,7 @@ typedef struct {
     float w_sub, w_mult, out_sub, out_mult;
     int flops_node; /* model node index of the conv (profiling) */
     int dual;       /* convolution with a second activation operand (in_buf[1]) instead of a residual */
+    long in_off0, out_off0; /* element offsets added to the first input / the output (slices and joins along the batch dimension) */
     int pool_k, pool_pad, pool_oH, pool_oW; /* pool_k > 0: the max pooling that follows runs inside the convolution launch */
     double flops_extra; /* FLOPs of the second convolution computed by the same launch */
 } step;
@@ -151,6 +152,7 @@ struct thb_engine {
     float last_ms;
     int peer_gather;
     /* arguments of the last forward, for the device-resident timing loop */
+    int whole_batch; /* the model has an operator that looks across the batch: one GPU, no sub-batches */
     int last_has_x, last_cp, last_bgr;
     float last_mean[3], last_std[3];
 };
@@ -862,6 +864,29 @@ static int plan_node(planner *P, int i)
         int dim = n->dim;
         if (dim == 1 && (in->s.rank == 1 || in->s.rank == 3)) dim--;
         int chan_dim = (in->s.rank == 4 || in->s.rank == 2) ? 1 : 0;
+        if (dim == 0 && chan_dim == 1) {
+            /* JoinTable.c:46-57 / Concat.c:21-76 along the batch dimension: the inputs' images one after the other */
+            if (P->I->slice_n != E->N) { thb_set_error("concatenation along the batch dimension needs the whole batch on one GPU"); return -1; }
+            shape os = in->s;
+            os.N = 0;
+            for (int k = 0; k < n->nin; k++) {
+                const value *v = &P->val[n->in[k]];
+                if (v->s.rank != in->s.rank || v->s.flat) { thb_set_error("Concatenation of tensors of different dimensionality"); return -1; }
+                if (v->s.H != in->s.H || v->s.W != in->s.W || v->s.C != in->s.C) { thb_set_error("Concatenation of tensors of different sizes"); return -1; }
+                os.N += v->s.N;
+            }
+            materialise(P, out, os);
+            long img = 0;
+            for (int k = 0; k < n->nin; k++) {
+                const value *v = &P->val[n->in[k]];
+                s = new_step(P, ST_COPY);
+                step_in(s, v); step_out(s, out);
+                s->pixels = (long)v->s.N * os.H * os.W; s->C = v->s.C;
+                s->out_off0 = img * os.H * os.W * out->ld;
+                img += v->s.N;
+            }
+            return 0;
+        }
         if (dim != chan_dim) { thb_set_error("concatenation along dimension %d is not supported", n->dim); return -1; }
         shape os = in->s;
         os.C = 0;
@@ -934,6 +959,133 @@ static int plan_node(planner *P, int i)
             return 0;
         }
         out->s.C = (int)per; out->s.H = out->s.W = 1;
+        return 0;
+    }
+    case OP_UPSAMPLE: {
+        /* Upsample.c:18-63 */
+        if (in->s.rank < 3 || in->s.flat) { thb_set_error("Only 3D and 4D input is supported"); return -1; }
+        shape os = in->s;
+        os.H *= 2; os.W *= 2;
+        materialise(P, out, os);
+        s = new_step(P, ST_UPSAMPLE);
+        step_in(s, in); step_out(s, out);
+        s->N = in->s.N; s->H = in->s.H; s->W = in->s.W; s->C = in->s.C;
+        return 0;
+    }
+    case OP_ZEROPAD: {
+        /* SpatialZeroPadding.c:17-60 (negative pads crop) */
+        if (in->s.rank < 3 || in->s.flat) { thb_set_error("input dimension must be 3 or 4"); return -1; }
+        shape os = in->s;
+        os.H = in->s.H + n->pad_t + n->pad_b; os.W = in->s.W + n->pad_l + n->pad_r;
+        if (os.H < 1 || os.W < 1) { thb_set_error("zero padding leaves an empty tensor"); return -1; }
+        materialise(P, out, os);
+        s = new_step(P, ST_ZEROPAD);
+        step_in(s, in); step_out(s, out);
+        s->N = in->s.N; s->H = in->s.H; s->W = in->s.W; s->C = in->s.C;
+        s->padW = n->pad_l; s->kW = n->pad_r; s->padH = n->pad_t; s->kH = n->pad_b;
+        return 0;
+    }
+    case OP_SLICE: {
+        /* Slice.c:34-39 + THFloatTensor_slice (thbasic.c:192-209): [from, to) along dimension `axis` of the tensor as the
+         * reference ranks it ([N,C,H,W], [C,H,W], [N,C] or [C]) */
+        if (in->s.flat) { thb_set_error("Slice of a flattened spatial tensor is not supported"); return -1; }
+        const int rank = in->s.rank, ax = n->slice_axis;
+        int which = -1; /* 0 batch, 1 channels, 2 rows, 3 columns */
+        if (rank == 4) which = ax;
+        else if (rank == 3) which = ax + 1;
+        else if (rank == 2) which = ax;
+        else if (rank == 1) which = ax == 0 ? 1 : -1;
+        const int size = which == 0 ? in->s.N : which == 1 ? in->s.C : which == 2 ? in->s.H : which == 3 ? in->s.W : -1;
+        if (which < 0 || which > 3 || (rank <= 2 && which > 1) || n->slice_from < 0 || n->slice_to <= n->slice_from || n->slice_to > size) {
+            thb_set_error("Slice [%d, %d) along dimension %d does not fit the tensor", n->slice_from, n->slice_to, ax);
+            return -1;
+        }
+        shape os = in->s;
+        const int len = n->slice_to - n->slice_from;
+        if (which == 1) {
+            os.C = len;
+            materialise(P, out, os);
+            s = new_step(P, ST_SLICEC);
+            step_in(s, in); step_out(s, out);
+            s->pixels = (long)os.N * os.H * os.W; s->C = len; s->flag = n->slice_from;
+        } else if (which == 0) {
+            if (P->I->slice_n != E->N) { thb_set_error("a slice along the batch dimension needs the whole batch on one GPU"); return -1; }
+            os.N = len;
+            materialise(P, out, os);
+            s = new_step(P, ST_COPY);
+            step_in(s, in); step_out(s, out);
+            s->pixels = (long)len * os.H * os.W; s->C = os.C;
+            s->in_off0 = (long)n->slice_from * os.H * os.W * in->ld;
+        } else {
+            if (which == 2) os.H = len; else os.W = len;
+            materialise(P, out, os);
+            s = new_step(P, ST_ZEROPAD);
+            step_in(s, in); step_out(s, out);
+            s->N = in->s.N; s->H = in->s.H; s->W = in->s.W; s->C = in->s.C;
+            s->padW = which == 3 ? -n->slice_from : 0; s->kW = which == 3 ? n->slice_to - in->s.W : 0;
+            s->padH = which == 2 ? -n->slice_from : 0; s->kH = which == 2 ? n->slice_to - in->s.H : 0;
+        }
+        return 0;
+    }
+    case OP_CMAX: {
+        /* Cmax.c:20-68 (inputs of one shape; the reference also takes shorter later inputs, which nothing here produces) */
+        if (n->nin > 8) { thb_set_error("Cmax of %d tensors is not supported", n->nin); return -1; }
+        for (int k = 0; k < n->nin; k++) {
+            const value *v = &P->val[n->in[k]];
+            if (v->s.rank != in->s.rank) { thb_set_error("Cmax of tensors of different dimensionality"); return -1; }
+            if (v->s.C != in->s.C || v->s.H != in->s.H || v->s.W != in->s.W || v->s.N != in->s.N || v->s.flat) {
+                thb_set_error("Cmax of tensors of different sizes");
+                return -1;
+            }
+        }
+        materialise(P, out, in->s);
+        s = new_step(P, ST_CMAX);
+        for (int k = 0; k < n->nin; k++) step_in(s, &P->val[n->in[k]]);
+        step_out(s, out);
+        s->pixels = (long)in->s.N * in->s.H * in->s.W; s->C = in->s.C;
+        return 0;
+    }
+    case OP_LOGSOFTMAX: {
+        if (in->s.flat) { thb_set_error("LogSoftMax on a flattened spatial tensor is not supported"); return -1; }
+        if (P->I->slice_n != E->N && !E->strict_math) { thb_set_error("LogSoftMax as the reference computes it needs the whole batch on one GPU"); return -1; }
+        materialise(P, out, in->s);
+        s = new_step(P, ST_LOGSOFTMAX);
+        step_in(s, in); step_out(s, out);
+        s->pixels = (long)in->s.N * in->s.H * in->s.W; s->C = in->s.C;
+        /* LogSoftMax.c:77 subtracts from the values at the start of the whole input; THB200_STRICT_MATH=1: from each position's own */
+        s->flag = !E->strict_math;
+        return 0;
+    }
+    case OP_NORMALIZE: {
+        /* Normalize.c:12-44: per row of a 2-D tensor, over the whole tensor (batch included) otherwise */
+        if (in->s.flat || in->coff || in->ld != ru(in->s.C, al)) { thb_set_error("Normalize needs a dense tensor"); return -1; }
+        const int per_row = in->s.rank == 2;
+        if (!per_row && P->I->slice_n != E->N) { thb_set_error("Normalize over a whole batch tensor needs the batch on one GPU"); return -1; }
+        materialise(P, out, in->s);
+        s = new_step(P, ST_NORMALIZE);
+        step_in(s, in); step_out(s, out);
+        s->N = in->s.N; s->pixels = (long)in->s.H * in->s.W * in->ld; s->flag = per_row;
+        s->aux_buf = new_buf(P, sizeof(float) * (size_t)(in->s.N > 0 ? in->s.N : 1));
+        return 0;
+    }
+    case OP_UNPOOL: {
+        /* SpatialMaxUnpooling.c:42-121: input 0 has the size of the pooling's output, the result that of its input */
+        const value *xin = &P->val[n->in[1]];
+        if (in->s.rank != 3 && in->s.rank != 4) { thb_set_error("3D or 4D (batch mode) tensor is expected"); return -1; }
+        if (in->s.flat || xin->s.flat || xin->buf < 0) { thb_set_error("SpatialMaxUnpooling needs spatial tensors"); return -1; }
+        const int oH = pool_out(xin->s.H, n->kH, n->dH, n->padH, n->ceil_mode, n->padH || n->padW);
+        const int oW = pool_out(xin->s.W, n->kW, n->dW, n->padW, n->ceil_mode, n->padH || n->padW);
+        if (in->s.H != oH || in->s.W != oW || in->s.C != xin->s.C || in->s.N != xin->s.N) {
+            thb_set_error("Invalid input size w.r.t current indices size");
+            return -1;
+        }
+        shape os = xin->s;
+        os.rank = in->s.rank;
+        materialise(P, out, os);
+        s = new_step(P, ST_UNPOOL);
+        step_in(s, in); step_in(s, xin); step_out(s, out);
+        s->N = os.N; s->H = os.H; s->W = os.W; s->C = os.C; s->oH = oH; s->oW = oW;
+        s->kH = n->kH; s->kW = n->kW; s->dH = n->dH; s->dW = n->dW; s->padH = n->padH; s->padW = n->padW;
         return 0;
     }
     case OP_ALIAS:
@@ -1103,7 +1255,9 @@ static int run_steps_ev(thb_engine *E, instance *I, cudaEvent_t *evs)
         step *s = &I->steps[t];
         const int dt = s->dtype;
         void *x0 = bufptr(I, s->in_buf[0], s->in_coff[0], dt);
+        if (x0 && s->in_off0) x0 = (char *)x0 + s->in_off0 * esize_of(dt);
         void *y = bufptr(I, s->out_buf, s->out_coff, dt);
+        if (y && s->out_off0) y = (char *)y + s->out_off0 * esize_of(dt);
         int rc = 0;
         double t0 = 0;
         if (th_profile) { cudaStreamSynchronize(I->stream); t0 = th_seconds(); }
@@ -1163,6 +1317,31 @@ static int run_steps_ev(thb_engine *E, instance *I, cudaEvent_t *evs)
             break;
         case ST_TO_NCHW:
             rc = thb_to_nchw(dt, x0, s->N, s->H, s->W, s->C, s->in_ld[0], y, st);
+            break;
+        case ST_UPSAMPLE:
+            rc = thb_upsample2x(dt, x0, s->N, s->H, s->W, s->C, s->in_ld[0], y, s->out_ld, st);
+            break;
+        case ST_ZEROPAD:
+            rc = thb_zero_pad(dt, x0, s->N, s->H, s->W, s->C, s->in_ld[0], s->padW, s->kW, s->padH, s->kH, y, s->out_ld, st);
+            break;
+        case ST_SLICEC:
+            rc = thb_slice_channels(dt, x0, s->pixels, s->flag, s->C, s->in_ld[0], y, s->out_ld, st);
+            break;
+        case ST_CMAX: {
+            const void *xs[8];
+            for (int k = 0; k < s->nin; k++) xs[k] = bufptr(I, s->in_buf[k], s->in_coff[k], dt);
+            rc = thb_cmax(dt, s->nin, xs, s->in_ld, s->pixels, s->C, y, s->out_ld, st);
+            break;
+        }
+        case ST_LOGSOFTMAX:
+            rc = thb_logsoftmax(dt, x0, s->pixels, s->C, s->in_ld[0], y, s->out_ld, s->flag, st);
+            break;
+        case ST_NORMALIZE:
+            rc = thb_l2_normalize(dt, x0, s->N, s->pixels, s->flag, (float *)bufptr(I, s->aux_buf, 0, THB_U8), y, st);
+            break;
+        case ST_UNPOOL:
+            rc = thb_max_unpool(dt, x0, s->in_ld[0], bufptr(I, s->in_buf[1], s->in_coff[1], dt), s->in_ld[1], s->N, s->H, s->W, s->C,
+                                s->kH, s->kW, s->dH, s->dW, s->padH, s->padW, s->oH, s->oW, y, s->out_ld, st);
             break;
         }
         if (rc) { thb_set_error("kernel launch %d (kind %d) failed: %d %s", t, s->kind, rc, thb_last_cuda_error()); return -1; }
@@ -1313,6 +1492,15 @@ thb_engine *thb_engine_create(thb_model *model, int mode, float lowp_range, int 
     E->ngpus = ngpus < 1 ? 1 : ngpus > ndev ? ndev : ngpus > 8 ? 8 : ngpus;
     const char *sm = getenv("THB200_STRICT_MATH");
     E->strict_math = sm && atoi(sm);
+    /* Operators that look across the images of a batch (a slice or a join along the batch dimension, the whole-tensor
+     * Normalize, the reference's LogSoftMax, which reads frame 0 for every frame) keep the batch on one GPU in one piece. */
+    for (int i = 0; i < model->nnodes; i++) {
+        const thb_node *nd = &model->nodes[i];
+        if ((nd->op == OP_SLICE && nd->slice_axis == 0) || (nd->op == OP_CONCAT && nd->dim == 0) || nd->op == OP_NORMALIZE ||
+            (nd->op == OP_LOGSOFTMAX && !E->strict_math))
+            E->whole_batch = 1;
+    }
+    if (E->whole_batch) E->ngpus = 1;
     const char *g = getenv("THB200_GATHER");
     E->peer_gather = !(g && !strcmp(g, "host"));
     return E;
@@ -1386,7 +1574,7 @@ static int engine_build(thb_engine *E, int N, int C, int H, int W, int rank, int
     E->chunks = E->dtype == THB_U8 || in_mb < 32 ? 1 : per_gpu >= 32 ? 2 : 1;
     const char *ce = getenv("THB200_CHUNKS");
     if (ce) E->chunks = atoi(ce) < 1 || E->dtype == THB_U8 ? 1 : atoi(ce) > 4 ? 4 : atoi(ce);
-    if (E->chunks > per_gpu) E->chunks = 1;
+    if (E->chunks > per_gpu || E->whole_batch) E->chunks = 1;
     return 0;
 }
 
@@ -1526,7 +1714,7 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
     int G = E->built;
     int peer_gather = E->peer_gather;
     int S = g_chunks_override ? g_chunks_override : E->chunks;
-    if (E->dtype == THB_U8 || S > E->inst[0].slice_n) S = 1;
+    if (E->dtype == THB_U8 || S > E->inst[0].slice_n || E->whole_batch) S = 1;
     if (S > 1) {
         if ((!E->pipe_built || E->pipe_chunks != S) && pipe_build(E, S)) return -1;
         set = E->pipe;

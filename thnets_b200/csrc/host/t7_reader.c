@@ -134,6 +134,16 @@ static int rd_storage(struct reader *r, struct thobject *obj, int idx, const cha
     if (es < 0) return es;
     if (rd_long(r, &s->nelem)) return ERR_READFILE;
     if (s->nelem < 0) return ERR_CORRUPTED;
+    {
+        /* a storage cannot hold more elements than the file has bytes left for (truncated or forged length) */
+        const long here = ftell(r->fp);
+        if (here >= 0 && !fseek(r->fp, 0, SEEK_END)) {
+            const long end = ftell(r->fp);
+            fseek(r->fp, here, SEEK_SET);
+            const long per = s->scalartype == TYPE_LONG && r->longsize == 4 ? 4 : es;
+            if (end >= here && s->nelem > (end - here) / per) return ERR_CORRUPTED;
+        }
+    }
     s->data = malloc((size_t)(s->nelem ? s->nelem : 1) * es);
     if (!s->data) THError("Out of memory loading a storage of %ld elements", s->nelem);
     if (s->scalartype == TYPE_LONG && r->longsize == 4) {
@@ -338,12 +348,32 @@ THFloatTensor *thb_t7_tensor(struct table *t, const char *name)
     struct thobject *o = field(t, name, TYPE_TENSOR);
     if (!o || o->tensor->ndim > 4 || o->tensor->scalartype != TYPE_FLOAT) return th;
     struct tensor *src = o->tensor;
+    {
+        /* the view must lie inside its storage: no negative size or stride, largest element index below nelem */
+        long last = src->storageoffset;
+        int bad = src->ndim < 0 || src->storageoffset < 0;
+        for (int i = 0; i < src->ndim && !bad; i++) {
+            if (src->size[i] < 0 || src->stride[i] < 0) bad = 1;
+            else if (src->size[i] > 0) last += (src->size[i] - 1) * src->stride[i];
+        }
+        if (!bad && src->storage && src->ndim > 0 && last >= src->storage->nelem) bad = 1;
+        if (bad) {
+            fprintf(stderr, "thb200: tensor field %s does not fit its storage; treated as absent\n", name);
+            return th;
+        }
+    }
     th->nDimension = src->ndim;
     memcpy(th->size, src->size, sizeof(long) * src->ndim);
     memcpy(th->stride, src->stride, sizeof(long) * src->ndim);
     th->storageOffset = src->storageoffset;
     if (src->storage) th->storage = THFloatStorage_newwithbuffer(src->storage->data);
     return th;
+}
+/* the nn module object a field refers to (SpatialMaxUnpooling.pooling), or NULL */
+struct nnmodule *thb_t7_nnmodule(struct table *t, const char *name)
+{
+    struct thobject *o = field(t, name, TYPE_NNMODULE);
+    return o ? o->nnmodule : 0;
 }
 void *thb_t7_storage(struct table *t, const char *name, int *nelem)
 {

@@ -10,11 +10,19 @@ double thb_t7_number(struct table *t, const char *name);
 int thb_t7_boolean(struct table *t, const char *name);
 THFloatTensor *thb_t7_tensor(struct table *t, const char *name);
 void *thb_t7_storage(struct table *t, const char *name, int *nelem);
+struct nnmodule *thb_t7_nnmodule(struct table *t, const char *name);
 
 /* ---- device-neutral model: a flat, topologically ordered operator list (model.c) ---- */
 enum thb_op {
     OP_INPUT, OP_CONV, OP_DECONV, OP_LINEAR, OP_BN, OP_ACT, OP_MAXPOOL, OP_AVGPOOL, OP_COMBINE, OP_CONCAT,
-    OP_SOFTMAX, OP_VIEW, OP_ALIAS, OP_SCALE
+    OP_SOFTMAX, OP_VIEW, OP_ALIAS, OP_SCALE,
+    OP_UPSAMPLE,   /* Upsample.c: 2x nearest neighbour */
+    OP_ZEROPAD,    /* SpatialZeroPadding.c: pad_l/r/t/b, negative values crop */
+    OP_SLICE,      /* Slice.c: elements [from, to) along one dimension of the tensor as the reference ranks it */
+    OP_CMAX,       /* Cmax.c: elementwise maximum of the inputs */
+    OP_LOGSOFTMAX, /* LogSoftMax.c */
+    OP_NORMALIZE,  /* Normalize.c: x / ||x||_2 per row of a 2-D tensor, over the whole tensor otherwise */
+    OP_UNPOOL      /* SpatialMaxUnpooling.c: in[0] pooled-size values, in[1] the input of the pooling it undoes */
 };
 #define THB_MAXIN 16
 
@@ -42,6 +50,9 @@ typedef struct thb_node {
     int numElements;
     /* scale (non-v2 Dropout): y = x * factor */
     float factor;
+    /* zero padding / slice */
+    int pad_l, pad_r, pad_t, pad_b;
+    int slice_axis, slice_from, slice_to;
 } thb_node;
 
 typedef struct thb_model {

@@ -29,6 +29,7 @@ namespace {
 
 constexpr int PT_THREADS = 640;        // warps: 0 copy producer, 1-2 MMA issuers, 3 idle, 4-19 epilogue
 constexpr int PT_MAX_STAGES = 4;
+constexpr int PT_NACC = 2;              // accumulator pairs in TMEM: the MMA issuers run one patch ahead of the epilogue (four measured no faster)
 constexpr int PT_CT_BYTES = 256 * 128;  // activated outputs of one patch, one 128-byte row each
 constexpr int PT_PT_BYTES = 64 * 128;   // pooled tile (at most 64 pooled pixels)
 constexpr size_t PT_SMEM_MAX = 232448;
@@ -51,7 +52,7 @@ struct PatchParams {
     float act_th, act_val, act_alpha;
     int kind;               // 0 fp16, 1 bf16
     int pdl;
-    int debug;              // timing experiments: 1 one tap only, 2 no epilogue work, 4 no patch copies, 8 no activation pass, 16 no pooling pass, 32 tap offsets rounded to 8 rows
+    int debug;              // timing experiments: 1 one tap only, 2 no epilogue work, 4 no patch copies, 8 no activation pass, 16 no pooling pass
     int *status;
 };
 
@@ -199,11 +200,12 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t *full = reinterpret_cast<uint64_t *>(smem), *empty = full + PT_MAX_STAGES;
-    uint64_t *acc_full = empty + PT_MAX_STAGES, *acc_empty = acc_full + 2, *w_full = acc_empty + 2;
+    uint64_t *acc_full = empty + PT_MAX_STAGES, *acc_empty = acc_full + PT_NACC, *w_full = acc_empty + PT_NACC;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(w_full + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-    uint32_t *s_tapoff = reinterpret_cast<uint32_t *>(smem + 128);   // per tap: (r*P + s) pixel rows, in 16-byte units (at most 64 taps)
-    float *s_slope = reinterpret_cast<float *>(smem + 384);
+    // header of 2048 bytes: [0, 256) mbarriers, the TMEM slot and the abort flag; [512, 768) PReLU slopes
+    static_assert((2 * PT_MAX_STAGES + 2 * PT_NACC + 1) * 8 + 8 <= 256, "the barriers outgrow their part of the header");
+    float *s_slope = reinterpret_cast<float *>(smem + 512);
     uint8_t *sW = smem + 2048;                          // resident weights: tap t at sW + t * 64 * PX
     uint8_t *sP = sW + p.w_bytes;                       // raw patch buffers
     uint8_t *ct = sP + p.nst * p.stage_bytes;           // output tile(s): one with pooling, two without
@@ -213,14 +215,14 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
     const int units = p.N * p.tiles_r * p.tiles_c;
     const int mine = (int)blockIdx.x < units ? (units - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
     const int taps = p.kH * p.kW;
-    constexpr uint32_t TMEM_COLS = 256;  // two units x two 64-column accumulators
+    constexpr uint32_t TMEM_COLS = PT_NACC * 128;  // per unit two 64-column accumulators
 
     if (tid == 0) {
         for (int s = 0; s < p.nst; s++) {
             mbar_init(smem_u32(&full[s]), 1);
             mbar_init(smem_u32(&empty[s]), 2);            // one commit per MMA issuer
         }
-        for (int b = 0; b < 2; b++) {
+        for (int b = 0; b < PT_NACC; b++) {
             mbar_init(smem_u32(&acc_full[b]), 2);          // one commit per MMA issuer
             mbar_init(smem_u32(&acc_empty[b]), 16);        // one arrival per epilogue warp
         }
@@ -228,12 +230,6 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
-    }
-    if (tid >= 128 && tid < 192) {
-        const int t = tid - 128;
-        int rows = (t / p.kW) * p.P + t % p.kW;
-        if (p.debug & 32) rows &= ~7;
-        s_tapoff[t] = t < taps ? (uint32_t)(rows * (PX / 16)) : 0u;
     }
     if (tid < 64) {
         // per-channel epilogue constants (uploaded when the network was planned: no kernel of this stream writes them)
@@ -295,7 +291,9 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
             const uint32_t idesc = p.kind == 1 ? IDESC_BF16 : IDESC_F16;
             constexpr int KSTEPS = PX / 32;      // tcgen05.mma of K = 16 elements per tap
             constexpr uint32_t HALF = 128u * PX / 16, BSTEP = 64u * PX / 16;   // descriptor steps: second accumulator's rows, next tap's weights
-            const int hsel = warp - 1;
+            constexpr uint32_t PXU = PX / 16;
+            const int hsel = warp - 1, kW = p.kW;
+            const uint32_t rowstep = (uint32_t)(p.P - p.kW + 1) * PXU;
             const uint64_t proto = make_rows_desc(0u, PX);
             const uint32_t hi = (uint32_t)(proto >> 32), lo_flags = (uint32_t)proto;
             const uint32_t b_lo0 = lo_flags | ((smem_u32(sW) >> 4) & 0x3FFFu);
@@ -308,8 +306,8 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
                 *abort_flag = 1;
             }
             for (int u = 0; u < mine && alive; u++) {
-                const int ab = u & 1;
-                if (!mbar_wait_bounded(smem_u32(&acc_empty[ab]), ((u >> 1) & 1) ^ 1)) {
+                const int ab = u % PT_NACC;
+                if (!mbar_wait_bounded(smem_u32(&acc_empty[ab]), ((u / PT_NACC) & 1) ^ 1)) {
                     atomicExch(p.status, 6);
                     *abort_flag = 1;
                     break;
@@ -325,12 +323,16 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
                 tc_fence_after();
                 const uint32_t d = tmem_base + ab * 128 + hsel * 64;
                 const uint32_t a_lo0 = (lo_flags | ((smem_u32(sP + s * p.stage_bytes) >> 4) & 0x3FFFu)) + hsel * HALF;
-                uint32_t b_lo = b_lo0;
-                mma_tap<KSTEPS>(d, a_lo0 + s_tapoff[0], b_lo, hi, idesc, 0u);   // first tap: the accumulator starts from zero
+                // tap (r, s) reads the patch from pixel row r*P + s on: one pixel (PXU address units) further per tap, and
+                // P - kW + 1 pixels further at the end of a kernel row -- all in registers, the loop touches no memory
+                uint32_t b_lo = b_lo0, a_lo = a_lo0;
+                int sx = 1;
+                mma_tap<KSTEPS>(d, a_lo, b_lo, hi, idesc, 0u);   // first tap: the accumulator starts from zero
 #pragma unroll 4
                 for (int t = 1; t < ntaps; t++) {
                     b_lo += BSTEP;
-                    mma_tap<KSTEPS>(d, a_lo0 + s_tapoff[t], b_lo, hi, idesc, 1u);
+                    if (sx == kW) { sx = 1; a_lo += rowstep; } else { sx++; a_lo += PXU; }
+                    mma_tap<KSTEPS>(d, a_lo, b_lo, hi, idesc, 1u);
                 }
                 tc_commit(smem_u32(&empty[s]));
                 tc_commit(smem_u32(&acc_full[ab]));
@@ -360,9 +362,9 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
         const int it_px = et >> 3, it_j = et & 7;
         const int it_pr = KP ? it_px / p.PC : 0, it_pc = it_px - it_pr * p.PC;
         for (int u = 0; u < mine; u++) {
-            const int ab = u & 1;
+            const int ab = u % PT_NACC;
             const Unit q = unit_of(p, blockIdx.x + u * gridDim.x);
-            if (!mbar_wait_bounded(smem_u32(&acc_full[ab]), (u >> 1) & 1)) {
+            if (!mbar_wait_bounded(smem_u32(&acc_full[ab]), (u / PT_NACC) & 1)) {
                 if (lane == 0) atomicExch(p.status, 2);
                 *abort_flag = 1;
             }

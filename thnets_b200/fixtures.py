@@ -121,6 +121,28 @@ class Graph:
     def tanh(self, x):
         return self._add("tanh", [x])
 
+    def upsample(self, x):
+        return self._add("upsample", [x])
+
+    def zeropad(self, x, pad_l, pad_r, pad_t, pad_b):
+        return self._add("zeropad", [x], dict(pad_l=int(pad_l), pad_r=int(pad_r), pad_t=int(pad_t), pad_b=int(pad_b)))
+
+    def slice(self, x, axis, start, stop):
+        return self._add("slice", [x], dict(axis=int(axis), start=int(start), stop=int(stop)))
+
+    def cmax(self, xs):
+        return self._add("cmax", list(xs))
+
+    def logsoftmax(self, x):
+        return self._add("logsoftmax", [x])
+
+    def l2normalize(self, x):
+        return self._add("l2normalize", [x])
+
+    def unpool(self, x, pool_node):
+        """SpatialMaxUnpooling of x against the max pooling that is node `pool_node` of this graph."""
+        return self._add("unpool", [x], dict(pool=int(pool_node)))
+
     def add(self, a, b):
         """Reference semantics for two inputs: a - b (CAddTable.c:59-69)."""
         return self._add("add", [a, b])
@@ -147,7 +169,7 @@ class Graph:
 _PYNAME = {
     "conv": "ConvNd", "deconv": "ConvTransposedNd", "linear": "Linear", "bn": "BatchNorm",
     "maxpool": "MaxPool2d", "avgpool": "AvgPool2d", "threshold": "Threshold", "dropout": "Dropout",
-    "softmax": "Softmax", "view": "View", "add": "Add", "concat": "Concat",
+    "softmax": "Softmax", "view": "View", "add": "Add", "concat": "Concat", "slice": "Slice", "cmax": "Cmax",
 }
 
 
@@ -182,7 +204,13 @@ def write_pymodel(graph: Graph, path: str):
             emitted.add(i)
             f.write(b"\x02" + struct.pack("<i", i))
             _w_str(f, "torch.nn.fn." + _PYNAME[node.op])
-            for k, v in node.attrs.items():
+            attrs = node.attrs
+            if node.op == "slice":
+                # Slice.c:3-14: the dump carries index = {from, to} and no axis (dimension 0 of the tensor)
+                if attrs["axis"] != 0:
+                    raise ValueError("the graph-dump Slice cuts dimension 0 only")
+                attrs = {"index": (attrs["start"], attrs["stop"])}
+            for k, v in attrs.items():
                 if isinstance(v, tuple):
                     f.write(b"\x06")
                     _w_str(f, k)
@@ -290,11 +318,18 @@ class _T7:
 
     def module(self, name, items):
         self.i32(4)
+        idx = self.idx
         self.i32(self.idx)
         self.idx += 1
         self.string_raw("V 1")
         self.string_raw(name)
         self.table(items)
+        return idx
+
+    def reference(self, idx):
+        """an object written earlier, by its index (how Torch serialises a second mention of the same object)"""
+        self.i32(4)
+        self.i32(idx)
 
 
 def _t7_module(t: _T7, spec):
@@ -310,14 +345,18 @@ def _t7_module(t: _T7, spec):
         t.module(name, items)
         return
     items = []
+    if not hasattr(t, "written"):
+        t.written = {}
     for k, v in spec[1].items():
         if isinstance(v, np.ndarray) or v is None:
             items.append((k, (lambda v=v: t.tensor(v))))
         elif isinstance(v, bool):
             items.append((k, (lambda v=v: t.boolean(v))))
+        elif isinstance(v, tuple) and v and v[0] == "ref":
+            items.append((k, (lambda v=v: t.reference(t.written[id(v[1])]))))   # a module spec written earlier
         else:
             items.append((k, (lambda v=v: t.number(v))))
-    t.module(name, items)
+    t.written[id(spec)] = t.module(name, items)
 
 
 def graph_to_t7_spec(graph: Graph):
@@ -325,7 +364,8 @@ def graph_to_t7_spec(graph: Graph):
     if not graph.is_sequential():
         raise ValueError("only sequential graphs map onto a flat nn.Sequential")
     mods = []
-    for node in graph.nodes[1:]:
+    spec_of = {}
+    for ni, node in enumerate(graph.nodes[1:], start=1):
         a = node.attrs
         ts = [arr for _, arr in node.tensors]
         if node.op == "conv":
@@ -363,8 +403,17 @@ def graph_to_t7_spec(graph: Graph):
                 adjW=a["output_padding"][1], adjH=a["output_padding"][0], kW=w.shape[3], kH=w.shape[2],
                 nInputPlane=w.shape[0], nOutputPlane=w.shape[1], weight=w,
                 bias=ts[1] if len(ts) > 1 else None)))
+        elif node.op == "zeropad":
+            mods.append(("nn.SpatialZeroPadding", dict(pad_l=a["pad_l"], pad_r=a["pad_r"], pad_t=a["pad_t"], pad_b=a["pad_b"])))
+        elif node.op == "l2normalize":
+            mods.append(("nn.Normalize", {}))
+        elif node.op == "logsoftmax":
+            mods.append(("nn.LogSoftMax", {}))
+        elif node.op == "unpool":
+            mods.append(("nn.SpatialMaxUnpooling", dict(pooling=("ref", spec_of[a["pool"]]))))
         else:
             raise ValueError("no Torch7 mapping for " + node.op)
+        spec_of[ni] = mods[-1]
     return ("nn.Sequential", mods)
 
 
@@ -510,6 +559,70 @@ def segnet(seed=3, width=1.0, size=512, classes=21, deconv_bias=None):
     return g
 
 
+def unpool_net(seed=5, size=16, classes=6, zeropad=True):
+    """Sequential Torch7-style network through the operators outside the benchmark configurations: zero padding (with a
+    crop), max pooling and the unpooling that undoes it, LogSoftMax."""
+    g = Graph(seed)
+    g.input_shape = (3, size, size)
+    x = g.relu(g.conv(0, 3, 8, 3, 1, 1, bias=0.1))
+    if zeropad:
+        x = g.zeropad(x, 2, -1, 1, 0)                # left 2, right crop 1, top 1: (size+1) x (size+1), square
+    else:
+        size -= 1
+    p = g.maxpool(x, 2, 2, 0, 1)
+    x = g.relu(g.conv(p, 8, 8, 3, 1, 1, bias=0.1))
+    x = g.unpool(x, p)
+    x = g.conv(x, 8, 4, 3, 1, 0, bias=0.1)
+    n = 4 * (size - 1) * (size - 1)
+    x = g.view(x, n)
+    x = g.linear(x, n, classes, bias=0.1)
+    g.logsoftmax(x)
+    return g
+
+
+def normalize_net(seed=6, size=12, feat=10):
+    """conv -> View -> Linear -> Normalize (rows of a 2-D tensor for a batch, the whole tensor for one image)."""
+    g = Graph(seed)
+    g.input_shape = (3, size, size)
+    x = g.relu(g.conv(0, 3, 6, 3, 2, 1, bias=0.1))
+    n = 6 * (size // 2) * (size // 2)
+    x = g.view(x, n)
+    x = g.linear(x, n, feat, bias=0.1)
+    g.l2normalize(x)
+    return g
+
+
+def cmax_slice_net(seed=7, size=10, batch_slice=(1, 3)):
+    """Graph-dump style network: two convolution branches meet in an elementwise maximum, then a Slice, which on this
+    route always cuts dimension 0 (the batch of a 4-D tensor)."""
+    g = Graph(seed)
+    g.input_shape = (3, size, size)
+    x = g.relu(g.conv(0, 3, 8, 3, 1, 1, bias=0.1))
+    a = g.conv(x, 8, 12, 3, 1, 1, bias=0.1)
+    b = g.conv(x, 8, 12, 1, 1, 0, bias=0.1)
+    m = g.cmax([a, b])
+    m = g.slice(m, 0, batch_slice[0], batch_slice[1])
+    g.conv(m, 12, 5, 3, 1, 1, bias=0.1)
+    return g
+
+
+def onnx_ops_net(seed=8, size=8):
+    """ONNX-only operators: Upsample (2x), Max, Slice along channels / rows / columns, LogSoftmax."""
+    g = Graph(seed)
+    g.input_shape = (3, size, size)
+    x = g.relu(g.conv(0, 3, 12, 3, 1, 1, bias=0.1))
+    u = g.upsample(g.maxpool(x, 2, 2))
+    m = g.cmax([x, u])
+    m = g.slice(m, 1, 3, 11)          # channels 3..10 (not aligned to a 16-byte group)
+    m = g.slice(m, 2, 1, size - 1)    # rows
+    m = g.slice(m, 3, 0, size - 2)    # columns
+    x = g.conv(m, 8, 6, 3, 1, 1, bias=0.1)
+    x = g.view(x, 6 * (size - 2) * (size - 2))
+    x = g.linear(x, 6 * (size - 2) * (size - 2), 7, bias=0.1)
+    g.logsoftmax(x)
+    return g
+
+
 BUILDERS = {"alexnet_owt": alexnet_owt, "resnet18": resnet18, "vgg16": vgg16, "segnet": segnet,
             "resnet50": resnet50}
 
@@ -558,6 +671,8 @@ def _onnx_attr(name, v):
         return out + _pb_int(3, v) + _pb_int(20, 2)
     if isinstance(v, str):
         return out + _pb_len(4, v.encode()) + _pb_int(20, 3)
+    if len(v) and isinstance(v[0], float):
+        return out + _pb_len(7, struct.pack("<%df" % len(v), *v)) + _pb_int(20, 6)   # floats, packed
     return out + b"".join(_pb_int(8, i) for i in v) + _pb_int(20, 7)
 
 
@@ -625,6 +740,14 @@ def write_onnx(graph: Graph, path: str, bias_as_add=False, pad_nodes=False):
             node("Add", ins, out)
         elif nd.op == "concat":
             node("Concat", ins, out, axis=int(a["dim"]))
+        elif nd.op == "upsample":
+            node("Upsample", ins, out, mode="nearest", scales=[1.0, 1.0, 2.0, 2.0])
+        elif nd.op == "cmax":
+            node("Max", ins, out)
+        elif nd.op == "slice":
+            node("Slice", ins, out, axes=[int(a["axis"])], starts=[int(a["start"])], ends=[int(a["stop"])])
+        elif nd.op == "logsoftmax":
+            node("LogSoftmax", ins, out, axis=1)
         else:
             raise ValueError("no ONNX form for " + nd.op)
     value_info = lambda n: _pb_len(1, n.encode())
