@@ -213,6 +213,10 @@ int thb_upsample2x(int dtype, const void *x, int N, int H, int W, int C, int x_l
  * reference's own loop strides rows by the height and leaves the right padding unwritten): y is [N][H+pad_t+pad_b][W+pad_l+pad_r][y_ld] */
 int thb_zero_pad(int dtype, const void *x, int N, int H, int W, int C, int x_ld, int pad_l, int pad_r, int pad_t, int pad_b, void *y,
                  int y_ld, thb_stream s);
+/* reflection padding (what an ONNX Pad node of mode "reflect" in front of a convolution asks for; the reference parses it
+ * into SpatialConvolution.refl_pad and no engine of its own honours it: used only when THB200_HONOUR_PADS=1) */
+int thb_reflect_pad(int dtype, const void *x, int N, int H, int W, int C, int x_ld, int pad_l, int pad_r, int pad_t, int pad_b, void *y,
+                    int y_ld, thb_stream s);
 /* channels [from, from + C) of every pixel of x -> y (modules/Slice.c:34-39 along the channel dimension, any `from`) */
 int thb_slice_channels(int dtype, const void *x, long pixels, int from, int C, int x_ld, void *y, int y_ld, thb_stream s);
 /* elementwise maximum of up to 8 tensors of one shape (modules/Cmax.c:20-68) */

@@ -257,8 +257,31 @@ class Oracle:
         return y
 
     # ---- graph execution -------------------------------------------------------
-    def run(self, graph, batch, keep=False, strict_bias=0):
-        """fp32 forward of `graph` on a raw [N,C,H,W] batch (normalised here first)."""
+    def conv2d_as_onnx_asks(self, x, w, b, a):
+        """What an ONNX convolution with ending pads / dilation / auto_pad / a reflect-mode Pad in front MEANS (the
+        reference ignores all four): the input padded explicitly with NumPy, the kernel written out with zeros between
+        its taps, then the plain convolution without padding."""
+        sh, sw = a["stride"]
+        dl = a.get("dilation", (1, 1))
+        kh, kw = (w.shape[2] - 1) * dl[0] + 1, (w.shape[3] - 1) * dl[1] + 1
+        pt, pl, pb, pr = a.get("pads4", tuple(a["padding"]) * 2)
+        if a.get("auto_pad"):
+            h, ww = x.shape[2:]
+            th = max((-(-h // sh) - 1) * sh + kh - h, 0)
+            tw = max((-(-ww // sw) - 1) * sw + kw - ww, 0)
+            if a["auto_pad"] == "SAME_UPPER":
+                pt, pl = th // 2, tw // 2
+            else:
+                pt, pl = th - th // 2, tw - tw // 2
+            pb, pr = th - pt, tw - pl
+        xp = np.pad(x, ((0, 0), (0, 0), (pt, pb), (pl, pr)), mode="reflect" if a.get("reflect") else "constant")
+        wd = np.zeros(w.shape[:2] + (kh, kw), np.float32)
+        wd[:, :, ::dl[0], ::dl[1]] = w
+        return self.conv2d(xp, wd, b, (sh, sw), (0, 0))
+
+    def run(self, graph, batch, keep=False, strict_bias=0, honour_pads=False):
+        """fp32 forward of `graph` on a raw [N,C,H,W] batch (normalised here first).  honour_pads: convolutions compute what
+        their ONNX-only attributes ask for instead of ignoring them as the reference does."""
         vals = {0: self.normalize(batch, graph.mean, graph.std)}
         for i, node in enumerate(graph.nodes):
             if i == 0:
@@ -267,7 +290,9 @@ class Oracle:
             ts = [t for _, t in node.tensors]
             xin = [vals[j] for j in node.inputs]
             x = xin[0]
-            if node.op == "conv":
+            if node.op == "conv" and honour_pads and any(k in a for k in ("pads4", "dilation", "auto_pad", "reflect")):
+                y = self.conv2d_as_onnx_asks(x, ts[0], ts[1] if len(ts) > 1 else None, a)
+            elif node.op == "conv":
                 y = self.conv2d(x, ts[0], ts[1] if len(ts) > 1 else None, a["stride"], a["padding"])
             elif node.op == "deconv":
                 y = self.fullconv2d(x, ts[0], ts[1] if len(ts) > 1 else None, a["stride"], a["padding"],

@@ -450,3 +450,43 @@ def test_concat_along_the_batch_dimension(th, oracle, tmp_path):
     assert out.size == ref.size
     assert rel_err(out, ref.ravel()) < 1e-4
     th.free_network(hc)
+
+
+def _onnx_attr_net():
+    """Convolutions with the attributes only ONNX files carry: ending pads that differ from the leading ones, dilation,
+    auto_pad (both kinds, stride 2 on an odd size) and a reflect-mode Pad node in front."""
+    g = fx.Graph(10)
+    g.input_shape = (3, 15, 13)
+    x = g.relu(g.conv(0, 3, 8, 3, 1, 0, bias=0.1, pads4=(1, 0, 2, 1)))
+    x = g.relu(g.conv(x, 8, 8, 3, 1, 2, bias=0.1, dilation=2))
+    x = g.relu(g.conv(x, 8, 16, 3, 2, 0, bias=0.1, auto_pad="SAME_UPPER"))
+    x = g.relu(g.conv(x, 16, 16, 3, 1, 0, bias=0.1, pads4=(2, 2, 2, 2), reflect=True))
+    g.conv(x, 16, 5, 4, 2, 0, bias=0.1, auto_pad="SAME_LOWER")
+    return g
+
+
+@pytest.mark.parametrize("mode", [0, 1], ids=["fp32", "fp16"])
+@pytest.mark.parametrize("honour", [False, True], ids=["ignored_as_by_the_reference", "honoured"])
+def test_onnx_only_convolution_attributes(th, oracle, tmp_path, monkeypatch, mode, honour):
+    """By default the ending pads, dilation, auto_pad and reflection padding of an ONNX convolution are ignored exactly as
+    the reference ignores them (SpatialConvolution.c:88-109 parses, nothing reads); with THB200_HONOUR_PADS=1 (read when a
+    network is converted) the result is what the ONNX model means, checked against a NumPy model of it."""
+    g = _onnx_attr_net()
+    x = g.make_input(3)
+    ref = oracle.run(g, x, honour_pads=honour)
+    p = str(tmp_path / "attrs.onnx")
+    fx.write_onnx(g, p)
+    h = th.load_network(p)
+    th.set_stats(h, g.mean, g.std)
+    if honour:
+        monkeypatch.setenv("THB200_HONOUR_PADS", "1")
+    th.lib.THB200_SetPrecision(mode)
+    hc = th.lib.THCreateCudaNetwork(h)
+    th.lib.THB200_SetPrecision(0)
+    assert hc, th.lib.THB200_LastErrorString()
+    th.free_network(h)
+    out, ow, oh = th.process_float(hc, x)
+    assert out.size == ref.size, (out.size, ref.shape)
+    assert (ow, oh) == (ref.shape[3], ref.shape[2])
+    assert rel_err(out, ref.ravel()) < TOL[mode]
+    th.free_network(hc)

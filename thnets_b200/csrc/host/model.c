@@ -85,6 +85,9 @@ static int lower_leaf(builder *b, struct module *m, val in, val *out)
         n->Cin = c->nInputPlane; n->Cout = c->nOutputPlane;
         n->kH = c->kH; n->kW = c->kW; n->dH = c->dH ? c->dH : 1; n->dW = c->dW ? c->dW : 1;
         n->padH = c->padH; n->padW = c->padW;
+        n->pad2H = c->padH2; n->pad2W = c->padW2; n->dlH = c->dlH ? c->dlH : 1; n->dlW = c->dlW ? c->dlW : 1;
+        n->autopad = c->autopad; n->refl_pad = c->refl_pad;
+        if (!c->dlH && !c->dlW) { n->pad2H = n->padH; n->pad2W = n->padW; } /* a record no loader of ours filled: symmetric */
         n->weight = copy_tensor(c->weight, &cnt);
         if (!n->weight || cnt != (long)n->Cin * n->Cout * n->kH * n->kW)
             return fail(b, "convolution weight has %ld elements, expected %dx%dx%dx%d", cnt, n->Cout, n->Cin, n->kH, n->kW);

@@ -85,6 +85,7 @@ static int build_torch_module(struct module *m, struct nnmodule *n)
         c->weight = thb_t7_tensor(t, "weight");
         view_as_matrix(c->weight);
         c->finput = THFloatTensor_new();
+        c->padH2 = c->padH; c->padW2 = c->padW; c->dlH = c->dlW = 1;
     } else if (!strcmp(cls, "nn.SpatialFullConvolution")) {
         struct SpatialFullConvolution *c = &m->SpatialFullConvolution;
         m->type = MT_SpatialFullConvolution;
@@ -315,6 +316,12 @@ void thb_build_py_module(const char *fname, struct pyfunction *f)
         c->kH = c->weight->size[2]; c->kW = c->weight->size[3];
         ivec2(p, "padding", &c->padH, &c->padW);
         ivec2(p, "stride", &c->dH, &c->dW);
+        /* the ONNX reader also passes the attributes the reference parses and ignores (SpatialConvolution.c:88-109) */
+        c->padH2 = c->padH; c->padW2 = c->padW; c->dlH = c->dlW = 1;
+        ivec2(p, "padding2", &c->padH2, &c->padW2);
+        ivec2(p, "dilation", &c->dlH, &c->dlW);
+        c->autopad = ival(p, "autopad", 0);
+        c->refl_pad = ival(p, "refl_pad", 0);
     } else if (!strcmp(op, "ConvTransposedNd")) {
         struct SpatialFullConvolution *c = &m->SpatialFullConvolution;
         m->type = MT_SpatialFullConvolution;

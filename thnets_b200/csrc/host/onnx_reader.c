@@ -490,8 +490,17 @@ static struct pyelement *ox_conv(ox_build *b, int idx, const ox_node *bn, const 
 {
     const ox_node *n = &b->g->nodes[idx];
     const int transposed = !strcmp(n->op, "ConvTranspose");
-    int padH, padW, dH, dW, aH = 0, aW = 0;
+    int padH, padW, padH2, padW2, dH, dW, dlH, dlW, aH = 0, aW = 0, refl = 0, autopad = 0;
     ox_ints2(n, "pads", 0, 0, &padH, &padW);
+    /* onnx: pads = {top, left, bottom, right}; SpatialConvolution.c:94-97 keeps the ending pair as padH2 / padW2 */
+    padH2 = padH; padW2 = padW;
+    {
+        const ox_attr *pa = ox_attr_of(n, "pads");
+        if (pa && pa->nints >= 4) { padH2 = (int)pa->ints[2]; padW2 = (int)pa->ints[3]; }
+        const ox_attr *ap = ox_attr_of(n, "auto_pad");
+        if (ap && ap->s) autopad = !strcmp(ap->s, "SAME_UPPER") ? 1 : !strcmp(ap->s, "SAME_LOWER") ? 2 : 0;   /* :88-93 */
+    }
+    ox_ints2(n, "dilations", 0, 1, &dlH, &dlW);
     ox_ints2(n, "strides", 0, 1, &dH, &dW);
     if (transposed) ox_ints2(n, "output_padding", 0, 0, &aH, &aW);
     /* a constant-mode Pad in front of a Conv adds to its padding and disappears (onnx.cc:667-700) */
@@ -501,10 +510,18 @@ static struct pyelement *ox_conv(ox_build *b, int idx, const ox_node *bn, const 
         const ox_node *pn = &b->g->nodes[pidx];
         const ox_attr *mode = ox_attr_of(pn, "mode"), *pads = ox_attr_of(pn, "pads");
         const ox_tensor *pt = pn->nin > 1 ? ox_init(b->g, pn->in[1]) : 0;
-        if (mode && mode->s && *mode->s && strcmp(mode->s, "constant")) { ox_fail(b, "Unsupported padding type %s", mode->s); return 0; }
-        if (pads && pads->nints >= 4) { padH += (int)pads->ints[2]; padW += (int)pads->ints[3]; }
-        else if (pt && pt->data_type == 7 && pt->count >= 4) { padH += (int)pt->i64[2]; padW += (int)pt->i64[3]; }
-        else { ox_fail(b, "Pad %s without pads", pn->out[0]); return 0; }
+        /* onnx.cc:677-690: "reflect" is noted in refl_pad, anything but "constant" and "reflect" is an error */
+        if (mode && mode->s && !strcmp(mode->s, "reflect")) refl = 1;
+        else if (mode && mode->s && *mode->s && strcmp(mode->s, "constant")) { ox_fail(b, "Unsupported padding type %s", mode->s); return 0; }
+        if (pads && pads->nints >= 4) {
+            padH += (int)pads->ints[2]; padW += (int)pads->ints[3];
+            if (pads->nints >= 8) { padH2 += (int)pads->ints[6]; padW2 += (int)pads->ints[7]; }
+            else { padH2 += (int)pads->ints[2]; padW2 += (int)pads->ints[3]; }
+        } else if (pt && pt->data_type == 7 && pt->count >= 4) {
+            padH += (int)pt->i64[2]; padW += (int)pt->i64[3];
+            if (pt->count >= 8) { padH2 += (int)pt->i64[6]; padW2 += (int)pt->i64[7]; }
+            else { padH2 += (int)pt->i64[2]; padW2 += (int)pt->i64[3]; }
+        } else { ox_fail(b, "Pad %s without pads", pn->out[0]); return 0; }
         src = pn->in[0];
     }
     struct pyelement *e = ox_function(b, idx, transposed ? "ConvTransposedNd" : "ConvNd", &src, 1);
@@ -513,6 +530,13 @@ static struct pyelement *ox_conv(ox_build *b, int idx, const ox_node *bn, const 
     par_ivec(&e->function, "padding", padH, padW);
     par_ivec(&e->function, "stride", dH, dW);
     if (transposed) par_ivec(&e->function, "output_padding", aH, aW);
+    else {
+        /* what the reference's loader parses and none of its engines reads (SpatialConvolution.c:88-109) */
+        par_ivec(&e->function, "padding2", padH2, padW2);
+        par_ivec(&e->function, "dilation", dlH, dlW);
+        par_int(&e->function, "autopad", autopad);
+        par_int(&e->function, "refl_pad", refl);
+    }
     return e;
 }
 

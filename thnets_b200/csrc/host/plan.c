@@ -74,7 +74,7 @@ typedef struct {
 
 enum step_kind {
     ST_CONV, ST_GEMV, ST_MAXPOOL, ST_AVGPOOL, ST_AFFINE, ST_U8THR, ST_U8COMBINE, ST_COMBINE, ST_COPY, ST_SOFTMAX, ST_COL2IM,
-    ST_CSUM, ST_TO_NCHW, ST_ZERO, ST_UPSAMPLE, ST_ZEROPAD, ST_SLICEC, ST_CMAX, ST_LOGSOFTMAX, ST_NORMALIZE, ST_UNPOOL
+    ST_CSUM, ST_TO_NCHW, ST_ZERO, ST_UPSAMPLE, ST_ZEROPAD, ST_REFLECTPAD, ST_SLICEC, ST_CMAX, ST_LOGSOFTMAX, ST_NORMALIZE, ST_UNPOOL
 };
 
 typedef struct {
@@ -152,6 +152,7 @@ struct thb_engine {
     float last_ms;
     int peer_gather;
     /* arguments of the last forward, for the device-resident timing loop */
+    int honour_pads; /* THB200_HONOUR_PADS=1: ending pads, dilation, auto_pad and reflection padding of ONNX convolutions are computed */
     int whole_batch; /* the model has an operator that looks across the batch: one GPU, no sub-batches */
     int last_has_x, last_cp, last_bgr;
     float last_mean[3], last_std[3];
@@ -319,6 +320,8 @@ static int plan_gemm_group(planner *P, int i)
 
     /* ---- geometry ---- */
     int kH = n->kH, kW = n->kW, Cin = n->Cin, H = is.H, W = is.W, in_ld = in->ld, permute_hw = 0;
+    int honour = 0, ekH = n->kH, ekW = n->kW, padT = n->padH, padB = n->padH, padL = n->padW, padR = n->padW;
+    value refl_val;
     if (is_linear) {
         long feat = is.flat ? (long)is.fC * is.fH * is.fW : (long)is.C * is.H * is.W;
         if (feat != n->Cin) { thb_set_error("Linear expects %d inputs, got %ld", n->Cin, feat); return -1; }
@@ -350,8 +353,53 @@ static int plan_gemm_group(planner *P, int i)
         if (is.rank < 3) { thb_set_error("convolution needs a 3D or 4D input"); return -1; }
         if (is.C != n->Cin) { thb_set_error("nInputPlane %d does not match input planes %d", n->Cin, is.C); return -1; }
         os.C = n->Cout;
-        os.H = conv_out(is.H, kH, n->dH, n->padH);
-        os.W = conv_out(is.W, kW, n->dW, n->padW);
+        /* Ending pads that differ from the leading ones, dilation, auto_pad and reflection padding: the reference's ONNX
+         * loader parses them and none of its engines reads them (SpatialConvolution.c:88-109, onnx.cc:677-690), so by
+         * default they are ignored here too -- and said so.  THB200_HONOUR_PADS=1 computes what the ONNX model asks for:
+         * auto_pad resolved from the input size, a reflection-padded copy of the input, the output size from both pads
+         * (the kernels pad with zeros wherever a window leaves the image, so only the size changes), and a dilated
+         * kernel written out with zeros between its taps. */
+        const int dlH = n->dlH > 0 ? n->dlH : 1, dlW = n->dlW > 0 ? n->dlW : 1;
+        const int nontrivial = n->op == OP_CONV && (n->pad2H != n->padH || n->pad2W != n->padW || dlH != 1 || dlW != 1 || n->autopad || n->refl_pad);
+        if (nontrivial && !(E->honour_pads && dtype != THB_U8)) {
+            static int told = 0;
+            if (!told++)
+                fprintf(stderr, "thb200: a convolution's ending pads / dilation / auto_pad / reflection padding are ignored, as by the "
+                                "reference (THB200_HONOUR_PADS=1 honours them)\n");
+        }
+        if (nontrivial && E->honour_pads && dtype != THB_U8) {
+            honour = 1;
+            ekH = (kH - 1) * dlH + 1; ekW = (kW - 1) * dlW + 1;
+            padT = n->padH; padB = n->pad2H; padL = n->padW; padR = n->pad2W;
+            if (n->autopad) {
+                /* SAME_UPPER (1): the odd pixel of padding goes to the end; SAME_LOWER (2): to the beginning */
+                int th_ = ((is.H + n->dH - 1) / n->dH - 1) * n->dH + ekH - is.H, tw_ = ((is.W + n->dW - 1) / n->dW - 1) * n->dW + ekW - is.W;
+                if (th_ < 0) th_ = 0;
+                if (tw_ < 0) tw_ = 0;
+                padT = n->autopad == 1 ? th_ / 2 : th_ - th_ / 2; padB = th_ - padT;
+                padL = n->autopad == 1 ? tw_ / 2 : tw_ - tw_ / 2; padR = tw_ - padL;
+            }
+            if (n->refl_pad && (padT || padB || padL || padR)) {
+                if (padT >= is.H || padB >= is.H || padL >= is.W || padR >= is.W) { thb_set_error("reflection padding larger than the image"); return -1; }
+                shape ps = is;
+                ps.H = is.H + padT + padB; ps.W = is.W + padL + padR;
+                memset(&refl_val, 0, sizeof(refl_val));
+                materialise(P, &refl_val, ps);
+                step *rs = new_step(P, ST_REFLECTPAD);
+                step_in(rs, in); step_out(rs, &refl_val);
+                rs->N = is.N; rs->H = is.H; rs->W = is.W; rs->C = is.C;
+                rs->padW = padL; rs->kW = padR; rs->padH = padT; rs->kH = padB;
+                in = &refl_val;
+                is = ps; H = is.H; W = is.W; in_ld = in->ld;
+                padT = padB = padL = padR = 0;
+            }
+            os.H = (is.H + padT + padB - ekH) / n->dH + 1;
+            os.W = (is.W + padL + padR - ekW) / n->dW + 1;
+            kH = ekH; kW = ekW;
+        } else {
+            os.H = conv_out(is.H, kH, n->dH, n->padH);
+            os.W = conv_out(is.W, kW, n->dW, n->padW);
+        }
         if (os.H < 1 || os.W < 1) { thb_set_error("Given input size: (%dx%dx%d). Output size is too small", is.C, is.H, is.W); return -1; }
     }
 
@@ -567,6 +615,20 @@ static int plan_gemm_group(planner *P, int i)
         w_oihw = w_tmp;
     } else {
         d->Cout = n->Cout; d->oH = os.H; d->oW = os.W;
+        if (honour) {
+            d->padH = padT; d->padW = padL;
+            if (ekH != n->kH || ekW != n->kW) {
+                /* dilation: the kernel written out at its full extent, zeros between the taps */
+                const float *src = w_fold ? w_fold : n->weight;
+                const int dlH = n->dlH > 0 ? n->dlH : 1, dlW = n->dlW > 0 ? n->dlW : 1;
+                w_tmp = calloc((size_t)n->Cout * Cin * ekH * ekW, sizeof(float));
+                for (long oc = 0; oc < (long)n->Cout * Cin; oc++)
+                    for (int r = 0; r < n->kH; r++)
+                        for (int q = 0; q < n->kW; q++)
+                            w_tmp[(oc * ekH + r * dlH) * ekW + q * dlW] = src[(oc * n->kH + r) * n->kW + q];
+                w_oihw = w_tmp;
+            }
+        }
     }
     if (dual_conv >= 0) {
         /* [Cout][cin1 + cin2] weights: each convolution's rows scaled by its batch-norm and its coefficient of the sum */
@@ -1193,6 +1255,7 @@ static int instance_build(thb_engine *E, instance *I, int device, int slice_off,
                        4 * E->C <= 16 && c1->Cin == E->C && E->H % 2 == 0 && E->W % 2 == 0 && E->rank == 4 && E->cp == 0 &&
                        (E->dtype == THB_F16 || E->dtype == THB_BF16 || (E->dtype == THB_U8 && !(u8off && atoi(u8off)))) &&
                        c1->padH <= c1->kH - 1 && c1->padW <= c1->kW - 1 &&
+                       !(E->honour_pads && (c1->pad2H != c1->padH || c1->pad2W != c1->padW || c1->dlH > 1 || c1->dlW > 1 || c1->autopad || c1->refl_pad)) &&
                        !(off && atoi(off));
         if (E->input_s2d) { in.C = 4 * E->C; in.H = E->H / 2; in.W = E->W / 2; }
     }
@@ -1323,6 +1386,9 @@ static int run_steps_ev(thb_engine *E, instance *I, cudaEvent_t *evs)
             break;
         case ST_ZEROPAD:
             rc = thb_zero_pad(dt, x0, s->N, s->H, s->W, s->C, s->in_ld[0], s->padW, s->kW, s->padH, s->kH, y, s->out_ld, st);
+            break;
+        case ST_REFLECTPAD:
+            rc = thb_reflect_pad(dt, x0, s->N, s->H, s->W, s->C, s->in_ld[0], s->padW, s->kW, s->padH, s->kH, y, s->out_ld, st);
             break;
         case ST_SLICEC:
             rc = thb_slice_channels(dt, x0, s->pixels, s->flag, s->C, s->in_ld[0], y, s->out_ld, st);
@@ -1492,6 +1558,8 @@ thb_engine *thb_engine_create(thb_model *model, int mode, float lowp_range, int 
     E->ngpus = ngpus < 1 ? 1 : ngpus > ndev ? ndev : ngpus > 8 ? 8 : ngpus;
     const char *sm = getenv("THB200_STRICT_MATH");
     E->strict_math = sm && atoi(sm);
+    const char *hp = getenv("THB200_HONOUR_PADS");
+    E->honour_pads = hp && atoi(hp);
     /* Operators that look across the images of a batch (a slice or a join along the batch dimension, the whole-tensor
      * Normalize, the reference's LogSoftMax, which reads frame 0 for every frame) keep the batch on one GPU in one piece. */
     for (int i = 0; i < model->nnodes; i++) {

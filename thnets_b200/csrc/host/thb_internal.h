@@ -31,6 +31,8 @@ typedef struct thb_node {
     int nin, in[THB_MAXIN];
     /* conv / deconv / linear */
     int Cin, Cout, kH, kW, dH, dW, padH, padW, adjH, adjW;
+    /* convolution attributes the reference parses and ignores (ending pads, dilation, auto_pad 1 upper / 2 lower, reflection) */
+    int pad2H, pad2W, dlH, dlW, autopad, refl_pad;
     float *weight, *bias; /* owned copies; conv OIHW, deconv IOHW, linear [out][in]; bias may be NULL */
     /* batch norm: folded to per-channel scale / shift at load time */
     float *scale, *shift;

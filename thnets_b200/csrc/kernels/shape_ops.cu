@@ -18,7 +18,8 @@ inline int nblk(long n, int bs = 256) { return (int)((n + bs - 1) / bs); }
     }
 
 // y[n][oh][ow][c] = x[n][oh + top][ow + left][c] inside the source, 0 outside (top/left may be negative = padding, or
-// positive = cropping); `scale` = 2: nearest-neighbour 2x upsampling instead (source pixel (oh/2, ow/2)).
+// positive = cropping); up2 = 1: nearest-neighbour 2x upsampling instead (source pixel (oh/2, ow/2)); up2 = 2: reflection
+// padding (positions outside mirror about the first / last row and column, the border itself not repeated).
 template <typename T>
 __global__ void window_copy_kernel(const T *__restrict__ x, int N, int H, int W, int C, int x_ld, int top, int left, int up2,
                                    int oH, int oW, T *__restrict__ y, int y_ld)
@@ -32,7 +33,11 @@ __global__ void window_copy_kernel(const T *__restrict__ x, int N, int H, int W,
     const int ow = (int)(pix % oW);
     pix /= oW;
     const int oh = (int)(pix % oH), n = (int)(pix / oH);
-    const int ih = up2 ? oh >> 1 : oh + top, iw = up2 ? ow >> 1 : ow + left;
+    int ih = up2 == 1 ? oh >> 1 : oh + top, iw = up2 == 1 ? ow >> 1 : ow + left;
+    if (up2 == 2) {
+        ih = ih < 0 ? -ih : ih >= H ? 2 * H - 2 - ih : ih;
+        iw = iw < 0 ? -iw : iw >= W ? 2 * W - 2 - iw : iw;
+    }
     uint4 v = make_uint4(0, 0, 0, 0);
     if ((unsigned)ih < (unsigned)H && (unsigned)iw < (unsigned)W)
         v = *reinterpret_cast<const uint4 *>(x + (((long)n * H + ih) * W + iw) * x_ld + ck * vec);
@@ -210,6 +215,19 @@ int thb_zero_pad(int dtype, const void *x, int N, int H, int W, int C, int x_ld,
     SHAPE_DISPATCH(dtype, (window_copy_kernel<T><<<nblk(total), 256, 0, (cudaStream_t)s>>>((const T *)x, N, H, W, C, x_ld, -pad_t, -pad_l, 0,
                                                                                            oH, oW, (T *)y, y_ld)));
     return THB_LAUNCH_CHECK("window_copy_kernel (zero padding)");
+}
+
+int thb_reflect_pad(int dtype, const void *x, int N, int H, int W, int C, int x_ld, int pad_l, int pad_r, int pad_t, int pad_b, void *y,
+                    int y_ld, thb_stream s)
+{
+    const int vec = dtype == THB_F32 ? 4 : 8;
+    const int oH = H + pad_t + pad_b, oW = W + pad_l + pad_r;
+    if (x_ld % vec || y_ld % vec || pad_l < 0 || pad_r < 0 || pad_t < 0 || pad_b < 0 || pad_t >= H || pad_b >= H || pad_l >= W || pad_r >= W)
+        return THB_ERR_ARG;
+    const long total = (long)N * oH * oW * ((C + vec - 1) / vec);
+    SHAPE_DISPATCH(dtype, (window_copy_kernel<T><<<nblk(total), 256, 0, (cudaStream_t)s>>>((const T *)x, N, H, W, C, x_ld, -pad_t, -pad_l, 2,
+                                                                                           oH, oW, (T *)y, y_ld)));
+    return THB_LAUNCH_CHECK("window_copy_kernel (reflection padding)");
 }
 
 int thb_slice_channels(int dtype, const void *x, long pixels, int from, int C, int x_ld, void *y, int y_ld, thb_stream s)

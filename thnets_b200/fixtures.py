@@ -54,14 +54,26 @@ class Graph:
         return (self.rng.standard_normal(shape) * np.sqrt(2.0 / fan_in)).astype(np.float32)
 
     # ---- layers --------------------------------------------------------------
-    def conv(self, x, cin, cout, k, stride=1, pad=0, bias="zero"):
+    def conv(self, x, cin, cout, k, stride=1, pad=0, bias="zero", pads4=None, dilation=None, auto_pad=None, reflect=False):
+        """pads4 (top, left, bottom, right), dilation, auto_pad ("SAME_UPPER" / "SAME_LOWER") and reflect (the padding
+        comes from a reflect-mode Pad node) exist in ONNX files only: the reference parses and ignores them."""
         kh, kw = (k, k) if isinstance(k, int) else k
         w = self.he((cout, cin, kh, kw), cin * kh * kw)
         t = [("", w)]
         b = self._bias(bias, cout)
         if b is not None:
             t.append(("", b))
-        return self._add("conv", [x], dict(stride=(stride, stride), padding=(pad, pad)), t)
+        attrs = dict(stride=(stride, stride), padding=(pad, pad))
+        if pads4 is not None:
+            attrs["pads4"] = tuple(int(v) for v in pads4)
+            attrs["padding"] = (int(pads4[0]), int(pads4[1]))
+        if dilation is not None:
+            attrs["dilation"] = (int(dilation), int(dilation))
+        if auto_pad is not None:
+            attrs["auto_pad"] = auto_pad
+        if reflect:
+            attrs["reflect"] = 1
+        return self._add("conv", [x], attrs, t)
 
     def deconv(self, x, cin, cout, k, stride=1, pad=0, adj=0, bias=None):
         w = self.he((cin, cout, k, k), cin * k * k)
@@ -211,6 +223,8 @@ def write_pymodel(graph: Graph, path: str):
                     raise ValueError("the graph-dump Slice cuts dimension 0 only")
                 attrs = {"index": (attrs["start"], attrs["stop"])}
             for k, v in attrs.items():
+                if k in ("pads4", "dilation", "auto_pad", "reflect"):
+                    continue
                 if isinstance(v, tuple):
                     f.write(b"\x06")
                     _w_str(f, k)
@@ -703,15 +717,20 @@ def write_onnx(graph: Graph, path: str, bias_as_add=False, pad_nodes=False):
         ins, out = [name[j] for j in nd.inputs], "v%d" % i
         name[i] = out
         if nd.op in ("conv", "deconv"):
-            src, pads = ins[0], list(a["padding"]) * 2
-            if pad_nodes and nd.op == "conv" and any(pads):
-                node("Pad", [src], out + "_pad", mode="constant", pads=[0, 0, pads[0], pads[1], 0, 0, pads[2], pads[3]])
+            src, pads = ins[0], list(a.get("pads4", list(a["padding"]) * 2))
+            if (a.get("reflect") or pad_nodes) and nd.op == "conv" and any(pads):
+                node("Pad", [src], out + "_pad", mode="reflect" if a.get("reflect") else "constant",
+                     pads=[0, 0, pads[0], pads[1], 0, 0, pads[2], pads[3]])
                 src, pads = out + "_pad", [0, 0, 0, 0]
             cin = [src, init(out + "_w", ts[0])]
             split_bias = bias_as_add and len(ts) > 1
             if len(ts) > 1 and not split_bias:
                 cin.append(init(out + "_b", ts[1]))
             extra = dict(output_padding=list(a["output_padding"])) if nd.op == "deconv" else {}
+            if "dilation" in a:
+                extra["dilations"] = list(a["dilation"])
+            if "auto_pad" in a:
+                extra["auto_pad"] = a["auto_pad"]
             node("Conv" if nd.op == "conv" else "ConvTranspose", cin, out + "_c" if split_bias else out,
                  kernel_shape=list(ts[0].shape[2:]), strides=list(a["stride"]), pads=pads, **extra)
             if split_bias:
