@@ -45,6 +45,11 @@ def test_every_declared_symbol_is_exported():
     assert not missing, missing
     for var in ("th_debug", "th_profile", "th_minmax", "th_convtot", "th_convflops"):
         C.c_int.in_dll(lib, var)
+    # ... and nothing but the documented ABI: the planner, the loaders' helpers and the launch internals stay local
+    exported = set(subprocess.check_output(["nm", "-D", "--defined-only", DEFAULT_LIB], text=True).split()[2::3])
+    internal = [n for n in exported if n.startswith(("thb_engine_", "thb_model_", "thb_t7_", "thb_lowp_", "thb_host_")) or n.startswith("_Z")]
+    assert not internal, internal
+    assert exported <= names | {"th_debug", "th_profile", "th_minmax", "th_convtot", "th_convflops", "loadonnx"}, exported - names
 
 
 EXPECTED_ABI = {
