@@ -307,6 +307,30 @@ def test_conv_maxpool_fused_rows_stored_with_padding(lib, G, oracle, prelu):
     assert G.rel_err(G.from_nhwc(y, cout), ref) < 1e-2
 
 
+def test_bounded_wait_gives_up_and_the_next_launch_is_correct(lib, G, oracle, knobs):
+    """Every device-side wait is bounded.  Here one runs out on purpose: a test switch makes the copy producer withhold
+    the last K block of each CTA's last tile (nothing else is in flight by then), with the limit shortened to ~10 ms.
+    The kernel must come back by itself with a non-zero status word, and the context must stay usable: the same
+    convolution launched again without the switch gives the right answer."""
+    case = (2, 64, 12, 12, 64, 1, 1, 0)
+    n, cin, h, w, cout, k, s, p = case
+    x, wt = _conv_inputs(case, 61, True)
+    ref = oracle.conv2d(x, wt, None, (s, s), (p, p))
+    conv = G.Conv(lib, K.THB_F16, x.shape, wt, (s, s), (p, p))
+    xt, _ = G.to_nhwc(x, K.THB_F16)
+    d = conv.d
+    y = torch.zeros((n, d.oH, d.oW, d.out_ld), dtype=torch.float16, device="cuda")
+    knobs(THB200_TEST_WITHHOLD=1, THB200_WAIT_LIMIT_CYCLES=20000000)
+    assert lib.thb_conv_fwd(C.byref(d), G.ptr(xt), G.ptr(y), None) == 0       # the launch itself succeeds
+    torch.cuda.synchronize()                                                   # ... and the kernel returns
+    status = int(conv.keep[3].cpu()[0])
+    assert status != 0, "the wait should have run out"
+    conv.keep[3].zero_()
+    knobs(THB200_TEST_WITHHOLD=0, THB200_WAIT_LIMIT_CYCLES=4000000000)
+    got = G.from_nhwc(conv.run(xt), cout)
+    assert G.rel_err(got, ref) < 1e-2
+
+
 @pytest.mark.parametrize("dtype", [K.THB_F32, K.THB_F16])
 def test_conv_strided_views(lib, G, oracle, dtype):
     """Input read from, and output written into, channel slices of wider buffers."""

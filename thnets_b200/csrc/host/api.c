@@ -15,6 +15,7 @@
  */
 #include <math.h>
 #include <stdarg.h>
+#include <stddef.h>
 #include <stdio.h>
 #include <string.h>
 #include <strings.h>
@@ -373,19 +374,68 @@ THFloatTensor *THForward(THNETWORK *network, THFloatTensor *in)
     return network->out;
 }
 
-/* One module on the device: host tensor in, the module's `output` tensor out (the operator-level boundary
- * external code uses, examples/thnets-tf.cc:113-138). */
+/* One module on the device: host tensor in, the module's `output` tensor out (the operator-level boundary external code
+ * uses, examples/thnets-tf.cc:113-138).  The lowered model, its plan and its uploaded weights are kept per module record
+ * (a small table keyed by the record's address and a signature of its contents), so that calling a module again costs a
+ * forward, not a conversion; a record whose contents changed, or another record at the same address, gets a new engine. */
+typedef struct {
+    struct module *m;
+    unsigned long long sig;
+    thb_engine *e;
+    unsigned long long used;
+} module_slot;
+static module_slot g_slots[64];
+static unsigned long long g_slot_clock;
+
+static unsigned long long module_signature(const struct module *m)
+{
+    /* FNV-1a over the record minus its output tensor: type, function pointers, parameter union (tensor pointers included) */
+    unsigned long long h = 1469598103934665603ull;
+    const unsigned char *p = (const unsigned char *)m;
+    const size_t lo = offsetof(struct module, output), hi = lo + sizeof(m->output);
+    for (size_t i = 0; i < sizeof(*m); i++) {
+        if (i >= lo && i < hi) continue;
+        h = (h ^ p[i]) * 1099511628211ull;
+    }
+    return h;
+}
+
+/* forget the engine kept for a module record (called when a loader-built record is released) */
+void thb_module_forget(struct module *m)
+{
+    for (int i = 0; i < 64; i++)
+        if (g_slots[i].m == m) {
+            thb_engine_destroy(g_slots[i].e);
+            memset(&g_slots[i], 0, sizeof(g_slots[i]));
+        }
+}
+
 THFloatTensor *thb_module_updateOutput(struct module *m, THFloatTensor *in)
 {
     static const float zero[3] = {0, 0, 0}, one[3] = {1, 1, 1};
     char err[256] = "";
     thb_result r;
     THInit();
-    thb_model *model = thb_model_from_module(m, err, sizeof(err));
-    if (!model) THError("%s", err);
-    thb_engine *e = thb_engine_create(model, THB_MODE_F32, 0, 1);
-    thb_model_release(model);
-    if (!e) THError("%s", thb_engine_error());
+    const unsigned long long sig = module_signature(m);
+    module_slot *slot = 0, *victim = &g_slots[0];
+    for (int i = 0; i < 64; i++) {
+        if (g_slots[i].m == m && g_slots[i].e) {
+            if (g_slots[i].sig == sig) slot = &g_slots[i];
+            else { thb_engine_destroy(g_slots[i].e); memset(&g_slots[i], 0, sizeof(g_slots[i])); }
+        }
+        if (g_slots[i].used < victim->used) victim = &g_slots[i];
+    }
+    if (!slot) {
+        thb_model *model = thb_model_from_module(m, err, sizeof(err));
+        if (!model) THError("%s", err);
+        thb_engine *e = thb_engine_create(model, THB_MODE_F32, 0, 1);
+        thb_model_release(model);
+        if (!e) THError("%s", thb_engine_error());
+        if (victim->e) thb_engine_destroy(victim->e);   /* the least recently used record makes room */
+        victim->m = m; victim->sig = sig; victim->e = e;
+        slot = victim;
+    }
+    slot->used = ++g_slot_clock;
     int rank = in->nDimension, N = 1, C = 1, H = 1, W = 1;
     if (rank == 4) { N = in->size[0]; C = in->size[1]; H = in->size[2]; W = in->size[3]; }
     else if (rank == 3) { C = in->size[0]; H = in->size[1]; W = in->size[2]; }
@@ -393,12 +443,11 @@ THFloatTensor *thb_module_updateOutput(struct module *m, THFloatTensor *in)
     else if (rank == 1) { C = in->size[0]; }
     else THError("updateOutput needs a 1D to 4D tensor");
     /* 1-D and 2-D inputs are [C] / [N, C] feature vectors: planned as 1 x 1 images of rank 3 / 4 */
-    if (thb_engine_forward(e, THFloatTensor_data(in), 0, 0, 0, 0, N, C, H, W, rank >= 3 ? rank : rank + 2, zero, one, 0, &r))
+    if (thb_engine_forward(slot->e, THFloatTensor_data(in), 0, 0, 0, 0, N, C, H, W, rank >= 3 ? rank : rank + 2, zero, one, 0, &r))
         THError("%s", thb_engine_error());
     if (!m->output) m->output = THFloatTensor_new();
     THFloatTensor_resize(m->output, r.size, r.ndim);
     memcpy(THFloatTensor_data(m->output), r.data, sizeof(float) * r.count);
-    thb_engine_destroy(e);
     return m->output;
 }
 

@@ -16,6 +16,7 @@
  * ============================================================================================== */
 static void release_tensors(struct module *m)
 {
+    thb_module_forget(m);   /* an engine kept for single-module execution goes with the record */
     switch (m->type) {
     case MT_SpatialConvolution: case MT_SpatialConvolutionMM: case MT_SpatialConvolutionVirtMM:
         THFloatTensor_free(m->SpatialConvolution.bias);

@@ -99,6 +99,7 @@ typedef struct {
     float w_sub, w_mult, out_sub, out_mult;
     int flops_node; /* model node index of the conv (profiling) */
     int dual;       /* convolution with a second activation operand (in_buf[1]) instead of a residual */
+    long out_pixels; int out_C; /* extent of the output tensor (th_minmax) */
     long in_off0, out_off0; /* element offsets added to the first input / the output (slices and joins along the batch dimension) */
     int pool_k, pool_pad, pool_oH, pool_oW; /* pool_k > 0: the max pooling that follows runs inside the convolution launch */
     double flops_extra; /* FLOPs of the second convolution computed by the same launch */
@@ -259,6 +260,30 @@ static void step_out(step *s, const value *v)
     s->out_buf = v->buf;
     s->out_ld = v->ld;
     s->out_coff = v->coff;
+    /* extent of the result, for the per-launch min/max report (th_minmax) */
+    s->out_pixels = v->s.flat ? (long)v->s.N * v->s.fH * v->s.fW : (long)v->s.N * v->s.H * v->s.W;
+    s->out_C = v->s.flat ? v->s.fC : v->s.C;
+}
+
+/* host-side value of one stored element (th_minmax report only) */
+static float element_as_float(const void *p, long i, int dtype)
+{
+    if (dtype == THB_F32) return ((const float *)p)[i];
+    if (dtype == THB_U8) return ((const unsigned char *)p)[i];
+    unsigned short h = ((const unsigned short *)p)[i];
+    unsigned int bits;
+    if (dtype == THB_BF16) bits = (unsigned int)h << 16;
+    else {
+        const unsigned int sign = (h & 0x8000u) << 16, exp = (h >> 10) & 31, man = h & 1023;
+        if (exp == 0) {
+            float f = (float)man * (1.0f / 16777216.0f); /* subnormal: man * 2^-24 */
+            return sign ? -f : f;
+        }
+        bits = exp == 31 ? sign | 0x7f800000u | (man << 13) : sign | ((exp + 112) << 23) | (man << 13);
+    }
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
 }
 
 static int sole_consumer(planner *P, int node)
@@ -1412,6 +1437,23 @@ static int run_steps_ev(thb_engine *E, instance *I, cudaEvent_t *evs)
         }
         if (rc) { thb_set_error("kernel launch %d (kind %d) failed: %d %s", t, s->kind, rc, thb_last_cuda_error()); return -1; }
         if (evs) cudaEventRecord(evs[t + 1], I->stream);
+        if (th_minmax && y && s->out_pixels > 0 && s->out_C > 0 && s->kind != ST_ZERO && s->kind != ST_CSUM) {
+            /* thapi.c:141-154, :197-202: smallest and largest value of every layer's output -- how a caller picks the
+             * lowp range.  A diagnostic: the tensor is read back and scanned on the host (uint8 tensors: their bytes). */
+            const size_t es = esize_of(dt), bytes = (size_t)s->out_pixels * s->out_ld * es;
+            unsigned char *hb = malloc(bytes ? bytes : 1);
+            if (hb && cudaStreamSynchronize(I->stream) == cudaSuccess && cudaMemcpy(hb, y, bytes, cudaMemcpyDeviceToHost) == cudaSuccess) {
+                float mn = INFINITY, mx = -INFINITY;
+                for (long px = 0; px < s->out_pixels; px++)
+                    for (int c = 0; c < s->out_C; c++) {
+                        const float v = element_as_float(hb, px * s->out_ld + c, dt);
+                        if (v > mx) mx = v;
+                        if (v < mn) mn = v;
+                    }
+                printf("Layer %d output: min=%f, max=%f\n", t + 1, mn, mx);
+            }
+            free(hb);
+        }
         if (th_profile) {
             /* thapi.c:211-233: wall clock per module, GFLOP/s for convolutions (serialises the stream) */
             cudaStreamSynchronize(I->stream);
@@ -1435,7 +1477,7 @@ static int run_steps(thb_engine *E, instance *I)
     if (I->graph_state == 0 && I->runs >= 1) {
         const char *ng = getenv("THB200_NO_GRAPH");
         I->graph_state = -1;
-        if (E->dtype != THB_U8 && !(ng && atoi(ng)) && !th_profile) {
+        if (E->dtype != THB_U8 && !(ng && atoi(ng)) && !th_profile && !th_minmax) {
             cudaGraph_t g = 0;
             if (cudaStreamBeginCapture(I->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
                 const int rc = run_steps_ev(E, I, 0);
@@ -1447,7 +1489,7 @@ static int run_steps(thb_engine *E, instance *I)
         }
     }
     I->runs++;
-    if (I->graph_state == 1 && !th_profile) {
+    if (I->graph_state == 1 && !th_profile && !th_minmax) {
         if (cudaGraphLaunch(I->graph, I->stream) == cudaSuccess) {
             thb_count_launches(I->nsteps);
             return 0;

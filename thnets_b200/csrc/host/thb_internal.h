@@ -107,6 +107,7 @@ void thb_lowp_bias_addends(const unsigned char *qbias, int n, float b_sub, float
 
 /* ---- single-module execution (api.c) ---- */
 THFloatTensor *thb_module_updateOutput(struct module *m, THFloatTensor *in);
+void thb_module_forget(struct module *m);
 
 /* private tail of a THNETWORK allocated by this library */
 typedef struct thb_netx {

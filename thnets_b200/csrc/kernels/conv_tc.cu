@@ -78,6 +78,8 @@ struct ConvTcParams {
     int use_l1;  // gather through L1: neighbouring taps of one tile re-read the same input pixels
     int *acc_out;
     int *status;
+    long long wait_limit;      // SM cycles a bounded wait may take before it gives up (about two seconds by default)
+    int test_withhold;         // tests only: the producer never delivers the last K block of the CTA's last tile
 };
 
 template <int KIND> struct kind_traits;  // 0 = fp16, 1 = bf16, 2 = u8
@@ -344,7 +346,7 @@ __device__ __forceinline__ void epilogue_tma(const ConvTcParams &p, int grp, int
         const bool last_block = cur.sb == walk.blocks_of(cur.j) - 1;
         uint8_t *tile_smem = tiles + b * EPI_TILE_BYTES;
         if (cur.sb == 0) {
-            if (!mbar_wait_bounded(smem_u32(&acc_full[ab]), (lt / NACC) & 1)) {
+            if (!mbar_wait_bounded(smem_u32(&acc_full[ab]), (lt / NACC) & 1, p.wait_limit)) {
                 if (lane == 0) atomicExch(p.status, 2);
                 *abort_flag = 1;
                 alive = false;
@@ -363,7 +365,7 @@ __device__ __forceinline__ void epilogue_tma(const ConvTcParams &p, int grp, int
             mbar_arrive(smem_u32(&acc_empty[ab]));
         }
         // the tile is ours once its previous store has read it out and, with a residual, the residual rows are in it
-        if (!mbar_wait_bounded(smem_u32(&avail[b]), wrap & 1)) {
+        if (!mbar_wait_bounded(smem_u32(&avail[b]), wrap & 1, p.wait_limit)) {
             if (lane == 0) atomicExch(p.status, 8);
             *abort_flag = 1;
             alive = false;
@@ -424,7 +426,7 @@ __device__ __forceinline__ void epilogue_agent(const ConvTcParams &p, const CUte
     for (; cur.j < walk.my_tiles; q++) {
         int m0, n0;
         walk.map.coords(walk.local(cur.j), m0, n0);
-        if (!mbar_wait_bounded(smem_u32(&rows_ready[b]), wrap & 1)) {
+        if (!mbar_wait_bounded(smem_u32(&rows_ready[b]), wrap & 1, p.wait_limit)) {
             atomicExch(p.status, 5);
             *abort_flag = 1;
             alive = false;
@@ -444,7 +446,7 @@ __device__ __forceinline__ void epilogue_agent(const ConvTcParams &p, const CUte
     bulk_wait_group<0>();
     // after an early exit, residual loads still in flight must land before the CTA may leave
     if (!alive && has_res)
-        for (int k = q; k < q_pre; k++) mbar_wait_bounded(smem_u32(&avail[k % nbuf]), (k / nbuf) & 1);
+        for (int k = q; k < q_pre; k++) mbar_wait_bounded(smem_u32(&avail[k % nbuf]), (k / nbuf) & 1, p.wait_limit);
 }
 
 template <int KIND, int BN, int STAGES>
@@ -579,7 +581,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     const int g = (kb + 1) * 8 + chunk;
                     ki_next = (kb + 1 < p.nkb && g < p.n_kchunks) ? __ldg(p.kinfo + g) : -1;
                 }
-                if (!mbar_wait_bounded(smem_u32(&empty[s]), ph ^ 1)) {
+                if (!mbar_wait_bounded(smem_u32(&empty[s]), ph ^ 1, p.wait_limit)) {
                     if (lane == 0) atomicExch(p.status, 1);
                     *abort_flag = 1;
                     alive = false;
@@ -646,12 +648,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     const int s = ring_s;
                     const uint32_t ph = ring_ph;
                     if (++ring_s == nst) { ring_s = 0; ring_ph ^= 1; }
-                    if (!mbar_wait_bounded(smem_u32(&empty[s]), ph ^ 1)) {
+                    if (!mbar_wait_bounded(smem_u32(&empty[s]), ph ^ 1, p.wait_limit)) {
                         atomicExch(p.status, 3);
                         *abort_flag = 1;
                         alive = false;
                         break;
                     }
+                    // (tests of the give-up path: every earlier copy has been consumed by then, nothing is in flight)
+                    if (p.test_withhold && kb == p.nkb - 1 && lt + halves >= map.n_local) break;
                     const uint32_t bar = smem_u32(&full[s]);
                     if (p.half) {
                         const int nh = 2 * kb + 1 < p.ntaps ? 2 : 1;
@@ -699,7 +703,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
             for (int lt = 0; lt < map.n_local && alive; lt += halves) {
                 // the accumulators of this unit's local tiles (two in pair mode) must have been drained
                 for (int h = 0; h < halves && alive; h++)
-                    if (!mbar_wait_bounded(smem_u32(&acc_empty[(lt + h) % NACC]), (((lt + h) / NACC) & 1) ^ 1)) {
+                    if (!mbar_wait_bounded(smem_u32(&acc_empty[(lt + h) % NACC]), (((lt + h) / NACC) & 1) ^ 1, p.wait_limit)) {
                         atomicExch(p.status, 6);
                         *abort_flag = 1;
                         alive = false;
@@ -711,7 +715,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     const int s = ring_s;
                     const uint32_t ph = ring_ph;
                     if (++ring_s == nst) { ring_s = 0; ring_ph ^= 1; }
-                    if (!mbar_wait_bounded(smem_u32(&full[s]), ph)) {
+                    if (!mbar_wait_bounded(smem_u32(&full[s]), ph, p.wait_limit)) {
                         atomicExch(p.status, 4);
                         *abort_flag = 1;
                         alive = false;
@@ -827,7 +831,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     // (re)build the table for this tile's channels: all four warps of the group, between two group barriers
                     bool ok = true;
                     mbar_arrive(bar_tbl);
-                    ok = mbar_wait_bounded(bar_tbl, tbl_phase & 1);
+                    ok = mbar_wait_bounded(bar_tbl, tbl_phase & 1, p.wait_limit);
                     tbl_phase++;
                     if (ok) {
                         const int ncc = 1 + 2 * p.padW, satw = p.kW + 1, satn = (p.kH + 1) * (p.kW + 1);
@@ -843,7 +847,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                         for (int col = et; col < BN; col += 128)
                             tbl[L::TBL_CAP + col] = p.bias_add ? __ldg(p.bias_add + min(n0 + col, p.Cout - 1)) : 0;
                         mbar_arrive(bar_tbl);
-                        ok = mbar_wait_bounded(bar_tbl, tbl_phase & 1);
+                        ok = mbar_wait_bounded(bar_tbl, tbl_phase & 1, p.wait_limit);
                         tbl_phase++;
                     }
                     if (!ok) {
@@ -876,7 +880,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     }
                 }
                 if (!have_acc) {
-                    if (!mbar_wait_bounded(smem_u32(&acc_full[ab]), (lt / NACC) & 1)) {
+                    if (!mbar_wait_bounded(smem_u32(&acc_full[ab]), (lt / NACC) & 1, p.wait_limit)) {
                         if (lane == 0) atomicExch(p.status, 2);
                         *abort_flag = 1;
                         alive = false;
@@ -889,7 +893,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                 // ---- phase 1: this thread's pixel row, SUBN accumulator columns -> staging tile
                 // (uint8: a warp stages and writes out its own 32 rows, so it synchronises with nobody but itself)
                 if (KIND != 2) {
-                    if (!mbar_wait_bounded(bar_free, (sub_it & 1) ^ 1)) {
+                    if (!mbar_wait_bounded(bar_free, (sub_it & 1) ^ 1, p.wait_limit)) {
                         if (lane == 0) atomicExch(p.status, 7);
                         *abort_flag = 1;
                         alive = false;
@@ -1035,7 +1039,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     __syncwarp();
                 } else {
                     mbar_arrive(bar_ready);
-                    if (!mbar_wait_bounded(bar_ready, sub_it & 1)) {
+                    if (!mbar_wait_bounded(bar_ready, sub_it & 1, p.wait_limit)) {
                         if (lane == 0) atomicExch(p.status, 5);
                         *abort_flag = 1;
                         alive = false;
@@ -1113,8 +1117,9 @@ done:
 // Diagnostic launcher switches (THB200_* environment variables), read ONCE: a launch costs no getenv call.
 // thb_conv_reload_knobs() re-reads them (the tests change them between cases).  -1 = not set.
 struct ConvKnobs {
-    int pair_min_kb, u8_fast, reverse, epi_groups, epi_bufs, pdl, conv_l1, half_taps, a_tma;
+    int pair_min_kb, u8_fast, reverse, epi_groups, epi_bufs, pdl, conv_l1, half_taps, a_tma, test_withhold;
     long pair_min_units;
+    long long wait_limit;
 };
 ConvKnobs g_knobs;
 bool g_knobs_read = false;
@@ -1136,6 +1141,9 @@ void read_knobs()
     g_knobs.conv_l1 = env_int("THB200_CONV_L1", -1);
     g_knobs.half_taps = env_int("THB200_HALF_TAPS", -1);
     g_knobs.a_tma = env_int("THB200_A_TMA", -1);
+    g_knobs.test_withhold = env_int("THB200_TEST_WITHHOLD", 0);
+    const char *wl = getenv("THB200_WAIT_LIMIT_CYCLES");
+    g_knobs.wait_limit = wl && atoll(wl) > 0 ? atoll(wl) : 4000000000ll;
     g_knobs_read = true;
 }
 const ConvKnobs &knobs()
@@ -1226,6 +1234,8 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
     }
     const int use_pdl = kn.pdl;
     p.pdl = use_pdl;
+    p.wait_limit = kn.wait_limit;
+    p.test_withhold = kn.test_withhold && p.a_tma;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(NTHREADS);
