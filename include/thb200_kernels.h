@@ -167,6 +167,10 @@ int thb_conv_padded_rows_supported(int dtype);
 /* u8 HWC images (already on the device, row stride `stride`) -> normalised NHWC dtype (thapi.c:20-46) */
 int thb_preprocess_images(const unsigned char *img, int N, int H, int W, int stride, int cp, int bgr,
                           const float *mean3, const float *std3, int dtype, void *y, int y_ld, thb_stream s);
+/* u8 HWC RGB images -> normalised, space-to-depth NHWC dtype in the padded-row layout of thb_preprocess_s2d_padded
+ * (F16 / BF16): THProcessImages feeding a stride-2 first convolution (thapi.c:20-46 arithmetic) */
+int thb_preprocess_images_s2d(const unsigned char *img, int N, int H, int W, int stride, int bgr, const float *mean3,
+                              const float *std3, int dtype, void *y, int y_ld, int row_pitch, int pad_left, thb_stream s);
 /* u8 HWC RGB images -> quantised NHWC u8 with the static input range the lowp image loader derives from mean/std
  * (lowp/lowp_basic.c:82-131); returns that range as *q_sub, *q_mult (host) */
 int thb_preprocess_images_lowp(const unsigned char *img, int N, int H, int W, int stride, int bgr, const float *mean3,

@@ -490,3 +490,26 @@ def test_onnx_only_convolution_attributes(th, oracle, tmp_path, monkeypatch, mod
     assert (ow, oh) == (ref.shape[3], ref.shape[2])
     assert rel_err(out, ref.ravel()) < TOL[mode]
     th.free_network(hc)
+
+
+@pytest.mark.parametrize("bgr", [0, 1])
+def test_process_images_through_the_space_to_depth_stem(th, oracle, tmp_path, bgr):
+    """THProcessImages on a network whose first convolution has stride 2 (fp16): the byte images are normalised and
+    regrouped space-to-depth by one kernel, so the stem and its pooling run as for a float batch."""
+    import ctypes as C
+    g = fx.resnet18(width=0.25, size=64, classes=10)
+    g.mean, g.std = np.array([0.45, 0.42, 0.40], np.float32), np.array([0.225, 0.23, 0.22], np.float32)
+    hc = _convert(th, g, "py", tmp_path, "r18img", 1)
+    rng = np.random.default_rng(23)
+    batch = 5
+    imgs = [rng.integers(0, 256, (64, 64, 3)).astype(np.uint8) for _ in range(batch)]
+    out, _, _ = th.process_images(hc, imgs, bgr=bgr)
+    dst = np.empty((batch, 3, 64, 64), np.float32)
+    ptrs = (C.POINTER(C.c_ubyte) * batch)(*[i.ctypes.data_as(C.POINTER(C.c_ubyte)) for i in imgs])
+    oracle.lib.orc_images_to_float(ptrs, batch, 64, 64, 64 * 3, 3, g.mean.ctypes.data_as(C.POINTER(C.c_float)),
+                                   g.std.ctypes.data_as(C.POINTER(C.c_float)), bgr, dst.ctypes.data_as(C.POINTER(C.c_float)))
+    plain = fx.Graph()
+    plain.nodes, plain.output = g.nodes, g.output   # same weights, identity statistics
+    ref = oracle.run(plain, dst)
+    assert rel_err(out, ref.ravel()) < TOL[1]
+    th.free_network(hc)

@@ -1277,7 +1277,9 @@ static int instance_build(thb_engine *E, instance *I, int device, int slice_off,
         thb_node *c1 = M->nnodes > 1 ? &M->nodes[1] : 0;
         const char *off = getenv("THB200_NO_S2D"), *u8off = getenv("THB200_NO_S2D_U8");
         E->input_s2d = c1 && c1->op == OP_CONV && c1->in[0] == 0 && P.uses[0] == 1 && c1->dH == 2 && c1->dW == 2 &&
-                       4 * E->C <= 16 && c1->Cin == E->C && E->H % 2 == 0 && E->W % 2 == 0 && E->rank == 4 && E->cp == 0 &&
+                       4 * E->C <= 16 && c1->Cin == E->C && E->H % 2 == 0 && E->W % 2 == 0 && E->rank == 4 &&
+                       /* a float batch, or three-plane byte images (converted and regrouped by one kernel) in the 16-bit modes */
+                       (E->cp == 0 || (E->cp == 3 && E->dtype != THB_U8)) &&
                        (E->dtype == THB_F16 || E->dtype == THB_BF16 || (E->dtype == THB_U8 && !(u8off && atoi(u8off)))) &&
                        c1->padH <= c1->kH - 1 && c1->padW <= c1->kW - 1 &&
                        !(E->honour_pads && (c1->pad2H != c1->padH || c1->pad2W != c1->padW || c1->dlH > 1 || c1->dlW > 1 || c1->autopad || c1->refl_pad)) &&
@@ -1779,7 +1781,10 @@ static int boundary_in(thb_engine *E, instance *I, int has_x, int inplace, int c
         rc = thb_preprocess_images_lowp(I->d_img, I->slice_n, H, W, W * cp, bgr, mean, std, in_ptr, I->in_val.ld, &q_sub,
                                         &q_mult, I->stream);
         set_dynamic_quant(I, q_sub, q_mult);
-    } else
+    } else if (E->input_s2d)
+        rc = thb_preprocess_images_s2d(I->d_img, I->slice_n, H, W, W * cp, bgr, mean, std, E->dtype, in_ptr, I->in_val.ld,
+                                       I->in_val.row_pitch ? I->in_val.row_pitch : W / 2, I->in_val.pad_left, I->stream);
+    else
         rc = thb_preprocess_images(I->d_img, I->slice_n, H, W, W * cp, cp, bgr, mean, std, E->dtype, in_ptr,
                                    I->in_val.ld, I->stream);
     if (rc) { thb_set_error("preprocess launch failed: %s", thb_last_cuda_error()); return -1; }
@@ -1845,6 +1850,16 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
         if (x) {
             CU(cudaMemcpyAsync(I->d_in, x + (size_t)I->slice_off * img_elems, (size_t)I->slice_n * img_elems * sizeof(float),
                                cudaMemcpyHostToDevice, I->stream));
+        } else if ((size_t)stride == (size_t)W * cp) {
+            /* tightly packed rows: one copy per run of images that also follow one another in host memory */
+            const size_t img_bytes = (size_t)H * W * cp;
+            for (int n = 0; n < I->slice_n;) {
+                int run = 1;
+                while (n + run < I->slice_n && images[I->slice_off + n + run] == images[I->slice_off + n + run - 1] + img_bytes) run++;
+                CU(cudaMemcpyAsync(I->d_img + (size_t)n * img_bytes, images[I->slice_off + n], (size_t)run * img_bytes,
+                                   cudaMemcpyHostToDevice, I->stream));
+                n += run;
+            }
         } else {
             for (int n = 0; n < I->slice_n; n++)
                 CU(cudaMemcpy2DAsync(I->d_img + (size_t)n * H * W * cp, (size_t)W * cp, images[I->slice_off + n], stride,

@@ -196,6 +196,39 @@ __global__ void preprocess_images_kernel(const uint8_t *img, int N, int H, int W
     Vec<T>::store(y + pix * y_ld, v);
 }
 
+// u8 HWC RGB images -> normalised space-to-depth NHWC T: the layout preprocess_s2d_kernel writes (channel (ph*2 + pw)*3 + c
+// of block (bh, bw) = pixel (2bh + ph, 2bw + pw), rows row_pitch pixels apart with pad_left zero pixels in front), with the
+// arithmetic of the image loader (thapi.c:20-46)
+template <typename T>
+__global__ void preprocess_images_s2d_kernel(const uint8_t *img, int N, int H, int W, int stride, int bgr, float3 mean, float3 istd,
+                                             T *y, int y_ld, int row_pitch, int pad_left)
+{
+    constexpr int VN = Vec<T>::N;
+    const int H2 = H / 2, W2 = W / 2;
+    const long pix = (long)blockIdx.x * blockDim.x + threadIdx.x;  // over the stored (padded) pixels
+    if (pix >= (long)N * H2 * row_pitch) return;
+    const long n = pix / ((long)H2 * row_pitch);
+    const int rem = (int)(pix - n * (long)H2 * row_pitch), bh = rem / row_pitch, bw = rem - bh * row_pitch - pad_left;
+    const bool real = bw >= 0 && bw < W2;
+    const float m[3] = {mean.x, mean.y, mean.z}, is[3] = {istd.x, istd.y, istd.z};
+    constexpr int Cs = 12, Cpad = (Cs + VN - 1) / VN * VN;
+    for (int c0 = 0; c0 < Cpad; c0 += VN) {
+        float v[VN];
+#pragma unroll
+        for (int i = 0; i < VN; i++) {
+            const int cs = c0 + i;
+            float val = 0.f;
+            if (real && cs < Cs) {
+                const int blk = cs / 3, c = cs - blk * 3;
+                const uint8_t *src = img + ((size_t)n * H + 2 * bh + (blk >> 1)) * stride + (size_t)(2 * bw + (blk & 1)) * 3;
+                val = __fmul_rn(__fsub_rn(__fmul_rn((float)src[bgr ? 2 - c : c], 0.003921568f), m[c]), is[c]);
+            }
+            v[i] = val;
+        }
+        Vec<T>::store(y + pix * y_ld + c0, v);
+    }
+}
+
 // u8 HWC images -> quantised NHWC u8 with the static input range of the lowp image loader
 // (lowp/lowp_basic.c:82-131, lowp/lowp_images.c): q = (unsigned char)(int)roundf((px - sub[c]) * mult[c])
 __global__ void preprocess_images_u8_kernel(const uint8_t *img, int N, int H, int W, int stride, int bgr, int3 sub, float3 mult,
@@ -720,6 +753,20 @@ int thb_preprocess_images(const unsigned char *img, int N, int H, int W, int str
     DISPATCH_FLOAT_DTYPE(dtype, (preprocess_images_kernel<T><<<nblocks(pix), 256, 0, (cudaStream_t)s>>>(
                                     img, N, H, W, stride, cp, bgr, m, is, (T *)y, y_ld)));
     return THB_LAUNCH_CHECK("preprocess_images_kernel");
+}
+
+int thb_preprocess_images_s2d(const unsigned char *img, int N, int H, int W, int stride, int bgr, const float *mean3, const float *std3,
+                              int dtype, void *y, int y_ld, int row_pitch, int pad_left, thb_stream s)
+{
+    if (((H | W) & 1) || pad_left < 0 || row_pitch < pad_left + W / 2 || y_ld < 12) return THB_ERR_ARG;
+    if (dtype != THB_F16 && dtype != THB_BF16) return THB_ERR_UNSUPPORTED;
+    const long pix = (long)N * (H / 2) * row_pitch;
+    if (pix == 0) return THB_OK;
+    float3 m = make_float3(mean3[0], mean3[1], mean3[2]);
+    float3 is = make_float3(1 / std3[0], 1 / std3[1], 1 / std3[2]);
+    DISPATCH_FLOAT_DTYPE(dtype, (preprocess_images_s2d_kernel<T><<<nblocks(pix), 256, 0, (cudaStream_t)s>>>(
+                                    img, N, H, W, stride, bgr, m, is, (T *)y, y_ld, row_pitch, pad_left)));
+    return THB_LAUNCH_CHECK("preprocess_images_s2d_kernel");
 }
 
 int thb_preprocess_images_lowp(const unsigned char *img, int N, int H, int W, int stride, int bgr, const float *mean3,
