@@ -151,22 +151,61 @@ __global__ void preprocess_s2d_kernel(const float *x, float *x_inplace, int N, i
     const bool real = bw >= 0 && bw < W2;
     const float m[3] = {mean.x, mean.y, mean.z}, sd[3] = {std_.x, std_.y, std_.z};
     const int Cs = 4 * C, Cpad = (Cs + VN - 1) / VN * VN;
-    for (int c0 = 0; c0 < Cpad; c0 += VN) {
+    // Three planes (every benchmark network): the block's 2 x 2 pixels of every plane as two 8-byte loads per plane (W is
+    // even, so a pixel pair never straddles a row and is 8-byte aligned), all issued before any is used, every index
+    // known at compile time.  Other plane counts take the element-wise loop below.
+    if (C != 3) {
+        for (int c0 = 0; c0 < Cpad; c0 += VN) {
+            float v[VN];
+#pragma unroll
+            for (int i = 0; i < VN; i++) {
+                const int cs = c0 + i;
+                float val = 0.f;
+                if (real && cs < Cs) {
+                    const int blk = cs / C, c = cs - blk * C;
+                    const long idx = ((n * C + c) * H + (2 * bh + (blk >> 1))) * W + 2 * bw + (blk & 1);
+                    val = x[idx];
+                    if (c < 3) val = __fdiv_rn(__fsub_rn(val, m[c]), sd[c]);
+                    if (x_inplace) x_inplace[idx] = val;
+                    if (sizeof(T) == 1) val = (float)(((int)(roundf(val * q_mult) - zr)) & 255);
+                }
+                v[i] = val;
+            }
+            Vec<T>::store(y + pix * y_ld + c0, v);
+        }
+        return;
+    }
+    float vals[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) vals[i] = 0.f;
+    if (real) {
+#pragma unroll
+        for (int c = 0; c < 3; c++) {
+#pragma unroll
+            for (int ph = 0; ph < 2; ph++) {
+                const long idx = ((n * C + c) * H + (2 * bh + ph)) * W + 2 * bw;
+                float2 v = *reinterpret_cast<const float2 *>(x + idx);
+                if (c < 3) {
+                    v.x = __fdiv_rn(__fsub_rn(v.x, m[c]), sd[c]);
+                    v.y = __fdiv_rn(__fsub_rn(v.y, m[c]), sd[c]);
+                }
+                if (x_inplace) *reinterpret_cast<float2 *>(x_inplace + idx) = v;
+                if (sizeof(T) == 1) {
+                    v.x = (float)(((int)(roundf(v.x * q_mult) - zr)) & 255);
+                    v.y = (float)(((int)(roundf(v.y * q_mult) - zr)) & 255);
+                }
+                // channel (ph*2 + pw)*3 + c of the regrouped pixel
+                vals[(ph * 2) * 3 + c] = v.x;
+                vals[(ph * 2 + 1) * 3 + c] = v.y;
+            }
+        }
+    }
+#pragma unroll
+    for (int c0 = 0; c0 < 16; c0 += VN) {
+        if (c0 >= Cpad) break;   // (12 channels rounded up to the type's 16-byte group: 12 for fp32, 16 otherwise)
         float v[VN];
 #pragma unroll
-        for (int i = 0; i < VN; i++) {
-            const int cs = c0 + i;
-            float val = 0.f;
-            if (real && cs < Cs) {
-                const int blk = cs / C, c = cs - blk * C;
-                const long idx = ((n * C + c) * H + (2 * bh + (blk >> 1))) * W + 2 * bw + (blk & 1);
-                val = x[idx];
-                if (c < 3) val = __fdiv_rn(__fsub_rn(val, m[c]), sd[c]);
-                if (x_inplace) x_inplace[idx] = val;
-                if (sizeof(T) == 1) val = (float)(((int)(roundf(val * q_mult) - zr)) & 255);
-            }
-            v[i] = val;
-        }
+        for (int i = 0; i < VN; i++) v[i] = vals[c0 + i];
         Vec<T>::store(y + pix * y_ld + c0, v);
     }
 }
