@@ -205,7 +205,8 @@ template <int KIND, int BN, int STAGES> struct Smem {
     // uint8: per epilogue group a table of zero-point correction terms per (border class, channel) and the bias addends
     static constexpr int TBL_ROW = BN + 4;                                 // ints between the rows of two classes
     static constexpr int TBL_CAP = 3400;                                   // ints the class table may take
-    static constexpr size_t TBL_BYTES = KIND == 2 ? (size_t)(TBL_CAP + 256) * 4 + 64 : 0;
+    // (after the class rows: 256 bias addends as ints, then the same addends as 128 words of two 16-bit halves)
+    static constexpr size_t TBL_BYTES = KIND == 2 ? (size_t)(TBL_CAP + 256 + 128) * 4 + 64 : 0;
     static constexpr size_t TOTAL =
         TMA_EPI ? 232448 : 1024 + BAR_BYTES + (size_t)STAGES * STAGE_BYTES + 3 * STAGING_PAD + 3 * TBL_BYTES;
     static_assert(TOTAL <= 232448, "shared memory plan exceeds the 227 KB a CTA can have");
@@ -274,8 +275,8 @@ template <int BN> struct EpiWalk {
 // row in the image plane's tail (where the reference's bias add wraps instead of clamping at 0) and a Threshold whose
 // replacement byte equals its threshold (max suffices); the integer pipe is what bounds this loop.
 struct U8Epi {
-    int corr;        // corr_pix + c_offset of this row
-    uint32_t mult, rnd;
+    uint32_t rc;     // (corr_pix + c_offset) * c_mult + rounding term of this row, modulo 2^32
+    uint32_t mult;
     int shift, tailmask, thr, rval, ca, cb, addend;
 };
 template <bool GENERAL, bool HAS_RES>
@@ -291,8 +292,8 @@ __device__ __forceinline__ void u8_chunk32(const uint32_t (&acc)[32], const int 
         int q[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const int a = (int)acc[g4 * 4 + i] + tv[i] + e.corr;
-            const int sres = (int)((uint32_t)a * e.mult + e.rnd) >> e.shift;
+            // (acc + t + corr) * mult + rnd in the ring of 32-bit words, with t * mult taken from the table
+            const int sres = (int)(acc[g4 * 4 + i] * e.mult + (uint32_t)tv[i] + e.rc) >> e.shift;
             const int q1 = __vimin_s32_relu(sres, 255);
             int v;
             if (GENERAL) {
@@ -311,6 +312,54 @@ __device__ __forceinline__ void u8_chunk32(const uint32_t (&acc)[32], const int 
         }
         const uint32_t lo = __byte_perm((uint32_t)q[0], (uint32_t)q[1], 0x0040), hi = __byte_perm((uint32_t)q[2], (uint32_t)q[3], 0x0040);
         words[g4] = __byte_perm(lo, hi, 0x5410);
+    }
+}
+
+// The common case of u8_chunk32 (GENERAL = false) with the arithmetic after the shift done on two 16-bit halves per
+// instruction.  What bounds this loop is the integer pipes: shifts, byte permutes, packing conversions and multiply-adds
+// issue every second cycle per scheduler, minimum / maximum (also on halfword pairs) and plain adds every cycle; so the
+// clamps are minima and maxima on pairs and every add is a plain 32-bit add of words whose halves cannot carry.
+// That needs non-negative halves, hence an offset: the bias words hold addend + OFF (addends clamped to +-255, which
+// saturates the same way), OFF = 256 without a residual and 384 with one, and
+//   pair = min(pack_u16(shifted values), 255)                 in [0, 255]
+//   S1   = clamp(pair + bias word, OFF (+ threshold byte when there is no residual), OFF + 255)
+//   S2   = clamp(S1 + R, 512 + threshold byte, 512 + 255)     R = 255 - r for q - r + 127 (RES 1), r for q + r - 128 (RES 3)
+// and the low bytes of the halves (offsets 256 and 512 leave them alone) are the result.
+template <int RES>
+__device__ __forceinline__ void u8_chunk32_pairs(const uint32_t (&acc)[32], const int *trow, const int *b2, const U8Epi &e,
+                                                 const uint4 &res0, const uint4 &res1, uint32_t (&words)[8])
+{
+    const uint32_t rw[8] = {res0.x, res0.y, res0.z, res0.w, res1.x, res1.y, res1.z, res1.w};
+    constexpr uint32_t OFF = RES ? 384u : 256u;
+    const uint32_t rv2 = (uint32_t)e.rval * 0x00010001u;
+    const uint32_t lo1 = OFF * 0x00010001u + (RES ? 0u : rv2), hi1 = (OFF + 255u) * 0x00010001u;
+    const uint32_t lo2 = 512u * 0x00010001u + rv2, hi2 = 767u * 0x00010001u;
+#pragma unroll
+    for (int g4 = 0; g4 < 8; g4++) {
+        const int4 t4 = *reinterpret_cast<const int4 *>(trow + g4 * 4);
+        const int2 bb = *reinterpret_cast<const int2 *>(b2 + g4 * 2);
+        const int tv[4] = {t4.x, t4.y, t4.z, t4.w};
+        int sr[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) sr[i] = (int)(acc[g4 * 4 + i] * e.mult + (uint32_t)tv[i] + e.rc) >> e.shift;
+        uint32_t s[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            uint32_t v;
+            asm("cvt.pack.sat.u16.s32 %0, %1, %2;" : "=r"(v) : "r"(sr[2 * h + 1]), "r"(sr[2 * h]));
+            asm("min.u16x2 %0, %0, %1;" : "+r"(v) : "r"(0x00ff00ffu));
+            v += (uint32_t)(h ? bb.y : bb.x);
+            asm("max.s16x2 %0, %0, %1;" : "+r"(v) : "r"(lo1));
+            asm("min.s16x2 %0, %0, %1;" : "+r"(v) : "r"(hi1));
+            if (RES != 0) {
+                const uint32_t r = RES == 1 ? ~rw[g4] : rw[g4];
+                v += __byte_perm(r, 0, h ? 0x4342 : 0x4140);
+                asm("max.s16x2 %0, %0, %1;" : "+r"(v) : "r"(lo2));
+                asm("min.s16x2 %0, %0, %1;" : "+r"(v) : "r"(hi2));
+            }
+            s[h] = v;
+        }
+        words[g4] = __byte_perm(s[0], s[1], 0x6420);
     }
 }
 
@@ -841,11 +890,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                             const int tr0 = rc >= 1 && rc <= p.padH ? rc : 0, tr1 = rc > p.padH ? p.kH - (rc - p.padH) : p.kH;
                             const int ts0 = cc >= 1 && cc <= p.padW ? cc : 0, ts1 = cc > p.padW ? p.kW - (cc - p.padW) : p.kW;
                             const int *t = p.wsat + (size_t)min(n0 + col, p.Cout - 1) * satn;
-                            tbl[k * L::TBL_ROW + col] = p.b_off * (__ldg(t + tr1 * satw + ts1) - __ldg(t + tr0 * satw + ts1) -
-                                                                   __ldg(t + tr1 * satw + ts0) + __ldg(t + tr0 * satw + ts0));
+                            // (stored times c_mult, modulo 2^32: the requantisation multiplies the corrected sum by it)
+                            tbl[k * L::TBL_ROW + col] = (int)((uint32_t)(p.b_off * (__ldg(t + tr1 * satw + ts1) - __ldg(t + tr0 * satw + ts1) -
+                                                                                    __ldg(t + tr1 * satw + ts0) + __ldg(t + tr0 * satw + ts0))) *
+                                                              (uint32_t)p.c_mult);
                         }
                         for (int col = et; col < BN; col += 128)
                             tbl[L::TBL_CAP + col] = p.bias_add ? __ldg(p.bias_add + min(n0 + col, p.Cout - 1)) : 0;
+                        // the addends once more for the paired arithmetic (u8_chunk32_pairs): two per word, each clamped
+                        // to +-255 and raised by the offset that keeps the halves non-negative
+                        const int off2 = p.res ? 384 : 256;
+                        for (int pr = et; pr < BN / 2; pr += 128) {
+                            const int ba = p.bias_add ? __ldg(p.bias_add + min(n0 + 2 * pr, p.Cout - 1)) : 0;
+                            const int bb = p.bias_add ? __ldg(p.bias_add + min(n0 + 2 * pr + 1, p.Cout - 1)) : 0;
+                            tbl[L::TBL_CAP + 256 + pr] = (min(max(ba, -255), 255) + off2) | ((min(max(bb, -255), 255) + off2) << 16);
+                        }
                         mbar_arrive(bar_tbl);
                         ok = mbar_wait_bounded(bar_tbl, tbl_phase & 1, p.wait_limit);
                         tbl_phase++;
@@ -907,15 +966,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     const int *trow = tbl + cls * L::TBL_ROW + sb * SUBN;
                     const int *brow = tbl + L::TBL_CAP + sb * SUBN;
                     U8Epi e;
-                    e.corr = corr_pix + p.c_off;
                     e.mult = (uint32_t)p.c_mult;
-                    e.rnd = p.c_shift >= 1 ? 1u << (p.c_shift - 1) : 0u;
+                    e.rc = (uint32_t)(corr_pix + p.c_off) * e.mult + (p.c_shift >= 1 ? 1u << (p.c_shift - 1) : 0u);
                     e.shift = p.c_shift > 0 ? p.c_shift : 0;
                     e.tailmask = plane_pos < p.tail_start ? 0 : 255;  // the reference's tail adds without the lower clamp
                     e.thr = p.relu_thr;                               // < 0: every byte passes
                     e.rval = p.relu_thr < 0 ? 0 : p.relu_val;
                     e.ca = (int)p.self_coef; e.cb = (int)p.res_coef; e.addend = p.res_addend;
                     const bool u8res = p.res != nullptr;
+                    // the form the fused residual takes in the paired arithmetic (0: neither, the scalar code does it)
+                    const int res_mode = e.ca == 1 && e.cb == -1 ? 1 : e.ca == 1 && e.cb == 1 ? 3 : 0;
+                    const int *b2row = tbl + L::TBL_CAP + 256 + sb * (SUBN / 2);
                     // the common case per warp: no tail row, Threshold replaces by its own threshold byte (or none)
                     const bool general = __any_sync(0xffffffffu, e.tailmask != 0) || (p.relu_thr >= 0 && p.relu_val != p.relu_thr);
                     const uint8_t *rrow = p.res + (size_t)(valid ? pm : 0) * p.res_ld + nsub0;
@@ -936,16 +997,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
 #pragma unroll
                             for (int i = 0; i < 32; i++) {
                                 const int c = nsub0 + cc * 32 + i;
-                                if (c < p.Cout) p.acc_out[(size_t)pm * p.Cout + c] = (int)acc[i] + trow[cc * 32 + i] + corr_pix;
+                                if (c < p.Cout) {
+                                    // the row's own tap rectangle, from the summed-area table of the channel's weights
+                                    const int satw = p.kW + 1;
+                                    const int *t = p.wsat + (size_t)c * (p.kH + 1) * satw;
+                                    const int wsum = __ldg(t + r1 * satw + s1) - __ldg(t + r0 * satw + s1) - __ldg(t + r1 * satw + s0) +
+                                                     __ldg(t + r0 * satw + s0);
+                                    p.acc_out[(size_t)pm * p.Cout + c] = (int)acc[i] + p.b_off * wsum + corr_pix;
+                                }
                             }
                         }
                         uint32_t words[8];
                         if (u8res) {
                             if (general) u8_chunk32<true, true>(acc, trow + cc * 32, brow + cc * 32, e, res0, res1, words);
+                            else if (res_mode == 1) u8_chunk32_pairs<1>(acc, trow + cc * 32, b2row + cc * 16, e, res0, res1, words);
+                            else if (res_mode == 3) u8_chunk32_pairs<3>(acc, trow + cc * 32, b2row + cc * 16, e, res0, res1, words);
                             else u8_chunk32<false, true>(acc, trow + cc * 32, brow + cc * 32, e, res0, res1, words);
                         } else {
                             if (general) u8_chunk32<true, false>(acc, trow + cc * 32, brow + cc * 32, e, res0, res1, words);
-                            else u8_chunk32<false, false>(acc, trow + cc * 32, brow + cc * 32, e, res0, res1, words);
+                            else u8_chunk32_pairs<0>(acc, trow + cc * 32, b2row + cc * 16, e, res0, res1, words);
                         }
                         if (check) {
                             // channels beyond the last real one are stored as zero bytes
@@ -956,7 +1026,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                             }
                         }
 #pragma unroll
-                        for (int g4 = 0; g4 < 8; g4++) rowsum = __dp4a(words[g4], 0x01010101u, rowsum);
+                        for (int g4 = 0; g4 < 8; g4++) rowsum = __dp4a(words[g4], 0x01010101u, rowsum);  // (dead code unless csum_out)
                         uint4 *dst = reinterpret_cast<uint4 *>(stg + row * (SUBN + 16) + cc * 32);
                         dst[0] = make_uint4(words[0], words[1], words[2], words[3]);
                         dst[1] = make_uint4(words[4], words[5], words[6], words[7]);
@@ -1205,7 +1275,11 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
         p.reverse = L::TMA_EPI && p.a_tma && (rev_mode == 1 ? (flip++ & 1) : rev_mode == 2);
     }
     const int tiles = (p.pair ? (p.m_tiles + 1) / 2 : p.m_tiles) * p.n_tiles;  // units of work
-    const int grid = tiles < num_sms() ? tiles : num_sms();
+    int grid = tiles < num_sms() ? tiles : num_sms();
+    // uint8: an epilogue group rebuilds its correction table whenever its next tile has other channels; with a grid that is a
+    // multiple of the column tiles every CTA stays on one column tile (148 -> 144 CTAs for 8 or 16 column tiles)
+    if (KIND == 2 && p.u8_classes > 0 && p.n_tiles > 1 && tiles > grid && grid % p.n_tiles && grid > 2 * p.n_tiles && knobs().u8_fast != 2)
+        grid -= grid % p.n_tiles;
     if (!L::TMA_EPI) {
         // staged epilogue: uint8 with nothing to gather runs a third group on warps 0-3 (a fourth accumulator exists below 256 columns)
         p.epi_groups = KIND == 2 && p.a_tma && BN < 256 ? 3 : 2;
