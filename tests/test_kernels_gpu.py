@@ -96,6 +96,33 @@ def test_conv_plain(lib, G, oracle, dtype, case):
     assert pad.numel() == 0 or float(pad.float().abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("case", [(1, 192, 13, 13, 384, 3, 1, 1), (1, 64, 27, 27, 192, 5, 1, 2), (2, 40, 9, 7, 72, 3, 2, 1)])
+def test_conv_f32_reduction_split_over_a_cluster(lib, G, oracle, case, knobs):
+    """fp32 convolution of few pixels (the batch-1 layers of AlexNet): the K steps are shared by the CTAs of a thread-block
+    cluster and summed in rank order through distributed shared memory.  Within the fp32 tolerance of the oracle, equal
+    from run to run (no atomics), and bias, residual and activation are applied once, by the cluster's first CTA."""
+    n, cin, h, w, cout, k, s, p = case
+    x, wt = _conv_inputs(case, 5, False)
+    rng = np.random.default_rng(6)
+    bias = rng.standard_normal(cout).astype(np.float32)
+    conv_ref = oracle.conv2d(x, wt, bias, (s, s), (p, p))
+    res = rng.standard_normal(conv_ref.shape).astype(np.float32)
+    ref = np.maximum(conv_ref - res, 0.0)
+    outs = []
+    for no_split in (0, 1, 0):
+        knobs(THB200_NO_SPLITK=no_split)
+        conv = G.Conv(lib, K.THB_F32, x.shape, wt, (s, s), (p, p))
+        conv.set_affine(None, bias)
+        rt, rld = G.to_nhwc(res, K.THB_F32)
+        conv.set_residual(rt, rld, 1.0, -1.0)
+        conv.set_act(K.ACT_THRESHOLD)
+        xt, _ = G.to_nhwc(x, K.THB_F32)
+        outs.append(G.from_nhwc(conv.run(xt, fill=3.0), cout))
+        assert G.rel_err(outs[-1], ref) < TOL[K.THB_F32], (case, no_split, G.rel_err(outs[-1], ref))
+    assert np.array_equal(outs[0], outs[2])            # the split sum does not depend on timing
+    assert G.rel_err(outs[0], outs[1]) < 1e-5          # and differs from the unsplit one by rounding order only
+
+
 @pytest.mark.parametrize("gather_only", [False, True])
 @pytest.mark.parametrize("crop", [0, 1])
 def test_conv_f16_rows_stored_with_padding(lib, G, oracle, gather_only, crop, knobs):

@@ -157,6 +157,34 @@ def test_lowp_vgg_bit_exact(th, oracle, tmp_path, batch):
     th.free_network(hl)
 
 
+@pytest.mark.parametrize("prec", [0, 1])
+def test_join_without_copies(th, oracle, tmp_path, monkeypatch, prec):
+    """JoinTable along the channels: the producers of the joined tensors (here the col2im of a transposed convolution and
+    an encoder convolution that a pooling reads as well) write straight into their channel slice of the joined buffer.
+    Same numbers as with the copies (THB200_JOIN_COPY=1), fewer launches, and both match the oracle."""
+    g = fx.segnet(width=0.5, size=32, classes=7)
+    x = g.make_input(3)
+    ref = oracle.run(g, x)
+    outs, launches = [], []
+    for keep in ("0", "1"):
+        monkeypatch.setenv("THB200_JOIN_COPY", keep)
+        h = _load(th, g, "py", tmp_path, "seg" + keep)
+        th.lib.THB200_SetPrecision(prec)
+        hc = th.lib.THCreateCudaNetwork(h)
+        th.free_network(h)
+        th.process_float(hc, x)                     # plans and warms up
+        n0 = th.lib.THB200_KernelLaunches()
+        out, _, _ = th.process_float(hc, x)
+        launches.append(th.lib.THB200_KernelLaunches() - n0)
+        outs.append(out.copy())
+        th.free_network(hc)
+    th.lib.THB200_SetPrecision(0)
+    assert np.array_equal(outs[0], outs[1])
+    assert launches[0] <= launches[1] - 6, launches   # four joins of two tensors, at least six copies gone
+    err = np.abs(outs[0] - ref.ravel()).max() / np.abs(ref).max()
+    assert err < (1e-4 if prec == 0 else 1e-2), err
+
+
 def test_lowp_rejects_what_the_reference_rejects(th, tmp_path):
     """SpatialFullConvolution and JoinTable have no lowp implementation (lowp_basic.c:197-208)."""
     g = fx.segnet(width=0.25, size=32, classes=5)

@@ -286,6 +286,66 @@ static float element_as_float(const void *p, long i, int dtype)
     return f;
 }
 
+/* Joining without a copy: when every launch that writes a value's buffer takes an output pitch (convolutions, pooling,
+ * elementwise kernels) and every reader takes an input pitch and a channel offset (the concatenation itself,
+ * convolutions, pooling), those launches are pointed at the value's channel slice of the joined buffer instead
+ * (thb_conv_desc.in_ld / out_ld and the kernels' x_ld / y_ld exist for this), and the value's own buffer is never
+ * allocated.  Returns 1 when done, 0 when the value has to be copied.  THB200_JOIN_COPY=1 keeps the copies (diagnostic). */
+static int write_into_slice(planner *P, int node, value *v, int jbuf, int jld, int coff)
+{
+    const char *e = getenv("THB200_JOIN_COPY"); /* (read while planning, not per launch) */
+    const int keep_copies = e && atoi(e);
+    instance *I = P->I;
+    if (keep_copies || node == P->M->output || v->buf < 0 || v->coff || v->row_pitch || v->s.flat || v->buf == I->in_val.buf)
+        return 0;
+    /* readers still to be planned will see the slice: all of them must be able to */
+    for (int j = 0; j < P->M->nnodes; j++) {
+        const thb_node *c = &P->M->nodes[j];
+        for (int q = 0; q < c->nin; q++)
+            if (c->in[q] == node && !(c->op == OP_CONCAT || c->op == OP_MAXPOOL || c->op == OP_AVGPOOL || (c->op == OP_CONV && q == 0)))
+                return 0;
+    }
+    /* no other value may live in the buffer (views and aliases), launches of the same fused chain apart */
+    for (int i = 0; i < P->M->nnodes; i++)
+        if (i != node && P->val[i].buf == v->buf && !P->absorbed[i]) return 0;
+    int writers = 0;
+    for (int t = 0; t < I->nsteps; t++) {
+        const step *s = &I->steps[t];
+        for (int k = 0; k < s->nin; k++)
+            if (s->in_buf[k] == v->buf) {
+                /* an earlier reader: its first operand, through a kernel that takes pitch and offset */
+                if (k != 0 || s->out_buf == v->buf || s->in_coff[0] || s->in_off0 || s->in_ld[0] != v->ld || s->dual ||
+                    !(s->kind == ST_CONV || s->kind == ST_MAXPOOL || s->kind == ST_AVGPOOL || s->kind == ST_CSUM || s->kind == ST_COPY))
+                    return 0;
+                if (s->kind == ST_CONV && (s->conv.in_ld != v->ld || s->conv.in_row_pitch)) return 0;
+            }
+        if (s->aux_buf == v->buf || s->aux2_buf == v->buf) return 0;
+        if (s->out_buf != v->buf) continue;
+        if (s->out_coff || s->out_off0 || s->out_ld != v->ld) return 0;
+        switch (s->kind) {
+        case ST_CONV: case ST_MAXPOOL: case ST_AVGPOOL: case ST_AFFINE: case ST_COMBINE: case ST_U8COMBINE: case ST_U8THR:
+        case ST_UPSAMPLE: case ST_COL2IM:
+            writers++;
+            break;
+        default:
+            return 0;
+        }
+    }
+    if (!writers) return 0;
+    for (int t = 0; t < I->nsteps; t++) {
+        step *s = &I->steps[t];
+        if (s->nin > 0 && s->in_buf[0] == v->buf) {
+            s->in_buf[0] = jbuf; s->in_ld[0] = jld; s->in_coff[0] = coff;
+            if (s->kind == ST_CONV) s->conv.in_ld = jld;
+        }
+        if (s->out_buf != v->buf) continue;
+        s->out_buf = jbuf; s->out_ld = jld; s->out_coff = coff;
+        if (s->kind == ST_CONV) s->conv.out_ld = jld;
+    }
+    v->buf = jbuf; v->ld = jld; v->coff = coff;
+    return 1;
+}
+
 static int sole_consumer(planner *P, int node)
 {
     if (P->uses[node] != 1 || node == P->M->output) return -1;
@@ -993,12 +1053,15 @@ static int plan_node(planner *P, int i)
         materialise(P, out, os);
         int coff = 0;
         for (int k = 0; k < n->nin; k++) {
-            const value *v = &P->val[n->in[k]];
-            s = new_step(P, ST_COPY);
-            step_in(s, v); step_out(s, out);
-            s->out_coff = coff;
-            s->pixels = (long)os.N * os.H * os.W; s->C = v->s.C;
-            coff += v->s.C;
+            value *v = &P->val[n->in[k]];
+            const int C = v->s.C;
+            if (!write_into_slice(P, n->in[k], v, out->buf, out->ld, coff)) {
+                s = new_step(P, ST_COPY);
+                step_in(s, v); step_out(s, out);
+                s->out_coff = coff;
+                s->pixels = (long)os.N * os.H * os.W; s->C = C;
+            }
+            coff += C;
         }
         return 0;
     }

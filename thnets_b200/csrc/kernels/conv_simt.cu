@@ -4,8 +4,15 @@
 // Block tile (16*TM) pixels x 64 output channels, K step 16, 256 threads, TM x 4 outputs per thread.
 // The A tile is gathered as float4 channel chunks (zero outside the image) and stored transposed in
 // shared memory; global loads of the next K step are issued before the current one is consumed.
+//
+// Few pixels (batch 1): the tile grid alone leaves most SMs idle and each CTA walks the whole reduction alone.  Then the
+// K steps are split over the CTAs of a thread-block cluster (grid z, up to 8): every CTA accumulates its share, the
+// others leave their partial tiles in their own shared memory, and the cluster's first CTA adds them up through
+// distributed shared memory in rank order (so the result does not depend on timing) and runs the epilogue.
 #include "common.cuh"
+#include <cooperative_groups.h>
 #include <string.h>
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -21,13 +28,16 @@ struct ConvSimtParams {
     float act_th, act_val, act_alpha;
 };
 
-template <int TM>
+int g_no_split = -1;  // THB200_NO_SPLITK, read once
+
+template <int TM, bool SPLIT>
 __global__ void __launch_bounds__(256) conv_simt_kernel(const ConvSimtParams p)
 {
     constexpr int BMT = 16 * TM, BNT = 64, BK = 16;
     constexpr int A_LOADS = (BMT * 4 + 255) / 256;
     __shared__ __align__(16) float As[BK][BMT + 4];
     __shared__ __align__(16) float Bs[BK][BNT];
+    __shared__ float red[SPLIT ? TM * 4 : 1][SPLIT ? 256 : 1];  // this CTA's partial tile, read by the cluster's first CTA
 
     const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
     const int m0 = blockIdx.x * BMT, n0 = blockIdx.y * BNT;
@@ -88,11 +98,14 @@ __global__ void __launch_bounds__(256) conv_simt_kernel(const ConvSimtParams p)
         *reinterpret_cast<float4 *>(&Bs[b_k][b_c]) = b_reg;
     };
 
-    load_global(0);
-    for (int kb = 0; kb < p.nkb; kb++) {
+    // this CTA's share of the K steps
+    const int kb0 = SPLIT ? (int)((long)p.nkb * blockIdx.z / gridDim.z) : 0;
+    const int kb1 = SPLIT ? (int)((long)p.nkb * (blockIdx.z + 1) / gridDim.z) : p.nkb;
+    if (kb0 < kb1) load_global(kb0);
+    for (int kb = kb0; kb < kb1; kb++) {
         store_smem();
         __syncthreads();
-        if (kb + 1 < p.nkb) load_global(kb + 1);
+        if (kb + 1 < kb1) load_global(kb + 1);
 #pragma unroll
         for (int k = 0; k < BK; k++) {
             float a[TM];
@@ -110,6 +123,27 @@ __global__ void __launch_bounds__(256) conv_simt_kernel(const ConvSimtParams p)
         __syncthreads();
     }
 
+    if (SPLIT) {
+        cg::cluster_group cluster = cg::this_cluster();
+        if (blockIdx.z != 0) {
+#pragma unroll
+            for (int i = 0; i < TM; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) red[i * 4 + j][t] = acc[i][j];
+        }
+        cluster.sync();
+        if (blockIdx.z == 0) {
+            for (unsigned r = 1; r < gridDim.z; r++) {
+                const float *remote = cluster.map_shared_rank(&red[0][0], r);
+#pragma unroll
+                for (int i = 0; i < TM; i++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) acc[i][j] += remote[(i * 4 + j) * 256 + t];
+            }
+        }
+        cluster.sync();  // the others' shared memory must outlive the reads above
+        if (blockIdx.z != 0) return;
+    }
     const int c0 = n0 + tx * 4;
     if (c0 >= p.Cout) return;
     float sc[4], sh[4], sl[4];
@@ -141,6 +175,9 @@ __global__ void __launch_bounds__(256) conv_simt_kernel(const ConvSimtParams p)
 
 }  // namespace
 
+// (library-internal: thb_conv_reload_knobs() calls it so that a test can switch THB200_NO_SPLITK between cases)
+extern "C" void thb_simt_reload_knobs(void) { g_no_split = -1; }
+
 extern "C" int thb_conv_fwd_simt(const thb_conv_desc *d, const void *x, void *y, thb_stream s)
 {
     if (!d->w || !d->kinfo) return THB_ERR_ARG;
@@ -160,9 +197,41 @@ extern "C" int thb_conv_fwd_simt(const thb_conv_desc *d, const void *x, void *y,
     const int gy = d->Cout_pad / 64;
     cudaStream_t st = (cudaStream_t)s;
     if ((long)((p.P + 127) / 128) * gy >= 120) {
-        conv_simt_kernel<8><<<dim3((p.P + 127) / 128, gy), 256, 0, st>>>(p);
+        conv_simt_kernel<8, false><<<dim3((p.P + 127) / 128, gy), 256, 0, st>>>(p);
     } else {
-        conv_simt_kernel<2><<<dim3((p.P + 31) / 32, gy), 256, 0, st>>>(p);
+        // how many CTAs share one tile's reduction: enough to give every SM about two CTAs, at least four K steps each
+        const long ctas = (long)((p.P + 31) / 32) * gy;
+        static int sms = 0;
+        int &no_split = g_no_split;
+        if (!sms) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (sms <= 0) sms = 148;
+        }
+        if (no_split < 0) {
+            const char *e = getenv("THB200_NO_SPLITK");
+            no_split = e && atoi(e) ? 1 : 0;
+        }
+        int split = 1;
+        while (split < 8 && ctas * split * 2 <= 2L * sms && p.nkb / (split * 2) >= 4) split *= 2;
+        if (split == 1 || no_split) {
+            conv_simt_kernel<2, false><<<dim3((p.P + 31) / 32, gy), 256, 0, st>>>(p);
+        } else {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((p.P + 31) / 32, gy, split);
+            cfg.blockDim = dim3(256);
+            cfg.stream = st;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 1;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = split;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            const cudaError_t le = cudaLaunchKernelEx(&cfg, conv_simt_kernel<2, true>, p);
+            if (le != cudaSuccess) return thb_note_launch(le, "conv_simt_kernel (split K)");
+        }
     }
     return THB_LAUNCH_CHECK("conv_simt_kernel");
 }

@@ -1505,7 +1505,12 @@ const CUtensorMap *weights_half_tmap(const thb_conv_desc *d)
 
 }  // namespace
 
-extern "C" void thb_conv_reload_knobs(void) { read_knobs(); }
+extern "C" void thb_simt_reload_knobs(void);
+extern "C" void thb_conv_reload_knobs(void)
+{
+    read_knobs();
+    thb_simt_reload_knobs();
+}
 
 extern "C" int thb_conv_make_tmap(const thb_conv_desc *d, thb_tmap *out)
 {

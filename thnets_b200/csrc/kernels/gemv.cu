@@ -67,16 +67,22 @@ __global__ void __launch_bounds__(256, 4) gemv_kernel(const T *x, int K, int x_l
     constexpr int VN = V16<T>::N, U = GemvWalk<T, NB>::U;
     __shared__ float part[2][8][NB];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nvec = K / VN;
+    GemvWalk<T, NB> walk{reinterpret_cast<const uint4 *>(w), nvec, (nvec + U * 256 - 1) / (U * 256), M, (int)gridDim.x,
+                         (int)blockIdx.x, 0};
+    uint4 buf0[U], buf1[U];
+    // Programmatic dependent launch: the weights do not depend on the kernel before this one, so the first batch of
+    // every CTA is on its way while that kernel drains (and the next kernel of the stream may start its own in the same
+    // way); x is read and y written only after the wait.
+    walk.load(buf0);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (blockIdx.x == 0) {
         // channels of the padded tail of y are kept at exact zero
         const int m = M + threadIdx.x;
         if (m < (M + VN - 1) / VN * VN && m < y_ld)
             for (int n = 0; n < NB; n++) dt<T>::st(y + (size_t)n * y_ld + m, 0.f);
     }
-    const int nvec = K / VN;
-    GemvWalk<T, NB> walk{reinterpret_cast<const uint4 *>(w), nvec, (nvec + U * 256 - 1) / (U * 256), M, (int)gridDim.x,
-                         (int)blockIdx.x, 0};
-    uint4 buf0[U], buf1[U];
     float acc[NB];
 #pragma unroll
     for (int n = 0; n < NB; n++) acc[n] = 0.f;
@@ -122,7 +128,6 @@ __global__ void __launch_bounds__(256, 4) gemv_kernel(const T *x, int K, int x_l
         crow += gridDim.x;
     };
 
-    walk.load(buf0);
     while (crow < M) {
         walk.load(buf1);
         consume(buf0);
@@ -144,15 +149,26 @@ int launch_gemv(const void *x, int N, int K, int x_ld, const void *w, int M, con
         if (sms <= 0) sms = 148;
     }
     const int grid = M < 4 * sms ? M : 4 * sms;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t le = cudaSuccess;
 #define GEMV_CASE(NB)                                                                                                   \
     case NB:                                                                                                            \
-        gemv_kernel<T, NB><<<grid, 256, 0, st>>>((const T *)x, K, x_ld, (const T *)w, M, scale, shift, a, (T *)y, y_ld); \
+        le = cudaLaunchKernelEx(&cfg, gemv_kernel<T, NB>, (const T *)x, K, x_ld, (const T *)w, M, scale, shift, a, (T *)y, y_ld); \
         break;
     switch (N) {
         GEMV_CASE(1) GEMV_CASE(2) GEMV_CASE(3) GEMV_CASE(4) GEMV_CASE(5) GEMV_CASE(6) GEMV_CASE(7) GEMV_CASE(8)
     default: return THB_ERR_UNSUPPORTED;
     }
 #undef GEMV_CASE
+    if (le != cudaSuccess) return thb_note_launch(le, "gemv_kernel");
     return THB_LAUNCH_CHECK("gemv_kernel");
 }
 
