@@ -10,16 +10,22 @@ ResNet-50, fp16, batch 256 per GPU, 3x224x224 synthetic inputs ~N(0,1), seeded H
                     [--dtype fp16|fp32|bf16|int8] [--batch B] [--impl reference]
 
 JSON line (rank 0):
-  value    device-resident throughput: inputs already in HBM, K forwards timed with CUDA events on the
-           launching stream, max over ranks;
+  value    device-resident throughput: the fp32 NCHW batch already in HBM, K forwards (boundary kernels at both ends
+           included) timed with CUDA events on the launching stream, max over ranks;
   e2e      the same through THProcessFloat with a pinned HOST batch: H2D of the fp32 input and D2H of the
-           logits inside the timed region (wall clock, max over ranks);
-  roofline the dominant kernel (implicit-GEMM convolution): algorithmic FLOPs of all its launches in one
-           forward / their summed event-timed durations, against the measured bf16 GEMM peak (twice that for
-           uint8); roofline.two_roof_bound: the time those launches would take if each ran at the slower of its
-           two roofs (FLOPs / tensor peak, algorithmic bytes / measured HBM bandwidth) and its ratio to the
-           measured time -- many layers of a residual network are HBM-bound;
-  cpu_baseline the unmodified reference CPU build timed on this box's host cores on a bounded sample.
+           logits inside the timed region (wall clock, max over ranks); e2e.pageable_host_buffer: an ordinary buffer;
+  roofline the dominant kernels (the implicit-GEMM convolutions): algorithmic FLOPs of all their launches in one
+           forward / their time per step (the step's event time x their share of the per-launch profile), against
+           the measured burst bf16 GEMM peak (twice that for uint8; the sustained figure beside it);
+           roofline.two_roof_bound: the time those launches would take if each ran at the slower of its two roofs
+           (FLOPs / tensor peak, algorithmic bytes / measured HBM bandwidth) and its ratio to the measured time --
+           more than half the launches of a residual network are HBM-bound; roofline.traffic: DRAM bytes per step
+           from the ncu capture summarised under profiles/;
+  parity   the logits of this run against the reference's for the same batch (max-abs error / max-abs value, argmax
+           agreement), when the reference ran;
+  cpu_baseline the unmodified reference CPU build timed on this box's host cores on a bounded sample;
+  e2e_images, int8, strong   sub-records: THProcessImages from byte images, the uint8 engine on the same network,
+           and (N > 1) one batch of 256 sharded over the N GPUs by rank 0 alone.
 `--impl reference` times only that CPU reference and prints the same line with "impl": "reference".
 """
 import argparse
@@ -52,8 +58,9 @@ LOWP_RANGE = 20.0
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the convolution launches of ONE forward, from the ncu capture whose
-# summary is kept under profiles/ (captured at batch 128, activations scaled to batch 256, weights once)
-NCU_DRAM_BYTES_PER_STEP = {("resnet50", "fp16", 256): 9.08e9}
+# summary is profiles/conv_resnet50_fp16_b128_dram_tensor.md (captured at batch 128: 4.423 GB, of which 0.051 GB are
+# weights; activations scaled to batch 256, weights counted once); None for workloads without a capture
+NCU_DRAM_BYTES_PER_STEP = {("resnet50", "fp16", 256): 8.80e9}
 
 
 def read_peaks():
@@ -343,7 +350,8 @@ def measure(arm, steps, warmup, world, barrier, max_over_ranks, peaks):
         # GEMM peak is the denominator (the sustained figure is given beside it).
         peak = peaks["tflops_burst"] * (2 if u8 else 1)
         ach = conv_fl / (conv_ms * 1e-3) / 1e12 if conv_ms > 0 else 0.0
-        roof = {"bound": "tensor", "kernel": "conv_tc_kernel" if arm.dtype != "fp32" else "conv_simt_kernel",
+        roof = {"bound": "tensor",
+                "kernel": "conv_simt_kernel" if arm.dtype == "fp32" else "conv_tc_kernel" if u8 else "conv_tc_kernel + conv_patch_tc_kernel",
                 "achieved": ach, "peak": peak, "unit": "TFLOP/s" if not u8 else "TOP/s", "frac": ach / peak,
                 "peak_source": "of " + peaks["src"] + (": bf16_tflops (burst)" if not u8 else ": 2 x bf16_tflops (burst)"),
                 "frac_of_sustained_peak": ach / (peaks["tflops"] * (2 if u8 else 1)),
