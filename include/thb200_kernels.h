@@ -167,6 +167,11 @@ int thb_conv_padded_rows_supported(int dtype);
 /* u8 HWC images (already on the device, row stride `stride`) -> normalised NHWC dtype (thapi.c:20-46) */
 int thb_preprocess_images(const unsigned char *img, int N, int H, int W, int stride, int cp, int bgr,
                           const float *mean3, const float *std3, int dtype, void *y, int y_ld, thb_stream s);
+/* one YUYV frame (already on the device, 2 bytes per pixel, W even) -> normalised NHWC dtype with 3 channels: the
+ * table-driven conversion of yuyv2fRGB (thapi.c:48-117) computed per pixel pair.  F32 / F16 / BF16; U8 is refused as the
+ * reference refuses THProcessYUYV on its lowp engine (thapi.c:588-591). */
+int thb_preprocess_yuyv(const unsigned char *frame, int H, int W, const float *mean3, const float *std3, int dtype, void *y,
+                        int y_ld, thb_stream s);
 /* u8 HWC RGB images -> normalised, space-to-depth NHWC dtype in the padded-row layout of thb_preprocess_s2d_padded
  * (F16 / BF16): THProcessImages feeding a stride-2 first convolution (thapi.c:20-46 arithmetic) */
 int thb_preprocess_images_s2d(const unsigned char *img, int N, int H, int W, int stride, int bgr, const float *mean3,

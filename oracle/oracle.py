@@ -50,6 +50,28 @@ def ref_lib(kind="auto"):
     return p if os.path.exists(p) else None
 
 
+def yuyv_to_float(frame, width, height, mean, std):
+    """The reference's YUYV frame -> normalised float RGB planes [3, height, width] (thapi.c:48-117): table-driven integer
+    conversion (every quotient truncated towards zero, as C integer division does), saturation to a byte, then
+    (byte * 0.003921568f - mean) * (1 / std) in float32.  Test infrastructure only."""
+    q = np.asarray(frame, np.uint8).reshape(height, width // 2, 4).astype(np.int64)
+
+    def tdiv(a):  # C division by 256
+        return np.where(a >= 0, a // 256, -((-a) // 256))
+    y0, u, y1, v = q[..., 0], q[..., 1] - 128, q[..., 2], q[..., 3] - 128
+    yur, yub = tdiv(459 * v), tdiv(541 * u)
+    yg = tdiv(-137 * u) + tdiv(-55 * v)
+    out = np.empty((3, height, width), np.float32)
+    mean = np.asarray(mean, np.float32)
+    istd = (np.float32(1) / np.asarray(std, np.float32)).astype(np.float32)
+    for k, yy in enumerate((y0, y1)):
+        ys = tdiv((yy - 16) * 298)
+        for c, term in enumerate((yur, yg, yub)):
+            byte = np.clip(ys + term, 0, 255).astype(np.float32)
+            out[c, :, k::2] = (byte * np.float32(0.003921568) - mean[c]) * istd[c]
+    return out
+
+
 def _fp(a):
     return a.ctypes.data_as(_f)
 

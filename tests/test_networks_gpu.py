@@ -240,6 +240,29 @@ def test_process_images_matches_float_path(th, oracle, tmp_path):
     th.free_network(h)
 
 
+def test_process_yuyv(th, oracle, tmp_path):
+    """THProcessYUYV (thapi.c:575-612): the frame is converted on the GPU with the reference's integer tables; a network
+    as loaded takes it, a converted one refuses it as the reference's converted networks do."""
+    from oracle.oracle import yuyv_to_float
+    g = fx.alexnet_owt(width=0.25, size=64, classes=10, fc=32)
+    h = _load(th, g, "t7", tmp_path, "alexyuv")
+    rng = np.random.default_rng(8)
+    frame = rng.integers(0, 256, 64 * 64 * 2).astype(np.uint8)
+    frame[:64] = np.tile(np.array([0, 0, 255, 255, 16, 128, 235, 128], np.uint8), 8)   # the corners of the tables
+    out, ow, oh = th.process_yuyv(h, frame, 64, 64)
+    x = yuyv_to_float(frame, 64, 64, g.mean, g.std)[None]
+    plain = fx.Graph()
+    plain.nodes, plain.output = g.nodes, g.output
+    ref = oracle.run(plain, x)
+    assert (ow, oh) == (1, 1)
+    assert rel_err(out, ref.ravel()) < 1e-4
+    hc = th.lib.THCreateCudaNetwork(h)
+    th.free_network(h)
+    none, _, _ = th.process_yuyv(hc, frame, 64, 64)
+    assert none is None and b"not supported" in th.lib.THB200_LastErrorString()
+    th.free_network(hc)
+
+
 def _convert(th, g, kind, tmp_path, name, mode):
     h = _load(th, g, kind, tmp_path, name)
     th.lib.THB200_SetPrecision(mode)

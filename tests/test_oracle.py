@@ -234,3 +234,25 @@ def test_upsample_restatement():
     o = Oracle()
     x = np.random.default_rng(3).standard_normal((2, 3, 4, 5)).astype(np.float32)
     assert np.array_equal(o.upsample2x(x), x.repeat(2, axis=2).repeat(2, axis=3))
+
+
+@needs_ref
+def test_yuyv_conversion_against_the_live_reference(oracle, tmp_path):
+    """THProcessYUYV of the reference (thapi.c:575-612) on a Torch7 network = the oracle's forward of the frame converted by
+    its restatement of yuyv2fRGB."""
+    from oracle.oracle import yuyv_to_float
+    from thnets_b200.capi import THNets
+    g = fx.alexnet_owt(width=0.25, size=64, classes=10, fc=32)
+    d = str(tmp_path / "alex")
+    fx.write_torch7(g, d)
+    ref = THNets(ref_lib())
+    h = ref.load_network(d)
+    rng = np.random.default_rng(8)
+    frame = rng.integers(0, 256, 64 * 64 * 2).astype(np.uint8)
+    out, _, _ = ref.process_yuyv(h, frame, 64, 64)
+    ref.free_network(h)
+    x = yuyv_to_float(frame, 64, 64, g.mean, g.std)[None]
+    plain = fx.Graph()
+    plain.nodes, plain.output = g.nodes, g.output   # same weights, identity statistics
+    want = oracle.run(plain, x)
+    assert rel_err(want.ravel(), out) < 2e-5

@@ -115,6 +115,20 @@ class THNets:
         out = np.ctypeslib.as_array(res, shape=(cnt,)).copy()
         return out, ow.value, oh.value
 
+    def process_yuyv(self, h, frame, width, height):
+        """frame: uint8 array of height*width*2 bytes (Y0 U Y1 V per pixel pair)."""
+        f = np.ascontiguousarray(frame, np.uint8)
+        res = C.POINTER(C.c_float)()
+        ow, oh = C.c_int(), C.c_int()
+        self.lib.THProcessYUYV.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.POINTER(C.c_float)),
+                                           C.POINTER(C.c_int), C.POINTER(C.c_int)]
+        self.lib.THProcessYUYV.restype = C.c_int
+        cnt = self.lib.THProcessYUYV(h, f.ctypes.data, width, height, C.byref(res), C.byref(ow), C.byref(oh))
+        if cnt <= 0:
+            return None, 0, 0
+        out = np.ctypeslib.as_array(res, shape=(cnt,)).copy()
+        return out, ow.value, oh.value
+
     def process_images(self, h, images, bgr=0):
         """images: list of uint8 [H,W,3] arrays of equal size."""
         n = len(images)

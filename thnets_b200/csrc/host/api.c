@@ -351,10 +351,21 @@ int THProcessImages(THNETWORK *network, unsigned char **images, int batchsize, i
 int THProcessYUYV(THNETWORK *network, unsigned char *image, int width, int height, float **results, int *outwidth,
                   int *outheight)
 {
-    (void)network; (void)image; (void)width; (void)height; (void)results; (void)outwidth; (void)outheight;
-    /* the reference refuses this entry point on every non-CPU engine (thapi.c:580-591) */
-    THError("This function is not supported with CUDA");
-    return 0;
+    /* thapi.c:575-612: one YUYV frame -> a 3 x height x width tensor (yuyv2fRGB with the network's mean / std) -> forward.
+     * The reference refuses this entry point on its converted (cuDNN, OpenCL, lowp) networks and so does this library;
+     * a network as THLoadNetwork returned it takes the frame: the bytes are copied as they are and converted on the GPU. */
+    thb_netx *x = netx(network);
+    thb_result r;
+    if (network->net && network->net->engine != ENGINE_CPU) {
+        thb_set_error(network->net->engine == ENGINE_LOWP ? "This function is not supported with Lowp"
+                                                          : "This function is not supported with CUDNN");
+        return fatal_or(0);
+    }
+    if (width < 2 || (width & 1) || height < 1) { thb_set_error("THProcessYUYV needs an even width"); return fatal_or(0); }
+    if (ensure_engine(x)) return fatal_or(0);
+    if (thb_engine_forward(x->engine, 0, &image, width * 2, 0, 2, 1, 3, height, width, 3, network->mean, network->std, 0, &r))
+        return fatal_or(0);
+    return publish(network, &r, results, outwidth, outheight);
 }
 
 THFloatTensor *THForward(THNETWORK *network, THFloatTensor *in)

@@ -1840,6 +1840,9 @@ static int boundary_in(thb_engine *E, instance *I, int has_x, int inplace, int c
     else if (has_x)
         rc = thb_preprocess(I->d_in, inplace ? I->d_in : 0, I->slice_n, C, H, W, mean, std, E->dtype, in_ptr, I->in_val.ld,
                             q_sub, q_mult, I->stream);
+    else if (cp == 2) /* one YUYV frame (THProcessYUYV) */
+        rc = E->dtype == THB_U8 ? THB_ERR_UNSUPPORTED
+                                : thb_preprocess_yuyv(I->d_img, H, W, mean, std, E->dtype, in_ptr, I->in_val.ld, I->stream);
     else if (E->dtype == THB_U8) {
         rc = thb_preprocess_images_lowp(I->d_img, I->slice_n, H, W, W * cp, bgr, mean, std, in_ptr, I->in_val.ld, &q_sub,
                                         &q_mult, I->stream);

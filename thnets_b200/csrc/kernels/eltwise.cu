@@ -268,6 +268,37 @@ __global__ void preprocess_images_s2d_kernel(const uint8_t *img, int N, int H, i
     }
 }
 
+// One YUYV frame (Y0 U Y1 V per pixel pair) -> normalised NHWC T with three channels, the arithmetic of the reference's
+// table-driven converter (thapi.c:48-117): Y' = (Y-16)*298/256, R = sat(Y' + 459*(V-128)/256),
+// G = sat(Y' - 137*(U-128)/256 - 55*(V-128)/256), B = sat(Y' + 541*(U-128)/256), every quotient truncated towards zero
+// as C integer division does, then (byte * 0.003921568f - mean) * (1/std).  One thread per pixel pair.
+template <typename T>
+__global__ void preprocess_yuyv_kernel(const uint8_t *frame, int H, int W, float3 mean, float3 istd, T *y, int y_ld)
+{
+    constexpr int VN = Vec<T>::N;
+    const long pair = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int W2 = W / 2;
+    if (pair >= (long)H * W2) return;
+    const uchar4 q = *reinterpret_cast<const uchar4 *>(frame + pair * 4);  // Y0 U Y1 V
+    const int u = (int)q.y - 128, v = (int)q.w - 128;
+    const int yur = 459 * v / 256, yub = 541 * u / 256, yg = -137 * u / 256 + -55 * v / 256;
+    const int ys[2] = {((int)q.x - 16) * 298 / 256, ((int)q.z - 16) * 298 / 256};
+    const float m[3] = {mean.x, mean.y, mean.z}, is[3] = {istd.x, istd.y, istd.z};
+#pragma unroll
+    for (int k = 0; k < 2; k++) {
+        const int rgb[3] = {min(255, max(0, ys[k] + yur)), min(255, max(0, ys[k] + yg)), min(255, max(0, ys[k] + yub))};
+        float out[VN > 4 ? VN : 4];
+#pragma unroll
+        for (int c = 0; c < (VN > 4 ? VN : 4); c++)
+            out[c] = c < 3 ? __fmul_rn(__fsub_rn(__fmul_rn((float)rgb[c], 0.003921568f), m[c]), is[c]) : 0.f;
+        // (the row of W pixels is contiguous: pixel index = 2 * pair + k)
+        float vv[VN];
+#pragma unroll
+        for (int c = 0; c < VN; c++) vv[c] = out[c];
+        Vec<T>::store(y + (pair * 2 + k) * y_ld, vv);
+    }
+}
+
 // u8 HWC images -> quantised NHWC u8 with the static input range of the lowp image loader
 // (lowp/lowp_basic.c:82-131, lowp/lowp_images.c): q = (unsigned char)(int)roundf((px - sub[c]) * mult[c])
 __global__ void preprocess_images_u8_kernel(const uint8_t *img, int N, int H, int W, int stride, int bgr, int3 sub, float3 mult,
@@ -792,6 +823,18 @@ int thb_preprocess_images(const unsigned char *img, int N, int H, int W, int str
     DISPATCH_FLOAT_DTYPE(dtype, (preprocess_images_kernel<T><<<nblocks(pix), 256, 0, (cudaStream_t)s>>>(
                                     img, N, H, W, stride, cp, bgr, m, is, (T *)y, y_ld)));
     return THB_LAUNCH_CHECK("preprocess_images_kernel");
+}
+
+int thb_preprocess_yuyv(const unsigned char *frame, int H, int W, const float *mean3, const float *std3, int dtype, void *y,
+                        int y_ld, thb_stream s)
+{
+    if (H < 1 || W < 2 || (W & 1) || y_ld < 3) return THB_ERR_ARG;
+    if (dtype == THB_U8) return THB_ERR_UNSUPPORTED;  // (the reference refuses this entry point on its lowp engine)
+    const long pairs = (long)H * (W / 2);
+    float3 m = make_float3(mean3[0], mean3[1], mean3[2]);
+    float3 is = make_float3(1 / std3[0], 1 / std3[1], 1 / std3[2]);
+    DISPATCH_FLOAT_DTYPE(dtype, (preprocess_yuyv_kernel<T><<<nblocks(pairs), 256, 0, (cudaStream_t)s>>>(frame, H, W, m, is, (T *)y, y_ld)));
+    return THB_LAUNCH_CHECK("preprocess_yuyv_kernel");
 }
 
 int thb_preprocess_images_s2d(const unsigned char *img, int N, int H, int W, int stride, int bgr, const float *mean3, const float *std3,
