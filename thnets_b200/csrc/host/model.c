@@ -177,6 +177,9 @@ static int lower_leaf(builder *b, struct module *m, val in, val *out)
         n->numElements = m->View.numElements;
         break;
     case MT_Reshape:
+        /* Reshape.c:22-36: to `size` without a batch dimension, or to `batchsize` with the input's batch in front; built
+         * for a one-dimensional target (the flatten in front of a classifier), where it is what View does */
+        if (m->Reshape.nsize > 1) return fail(b, "Reshape to more than one dimension is not supported by the B200 engine");
         n = new_node(b, OP_VIEW, 1, in.id);
         n->numElements = m->Reshape.numElements;
         break;
