@@ -1742,11 +1742,14 @@ static int engine_build(thb_engine *E, int N, int C, int H, int W, int rank, int
         }
     }
     E->built = G;
-    /* sub-batches per GPU for pipelined host-input forwards: worth it once a slice's input copy takes about a
-     * millisecond; the uint8 engine needs the input range of the whole batch before any kernel can start */
+    /* Sub-batches per GPU for pipelined host-input forwards.  Two sub-batches hide about 0.6 of the input copy (measured
+     * at ~50 GB/s from pinned memory) and cost every launch's fill and drain a second time (~6 us each, with a margin):
+     * worth it for a float batch of ResNet-50 (154 MB, 2.8 ms of copy), not for the same batch as byte images (38 MB).
+     * The uint8 engine needs the input range of the whole batch before any kernel can start. */
     const int per_gpu = N / G;
-    const double in_mb = (double)per_gpu * C * H * W * 4 / 1e6;
-    E->chunks = E->dtype == THB_U8 || in_mb < 32 ? 1 : per_gpu >= 32 ? 2 : 1;
+    const double in_mb = (double)per_gpu * (cp ? (double)H * W * cp : (double)C * H * W * 4) / 1e6;
+    const double copy_ms = in_mb / 50.0, refill_ms = E->inst[0].nsteps * 0.006 * 1.5 + 0.1;
+    E->chunks = E->dtype == THB_U8 || per_gpu < 32 || copy_ms * 0.6 <= refill_ms ? 1 : 2;
     const char *ce = getenv("THB200_CHUNKS");
     if (ce) E->chunks = atoi(ce) < 1 || E->dtype == THB_U8 ? 1 : atoi(ce) > 4 ? 4 : atoi(ce);
     if (E->chunks > per_gpu || E->whole_batch) E->chunks = 1;
