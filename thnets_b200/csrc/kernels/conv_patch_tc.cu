@@ -52,7 +52,6 @@ struct PatchParams {
     float act_th, act_val, act_alpha;
     int kind;               // 0 fp16, 1 bf16
     int pdl;
-    int debug;              // timing experiments: 1 one tap only, 2 no epilogue work, 4 no patch copies, 8 no activation pass, 16 no pooling pass
     int *status;
 };
 
@@ -276,7 +275,6 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
                     break;
                 }
                 const uint32_t bar = smem_u32(&full[s]);
-                if (p.debug & 4) { mbar_arrive(bar); continue; }
                 mbar_arrive_expect_tx(bar, box_bytes);
                 tma_load_4d(smem_u32(sP + s * p.stage_bytes), &tmapA, bar, 0, q.c0 - p.padW + p.xoff, q.r0 - p.padH, q.n);
             }
@@ -297,7 +295,7 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
             const uint64_t proto = make_rows_desc(0u, PX);
             const uint32_t hi = (uint32_t)(proto >> 32), lo_flags = (uint32_t)proto;
             const uint32_t b_lo0 = lo_flags | ((smem_u32(sW) >> 4) & 0x3FFFu);
-            const int ntaps = (p.debug & 1) ? 1 : taps;
+            const int ntaps = taps;
             int ring_s = 0;
             uint32_t ring_ph = 0;
             bool alive = mbar_wait_bounded(smem_u32(w_full), 0);
@@ -376,7 +374,6 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&acc_empty[ab]));
-            if (p.debug & 2) continue;
             // the tile about to be written was the source of the store two units ago (of the last one with a single tile)
             if (et == 0) {
                 if (!KP && p.ct_bufs == 1) bulk_wait_group_read<0>();
@@ -384,7 +381,7 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
             }
             uint8_t *tile = KP || p.ct_bufs == 1 ? ct : ct + (u & 1) * PT_CT_BYTES;
             if (!KP) epi_bar_sync();
-            if (valid && !(p.debug & 8)) {
+            if (valid) {
                 uint4 o[4];
                 if (ch == 0) activate_half<0>(acc, p, act_mode, s_slope, o);
                 else activate_half<1>(acc, p, act_mode, s_slope, o);
@@ -406,7 +403,7 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
             epi_bar_sync();                       // the activated patch is complete
             if (*abort_flag) break;
             uint8_t *ptile = pt + (u & 1) * PT_PT_BYTES;
-            if (et < items && !(p.debug & 16)) {
+            if (et < items) {
                 // window of this thread's pooled pixel, clipped to the convolution output
                 const int gr0 = q.r0 + 2 * it_pr, gc0 = q.c0 + 2 * it_pc;
                 uint32_t mx[4] = {neg_inf2, neg_inf2, neg_inf2, neg_inf2};
@@ -652,7 +649,6 @@ int patch_launch(const thb_conv_desc *d, int pk, int ppad, int pH, int pW, const
         use_pdl = ev ? atoi(ev) : 1;
     }
     p.pdl = use_pdl;
-    if (const char *dv = getenv("THB200_PATCH_DEBUG")) p.debug = atoi(dv);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(PT_THREADS);
