@@ -240,6 +240,29 @@ def test_process_images_matches_float_path(th, oracle, tmp_path):
     th.free_network(h)
 
 
+def test_pageable_batches_are_staged_through_pinned_memory(th, tmp_path, monkeypatch):
+    """A float batch in ordinary host memory (>= 8 MB) is copied into the library's pinned buffer by the host threads, slice
+    by slice, and sent from there: same result as handing the pointer to the driver (THB200_NO_STAGING=1), with and
+    without sub-batches, and the caller's buffer gets its in-place normalisation either way."""
+    g = fx.alexnet_owt(width=0.25, size=224, classes=20, fc=64)
+    x = g.make_input(16)                                   # 9.6 MB
+    h = _load(th, g, "t7", tmp_path, "alexpg")
+    outs, bufs = [], []
+    for chunks, nostage in ((1, "0"), (2, "0"), (1, "1"), (2, "1")):
+        monkeypatch.setenv("THB200_NO_STAGING", nostage)
+        th.lib.THB200_SetPipelineChunks(chunks)
+        buf = np.array(x, copy=True)
+        out, _, _ = th.process_float(h, buf, copy_input=False)
+        outs.append(out)
+        bufs.append(buf)
+    th.lib.THB200_SetPipelineChunks(0)
+    th.free_network(h)
+    assert np.array_equal(outs[0], outs[2]) and np.array_equal(outs[1], outs[3])      # staged == not staged
+    assert rel_err(outs[1], outs[0]) < 1e-5     # (sub-batches of 6 and 10 images may take other fp32 tile shapes than 16)
+    assert all(np.array_equal(bufs[0], b) for b in bufs[1:])
+    assert not np.array_equal(bufs[0], x)                  # mean 0.45 / std 0.225: normalised in place
+
+
 def test_process_yuyv(th, oracle, tmp_path):
     """THProcessYUYV (thapi.c:575-612): the frame is converted on the GPU with the reference's integer tables; a network
     as loaded takes it, a converted one refuses it as the reference's converted networks do."""

@@ -150,6 +150,8 @@ struct thb_engine {
     int chunks, pipe_built, pipe_chunks;
     float *h_out;
     size_t h_out_bytes;
+    float *h_stage; /* pinned staging buffer for float batches that arrive in pageable host memory */
+    size_t h_stage_bytes;
     float last_ms;
     int peer_gather;
     /* arguments of the last forward, for the device-resident timing loop */
@@ -1687,6 +1689,7 @@ void thb_engine_destroy(thb_engine *E)
     for (int g = 0; g < 8; g++) instance_free(&E->inst[g]);
     for (int g = 0; g < 32; g++) instance_free(&E->pipe[g]);
     thb_host_free_pinned(E->h_out);
+    thb_host_free_pinned(E->h_stage);
     thb_model_release(E->model);
     free(E);
 }
@@ -1885,6 +1888,27 @@ static int device_forward(thb_engine *E, instance *I, int has_x, int inplace, in
     return boundary_out(E, I, dst);
 }
 
+/* 1 when `p` is ordinary (pageable) host memory: a copy from it is staged by the driver at a fraction of the link rate and
+ * blocks the calling thread */
+static int host_is_pageable(const void *p)
+{
+    struct cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return a.type == cudaMemoryTypeUnregistered;
+}
+
+/* host-to-host copy by all the host threads OpenMP gives this process (1 MB blocks) */
+static void parallel_copy(void *dst, const void *src, size_t bytes)
+{
+    const size_t blk = (size_t)1 << 20;
+    const long nb = (long)((bytes + blk - 1) / blk);
+#pragma omp parallel for schedule(static)
+    for (long b = 0; b < nb; b++) {
+        const size_t o = (size_t)b * blk;
+        memcpy((char *)dst + o, (const char *)src + o, bytes - o < blk ? bytes - o : blk);
+    }
+}
+
 int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stride, int bgr, int cp, int N, int C, int H,
                        int W, int rank, const float *mean, const float *std, int inplace, thb_result *res)
 {
@@ -1912,34 +1936,6 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
     const size_t img_elems = (size_t)C * H * W;
     float q_sub = 0, q_mult = 0;
 
-    /* stage the input slices */
-    for (int g = 0; g < G; g++) {
-        instance *I = &set[g];
-        CU(cudaSetDevice(I->device));
-        if (x) {
-            CU(cudaMemcpyAsync(I->d_in, x + (size_t)I->slice_off * img_elems, (size_t)I->slice_n * img_elems * sizeof(float),
-                               cudaMemcpyHostToDevice, I->stream));
-        } else if ((size_t)stride == (size_t)W * cp) {
-            /* tightly packed rows: one copy per run of images that also follow one another in host memory */
-            const size_t img_bytes = (size_t)H * W * cp;
-            for (int n = 0; n < I->slice_n;) {
-                int run = 1;
-                while (n + run < I->slice_n && images[I->slice_off + n + run] == images[I->slice_off + n + run - 1] + img_bytes) run++;
-                CU(cudaMemcpyAsync(I->d_img + (size_t)n * img_bytes, images[I->slice_off + n], (size_t)run * img_bytes,
-                                   cudaMemcpyHostToDevice, I->stream));
-                n += run;
-            }
-        } else {
-            for (int n = 0; n < I->slice_n; n++)
-                CU(cudaMemcpy2DAsync(I->d_img + (size_t)n * H * W * cp, (size_t)W * cp, images[I->slice_off + n], stride,
-                                     (size_t)W * cp, H, cudaMemcpyHostToDevice, I->stream));
-        }
-    }
-    if (lowp_input_range(E, set, G, x != 0, cp, C, H, W, mean, std, &q_sub, &q_mult)) return -1;
-    /* what the device-resident timing loop needs to repeat this forward from the staged input */
-    E->last_has_x = x != 0; E->last_cp = cp; E->last_bgr = bgr;
-    for (int k = 0; k < 3; k++) { E->last_mean[k] = mean[k]; E->last_std[k] = std[k]; }
-
     long total = 0;
     for (int g = 0; g < G; g++) total += set[g].out_count;
     if ((size_t)total * sizeof(float) > E->h_out_bytes) {
@@ -1948,21 +1944,75 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
         E->h_out = thb_host_alloc_pinned(E->h_out_bytes);
         if (!E->h_out) { thb_set_error("pinned result allocation failed"); return -1; }
     }
+    /* A float batch in pageable memory (what a caller of the reference passes) goes through a pinned buffer of the
+     * library, filled slice by slice by the host's threads, so that the copy to the device runs at link speed and under
+     * the previous slice's kernels (THB200_NO_STAGING=1: hand the caller's pointer to the driver as it is). */
+    int staged = 0;
+    if (x && (size_t)N * img_elems * sizeof(float) >= ((size_t)8 << 20) && host_is_pageable(x)) {
+        const char *ns = getenv("THB200_NO_STAGING");
+        staged = !(ns && atoi(ns));
+        if (staged && (size_t)N * img_elems * sizeof(float) > E->h_stage_bytes) {
+            thb_host_free_pinned(E->h_stage);
+            E->h_stage_bytes = (size_t)N * img_elems * sizeof(float);
+            E->h_stage = thb_host_alloc_pinned(E->h_stage_bytes);
+            if (!E->h_stage) { E->h_stage_bytes = 0; staged = 0; }
+        }
+    }
+    /* what the device-resident timing loop needs to repeat this forward from the staged input */
+    E->last_has_x = x != 0; E->last_cp = cp; E->last_bgr = bgr;
+    for (int k = 0; k < 3; k++) { E->last_mean[k] = mean[k]; E->last_std[k] = std[k]; }
 
-    for (int g = 0; g < G; g++) {
-        instance *I = &set[g];
-        CU(cudaSetDevice(I->device));
-        long off = 0;
-        for (int k = 0; k < g; k++) off += set[k].out_count;
-        float *dst = gather && I->device == dev0 ? gather + off : I->d_out;
-        if (device_forward(E, I, x != 0, inplace, cp, bgr, C, H, W, mean, std, q_sub, q_mult,
-                           x && inplace ? x + (size_t)I->slice_off * img_elems : 0, dst)) return -1;
-        CU(cudaEventRecord(I->ev1, I->stream));
-        if (gather) {
-            if (I->device != dev0)
-                CU(cudaMemcpyPeerAsync(gather + off, dev0, I->d_out, I->device, (size_t)I->out_count * sizeof(float), I->stream));
-        } else
-            CU(cudaMemcpyAsync(E->h_out + off, I->d_out, (size_t)I->out_count * sizeof(float), cudaMemcpyDeviceToHost, I->stream));
+    /* The uint8 engine needs the input range of the whole batch before any kernel can start: it stages every slice, then
+     * measures, then launches.  The other modes launch a slice's kernels as soon as its copy is queued. */
+    const int two_phase = E->dtype == THB_U8;
+    for (int phase = 0; phase < 2; phase++) {
+        if (phase == 1) {
+            if (!two_phase) break;
+            if (lowp_input_range(E, set, G, x != 0, cp, C, H, W, mean, std, &q_sub, &q_mult)) return -1;
+        }
+        for (int g = 0; g < G; g++) {
+            instance *I = &set[g];
+            CU(cudaSetDevice(I->device));
+            if (phase == 0) {
+                /* stage the input slice */
+                if (x) {
+                    const size_t bytes = (size_t)I->slice_n * img_elems * sizeof(float);
+                    const float *src = x + (size_t)I->slice_off * img_elems;
+                    if (staged) {
+                        float *st = E->h_stage + (size_t)I->slice_off * img_elems;
+                        parallel_copy(st, src, bytes);
+                        src = st;
+                    }
+                    CU(cudaMemcpyAsync(I->d_in, src, bytes, cudaMemcpyHostToDevice, I->stream));
+                } else if ((size_t)stride == (size_t)W * cp) {
+                    /* tightly packed rows: one copy per run of images that also follow one another in host memory */
+                    const size_t img_bytes = (size_t)H * W * cp;
+                    for (int n = 0; n < I->slice_n;) {
+                        int run = 1;
+                        while (n + run < I->slice_n && images[I->slice_off + n + run] == images[I->slice_off + n + run - 1] + img_bytes) run++;
+                        CU(cudaMemcpyAsync(I->d_img + (size_t)n * img_bytes, images[I->slice_off + n], (size_t)run * img_bytes,
+                                           cudaMemcpyHostToDevice, I->stream));
+                        n += run;
+                    }
+                } else {
+                    for (int n = 0; n < I->slice_n; n++)
+                        CU(cudaMemcpy2DAsync(I->d_img + (size_t)n * H * W * cp, (size_t)W * cp, images[I->slice_off + n], stride,
+                                             (size_t)W * cp, H, cudaMemcpyHostToDevice, I->stream));
+                }
+                if (two_phase) continue;
+            }
+            long off = 0;
+            for (int k = 0; k < g; k++) off += set[k].out_count;
+            float *dst = gather && I->device == dev0 ? gather + off : I->d_out;
+            if (device_forward(E, I, x != 0, inplace, cp, bgr, C, H, W, mean, std, q_sub, q_mult,
+                               x && inplace ? x + (size_t)I->slice_off * img_elems : 0, dst)) return -1;
+            CU(cudaEventRecord(I->ev1, I->stream));
+            if (gather) {
+                if (I->device != dev0)
+                    CU(cudaMemcpyPeerAsync(gather + off, dev0, I->d_out, I->device, (size_t)I->out_count * sizeof(float), I->stream));
+            } else
+                CU(cudaMemcpyAsync(E->h_out + off, I->d_out, (size_t)I->out_count * sizeof(float), cudaMemcpyDeviceToHost, I->stream));
+        }
     }
     float ms_max = 0;
     for (int g = G - 1; g >= 0; g--) {
