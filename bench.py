@@ -394,9 +394,17 @@ def measure_images(arm, steps, world, barrier, max_over_ranks):
     for _ in range(3):
         n = fwd()
     dt = time_loop(fwd, steps, barrier, max_over_ranks)
+    # the same images in an ordinary (pageable) array, as a caller of the reference would pass them
+    pageable = np.array(img, copy=True)
+    base = pageable.ctypes.data
+    ptrs = (C.c_void_p * b)(*[base + i * hh * ww * 3 for i in range(b)])
+    fwd()
+    dt_pageable = time_loop(fwd, max(2, steps // 4), barrier, max_over_ranks)
+    del pageable
     lib.THB200_HostFree(hptr)
     return {"value": world * b / dt, "unit": "images/s", "ms_per_step": dt * 1e3, "entry": "THProcessImages",
-            "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": n * 4, "host_buffer": "pinned (THB200_HostAlloc)"}
+            "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": n * 4, "host_buffer": "pinned (THB200_HostAlloc)",
+            "pageable_host_buffer": {"value": world * b / dt_pageable, "ms_per_step": dt_pageable * 1e3}}
 
 
 def measure_strong(th, workload, dtype, batch, ngpus, steps, warmup, tmpdir, one_gpu_out):

@@ -261,6 +261,15 @@ def test_pageable_batches_are_staged_through_pinned_memory(th, tmp_path, monkeyp
     assert rel_err(outs[1], outs[0]) < 1e-5     # (sub-batches of 6 and 10 images may take other fp32 tile shapes than 16)
     assert all(np.array_equal(bufs[0], b) for b in bufs[1:])
     assert not np.array_equal(bufs[0], x)                  # mean 0.45 / std 0.225: normalised in place
+    # byte images that follow one another in ordinary memory take the same route
+    h = _load(th, g, "t7", tmp_path, "alexpg2")
+    imgs = np.random.default_rng(4).integers(0, 256, (64, 224, 224, 3)).astype(np.uint8)   # 9.6 MB
+    got = []
+    for nostage in ("0", "1"):
+        monkeypatch.setenv("THB200_NO_STAGING", nostage)
+        got.append(th.process_images(h, list(imgs))[0])
+    th.free_network(h)
+    assert np.array_equal(got[0], got[1])
 
 
 def test_process_yuyv(th, oracle, tmp_path):

@@ -1948,12 +1948,13 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
      * library, filled slice by slice by the host's threads, so that the copy to the device runs at link speed and under
      * the previous slice's kernels (THB200_NO_STAGING=1: hand the caller's pointer to the driver as it is). */
     int staged = 0;
-    if (x && (size_t)N * img_elems * sizeof(float) >= ((size_t)8 << 20) && host_is_pageable(x)) {
+    const size_t in_bytes = x ? (size_t)N * img_elems * sizeof(float) : (size_t)N * H * W * cp;
+    if (in_bytes >= ((size_t)8 << 20) && (x || (size_t)stride == (size_t)W * cp) && host_is_pageable(x ? (const void *)x : images[0])) {
         const char *ns = getenv("THB200_NO_STAGING");
         staged = !(ns && atoi(ns));
-        if (staged && (size_t)N * img_elems * sizeof(float) > E->h_stage_bytes) {
+        if (staged && in_bytes > E->h_stage_bytes) {
             thb_host_free_pinned(E->h_stage);
-            E->h_stage_bytes = (size_t)N * img_elems * sizeof(float);
+            E->h_stage_bytes = in_bytes;
             E->h_stage = thb_host_alloc_pinned(E->h_stage_bytes);
             if (!E->h_stage) { E->h_stage_bytes = 0; staged = 0; }
         }
@@ -1990,8 +1991,13 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
                     for (int n = 0; n < I->slice_n;) {
                         int run = 1;
                         while (n + run < I->slice_n && images[I->slice_off + n + run] == images[I->slice_off + n + run - 1] + img_bytes) run++;
-                        CU(cudaMemcpyAsync(I->d_img + (size_t)n * img_bytes, images[I->slice_off + n], (size_t)run * img_bytes,
-                                           cudaMemcpyHostToDevice, I->stream));
+                        const unsigned char *src = images[I->slice_off + n];
+                        if (staged) {
+                            unsigned char *st = (unsigned char *)E->h_stage + (size_t)(I->slice_off + n) * img_bytes;
+                            parallel_copy(st, src, (size_t)run * img_bytes);
+                            src = st;
+                        }
+                        CU(cudaMemcpyAsync(I->d_img + (size_t)n * img_bytes, src, (size_t)run * img_bytes, cudaMemcpyHostToDevice, I->stream));
                         n += run;
                     }
                 } else {
