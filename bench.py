@@ -24,6 +24,8 @@ JSON line (rank 0):
   parity   the logits of this run against the reference's for the same batch (max-abs error / max-abs value, argmax
            agreement), when the reference ran;
   cpu_baseline the unmodified reference CPU build timed on this box's host cores on a bounded sample;
+  other_configs   (N = 1) the baseline's other configurations -- AlexNet-OWT fp32 batch 1, ResNet-18 fp16 batch 64, VGG-16 uint8 /
+           fp16 batch 32, the segmentation net fp16 batch 16 -- each measured like the headline at its own size;
   e2e_images, int8, strong   sub-records: THProcessImages from byte images, the uint8 engine on the same network,
            and (N > 1) one batch of 256 sharded over the N GPUs by rank 0 alone.
 `--impl reference` times only that CPU reference and prints the same line with "impl": "reference".
@@ -558,6 +560,23 @@ def main():
             out["int8"] = {"config": f"{args.workload}_int8_b{batch} (uint8 lowp engine, range {LOWP_RANGE:g})", "value": sub["value"],
                            "unit": "images/s", "ms_per_step": sub["ms_per_step"], "e2e": sub["e2e"], "gpu_launches": sub["gpu_launches"],
                            "roofline": sub.get("roofline")}
+    # ---- the other configurations of the baseline (its CPU-runnable case, the small-batch and the segmentation cases), each
+    # measured the same way at its own batch size on this rank's GPU: N = 1 only, they are parity cases, not the headline
+    if world == 1 and not args.no_sub_records and args.workload == "resnet50" and args.batch is None and args.dtype is None:
+        others = []
+        for wl, dt, b in (("alexnet_owt", "fp32", 1), ("resnet18", "fp16", 64), ("vgg16", "int8", 32), ("vgg16", "fp16", 32),
+                          ("segnet", "fp16", 16)):
+            try:
+                a2 = Arm(th, wl, dt, b, rank, tmp.name)
+                sub, _ = measure(a2, args.steps, warmup, world, barrier, max_over_ranks, peaks)
+                a2.close()
+                rf = sub.get("roofline") or {}
+                others.append({"workload": f"{wl}_{dt}_b{b}", "value": sub["value"], "unit": "images/s",
+                               "ms_per_step": sub["ms_per_step"], "e2e": sub["e2e"]["value"], "gpu_launches": sub["gpu_launches"],
+                               "roofline_frac": rf.get("frac"), "two_roof_frac": (rf.get("two_roof_bound") or {}).get("frac")})
+            except SystemExit as e:
+                others.append({"workload": f"{wl}_{dt}_b{b}", "unavailable": str(e)[:200]})
+        out["other_configs"] = others
     # ---- strong scaling inside the library: ONE batch over the N GPUs of this box (rank 0 alone drives them; the other
     # ranks hold no work and wait on the host, through the rendezvous store, so that no kernel of theirs sits on a GPU)
     if world > 1 and not args.no_sub_records:
