@@ -110,6 +110,11 @@ typedef struct thb_conv_desc {
      * (Cout_pad == BN) the sums are stored; otherwise each column tile ADDS its part, and the caller clears the buffer
      * before the launch. */
     int *csum_out;
+    /* Optional host copies of scale / shift (NULL: none), Cout floats each.  The patch convolution (thb_conv_patch_fwd,
+     * thb_conv_maxpool_fwd) hands the per-channel constants to its kernel as launch parameters: with the host copies it
+     * takes them from here; without them it reads the device arrays back with a blocking copy at EVERY launch, which is
+     * fine for a test and must not happen inside a stream capture. */
+    const float *scale_host, *shift_host;
 } thb_conv_desc;
 
 int thb_channel_align(int dtype);               /* 4 (F32), 8 (F16/BF16), 16 (U8) */

@@ -89,11 +89,18 @@ class Conv:
         out[:v.size] = v
         return out
 
-    def set_affine(self, scale, shift):
+    def set_affine(self, scale, shift, host_copies=False):
+        """host_copies: also fill thb_conv_desc.scale_host / shift_host (what the planner does)."""
         if scale is not None:
-            t = dev(self._padded(scale)); self.keep.append(t); self.d.scale = t.data_ptr()
+            h = self._padded(scale)
+            t = dev(h); self.keep.append(t); self.d.scale = t.data_ptr()
+            if host_copies:
+                self.keep.append(h); self.d.scale_host = h.ctypes.data
         if shift is not None:
-            t = dev(self._padded(shift)); self.keep.append(t); self.d.shift = t.data_ptr()
+            h = self._padded(shift)
+            t = dev(h); self.keep.append(t); self.d.shift = t.data_ptr()
+            if host_copies:
+                self.keep.append(h); self.d.shift_host = h.ctypes.data
 
     def set_act(self, kind, threshold=0.0, value=0.0, alpha=0.0, slope=None):
         a = self.d.act

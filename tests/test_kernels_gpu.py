@@ -247,7 +247,8 @@ def test_conv_fused_epilogue(lib, G, oracle, dtype):
 @pytest.mark.parametrize("case", [(2, 64, 20, 24, 64, 3, 1, 1), (3, 64, 9, 7, 24, 3, 1, 0), (1, 64, 57, 61, 40, 3, 1, 1), (2, 64, 30, 18, 64, 2, 1, 1),
                                   (2, 16, 21, 19, 56, 4, 1, 2), (3, 12, 15, 33, 64, 5, 1, 2), (1, 16, 40, 40, 48, 3, 1, 1),
                                   (2, 64, 5, 300, 64, 3, 1, 1), (2, 16, 300, 6, 64, 3, 1, 1), (4, 64, 4, 4, 64, 3, 1, 1), (4, 64, 2, 2, 64, 3, 1, 1)])
-def test_conv_patch_path(lib, G, oracle, case):
+@pytest.mark.parametrize("host_copies", [False, True])
+def test_conv_patch_path(lib, G, oracle, case, host_copies):
     """Stride-1 convolutions on 16 or 64 channels per pixel with at most 64 output channels take the patch kernel (one raw
     input patch per unit, every tap reads it in place): maps narrower and wider than a patch row, odd sizes, every
     padding, Cout below 64, several patches per image.  The descriptor must qualify, so a silent fall-back cannot pass."""
@@ -258,7 +259,7 @@ def test_conv_patch_path(lib, G, oracle, case):
     shift = rng.standard_normal(cout).astype(np.float32)
     ref = oracle.conv2d(x, wt, None, (s, s), (p, p)) * scale[None, :, None, None] + shift[None, :, None, None]
     conv = G.Conv(lib, K.THB_F16, x.shape, wt, (s, s), (p, p), bn_tile=64)
-    conv.set_affine(scale, shift)
+    conv.set_affine(scale, shift, host_copies)   # (constants from the descriptor's host copies, or read back per launch)
     lib.thb_conv_patch_supported.argtypes = [C.c_void_p]
     assert lib.thb_conv_patch_supported(C.byref(conv.d)) == 1, "the case must qualify for the patch kernel"
     xt, _ = G.to_nhwc(x, K.THB_F16)
@@ -266,6 +267,30 @@ def test_conv_patch_path(lib, G, oracle, case):
     assert G.rel_err(G.from_nhwc(y, cout), ref) < 1e-2, (case, G.rel_err(G.from_nhwc(y, cout), ref))
     pad = y[..., cout:G.ru(cout, 8)]
     assert pad.numel() == 0 or float(pad.float().abs().max()) == 0.0
+
+
+def test_conv_patch_constants_are_not_cached_by_address(lib, G, oracle):
+    """Two layers of one shape whose buffers sit at the same device addresses, with other scale / shift values in them:
+    the second launch must use the second values (the launcher keeps tensor maps per address, never the constants)."""
+    case = (2, 64, 12, 12, 64, 3, 1, 1)
+    n, cin, h, w, cout, k, s, p = case
+    x, wt = _conv_inputs(case, 61, True)
+    conv = G.Conv(lib, K.THB_F16, x.shape, wt, (s, s), (p, p), bn_tile=64)
+    xt, _ = G.to_nhwc(x, K.THB_F16)
+    rng = np.random.default_rng(62)
+    plain = oracle.conv2d(x, wt, None, (s, s), (p, p))
+    sc_t = G.dev(np.zeros(64, np.float32)); sh_t = G.dev(np.zeros(64, np.float32))
+    conv.keep += [sc_t, sh_t]
+    conv.d.scale, conv.d.shift = sc_t.data_ptr(), sh_t.data_ptr()
+    y = torch.zeros((n, conv.d.oH, conv.d.oW, conv.d.out_ld), dtype=torch.float16, device="cuda")
+    for _ in range(2):
+        scale = rng.uniform(0.5, 1.5, cout).astype(np.float32)
+        shift = rng.standard_normal(cout).astype(np.float32)
+        sc_t.copy_(torch.from_numpy(scale)); sh_t.copy_(torch.from_numpy(shift))
+        assert lib.thb_conv_fwd(C.byref(conv.d), G.ptr(xt), G.ptr(y), None) == 0
+        torch.cuda.synchronize()
+        ref = plain * scale[None, :, None, None] + shift[None, :, None, None]
+        assert G.rel_err(G.from_nhwc(y, cout), ref) < 1e-2
 
 
 @pytest.mark.parametrize("pool", [(3, 1, 0), (2, 0, 0), (3, 0, 1), (2, 0, 1)], ids=["3s2p1", "2s2", "3s2ceil", "2s2ceil"])

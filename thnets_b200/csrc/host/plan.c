@@ -111,6 +111,8 @@ typedef struct instance {
     cudaEvent_t ev0, ev1;
     void **allocs;
     int nallocs, capallocs;
+    void **hostmem; /* host arrays the launches' descriptors point to */
+    int nhost, caphost;
     unsigned char *arena;
     size_t arena_bytes;
     float *d_in;          /* staged NCHW fp32 input */
@@ -179,6 +181,15 @@ static void *dalloc(instance *I, size_t bytes)
     }
     I->allocs[I->nallocs++] = p;
     return p;
+}
+/* host memory that lives as long as the instance */
+static void host_keep(instance *I, void *p)
+{
+    if (I->nhost == I->caphost) {
+        I->caphost = I->caphost ? I->caphost * 2 : 64;
+        I->hostmem = realloc(I->hostmem, I->caphost * sizeof(void *));
+    }
+    I->hostmem[I->nhost++] = p;
 }
 static void *dupload(instance *I, const void *host, size_t bytes)
 {
@@ -562,6 +573,7 @@ static int plan_gemm_group(planner *P, int i)
 
     /* ---- per-channel scale / shift ---- */
     float *scale = 0, *shift = 0;
+    float *scale_h = 0, *shift_h = 0; /* host copies, owned by the instance (thb_conv_desc.scale_host / shift_host) */
     if (dtype != THB_U8) {
         int Cp = ru(n->Cout, 64);
         float *hs = calloc(Cp, sizeof(float)), *hh = calloc(Cp, sizeof(float));
@@ -581,9 +593,10 @@ static int plan_gemm_group(planner *P, int i)
                 hs[c] = 1.f;
             }
         }
-        if (bn >= 0 && dual_conv < 0) scale = dupload(P->I, hs, sizeof(float) * Cp);
-        if ((dual_conv >= 0 || bn >= 0 || n->bias) && !is_deconv) shift = dupload(P->I, hh, sizeof(float) * Cp);
-        free(hs); free(hh);
+        if (bn >= 0 && dual_conv < 0) { scale = dupload(P->I, hs, sizeof(float) * Cp); scale_h = hs; }
+        if ((dual_conv >= 0 || bn >= 0 || n->bias) && !is_deconv) { shift = dupload(P->I, hh, sizeof(float) * Cp); shift_h = hh; }
+        if (scale_h) host_keep(P->I, hs); else free(hs);
+        if (shift_h) host_keep(P->I, hh); else free(hh);
     }
 
     value *out = &P->val[cur];
@@ -824,6 +837,7 @@ static int plan_gemm_group(planner *P, int i)
         }
     } else {
         d->scale = scale; d->shift = shift;
+        d->scale_host = scale_h; d->shift_host = shift_h;
         if (act >= 0 && !is_deconv && fill_act(P, &d->act, &M->nodes[act], n->Cout)) return -1;
         if (res_node >= 0) {
             const value *rv = &P->val[res_node];
@@ -1295,6 +1309,8 @@ static size_t pack_arena(instance *I)
 static void instance_free(instance *I)
 {
     if (!I->allocs && !I->steps) return;
+    for (int i = 0; i < I->nhost; i++) free(I->hostmem[i]);
+    free(I->hostmem);
     cudaSetDevice(I->device);
     if (I->stream) cudaStreamSynchronize(I->stream);
     for (int i = 0; i < I->nallocs; i++) cudaFree(I->allocs[i]);

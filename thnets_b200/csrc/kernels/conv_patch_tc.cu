@@ -538,9 +538,9 @@ bool patch_geometry_ok(const thb_conv_desc *d, int pk, int ps, int ppad)
     return true;
 }
 
+// (the cache holds tensor maps only, i.e. addresses and shapes: nothing in it can go stale when memory is reused)
 struct PtMapEntry {
-    const void *x, *y, *wptr, *scale, *shift;
-    float cscale[64], cshift[64];   // host copies of the per-channel constants (they travel as kernel parameters)
+    const void *x, *y, *wptr;
     int key[20];
     alignas(64) CUtensorMap w, a, y_map;
 };
@@ -574,7 +574,7 @@ int patch_launch(const thb_conv_desc *d, int pk, int ppad, int pH, int pW, const
                          p.CR, p.CC, p.PR, p.PC, d->kH, d->kW, d->Ktot_pad};
     PtMapEntry *e = nullptr;
     for (int i = 0; i < used; i++)
-        if (cache[i].x == x && cache[i].y == y && cache[i].wptr == d->w && cache[i].scale == d->scale && cache[i].shift == d->shift && !memcmp(cache[i].key, key, sizeof(key))) { e = &cache[i]; break; }
+        if (cache[i].x == x && cache[i].y == y && cache[i].wptr == d->w && !memcmp(cache[i].key, key, sizeof(key))) { e = &cache[i]; break; }
     if (!e) {
         e = &cache[used < 128 ? used++ : (next++ % 128)];
         e->x = nullptr;
@@ -610,19 +610,23 @@ int patch_launch(const thb_conv_desc *d, int pk, int ppad, int pH, int pW, const
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
                 return thb_note_launch(cudaErrorInvalidValue, "conv_patch: output tensor map");
         }
-        // The per-channel constants are fetched from the device once per layer (a blocking copy: the first forward of a
-        // plan launches directly, before any stream capture, so this never runs inside one).
-        for (int c = 0; c < 64; c++) { e->cscale[c] = c < d->Cout ? 1.f : 0.f; e->cshift[c] = 0.f; }
-        if (d->scale && cudaMemcpy(e->cscale, d->scale, sizeof(float) * d->Cout, cudaMemcpyDeviceToHost) != cudaSuccess)
-            return thb_note_launch(cudaGetLastError(), "conv_patch: reading the scale constants");
-        if (d->shift && cudaMemcpy(e->cshift, d->shift, sizeof(float) * d->Cout, cudaMemcpyDeviceToHost) != cudaSuccess)
-            return thb_note_launch(cudaGetLastError(), "conv_patch: reading the shift constants");
-        e->x = x; e->y = y; e->wptr = d->w; e->scale = d->scale; e->shift = d->shift;
+        e->x = x; e->y = y; e->wptr = d->w;
         memcpy(e->key, key, sizeof(key));
     }
 
-    memcpy(p.cscale, e->cscale, sizeof(p.cscale));
-    memcpy(p.cshift, e->cshift, sizeof(p.cshift));
+    // The per-channel constants travel as kernel parameters: from the descriptor's host copies when it has them, else
+    // read back from the device (a blocking copy at every launch: callers that capture streams give the host copies).
+    for (int c = 0; c < 64; c++) { p.cscale[c] = c < d->Cout ? 1.f : 0.f; p.cshift[c] = 0.f; }
+    if (d->scale) {
+        if (d->scale_host) memcpy(p.cscale, d->scale_host, sizeof(float) * d->Cout);
+        else if (cudaMemcpy(p.cscale, d->scale, sizeof(float) * d->Cout, cudaMemcpyDeviceToHost) != cudaSuccess)
+            return thb_note_launch(cudaGetLastError(), "conv_patch: reading the scale constants");
+    }
+    if (d->shift) {
+        if (d->shift_host) memcpy(p.cshift, d->shift_host, sizeof(float) * d->Cout);
+        else if (cudaMemcpy(p.cshift, d->shift, sizeof(float) * d->Cout, cudaMemcpyDeviceToHost) != cudaSuccess)
+            return thb_note_launch(cudaGetLastError(), "conv_patch: reading the shift constants");
+    }
     static bool configured[16] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
