@@ -124,6 +124,33 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm), "window": window}
 
 
+def prefer_gpu_numa_node(local_rank):
+    """Ask the kernel to place this process's new pages on the NUMA node of its GPU (set_mempolicy, MPOL_PREFERRED), so that
+    the pinned host batch is local to the PCIe root the GPU hangs off.  Returns what was found and done, for the JSON line;
+    never fatal (containers may hide the topology or refuse the call).  THB200_BENCH_NUMA=0 skips it."""
+    info = {"gpu_node": None, "policy": "default"}
+    if os.environ.get("THB200_BENCH_NUMA", "1") == "0":
+        return info
+    try:
+        import torch
+        bus = torch.cuda.get_device_properties(local_rank).pci_bus_id
+        dom = getattr(torch.cuda.get_device_properties(local_rank), "pci_domain_id", 0)
+        path = "/sys/bus/pci/devices/%04x:%02x:00.0/numa_node" % (dom, bus)
+        node = int(open(path).read().strip())
+        info["gpu_node"] = node
+        nodes = [d for d in os.listdir("/sys/devices/system/node") if d.startswith("node") and d[4:].isdigit()]
+        info["nodes"] = len(nodes)
+        if node < 0 or len(nodes) < 2:
+            return info
+        libc = C.CDLL(None, use_errno=True)
+        mask = C.c_ulong(1 << node)
+        rc = libc.syscall(238, 1, C.byref(mask), 64)   # x86-64 set_mempolicy(MPOL_PREFERRED, &mask, maxnode)
+        info["policy"] = "preferred node %d" % node if rc == 0 else "set_mempolicy failed (errno %d)" % C.get_errno()
+    except Exception as e:  # noqa: BLE001
+        info["policy"] = "unavailable: %s" % str(e)[:80]
+    return info
+
+
 def build_fixture(workload, tmpdir, dtype=None):
     builder, _, _, kind = WORKLOADS[workload]
     # the uint8 engine cannot quantise an all-zero bias: the residual networks get a small random one on their classifier
@@ -511,6 +538,7 @@ def main():
 
     # ---------------------------------------------------------------- B200 arm
     os.environ["THB200_DEVICE"] = str(local_rank)
+    numa = prefer_gpu_numa_node(local_rank)
     from thnets_b200.distributed import Ranks
     ranks = Ranks("nccl" if world > 1 else None)
     from thnets_b200.capi import THNets
@@ -542,7 +570,7 @@ def main():
         out = {"metric": "images_per_second", "value": head["value"], "unit": "images/s", "n_gpus": world,
                "steps": args.steps, "warmup": warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak",
                "vs_baseline": None, "dtype": {"fp16": "f16", "fp32": "f32", "bf16": "bf16", "int8": "u8"}[dtype], "data": "synthetic",
-               "config": config, "e2e": head["e2e"], "gpu_launches": head["gpu_launches"], "clocks": clocks,
+               "config": config, "e2e": head["e2e"], "gpu_launches": head["gpu_launches"], "clocks": clocks, "host_numa": numa,
                "roofline": head.get("roofline"),
                "timed_region": "value: boundary kernels (fp32 NCHW <-> the engine's layout) and every planned launch, batch and "
                                "result resident in HBM; e2e: the THProcessFloat call with host buffers"}

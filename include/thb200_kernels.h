@@ -139,8 +139,8 @@ int thb_conv_maxpool_fwd(const thb_conv_desc *d, int pk, int ps, int ppad, int p
                          thb_stream s);
 
 /* The patch kernel behind both: thb_conv_fwd itself takes this route for the same class of convolutions (kernel larger
- * than 1 x 1, no residual) -- the raw input patch of a rectangle of outputs is loaded once and every tap reads it in place.
- * THB200_NO_PATCH=1 switches the route off. */
+ * than 1 x 1; a fused residual with self_coef = +-1 is allowed here, not with the pooling) -- the raw input patch of a
+ * rectangle of outputs is loaded once and every tap reads it in place.  THB200_NO_PATCH=1 switches the route off. */
 int thb_conv_patch_supported(const thb_conv_desc *d);
 int thb_conv_patch_fwd(const thb_conv_desc *d, const void *x, void *y, thb_stream s);
 

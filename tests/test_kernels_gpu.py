@@ -269,6 +269,35 @@ def test_conv_patch_path(lib, G, oracle, case, host_copies):
     assert pad.numel() == 0 or float(pad.float().abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("coefs", [(1.0, -1.0), (-1.0, 1.0), (1.0, 1.0)])
+@pytest.mark.parametrize("case", [(2, 64, 20, 24, 64, 3, 1, 1), (3, 16, 9, 7, 24, 3, 1, 1), (1, 64, 57, 61, 40, 3, 1, 1),
+                                  (8, 64, 56, 56, 64, 3, 1, 1), (2, 64, 5, 300, 64, 3, 1, 1)])
+def test_conv_patch_residual(lib, G, oracle, case, coefs):
+    """The patch kernel with a fused residual: y = relu(self * (conv * scale + shift) + res_coef * r), the residual tile
+    copied into the output tile one unit ahead.  One tile and many tiles per CTA (8 x 56 x 56: 3 units per CTA), ragged
+    edges, every sign combination CAddTable / CSubTable produce."""
+    n, cin, h, w, cout, k, s, p = case
+    x, wt = _conv_inputs(case, 71, True)
+    rng = np.random.default_rng(72)
+    scale = rng.uniform(0.5, 1.5, cout).astype(np.float32)
+    shift = rng.standard_normal(cout).astype(np.float32)
+    conv_ref = oracle.conv2d(x, wt, None, (s, s), (p, p)) * scale[None, :, None, None] + shift[None, :, None, None]
+    res = rng.standard_normal(conv_ref.shape).astype(np.float16).astype(np.float32)
+    ref = np.maximum(coefs[0] * conv_ref + coefs[1] * res, 0.0)
+    conv = G.Conv(lib, K.THB_F16, x.shape, wt, (s, s), (p, p), bn_tile=64)
+    conv.set_affine(scale, shift, host_copies=True)
+    rt, rld = G.to_nhwc(res, K.THB_F16)
+    conv.set_residual(rt, rld, coefs[0], coefs[1])
+    conv.set_act(K.ACT_THRESHOLD)
+    lib.thb_conv_patch_supported.argtypes = [C.c_void_p]
+    assert lib.thb_conv_patch_supported(C.byref(conv.d)) == 1, "the case must qualify for the patch kernel"
+    xt, _ = G.to_nhwc(x, K.THB_F16)
+    y = conv.run(xt, fill=7.0)
+    assert G.rel_err(G.from_nhwc(y, cout), ref) < 1e-2, (case, G.rel_err(G.from_nhwc(y, cout), ref))
+    pad = y[..., cout:G.ru(cout, 8)]
+    assert pad.numel() == 0 or float(pad.float().abs().max()) == 0.0
+
+
 def test_conv_patch_constants_are_not_cached_by_address(lib, G, oracle):
     """Two layers of one shape whose buffers sit at the same device addresses, with other scale / shift values in them:
     the second launch must use the second values (the launcher keeps tensor maps per address, never the constants)."""

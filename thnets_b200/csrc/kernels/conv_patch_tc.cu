@@ -52,6 +52,8 @@ struct PatchParams {
     float act_th, act_val, act_alpha;
     int kind;               // 0 fp16, 1 bf16
     int pdl;
+    int has_res;            // a residual tensor (the output's shape) is added before the activation: y = act(conv' + res_coef * r)
+    float res_coef;         // (the convolution's own coefficient, +-1, is folded into cscale / cshift)
     int *status;
 };
 
@@ -190,20 +192,53 @@ __device__ __forceinline__ void activate_half(const uint32_t (&acc)[32], const P
     }
 }
 
+// the same with a residual: r holds the thread's 32 channels of the residual pixel (the four chunks its result replaces)
+template <int CH>
+__device__ __forceinline__ void activate_half_res(const uint32_t (&acc)[32], const PatchParams &p, int act_mode, const float *s_slope,
+                                                  const uint4 (&r)[4], uint4 (&o)[4])
+{
+#pragma unroll
+    for (int cj = 0; cj < 4; cj++) {
+        const uint32_t rw[4] = {r[cj].x, r[cj].y, r[cj].z, r[cj].w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int h = 0; h < 4; h++) {
+            const int c = CH * 32 + cj * 8 + h * 2;
+            float2 rr;
+            if (p.kind == 0) rr = __half22float2(*reinterpret_cast<const __half2 *>(&rw[h]));
+            else rr = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&rw[h]));
+            float v0 = fmaf(p.res_coef, rr.x, fmaf(__uint_as_float(acc[cj * 8 + h * 2]), p.cscale[c], p.cshift[c]));
+            float v1 = fmaf(p.res_coef, rr.y, fmaf(__uint_as_float(acc[cj * 8 + h * 2 + 1]), p.cscale[c + 1], p.cshift[c + 1]));
+            if (act_mode == 3) {
+                v0 = fmaxf(v0, 0.f);
+                v1 = fmaxf(v1, 0.f);
+            } else if (act_mode != 0) {
+                v0 = thb_apply_act(v0, p.act_kind, p.act_th, p.act_val, p.act_alpha, s_slope[c]);
+                v1 = thb_apply_act(v1, p.act_kind, p.act_th, p.act_val, p.act_alpha, s_slope[c + 1]);
+            }
+            if (c >= p.Cout) v0 = 0.f;       // padded channels stay exact zeros
+            if (c + 1 >= p.Cout) v1 = 0.f;
+            ow[h] = pack_pair(v0, v1, p.kind);
+        }
+        o[cj] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
 // PX: bytes per input pixel in shared memory (32 or 128); KP: pooling window fused behind the convolution (0: none)
 template <int PX, int KP>
 __global__ void __launch_bounds__(PT_THREADS, 1)
 conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_constant__ CUtensorMap tmapA,
-                     const __grid_constant__ CUtensorMap tmapY, const PatchParams p)
+                     const __grid_constant__ CUtensorMap tmapY, const __grid_constant__ CUtensorMap tmapR, const PatchParams p)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t *full = reinterpret_cast<uint64_t *>(smem), *empty = full + PT_MAX_STAGES;
     uint64_t *acc_full = empty + PT_MAX_STAGES, *acc_empty = acc_full + PT_NACC, *w_full = acc_empty + PT_NACC;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(w_full + 1);
+    uint64_t *res_full = w_full + 1;                    // residual tile landed in output tile 0 / 1
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(res_full + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     // header of 2048 bytes: [0, 256) mbarriers, the TMEM slot and the abort flag; [512, 768) PReLU slopes
-    static_assert((2 * PT_MAX_STAGES + 2 * PT_NACC + 1) * 8 + 8 <= 256, "the barriers outgrow their part of the header");
+    static_assert((2 * PT_MAX_STAGES + 2 * PT_NACC + 1 + 2) * 8 + 8 <= 256, "the barriers outgrow their part of the header");
     float *s_slope = reinterpret_cast<float *>(smem + 512);
     uint8_t *sW = smem + 2048;                          // resident weights: tap t at sW + t * 64 * PX
     uint8_t *sP = sW + p.w_bytes;                       // raw patch buffers
@@ -226,6 +261,8 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
             mbar_init(smem_u32(&acc_empty[b]), 16);        // one arrival per epilogue warp
         }
         mbar_init(smem_u32(w_full), 1);
+        mbar_init(smem_u32(&res_full[0]), 1);
+        mbar_init(smem_u32(&res_full[1]), 1);
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
@@ -239,6 +276,7 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
         tma_prefetch_desc(&tmapW);
         tma_prefetch_desc(&tmapA);
         tma_prefetch_desc(&tmapY);
+        if (p.has_res) tma_prefetch_desc(&tmapR);
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
@@ -359,7 +397,19 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
         const int items = KP ? p.PR * p.PC * 8 : 0;
         const int it_px = et >> 3, it_j = et & 7;
         const int it_pr = KP ? it_px / p.PC : 0, it_pc = it_px - it_pr * p.PC;
-        for (int u = 0; u < mine; u++) {
+        // Fused residual (no pooling, two output tiles): the residual tile of unit u is copied into the output tile the unit
+        // will fill -- same box, same swizzle -- one unit ahead, so a thread finds its residual chunks where its result goes.
+        const bool with_res = !KP && p.has_res;
+        const uint32_t res_tile_bytes = (uint32_t)(p.CR * p.CC * 128);
+        int res_issued = 0;
+        if (with_res && et == 0 && mine > 0) {
+            const Unit q0 = unit_of(p, blockIdx.x);
+            mbar_arrive_expect_tx(smem_u32(&res_full[0]), res_tile_bytes);
+            tma_load_4d(smem_u32(ct), &tmapR, smem_u32(&res_full[0]), 0, q0.c0, q0.r0, q0.n);
+            res_issued = 1;
+        }
+        int u = 0;
+        for (; u < mine; u++) {
             const int ab = u % PT_NACC;
             const Unit q = unit_of(p, blockIdx.x + u * gridDim.x);
             if (!mbar_wait_bounded(smem_u32(&acc_full[ab]), (u / PT_NACC) & 1)) {
@@ -375,18 +425,30 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&acc_empty[ab]));
             // the tile about to be written was the source of the store two units ago (of the last one with a single tile)
-            if (et == 0) {
+            if (et == 0 && !with_res) {   // (with a residual the wait came before the residual copy into this tile was issued)
                 if (!KP && p.ct_bufs == 1) bulk_wait_group_read<0>();
                 else bulk_wait_group_read<1>();
             }
             uint8_t *tile = KP || p.ct_bufs == 1 ? ct : ct + (u & 1) * PT_CT_BYTES;
             if (!KP) epi_bar_sync();
+            if (with_res) {
+                if (!mbar_wait_bounded(smem_u32(&res_full[u & 1]), (u >> 1) & 1)) {
+                    if (lane == 0) atomicExch(p.status, 6);
+                    *abort_flag = 1;
+                }
+            }
             if (valid) {
                 uint4 o[4];
-                if (ch == 0) activate_half<0>(acc, p, act_mode, s_slope, o);
-                else activate_half<1>(acc, p, act_mode, s_slope, o);
                 uint8_t *row_smem = tile + ci * 128;
                 const int rsw = ci & 7;
+                if (with_res) {
+                    uint4 r[4];
+#pragma unroll
+                    for (int cj = 0; cj < 4; cj++) r[cj] = *reinterpret_cast<const uint4 *>(row_smem + (((ch * 4 + cj) ^ rsw) << 4));
+                    if (ch == 0) activate_half_res<0>(acc, p, act_mode, s_slope, r, o);
+                    else activate_half_res<1>(acc, p, act_mode, s_slope, r, o);
+                } else if (ch == 0) activate_half<0>(acc, p, act_mode, s_slope, o);
+                else activate_half<1>(acc, p, act_mode, s_slope, o);
 #pragma unroll
                 for (int cj = 0; cj < 4; cj++) *reinterpret_cast<uint4 *>(row_smem + (((ch * 4 + cj) ^ rsw) << 4)) = o[cj];
             }
@@ -397,6 +459,16 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
                 if (et == 0) {
                     tma_store_4d(&tmapY, smem_u32(tile), 0, q.c0, q.r0, q.n);  // clips rows and columns beyond the map
                     bulk_commit_group();
+                    if (with_res && u + 1 < mine) {
+                        // the other tile was the source of the store of unit u - 1: once that has been read out, the
+                        // residual of unit u + 1 may land there
+                        bulk_wait_group_read<1>();
+                        const Unit qn = unit_of(p, blockIdx.x + (u + 1) * gridDim.x);
+                        const uint32_t bar = smem_u32(&res_full[(u + 1) & 1]);
+                        mbar_arrive_expect_tx(bar, res_tile_bytes);
+                        tma_load_4d(smem_u32(ct + ((u + 1) & 1) * PT_CT_BYTES), &tmapR, bar, 0, qn.c0, qn.r0, qn.n);
+                        res_issued = u + 2;
+                    }
                 }
                 continue;
             }
@@ -433,6 +505,9 @@ conv_patch_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_con
             }
         }
         if (et == 0) bulk_wait_group<0>();
+        // (after a give-up: a residual copy that nobody waited for must land before the CTA's shared memory goes away)
+        if (with_res && et == 0 && u < mine && res_issued > u)
+            for (int k = u; k < res_issued; k++) mbar_wait_bounded(smem_u32(&res_full[k & 1]), (k >> 1) & 1);
     }
 
     tc_fence_before();
@@ -466,7 +541,7 @@ struct Geometry {
 };
 
 // shared-memory plan of a candidate patch: resident weights, raw patch buffers, output tile(s), pooled tiles
-bool plan_smem(int kH, int kW, int px_bytes, int kp, Geometry *g)
+bool plan_smem(int kH, int kW, int px_bytes, int kp, bool two_tiles, Geometry *g)
 {
     g->w_bytes = (kH * kW * 64 * px_bytes + 1023) & ~1023;
     // a patch buffer holds the copied pixels and whatever the 256 GEMM rows of the last tap reach beyond them
@@ -478,7 +553,8 @@ bool plan_smem(int kH, int kW, int px_bytes, int kp, Geometry *g)
         if (fixed + 2 * (size_t)g->stage_bytes > PT_SMEM_MAX) continue;
         g->nst = (int)((PT_SMEM_MAX - fixed) / g->stage_bytes);
         if (g->nst > PT_MAX_STAGES) g->nst = PT_MAX_STAGES;
-        if (g->nst < 3 && g->ct_bufs == 2) continue;   // a third patch in flight is worth more than a second output tile
+        if (two_tiles && g->ct_bufs != 2) return false; // (a fused residual is copied into the tile of the NEXT unit)
+        if (!two_tiles && g->nst < 3 && g->ct_bufs == 2) continue;   // a third patch in flight is worth more than a second output tile
         g->smem = fixed + (size_t)g->nst * g->stage_bytes;
         return true;
     }
@@ -487,7 +563,7 @@ bool plan_smem(int kH, int kW, int px_bytes, int kp, Geometry *g)
 
 // The patch that covers the map with the fewest units: CR output rows x CC output columns with CR * (CC + kW - 1) <= 256
 // GEMM rows; with a pooling behind the convolution the patch is made of whole windows (CR = 2(PR-1)+kp, CC likewise).
-bool choose_patch(int oH, int oW, int kH, int kW, int px_bytes, int kp, int pH, int pW, Geometry *best)
+bool choose_patch(int oH, int oW, int kH, int kW, int px_bytes, int kp, int pH, int pW, bool two_tiles, Geometry *best)
 {
     long best_tiles = -1;
     for (int a = 1; a <= 64; a++) {
@@ -512,7 +588,7 @@ bool choose_patch(int oH, int oW, int kH, int kW, int px_bytes, int kp, int pH, 
         if (g.P > 256 || g.CR + kH - 1 > 256 || g.CR * g.P > 256) continue;
         g.tiles_r = kp ? (pH + a - 1) / a : (oH + g.CR - 1) / g.CR;
         g.tiles_c = kp ? (pW + g.PC - 1) / g.PC : (oW + g.CC - 1) / g.CC;
-        if (!plan_smem(kH, kW, px_bytes, kp, &g)) continue;
+        if (!plan_smem(kH, kW, px_bytes, kp, two_tiles, &g)) continue;
         const long tiles = (long)g.tiles_r * g.tiles_c;
         if (best_tiles < 0 || tiles < best_tiles || (tiles == best_tiles && g.nst > best->nst)) {
             best_tiles = tiles;
@@ -526,7 +602,9 @@ bool choose_patch(int oH, int oW, int kH, int kW, int px_bytes, int kp, int pH, 
 bool patch_geometry_ok(const thb_conv_desc *d, int pk, int ps, int ppad)
 {
     if (d->dtype != THB_F16 && d->dtype != THB_BF16) return false;
-    if (d->Cout > 64 || d->BN != 64 || d->dH != 1 || d->dW != 1 || d->x2 || d->res) return false;
+    if (d->Cout > 64 || d->BN != 64 || d->dH != 1 || d->dW != 1 || d->x2) return false;
+    // a fused residual: without pooling, coefficients of +-1 for the convolution's own term, rows of whole 16-byte chunks
+    if (d->res && (pk || d->res_ld % 8 || ((uintptr_t)d->res & 15) || (d->self_coef != 1.f && d->self_coef != -1.f))) return false;
     if (d->Cin_pad != 16 && d->Cin_pad != 64) return false;
     if (d->in_ld < d->Cin_pad || d->in_ld % 8) return false;
     if (d->kH < 1 || d->kW < 1 || d->kH > 8 || d->kW > 8 || d->padH >= d->kH || d->padW >= d->kW) return false;
@@ -540,9 +618,9 @@ bool patch_geometry_ok(const thb_conv_desc *d, int pk, int ps, int ppad)
 
 // (the cache holds tensor maps only, i.e. addresses and shapes: nothing in it can go stale when memory is reused)
 struct PtMapEntry {
-    const void *x, *y, *wptr;
+    const void *x, *y, *wptr, *res;
     int key[20];
-    alignas(64) CUtensorMap w, a, y_map;
+    alignas(64) CUtensorMap w, a, y_map, r_map;
 };
 
 int patch_launch(const thb_conv_desc *d, int pk, int ppad, int pH, int pW, const void *x, void *y, int y_ld, thb_stream s)
@@ -552,7 +630,7 @@ int patch_launch(const thb_conv_desc *d, int pk, int ppad, int pH, int pW, const
     PatchParams p;
     memset(&p, 0, sizeof(p));
     Geometry g;
-    if (!choose_patch(d->oH, d->oW, d->kH, d->kW, d->Cin_pad * 2, pk, pH, pW, &g)) return THB_ERR_UNSUPPORTED;
+    if (!choose_patch(d->oH, d->oW, d->kH, d->kW, d->Cin_pad * 2, pk, pH, pW, d->res != nullptr, &g)) return THB_ERR_UNSUPPORTED;
     p.N = d->N; p.oH = d->oH; p.oW = d->oW;
     p.CR = g.CR; p.CC = g.CC; p.P = g.P; p.tiles_r = g.tiles_r; p.tiles_c = g.tiles_c; p.PR = g.PR; p.PC = g.PC;
     p.kH = d->kH; p.kW = d->kW; p.padH = d->padH; p.padW = d->padW;
@@ -571,10 +649,10 @@ int patch_launch(const thb_conv_desc *d, int pk, int ppad, int pH, int pW, const
     static PtMapEntry cache[128];
     static int used = 0, next = 0;
     const int key[20] = {d->dtype, d->N, d->H, d->W, d->Cin_pad, d->in_ld, d->in_row_pitch, d->oH, d->oW, pH, pW, y_ld, d->Cout,
-                         p.CR, p.CC, p.PR, p.PC, d->kH, d->kW, d->Ktot_pad};
+                         p.CR, p.CC, p.PR, p.PC, d->kH * 16 + d->kW, d->res ? d->res_ld : 0, d->Ktot_pad};
     PtMapEntry *e = nullptr;
     for (int i = 0; i < used; i++)
-        if (cache[i].x == x && cache[i].y == y && cache[i].wptr == d->w && !memcmp(cache[i].key, key, sizeof(key))) { e = &cache[i]; break; }
+        if (cache[i].x == x && cache[i].y == y && cache[i].wptr == d->w && cache[i].res == d->res && !memcmp(cache[i].key, key, sizeof(key))) { e = &cache[i]; break; }
     if (!e) {
         e = &cache[used < 128 ? used++ : (next++ % 128)];
         e->x = nullptr;
@@ -610,7 +688,17 @@ int patch_launch(const thb_conv_desc *d, int pk, int ppad, int pH, int pW, const
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
                 return thb_note_launch(cudaErrorInvalidValue, "conv_patch: output tensor map");
         }
-        e->x = x; e->y = y; e->wptr = d->w;
+        if (d->res) {
+            // the residual: the output's shape and box with its own pitch
+            const int c8 = (d->Cout + 7) & ~7;
+            cuuint64_t dims[4] = {(cuuint64_t)c8, (cuuint64_t)d->oW, (cuuint64_t)d->oH, (cuuint64_t)d->N};
+            cuuint64_t strides[3] = {(cuuint64_t)d->res_ld * 2, (cuuint64_t)d->oW * d->res_ld * 2, (cuuint64_t)d->oH * d->oW * d->res_ld * 2};
+            cuuint32_t box[4] = {64, (cuuint32_t)p.CC, (cuuint32_t)p.CR, 1};
+            if (enc(&e->r_map, t, 4, const_cast<void *>(d->res), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+                return thb_note_launch(cudaErrorInvalidValue, "conv_patch: residual tensor map");
+        }
+        e->x = x; e->y = y; e->wptr = d->w; e->res = d->res;
         memcpy(e->key, key, sizeof(key));
     }
 
@@ -627,11 +715,18 @@ int patch_launch(const thb_conv_desc *d, int pk, int ppad, int pH, int pW, const
         else if (cudaMemcpy(p.cshift, d->shift, sizeof(float) * d->Cout, cudaMemcpyDeviceToHost) != cudaSuccess)
             return thb_note_launch(cudaGetLastError(), "conv_patch: reading the shift constants");
     }
+    p.has_res = d->res != nullptr;
+    p.res_coef = d->res_coef;
+    if (p.has_res) {
+        if (p.ct_bufs != 2) return THB_ERR_UNSUPPORTED;   // (the residual copy runs one unit ahead: it needs the second tile)
+        if (d->self_coef != 1.f)                          // the convolution's own +-1 goes into its constants (exact)
+            for (int c = 0; c < 64; c++) { p.cscale[c] *= d->self_coef; p.cshift[c] *= d->self_coef; }
+    }
     static bool configured[16] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 16) dev = 0;
-    typedef void (*kern_t)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const PatchParams);
+    typedef void (*kern_t)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const PatchParams);
     static const kern_t kerns[6] = {conv_patch_tc_kernel<32, 0>,  conv_patch_tc_kernel<32, 2>,  conv_patch_tc_kernel<32, 3>,
                                     conv_patch_tc_kernel<128, 0>, conv_patch_tc_kernel<128, 2>, conv_patch_tc_kernel<128, 3>};
     if (!configured[dev]) {
@@ -663,7 +758,7 @@ int patch_launch(const thb_conv_desc *d, int pk, int ppad, int pH, int pW, const
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = use_pdl ? 1 : 0;
-    const cudaError_t le = cudaLaunchKernelEx(&cfg, kern, e->w, e->a, e->y_map, p);
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, kern, e->w, e->a, e->y_map, p.has_res ? e->r_map : e->y_map, p);
     return thb_note_launch(le != cudaSuccess ? le : cudaGetLastError(), "conv_patch_tc_kernel");
 }
 
@@ -684,7 +779,7 @@ extern "C" int thb_conv_patch_supported(const thb_conv_desc *d)
 {
     Geometry g;
     return !patch_disabled() && patch_geometry_ok(d, 0, 0, 0) &&
-           choose_patch(d->oH, d->oW, d->kH, d->kW, d->Cin_pad * 2, 0, 0, 0, &g) ? 1 : 0;
+           choose_patch(d->oH, d->oW, d->kH, d->kW, d->Cin_pad * 2, 0, 0, 0, d->res != nullptr, &g) ? 1 : 0;
 }
 
 extern "C" int thb_conv_patch_fwd(const thb_conv_desc *d, const void *x, void *y, thb_stream s)
@@ -705,7 +800,7 @@ extern "C" int thb_conv_maxpool_supported(const thb_conv_desc *d, int pk, int ps
     }
     Geometry g;
     return !disabled && !patch_disabled() && pk > 0 && patch_geometry_ok(d, pk, ps, ppad) &&
-           choose_patch(d->oH, d->oW, d->kH, d->kW, d->Cin_pad * 2, pk, d->oH / 2 + 1, d->oW / 2 + 1, &g) ? 1 : 0;
+           choose_patch(d->oH, d->oW, d->kH, d->kW, d->Cin_pad * 2, pk, d->oH / 2 + 1, d->oW / 2 + 1, false, &g) ? 1 : 0;
 }
 
 extern "C" int thb_conv_maxpool_fwd(const thb_conv_desc *d, int pk, int ps, int ppad, int pH, int pW, const void *x, void *y,
