@@ -272,6 +272,38 @@ def test_pageable_batches_are_staged_through_pinned_memory(th, tmp_path, monkeyp
     assert np.array_equal(got[0], got[1])
 
 
+@pytest.mark.parametrize("entry", ["float", "images"])
+def test_first_layer_on_sixteen_stored_channels(th, oracle, tmp_path, monkeypatch, entry):
+    """A stride-1 first convolution on three channels (VGG, the segmentation net) in the 16-bit modes: the input is staged
+    with 16 channels per pixel (zeros behind the real ones) and the layer runs as a 16-channel convolution through the
+    patch kernel.  Same result as the gathered 8-channel layout (THB200_NO_PAD16=1) within fp16 rounding, both within
+    tolerance of the oracle, through both entry points."""
+    g = fx.vgg16(width=0.25, size=64, classes=10, fc=64)
+    rng = np.random.default_rng(11)
+    if entry == "float":
+        x = g.make_input(3)
+        ref = oracle.run(g, x).ravel()
+    else:
+        imgs = [rng.integers(0, 256, (64, 64, 3)).astype(np.uint8) for _ in range(3)]
+        import ctypes as C
+        dst = np.empty((3, 3, 64, 64), np.float32)
+        ptrs = (C.POINTER(C.c_ubyte) * 3)(*[i.ctypes.data_as(C.POINTER(C.c_ubyte)) for i in imgs])
+        oracle.lib.orc_images_to_float(ptrs, 3, 64, 64, 64 * 3, 3, g.mean.ctypes.data_as(C.POINTER(C.c_float)),
+                                       g.std.ctypes.data_as(C.POINTER(C.c_float)), 0, dst.ctypes.data_as(C.POINTER(C.c_float)))
+        plain = fx.Graph()
+        plain.nodes, plain.output = g.nodes, g.output
+        ref = oracle.run(plain, dst).ravel()
+    outs = []
+    for off in ("0", "1"):
+        monkeypatch.setenv("THB200_NO_PAD16", off)
+        hc = _convert(th, g, "t7", tmp_path, "vggp16" + off + entry, 1)
+        out = th.process_float(hc, x)[0] if entry == "float" else th.process_images(hc, imgs)[0]
+        th.free_network(hc)
+        assert rel_err(out, ref) < 1e-2
+        outs.append(out)
+    assert rel_err(outs[0], outs[1]) < 5e-3
+
+
 def test_process_yuyv(th, oracle, tmp_path):
     """THProcessYUYV (thapi.c:575-612): the frame is converted on the GPU with the reference's integer tables; a network
     as loaded takes it, a converted one refuses it as the reference's converted networks do."""

@@ -144,6 +144,8 @@ struct thb_engine {
     int N, C, H, W, rank, cp;
     int built;
     int input_s2d; /* the network input is staged space-to-depth for a stride-2 first convolution */
+    int input_pad16; /* the network input is staged with 16 channels per pixel (zeros behind the real ones) for a stride-1
+                      * first convolution, which then runs as a 16-channel convolution through the patch kernel */
     instance inst[8];
     /* Host-input forwards are pipelined: the batch slice of each GPU is cut into `chunks` sub-batches, each with its own
      * plan instance and stream on that GPU, so that the host-to-device copy of one sub-batch runs under the kernels of
@@ -413,6 +415,7 @@ static int plan_gemm_group(planner *P, int i)
     /* stride-2 first convolution on a space-to-depth input (see instance_build): rewritten as a stride-1 convolution
      * over 4*Cin channels.  Input row 2*oh - pad + r is block row oh + floor((r - pad)/2), phase (r - pad) mod 2. */
     const int s2d = E->input_s2d && n->in[0] == 0 && n->op == OP_CONV;
+    const int pad16 = E->input_pad16 && n->in[0] == 0 && n->op == OP_CONV;  /* 16 stored channels, zeros behind the real ones */
     const int s2d_padH = (n->padH + 1) / 2, s2d_padW = (n->padW + 1) / 2;
     const int s2d_kH = (n->kH - 1 - n->padH) / 2 + s2d_padH + 1, s2d_kW = (n->kW - 1 - n->padW) / 2 + s2d_padW + 1;
 
@@ -712,6 +715,16 @@ static int plan_gemm_group(planner *P, int i)
                         w_tmp[(((size_t)co * Cin + (ph * 2 + pw) * n->Cin + c) * kH + dh) * kW + dw] =
                             (w_fold ? w_fold : n->weight)[(((size_t)co * n->Cin + c) * n->kH + r) * n->kW + q];
                     }
+        w_oihw = w_tmp;
+    } else if (pad16) {
+        /* the same convolution over 16 input channels, the added ones with zero weights */
+        d->Cout = n->Cout; d->oH = os.H; d->oW = os.W;
+        d->Cin = 16;
+        d->BN = 64; /* (the patch kernel's tile, also below 33 output channels) */
+        const float *src = w_fold ? w_fold : n->weight;
+        w_tmp = calloc((size_t)n->Cout * 16 * kH * kW, sizeof(float));
+        for (int co = 0; co < n->Cout; co++)
+            memcpy(w_tmp + (size_t)co * 16 * kH * kW, src + (size_t)co * n->Cin * kH * kW, sizeof(float) * n->Cin * kH * kW);
         w_oihw = w_tmp;
     } else {
         d->Cout = n->Cout; d->oH = os.H; d->oW = os.W;
@@ -1367,7 +1380,25 @@ static int instance_build(thb_engine *E, instance *I, int device, int slice_off,
                        !(off && atoi(off));
         if (E->input_s2d) { in.C = 4 * E->C; in.H = E->H / 2; in.W = E->W / 2; }
     }
+    {
+        /* A stride-1 convolution with at most 64 output channels on very few input channels (VGG, the segmentation net):
+         * with 32-byte pixels it is a case for the patch kernel (one copy per input patch) instead of a gather of
+         * 16-byte chunks that are mostly padding. */
+        thb_node *c1 = M->nnodes > 1 ? &M->nodes[1] : 0;
+        const char *off = getenv("THB200_NO_PAD16");
+        E->input_pad16 = !E->input_s2d && c1 && c1->op == OP_CONV && c1->in[0] == 0 && P.uses[0] == 1 && c1->dH == 1 && c1->dW == 1 &&
+                         E->C <= 8 && c1->Cin == E->C && c1->Cout <= 64 && c1->kH <= 8 && c1->kW <= 8 && c1->kH * c1->kW > 1 &&
+                         c1->padH < c1->kH && c1->padW < c1->kW && (E->dtype == THB_F16 || E->dtype == THB_BF16) &&
+                         !(E->honour_pads && (c1->pad2H != c1->padH || c1->pad2W != c1->padW || c1->dlH > 1 || c1->dlW > 1 || c1->autopad || c1->refl_pad)) &&
+                         !(off && atoi(off));
+    }
     materialise(&P, &P.val[0], in);
+    if (E->input_pad16) {
+        value *v = &P.val[0];
+        v->ld = 16;
+        I->nbufs--; /* re-create the buffer with 16 channels per pixel */
+        v->buf = new_buf(&P, (size_t)in.N * in.H * in.W * v->ld * esize_of(E->dtype));
+    }
     if (E->input_s2d) {
         /* When the rewritten convolution's kernel row fills one 128-byte K block, store the staged rows with their
          * zero padding: one copy then fetches a whole kernel row of an output pixel (thb_conv_desc.in_row_pitch). */

@@ -112,8 +112,8 @@ __global__ void preprocess_kernel(const float *x, float *x_inplace, int N, int C
     const long n = pix / HW, hw = pix - n * HW;
     const float m[3] = {mean.x, mean.y, mean.z}, sd[3] = {std_.x, std_.y, std_.z};
     const float zr = roundf(q_min * q_mult);
-    const int Cpad = (C + VN - 1) / VN * VN;
-    for (int c0 = 0; c0 < Cpad; c0 += VN) {
+    // every stored channel of the pixel is written (y_ld may exceed the rounded channel count: zeros there)
+    for (int c0 = 0; c0 < y_ld; c0 += VN) {
         float v[VN];
 #pragma unroll
         for (int i = 0; i < VN; i++) {
@@ -233,6 +233,10 @@ __global__ void preprocess_images_kernel(const uint8_t *img, int N, int H, int W
         v[i] = val;
     }
     Vec<T>::store(y + pix * y_ld, v);
+    // (a pixel stored with more channels than one group: zeros behind)
+#pragma unroll
+    for (int i = 0; i < VN; i++) v[i] = 0.f;
+    for (int c0 = VN; c0 < y_ld; c0 += VN) Vec<T>::store(y + pix * y_ld + c0, v);
 }
 
 // u8 HWC RGB images -> normalised space-to-depth NHWC T: the layout preprocess_s2d_kernel writes (channel (ph*2 + pw)*3 + c
@@ -296,6 +300,9 @@ __global__ void preprocess_yuyv_kernel(const uint8_t *frame, int H, int W, float
 #pragma unroll
         for (int c = 0; c < VN; c++) vv[c] = out[c];
         Vec<T>::store(y + (pair * 2 + k) * y_ld, vv);
+#pragma unroll
+        for (int c = 0; c < VN; c++) vv[c] = 0.f;
+        for (int c0 = VN; c0 < y_ld; c0 += VN) Vec<T>::store(y + (pair * 2 + k) * y_ld + c0, vv);
     }
 }
 
