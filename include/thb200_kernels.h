@@ -115,6 +115,12 @@ typedef struct thb_conv_desc {
      * takes them from here; without them it reads the device arrays back with a blocking copy at EVERY launch, which is
      * fine for a test and must not happen inside a stream capture. */
     const float *scale_host, *shift_host;
+    /* Split K (F16 / BF16, optional; 0 or 1: none).  A convolution of few tiles leaves most SMs idle: with splits = S the K
+     * blocks of every tile are shared by S CTAs, which store fp32 partial tiles to splitk_scratch ([S][N*oH*oW][Cout_pad]
+     * floats, thb_conv_splitk_plan gives S and the size), and a second launch adds them in split order and runs the
+     * epilogue.  The launcher falls back to one launch when the layer's operand layout has no split form. */
+    int splits;
+    float *splitk_scratch;
 } thb_conv_desc;
 
 int thb_channel_align(int dtype);               /* 4 (F32), 8 (F16/BF16), 16 (U8) */
@@ -126,6 +132,8 @@ int thb_conv_pack_weights_host(const thb_conv_desc *d, const float *w_oihw, cons
                                void *packed_host, int *kinfo_host, int *wsat_host);
 int thb_conv_make_tmap(const thb_conv_desc *d, thb_tmap *out);
 int thb_conv_fwd(const thb_conv_desc *d, const void *x, void *y, thb_stream s);
+/* the split count that suits a convolution's tile count (1: none) and the scratch bytes it needs; THB200_NO_SPLITK=1: always 1 */
+int thb_conv_splitk_plan(const thb_conv_desc *d, size_t *scratch_bytes);
 
 /* Convolution + epilogue as above (no residual) + max pooling with a pk x pk window (2 or 3), stride 2 and padding ppad
  * in ONE launch: the convolution's own output is never written, only the [N][pH][pW][y_ld] pooled tensor.  Replaces

@@ -123,6 +123,47 @@ def test_conv_f32_reduction_split_over_a_cluster(lib, G, oracle, case, knobs):
     assert G.rel_err(outs[0], outs[1]) < 1e-5          # and differs from the unsplit one by rounding order only
 
 
+@pytest.mark.parametrize("dtype", [K.THB_F16, K.THB_BF16])
+@pytest.mark.parametrize("case", [(1, 512, 7, 7, 512, 3, 1, 1), (4, 256, 14, 14, 256, 3, 1, 1), (2, 1024, 14, 14, 256, 1, 1, 0),
+                                  (2, 128, 28, 28, 256, 3, 2, 1), (2, 256, 9, 9, 200, 3, 1, 1), (1, 192, 13, 13, 384, 3, 1, 1)])
+def test_conv_tc_reduction_split_over_ctas(lib, G, oracle, case, dtype):
+    """Tensor-core convolutions of few tiles (the batch-1 and small-batch layers): thb_conv_splitk_plan proposes how many
+    CTAs share each tile's K blocks; they store fp32 partial tiles and a second launch adds them in split order and runs
+    the epilogue (scale, shift, residual, PReLU).  Within tolerance of the oracle, equal from run to run, and equal to the
+    unsplit launch up to the rounding order of the sums."""
+    n, cin, h, w, cout, k, s, p = case
+    x, wt = _conv_inputs(case, 81, True)
+    rng = np.random.default_rng(82)
+    scale = rng.uniform(0.5, 1.5, cout).astype(np.float32)
+    shift = rng.standard_normal(cout).astype(np.float32)
+    slope = rng.uniform(0.05, 0.3, cout).astype(np.float32)
+    conv_ref = oracle.conv2d(x, wt, None, (s, s), (p, p)) * scale[None, :, None, None] + shift[None, :, None, None]
+    res = rng.standard_normal(conv_ref.shape).astype(np.float16).astype(np.float32)
+    v = conv_ref - res
+    ref = np.where(v > 0, v, v * slope[None, :, None, None])
+    tol = 1e-2 if dtype == K.THB_F16 else 6e-2
+    outs = []
+    for split in (True, False, True):
+        conv = G.Conv(lib, dtype, x.shape, wt, (s, s), (p, p))
+        conv.set_affine(scale, shift, host_copies=True)
+        rt, rld = G.to_nhwc(res, dtype)
+        conv.set_residual(rt, rld, 1.0, -1.0)
+        conv.set_act(K.ACT_PRELU, slope=slope)
+        if split:
+            nbytes = C.c_size_t(0)
+            lib.thb_conv_splitk_plan.argtypes = [C.c_void_p, C.POINTER(C.c_size_t)]
+            S = lib.thb_conv_splitk_plan(C.byref(conv.d), C.byref(nbytes))
+            assert S > 1 and nbytes.value > 0, "the case must be one the planner would split"
+            scratch = torch.full((nbytes.value // 4,), float("nan"), dtype=torch.float32, device="cuda")
+            conv.keep.append(scratch)
+            conv.d.splits, conv.d.splitk_scratch = S, scratch.data_ptr()
+        xt, _ = G.to_nhwc(x, dtype)
+        outs.append(G.from_nhwc(conv.run(xt, fill=3.0), cout))
+        assert G.rel_err(outs[-1], ref) < tol, (case, split, G.rel_err(outs[-1], ref))
+    assert np.array_equal(outs[0], outs[2])
+    assert G.rel_err(outs[0], outs[1]) < (2e-3 if dtype == K.THB_F16 else 2e-2)
+
+
 @pytest.mark.parametrize("gather_only", [False, True])
 @pytest.mark.parametrize("crop", [0, 1])
 def test_conv_f16_rows_stored_with_padding(lib, G, oracle, gather_only, crop, knobs):

@@ -79,6 +79,7 @@ enum step_kind {
 
 typedef struct {
     int kind, dtype;
+    int scratch_buf; /* fp32 partial tiles of a convolution whose K blocks are split over several CTAs (-1: none) */
     int nin, in_buf[8], in_ld[8], in_coff[8];
     int out_buf, out_ld, out_coff;
     int aux_buf; /* csum scratch (conv u8) */
@@ -248,7 +249,7 @@ static step *new_step(planner *P, int kind)
     memset(s, 0, sizeof(*s));
     s->kind = kind;
     s->dtype = P->E->dtype;
-    s->out_buf = s->aux_buf = s->aux2_buf = -1;
+    s->out_buf = s->aux_buf = s->aux2_buf = s->scratch_buf = -1;
     for (int i = 0; i < 8; i++) s->in_buf[i] = -1;
     s->flops_node = -1;
     return s;
@@ -769,6 +770,15 @@ static int plan_gemm_group(planner *P, int i)
         thb_conv_geometry(d);
     }
     if (dual_conv < 0 && in_ld < d->Cin_pad) { free(w_tmp); thb_set_error("internal: input stride %d below padded channels %d", in_ld, d->Cin_pad); return -1; }
+    if (pool < 0 && dual_conv < 0 && (dtype == THB_F16 || dtype == THB_BF16) && !thb_conv_patch_supported(d)) {
+        /* a launch of few tiles: several CTAs share each tile's reduction, through an fp32 scratch that lives for this launch */
+        size_t sk_bytes = 0;
+        const int S = thb_conv_splitk_plan(d, &sk_bytes);
+        if (S > 1) {
+            d->splits = S;
+            s->scratch_buf = new_buf(P, sk_bytes);
+        }
+    }
 
     size_t wbytes = thb_conv_weight_bytes(d), kwords = thb_conv_kinfo_words(d);
     void *packed = malloc(wbytes);
@@ -1285,6 +1295,7 @@ static size_t pack_arena(instance *I)
         ids[n++] = s->out_buf;
         ids[n++] = s->aux_buf;
         ids[n++] = s->aux2_buf;
+        ids[n++] = s->scratch_buf;
         for (int k = 0; k < n; k++)
             if (ids[k] >= 0) {
                 abuf *b = &I->bufs[ids[k]];
@@ -1470,6 +1481,7 @@ static int run_steps_ev(thb_engine *E, instance *I, cudaEvent_t *evs)
             else if (s->nin > 1) d->res = bufptr(I, s->in_buf[1], s->in_coff[1], dt);
             if (s->aux_buf >= 0) d->csum = (const int *)bufptr(I, s->aux_buf, 0, THB_U8);
             if (s->aux2_buf >= 0) d->csum_out = (int *)bufptr(I, s->aux2_buf, 0, THB_U8);
+            if (s->scratch_buf >= 0) d->splitk_scratch = (float *)bufptr(I, s->scratch_buf, 0, THB_U8);
             rc = s->pool_k ? thb_conv_maxpool_fwd(d, s->pool_k, 2, s->pool_pad, s->pool_oH, s->pool_oW, x0, y, s->out_ld, st)
                            : thb_conv_fwd(d, x0, y, st);
             break;

@@ -78,6 +78,11 @@ struct ConvTcParams {
     int use_l1;  // gather through L1: neighbouring taps of one tile re-read the same input pixels
     int *acc_out;
     int *status;
+    int splits;                // > 1: the K blocks of every tile are shared by this many CTAs (units of work = tiles x splits, the
+                               // split index innermost); each stores its raw fp32 partial tile to `partial` and
+                               // splitk_finish_kernel adds them up in split order and runs the epilogue
+    float *partial;            // [splits][P][partial_ld] fp32
+    int partial_ld;
     long long wait_limit;      // SM cycles a bounded wait may take before it gives up (about two seconds by default)
     int test_withhold;         // tests only: the producer never delivers the last K block of the CTA's last tile
 };
@@ -222,20 +227,31 @@ struct EpiCursor {
 // lt*gridDim.x of the (pixel tile, column tile) grid.  Pair mode: the CTA takes UNITS of two vertically adjacent pixel
 // tiles with the same column tile; local tiles 2i and 2i+1 are the halves of its i-th unit.  A second half beyond
 // the last pixel tile (odd tile count) is a phantom: it is computed from zero-filled loads and never stored.
-template <int BN> struct TileMap {
-    int pair, n_tiles, n_local, last_um;
+template <int BN, bool SPLIT = false> struct TileMap {
+    int pair, n_tiles, n_local, last_um, splits, nkb;
     __device__ TileMap(const ConvTcParams &p)
     {
         pair = p.pair;
         n_tiles = p.n_tiles;
+        splits = SPLIT && p.splits > 1 ? p.splits : 1;   // (never with pair mode or a reversed walk)
+        nkb = p.nkb;
         last_um = p.reverse ? (pair ? (p.m_tiles + 1) >> 1 : p.m_tiles) - 1 : -1;
-        const int units = (pair ? (p.m_tiles + 1) >> 1 : p.m_tiles) * n_tiles;
+        const int units = (pair ? (p.m_tiles + 1) >> 1 : p.m_tiles) * n_tiles * splits;
         const int mine = (int)blockIdx.x < units ? (units - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
         n_local = pair ? 2 * mine : mine;
     }
+    // split index of local tile lt, and the K blocks [kb0, kb1) it covers
+    __device__ int split_of(int lt) const { return SPLIT && splits > 1 ? (int)((blockIdx.x + lt * gridDim.x) % splits) : 0; }
+    __device__ void kblocks(int lt, int &kb0, int &kb1) const
+    {
+        const int sp = split_of(lt);
+        kb0 = (int)((long)nkb * sp / splits);
+        kb1 = (int)((long)nkb * (sp + 1) / splits);
+    }
     __device__ void coords(int lt, int &m0, int &n0) const
     {
-        const int u = blockIdx.x + (pair ? lt >> 1 : lt) * gridDim.x;
+        int u = blockIdx.x + (pair ? lt >> 1 : lt) * gridDim.x;
+        if (SPLIT && splits > 1) u /= splits;
         int um = u / n_tiles;
         n0 = (u - um * n_tiles) * BN;
         if (last_um >= 0) um = last_um - um;  // walk the pixel tiles from the end of the tensor
@@ -245,8 +261,8 @@ template <int BN> struct TileMap {
 
 // The sequence of 64-channel blocks an epilogue group walks: every ngrp-th local tile of this CTA, and of each tile
 // the blocks that hold real channels.
-template <int BN> struct EpiWalk {
-    TileMap<BN> map;
+template <int BN, bool SPLIT = false> struct EpiWalk {
+    TileMap<BN, SPLIT> map;
     int grp, ngrp, my_tiles, cout8;
     __device__ EpiWalk(const ConvTcParams &p, int g) : map(p)
     {
@@ -369,7 +385,7 @@ __device__ __forceinline__ void u8_chunk32_pairs(const uint32_t (&acc)[32], cons
 // available (for a fused residual that is the arrival of the residual tile, loaded by the group's agent), reads its 64
 // accumulator columns from TMEM, combines them with its residual row in place, leaves the converted row in the tile
 // and arrives on the tile's rows_ready barrier.  The agent (epilogue_agent) does the rest.
-template <int KIND, int BN, int NACC>
+template <int KIND, int BN, int NACC, bool SPLIT>
 __device__ __forceinline__ void epilogue_tma(const ConvTcParams &p, int grp, int warp, int lane, uint32_t tmem_base,
                                              uint8_t *tiles, uint64_t *acc_full, uint64_t *acc_empty, uint64_t *rows_ready,
                                              uint64_t *avail, volatile int *abort_flag)
@@ -381,7 +397,7 @@ __device__ __forceinline__ void epilogue_tma(const ConvTcParams &p, int grp, int
     const int act_mode = p.act_kind == THB_ACT_NONE ? 0
                          : p.act_kind != THB_ACT_THRESHOLD ? 2
                          : (p.act_th == 0.f && p.act_val == 0.f) ? 3 : 1;
-    const EpiWalk<BN> walk(p, grp);
+    const EpiWalk<BN, SPLIT> walk(p, grp);
     EpiCursor cur = {0, 0};
     int b = 0;            // tile of the current block, and how often the ring of tiles has wrapped
     uint32_t wrap = 0;
@@ -412,6 +428,22 @@ __device__ __forceinline__ void epilogue_tma(const ConvTcParams &p, int grp, int
         if (last_block) {  // every column of this accumulator has been read: hand it back to the MMA warp
             tc_fence_before();
             mbar_arrive(smem_u32(&acc_empty[ab]));
+        }
+        if constexpr (SPLIT) {
+            // split K: this CTA holds a partial sum of the tile.  The thread's 64 columns go to the fp32 scratch of its split
+            // as they are; splitk_finish_kernel adds the splits and runs the epilogue.  No shared-memory tile, no agent.
+            const int pm = m0 + row;
+            if (pm < p.P) {
+                float4 *dst = reinterpret_cast<float4 *>(p.partial + ((size_t)walk.map.split_of(lt) * p.P + pm) * p.partial_ld + nsub0);
+#pragma unroll
+                for (int q = 0; q < 8; q++) dst[q] = make_float4(__uint_as_float(acc0[4 * q]), __uint_as_float(acc0[4 * q + 1]),
+                                                                 __uint_as_float(acc0[4 * q + 2]), __uint_as_float(acc0[4 * q + 3]));
+#pragma unroll
+                for (int q = 0; q < 8; q++) dst[8 + q] = make_float4(__uint_as_float(acc1[4 * q]), __uint_as_float(acc1[4 * q + 1]),
+                                                                     __uint_as_float(acc1[4 * q + 2]), __uint_as_float(acc1[4 * q + 3]));
+            }
+            walk.advance(cur);
+            continue;
         }
         // the tile is ours once its previous store has read it out and, with a residual, the residual rows are in it
         if (!mbar_wait_bounded(smem_u32(&avail[b]), wrap & 1, p.wait_limit)) {
@@ -498,7 +530,7 @@ __device__ __forceinline__ void epilogue_agent(const ConvTcParams &p, const CUte
         for (int k = q; k < q_pre; k++) mbar_wait_bounded(smem_u32(&avail[k % nbuf]), (k / nbuf) & 1, p.wait_limit);
 }
 
-template <int KIND, int BN, int STAGES>
+template <int KIND, int BN, int STAGES, bool SPLIT>
 __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_constant__ CUtensorMap tmapW, const __grid_constant__ CUtensorMap tmapA,
                                                                const __grid_constant__ CUtensorMap tmapY, const __grid_constant__ CUtensorMap tmapR,
                                                                const ConvTcParams p)
@@ -577,7 +609,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
     if (warp == 14) {
         // ================================================================== epilogue agents (TMA epilogue only)
         if constexpr (L::TMA_EPI)
-            if (lane < p.epi_groups)
+            if (lane < p.epi_groups && !SPLIT)   // (split K: the partial tiles go straight to the fp32 scratch)
                 epilogue_agent<BN>(p, &tmapY, &tmapR, lane, stage_buf + lane * p.epi_bufs * EPI_TILE_BYTES, rows_ready + lane * 3,
                                    avail + lane * 3, abort_flag);
         __syncwarp();
@@ -588,7 +620,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
             // nothing to gather: these four warps are the third epilogue group
             if constexpr (L::TMA_EPI)
                 if (p.epi_groups == 3)
-                    epilogue_tma<KIND, BN, NACC>(p, 2, warp, lane, tmem_base, stage_buf + 2 * p.epi_bufs * EPI_TILE_BYTES,
+                    epilogue_tma<KIND, BN, NACC, SPLIT>(p, 2, warp, lane, tmem_base, stage_buf + 2 * p.epi_bufs * EPI_TILE_BYTES,
                                                  acc_full, acc_empty, rows_ready + 6, avail + 6, abort_flag);
             goto done;
         }
@@ -665,7 +697,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
         // ================================================================== TMA producer: per K block the weight tile
         // and, in the TMA modes, the activation tile (both halves' tiles in pair mode)
         if (lane == 0) {
-            const TileMap<BN> map(p);
+            const TileMap<BN, SPLIT> map(p);
             const int halves = pair ? 2 : 1;
             int ring_s = 0;  // stage and phase in the ring of nst stages
             uint32_t ring_ph = 0;
@@ -693,7 +725,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                         ih[h] = oh * p.dH - p.padH;
                         iw[h] = (rem - oh * p.oW) * p.dW - p.tma_padw;
                     }
-                for (int kb = 0; kb < p.nkb; kb++) {
+                // split K: this unit covers the K blocks [kb0, kb1) of its tile, starting at the tap and slab of kb0
+                int kb0 = 0, kb1 = p.nkb;
+                if (SPLIT) {
+                    map.kblocks(lt, kb0, kb1);
+                    if (p.a_tma == 2) {
+                        const int tap = kb0 / p.slabs;
+                        slab = kb0 - tap * p.slabs;
+                        tap_h = tap / p.tma_kw;
+                        tap_w = tap - tap_h * p.tma_kw;
+                    }
+                }
+                for (int kb = kb0; kb < kb1; kb++) {
                     const int s = ring_s;
                     const uint32_t ph = ring_ph;
                     if (++ring_s == nst) { ring_s = 0; ring_ph ^= 1; }
@@ -704,7 +747,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                         break;
                     }
                     // (tests of the give-up path: every earlier copy has been consumed by then, nothing is in flight)
-                    if (p.test_withhold && kb == p.nkb - 1 && lt + halves >= map.n_local) break;
+                    if (p.test_withhold && kb == kb1 - 1 && lt + halves >= map.n_local) break;
                     const uint32_t bar = smem_u32(&full[s]);
                     if (p.half) {
                         const int nh = 2 * kb + 1 < p.ntaps ? 2 : 1;
@@ -744,7 +787,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
     } else if (warp == 5) {
         // ================================================================== MMA issuer
         if (lane == 0) {
-            const TileMap<BN> map(p);
+            const TileMap<BN, SPLIT> map(p);
             const int halves = pair ? 2 : 1;
             int ring_s = 0;
             uint32_t ring_ph = 0;
@@ -760,7 +803,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                 if (!alive) break;
                 tc_fence_after();
                 const uint32_t d0 = tmem_base + (lt % NACC) * BN, d1 = tmem_base + ((lt + 1) % NACC) * BN;
-                for (int kb = 0; kb < p.nkb; kb++) {
+                int kb0 = 0, kb1 = p.nkb;
+                if (SPLIT) map.kblocks(lt, kb0, kb1);
+                for (int kb = kb0; kb < kb1; kb++) {
                     const int s = ring_s;
                     const uint32_t ph = ring_ph;
                     if (++ring_s == nst) { ring_s = 0; ring_ph ^= 1; }
@@ -779,7 +824,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                             const uint64_t bd = make_sw64_kmajor_desc(smem_u32(sB + s * B_STAGE_BYTES + h * (B_STAGE_BYTES / 2)));
 #pragma unroll
                             for (int k = 0; k < 2; k++) {
-                                const uint32_t accum = (kb | h | k) != 0;
+                                const uint32_t accum = ((kb - kb0) | h | k) != 0;
                                 if (KIND == 2) tc_mma_i8(d0, ad + 2 * k, bd + 2 * k, IDESC, accum);
                                 else tc_mma_f16(d0, ad + 2 * k, bd + 2 * k, IDESC, accum);
                             }
@@ -791,7 +836,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
                     const uint64_t bdesc = make_sw128_kmajor_desc(smem_u32(sB + s * B_STAGE_BYTES));
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
-                        const uint32_t accum = (kb | k) != 0;
+                        const uint32_t accum = ((kb - kb0) | k) != 0;
                         if (KIND == 2) tc_mma_i8(d0, adesc + 2 * k, bdesc + 2 * k, IDESC, accum);
                         else tc_mma_f16(d0, adesc + 2 * k, bdesc + 2 * k, IDESC, accum);
                     }
@@ -816,7 +861,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_tc_kernel(const __grid_const
         const int et = warp < 4 ? tid : tid - 192 - grp * 128;  // 0..127 within the group
         const int ngrp = L::TMA_EPI ? 2 : (p.epi_groups == 3 ? 3 : 2);  // groups sharing the staged epilogue's tiles
         if constexpr (L::TMA_EPI) {
-            epilogue_tma<KIND, BN, NACC>(p, grp, warp, lane, tmem_base, stage_buf + grp * p.epi_bufs * EPI_TILE_BYTES, acc_full,
+            epilogue_tma<KIND, BN, NACC, SPLIT>(p, grp, warp, lane, tmem_base, stage_buf + grp * p.epi_bufs * EPI_TILE_BYTES, acc_full,
                                          acc_empty, rows_ready + grp * 3, avail + grp * 3, abort_flag);
             goto done;
         }
@@ -1184,6 +1229,38 @@ done:
     }
 }
 
+// Split K, second launch: one thread per pixel and 8-channel chunk adds the partial sums of the splits in split order (the
+// result does not depend on timing) and runs the floating-point epilogue of epi_chunk on the sum.
+template <int KIND, bool HAS_RES>
+__global__ void __launch_bounds__(256) splitk_finish_kernel(const ConvTcParams p)
+{
+    const int chunks = (p.Cout + 7) >> 3;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)p.P * chunks) return;
+    const long pm = idx / chunks;
+    const int c0 = (int)(idx - pm * chunks) * 8;
+    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+    for (int sp = 0; sp < p.splits; sp++) {
+        const float4 *src = reinterpret_cast<const float4 *>(p.partial + ((size_t)sp * p.P + pm) * p.partial_ld + c0);
+        const float4 t0 = src[0], t1 = src[1];
+        a0.x += t0.x; a0.y += t0.y; a0.z += t0.z; a0.w += t0.w;
+        a1.x += t1.x; a1.y += t1.y; a1.z += t1.z; a1.w += t1.w;
+    }
+    const float self = HAS_RES ? p.self_coef : 1.f;
+    float sc[8], sh[8], sl[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        // (the per-channel arrays are padded to multiples of 64 floats: reading a chunk's eight is always in bounds)
+        sc[i] = (p.scale ? p.scale[c0 + i] : 1.f) * self;
+        sh[i] = (p.shift ? p.shift[c0 + i] : 0.f) * self;
+        sl[i] = p.slope ? p.slope[c0 + i] : 0.f;
+    }
+    uint4 rv = make_uint4(0, 0, 0, 0);
+    if (HAS_RES) rv = __ldg(reinterpret_cast<const uint4 *>(p.res + ((size_t)pm * p.res_ld + c0) * 2));
+    const uint4 o = epi_chunk<KIND, HAS_RES, 2, true>(a0, a1, sc, sh, sl, rv, p, c0);
+    *reinterpret_cast<uint4 *>(p.y + ((size_t)pm * p.out_ld + c0) * 2) = o;
+}
+
 // Diagnostic launcher switches (THB200_* environment variables), read ONCE: a launch costs no getenv call.
 // thb_conv_reload_knobs() re-reads them (the tests change them between cases).  -1 = not set.
 struct ConvKnobs {
@@ -1240,14 +1317,18 @@ template <int KIND, int BN, int STAGES>
 int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
 {
     static bool configured[16] = {false};
-    auto kern = conv_tc_kernel<KIND, BN, STAGES>;
+    // (the split-K variant is a kernel of its own, so that the ordinary one carries none of its code)
+    constexpr bool CAN_SPLIT = Smem<KIND, BN, STAGES>::TMA_EPI;
+    auto kern_plain = conv_tc_kernel<KIND, BN, STAGES, false>;
+    auto kern_split = conv_tc_kernel<KIND, BN, STAGES, CAN_SPLIT>;
     constexpr size_t smem = Smem<KIND, BN, STAGES>::TOTAL;
     static_assert(smem <= 232448, "shared memory plan exceeds the 227 KB a CTA can have");
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 16) dev = 0;
     if (!configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(kern_plain, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess && CAN_SPLIT) e = cudaFuncSetAttribute(kern_split, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return thb_note_launch(e, "conv_tc smem attribute");
         configured[dev] = true;
     }
@@ -1274,7 +1355,13 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
         const int rev_mode = kn.reverse;
         p.reverse = L::TMA_EPI && p.a_tma && (rev_mode == 1 ? (flip++ & 1) : rev_mode == 2);
     }
-    const int tiles = (p.pair ? (p.m_tiles + 1) / 2 : p.m_tiles) * p.n_tiles;  // units of work
+    if (p.splits > 1) {
+        // split K needs both operands through TMA (the K block -> tap decoding of the producer), whole 128-byte taps, one
+        // activation operand and the TMA epilogue's accumulator walk; otherwise the launch runs unsplit
+        if (!L::TMA_EPI || !p.a_tma || p.half || p.nkb1 || p.nkb < 4 * p.splits) p.splits = 1;
+        else p.pair = 0, p.reverse = 0;
+    }
+    const int tiles = (p.pair ? (p.m_tiles + 1) / 2 : p.m_tiles) * p.n_tiles * (p.splits > 1 ? p.splits : 1);  // units of work
     int grid = tiles < num_sms() ? tiles : num_sms();
     // uint8: an epilogue group rebuilds its correction table whenever its next tile has other channels; with a grid that is a
     // multiple of the column tiles every CTA stays on one column tile (148 -> 144 CTAs for 8 or 16 column tiles)
@@ -1320,8 +1407,19 @@ int launch_tc(const ConvTmaps &tm, ConvTcParams p, cudaStream_t st)
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = use_pdl ? 1 : 0;
-    const cudaError_t le = cudaLaunchKernelEx(&cfg, kern, *tm.w, *tm.a, tm.y ? *tm.y : *tm.w, tm.r ? *tm.r : *tm.w, p);
-    return thb_note_launch(le != cudaSuccess ? le : cudaGetLastError(), "conv_tc_kernel");
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, p.splits > 1 ? kern_split : kern_plain, *tm.w, *tm.a, tm.y ? *tm.y : *tm.w,
+                                              tm.r ? *tm.r : *tm.w, p);
+    const int rc = thb_note_launch(le != cudaSuccess ? le : cudaGetLastError(), "conv_tc_kernel");
+    if (rc != THB_OK || p.splits <= 1) return rc;
+    if constexpr (KIND != 2) {
+        // the partial tiles of the splits -> the layer's output
+        const long items = (long)p.P * ((p.Cout + 7) >> 3);
+        const unsigned blocks = (unsigned)((items + 255) / 256);
+        if (p.res) splitk_finish_kernel<KIND, true><<<blocks, 256, 0, st>>>(p);
+        else splitk_finish_kernel<KIND, false><<<blocks, 256, 0, st>>>(p);
+        return thb_note_launch(cudaGetLastError(), "splitk_finish_kernel");
+    }
+    return rc;
 }
 
 template <int KIND>
@@ -1591,6 +1689,11 @@ extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, t
     }
     p.tail_start = d->tail_start; p.relu_thr = d->relu_thr; p.relu_val = d->relu_val;
     p.acc_out = d->acc_out;
+    if (d->splits > 1 && d->splitk_scratch && d->dtype != THB_U8 && !d->x2) {
+        p.splits = d->splits > 8 ? 8 : d->splits;
+        p.partial = d->splitk_scratch;
+        p.partial_ld = d->Cout_pad;
+    }
     p.use_l1 = d->kH * d->kW > 1;
     const ConvKnobs &kn = knobs();
     if (kn.conv_l1 >= 0) p.use_l1 = kn.conv_l1;
@@ -1693,4 +1796,35 @@ extern "C" int thb_conv_fwd_tc(const thb_conv_desc *d, const void *x, void *y, t
     case THB_U8: return dispatch_bn<2>(d->BN, maps, p, st);
     }
     return THB_ERR_UNSUPPORTED;
+}
+
+// How many CTAs should share the K blocks of each tile of this convolution (1: no split), and the bytes of fp32 scratch
+// that takes.  A launch of fewer tiles than SMs, or of a wave and a bit, leaves SMs idle for most of its duration: with
+// the tiles' reductions cut in S parts the units fill the machine in ceil(tiles * S / SMs) rounds of 1/S the length.
+// S minimises rounds / S plus a charge for the second launch's extra traffic; every part keeps at least four K blocks.
+extern "C" int thb_conv_splitk_plan(const thb_conv_desc *d, size_t *scratch_bytes)
+{
+    if (scratch_bytes) *scratch_bytes = 0;
+    static int off = -1;
+    if (off < 0) {
+        const char *e = getenv("THB200_NO_SPLITK");
+        off = e && atoi(e) ? 1 : 0;
+    }
+    if (off || (d->dtype != THB_F16 && d->dtype != THB_BF16) || d->BN < 64 || d->x2 || d->csum_out) return 1;
+    const long P = (long)d->N * d->oH * d->oW;
+    const long tiles = ((P + BM - 1) / BM) * (d->Cout_pad / d->BN);
+    const int nkb = d->Ktot_pad / 64, sms = num_sms();
+    // (the partial tiles cost S x 8 bytes of traffic per output element: only launches that leave at least half the SMs
+    // idle and whose whole scratch stays small gain from the split -- 100-200 tiles of a 14 x 14 layer at batch 64 do not)
+    if (tiles <= 0 || 2 * tiles > sms || nkb < 8) return 1;
+    int best = 1;
+    double best_cost = (double)((tiles + sms - 1) / sms);
+    for (int S = 2; S <= 8 && nkb / S >= 4; S++) {
+        const double cost = (double)((tiles * S + sms - 1) / sms) / S + 0.04 * (S - 1);
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = S; }
+    }
+    const size_t bytes = (size_t)best * P * d->Cout_pad * sizeof(float);
+    if (best > 1 && bytes > ((size_t)16 << 20)) return 1;
+    if (best > 1 && scratch_bytes) *scratch_bytes = bytes;
+    return best;
 }

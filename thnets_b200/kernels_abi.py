@@ -50,6 +50,7 @@ class ConvDesc(C.Structure):
         ("x2", C.c_void_p), ("x2_ld", C.c_int), ("x2_H", C.c_int), ("x2_W", C.c_int), ("x2_d", C.c_int), ("cin1", C.c_int),
         ("csum_out", C.c_void_p),
         ("scale_host", C.c_void_p), ("shift_host", C.c_void_p),
+        ("splits", C.c_int), ("splitk_scratch", C.c_void_p),
     ]
 
 
