@@ -770,6 +770,18 @@ static int plan_gemm_group(planner *P, int i)
         thb_conv_geometry(d);
     }
     if (dual_conv < 0 && in_ld < d->Cin_pad) { free(w_tmp); thb_set_error("internal: input stride %d below padded channels %d", in_ld, d->Cin_pad); return -1; }
+    if (is_linear && (dtype == THB_F16 || dtype == THB_BF16) && d->BN < 128 && d->Cout >= 128) {
+        /* A Linear on a batch of rows is a handful of tiles with a very long reduction.  The geometry rule narrows its tiles
+         * so that more SMs get a share of the weights; where the reduction can be split over CTAs instead, wide tiles
+         * move four times the weight bytes per barrier round (25088 -> 4096 on 32 rows: 135 -> about 40 us). */
+        const int bn_narrow = d->BN;
+        size_t bytes = 0;
+        d->BN = 128;
+        if (thb_conv_geometry(d) || thb_conv_splitk_plan(d, &bytes) < 2) {
+            d->BN = bn_narrow;
+            thb_conv_geometry(d);
+        }
+    }
     if (pool < 0 && dual_conv < 0 && (dtype == THB_F16 || dtype == THB_BF16) && !thb_conv_patch_supported(d)) {
         /* a launch of few tiles: several CTAs share each tile's reduction, through an fp32 scratch that lives for this launch */
         size_t sk_bytes = 0;
