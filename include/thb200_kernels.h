@@ -173,6 +173,12 @@ int thb_preprocess_s2d_padded(const float *x_nchw, float *x_inplace, int N, int 
  * (lowp/lowp_basic.c:15-35), store space-to-depth.  Zero weights quantise to the weights' zero point, whose products
  * vanish exactly (lowp_basic.c:310-320: the offsets are the rounded zero points), so the rewritten stride-1 convolution
  * gives the accumulators of the stride-2 one bit for bit. */
+/* uint8, a 3x3 / stride 1 / pad 1 first convolution on three planes: NCHW fp32 -> [N][H][W][y_ld >= 32] bytes whose channel
+ * (r*3 + s)*3 + c is plane c of pixel (h - 1 + r, w - 1 + s), normalised and quantised like thb_preprocess does (the
+ * byte of 0.0 outside the image): the convolution becomes a 1x1 one over 27 channels with weights in the same order.
+ * No counterpart in the reference (nn_unfolded_copy, modules/SpatialConvolutionMM.c:11-60, unfolds floats for every layer). */
+int thb_preprocess_neigh_u8(const float *x_nchw, float *x_inplace, int N, int H, int W, const float *mean3, const float *std3,
+                            void *y, int y_ld, float q_sub, float q_mult, thb_stream s);
 int thb_preprocess_s2d_u8(const float *x_nchw, float *x_inplace, int N, int C, int H, int W, const float *mean3,
                           const float *std3, void *y, int y_ld, float q_sub, float q_mult, thb_stream s);
 /* 1 when the device and driver accept the single-copy row fetch described at thb_conv_desc.in_row_pitch */

@@ -304,6 +304,32 @@ def test_first_layer_on_sixteen_stored_channels(th, oracle, tmp_path, monkeypatc
     assert rel_err(outs[0], outs[1]) < 5e-3
 
 
+@pytest.mark.parametrize("batch", [1, 3])
+def test_lowp_first_layer_staged_as_neighbourhoods(th, oracle, tmp_path, monkeypatch, batch):
+    """uint8 engine, VGG's first layer (3x3 / stride 1 / pad 1 on three planes): the boundary kernel stages every pixel's 27
+    quantised neighbours (the byte of 0.0 outside the image) and the layer runs as a 1x1 convolution.  Every output byte
+    equals the gathered 3x3 layer's (THB200_NO_NEIGH_U8=1) and the lowp oracle's; the caller's buffer is normalised in
+    place the same way."""
+    rng_ = 16.0
+    g = fx.vgg16(width=0.125, size=32, classes=10, fc=64)
+    x = g.make_input(batch)
+    ref = oracle.run_lowp(g, x, rng_, 32)
+    outs, bufs = [], []
+    for off in ("0", "1"):
+        monkeypatch.setenv("THB200_NO_NEIGH_U8", off)
+        h = _load(th, g, "t7", tmp_path, "vggn" + off)
+        th.make_spatial(h, 32)
+        hl = th.create_lowp_network(h, rng_)
+        th.free_network(h)
+        buf = np.array(x, copy=True)
+        out, _, _ = th.process_float(hl, buf, copy_input=False)
+        th.free_network(hl)
+        assert np.array_equal(out, ref.ravel()), np.abs(out - ref.ravel()).max()
+        outs.append(out)
+        bufs.append(buf)
+    assert np.array_equal(bufs[0], bufs[1])
+
+
 def test_process_yuyv(th, oracle, tmp_path):
     """THProcessYUYV (thapi.c:575-612): the frame is converted on the GPU with the reference's integer tables; a network
     as loaded takes it, a converted one refuses it as the reference's converted networks do."""

@@ -145,6 +145,9 @@ struct thb_engine {
     int N, C, H, W, rank, cp;
     int built;
     int input_s2d; /* the network input is staged space-to-depth for a stride-2 first convolution */
+    int input_neigh; /* uint8 engine, 3x3 / stride 1 / pad 1 first convolution on a three-plane float batch: the boundary kernel
+                      * stages every pixel's 27 quantised neighbours as the channels of that pixel (taps outside the image: the
+                      * byte of 0.0), and the layer runs as a 1x1 convolution over them -- no gather, no border classes */
     int input_pad16; /* the network input is staged with 16 channels per pixel (zeros behind the real ones) for a stride-1
                       * first convolution, which then runs as a 16-channel convolution through the patch kernel */
     instance inst[8];
@@ -417,6 +420,7 @@ static int plan_gemm_group(planner *P, int i)
      * over 4*Cin channels.  Input row 2*oh - pad + r is block row oh + floor((r - pad)/2), phase (r - pad) mod 2. */
     const int s2d = E->input_s2d && n->in[0] == 0 && n->op == OP_CONV;
     const int pad16 = E->input_pad16 && n->in[0] == 0 && n->op == OP_CONV;  /* 16 stored channels, zeros behind the real ones */
+    const int neigh = E->input_neigh && n->in[0] == 0 && n->op == OP_CONV;  /* 27 neighbours per pixel: a 1x1 convolution */
     const int s2d_padH = (n->padH + 1) / 2, s2d_padW = (n->padW + 1) / 2;
     const int s2d_kH = (n->kH - 1 - n->padH) / 2 + s2d_padH + 1, s2d_kW = (n->kW - 1 - n->padW) / 2 + s2d_padW + 1;
 
@@ -444,6 +448,10 @@ static int plan_gemm_group(planner *P, int i)
         os.C = n->Cout;
         os.H = (is.H - 1) * n->dH - 2 * n->padH + n->kH + n->adjH;
         os.W = (is.W - 1) * n->dW - 2 * n->padW + n->kW + n->adjW;
+    } else if (neigh) {
+        os.C = n->Cout;  /* same spatial size (3x3, pad 1, stride 1) */
+        Cin = 27;
+        kH = kW = 1;
     } else if (s2d) {
         /* the logical input is still [N, Cin, 2H', 2W']: output size from the original geometry */
         os.C = n->Cout;
@@ -663,6 +671,7 @@ static int plan_gemm_group(planner *P, int i)
     d->N = is.N; d->H = H; d->W = W; d->Cin = Cin; d->in_ld = in_ld;
     d->in_row_pitch = in->row_pitch; d->in_pad_left = in->pad_left;
     d->kH = kH; d->kW = kW; d->dH = n->dH; d->dW = n->dW; d->padH = n->padH; d->padW = n->padW;
+    if (neigh) d->padH = d->padW = 0;
     d->self_coef = 1.f; d->res_coef = 0.f; d->relu_thr = -1;
     int Cp_out = ru(n->Cout, al);
     float *w_oihw = n->weight, *w_tmp = 0;
@@ -716,6 +725,17 @@ static int plan_gemm_group(planner *P, int i)
                         w_tmp[(((size_t)co * Cin + (ph * 2 + pw) * n->Cin + c) * kH + dh) * kW + dw] =
                             (w_fold ? w_fold : n->weight)[(((size_t)co * n->Cin + c) * n->kH + r) * n->kW + q];
                     }
+        w_oihw = w_tmp;
+    } else if (neigh) {
+        /* W'[co][(r*3 + s)*3 + c] = W[co][c][r][s]: the order the boundary kernel stores a pixel's neighbours in */
+        d->Cout = n->Cout; d->oH = os.H; d->oW = os.W;
+        const float *src = w_fold ? w_fold : n->weight;
+        w_tmp = calloc((size_t)n->Cout * 27, sizeof(float));
+        for (int co = 0; co < n->Cout; co++)
+            for (int c = 0; c < 3; c++)
+                for (int r = 0; r < 3; r++)
+                    for (int q = 0; q < 3; q++)
+                        w_tmp[(size_t)co * 27 + (r * 3 + q) * 3 + c] = src[(((size_t)co * 3 + c) * 3 + r) * 3 + q];
         w_oihw = w_tmp;
     } else if (pad16) {
         /* the same convolution over 16 input channels, the added ones with zero weights */
@@ -1415,6 +1435,17 @@ static int instance_build(thb_engine *E, instance *I, int device, int slice_off,
                          !(E->honour_pads && (c1->pad2H != c1->padH || c1->pad2W != c1->padW || c1->dlH > 1 || c1->dlW > 1 || c1->autopad || c1->refl_pad)) &&
                          !(off && atoi(off));
     }
+    {
+        /* uint8: a 3x3 / stride 1 / pad 1 first convolution on three planes of a float batch */
+        thb_node *c1 = M->nnodes > 1 ? &M->nodes[1] : 0;
+        const char *off = getenv("THB200_NO_NEIGH_U8");
+        E->input_neigh = E->dtype == THB_U8 && !E->input_s2d && E->cp == 0 && E->C == 3 && E->rank == 4 && c1 && c1->op == OP_CONV &&
+                         c1->in[0] == 0 && P.uses[0] == 1 && c1->Cin == 3 && c1->kH == 3 && c1->kW == 3 && c1->dH == 1 && c1->dW == 1 &&
+                         c1->padH == 1 && c1->padW == 1 &&
+                         !(E->honour_pads && (c1->pad2H != c1->padH || c1->pad2W != c1->padW || c1->dlH > 1 || c1->dlW > 1 || c1->autopad || c1->refl_pad)) &&
+                         !(off && atoi(off));
+        if (E->input_neigh) in.C = 27;
+    }
     materialise(&P, &P.val[0], in);
     if (E->input_pad16) {
         value *v = &P.val[0];
@@ -1907,7 +1938,10 @@ static int boundary_in(thb_engine *E, instance *I, int has_x, int inplace, int c
 {
     int rc;
     void *in_ptr = bufptr(I, I->in_val.buf, 0, E->dtype);
-    if (has_x && E->input_s2d && E->dtype == THB_U8)
+    if (has_x && E->input_neigh)
+        rc = thb_preprocess_neigh_u8(I->d_in, inplace ? I->d_in : 0, I->slice_n, H, W, mean, std, in_ptr, I->in_val.ld, q_sub, q_mult,
+                                     I->stream);
+    else if (has_x && E->input_s2d && E->dtype == THB_U8)
         rc = thb_preprocess_s2d_u8(I->d_in, inplace ? I->d_in : 0, I->slice_n, C, H, W, mean, std, in_ptr, I->in_val.ld, q_sub,
                                    q_mult, I->stream);
     else if (has_x && E->input_s2d)

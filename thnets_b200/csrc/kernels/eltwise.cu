@@ -210,6 +210,49 @@ __global__ void preprocess_s2d_kernel(const float *x, float *x_inplace, int N, i
     }
 }
 
+// uint8 engine, 3x3 / stride 1 / pad 1 first convolution on a three-plane float batch: every pixel's 27 neighbours,
+// normalised and quantised as preprocess_kernel does, become the channels of that pixel of an [N][H][W][32] byte tensor
+// (channel (r*3 + s)*3 + c = plane c of pixel (h - 1 + r, w - 1 + s)); neighbours outside the image hold the byte that 0.0
+// quantises to -- with the input zero point b_offset = roundf(q_min * q_mult) of the convolution (lowp_basic.c:15-29) such a
+// byte plus b_offset is exactly 0, so the tap contributes nothing, as in the reference, which never visits it.  The layer
+// is then a 1x1 convolution over 27 channels.  The in-place side effect writes each pixel once, as the centre tap.
+__global__ void preprocess_neigh_u8_kernel(const float *x, float *x_inplace, int N, int H, int W, float3 mean, float3 std_,
+                                           uint8_t *y, int y_ld, float q_min, float q_mult)
+{
+    const long pix = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long HW = (long)H * W;
+    if (pix >= (long)N * HW) return;
+    const long n = pix / HW;
+    const int hw = (int)(pix - n * HW), h = hw / W, w = hw - h * W;
+    const float m[3] = {mean.x, mean.y, mean.z}, sd[3] = {std_.x, std_.y, std_.z};
+    const float zr = roundf(q_min * q_mult);
+    const uint32_t zp = (uint32_t)(-(int)zr) & 255u;
+    uint32_t words[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int r = 0; r < 3; r++)
+#pragma unroll
+        for (int q = 0; q < 3; q++) {
+            const int ih = h - 1 + r, iw = w - 1 + q;
+            const bool inside = (unsigned)ih < (unsigned)H && (unsigned)iw < (unsigned)W;
+#pragma unroll
+            for (int c = 0; c < 3; c++) {
+                const int k = (r * 3 + q) * 3 + c;
+                uint32_t byte = zp;
+                if (inside) {
+                    const long idx = (n * 3 + c) * HW + (long)ih * W + iw;
+                    float val = __fdiv_rn(__fsub_rn(x[idx], m[c]), sd[c]);
+                    if (x_inplace && r == 1 && q == 1) x_inplace[idx] = val;
+                    byte = (uint32_t)(((int)(roundf(val * q_mult) - zr)) & 255);
+                }
+                words[k >> 2] |= byte << (8 * (k & 3));
+            }
+        }
+    uint4 *dst = reinterpret_cast<uint4 *>(y + pix * y_ld);
+    dst[0] = make_uint4(words[0], words[1], words[2], words[3]);
+    dst[1] = make_uint4(words[4], words[5], words[6], words[7]);
+    for (int c0 = 32; c0 < y_ld; c0 += 16) *reinterpret_cast<uint4 *>(y + pix * y_ld + c0) = make_uint4(0, 0, 0, 0);
+}
+
 // u8 HWC images -> normalised NHWC T (thapi.c:20-46: multiply by 0.003921568f and by 1/std)
 template <typename T>
 __global__ void preprocess_images_kernel(const uint8_t *img, int N, int H, int W, int stride, int cp, int bgr, float3 mean,
@@ -811,6 +854,17 @@ int thb_preprocess_s2d_u8(const float *x, float *x_inplace, int N, int C, int H,
     preprocess_s2d_kernel<uint8_t><<<nblocks(pix), 256, 0, (cudaStream_t)s>>>(x, x_inplace, N, C, H, W, m, sd, (uint8_t *)y, y_ld,
                                                                               W / 2, 0, q_sub, q_mult);
     return THB_LAUNCH_CHECK("preprocess_s2d_kernel<u8>");
+}
+
+int thb_preprocess_neigh_u8(const float *x, float *x_inplace, int N, int H, int W, const float *mean3, const float *std3, void *y,
+                            int y_ld, float q_sub, float q_mult, thb_stream s)
+{
+    if (y_ld < 32 || y_ld % 16) return THB_ERR_ARG;
+    const long pix = (long)N * H * W;
+    if (pix == 0) return THB_OK;
+    float3 m = make_float3(mean3[0], mean3[1], mean3[2]), sd = make_float3(std3[0], std3[1], std3[2]);
+    preprocess_neigh_u8_kernel<<<nblocks(pix), 256, 0, (cudaStream_t)s>>>(x, x_inplace, N, H, W, m, sd, (uint8_t *)y, y_ld, q_sub, q_mult);
+    return THB_LAUNCH_CHECK("preprocess_neigh_u8_kernel");
 }
 
 int thb_preprocess_s2d(const float *x, float *x_inplace, int N, int C, int H, int W, const float *mean3,
