@@ -330,6 +330,29 @@ def test_lowp_first_layer_staged_as_neighbourhoods(th, oracle, tmp_path, monkeyp
     assert np.array_equal(bufs[0], bufs[1])
 
 
+def test_split_reductions_on_request(th, oracle, tmp_path, monkeypatch):
+    """THB200_SPLITK=1: few-tile layers of the 16-bit engines (here every layer of a small-batch VGG and its Linear layers)
+    share their reductions among CTAs.  Within tolerance of the oracle and of the default plan; off by default because a
+    sharded batch would no longer reproduce the whole batch bit for bit."""
+    g = fx.vgg16(width=0.5, size=32, classes=10, fc=256)
+    x = g.make_input(4)
+    ref = oracle.run(g, x).ravel()
+    outs, launches = [], []
+    for on in ("0", "1"):
+        monkeypatch.setenv("THB200_SPLITK", on)
+        hc = _convert(th, g, "t7", tmp_path, "vggsk" + on, 1)
+        th.process_float(hc, x)
+        n0 = th.lib.THB200_KernelLaunches()
+        monkeypatch.setenv("THB200_NO_GRAPH", "1")
+        out = th.process_float(hc, x)[0]
+        launches.append(th.lib.THB200_KernelLaunches() - n0)
+        th.free_network(hc)
+        assert rel_err(out, ref) < 1e-2
+        outs.append(out)
+    assert launches[1] > launches[0], launches           # the finishing launches of the split layers
+    assert rel_err(outs[1], outs[0]) < 5e-3
+
+
 def test_process_yuyv(th, oracle, tmp_path):
     """THProcessYUYV (thapi.c:575-612): the frame is converted on the GPU with the reference's integer tables; a network
     as loaded takes it, a converted one refuses it as the reference's converted networks do."""

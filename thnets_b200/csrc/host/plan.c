@@ -790,7 +790,13 @@ static int plan_gemm_group(planner *P, int i)
         thb_conv_geometry(d);
     }
     if (dual_conv < 0 && in_ld < d->Cin_pad) { free(w_tmp); thb_set_error("internal: input stride %d below padded channels %d", in_ld, d->Cin_pad); return -1; }
-    if (is_linear && (dtype == THB_F16 || dtype == THB_BF16) && d->BN < 128 && d->Cout >= 128) {
+    /* Splitting a reduction over CTAs changes the order in which its fp32 partial sums are added, and whether a layer is
+     * split depends on how many tiles the (sub-)batch gives it: with it, a batch sharded over GPUs or cut into sub-batches
+     * no longer reproduces the whole batch bit for bit.  That identity is worth more than the few-tile layers' time, so
+     * the 16-bit engines split only on request (THB200_SPLITK=1). */
+    const char *ske = getenv("THB200_SPLITK");
+    const int want_split = ske && atoi(ske);
+    if (want_split && is_linear && (dtype == THB_F16 || dtype == THB_BF16) && d->BN < 128 && d->Cout >= 128) {
         /* A Linear on a batch of rows is a handful of tiles with a very long reduction.  The geometry rule narrows its tiles
          * so that more SMs get a share of the weights; where the reduction can be split over CTAs instead, wide tiles
          * move four times the weight bytes per barrier round (25088 -> 4096 on 32 rows: 135 -> about 40 us). */
@@ -802,7 +808,7 @@ static int plan_gemm_group(planner *P, int i)
             thb_conv_geometry(d);
         }
     }
-    if (pool < 0 && dual_conv < 0 && (dtype == THB_F16 || dtype == THB_BF16) && !thb_conv_patch_supported(d)) {
+    if (want_split && pool < 0 && dual_conv < 0 && (dtype == THB_F16 || dtype == THB_BF16) && !thb_conv_patch_supported(d)) {
         /* a launch of few tiles: several CTAs share each tile's reduction, through an fp32 scratch that lives for this launch */
         size_t sk_bytes = 0;
         const int S = thb_conv_splitk_plan(d, &sk_bytes);
