@@ -73,7 +73,9 @@ typedef struct thb_conv_desc {
     int N, H, W, Cin, in_ld;
     int Cout, kH, kW, dH, dW, padH, padW, oH, oW, out_ld;
     /* fp epilogue */
-    const float *scale, *shift; /* NULL: 1 / 0 */
+    const float *scale, *shift; /* NULL: 1 / 0.  Device arrays of Cout floats ROUNDED UP TO A MULTIPLE OF 64 (the kernels read them
+                                 * in 16-byte groups and per 64-column block; the values behind Cout are ignored); the same
+                                 * holds for act.slope.  (wsat and bias_add are read with clamped indices: Cout entries.) */
     const void *res;            /* NULL: none; same dtype and spatial shape as the output */
     int res_ld;
     float self_coef, res_coef;
