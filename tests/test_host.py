@@ -307,6 +307,41 @@ def test_static_scratch_entry_validates_before_any_launch():
     assert lib.thb_conv_u8_fwd_static(None, fake, fake, None) == ARG
 
 
+def test_split_plan_is_for_launches_that_leave_the_machine_idle():
+    """thb_conv_splitk_plan (host arithmetic only; without a device it assumes 148 SMs): a handful of tiles with a long
+    reduction is split so that the units fill the machine, with at least four K blocks per part and a bounded scratch;
+    launches of a wave or more, short reductions, narrow tiles, the uint8 type and two-operand convolutions are not."""
+    from thnets_b200 import kernels_abi as K
+    lib = K.load()
+    lib.thb_conv_splitk_plan.argtypes = [C.c_void_p, C.POINTER(C.c_size_t)]
+
+    def plan(n, cin, hw, cout, k, dtype=K.THB_F16, **kw):
+        d = K.ConvDesc()
+        d.dtype = dtype
+        d.N, d.H, d.W, d.Cin, d.Cout = n, hw, hw, cin, cout
+        d.kH = d.kW = k
+        d.dH = d.dW = 1
+        d.padH = d.padW = k // 2
+        d.oH = d.oW = hw
+        d.in_ld = cin
+        assert lib.thb_conv_geometry(C.byref(d)) == 0
+        for key, v in kw.items():
+            setattr(d, key, v)
+        nbytes = C.c_size_t(0)
+        return lib.thb_conv_splitk_plan(C.byref(d), C.byref(nbytes)), nbytes.value, d
+
+    s, nbytes, d = plan(1, 512, 7, 512, 3)                 # 1 pixel tile x 4 column tiles, 72 K blocks
+    assert 2 <= s <= 8 and d.Ktot_pad // 64 // s >= 4
+    assert nbytes == s * 49 * d.Cout_pad * 4
+    assert plan(32, 25088, 1, 4096, 1, BN=128)[0] >= 2    # a Linear on 32 rows with wide tiles
+    assert plan(256, 256, 14, 256, 3)[0] == 1             # 392 tiles: more than a wave
+    assert plan(64, 256, 14, 256, 3)[0] == 1              # 196 tiles: the partial sums would cost more than they save
+    assert plan(1, 64, 7, 512, 1)[0] == 1                 # one K block
+    assert plan(1, 512, 7, 32, 3)[0] == 1                 # 32-column tiles have no split form
+    assert plan(1, 512, 7, 512, 3, dtype=K.THB_U8)[0] == 1
+    assert plan(1, 512, 7, 512, 3, x2=1 << 20)[0] == 1
+
+
 def test_loaders_accept_the_remaining_operators(th, tmp_path):
     """SpatialZeroPadding / SpatialMaxUnpooling (with its reference to the pooling module) / LogSoftMax / Normalize from
     Torch7 files, Cmax / Slice from a graph dump, Upsample / Max / Slice / LogSoftmax from ONNX: loaded and lowered."""
