@@ -342,6 +342,51 @@ def test_split_plan_is_for_launches_that_leave_the_machine_idle():
     assert plan(1, 512, 7, 512, 3, x2=1 << 20)[0] == 1
 
 
+def test_patch_kernel_eligibility_rules():
+    """thb_conv_patch_supported / thb_conv_maxpool_supported decide on the host which convolutions the patch kernel takes:
+    16-bit types, stride 1, at most 64 output channels on 64-column tiles, 16 or 64 stored input channels, kernels up to
+    8 x 8 whose weights fit in shared memory; a fused residual needs +-1 for the convolution's own term and has no pooled
+    form; pooling windows of 2 or 3 with stride 2."""
+    from thnets_b200 import kernels_abi as K
+    lib = K.load()
+    lib.thb_conv_patch_supported.argtypes = [C.c_void_p]
+    lib.thb_conv_maxpool_supported.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
+
+    def desc(cin=64, cout=64, k=3, stride=1, hw=56, dtype=K.THB_F16, **kw):
+        d = K.ConvDesc()
+        d.dtype = dtype
+        d.N, d.H, d.W, d.Cin, d.Cout = 4, hw, hw, cin, cout
+        d.kH = d.kW = k
+        d.dH = d.dW = stride
+        d.padH = d.padW = k // 2
+        d.oH = d.oW = (hw + 2 * (k // 2) - k) // stride + 1
+        d.in_ld = max(cin, 8)
+        d.BN = 64 if cout <= 64 else 0
+        assert lib.thb_conv_geometry(C.byref(d)) == 0
+        for key, v in kw.items():
+            setattr(d, key, v)
+        return d
+
+    ok = lambda d: lib.thb_conv_patch_supported(C.byref(d))
+    assert ok(desc()) == 1
+    assert ok(desc(cin=16, cout=24, k=5)) == 1
+    assert ok(desc(dtype=K.THB_BF16)) == 1
+    assert ok(desc(res=1 << 20, res_ld=64, self_coef=1.0, res_coef=-1.0)) == 1
+    assert ok(desc(res=1 << 20, res_ld=64, self_coef=0.5, res_coef=1.0)) == 0
+    assert ok(desc(res=(1 << 20) + 8, res_ld=64, self_coef=1.0, res_coef=1.0)) == 0
+    assert ok(desc(cout=128)) == 0
+    assert ok(desc(stride=2)) == 0
+    assert ok(desc(cin=32)) == 0
+    assert ok(desc(dtype=K.THB_U8, cin=64)) == 0
+    assert ok(desc(cin=64, k=7)) == 0                      # 49 x 64 x 128 bytes of weights do not fit
+    d = desc()
+    assert lib.thb_conv_maxpool_supported(C.byref(d), 3, 2, 1) == 1
+    assert lib.thb_conv_maxpool_supported(C.byref(d), 2, 2, 0) == 1
+    assert lib.thb_conv_maxpool_supported(C.byref(d), 3, 1, 1) == 0
+    assert lib.thb_conv_maxpool_supported(C.byref(d), 4, 2, 0) == 0
+    assert lib.thb_conv_maxpool_supported(C.byref(desc(res=1 << 20, res_ld=64, self_coef=1.0, res_coef=1.0)), 3, 2, 1) == 0
+
+
 def test_loaders_accept_the_remaining_operators(th, tmp_path):
     """SpatialZeroPadding / SpatialMaxUnpooling (with its reference to the pooling module) / LogSoftMax / Normalize from
     Torch7 files, Cmax / Slice from a graph dump, Upsample / Max / Slice / LogSoftmax from ONNX: loaded and lowered."""
