@@ -2091,11 +2091,16 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
                     const size_t bytes = (size_t)I->slice_n * img_elems * sizeof(float);
                     const float *src = x + (size_t)I->slice_off * img_elems;
                     if (staged) {
-                        float *st = E->h_stage + (size_t)I->slice_off * img_elems;
-                        parallel_copy(st, src, bytes);
-                        src = st;
-                    }
-                    CU(cudaMemcpyAsync(I->d_in, src, bytes, cudaMemcpyHostToDevice, I->stream));
+                        /* in pieces of 16 MB: the copy to the device of one piece runs while the host threads fill the next */
+                        char *st = (char *)(E->h_stage + (size_t)I->slice_off * img_elems);
+                        const size_t piece = (size_t)16 << 20;
+                        for (size_t o = 0; o < bytes; o += piece) {
+                            const size_t nb = bytes - o < piece ? bytes - o : piece;
+                            parallel_copy(st + o, (const char *)src + o, nb);
+                            CU(cudaMemcpyAsync((char *)I->d_in + o, st + o, nb, cudaMemcpyHostToDevice, I->stream));
+                        }
+                    } else
+                        CU(cudaMemcpyAsync(I->d_in, src, bytes, cudaMemcpyHostToDevice, I->stream));
                 } else if ((size_t)stride == (size_t)W * cp) {
                     /* tightly packed rows: one copy per run of images that also follow one another in host memory */
                     const size_t img_bytes = (size_t)H * W * cp;
