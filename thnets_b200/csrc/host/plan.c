@@ -110,6 +110,9 @@ typedef struct instance {
     int device, slice_n, slice_off;
     cudaStream_t stream;
     cudaEvent_t ev0, ev1;
+    cudaStream_t wb_stream; /* carries the copy of the normalised input back to the caller, beside the forward (made on first use) */
+    cudaEvent_t ev_wb;
+    int wb_pending;
     void **allocs;
     int nallocs, capallocs;
     void **hostmem; /* host arrays the launches' descriptors point to */
@@ -1380,6 +1383,8 @@ static void instance_free(instance *I)
     if (I->graph) cudaGraphExecDestroy(I->graph);
     if (I->ev0) cudaEventDestroy(I->ev0);
     if (I->ev1) cudaEventDestroy(I->ev1);
+    if (I->ev_wb) cudaEventDestroy(I->ev_wb);
+    if (I->wb_stream) cudaStreamDestroy(I->wb_stream);
     if (I->stream) cudaStreamDestroy(I->stream);
     free(I->allocs); free(I->steps); free(I->bufs);
     memset(I, 0, sizeof(*I));
@@ -1992,8 +1997,18 @@ static int device_forward(thb_engine *E, instance *I, int has_x, int inplace, in
                           const float *mean, const float *std, float q_sub, float q_mult, float *writeback, float *dst)
 {
     if (boundary_in(E, I, has_x, inplace, cp, bgr, C, H, W, mean, std, q_sub, q_mult)) return -1;
-    if (writeback)
-        CU(cudaMemcpyAsync(writeback, I->d_in, (size_t)I->slice_n * C * H * W * sizeof(float), cudaMemcpyDeviceToHost, I->stream));
+    if (writeback) {
+        /* the normalised values go back to the caller on a stream of their own: the link is full duplex and the forward does
+         * not wait for them (the caller does, before THProcessFloat returns) */
+        if (!I->wb_stream) {
+            CU(cudaStreamCreateWithFlags(&I->wb_stream, cudaStreamNonBlocking));
+            CU(cudaEventCreateWithFlags(&I->ev_wb, cudaEventDisableTiming));
+        }
+        CU(cudaEventRecord(I->ev_wb, I->stream));
+        CU(cudaStreamWaitEvent(I->wb_stream, I->ev_wb, 0));
+        CU(cudaMemcpyAsync(writeback, I->d_in, (size_t)I->slice_n * C * H * W * sizeof(float), cudaMemcpyDeviceToHost, I->wb_stream));
+        I->wb_pending = 1;
+    }
     CU(cudaEventRecord(I->ev0, I->stream));
     if (run_steps(E, I)) return -1;
     return boundary_out(E, I, dst);
@@ -2017,6 +2032,29 @@ static void parallel_copy(void *dst, const void *src, size_t bytes)
     for (long b = 0; b < nb; b++) {
         const size_t o = (size_t)b * blk;
         memcpy((char *)dst + o, (const char *)src + o, bytes - o < blk ? bytes - o : blk);
+    }
+}
+
+/* The same for planes [p0, p1) of an NCHW float batch (plane p = image p / C, channel p % C, HW floats), normalising the
+ * first three channels on the way exactly as the boundary kernels do -- (x - mean) / std, a subtraction and a division in
+ * fp32 -- and writing the normalised values back over the caller's planes: THProcessFloat's in-place side effect
+ * (thapi.c:396-403) done where the reference does it, on the host, instead of a 12-bytes-per-pixel copy back from the
+ * device. */
+static void stage_planes_normalised(float *dst, float *src, long p0, long p1, int C, long HW, const float *mean, const float *std)
+{
+#pragma omp parallel for schedule(static)
+    for (long p = p0; p < p1; p++) {
+        const int c = (int)(p % C);
+        float *s = src + p * HW, *d = dst + p * HW;
+        if (c < 3) {
+            const float m = mean[c], sd = std[c];
+            for (long i = 0; i < HW; i++) {
+                const float v = (s[i] - m) / sd;
+                s[i] = v;
+                d[i] = v;
+            }
+        } else
+            memcpy(d, s, (size_t)HW * sizeof(float));
     }
 }
 
@@ -2070,6 +2108,12 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
             if (!E->h_stage) { E->h_stage_bytes = 0; staged = 0; }
         }
     }
+    /* A staged float batch that is to be normalised in place is normalised by the host threads while they stage it: the
+     * device then gets normalised values (identity statistics from here on) and copies nothing back. */
+    static const float zero3[3] = {0, 0, 0}, one3[3] = {1, 1, 1};
+    const float *host_mean = mean, *host_std = std;
+    const int host_norm = staged && x && inplace;
+    if (host_norm) { mean = zero3; std = one3; inplace = 0; }
     /* what the device-resident timing loop needs to repeat this forward from the staged input */
     E->last_has_x = x != 0; E->last_cp = cp; E->last_bgr = bgr;
     for (int k = 0; k < 3; k++) { E->last_mean[k] = mean[k]; E->last_std[k] = std[k]; }
@@ -2091,13 +2135,19 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
                     const size_t bytes = (size_t)I->slice_n * img_elems * sizeof(float);
                     const float *src = x + (size_t)I->slice_off * img_elems;
                     if (staged) {
-                        /* in pieces of 16 MB: the copy to the device of one piece runs while the host threads fill the next */
-                        char *st = (char *)(E->h_stage + (size_t)I->slice_off * img_elems);
-                        const size_t piece = (size_t)16 << 20;
-                        for (size_t o = 0; o < bytes; o += piece) {
-                            const size_t nb = bytes - o < piece ? bytes - o : piece;
-                            parallel_copy(st + o, (const char *)src + o, nb);
-                            CU(cudaMemcpyAsync((char *)I->d_in + o, st + o, nb, cudaMemcpyHostToDevice, I->stream));
+                        /* in pieces of about 16 MB (whole planes): the copy to the device of one piece runs while the host
+                         * threads fill the next */
+                        float *st = E->h_stage + (size_t)I->slice_off * img_elems;
+                        float *xs = x + (size_t)I->slice_off * img_elems;
+                        const long HW = (long)H * W, planes = (long)I->slice_n * C;
+                        long per_piece = (((long)16 << 20) / (long)sizeof(float)) / HW;
+                        if (per_piece < 1) per_piece = 1;
+                        for (long p0 = 0; p0 < planes; p0 += per_piece) {
+                            const long p1 = p0 + per_piece < planes ? p0 + per_piece : planes;
+                            const size_t o = (size_t)p0 * HW, cnt = (size_t)(p1 - p0) * HW;
+                            if (host_norm) stage_planes_normalised(st, xs, p0, p1, C, HW, host_mean, host_std);
+                            else parallel_copy(st + o, xs + o, cnt * sizeof(float));
+                            CU(cudaMemcpyAsync(I->d_in + o, st + o, cnt * sizeof(float), cudaMemcpyHostToDevice, I->stream));
                         }
                     } else
                         CU(cudaMemcpyAsync(I->d_in, src, bytes, cudaMemcpyHostToDevice, I->stream));
@@ -2144,6 +2194,10 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
         if (g == 0 && gather)
             CU(cudaMemcpyAsync(E->h_out, gather, (size_t)total * sizeof(float), cudaMemcpyDeviceToHost, I->stream));
         CU(cudaStreamSynchronize(I->stream));
+        if (I->wb_pending) {
+            CU(cudaStreamSynchronize(I->wb_stream));
+            I->wb_pending = 0;
+        }
         float ms = 0;
         cudaEventElapsedTime(&ms, I->ev0, I->ev1);
         I->last_ms = ms;
