@@ -434,6 +434,25 @@ def test_graph_replay_matches_direct_launches(th, tmp_path):
     th.free_network(hc)
 
 
+def test_lowp_graph_replay_follows_the_input_range(th, oracle, tmp_path):
+    """The uint8 engine measures the input's quantisation per batch (lowp_basic.c:299-321): the convolutions that read
+    the network input are launched directly with that batch's parameters and only the launches after them are replayed
+    from the graph.  Batches of different ranges, one after the other through the same network: every result equals the
+    oracle's for that batch."""
+    size, rng = 64, 20.0
+    g = fx.resnet50(width=0.125, size=size, classes=10, fc_bias=0.05)
+    h = _load(th, g, "py", tmp_path, "r50lg")
+    hl = th.create_lowp_network(h, rng)
+    th.free_network(h)
+    x0 = g.make_input(3)
+    for k, gain in enumerate([1.0, 0.37, 2.5, 1.0, 0.05]):      # 1st: direct; 2nd: captured; then replays
+        x = (x0 * gain + 0.1 * k).astype(np.float32)
+        ref = oracle.run_lowp(g, x, rng, size)
+        out, _, _ = th.process_float(hl, x.copy())
+        assert np.array_equal(out, ref.ravel()), (k, np.abs(out - ref.ravel()).max())
+    th.free_network(hl)
+
+
 def test_batch_sharded_over_two_gpus(th, oracle, tmp_path):
     import torch
     if torch.cuda.device_count() < 2:

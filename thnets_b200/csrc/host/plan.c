@@ -137,6 +137,8 @@ typedef struct instance {
      * which also sets every kernel's attributes), replayed with a single launch afterwards */
     cudaGraphExec_t graph;
     int runs, graph_state; /* graph_state: 0 not tried, 1 usable, -1 capture failed or switched off */
+    int graph_from;        /* first launch inside the graph (the ones before it are issued directly every forward) */
+    int graph_launches;    /* kernel launches one replay stands for */
 } instance;
 
 struct thb_engine {
@@ -1515,10 +1517,10 @@ static void *bufptr(instance *I, int buf, int coff, int dtype)
     return buf < 0 ? 0 : I->arena + I->bufs[buf].offset + (size_t)coff * esize_of(dtype);
 }
 
-static int run_steps_ev(thb_engine *E, instance *I, cudaEvent_t *evs)
+static int run_steps_ev(thb_engine *E, instance *I, cudaEvent_t *evs, int from, int to)
 {
     thb_stream st = I->stream;
-    for (int t = 0; t < I->nsteps; t++) {
+    for (int t = from; t < to; t++) {
         step *s = &I->steps[t];
         const int dt = s->dtype;
         void *x0 = bufptr(I, s->in_buf[0], s->in_coff[0], dt);
@@ -1650,17 +1652,25 @@ static int run_steps_ev(thb_engine *E, instance *I, cudaEvent_t *evs)
 }
 
 /* The launches of one forward on the instance's stream: directly the first time, from then on as a replay of the
- * graph captured from them.  The uint8 engine changes kernel arguments every forward (dynamic input quantisation), so
- * it always launches directly; so does THB200_NO_GRAPH=1 and the per-module profile mode. */
+ * graph captured from them.  In the uint8 engine the convolutions that read the network input take kernel arguments
+ * that change every forward (the input's quantisation is measured per batch, lowp_basic.c:299-321): the launches up to
+ * and including the last of them are always issued directly and the graph holds the rest.  THB200_NO_GRAPH=1 and the
+ * per-module profile mode launch everything directly. */
 static int run_steps(thb_engine *E, instance *I)
 {
     if (I->graph_state == 0 && I->runs >= 1) {
         const char *ng = getenv("THB200_NO_GRAPH");
         I->graph_state = -1;
-        if (E->dtype != THB_U8 && !(ng && atoi(ng)) && !th_profile && !th_minmax) {
+        I->graph_from = 0;
+        for (int t = 0; t < I->nsteps; t++)
+            if (I->steps[t].kind == ST_CONV && I->steps[t].dyn_quant) I->graph_from = t + 1;
+        if (I->graph_from < I->nsteps && !(ng && atoi(ng)) && !th_profile && !th_minmax) {
             cudaGraph_t g = 0;
             if (cudaStreamBeginCapture(I->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
-                const int rc = run_steps_ev(E, I, 0);
+                const int l0 = thb_kernel_launch_count();
+                const int rc = run_steps_ev(E, I, 0, I->graph_from, I->nsteps);
+                I->graph_launches = thb_kernel_launch_count() - l0; /* kernels in the graph (its memset nodes are not launches) */
+                thb_count_launches(-I->graph_launches);             /* they have not run yet: the replay below counts them */
                 const cudaError_t ce = cudaStreamEndCapture(I->stream, &g);
                 if (!rc && ce == cudaSuccess && g && cudaGraphInstantiate(&I->graph, g, 0) == cudaSuccess) I->graph_state = 1;
                 if (g) cudaGraphDestroy(g);
@@ -1670,14 +1680,15 @@ static int run_steps(thb_engine *E, instance *I)
     }
     I->runs++;
     if (I->graph_state == 1 && !th_profile && !th_minmax) {
+        if (I->graph_from && run_steps_ev(E, I, 0, 0, I->graph_from)) return -1;
         if (cudaGraphLaunch(I->graph, I->stream) == cudaSuccess) {
-            thb_count_launches(I->nsteps);
+            thb_count_launches(I->graph_launches);
             return 0;
         }
         thb_set_error("graph launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         return -1;
     }
-    return run_steps_ev(E, I, 0);
+    return run_steps_ev(E, I, 0, 0, I->nsteps);
 }
 
 static int lowp_input_range(thb_engine *E, instance *set, int G, int has_x, int cp, int C, int H, int W, const float *mean,
@@ -1708,7 +1719,7 @@ int thb_engine_profile(thb_engine *E, int iters, int max_steps, int *kinds, floa
         cudaEventRecord(evs[0], I->stream);
         if (!rc) rc = boundary_in(E, I, E->last_has_x, 0, E->last_cp, E->last_bgr, E->C, E->H, E->W, E->last_mean, E->last_std, q_sub, q_mult);
         cudaEventRecord(evs[1], I->stream);
-        if (!rc) rc = run_steps_ev(E, I, evs + 1);
+        if (!rc) rc = run_steps_ev(E, I, evs + 1, 0, I->nsteps);
         if (!rc) rc = boundary_out(E, I, I->d_out);
         cudaEventRecord(evs[total], I->stream);
         if (cudaStreamSynchronize(I->stream) != cudaSuccess) rc = -1;
