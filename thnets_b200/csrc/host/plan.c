@@ -1896,12 +1896,14 @@ static int pipe_build(thb_engine *E, int S)
         for (int c = 0; c < S; c++) {
             int off, n;
             thb_slice_batch(E->inst[g].slice_n, S, c, &off, &n);
-            if (S == 2 && E->inst[g].slice_n >= 8) {
-                /* two sub-batches: a smaller first one (3/8) starts the kernels sooner, and the copy of the larger second
-                 * one still ends before they do (ResNet-50 batch 256: 96 + 160 images) */
-                const int first = (E->inst[g].slice_n * 3 + 4) / 8;
-                off = c ? first : 0;
-                n = c ? E->inst[g].slice_n - first : first;
+            if (S <= 4 && E->inst[g].slice_n >= 8 * S) {
+                /* growing sub-batches: a small first one starts the kernels sooner, and the copy of each later one still
+                 * ends before the kernels ahead of it do (ResNet-50 batch 256 in two: 96 + 160 images).  Boundaries in
+                 * sixteenths of the slice. */
+                static const int cut[5][5] = {{0}, {0, 16}, {0, 6, 16}, {0, 3, 8, 16}, {0, 2, 6, 11, 16}};
+                const int sn = E->inst[g].slice_n;
+                off = (sn * cut[S][c] + 8) / 16;
+                n = (sn * cut[S][c + 1] + 8) / 16 - off;
             }
             if (instance_build(E, &E->pipe[g * S + c], E->inst[g].device, E->inst[g].slice_off + off, n)) return -1;
         }
@@ -2132,6 +2134,9 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
     /* The uint8 engine needs the input range of the whole batch before any kernel can start: it stages every slice, then
      * measures, then launches.  The other modes launch a slice's kernels as soon as its copy is queued. */
     const int two_phase = E->dtype == THB_U8;
+    cudaEvent_t ev_call = 0;
+    if (th_debug > 1 && cudaSetDevice(set[0].device) == cudaSuccess && cudaEventCreate(&ev_call) == cudaSuccess)
+        cudaEventRecord(ev_call, set[0].stream);
     for (int phase = 0; phase < 2; phase++) {
         if (phase == 1) {
             if (!two_phase) break;
@@ -2211,6 +2216,13 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
         }
         float ms = 0;
         cudaEventElapsedTime(&ms, I->ev0, I->ev1);
+        if (ev_call && I->device == set[0].device) {
+            /* debug level 2: when each sub-batch's planned launches began and ended, from the start of the call */
+            float a = 0, b = 0;
+            cudaEventElapsedTime(&a, ev_call, I->ev0);
+            cudaEventElapsedTime(&b, ev_call, I->ev1);
+            fprintf(stderr, "thb200: sub-batch %d (%d images): launches from %.3f to %.3f ms\n", g, I->slice_n, a, b);
+        }
         I->last_ms = ms;
         if (ms > ms_max) ms_max = ms;
         int status = 0;
@@ -2222,6 +2234,7 @@ int thb_engine_forward(thb_engine *E, float *x, unsigned char **images, int stri
         }
     }
     E->last_ms = ms_max;
+    if (ev_call) cudaEventDestroy(ev_call);
 
     shape os = set[0].out_shape;
     res->data = E->h_out;
