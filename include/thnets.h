@@ -274,6 +274,8 @@ int THB200_ProfileForward(THNETWORK *network, int iters, int max_steps, int *kin
 int THB200_ProfileForwardBytes(THNETWORK *network, int max_steps, double *bytes);
 /* the contiguous slice [offset, offset+count) of an N-image batch that GPU g of G processes */
 void THB200_SliceBatch(int N, int G, int g, int *offset, int *count);
+/* sub-batch c of the S pipelined sub-batches that a GPU's slice of n images is cut into (THB200_SetPipelineChunks) */
+void THB200_SliceSubBatches(int n, int S, int c, int *offset, int *count);
 int THB200_KernelLaunches(void);
 /* one text line per operator of the lowered network; returns the length written, < 0 on error */
 int THB200_DescribeNetwork(THNETWORK *network, char *buf, int len);

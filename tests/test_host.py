@@ -267,6 +267,29 @@ def test_batch_slicing(th):
             assert covered == list(range(n))
 
 
+def test_sub_batch_slicing(th):
+    """Pipelined sub-batches cover a GPU's slice once, in order, none empty; up to four of them grow from first to last
+    (the first copy is short, each later copy ends under the kernels ahead of it)."""
+    off, cnt = C.c_int(), C.c_int()
+    for n in (1, 5, 16, 31, 32, 64, 250, 256):
+        for s in (1, 2, 3, 4):
+            if s > n:
+                continue
+            covered, sizes = [], []
+            for c in range(s):
+                th.lib.THB200_SliceSubBatches(n, s, c, C.byref(off), C.byref(cnt))
+                assert cnt.value >= 1
+                covered += list(range(off.value, off.value + cnt.value))
+                sizes.append(cnt.value)
+            assert covered == list(range(n)), (n, s, sizes)
+            if n >= 8 * s:
+                assert sizes == sorted(sizes), (n, s, sizes)
+    th.lib.THB200_SliceSubBatches(256, 2, 0, C.byref(off), C.byref(cnt))
+    assert (off.value, cnt.value) == (0, 96)
+    th.lib.THB200_SliceSubBatches(256, 4, 3, C.byref(off), C.byref(cnt))
+    assert (off.value, cnt.value) == (176, 80)
+
+
 def test_fixture_writers_round_trip_through_the_reference_formats(tmp_path):
     """the .t7 writer emits objects with strictly increasing indices and float tensors with 1-based offsets"""
     g = fx.vgg16(width=0.125, size=32, classes=10, fc=64)

@@ -517,5 +517,6 @@ int THB200_ProfileForwardBytes(THNETWORK *network, int max_steps, double *bytes)
     return thb_engine_profile_bytes(netx(network)->engine, max_steps, bytes);
 }
 void THB200_SliceBatch(int N, int G, int g, int *offset, int *count) { thb_slice_batch(N, G, g, offset, count); }
+void THB200_SliceSubBatches(int n, int S, int c, int *offset, int *count) { thb_slice_sub_batches(n, S, c, offset, count); }
 float THB200_LastDeviceMs(THNETWORK *network) { return thb_engine_last_ms(netx(network)->engine); }
 float THB200_TimeForward(THNETWORK *network, int iters) { return thb_engine_time_forward(netx(network)->engine, iters); }

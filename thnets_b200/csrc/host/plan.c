@@ -1826,6 +1826,21 @@ void thb_slice_batch(int N, int G, int g, int *offset, int *count)
     *offset = g * base + (g < extra ? g : extra);
 }
 
+/* The pipelined sub-batches of one GPU's slice of n images: sub-batch c of S.  Up to four of them grow from the first to
+ * the last: a small first one starts the kernels sooner, and the copy of each later one still ends before the kernels
+ * ahead of it do (ResNet-50 batch 256 in two: 96 + 160 images).  Boundaries in sixteenths of the slice; slices too small
+ * for that, and more than four sub-batches, are cut evenly. */
+void thb_slice_sub_batches(int n, int S, int c, int *offset, int *count)
+{
+    static const int cut[5][5] = {{0}, {0, 16}, {0, 6, 16}, {0, 3, 8, 16}, {0, 2, 6, 11, 16}};
+    if (S < 1 || S > 4 || n < 8 * S) {
+        thb_slice_batch(n, S < 1 ? 1 : S, c, offset, count);
+        return;
+    }
+    *offset = (n * cut[S][c] + 8) / 16;
+    *count = (n * cut[S][c + 1] + 8) / 16 - *offset;
+}
+
 static int engine_build(thb_engine *E, int N, int C, int H, int W, int rank, int cp)
 {
     for (int g = 0; g < 8; g++) instance_free(&E->inst[g]);
@@ -1895,16 +1910,7 @@ static int pipe_build(thb_engine *E, int S)
     for (int g = 0; g < G; g++)
         for (int c = 0; c < S; c++) {
             int off, n;
-            thb_slice_batch(E->inst[g].slice_n, S, c, &off, &n);
-            if (S <= 4 && E->inst[g].slice_n >= 8 * S) {
-                /* growing sub-batches: a small first one starts the kernels sooner, and the copy of each later one still
-                 * ends before the kernels ahead of it do (ResNet-50 batch 256 in two: 96 + 160 images).  Boundaries in
-                 * sixteenths of the slice. */
-                static const int cut[5][5] = {{0}, {0, 16}, {0, 6, 16}, {0, 3, 8, 16}, {0, 2, 6, 11, 16}};
-                const int sn = E->inst[g].slice_n;
-                off = (sn * cut[S][c] + 8) / 16;
-                n = (sn * cut[S][c + 1] + 8) / 16 - off;
-            }
+            thb_slice_sub_batches(E->inst[g].slice_n, S, c, &off, &n);
             if (instance_build(E, &E->pipe[g * S + c], E->inst[g].device, E->inst[g].slice_off + off, n)) return -1;
         }
     E->pipe_built = G * S;

@@ -91,6 +91,7 @@ float thb_engine_time_forward(thb_engine *e, int iters);
 int thb_engine_profile(thb_engine *e, int iters, int max_steps, int *kinds, float *ms, double *flops);
 int thb_engine_profile_bytes(thb_engine *e, int max_steps, double *bytes);
 void thb_slice_batch(int N, int G, int g, int *offset, int *count);
+void thb_slice_sub_batches(int n, int S, int c, int *offset, int *count);
 const char *thb_engine_error(void);
 void thb_set_error(const char *fmt, ...);
 
