@@ -249,6 +249,9 @@ int thb_reflect_pad(int dtype, const void *x, int N, int H, int W, int C, int x_
                     int y_ld, thb_stream s);
 /* channels [from, from + C) of every pixel of x -> y (modules/Slice.c:34-39 along the channel dimension, any `from`) */
 int thb_slice_channels(int dtype, const void *x, long pixels, int from, int C, int x_ld, void *y, int y_ld, thb_stream s);
+/* Reshape to three dimensions (modules/Reshape.c:22-36): row n of x (x_ld elements apart) holds C*H*W values in (channel,
+ * row, column) order; they become the channels-innermost map y[n][h][w][c] (fp32, fp16, bf16; padded channels 0) */
+int thb_from_nchw(int dtype, const void *x, int N, int H, int W, int C, int x_ld, void *y, int y_ld, thb_stream s);
 /* elementwise maximum of up to 8 tensors of one shape (modules/Cmax.c:20-68) */
 int thb_cmax(int dtype, int nin, const void *const *x_host, const int *ld_host, long pixels, int C, void *y, int y_ld, thb_stream s);
 /* log-softmax over the channels of each pixel (modules/LogSoftMax.c:19-81).  first_frame_quirk = 1 reproduces the

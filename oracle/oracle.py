@@ -331,6 +331,9 @@ class Oracle:
                 y = self.avgpool(x, a["kernel_size"], a["stride"], a["padding"], a["ceil_mode"])
             elif node.op == "view":
                 y = x.reshape(-1, a["sizes"][1])
+            elif node.op == "reshape":
+                # modules/Reshape.c:22-36: every image's elements, in order, as a [c, h, w] map
+                y = x.reshape(-1, *a["sizes"])
             elif node.op == "dropout":
                 y = x
             elif node.op == "softmax":

@@ -267,6 +267,18 @@ def test_batch_slicing(th):
             assert covered == list(range(n))
 
 
+def test_reshape_lowering(th, tmp_path):
+    """nn.Reshape to three dimensions lowers to an operator of its own with the target map; to one dimension it is a View"""
+    g = fx.reshape_net()
+    d = str(tmp_path / "reshape")
+    fx.write_torch7(g, d)
+    h = th.load_network(d)
+    lines = describe(th, h)
+    assert any(" reshape in=5 3x5x4" in ln for ln in lines), lines
+    assert lines[-1].startswith("7 conv in=6 3->6") and lines[-1].endswith("<- output")
+    th.free_network(h)
+
+
 def test_sub_batch_slicing(th):
     """Pipelined sub-batches cover a GPU's slice once, in order, none empty; up to four of them grow from first to last
     (the first copy is short, each later copy ends under the kernels ahead of it)."""

@@ -583,13 +583,17 @@ def test_lowp_first_convolution_15x15_stride_2(th, oracle, tmp_path):
                                   ("normalize_b1", lambda: fx.normalize_net(), "t7", 1, 0),
                                   ("normalize_b4", lambda: fx.normalize_net(), "t7", 4, 0),
                                   ("normalize_b4_fp16", lambda: fx.normalize_net(), "t7", 4, 1),
+                                  ("reshape_b1", lambda: fx.reshape_net(), "t7", 1, 0),
+                                  ("reshape_b3", lambda: fx.reshape_net(), "t7", 3, 0),
+                                  ("reshape_b3_fp16", lambda: fx.reshape_net(), "t7", 3, 1),
                                   ("cmax_slice_b4", lambda: fx.cmax_slice_net(), "py", 4, 0),
                                   ("cmax_slice_b4_fp16", lambda: fx.cmax_slice_net(), "py", 4, 1),
                                   ("onnx_ops_b3", lambda: fx.onnx_ops_net(), "onnx", 3, 0),
                                   ("onnx_ops_b1", lambda: fx.onnx_ops_net(), "onnx", 1, 0)], ids=lambda c: c[0])
 def test_remaining_operators(th, oracle, tmp_path, case):
     """SpatialZeroPadding, SpatialMaxUnpooling (positions recomputed from the pooling's input), LogSoftMax (with the
-    reference's first-frame quirk), Normalize, Cmax, Slice along every dimension and Upsample, through the three loaders,
+    reference's first-frame quirk), Normalize, Reshape to a [c, h, w] map (with and without a batch dimension), Cmax,
+    Slice along every dimension and Upsample, through the three loaders,
     against the oracle functions that are pinned to the live reference."""
     name, build, kind, batch, mode = case
     g = build()

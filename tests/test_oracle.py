@@ -209,6 +209,28 @@ def test_normalize_against_the_live_reference(oracle, tmp_path, batch):
     assert np.abs(out - ref.ravel()).max() / np.abs(ref).max() < 2e-5
 
 
+@pytest.mark.parametrize("batch", [1, 3])
+def test_reshape_against_the_live_reference(oracle, tmp_path, batch):
+    """nn.Reshape(c, h, w) after a Linear (modules/Reshape.c:22-36): one image gives a 3-D map (the tensor has exactly
+    `nelement` elements and its first dimension is not 1), a batch gives [batch, c, h, w]; the convolution behind it sees
+    the vector's elements in (channel, row, column) order either way."""
+    from oracle.oracle import ref_lib
+    from thnets_b200 import fixtures as fx
+    from thnets_b200.capi import THNets
+    if ref_lib() is None:
+        pytest.skip("reference library not built")
+    g = fx.reshape_net()
+    d = str(tmp_path / "reshape")
+    fx.write_torch7(g, d)
+    th = THNets(ref_lib())
+    h = th.load_network(d)
+    x = g.make_input(batch)
+    out, ow, oh = th.process_float(h, x)
+    ref = oracle.run(g, x)
+    assert (ow, oh) == (4, 5) and out.size == ref.size
+    assert np.abs(out - ref.ravel()).max() / np.abs(ref).max() < 2e-5
+
+
 def test_cmax_slice_against_the_live_reference(oracle, tmp_path):
     from oracle.oracle import ref_lib
     from thnets_b200 import fixtures as fx

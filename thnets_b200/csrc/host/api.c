@@ -479,7 +479,7 @@ int THB200_DescribeNetwork(THNETWORK *network, char *buf, int len)
 {
     static const char *names[] = {"input", "conv", "deconv", "linear", "bn", "act", "maxpool", "avgpool", "combine",
                                   "concat", "softmax", "view", "alias", "scale", "upsample", "zeropad", "slice", "cmax",
-                                  "logsoftmax", "normalize", "unpool"};
+                                  "logsoftmax", "normalize", "unpool", "reshape"};
     char err[256] = "";
     if (!buf || len < 2) return -1;
     thb_model *m = thb_model_from_network(network, err, sizeof(err));
@@ -502,6 +502,7 @@ int THB200_DescribeNetwork(THNETWORK *network, char *buf, int len)
         else if (n->op == OP_CONCAT) pos = describe_append(buf, len, pos, " dim=%d", n->dim);
         else if (n->op == OP_ZEROPAD) pos = describe_append(buf, len, pos, " l%d r%d t%d b%d", n->pad_l, n->pad_r, n->pad_t, n->pad_b);
         else if (n->op == OP_SLICE) pos = describe_append(buf, len, pos, " axis=%d [%d,%d)", n->slice_axis, n->slice_from, n->slice_to);
+        else if (n->op == OP_RESHAPE) pos = describe_append(buf, len, pos, " %dx%dx%d", n->reshape[0], n->reshape[1], n->reshape[2]);
         pos = describe_append(buf, len, pos, "%s\n", i == m->output ? " <- output" : "");
     }
     thb_model_release(m);

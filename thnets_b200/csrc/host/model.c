@@ -179,7 +179,14 @@ static int lower_leaf(builder *b, struct module *m, val in, val *out)
     case MT_Reshape:
         /* Reshape.c:22-36: to `size` without a batch dimension, or to `batchsize` with the input's batch in front; built
          * for a one-dimensional target (the flatten in front of a classifier), where it is what View does */
-        if (m->Reshape.nsize > 1) return fail(b, "Reshape to more than one dimension is not supported by the B200 engine");
+        if (m->Reshape.nsize == 3) {
+            n = new_node(b, OP_RESHAPE, 1, in.id);
+            n->numElements = m->Reshape.numElements;
+            n->batch_mode = m->Reshape.batchMode;
+            for (int k = 0; k < 3; k++) n->reshape[k] = (int)m->Reshape.size[k];
+            break;
+        }
+        if (m->Reshape.nsize > 1) return fail(b, "Reshape to two or four dimensions is not supported by the B200 engine");
         n = new_node(b, OP_VIEW, 1, in.id);
         n->numElements = m->Reshape.numElements;
         break;

@@ -74,7 +74,7 @@ typedef struct {
 
 enum step_kind {
     ST_CONV, ST_GEMV, ST_MAXPOOL, ST_AVGPOOL, ST_AFFINE, ST_U8THR, ST_U8COMBINE, ST_COMBINE, ST_COPY, ST_SOFTMAX, ST_COL2IM,
-    ST_CSUM, ST_TO_NCHW, ST_ZERO, ST_UPSAMPLE, ST_ZEROPAD, ST_REFLECTPAD, ST_SLICEC, ST_CMAX, ST_LOGSOFTMAX, ST_NORMALIZE, ST_UNPOOL
+    ST_CSUM, ST_TO_NCHW, ST_ZERO, ST_UPSAMPLE, ST_ZEROPAD, ST_REFLECTPAD, ST_SLICEC, ST_CMAX, ST_LOGSOFTMAX, ST_NORMALIZE, ST_UNPOOL, ST_FROM_NCHW
 };
 
 typedef struct {
@@ -1193,6 +1193,28 @@ static int plan_node(planner *P, int i)
         out->s.C = (int)per; out->s.H = out->s.W = 1;
         return 0;
     }
+    case OP_RESHAPE: {
+        /* Reshape.c:22-36: the elements of each image, in the reference's (channel, row, column) order, become a
+         * [C, H, W] map.  Without a batch dimension (3-D result) when batchMode is false, or absent while the tensor has
+         * exactly numElements elements and its first dimension is not 1; with the input's batch in front otherwise. */
+        if (dtype == THB_U8) { thb_set_error("Reshape is not supported in Lowp"); return -1; }
+        const int rC = n->reshape[0], rH = n->reshape[1], rW = n->reshape[2];
+        const long total = (long)in->s.N * in->s.C * in->s.H * in->s.W, per = (long)rC * rH * rW;
+        const int size0 = in->s.rank == 4 || in->s.rank == 2 ? in->s.N : in->s.C;
+        const int nonbatch = n->batch_mode == 0 || (n->batch_mode == -1 && total == n->numElements && size0 != 1);
+        if (rC < 1 || rH < 1 || rW < 1 || per != n->numElements || per * in->s.N != total || (nonbatch && in->s.N != 1)) {
+            thb_set_error("Reshape to %dx%dx%d does not fit %ld elements in %d image(s)", rC, rH, rW, total, in->s.N);
+            return -1;
+        }
+        if (in->s.flat || in->s.H * in->s.W != 1) { thb_set_error("Reshape of a spatial tensor to three dimensions is not supported"); return -1; }
+        shape os = in->s;
+        os.C = rC; os.H = rH; os.W = rW; os.rank = nonbatch ? 3 : 4;
+        materialise(P, out, os);
+        s = new_step(P, ST_FROM_NCHW);
+        step_in(s, in); step_out(s, out);
+        s->N = in->s.N; s->H = rH; s->W = rW; s->C = rC;
+        return 0;
+    }
     case OP_UPSAMPLE: {
         /* Upsample.c:18-63 */
         if (in->s.rank < 3 || in->s.flat) { thb_set_error("Only 3D and 4D input is supported"); return -1; }
@@ -1587,6 +1609,9 @@ static int run_steps_ev(thb_engine *E, instance *I, cudaEvent_t *evs, int from, 
             break;
         case ST_TO_NCHW:
             rc = thb_to_nchw(dt, x0, s->N, s->H, s->W, s->C, s->in_ld[0], y, st);
+            break;
+        case ST_FROM_NCHW:
+            rc = thb_from_nchw(dt, x0, s->N, s->H, s->W, s->C, s->in_ld[0], y, s->out_ld, st);
             break;
         case ST_UPSAMPLE:
             rc = thb_upsample2x(dt, x0, s->N, s->H, s->W, s->C, s->in_ld[0], y, s->out_ld, st);

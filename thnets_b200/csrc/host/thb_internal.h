@@ -22,7 +22,8 @@ enum thb_op {
     OP_CMAX,       /* Cmax.c: elementwise maximum of the inputs */
     OP_LOGSOFTMAX, /* LogSoftMax.c */
     OP_NORMALIZE,  /* Normalize.c: x / ||x||_2 per row of a 2-D tensor, over the whole tensor otherwise */
-    OP_UNPOOL      /* SpatialMaxUnpooling.c: in[0] pooled-size values, in[1] the input of the pooling it undoes */
+    OP_UNPOOL,     /* SpatialMaxUnpooling.c: in[0] pooled-size values, in[1] the input of the pooling it undoes */
+    OP_RESHAPE     /* Reshape.c: a vector per image becomes a [C, H, W] map (one-dimensional targets are OP_VIEW) */
 };
 #define THB_MAXIN 16
 
@@ -55,6 +56,8 @@ typedef struct thb_node {
     /* zero padding / slice */
     int pad_l, pad_r, pad_t, pad_b;
     int slice_axis, slice_from, slice_to;
+    /* reshape: the target [C, H, W] and the module's batchMode (-1 absent, 0 false, 1 true) */
+    int reshape[3], batch_mode;
 } thb_node;
 
 typedef struct thb_model {

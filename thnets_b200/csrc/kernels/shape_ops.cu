@@ -55,6 +55,18 @@ __global__ void channel_slice_kernel(const T *__restrict__ x, long pixels, int f
     dt<T>::st(y + p * y_ld + c, c < C ? dt<T>::ld(x + p * x_ld + from + c) : 0.f);
 }
 
+// y[n][p][c] = x[n][c * HW + p]: a vector per image in (channel, row, column) order becomes a channels-innermost map;
+// padded channels of y become 0
+template <typename T>
+__global__ void from_nchw_kernel(const T *__restrict__ x, int x_ld, long images_pixels, long HW, int C, T *__restrict__ y, int y_ld, int y_pad)
+{
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= images_pixels * y_pad) return;
+    const int c = (int)(i % y_pad);
+    const long np = i / y_pad, n = np / HW, p = np % HW;
+    dt<T>::st(y + np * y_ld + c, c < C ? dt<T>::ld(x + n * x_ld + c * HW + p) : 0.f);
+}
+
 struct MaxIn {
     const void *x[8];
     int ld[8];
@@ -238,6 +250,16 @@ int thb_slice_channels(int dtype, const void *x, long pixels, int from, int C, i
     SHAPE_DISPATCH(dtype, (channel_slice_kernel<T><<<nblk(pixels * y_pad), 256, 0, (cudaStream_t)s>>>((const T *)x, pixels, from, C, x_ld,
                                                                                                       (T *)y, y_ld, y_pad)));
     return THB_LAUNCH_CHECK("channel_slice_kernel");
+}
+
+int thb_from_nchw(int dtype, const void *x, int N, int H, int W, int C, int x_ld, void *y, int y_ld, thb_stream s)
+{
+    const int al = dtype == THB_F32 ? 4 : 8, y_pad = (C + al - 1) / al * al;
+    const long HW = (long)H * W;
+    if (N < 1 || C < 1 || HW < 1 || y_pad > y_ld || (long)C * HW > x_ld) return THB_ERR_ARG;
+    SHAPE_DISPATCH(dtype, (from_nchw_kernel<T><<<nblk(N * HW * y_pad), 256, 0, (cudaStream_t)s>>>((const T *)x, x_ld, N * HW, HW, C, (T *)y,
+                                                                                                 y_ld, y_pad)));
+    return THB_LAUNCH_CHECK("from_nchw_kernel");
 }
 
 int thb_cmax(int dtype, int nin, const void *const *x_host, const int *ld_host, long pixels, int C, void *y, int y_ld, thb_stream s)

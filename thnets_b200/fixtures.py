@@ -121,6 +121,10 @@ class Graph:
     def view(self, x, n):
         return self._add("view", [x], dict(sizes=(-1, int(n))))
 
+    def reshape(self, x, c, h, w):
+        """nn.Reshape(c, h, w): the vector of every image becomes a [c, h, w] map"""
+        return self._add("reshape", [x], dict(sizes=(int(c), int(h), int(w))))
+
     def dropout(self, x):
         return self._add("dropout", [x])
 
@@ -317,6 +321,17 @@ class _T7:
         self.i64(arr.size)
         self.f.write(arr.tobytes())
 
+    def long_storage(self, values):
+        """a torch.LongStorage object (8-byte elements): what nn.Reshape keeps its sizes in"""
+        self.i32(4)
+        self.i32(self.idx)
+        self.idx += 1
+        self.string_raw("V 1")
+        self.string_raw("torch.LongStorage")
+        self.i64(len(values))
+        for v in values:
+            self.i64(int(v))
+
     def table(self, items):
         """items: list of (key, writer-callable); string or number keys."""
         self.i32(3)
@@ -366,6 +381,8 @@ def _t7_module(t: _T7, spec):
             items.append((k, (lambda v=v: t.tensor(v))))
         elif isinstance(v, bool):
             items.append((k, (lambda v=v: t.boolean(v))))
+        elif isinstance(v, tuple) and v and v[0] == "longs":
+            items.append((k, (lambda v=v: t.long_storage(v[1]))))
         elif isinstance(v, tuple) and v and v[0] == "ref":
             items.append((k, (lambda v=v: t.reference(t.written[id(v[1])]))))   # a module spec written earlier
         else:
@@ -403,6 +420,10 @@ def graph_to_t7_spec(graph: Graph):
                 count_include_pad=0)))
         elif node.op == "view":
             mods.append(("nn.View", dict(numElements=a["sizes"][1])))
+        elif node.op == "reshape":
+            # as nn.Reshape writes itself: `size`, `batchsize` with a placeholder in front, no batchMode (nil)
+            sz = list(a["sizes"])
+            mods.append(("nn.Reshape", dict(nelement=int(np.prod(sz)), size=("longs", sz), batchsize=("longs", [-1] + sz))))
         elif node.op == "dropout":
             mods.append(("nn.Dropout", dict(p=0.5, v2=True, inplace=False)))
         elif node.op == "softmax":
@@ -591,6 +612,20 @@ def unpool_net(seed=5, size=16, classes=6, zeropad=True):
     x = g.view(x, n)
     x = g.linear(x, n, classes, bias=0.1)
     g.logsoftmax(x)
+    return g
+
+
+def reshape_net(seed=11, size=10, maps=(3, 5, 4)):
+    """conv -> View -> Linear -> Reshape(c, h, w) -> conv: a vector per image turned back into a map (Torch7 route)."""
+    g = Graph(seed)
+    g.input_shape = (3, size, size)
+    x = g.relu(g.conv(0, 3, 4, 3, 2, 1, bias=0.1))
+    n = 4 * (size // 2) * (size // 2)
+    x = g.view(x, n)
+    c, h, w = maps
+    x = g.relu(g.linear(x, n, c * h * w, bias=0.1))
+    x = g.reshape(x, c, h, w)
+    g.conv(x, c, 6, 3, 1, 1, bias=0.1)
     return g
 
 
