@@ -629,6 +629,28 @@ def test_maxpool(lib, G, oracle, dtype, geom):
 
 
 @pytest.mark.parametrize("dtype", [K.THB_F32, K.THB_F16])
+def test_vector_per_image_to_map(lib, G, dtype):
+    """Reshape to [c, h, w] (modules/Reshape.c:22-36): row n of the input holds the map in (channel, row, column) order;
+    the result is channels-innermost with its padded channels zeroed, whatever was in the buffer."""
+    rng = np.random.default_rng(33)
+    n, c, h, w, x_ld = 3, 5, 4, 7, 144
+    x = rng.standard_normal((n, x_ld)).astype(np.float32)
+    td = torch.float32 if dtype == K.THB_F32 else torch.float16
+    xt = torch.from_numpy(x).cuda().to(td)
+    y_ld = G.ru(c, K.ALIGN[dtype]) + K.ALIGN[dtype]          # one more group of channels than the padding: left untouched
+    y = torch.full((n, h, w, y_ld), 7.0, dtype=td, device="cuda")
+    rc = lib.thb_from_nchw(dtype, G.ptr(xt), n, h, w, c, x_ld, G.ptr(y), y_ld, None)
+    torch.cuda.synchronize()
+    assert rc == 0
+    got = y.float().cpu().numpy()
+    ref = xt.float().cpu().numpy()[:, :c * h * w].reshape(n, c, h, w).transpose(0, 2, 3, 1)
+    pad = G.ru(c, K.ALIGN[dtype])
+    assert np.array_equal(got[..., :c], ref)
+    assert np.all(got[..., c:pad] == 0) and np.all(got[..., pad:] == 7.0)
+    assert lib.thb_from_nchw(dtype, G.ptr(xt), n, h, w, c, c * h * w - 1, G.ptr(y), y_ld, None) != 0   # rows shorter than a map
+
+
+@pytest.mark.parametrize("dtype", [K.THB_F32, K.THB_F16])
 @pytest.mark.parametrize("geom", [(7, 7, 0), (3, 2, 1), (2, 2, 0)])
 def test_avgpool(lib, G, oracle, dtype, geom):
     k, s, p = geom

@@ -4,6 +4,7 @@ on the GPU, against the CPU oracle on the same seeded fixture files and inputs.
 The five benchmark architectures run at reduced width / size so that the CPU side finishes in seconds.
 Metric: max|y - ref| / max|ref| per output tensor; fp32 <= 1e-4, fp16/bf16 <= 1e-2; uint8 bit-exact.
 """
+import ctypes as C
 import os
 
 import numpy as np
@@ -260,7 +261,7 @@ def test_pageable_batches_are_staged_through_pinned_memory(th, tmp_path, monkeyp
     assert np.array_equal(outs[0], outs[2]) and np.array_equal(outs[1], outs[3])      # staged == not staged
     assert rel_err(outs[1], outs[0]) < 1e-5     # (sub-batches of 6 and 10 images may take other fp32 tile shapes than 16)
     assert all(np.array_equal(bufs[0], b) for b in bufs[1:])
-    assert not np.array_equal(bufs[0], x)                  # mean 0.45 / std 0.225: normalised in place
+    assert np.array_equal(bufs[0], (x - np.float32(0.45)) / np.float32(0.225))   # normalised in place: thapi.c:396-403
     # byte images that follow one another in ordinary memory take the same route
     h = _load(th, g, "t7", tmp_path, "alexpg2")
     imgs = np.random.default_rng(4).integers(0, 256, (64, 224, 224, 3)).astype(np.uint8)   # 9.6 MB
@@ -270,6 +271,28 @@ def test_pageable_batches_are_staged_through_pinned_memory(th, tmp_path, monkeyp
         got.append(th.process_images(h, list(imgs))[0])
     th.free_network(h)
     assert np.array_equal(got[0], got[1])
+
+
+def test_in_place_normalisation_of_a_page_locked_batch(th, tmp_path):
+    """THProcessFloat leaves (x - mean) / std in the caller's tensor (thapi.c:396-403).  For a batch in page-locked memory
+    the device normalises and the values come back on a stream of their own beside the forward: when the call returns the
+    buffer holds them, and the result equals that of the same batch in ordinary memory."""
+    g = fx.alexnet_owt(width=0.25, size=224, classes=20, fc=64)
+    x = g.make_input(3)                                    # 1.8 MB: below the size from which ordinary memory is staged
+    h = _load(th, g, "t7", tmp_path, "alexpin")
+    p = th.lib.THB200_HostAlloc(C.c_size_t(x.nbytes))
+    assert p
+    pinned = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=x.shape)
+    want = (x - np.float32(0.45)) / np.float32(0.225)
+    for _ in range(3):                                     # direct launches, the capture, a replay
+        pinned[...] = x
+        out, _, _ = th.process_float(h, pinned, copy_input=False)
+        assert np.array_equal(pinned, want)
+        plain = np.array(x, copy=True)
+        out2, _, _ = th.process_float(h, plain, copy_input=False)
+        assert np.array_equal(plain, want) and np.array_equal(out, out2)
+    th.free_network(h)
+    th.lib.THB200_HostFree(C.c_void_p(p))
 
 
 @pytest.mark.parametrize("entry", ["float", "images"])

@@ -82,6 +82,7 @@ def load(libpath: str | None = None):
     lib.thb_minmax_normalized.argtypes = [vp, ci, ci, ci, ci, vp, vp, vp, vp]
     lib.thb_postprocess.argtypes = [vp, ci, ci, ci, ci, ci, ci, cf, cf, vp, vp]
     lib.thb_maxpool.argtypes = [ci, vp] + [ci] * 13 + [vp, ci, vp]
+    lib.thb_from_nchw.argtypes = [ci, vp, ci, ci, ci, ci, ci, vp, ci, vp]
     lib.thb_avgpool.argtypes = [ci, vp] + [ci] * 14 + [vp, ci, vp]
     lib.thb_affine_act.argtypes = [ci, vp, cl, ci, ci, vp, vp, C.POINTER(Act), vp, ci, vp]
     lib.thb_u8_threshold.argtypes = [vp, cl, ci, ci, ci, ci, vp, ci, vp]
