@@ -377,6 +377,48 @@ def test_split_plan_is_for_launches_that_leave_the_machine_idle():
     assert plan(1, 512, 7, 512, 3, x2=1 << 20)[0] == 1
 
 
+def test_tile_width_rules():
+    """thb_conv_geometry picks the output-channel width of a tile on the host: the narrowest of 32 / 64 / 128 that holds
+    the layer's channels; 256 once the reduction is at least four K blocks long, every SM gets a tile and the padding is
+    not increased by it; 64 where wide tiles would leave most SMs without work; 32 for a Linear proper of few rows.  The
+    padded extents follow from it; fp32 always works on 64 columns; a width set by the caller is kept."""
+    from thnets_b200 import kernels_abi as K
+    lib = K.load()
+
+    def geom(n, cin, hw, cout, k, dtype=K.THB_F16, bn=0):
+        d = K.ConvDesc()
+        d.dtype = dtype
+        d.N, d.H, d.W, d.Cin, d.Cout = n, hw, hw, cin, cout
+        d.kH = d.kW = k
+        d.dH = d.dW = 1
+        d.padH = d.padW = k // 2
+        d.oH = d.oW = hw
+        d.in_ld = cin
+        d.BN = bn
+        assert lib.thb_conv_geometry(C.byref(d)) == 0
+        return d
+
+    assert geom(4, 64, 56, 24, 3).BN == 32
+    assert geom(4, 64, 56, 64, 3).BN == 64
+    assert geom(4, 64, 56, 128, 1).BN == 128
+    assert geom(256, 256, 14, 1024, 1).BN == 256            # 392 pixel tiles, K = 4 blocks
+    assert geom(256, 64, 56, 256, 1).BN == 128              # one K block: the epilogue outweighs the reduction
+    assert geom(256, 512, 7, 512, 3).BN == 256              # 98 x 2 wide tiles: every SM still gets one
+    assert geom(64, 512, 7, 512, 3).BN == 128               # 25 x 2 wide tiles would leave SMs idle
+    assert geom(256, 256, 14, 384, 3).BN == 128             # 384 channels pad to 512 on wide tiles
+    assert geom(1, 256, 13, 256, 3).BN == 64                # 2 pixel tiles x 2: narrower tiles for more SMs
+    d = geom(256, 2048, 1, 1000, 1)
+    assert d.BN == 32 and d.Cout_pad == 1024                # a Linear on 256 rows
+    assert geom(256, 256, 14, 1024, 1, bn=128).BN == 128    # the caller's choice stands
+    d = geom(4, 3, 224, 64, 3, dtype=K.THB_F32)
+    assert d.BN == 64 and d.Cin_pad == 4 and d.Ktot_pad == 48
+    d = geom(4, 100, 14, 130, 3, dtype=K.THB_U8)
+    assert d.Cin_pad == 112 and d.Ktot_pad == 1024 and d.Cout_pad % d.BN == 0 and d.Cout_pad >= 130
+    bad = K.ConvDesc()
+    bad.dtype = K.THB_F16
+    assert lib.thb_conv_geometry(C.byref(bad)) != 0          # no kernel extent
+
+
 def test_patch_kernel_eligibility_rules():
     """thb_conv_patch_supported / thb_conv_maxpool_supported decide on the host which convolutions the patch kernel takes:
     16-bit types, stride 1, at most 64 output channels on 64-column tiles, 16 or 64 stored input channels, kernels up to
