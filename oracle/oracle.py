@@ -324,7 +324,9 @@ class Oracle:
             elif node.op == "bn":
                 y = self.batchnorm(x, ts[0], ts[1], ts[2], ts[3], a["eps"])
             elif node.op == "threshold":
-                y = self.threshold(x, a["threshold"], a["value"])
+                y = self.threshold(x, a["threshold"], a["value"], a.get("alpha", 0.0))
+            elif node.op == "prelu":
+                y = self.prelu(x, ts[0], a["planes"])
             elif node.op == "maxpool":
                 y = self.maxpool(x, a["kernel_size"], a["stride"], a["padding"], a["ceil_mode"])
             elif node.op == "avgpool":

@@ -267,6 +267,20 @@ def test_batch_slicing(th):
             assert covered == list(range(n))
 
 
+def test_onnx_reader_leaky_and_prelu(th, tmp_path):
+    """ONNX LeakyRelu becomes a Threshold record with the node's alpha (onnx.cc:36, Threshold.c:30-35), PRelu a PReLU with
+    one slope per plane taken from the second input (onnx.cc:35, PReLU.c:21-29); both lower to activations."""
+    g = fx.prelu_net(onnx_form=True)
+    p = str(tmp_path / "prelu.onnx")
+    fx.write_onnx(g, p)
+    h = th.load_network(p)
+    assert h, th.lib.THB200_LastErrorString()
+    lines = describe(th, h)
+    kinds = [ln.split("kind=")[1].split()[0] for ln in lines if " act " in ln]
+    assert kinds == ["3", "2", "3"], lines            # PReLU, leaky, PReLU
+    th.free_network(h)
+
+
 def test_reshape_lowering(th, tmp_path):
     """nn.Reshape to three dimensions lowers to an operator of its own with the target map; to one dimension it is a View"""
     g = fx.reshape_net()

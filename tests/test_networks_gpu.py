@@ -609,13 +609,19 @@ def test_lowp_first_convolution_15x15_stride_2(th, oracle, tmp_path):
                                   ("reshape_b1", lambda: fx.reshape_net(), "t7", 1, 0),
                                   ("reshape_b3", lambda: fx.reshape_net(), "t7", 3, 0),
                                   ("reshape_b3_fp16", lambda: fx.reshape_net(), "t7", 3, 1),
+                                  ("prelu_b1", lambda: fx.prelu_net(), "t7", 1, 0),
+                                  ("prelu_b3", lambda: fx.prelu_net(), "t7", 3, 0),
+                                  ("prelu_b3_fp16", lambda: fx.prelu_net(), "t7", 3, 1),
+                                  ("prelu_leaky_onnx_b3", lambda: fx.prelu_net(onnx_form=True), "onnx", 3, 0),
+                                  ("prelu_leaky_onnx_b3_fp16", lambda: fx.prelu_net(onnx_form=True), "onnx", 3, 1),
                                   ("cmax_slice_b4", lambda: fx.cmax_slice_net(), "py", 4, 0),
                                   ("cmax_slice_b4_fp16", lambda: fx.cmax_slice_net(), "py", 4, 1),
                                   ("onnx_ops_b3", lambda: fx.onnx_ops_net(), "onnx", 3, 0),
                                   ("onnx_ops_b1", lambda: fx.onnx_ops_net(), "onnx", 1, 0)], ids=lambda c: c[0])
 def test_remaining_operators(th, oracle, tmp_path, case):
     """SpatialZeroPadding, SpatialMaxUnpooling (positions recomputed from the pooling's input), LogSoftMax (with the
-    reference's first-frame quirk), Normalize, Reshape to a [c, h, w] map (with and without a batch dimension), Cmax,
+    reference's first-frame quirk), Normalize, Reshape to a [c, h, w] map (with and without a batch dimension), PReLU (a
+    slope per channel, one shared slope, on maps and on vectors) and the leaky Threshold an ONNX LeakyRelu makes, Cmax,
     Slice along every dimension and Upsample, through the three loaders,
     against the oracle functions that are pinned to the live reference."""
     name, build, kind, batch, mode = case

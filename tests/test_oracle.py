@@ -231,6 +231,34 @@ def test_reshape_against_the_live_reference(oracle, tmp_path, batch):
     assert np.abs(out - ref.ravel()).max() / np.abs(ref).max() < 2e-5
 
 
+@pytest.mark.parametrize("batch", [1, 3])
+def test_prelu_against_the_live_reference(oracle, tmp_path, batch):
+    """nn.PReLU (modules/PReLU.c:32-92) with a slope per plane on a map, with one shared slope, and per feature on the
+    2-D (batch) or 1-D (one image) tensor behind a Linear, against the unmodified reference on the same Torch7 file."""
+    from oracle.oracle import ref_lib
+    from thnets_b200 import fixtures as fx
+    from thnets_b200.capi import THNets
+    if ref_lib() is None:
+        pytest.skip("reference library not built")
+    g = fx.prelu_net()
+    d = str(tmp_path / "prelu")
+    fx.write_torch7(g, d)
+    th = THNets(ref_lib())
+    h = th.load_network(d)
+    x = g.make_input(batch)
+    out, _, _ = th.process_float(h, x)
+    ref = oracle.run(g, x)
+    assert out.size == ref.size == batch * 5
+    assert np.abs(out - ref.ravel()).max() / np.abs(ref).max() < 2e-5
+
+
+def test_leaky_threshold_restatement(oracle):
+    """Threshold.c:55-57: with alpha set the module computes x >= 0 ? x : alpha * x and ignores threshold and value"""
+    x = np.array([-2.0, -0.0, 0.0, 0.5, 3.0], np.float32)
+    assert np.array_equal(oracle.threshold(x, 1.0, 7.0, 0.25), np.array([-0.5, 0.0, 0.0, 0.5, 3.0], np.float32))
+    assert np.array_equal(oracle.threshold(x, 1.0, 7.0, 0.0), np.array([7.0, 7.0, 7.0, 7.0, 3.0], np.float32))
+
+
 def test_cmax_slice_against_the_live_reference(oracle, tmp_path):
     from oracle.oracle import ref_lib
     from thnets_b200 import fixtures as fx

@@ -368,6 +368,11 @@ void thb_build_py_module(const char *fname, struct pyfunction *f)
         m->Threshold.threshold = fval(p, "threshold", 0);
         m->Threshold.val = fval(p, "value", 0);
         m->Threshold.inplace = ival(p, "inplace", 0);
+        m->Threshold.alpha = fval(p, "alpha", 0);    /* the ONNX reader's LeakyRelu only (Threshold.c:30-35) */
+    } else if (!strcmp(op, "PReLU")) {               /* the ONNX reader only (onnx.cc:35, PReLU.c:21-29) */
+        m->type = MT_PReLU;
+        m->PReLU.weight = param_tensor(p, "", 0);
+        m->PReLU.nOutputPlane = m->PReLU.weight ? (int)m->PReLU.weight->size[0] : 0;
     } else if (!strcmp(op, "Dropout")) {
         m->type = MT_Dropout;
         m->Dropout.inplace = 1; m->Dropout.v2 = 1; m->Dropout.p = 0;

@@ -623,6 +623,20 @@ static struct pyelement *ox_value(ox_build *b, const char *name)
         par_float(&e->function, "threshold", 0.f);
         par_float(&e->function, "value", 0.f);
         par_int(&e->function, "inplace", 0);
+    } else if (!strcmp(op, "LeakyRelu")) {
+        /* onnx.cc:36, Threshold.c:30-35: a Threshold record with the node's alpha -- 0 when the attribute is absent, which
+         * makes it a ReLU (Threshold.c:55-60), not the 0.01 the operator's specification gives */
+        if (!(e = ox_function(b, idx, "Threshold", (const char *const *)&n->in[0], 1))) return 0;
+        par_float(&e->function, "threshold", 0.f);
+        par_float(&e->function, "value", 0.f);
+        par_int(&e->function, "inplace", 0);
+        par_float(&e->function, "alpha", ox_float(n, "alpha", 0.f));
+    } else if (!strcmp(op, "PRelu")) {
+        /* onnx.cc:35, PReLU.c:21-29: the slopes are the second input, one per plane: its first dimension */
+        const ox_tensor *w = n->nin > 1 ? ox_init(g, n->in[1]) : 0;
+        if (!w || w->data_type != 1 || w->ndims < 1 || w->count < w->dims[0]) { ox_fail(b, "PRelu %s needs a constant slope tensor", n->out[0]); return 0; }
+        if (!(e = ox_function(b, idx, "PReLU", (const char *const *)&n->in[0], 1))) return 0;
+        par_tensor(&e->function, "", w->f, &w->dims[0], 1);
     } else if (!strcmp(op, "Dropout") || !strcmp(op, "Identity"))
         e = ox_function(b, idx, "Dropout", (const char *const *)&n->in[0], 1);
     else if (!strcmp(op, "Softmax") || !strcmp(op, "Sigmoid") || !strcmp(op, "Tanh") || !strcmp(op, "LogSoftmax"))

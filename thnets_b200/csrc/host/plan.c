@@ -396,14 +396,16 @@ static int fill_act(planner *P, thb_act *a, const thb_node *n, int C)
     a->alpha = n->act_alpha;
     a->slope = 0;
     if (n->act_kind == THB_ACT_PRELU) {
-        float *tmp = malloc(sizeof(float) * C);
-        if (n->nslope && n->nslope != C) {
+        /* the kernels read per-channel arrays in 16-byte groups and per 64-column block: a multiple of 64 floats */
+        const int padded = ru(C, 64);
+        float *tmp = calloc(padded, sizeof(float));
+        if (!tmp || (n->nslope && n->nslope != C)) {
             free(tmp);
             thb_set_error("wrong number of input planes for PReLU (%d slopes, %d channels)", n->nslope, C);
             return -1;
         }
         for (int i = 0; i < C; i++) tmp[i] = n->nslope ? n->slope[i] : n->slope[0];
-        a->slope = dupload(P->I, tmp, sizeof(float) * C);
+        a->slope = dupload(P->I, tmp, sizeof(float) * padded);
         free(tmp);
         if (!a->slope) return -1;
     }

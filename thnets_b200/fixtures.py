@@ -109,6 +109,15 @@ class Graph:
     def relu(self, x, threshold=0.0, value=0.0):
         return self._add("threshold", [x], dict(threshold=float(threshold), value=float(value), inplace=0))
 
+    def leaky(self, x, alpha):
+        """x >= 0 ? x : alpha * x -- a Threshold record with `alpha` set (Threshold.c:55-57), which only an ONNX LeakyRelu makes"""
+        return self._add("threshold", [x], dict(threshold=0.0, value=0.0, inplace=0, alpha=float(alpha)))
+
+    def prelu(self, x, channels, shared=False):
+        """nn.PReLU: one slope per channel, or one for all (nOutputPlane = 0)"""
+        w = (0.05 + 0.4 * self.rng.random(1 if shared else channels)).astype(np.float32)
+        return self._add("prelu", [x], dict(planes=0 if shared else int(channels)), [("weight", w)])
+
     def maxpool(self, x, k, stride, pad=0, ceil_mode=0):
         return self._add("maxpool", [x], dict(kernel_size=(k, k), stride=(stride, stride),
                                              padding=(pad, pad), ceil_mode=int(ceil_mode)))
@@ -218,6 +227,8 @@ def write_pymodel(graph: Graph, path: str):
                 f.write(b"\x07" + struct.pack("<i", i))
                 return
             emitted.add(i)
+            if node.op not in _PYNAME or node.attrs.get("alpha"):
+                raise ValueError("no graph-dump form for " + node.op)
             f.write(b"\x02" + struct.pack("<i", i))
             _w_str(f, "torch.nn.fn." + _PYNAME[node.op])
             attrs = node.attrs
@@ -408,7 +419,11 @@ def graph_to_t7_spec(graph: Graph):
         elif node.op == "linear":
             mods.append(("nn.Linear", dict(weight=ts[0], bias=ts[1])))
         elif node.op == "threshold":
+            if a.get("alpha"):
+                raise ValueError("no Torch7 mapping for a leaky threshold")
             mods.append(("nn.Threshold", dict(threshold=a["threshold"], val=a["value"], inplace=False)))
+        elif node.op == "prelu":
+            mods.append(("nn.PReLU", dict(nOutputPlane=a["planes"], weight=ts[0])))
         elif node.op == "maxpool":
             mods.append(("nn.SpatialMaxPooling", dict(
                 padW=a["padding"][1], padH=a["padding"][0], dW=a["stride"][1], dH=a["stride"][0],
@@ -629,6 +644,22 @@ def reshape_net(seed=11, size=10, maps=(3, 5, 4)):
     return g
 
 
+def prelu_net(seed=12, size=12, onnx_form=False):
+    """conv -> PReLU (a slope per channel) -> conv -> PReLU with one shared slope (Torch7) or a leaky threshold (an ONNX
+    LeakyRelu) -> max pooling -> View -> Linear -> PReLU per feature on the 2-D (batch) or 1-D (one image) tensor -> Linear."""
+    g = Graph(seed)
+    g.input_shape = (3, size, size)
+    x = g.prelu(g.conv(0, 3, 8, 3, 1, 1, bias=0.1), 8)
+    x = g.conv(x, 8, 12, 3, 1, 1, bias=0.1)
+    x = g.leaky(x, 0.2) if onnx_form else g.prelu(x, 12, shared=True)
+    x = g.maxpool(x, 2, 2)
+    n = 12 * (size // 2) * (size // 2)
+    x = g.view(x, n)
+    x = g.prelu(g.linear(x, n, 16, bias=0.1), 16)
+    g.linear(x, 16, 5, bias=0.1)
+    return g
+
+
 def normalize_net(seed=6, size=12, feat=10):
     """conv -> View -> Linear -> Normalize (rows of a 2-D tensor for a batch, the whole tensor for one image)."""
     g = Graph(seed)
@@ -777,7 +808,14 @@ def write_onnx(graph: Graph, path: str, bias_as_add=False, pad_nodes=False):
         elif nd.op == "threshold":
             if a["threshold"] != 0 or a["value"] != 0:
                 raise ValueError("only ReLU maps onto ONNX here")
-            node("Relu", ins, out)
+            if a.get("alpha"):
+                node("LeakyRelu", ins, out, alpha=float(a["alpha"]))
+            else:
+                node("Relu", ins, out)
+        elif nd.op == "prelu":
+            if not a["planes"]:
+                raise ValueError("one shared slope has no ONNX form the reference accepts (PReLU.c:21-29 takes the tensor's length as the plane count)")
+            node("PRelu", [ins[0], init(out + "_slope", ts[0].reshape(-1, 1, 1))], out)
         elif nd.op in ("maxpool", "avgpool"):
             extra = dict(ceil_mode=int(a["ceil_mode"])) if a["ceil_mode"] else {}
             node("MaxPool" if nd.op == "maxpool" else "AveragePool", ins, out, kernel_shape=list(a["kernel_size"]),
