@@ -281,6 +281,30 @@ def test_onnx_reader_leaky_and_prelu(th, tmp_path):
     th.free_network(h)
 
 
+def test_onnx_reader_whole_map_average(th, tmp_path):
+    """GlobalAveragePool and ReduceMean over axes (2, 3) both become an average pooling with kernel 0 -- the whole map
+    (onnx.cc:49-50, SpatialAveragePooling.c:47-67, :116-119) -- which the planner sizes to its input, so the launch is the
+    one an AveragePool with the map's extent gets; ReduceMean over other axes is refused as by the reference."""
+    g = fx.resnet18(width=0.125, size=32, classes=5)
+    lines = {}
+    for how in (None, "GlobalAveragePool", "ReduceMean"):
+        p = str(tmp_path / ("r18_%s.onnx" % how))
+        fx.write_onnx(g, p, global_pool=how)
+        h = th.load_network(p)
+        assert h, th.lib.THB200_LastErrorString()
+        lines[how] = describe(th, h)
+        th.free_network(h)
+    pools = {how: [ln for ln in ls if " avgpool " in ln] for how, ls in lines.items()}
+    assert len(pools[None]) == 1 and " k1x1 " in pools[None][0]            # a 32 x 32 input leaves a 1 x 1 map
+    assert pools["GlobalAveragePool"] == pools["ReduceMean"] and " k0x0 s1,1 p0,0" in pools["ReduceMean"][0]
+    strip = lambda ls: [ln for ln in ls if " avgpool " not in ln]
+    assert strip(lines[None]) == strip(lines["ReduceMean"]) == strip(lines["GlobalAveragePool"])
+    p = str(tmp_path / "r18_bad.onnx")
+    fx.write_onnx(g, p, global_pool=("ReduceMean", [1]))
+    assert not th.lib.THLoadNetwork(p.encode())
+    assert b"ReduceMean along channel" in th.lib.THB200_LastErrorString()
+
+
 def test_reshape_lowering(th, tmp_path):
     """nn.Reshape to three dimensions lowers to an operator of its own with the target map; to one dimension it is a View"""
     g = fx.reshape_net()

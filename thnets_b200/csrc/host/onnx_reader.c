@@ -606,9 +606,17 @@ static struct pyelement *ox_value(ox_build *b, const char *name)
         par_tensor(&e->function, "", wd, dims, 2);
         free(wd);
         if (bias && bias->count >= dims[0] && ox_float(n, "beta", 1.f) != 0.f) par_tensor(&e->function, "", bias->f, &dims[0], 1);
-    } else if (!strcmp(op, "MaxPool") || !strcmp(op, "AveragePool") || !strcmp(op, "GlobalAveragePool")) {
+    } else if (!strcmp(op, "MaxPool") || !strcmp(op, "AveragePool") || !strcmp(op, "GlobalAveragePool") || !strcmp(op, "ReduceMean")) {
         int kH = 0, kW = 0, dH = 1, dW = 1, padH = 0, padW = 0;
-        if (strcmp(op, "GlobalAveragePool")) {
+        if (!strcmp(op, "ReduceMean")) {
+            /* onnx.cc:50, SpatialAveragePooling.c:47-51: the mean over rows and columns is an average pooling over the
+             * whole map (no kernel_shape: kernel 0); any other axes are refused with the reference's message */
+            const ox_attr *ax = ox_attr_of(n, "axes");
+            if (ax && !(ax->nints == 0 || (ax->nints == 2 && ax->ints[0] == 2 && ax->ints[1] == 3))) {
+                ox_fail(b, "ReduceMean along channel is not supported (%s)", n->out[0]);
+                return 0;
+            }
+        } else if (strcmp(op, "GlobalAveragePool")) {
             ox_ints2(n, "kernel_shape", 0, 1, &kH, &kW);
             ox_ints2(n, "strides", 0, 1, &dH, &dW);
             ox_ints2(n, "pads", 0, 0, &padH, &padW);

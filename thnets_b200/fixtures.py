@@ -756,13 +756,15 @@ def _onnx_attr(name, v):
     return out + b"".join(_pb_int(8, i) for i in v) + _pb_int(20, 7)
 
 
-def write_onnx(graph: Graph, path: str, bias_as_add=False, pad_nodes=False):
+def write_onnx(graph: Graph, path: str, bias_as_add=False, pad_nodes=False, global_pool=None):
     """Serialise `graph` as an ONNX ModelProto with a hand-written protobuf encoder (no onnx package needed).
 
     conv -> Conv, deconv -> ConvTranspose, linear -> Gemm(transB=1), bn -> BatchNormalization, threshold(0, 0) -> Relu,
     maxpool -> MaxPool, avgpool -> AveragePool, view -> Flatten, add -> Add, concat -> Concat, softmax -> Softmax,
     dropout -> Dropout.  bias_as_add writes a convolution's bias as a separate Add of a constant; pad_nodes writes its
-    padding as a Pad node in front of it (two shapes the reference's loader folds back, onnx.cc:605-700).
+    padding as a Pad node in front of it (two shapes the reference's loader folds back, onnx.cc:605-700).  global_pool
+    ("GlobalAveragePool", "ReduceMean" or ("ReduceMean", axes)) writes every average pooling as that operator over the
+    whole map -- for graphs whose average poolings cover their whole input.
     """
     nodes, inits = [], []
 
@@ -816,6 +818,12 @@ def write_onnx(graph: Graph, path: str, bias_as_add=False, pad_nodes=False):
             if not a["planes"]:
                 raise ValueError("one shared slope has no ONNX form the reference accepts (PReLU.c:21-29 takes the tensor's length as the plane count)")
             node("PRelu", [ins[0], init(out + "_slope", ts[0].reshape(-1, 1, 1))], out)
+        elif nd.op == "avgpool" and global_pool:
+            if global_pool == "GlobalAveragePool":
+                node("GlobalAveragePool", ins, out)
+            else:
+                axes = global_pool[1] if isinstance(global_pool, tuple) else [2, 3]
+                node("ReduceMean", ins, out, axes=list(axes), keepdims=1)
         elif nd.op in ("maxpool", "avgpool"):
             extra = dict(ceil_mode=int(a["ceil_mode"])) if a["ceil_mode"] else {}
             node("MaxPool" if nd.op == "maxpool" else "AveragePool", ins, out, kernel_shape=list(a["kernel_size"]),
